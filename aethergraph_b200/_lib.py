@@ -1,0 +1,137 @@
+"""ctypes binding of libaethergpu.so (the CUDA kernels behind the C ABI).
+
+There is no fallback of any kind: if the shared library is missing or cannot be
+loaded this module raises, and every compute entry point fails loudly when no
+CUDA device is usable.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libaethergpu.so")
+
+AG_OK, AG_ERR_VALUE, AG_ERR_LOAD, AG_ERR_SAMPLING, AG_ERR_TIMEOUT, AG_ERR_WORKER, AG_ERR_CUDA, \
+    AG_ERR_SHUTDOWN = range(8)
+AG_MEM_HOST, AG_MEM_DEVICE = 0, 1
+AG_F32, AG_F16, AG_BF16 = 0, 1, 2
+DTYPE_TAG = {"f32": AG_F32, "f16": AG_F16, "bf16": AG_BF16}
+DTYPE_NAME = {v: k for k, v in DTYPE_TAG.items()}
+VALIDATION = {"auto": 0, "header_only": 1, "offsets_only": 2, "full": 3}
+AG_RNG_WYRAND_EXACT, AG_RNG_PHILOX = 0, 1
+RNG_MODE = {"wyrand_exact": AG_RNG_WYRAND_EXACT, "philox": AG_RNG_PHILOX,
+            "philox_fast": AG_RNG_PHILOX}
+AG_MAX_HOPS = 8
+
+
+class GraphLoadError(Exception):
+    """Raised when graph loading fails."""
+
+
+class SamplingError(Exception):
+    """Raised when sampling fails."""
+
+
+class SamplingConfigC(C.Structure):
+    _fields_ = [("num_hops", C.c_uint32), ("fanout", C.c_uint32 * AG_MAX_HOPS),
+                ("replace", C.c_int32), ("weighted", C.c_int32), ("track_edge_ids", C.c_int32),
+                ("seed", C.c_uint64), ("rng_mode", C.c_int32), ("max_seeds", C.c_uint32)]
+
+
+class SubgraphBuffers(C.Structure):
+    _fields_ = [("cap_nodes", C.c_uint64), ("cap_edges", C.c_uint64), ("cap_seeds", C.c_uint64),
+                ("nodes", C.c_void_p), ("edge_src", C.c_void_p), ("edge_dst", C.c_void_p),
+                ("edge_ids", C.c_void_p), ("src_local", C.c_void_p), ("dst_local", C.c_void_p),
+                ("seed_locals", C.c_void_p), ("n_id", C.c_void_p),
+                ("edge_index_local", C.c_void_p), ("e_id", C.c_void_p),
+                ("seed_index", C.c_void_p), ("x", C.c_void_p)]
+
+
+class SampleCounts(C.Structure):
+    _fields_ = [("num_nodes", C.c_uint32), ("num_edges", C.c_uint32), ("num_seeds", C.c_uint32),
+                ("num_hops", C.c_uint32), ("nodes_per_hop", C.c_uint32 * (AG_MAX_HOPS + 1)),
+                ("edges_per_hop", C.c_uint32 * AG_MAX_HOPS), ("draws", C.c_uint64),
+                ("error", C.c_uint32), ("reserved", C.c_uint32)]
+
+
+_P = C.c_void_p
+_PP = C.POINTER(C.c_void_p)
+_U64P = C.POINTER(C.c_uint64)
+_I32P = C.POINTER(C.c_int32)
+
+# name -> (restype, argtypes).  Every symbol include/aethergpu.h declares.
+SIGNATURES = {
+    "ag_last_error": (C.c_char_p, []),
+    "ag_abi_version": (C.c_int32, []),
+    "ag_batch_seed": (C.c_uint64, [C.c_uint64, C.c_uint64]),
+    "ag_graph_load": (C.c_int32, [C.c_char_p, C.c_int32, C.c_int32, _PP]),
+    "ag_graph_from_csr": (C.c_int32, [C.c_uint64, C.c_uint64, _P, _P, _P, C.c_int32, C.c_int32, _PP]),
+    "ag_graph_adopt_device_csr": (C.c_int32, [C.c_uint64, C.c_uint64, _P, _P, _P, C.c_int32, _PP]),
+    "ag_graph_from_edges": (C.c_int32, [C.c_uint64, _P, _P, _P, C.c_uint64, C.c_int32, _PP]),
+    "ag_graph_save": (C.c_int32, [_P, C.c_char_p]),
+    "ag_graph_info": (C.c_int32, [_P, _U64P, _U64P, _I32P, _I32P]),
+    "ag_graph_device_ptrs": (C.c_int32, [_P, _PP, _PP, _PP]),
+    "ag_graph_degrees": (C.c_int32, [_P, _P, C.c_uint64, _P]),
+    "ag_graph_neighbors": (C.c_int32, [_P, C.c_uint32, _P, _P, C.c_uint64, _U64P]),
+    "ag_graph_free": (None, [_P]),
+    "ag_features_save": (C.c_int32, [C.c_char_p, _P, C.c_uint64, C.c_uint64, C.c_int32]),
+    "ag_features_load": (C.c_int32, [C.c_char_p, C.c_int32, _PP]),
+    "ag_features_load_range": (C.c_int32, [C.c_char_p, C.c_int32, C.c_uint64, C.c_uint64, _PP]),
+    "ag_features_from_memory": (C.c_int32, [_P, C.c_uint64, C.c_uint64, C.c_int32, C.c_int32, C.c_int32, _PP]),
+    "ag_features_from_f32": (C.c_int32, [_P, C.c_uint64, C.c_uint64, C.c_int32, C.c_int32, C.c_int32, _PP]),
+    "ag_features_adopt_device": (C.c_int32, [_P, C.c_uint64, C.c_uint64, C.c_int32, C.c_int32, _PP]),
+    "ag_features_info": (C.c_int32, [_P, _U64P, _U64P, _I32P, _I32P, _U64P]),
+    "ag_features_device_ptr": (C.c_int32, [_P, _PP]),
+    "ag_features_get_batch": (C.c_int32, [_P, _P, C.c_uint64, _P]),
+    "ag_gather": (C.c_int32, [_P, _P, C.c_int32, C.c_uint64, _P, _P, _P]),
+    "ag_features_check": (C.c_int32, [_P]),
+    "ag_features_free": (None, [_P]),
+    "ag_sampler_create": (C.c_int32, [_P, C.POINTER(SamplingConfigC), _PP]),
+    "ag_sampler_reseed": (C.c_int32, [_P, C.c_uint64]),
+    "ag_sampler_bounds": (C.c_int32, [_P, C.c_uint64, _U64P, _U64P]),
+    "ag_sample_into": (C.c_int32, [_P, _P, C.c_uint64, C.c_int32, _P, C.POINTER(SubgraphBuffers), _P]),
+    "ag_sample_wait": (C.c_int32, [_P, C.POINTER(SampleCounts)]),
+    "ag_sample": (C.c_int32, [_P, _P, C.c_uint64, _P, C.c_int32, C.POINTER(SubgraphBuffers), _P]),
+    "ag_subgraph_release": (C.c_int32, [_P, C.POINTER(SubgraphBuffers)]),
+    "ag_sampler_free": (None, [_P]),
+}
+
+_lib = None
+
+
+def lib():
+    """The loaded library.  Raises if it was never built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m aethergraph_b200.build`. "
+                "aethergraph_b200 has no CPU or PyTorch fallback.")
+        L = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(L, name)  # AttributeError if the .so lacks a declared symbol
+            fn.restype = res
+            fn.argtypes = args
+        _lib = L
+    return _lib
+
+
+def last_error() -> str:
+    return lib().ag_last_error().decode(errors="replace")
+
+
+def check(status: int) -> None:
+    """Raise the exception class the reference raises for this status."""
+    if status == AG_OK:
+        return
+    msg = last_error()
+    if status == AG_ERR_VALUE:
+        raise ValueError(msg)
+    if status == AG_ERR_LOAD:
+        raise GraphLoadError(msg)
+    if status == AG_ERR_SAMPLING:
+        raise SamplingError(msg)
+    if status == AG_ERR_TIMEOUT:
+        raise TimeoutError(msg)
+    raise RuntimeError(msg)

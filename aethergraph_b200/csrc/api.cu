@@ -1,0 +1,720 @@
+// C ABI: error plumbing, graph handles (AETH v1 files, CSR in HBM) and feature
+// store handles (AETHFEAT files, payload in HBM).
+#include <errno.h>
+#include <fcntl.h>
+#include <stdarg.h>
+#include <string.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <algorithm>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+#include "internal.h"
+
+namespace ag {
+
+static thread_local char g_error[1024] = "";
+
+void set_error(const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof g_error, fmt, ap);
+    va_end(ap);
+}
+
+int32_t fail(int32_t status, const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof g_error, fmt, ap);
+    va_end(ap);
+    return status;
+}
+
+namespace {
+
+// CRC32 (IEEE), the integrity checksum of the AETH body
+// (reference: internal/mmap.rs:642-652).
+uint32_t crc32_update(uint32_t crc, const void *data, size_t len) {
+    static uint32_t table[8][256];
+    static bool ready = false;
+    if (!ready) {
+        for (uint32_t i = 0; i < 256; ++i) {
+            uint32_t c = i;
+            for (int k = 0; k < 8; ++k) c = (c & 1u) ? 0xEDB88320u ^ (c >> 1) : c >> 1;
+            table[0][i] = c;
+        }
+        for (uint32_t i = 0; i < 256; ++i)
+            for (int t = 1; t < 8; ++t) table[t][i] = table[0][table[t - 1][i] & 0xFF] ^ (table[t - 1][i] >> 8);
+        ready = true;
+    }
+    const uint8_t *p = (const uint8_t *)data;
+    crc = ~crc;
+    while (len >= 8) {  // slicing-by-8
+        uint32_t a, b;
+        memcpy(&a, p, 4); memcpy(&b, p + 4, 4);
+        a ^= crc;
+        crc = table[7][a & 0xFF] ^ table[6][(a >> 8) & 0xFF] ^ table[5][(a >> 16) & 0xFF] ^ table[4][a >> 24] ^
+              table[3][b & 0xFF] ^ table[2][(b >> 8) & 0xFF] ^ table[1][(b >> 16) & 0xFF] ^ table[0][b >> 24];
+        p += 8; len -= 8;
+    }
+    while (len--) crc = table[0][(crc ^ *p++) & 0xFF] ^ (crc >> 8);
+    return ~crc;
+}
+
+__global__ void k_validate_csr(const uint64_t *offsets, const uint32_t *dst, uint64_t n, uint64_t e,
+                               uint64_t dst_bound, uint32_t *flag) {
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (tid == 0) {
+        if (offsets[0] != 0) atomicOr(flag, 1u);
+        if (offsets[n] != e) atomicOr(flag, 2u);
+    }
+    for (uint64_t i = tid; i < n; i += stride)
+        if (offsets[i] > offsets[i + 1]) atomicOr(flag, 4u);
+    if (dst)
+        for (uint64_t i = tid; i < e; i += stride)
+            if ((uint64_t)dst[i] >= dst_bound) atomicOr(flag, 8u);
+}
+
+__global__ void k_degrees(const uint64_t *offsets, uint64_t num_nodes, const uint32_t *ids, uint64_t n,
+                          uint32_t *out) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t v = ids ? ids[i] : i;
+        uint64_t d = 0;
+        if (v < num_nodes) {
+            const uint64_t a = offsets[v], b = offsets[v + 1];
+            d = b >= a ? b - a : 0;
+        }
+        out[i] = (uint32_t)std::min<uint64_t>(d, 0xFFFFFFFFull);
+    }
+}
+
+int grid_for(uint64_t n) {
+    const uint64_t b = (n + 255) / 256;
+    return (int)std::max<uint64_t>(1, std::min<uint64_t>(b, (uint64_t)kSMs * 8));
+}
+
+}  // namespace
+
+cudaError_t launch_validate_csr(const uint64_t *offsets, const uint32_t *dst, uint64_t n, uint64_t e,
+                                uint64_t dst_bound, uint32_t *flag_dev, cudaStream_t st) {
+    k_validate_csr<<<grid_for(std::max(n, e)), 256, 0, st>>>(offsets, dst, n, e, dst_bound, flag_dev);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_degrees(const uint64_t *offsets, uint64_t num_nodes, const uint32_t *ids, uint64_t n,
+                           uint32_t *out, cudaStream_t st) {
+    if (n == 0) return cudaSuccess;
+    k_degrees<<<grid_for(n), 256, 0, st>>>(offsets, num_nodes, ids, n, out);
+    return cudaGetLastError();
+}
+
+namespace {
+
+int32_t validate_on_device(const ag_graph *g, bool check_dst) {
+    uint32_t *flag = nullptr;
+    AG_CUDA(cudaMalloc(&flag, 4));
+    cudaMemset(flag, 0, 4);
+    cudaError_t e = launch_validate_csr(g->offsets, check_dst ? g->dst : nullptr, g->num_nodes, g->num_edges,
+                                        g->num_nodes, flag, 0);
+    uint32_t h = 0;
+    if (e == cudaSuccess) e = cudaMemcpy(&h, flag, 4, cudaMemcpyDeviceToHost);
+    cudaFree(flag);
+    if (e != cudaSuccess) return fail(AG_ERR_CUDA, "CSR validation failed to run: %s", cudaGetErrorString(e));
+    if (h & 1u) return fail(AG_ERR_LOAD, "invalid CSR: offsets[0] != 0");
+    if (h & 2u) return fail(AG_ERR_LOAD, "invalid CSR: offsets[num_nodes] != num_edges");
+    if (h & 4u) return fail(AG_ERR_LOAD, "invalid CSR: offsets are not non-decreasing");
+    if (h & 8u) return fail(AG_ERR_LOAD, "invalid CSR: an edge destination is >= num_nodes");
+    return AG_OK;
+}
+
+int32_t upload(void **dev, const void *src, uint64_t bytes, int mem_kind) {
+    AG_CUDA(cudaMalloc(dev, std::max<uint64_t>(bytes, 16)));
+    if (bytes)
+        AG_CUDA(cudaMemcpy(*dev, src, bytes, mem_kind == AG_MEM_HOST ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToDevice));
+    return AG_OK;
+}
+
+// Reads exactly `bytes` at `offset`; false on a short read.
+bool read_exact(int fd, void *buf, uint64_t bytes, uint64_t offset) {
+    uint8_t *p = (uint8_t *)buf;
+    while (bytes) {
+        const ssize_t r = pread(fd, p, (size_t)std::min<uint64_t>(bytes, 1ull << 30), (off_t)offset);
+        if (r <= 0) return false;
+        p += r; offset += (uint64_t)r; bytes -= (uint64_t)r;
+    }
+    return true;
+}
+
+// Streams a file section into device memory through a pinned bounce buffer.
+int32_t stream_to_device(int fd, uint64_t offset, uint64_t bytes, void *dev, uint32_t *crc) {
+    const uint64_t chunk = 64ull << 20;
+    void *pinned = nullptr;
+    AG_CUDA(cudaHostAlloc(&pinned, (size_t)std::min(chunk, std::max<uint64_t>(bytes, 16)), cudaHostAllocDefault));
+    int32_t st = AG_OK;
+    for (uint64_t done = 0; done < bytes; done += chunk) {
+        const uint64_t n = std::min(chunk, bytes - done);
+        if (!read_exact(fd, pinned, n, offset + done)) { st = fail(AG_ERR_LOAD, "short read at offset %llu", (unsigned long long)(offset + done)); break; }
+        if (crc) *crc = crc32_update(*crc, pinned, n);
+        if (cudaMemcpy((uint8_t *)dev + done, pinned, n, cudaMemcpyHostToDevice) != cudaSuccess) {
+            st = fail(AG_ERR_CUDA, "copy to device failed: %s", cudaGetErrorString(cudaGetLastError()));
+            break;
+        }
+    }
+    cudaFreeHost(pinned);
+    return st;
+}
+
+int write_all(int fd, const void *buf, uint64_t bytes) {
+    const uint8_t *p = (const uint8_t *)buf;
+    while (bytes) {
+        const ssize_t w = write(fd, p, (size_t)std::min<uint64_t>(bytes, 1ull << 30));
+        if (w <= 0) return -1;
+        p += w; bytes -= (uint64_t)w;
+    }
+    return 0;
+}
+
+// Writes go to a sibling temporary that is fsynced and renamed over the target
+// (reference: internal/mmap.rs:38-87, features/store.rs:923-986).
+struct AtomicFile {
+    std::string path, tmp;
+    int fd = -1;
+    bool open_tmp(const char *target) {
+        path = target;
+        static int seq = 0;
+        std::string dir = ".", name = path;
+        const size_t slash = path.find_last_of('/');
+        if (slash != std::string::npos) { dir = path.substr(0, slash); name = path.substr(slash + 1); if (dir.empty()) dir = "/"; }
+        char suffix[64];
+        snprintf(suffix, sizeof suffix, ".tmp.%d.%d", (int)getpid(), seq++);
+        tmp = dir + "/." + name + suffix;
+        fd = open(tmp.c_str(), O_WRONLY | O_CREAT | O_EXCL, 0644);
+        return fd >= 0;
+    }
+    bool commit() {
+        bool ok = fsync(fd) == 0;
+        close(fd); fd = -1;
+        if (ok) ok = rename(tmp.c_str(), path.c_str()) == 0;
+        if (!ok) unlink(tmp.c_str());
+        return ok;
+    }
+    void abort() { if (fd >= 0) { close(fd); fd = -1; unlink(tmp.c_str()); } }
+};
+
+constexpr uint32_t kGraphMagic = 0x41455448u;  // "AETH" (internal/mmap.rs:20)
+constexpr uint64_t kMaxEdges = 100000000000ull;  // internal/mmap.rs:31
+constexpr uint64_t kFullValidationBytes = 512ull << 20;  // internal/mmap.rs:27
+
+}  // namespace
+}  // namespace ag
+
+using namespace ag;
+
+extern "C" const char *ag_last_error(void) { return g_error; }
+extern "C" int32_t ag_abi_version(void) { return 1; }
+
+// reference: loader/sampler.rs:69-75
+extern "C" uint64_t ag_batch_seed(uint64_t base, uint64_t batch_idx) {
+    uint64_t z = base ^ (batch_idx * 0x9E3779B97F4A7C15ull);
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+
+// ------------------------------------------------------------------ graph --
+extern "C" void ag_graph_free(ag_graph *g) {
+    if (!g) return;
+    DeviceGuard guard(g->device);
+    cudaFree(g->offsets); cudaFree(g->dst); cudaFree(g->weights);
+    delete g;
+}
+
+extern "C" int32_t ag_graph_from_csr(uint64_t num_nodes, uint64_t num_edges, const uint64_t *offsets,
+                                     const uint32_t *dst, const float *weights, int32_t mem_kind,
+                                     int32_t device, ag_graph **out) {
+    if (!offsets || (!dst && num_edges) || !out) return fail(AG_ERR_VALUE, "ag_graph_from_csr: null argument");
+    if (num_nodes > 0xFFFFFFFFull) return fail(AG_ERR_LOAD, "num_nodes %llu exceeds the u32 id space", (unsigned long long)num_nodes);
+    DeviceGuard guard(device);
+    if (!guard.ok) return AG_ERR_CUDA;
+    ag_graph *g = new ag_graph();
+    g->device = device; g->num_nodes = num_nodes; g->num_edges = num_edges;
+    int32_t st = upload((void **)&g->offsets, offsets, (num_nodes + 1) * 8, mem_kind);
+    if (st == AG_OK) st = upload((void **)&g->dst, dst, num_edges * 4, mem_kind);
+    if (st == AG_OK && weights) st = upload((void **)&g->weights, weights, num_edges * 4, mem_kind);
+    if (st == AG_OK) st = validate_on_device(g, true);
+    if (st != AG_OK) { ag_graph_free(g); return st; }
+    *out = g;
+    return AG_OK;
+}
+
+extern "C" int32_t ag_graph_adopt_device_csr(uint64_t num_nodes, uint64_t num_edges, uint64_t *offsets_dev,
+                                             uint32_t *dst_dev, float *weights_dev, int32_t device, ag_graph **out) {
+    if (!offsets_dev || (!dst_dev && num_edges) || !out) return fail(AG_ERR_VALUE, "ag_graph_adopt_device_csr: null argument");
+    if (num_nodes > 0xFFFFFFFFull) return fail(AG_ERR_LOAD, "num_nodes %llu exceeds the u32 id space", (unsigned long long)num_nodes);
+    DeviceGuard guard(device);
+    if (!guard.ok) return AG_ERR_CUDA;
+    ag_graph tmp;
+    tmp.device = device; tmp.num_nodes = num_nodes; tmp.num_edges = num_edges;
+    tmp.offsets = offsets_dev; tmp.dst = dst_dev; tmp.weights = weights_dev;
+    AG_TRY(validate_on_device(&tmp, true));
+    *out = new ag_graph(tmp);
+    return AG_OK;
+}
+
+// Counting sort by source, input order kept within a row
+// (reference: graph/csr.rs:568-571, 631-750).
+extern "C" int32_t ag_graph_from_edges(uint64_t num_nodes, const uint32_t *src, const uint32_t *dst,
+                                       const float *weights, uint64_t num_edges, int32_t device, ag_graph **out) {
+    if ((num_edges && (!src || !dst)) || !out) return fail(AG_ERR_VALUE, "ag_graph_from_edges: null argument");
+    for (uint64_t i = 0; i < num_edges; ++i) {
+        if ((uint64_t)src[i] >= num_nodes || (uint64_t)dst[i] >= num_nodes)
+            return fail(AG_ERR_VALUE, "edge %llu (%u -> %u) is out of range for %llu nodes",
+                        (unsigned long long)i, src[i], dst[i], (unsigned long long)num_nodes);
+    }
+    std::vector<uint64_t> offsets(num_nodes + 1, 0);
+    for (uint64_t i = 0; i < num_edges; ++i) offsets[(uint64_t)src[i] + 1]++;
+    for (uint64_t v = 0; v < num_nodes; ++v) offsets[v + 1] += offsets[v];
+    std::vector<uint64_t> cursor(offsets.begin(), offsets.end() - 1);
+    std::vector<uint32_t> edges(num_edges);
+    std::vector<float> w(weights ? num_edges : 0);
+    for (uint64_t i = 0; i < num_edges; ++i) {
+        const uint64_t at = cursor[src[i]]++;
+        edges[at] = dst[i];
+        if (weights) w[at] = weights[i];
+    }
+    return ag_graph_from_csr(num_nodes, num_edges, offsets.data(), edges.data(), weights ? w.data() : nullptr,
+                             AG_MEM_HOST, device, out);
+}
+
+// AETH v1 (reference: internal/mmap.rs:114-121 header, :502-600 layout,
+// :601-632 checksum policy, :633-643 default validation level).
+extern "C" int32_t ag_graph_load(const char *path, int32_t validation, int32_t device, ag_graph **out) {
+    if (!path || !out) return fail(AG_ERR_VALUE, "ag_graph_load: null argument");
+    const int fd = open(path, O_RDONLY);
+    if (fd < 0) return fail(AG_ERR_LOAD, "failed to open graph file %s: %s", path, strerror(errno));
+    struct stat sb;
+    if (fstat(fd, &sb) != 0) { close(fd); return fail(AG_ERR_LOAD, "failed to stat %s", path); }
+    const uint64_t file_size = (uint64_t)sb.st_size;
+    uint8_t h[32];
+    if (file_size < 32 || !read_exact(fd, h, 32, 0)) {
+        close(fd);
+        return fail(AG_ERR_LOAD, "insufficient bytes for header: got %llu, need 32", (unsigned long long)file_size);
+    }
+    uint32_t magic, version, has_w, checksum;
+    uint64_t n, e;
+    memcpy(&magic, h, 4); memcpy(&version, h + 4, 4); memcpy(&n, h + 8, 8); memcpy(&e, h + 16, 8);
+    memcpy(&has_w, h + 24, 4); memcpy(&checksum, h + 28, 4);
+    auto bail = [&](int32_t st) { close(fd); return st; };
+    if (magic != kGraphMagic) return bail(fail(AG_ERR_LOAD, "invalid magic number"));
+    if (version != 1) return bail(fail(AG_ERR_LOAD, "unsupported version: expected 1, got %u", version));
+    if (n > 0xFFFFFFFFull) return bail(fail(AG_ERR_LOAD, "num_nodes %llu exceeds maximum %llu", (unsigned long long)n, 0xFFFFFFFFull));
+    if (e > kMaxEdges) return bail(fail(AG_ERR_LOAD, "num_edges %llu exceeds maximum %llu", (unsigned long long)e, (unsigned long long)kMaxEdges));
+    const uint64_t off_bytes = (n + 1) * 8, edge_bytes = e * 4, w_bytes = has_w ? e * 4 : 0;
+    const uint64_t need = 32 + off_bytes + edge_bytes + w_bytes;
+    if (file_size < need)
+        return bail(fail(AG_ERR_LOAD, "file too small: expected at least %llu bytes, got %llu",
+                         (unsigned long long)need, (unsigned long long)file_size));
+    if (validation == AG_VALIDATE_AUTO)
+        validation = file_size > kFullValidationBytes ? AG_VALIDATE_OFFSETS : AG_VALIDATE_FULL;
+
+    DeviceGuard guard(device);
+    if (!guard.ok) return bail(AG_ERR_CUDA);
+    ag_graph *g = new ag_graph();
+    g->device = device; g->num_nodes = n; g->num_edges = e;
+    int32_t st = AG_OK;
+    uint32_t crc = 0;
+    const bool want_crc = validation == AG_VALIDATE_FULL && checksum != 0;
+    do {
+        if (cudaMalloc(&g->offsets, std::max<uint64_t>(off_bytes, 16)) != cudaSuccess ||
+            cudaMalloc(&g->dst, std::max<uint64_t>(edge_bytes, 16)) != cudaSuccess ||
+            (has_w && cudaMalloc(&g->weights, std::max<uint64_t>(w_bytes, 16)) != cudaSuccess)) {
+            st = fail(AG_ERR_CUDA, "out of device memory loading %s: %s", path, cudaGetErrorString(cudaGetLastError()));
+            break;
+        }
+        if ((st = stream_to_device(fd, 32, off_bytes, g->offsets, want_crc ? &crc : nullptr)) != AG_OK) break;
+        if ((st = stream_to_device(fd, 32 + off_bytes, edge_bytes, g->dst, want_crc ? &crc : nullptr)) != AG_OK) break;
+        if (has_w && (st = stream_to_device(fd, 32 + off_bytes + edge_bytes, w_bytes, g->weights, nullptr)) != AG_OK) break;
+        if (want_crc && crc != checksum) {
+            st = fail(AG_ERR_LOAD, "graph integrity checksum mismatch: expected %#x, got %#x", checksum, crc);
+            break;
+        }
+        // The sampler indexes its tables by destination id, so destinations are
+        // always proven in range here, whatever level the caller asked for.
+        st = validate_on_device(g, true);
+    } while (0);
+    close(fd);
+    if (st != AG_OK) { ag_graph_free(g); return st; }
+    *out = g;
+    return AG_OK;
+}
+
+extern "C" int32_t ag_graph_save(const ag_graph *g, const char *path) {
+    if (!g || !path) return fail(AG_ERR_VALUE, "ag_graph_save: null argument");
+    DeviceGuard guard(g->device);
+    if (!guard.ok) return AG_ERR_CUDA;
+    std::vector<uint64_t> offsets(g->num_nodes + 1);
+    std::vector<uint32_t> edges(g->num_edges);
+    std::vector<float> w(g->weights ? g->num_edges : 0);
+    AG_CUDA(cudaMemcpy(offsets.data(), g->offsets, offsets.size() * 8, cudaMemcpyDeviceToHost));
+    if (g->num_edges) AG_CUDA(cudaMemcpy(edges.data(), g->dst, edges.size() * 4, cudaMemcpyDeviceToHost));
+    if (g->weights && g->num_edges) AG_CUDA(cudaMemcpy(w.data(), g->weights, w.size() * 4, cudaMemcpyDeviceToHost));
+    uint32_t crc = crc32_update(0, offsets.data(), offsets.size() * 8);
+    crc = crc32_update(crc, edges.data(), edges.size() * 4);
+    uint8_t h[32] = {0};
+    const uint32_t version = 1, has_w = g->weights ? 1 : 0;
+    memcpy(h, &kGraphMagic, 4); memcpy(h + 4, &version, 4); memcpy(h + 8, &g->num_nodes, 8);
+    memcpy(h + 16, &g->num_edges, 8); memcpy(h + 24, &has_w, 4); memcpy(h + 28, &crc, 4);
+    AtomicFile f;
+    if (!f.open_tmp(path)) return fail(AG_ERR_LOAD, "failed to create %s: %s", path, strerror(errno));
+    if (write_all(f.fd, h, 32) || write_all(f.fd, offsets.data(), offsets.size() * 8) ||
+        write_all(f.fd, edges.data(), edges.size() * 4) || (has_w && write_all(f.fd, w.data(), w.size() * 4))) {
+        f.abort();
+        return fail(AG_ERR_LOAD, "failed to write %s: %s", path, strerror(errno));
+    }
+    if (!f.commit()) return fail(AG_ERR_LOAD, "failed to move output into %s: %s", path, strerror(errno));
+    return AG_OK;
+}
+
+extern "C" int32_t ag_graph_info(const ag_graph *g, uint64_t *num_nodes, uint64_t *num_edges,
+                                 int32_t *has_weights, int32_t *device) {
+    if (!g) return fail(AG_ERR_VALUE, "ag_graph_info: null graph");
+    if (num_nodes) *num_nodes = g->num_nodes;
+    if (num_edges) *num_edges = g->num_edges;
+    if (has_weights) *has_weights = g->weights ? 1 : 0;
+    if (device) *device = g->device;
+    return AG_OK;
+}
+
+extern "C" int32_t ag_graph_device_ptrs(const ag_graph *g, const uint64_t **offsets_dev,
+                                        const uint32_t **dst_dev, const float **weights_dev) {
+    if (!g) return fail(AG_ERR_VALUE, "ag_graph_device_ptrs: null graph");
+    if (offsets_dev) *offsets_dev = g->offsets;
+    if (dst_dev) *dst_dev = g->dst;
+    if (weights_dev) *weights_dev = g->weights;
+    return AG_OK;
+}
+
+extern "C" int32_t ag_graph_degrees(const ag_graph *g, const uint32_t *ids, uint64_t n, uint32_t *out) {
+    if (!g || (!out && n)) return fail(AG_ERR_VALUE, "ag_graph_degrees: null argument");
+    if (n == 0) return AG_OK;
+    DeviceGuard guard(g->device);
+    if (!guard.ok) return AG_ERR_CUDA;
+    uint32_t *ids_dev = nullptr, *out_dev = nullptr;
+    int32_t st = AG_OK;
+    do {
+        if (ids && (st = upload((void **)&ids_dev, ids, n * 4, AG_MEM_HOST)) != AG_OK) break;
+        if (cudaMalloc(&out_dev, n * 4) != cudaSuccess) { st = fail(AG_ERR_CUDA, "out of device memory"); break; }
+        cudaError_t e = launch_degrees(g->offsets, g->num_nodes, ids_dev, n, out_dev, 0);
+        if (e == cudaSuccess) e = cudaMemcpy(out, out_dev, n * 4, cudaMemcpyDeviceToHost);
+        if (e != cudaSuccess) st = fail(AG_ERR_CUDA, "degrees failed: %s", cudaGetErrorString(e));
+    } while (0);
+    cudaFree(ids_dev); cudaFree(out_dev);
+    return st;
+}
+
+extern "C" int32_t ag_graph_neighbors(const ag_graph *g, uint32_t node, uint32_t *out, float *weights_out,
+                                      uint64_t cap, uint64_t *degree) {
+    if (!g) return fail(AG_ERR_VALUE, "ag_graph_neighbors: null graph");
+    if (degree) *degree = 0;
+    if ((uint64_t)node >= g->num_nodes) return AG_OK;  // empty row, like graph/csr.rs:318-335
+    DeviceGuard guard(g->device);
+    if (!guard.ok) return AG_ERR_CUDA;
+    uint64_t ab[2];
+    AG_CUDA(cudaMemcpy(ab, g->offsets + node, 16, cudaMemcpyDeviceToHost));
+    if (ab[0] > ab[1] || ab[1] > g->num_edges) return AG_OK;
+    const uint64_t d = ab[1] - ab[0];
+    if (degree) *degree = d;
+    const uint64_t m = std::min(d, cap);
+    if (m && out) AG_CUDA(cudaMemcpy(out, g->dst + ab[0], m * 4, cudaMemcpyDeviceToHost));
+    if (m && weights_out && g->weights) AG_CUDA(cudaMemcpy(weights_out, g->weights + ab[0], m * 4, cudaMemcpyDeviceToHost));
+    return AG_OK;
+}
+
+// --------------------------------------------------------------- features --
+namespace {
+
+constexpr uint64_t kFeatHeader = 32;       // features/header.rs:118
+constexpr uint64_t kFeatDataOffset = 512;  // features/store.rs:45
+constexpr uint64_t kMaxFeatNodes = 10000000000ull, kMaxFeatDim = 100000ull;  // header.rs:120-121
+
+struct FeatHeader { uint64_t n, dim, offset; int dtype; };
+
+// reference: features/header.rs:165-244
+int32_t parse_feature_header(int fd, uint64_t file_size, FeatHeader *out) {
+    uint8_t p[33] = {0};
+    const uint64_t len = std::min<uint64_t>(33, file_size);
+    if (file_size < kFeatHeader || !read_exact(fd, p, len, 0))
+        return fail(AG_ERR_LOAD, "feature file too small: %llu bytes", (unsigned long long)file_size);
+    if (memcmp(p, "AETHFEAT", 8) != 0) return fail(AG_ERR_LOAD, "invalid feature file format (bad magic)");
+    uint64_t n, dim, off;
+    memcpy(&n, p + 8, 8); memcpy(&dim, p + 16, 8); memcpy(&off, p + 24, 8);
+    if (n > kMaxFeatNodes) return fail(AG_ERR_LOAD, "num_nodes %llu exceeds maximum %llu", (unsigned long long)n, (unsigned long long)kMaxFeatNodes);
+    if (dim > kMaxFeatDim) return fail(AG_ERR_LOAD, "feature_dim %llu exceeds maximum %llu", (unsigned long long)dim, (unsigned long long)kMaxFeatDim);
+    if (off <= kFeatHeader) return fail(AG_ERR_LOAD, "invalid data_offset %llu (must be > 32)", (unsigned long long)off);
+    if (off % 4) return fail(AG_ERR_LOAD, "invalid data_offset %llu (must be 4-byte aligned)", (unsigned long long)off);
+    if (off > file_size) return fail(AG_ERR_LOAD, "invalid data_offset %llu for file size %llu", (unsigned long long)off, (unsigned long long)file_size);
+    if (len < 33) return fail(AG_ERR_LOAD, "failed to read dtype tag");
+    const int tag = p[32];
+    if (tag > 2) return fail(AG_ERR_LOAD, "unknown feature dtype tag: %d", tag);
+    const uint64_t row = dim * elem_size(tag);
+    if (n && row > (0xFFFFFFFFFFFFFFFFull - off) / n) return fail(AG_ERR_LOAD, "feature data size overflow");
+    if (file_size < off + n * row)
+        return fail(AG_ERR_LOAD, "feature file truncated: expected at least %llu bytes, got %llu",
+                    (unsigned long long)(off + n * row), (unsigned long long)file_size);
+    out->n = n; out->dim = dim; out->offset = off; out->dtype = tag;
+    return AG_OK;
+}
+
+ag_features *new_features(int device, uint64_t n, uint64_t begin, uint64_t rows, uint64_t dim, int dtype) {
+    ag_features *f = new ag_features();
+    f->device = device; f->num_nodes = n; f->row_begin = begin; f->rows = rows; f->dim = dim; f->dtype = dtype;
+    return f;
+}
+
+int32_t alloc_features(ag_features *f, bool alloc_payload) {
+    if (alloc_payload)
+        AG_CUDA(cudaMalloc(&f->payload, std::max<uint64_t>(f->rows * f->dim * elem_size(f->dtype), 16)));
+    AG_CUDA(cudaMalloc(&f->err, 4));
+    AG_CUDA(cudaMemset(f->err, 0, 4));
+    return AG_OK;
+}
+
+uint16_t f32_to_bf16_host(float v) {  // features/store.rs:1094-1104
+    uint32_t bits;
+    memcpy(&bits, &v, 4);
+    if (v != v) return (uint16_t)((bits >> 16) | 0x0040u);
+    return (uint16_t)((bits + 0x7FFFu + ((bits >> 16) & 1u)) >> 16);
+}
+
+uint16_t f32_to_f16_host(float v) {  // IEEE RNE, as half::f16::from_f32
+    uint32_t x;
+    memcpy(&x, &v, 4);
+    const uint32_t sign = (x >> 16) & 0x8000u, exp = (x >> 23) & 0xFFu;
+    uint32_t man = x & 0x7FFFFFu;
+    if (exp == 0xFFu) return (uint16_t)(man ? (sign | 0x7E00u | (man >> 13)) : (sign | 0x7C00u));
+    const int e = (int)exp - 112;
+    if (e >= 0x1F) return (uint16_t)(sign | 0x7C00u);
+    if (e <= 0) {
+        if (e < -10) return (uint16_t)sign;
+        man |= 0x800000u;
+        const uint32_t shift = (uint32_t)(14 - e);
+        uint32_t hm = man >> shift;
+        const uint32_t rem = man & ((1u << shift) - 1u), half = 1u << (shift - 1);
+        if (rem > half || (rem == half && (hm & 1u))) hm++;
+        return (uint16_t)(sign | hm);
+    }
+    uint32_t hh = ((uint32_t)e << 10) | (man >> 13);
+    const uint32_t rem = man & 0x1FFFu;
+    if (rem > 0x1000u || (rem == 0x1000u && (hh & 1u))) hh++;
+    return (uint16_t)(sign | hh);
+}
+
+}  // namespace
+
+// reference: features/store.rs:923-986 (write_feature_file)
+extern "C" int32_t ag_features_save(const char *path, const float *features, uint64_t num_nodes, uint64_t dim, int32_t dtype) {
+    if (!path || (!features && num_nodes * dim)) return fail(AG_ERR_VALUE, "ag_features_save: null argument");
+    if (dtype < 0 || dtype > 2) return fail(AG_ERR_VALUE, "unknown feature dtype tag: %d", dtype);
+    AtomicFile f;
+    if (!f.open_tmp(path)) return fail(AG_ERR_LOAD, "failed to create feature file %s: %s", path, strerror(errno));
+    uint8_t header[kFeatDataOffset] = {0};
+    memcpy(header, "AETHFEAT", 8); memcpy(header + 8, &num_nodes, 8); memcpy(header + 16, &dim, 8);
+    memcpy(header + 24, &kFeatDataOffset, 8);
+    header[32] = (uint8_t)dtype;
+    bool ok = write_all(f.fd, header, sizeof header) == 0;
+    const uint64_t total = num_nodes * dim;
+    if (ok && dtype == AG_F32) ok = write_all(f.fd, features, total * 4) == 0;
+    else if (ok) {
+        const uint64_t chunk = 1 << 20;
+        std::vector<uint16_t> buf(std::min(chunk, std::max<uint64_t>(total, 1)));
+        for (uint64_t done = 0; ok && done < total; done += chunk) {
+            const uint64_t m = std::min(chunk, total - done);
+            for (uint64_t i = 0; i < m; ++i)
+                buf[i] = dtype == AG_BF16 ? f32_to_bf16_host(features[done + i]) : f32_to_f16_host(features[done + i]);
+            ok = write_all(f.fd, buf.data(), m * 2) == 0;
+        }
+    }
+    if (!ok) { f.abort(); return fail(AG_ERR_LOAD, "failed to write feature file %s: %s", path, strerror(errno)); }
+    if (!f.commit()) return fail(AG_ERR_LOAD, "failed to replace %s: %s", path, strerror(errno));
+    return AG_OK;
+}
+
+extern "C" void ag_features_free(ag_features *f) {
+    if (!f) return;
+    DeviceGuard guard(f->device);
+    if (f->owns_payload) cudaFree(f->payload);
+    cudaFree(f->err);
+    delete f;
+}
+
+extern "C" int32_t ag_features_load_range(const char *path, int32_t device, uint64_t row_begin, uint64_t row_end, ag_features **out) {
+    if (!path || !out) return fail(AG_ERR_VALUE, "ag_features_load: null argument");
+    const int fd = open(path, O_RDONLY);
+    if (fd < 0) return fail(AG_ERR_LOAD, "failed to open feature file %s: %s", path, strerror(errno));
+    struct stat sb;
+    if (fstat(fd, &sb) != 0) { close(fd); return fail(AG_ERR_LOAD, "failed to stat feature file"); }
+    FeatHeader h{};
+    int32_t st = parse_feature_header(fd, (uint64_t)sb.st_size, &h);
+    if (st != AG_OK) { close(fd); return st; }
+    row_end = std::min(row_end, h.n);
+    row_begin = std::min(row_begin, row_end);
+    DeviceGuard guard(device);
+    if (!guard.ok) { close(fd); return AG_ERR_CUDA; }
+    ag_features *f = new_features(device, h.n, row_begin, row_end - row_begin, h.dim, h.dtype);
+    st = alloc_features(f, true);
+    const uint64_t row = h.dim * elem_size(h.dtype);
+    if (st == AG_OK) st = stream_to_device(fd, h.offset + row_begin * row, f->rows * row, f->payload, nullptr);
+    close(fd);
+    if (st != AG_OK) { ag_features_free(f); return st; }
+    *out = f;
+    return AG_OK;
+}
+
+extern "C" int32_t ag_features_load(const char *path, int32_t device, ag_features **out) {
+    return ag_features_load_range(path, device, 0, 0xFFFFFFFFFFFFFFFFull, out);
+}
+
+extern "C" int32_t ag_features_from_memory(const void *payload, uint64_t num_nodes, uint64_t dim, int32_t dtype,
+                                           int32_t mem_kind, int32_t device, ag_features **out) {
+    if ((!payload && num_nodes * dim) || !out) return fail(AG_ERR_VALUE, "ag_features_from_memory: null argument");
+    if (dtype < 0 || dtype > 2) return fail(AG_ERR_VALUE, "unknown feature dtype tag: %d", dtype);
+    DeviceGuard guard(device);
+    if (!guard.ok) return AG_ERR_CUDA;
+    ag_features *f = new_features(device, num_nodes, 0, num_nodes, dim, dtype);
+    int32_t st = alloc_features(f, true);
+    const uint64_t bytes = num_nodes * dim * elem_size(dtype);
+    if (st == AG_OK && bytes &&
+        cudaMemcpy(f->payload, payload, bytes, mem_kind == AG_MEM_HOST ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToDevice) != cudaSuccess)
+        st = fail(AG_ERR_CUDA, "feature upload failed: %s", cudaGetErrorString(cudaGetLastError()));
+    if (st != AG_OK) { ag_features_free(f); return st; }
+    *out = f;
+    return AG_OK;
+}
+
+extern "C" int32_t ag_features_from_f32(const float *features, uint64_t num_nodes, uint64_t dim, int32_t dtype,
+                                        int32_t mem_kind, int32_t device, ag_features **out) {
+    if ((!features && num_nodes * dim) || !out) return fail(AG_ERR_VALUE, "ag_features_from_f32: null argument");
+    if (dtype < 0 || dtype > 2) return fail(AG_ERR_VALUE, "unknown feature dtype tag: %d", dtype);
+    DeviceGuard guard(device);
+    if (!guard.ok) return AG_ERR_CUDA;
+    ag_features *f = new_features(device, num_nodes, 0, num_nodes, dim, dtype);
+    int32_t st = alloc_features(f, true);
+    const uint64_t count = num_nodes * dim;
+    float *staged = nullptr;
+    do {
+        if (st != AG_OK || count == 0) break;
+        const float *src = features;
+        if (mem_kind == AG_MEM_HOST) {
+            if (cudaMalloc(&staged, count * 4) != cudaSuccess ||
+                cudaMemcpy(staged, features, count * 4, cudaMemcpyHostToDevice) != cudaSuccess) {
+                st = fail(AG_ERR_CUDA, "feature upload failed: %s", cudaGetErrorString(cudaGetLastError()));
+                break;
+            }
+            src = staged;
+        }
+        cudaError_t e = launch_encode(src, f->payload, count, dtype, 0);
+        if (e == cudaSuccess) e = cudaDeviceSynchronize();
+        if (e != cudaSuccess) st = fail(AG_ERR_CUDA, "feature encode failed: %s", cudaGetErrorString(e));
+    } while (0);
+    cudaFree(staged);
+    if (st != AG_OK) { ag_features_free(f); return st; }
+    *out = f;
+    return AG_OK;
+}
+
+extern "C" int32_t ag_features_adopt_device(void *payload_dev, uint64_t num_nodes, uint64_t dim, int32_t dtype,
+                                            int32_t device, ag_features **out) {
+    if (!payload_dev || !out) return fail(AG_ERR_VALUE, "ag_features_adopt_device: null argument");
+    if (dtype < 0 || dtype > 2) return fail(AG_ERR_VALUE, "unknown feature dtype tag: %d", dtype);
+    DeviceGuard guard(device);
+    if (!guard.ok) return AG_ERR_CUDA;
+    ag_features *f = new_features(device, num_nodes, 0, num_nodes, dim, dtype);
+    f->payload = (uint8_t *)payload_dev;
+    const int32_t st = alloc_features(f, false);
+    if (st != AG_OK) { f->owns_payload = false; ag_features_free(f); return st; }
+    *out = f;
+    return AG_OK;
+}
+
+extern "C" int32_t ag_features_info(const ag_features *f, uint64_t *num_nodes, uint64_t *dim, int32_t *dtype,
+                                    int32_t *device, uint64_t *row_begin) {
+    if (!f) return fail(AG_ERR_VALUE, "ag_features_info: null store");
+    if (num_nodes) *num_nodes = f->num_nodes;
+    if (dim) *dim = f->dim;
+    if (dtype) *dtype = f->dtype;
+    if (device) *device = f->device;
+    if (row_begin) *row_begin = f->row_begin;
+    return AG_OK;
+}
+
+extern "C" int32_t ag_features_device_ptr(const ag_features *f, const void **payload_dev) {
+    if (!f || !payload_dev) return fail(AG_ERR_VALUE, "ag_features_device_ptr: null argument");
+    *payload_dev = f->payload;
+    return AG_OK;
+}
+
+extern "C" int32_t ag_gather(const ag_features *f, const void *ids_dev, int32_t ids_are_i64, uint64_t n,
+                             const uint32_t *n_dev, float *out_dev, void *stream) {
+    if (!f || (!ids_dev && n) || (!out_dev && n)) return fail(AG_ERR_VALUE, "ag_gather: null argument");
+    if (n == 0) return AG_OK;
+    DeviceGuard guard(f->device);
+    if (!guard.ok) return AG_ERR_CUDA;
+    GatherArgs a{};
+    a.payload = f->payload; a.row_begin = f->row_begin; a.rows = f->rows;
+    a.row_bytes = (uint32_t)(f->dim * elem_size(f->dtype)); a.dim = (uint32_t)f->dim;
+    a.ids = ids_dev; a.ids64 = ids_are_i64; a.n = n; a.n_dev = n_dev; a.out = out_dev; a.err = f->err;
+    AG_CUDA(launch_gather(a, f->dtype, (cudaStream_t)stream));
+    return AG_OK;
+}
+
+extern "C" int32_t ag_features_check(const ag_features *f) {
+    if (!f) return fail(AG_ERR_VALUE, "ag_features_check: null store");
+    DeviceGuard guard(f->device);
+    if (!guard.ok) return AG_ERR_CUDA;
+    uint32_t h = 0;
+    AG_CUDA(cudaDeviceSynchronize());
+    AG_CUDA(cudaMemcpy(&h, f->err, 4, cudaMemcpyDeviceToHost));
+    if (h) {
+        cudaMemset(f->err, 0, 4);
+        return fail(AG_ERR_VALUE, "a gathered node id is out of bounds (num_nodes=%llu)", (unsigned long long)f->num_nodes);
+    }
+    return AG_OK;
+}
+
+// reference: features/store.rs:691-769 — every id is checked before any row is read.
+extern "C" int32_t ag_features_get_batch(const ag_features *f, const int64_t *ids, uint64_t n, float *out) {
+    if (!f || (!ids && n) || (!out && n)) return fail(AG_ERR_VALUE, "ag_features_get_batch: null argument");
+    for (uint64_t i = 0; i < n; ++i) {
+        if (ids[i] < 0 || (uint64_t)ids[i] > 0xFFFFFFFFull) return fail(AG_ERR_VALUE, "invalid node id: %lld", (long long)ids[i]);
+        if ((uint64_t)ids[i] >= f->num_nodes) return fail(AG_ERR_VALUE, "node %lld out of bounds", (long long)ids[i]);
+        if ((uint64_t)ids[i] < f->row_begin || (uint64_t)ids[i] >= f->row_begin + f->rows)
+            return fail(AG_ERR_VALUE, "node %lld is not held by this shard (rows %llu..%llu)", (long long)ids[i],
+                        (unsigned long long)f->row_begin, (unsigned long long)(f->row_begin + f->rows));
+    }
+    if (n == 0 || f->dim == 0) return AG_OK;
+    DeviceGuard guard(f->device);
+    if (!guard.ok) return AG_ERR_CUDA;
+    int64_t *ids_dev = nullptr;
+    float *out_dev = nullptr;
+    int32_t st = AG_OK;
+    do {
+        if (cudaMalloc(&ids_dev, n * 8) != cudaSuccess || cudaMalloc(&out_dev, n * f->dim * 4) != cudaSuccess) {
+            st = fail(AG_ERR_CUDA, "out of device memory: %s", cudaGetErrorString(cudaGetLastError()));
+            break;
+        }
+        cudaError_t e = cudaMemcpy(ids_dev, ids, n * 8, cudaMemcpyHostToDevice);
+        if (e == cudaSuccess) {
+            st = ag_gather(f, ids_dev, 1, n, nullptr, out_dev, nullptr);
+            if (st != AG_OK) break;
+            e = cudaMemcpy(out, out_dev, n * f->dim * 4, cudaMemcpyDeviceToHost);
+        }
+        if (e != cudaSuccess) st = fail(AG_ERR_CUDA, "get_batch failed: %s", cudaGetErrorString(e));
+    } while (0);
+    cudaFree(ids_dev); cudaFree(out_dev);
+    return st;
+}

@@ -1,0 +1,242 @@
+// Feature-row gather with fused f16/bf16 -> f32 upcast.
+//
+// Follows FeatureStore::get_batch_into of the reference
+// (crates/aethergraph-core/src/features/store.rs:777-838; row decoders
+// features/header.rs:110-116, internal/simd.rs:97-101,233-238): output row i is
+// the decoded stored row ids[i], in ids order, duplicates re-read.
+//
+// Shape.  The path is HBM-bound byte movement: per output row it reads
+// row_bytes (a whole number of 32-byte sectors when rows are 32-byte aligned)
+// and writes dim * 4 bytes.  A row is split into 16-byte vectors; a group of
+// LPR lanes (the power of two >= vectors-per-row, at most 32) owns one row, so
+// a warp reads 32/LPR rows with fully coalesced 16-byte loads.  Every thread
+// issues kInFlight independent row loads before it converts or stores any of
+// them, which keeps >= 2 KB per warp in flight — enough to cover HBM latency at
+// full occupancy.  Loads bypass L1 (rows are touched once); stores are
+// evict-first.  The grid is a whole number of waves of the 148 SMs and strides
+// over the rows, so the row count may live on the device (the sampler's node
+// count) without a host round trip.
+#include "common.cuh"
+#include "internal.h"
+
+namespace ag {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kInFlight = 4;
+
+__device__ __forceinline__ float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+
+// IEEE binary16 -> binary32, exact; a NaN keeps its payload and comes out quiet
+// (what the reference's half / F16C converters produce).
+__device__ __forceinline__ float f16_to_f32_bits(uint32_t h) {
+    const uint32_t sign = (h & 0x8000u) << 16;
+    const uint32_t exp = (h >> 10) & 0x1Fu;
+    uint32_t man = h & 0x3FFu;
+    if (exp == 0x1Fu) return __uint_as_float(man ? (sign | 0x7FC00000u | (man << 13)) : (sign | 0x7F800000u));
+    if (exp == 0) {
+        if (man == 0) return __uint_as_float(sign);
+        const int shift = __clz(man) - 21;  // bring the top set bit to bit 10
+        man = (man << shift) & 0x3FFu;
+        return __uint_as_float(sign | ((uint32_t)(113 - shift) << 23) | (man << 13));
+    }
+    return __uint_as_float(sign | ((exp + 112u) << 23) | (man << 13));
+}
+
+template <int DTYPE>
+__device__ __forceinline__ void store_decoded(float *dst, uint4 v) {
+    if (DTYPE == AG_F32) {
+        st_stream_v4(dst, v);
+    } else if (DTYPE == AG_BF16) {
+        uint4 a, b;
+        a.x = v.x << 16; a.y = v.x & 0xFFFF0000u; a.z = v.y << 16; a.w = v.y & 0xFFFF0000u;
+        b.x = v.z << 16; b.y = v.z & 0xFFFF0000u; b.z = v.w << 16; b.w = v.w & 0xFFFF0000u;
+        st_stream_v4(dst, a);
+        st_stream_v4(dst + 4, b);
+    } else {
+        uint4 a, b;
+        a.x = __float_as_uint(f16_to_f32_bits(v.x & 0xFFFFu)); a.y = __float_as_uint(f16_to_f32_bits(v.x >> 16));
+        a.z = __float_as_uint(f16_to_f32_bits(v.y & 0xFFFFu)); a.w = __float_as_uint(f16_to_f32_bits(v.y >> 16));
+        b.x = __float_as_uint(f16_to_f32_bits(v.z & 0xFFFFu)); b.y = __float_as_uint(f16_to_f32_bits(v.z >> 16));
+        b.z = __float_as_uint(f16_to_f32_bits(v.w & 0xFFFFu)); b.w = __float_as_uint(f16_to_f32_bits(v.w >> 16));
+        st_stream_v4(dst, a);
+        st_stream_v4(dst + 4, b);
+    }
+}
+
+__device__ __forceinline__ uint64_t load_id(const void *ids, int ids64, uint64_t i) {
+    return ids64 ? (uint64_t)((const int64_t *)ids)[i] : (uint64_t)((const uint32_t *)ids)[i];
+}
+
+// Vector path: row_bytes % 16 == 0 and the payload base is 16-byte aligned.
+// LPR lanes share a row; vecs = row_bytes / 16.
+template <int DTYPE, int LPR>
+__global__ void __launch_bounds__(kThreads)
+k_gather_vec(GatherArgs a) {
+    constexpr int kRowsPerBlock = kThreads / LPR;
+    const uint64_t n = a.n_dev ? min((uint64_t)*a.n_dev, a.n) : a.n;
+    const int lane = threadIdx.x % LPR;
+    const int sub = threadIdx.x / LPR;
+    const uint32_t vecs = a.row_bytes >> 4;
+    const uint32_t out_per_vec = (DTYPE == AG_F32) ? 4u : 8u;  // floats per 16-byte vector
+    const uint64_t stride = (uint64_t)gridDim.x * kRowsPerBlock;
+
+    for (uint64_t base = (uint64_t)blockIdx.x * kRowsPerBlock + sub; base < n; base += stride * kInFlight) {
+        for (uint32_t v0 = 0; v0 < vecs; v0 += LPR) {
+            const uint32_t v = v0 + lane;
+            uint4 val[kInFlight];
+            bool ok[kInFlight];
+#pragma unroll
+            for (int u = 0; u < kInFlight; ++u) {
+                const uint64_t r = base + (uint64_t)u * stride;
+                ok[u] = false;
+                val[u] = make_uint4(0, 0, 0, 0);
+                if (r < n && v < vecs) {
+                    const uint64_t id = load_id(a.ids, a.ids64, r);
+                    const uint64_t local = id - a.row_begin;
+                    ok[u] = true;
+                    if (id >= a.row_begin && local < a.rows) {
+                        val[u] = ld_stream_v4(a.payload + local * a.row_bytes + ((uint64_t)v << 4));
+                    } else if (lane == 0) {
+                        atomicOr(a.err, kErrBadId);
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kInFlight; ++u) {
+                if (ok[u]) {
+                    const uint64_t r = base + (uint64_t)u * stride;
+                    store_decoded<DTYPE>(a.out + r * a.dim + (uint64_t)v * out_per_vec, val[u]);
+                }
+            }
+        }
+    }
+}
+
+// Element path for rows that are not a whole number of 16-byte vectors.
+template <int DTYPE>
+__global__ void __launch_bounds__(kThreads)
+k_gather_elem(GatherArgs a) {
+    const uint64_t n = a.n_dev ? min((uint64_t)*a.n_dev, a.n) : a.n;
+    const uint64_t total = n * a.dim;
+    for (uint64_t g = (uint64_t)blockIdx.x * kThreads + threadIdx.x; g < total;
+         g += (uint64_t)gridDim.x * kThreads) {
+        const uint64_t r = g / a.dim;
+        const uint32_t j = (uint32_t)(g - r * a.dim);
+        const uint64_t id = load_id(a.ids, a.ids64, r);
+        const uint64_t local = id - a.row_begin;
+        float f = 0.f;
+        if (id >= a.row_begin && local < a.rows) {
+            const uint8_t *row = a.payload + local * a.row_bytes;
+            if (DTYPE == AG_F32) f = __uint_as_float(ld_stream_u32(row + 4ull * j));
+            else if (DTYPE == AG_BF16) f = bf16lo(ld_stream_u16(row + 2ull * j));
+            else f = f16_to_f32_bits(ld_stream_u16(row + 2ull * j));
+        } else if (j == 0) {
+            atomicOr(a.err, kErrBadId);
+        }
+        a.out[g] = f;
+    }
+}
+
+template <int DTYPE>
+cudaError_t launch_vec(const GatherArgs &a, int blocks, cudaStream_t st) {
+    const uint32_t vecs = a.row_bytes >> 4;
+    if (vecs <= 4) k_gather_vec<DTYPE, 4><<<blocks, kThreads, 0, st>>>(a);
+    else if (vecs <= 8) k_gather_vec<DTYPE, 8><<<blocks, kThreads, 0, st>>>(a);
+    else if (vecs <= 16) k_gather_vec<DTYPE, 16><<<blocks, kThreads, 0, st>>>(a);
+    else k_gather_vec<DTYPE, 32><<<blocks, kThreads, 0, st>>>(a);
+    return cudaGetLastError();
+}
+
+// f32 -> stored dtype, used to build a store from f32 rows on the device.
+// bf16: round to nearest even on the dropped 16 bits, NaN -> (bits >> 16) | 0x40
+// (reference: features/store.rs:1094-1104).  f16: IEEE RNE (__float2half_rn),
+// NaN -> sign | 0x7E00 | (mantissa >> 13) as the reference's half crate does.
+__global__ void k_encode(const float *src, uint16_t *dst, uint64_t count, int dtype) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count;
+         i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t bits = __float_as_uint(src[i]);
+        uint16_t o;
+        if (dtype == AG_BF16) {
+            if ((bits & 0x7FFFFFFFu) > 0x7F800000u) o = (uint16_t)((bits >> 16) | 0x0040u);
+            else o = (uint16_t)((bits + 0x7FFFu + ((bits >> 16) & 1u)) >> 16);
+        } else {
+            if ((bits & 0x7FFFFFFFu) > 0x7F800000u)
+                o = (uint16_t)(((bits >> 16) & 0x8000u) | 0x7E00u | ((bits & 0x7FFFFFu) >> 13));
+            else {
+                const uint32_t sign = (bits >> 16) & 0x8000u, exp = (bits >> 23) & 0xFFu;
+                uint32_t man = bits & 0x7FFFFFu;
+                const int e = (int)exp - 112;
+                if (exp == 0xFFu || e >= 0x1F) o = (uint16_t)(sign | 0x7C00u);
+                else if (e <= 0) {
+                    if (e < -10) o = (uint16_t)sign;
+                    else {
+                        man |= 0x800000u;
+                        const uint32_t shift = (uint32_t)(14 - e);
+                        uint32_t hm = man >> shift;
+                        const uint32_t rem = man & ((1u << shift) - 1u), half = 1u << (shift - 1);
+                        if (rem > half || (rem == half && (hm & 1u))) hm++;
+                        o = (uint16_t)(sign | hm);
+                    }
+                } else {
+                    uint32_t h = ((uint32_t)e << 10) | (man >> 13);
+                    const uint32_t rem = man & 0x1FFFu;
+                    if (rem > 0x1000u || (rem == 0x1000u && (h & 1u))) h++;
+                    o = (uint16_t)(sign | h);
+                }
+            }
+        }
+        dst[i] = o;
+    }
+}
+
+}  // namespace
+
+int gather_grid_blocks(uint64_t n, uint32_t row_bytes) {
+    // Whole waves of 148 SMs x 8 resident 256-thread blocks; fewer blocks when
+    // the batch is small enough that one pass covers it.
+    const uint32_t vecs = row_bytes >> 4;
+    const int lpr = vecs <= 4 ? 4 : vecs <= 8 ? 8 : vecs <= 16 ? 16 : 32;
+    const uint64_t rows_per_block = (uint64_t)(kThreads / lpr) * kInFlight;
+    const uint64_t need = (n + rows_per_block - 1) / rows_per_block;
+    const uint64_t full = (uint64_t)kSMs * 8;
+    if (need >= full) return (int)full;
+    const uint64_t waves = (need + kSMs - 1) / kSMs;
+    return (int)(waves ? waves * kSMs : kSMs);
+}
+
+cudaError_t launch_gather(const GatherArgs &a, int dtype, cudaStream_t st) {
+    if (a.n == 0) return cudaSuccess;
+    const bool vec_ok = (a.row_bytes % 16 == 0) && (((uintptr_t)a.payload) % 16 == 0) &&
+                        (((uintptr_t)a.out) % 16 == 0);
+    if (vec_ok) {
+        const int blocks = gather_grid_blocks(a.n, a.row_bytes);
+        switch (dtype) {
+            case AG_F32: return launch_vec<AG_F32>(a, blocks, st);
+            case AG_F16: return launch_vec<AG_F16>(a, blocks, st);
+            default: return launch_vec<AG_BF16>(a, blocks, st);
+        }
+    }
+    const uint64_t total = a.n * a.dim;
+    uint64_t blocks = (total + kThreads - 1) / kThreads;
+    if (blocks > (uint64_t)kSMs * 8) blocks = (uint64_t)kSMs * 8;
+    switch (dtype) {
+        case AG_F32: k_gather_elem<AG_F32><<<(int)blocks, kThreads, 0, st>>>(a); break;
+        case AG_F16: k_gather_elem<AG_F16><<<(int)blocks, kThreads, 0, st>>>(a); break;
+        default: k_gather_elem<AG_BF16><<<(int)blocks, kThreads, 0, st>>>(a); break;
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t launch_encode(const float *src, void *dst, uint64_t count, int dtype, cudaStream_t st) {
+    if (count == 0) return cudaSuccess;
+    if (dtype == AG_F32) return cudaMemcpyAsync(dst, src, count * 4, cudaMemcpyDeviceToDevice, st);
+    uint64_t blocks = (count + 255) / 256;
+    if (blocks > (uint64_t)kSMs * 8) blocks = (uint64_t)kSMs * 8;
+    k_encode<<<(int)blocks, 256, 0, st>>>(src, (uint16_t *)dst, count, dtype);
+    return cudaGetLastError();
+}
+
+}  // namespace ag

@@ -1,0 +1,797 @@
+// Homogeneous k-hop neighbor sampler with frontier dedup and relabel.
+//
+// Computes exactly what the reference's NeighborSampler::sample computes
+// (crates/aethergraph-core/src/loader/sampler.rs:845-961 with the hop loop at
+// :754-842 and the per-node dispatch at :1178-1235), but as a short chain of
+// data-parallel kernels per batch instead of one sequential loop:
+//
+//   insert   every seed (or every edge of a hop) is inserted into a hash table
+//            keyed by vertex id with atomicMin(position): the smallest position
+//            that names a vertex is its first sighting.
+//   assign   one single-pass scan over the items in position order turns the
+//            first-sighting flags into local ids (= discovery order, exactly
+//            the order the sequential reference assigns them in), appends the
+//            new vertices to `nodes` and to the next frontier, and in the same
+//            pass reads each new vertex's CSR row bounds and scans how many
+//            edges and how many RNG draws it will need in the next hop.
+//   pick     a group of lanes per frontier vertex reproduces the reference's
+//            choice of row positions — take-all (:1312-1328), Floyd
+//            (:1332-1380), with replacement (:1289-1308) or the weighted
+//            Efraimidis-Spirakis keys (:1418-1469) — writes the edges at their
+//            scanned slots and inserts the destinations for the next assign.
+//   finalize every edge and seed reads its endpoint's final local id from the
+//            table; the int64 views the Python API exposes are written here.
+//
+// The reference draws from one sequential WyRand stream per batch.  WyRand's
+// state is an additive counter, so draw d is a pure function of (seed, d); the
+// scan of per-vertex draw counts gives every vertex the index of its first
+// draw, and the parallel picks are bit-identical to the sequential ones.
+#include <string.h>
+
+#include <algorithm>
+#include <vector>
+
+#include "common.cuh"
+#include "internal.h"
+#include "sampler.cuh"
+
+namespace ag {
+
+namespace {
+
+constexpr int kAssignThreads = 512;  // one item per thread, one tile per block
+constexpr int kPickThreads = 256;
+constexpr int kLargeK = 1024;        // largest fanout the k > 32 path keeps in shared memory
+
+enum : int { kModeUniform = 0, kModeReplace = 1, kModeWeighted = 2 };
+
+struct SampleParams {
+    const uint64_t *offsets;
+    const uint32_t *dst;
+    const float *weights;
+    uint64_t num_nodes, num_edges;
+    DedupTable table;
+    BatchState *state;
+    TileDesc *tiles;
+    uint32_t epoch;
+    uint64_t seed;
+    int rng_mode;
+    int mode;
+    // outputs
+    uint32_t *nodes;
+    uint32_t *edge_src, *edge_dst, *src_local, *dst_local, *seed_locals;
+    uint64_t *edge_ids;
+    uint64_t cap_nodes, cap_edges;
+    // scratch
+    uint32_t *slot_of_seed;
+    uint32_t *slot_of_edge;
+    FrontierEntry *frontier_in, *frontier_out;
+    uint64_t frontier_cap;
+};
+
+// Row bounds with the reference's guard (graph/csr.rs:318-335): an inverted
+// pair or one past num_edges is an empty row.
+__device__ __forceinline__ void row_bounds(const uint64_t *offsets, uint64_t num_nodes,
+                                           uint64_t num_edges, uint32_t id, uint64_t &off,
+                                           uint64_t &deg) {
+    off = 0; deg = 0;
+    if ((uint64_t)id >= num_nodes) return;
+    const uint64_t a = __ldg(offsets + id), b = __ldg(offsets + id + 1);
+    if (a > b || b > num_edges) return;
+    off = a; deg = b - a;
+}
+
+// How many edges and draws a row of `deg` asks for at fanout k
+// (sampler.rs:1226-1233 uniform, :1289-1308 replace, :1427-1457 weighted).
+__device__ __forceinline__ void row_demand(int mode, uint64_t deg, uint32_t k, uint32_t &take,
+                                           uint64_t &draws) {
+    take = 0; draws = 0;
+    if (deg == 0 || k == 0) return;
+    if (mode == kModeReplace) { take = k; draws = k; return; }
+    if ((uint64_t)k >= deg) { take = (uint32_t)deg; return; }
+    take = k;
+    draws = (mode == kModeWeighted) ? deg : (uint64_t)k;
+}
+
+// ------------------------------------------------------------ seed insert --
+__global__ void k_insert_seeds(SampleParams p, const uint32_t *seeds, uint32_t n_seeds) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_seeds) return;
+    const uint32_t id = seeds[i];
+    if ((uint64_t)id >= p.num_nodes) {
+        atomicOr(&p.state->error, kErrBadSeed);
+        p.slot_of_seed[i] = 0xFFFFFFFFu;
+        return;
+    }
+    p.slot_of_seed[i] = table_insert_min(p.table, id, kPending | i, &p.state->error);
+}
+
+// ----------------------------------------------------------------- assign --
+// Items of stage s in position order: the seeds (s == 0) or the edges of hop
+// s - 1.  next_k is the fanout of the hop the new vertices will be expanded
+// at, or 0 after the last hop.
+__global__ void __launch_bounds__(kAssignThreads)
+k_assign(SampleParams p, uint32_t stage, uint32_t n_seeds, uint32_t next_k, int has_next) {
+    __shared__ uint32_t s_tile;
+    __shared__ ScanVal s_warp[kAssignThreads / 32];
+    __shared__ ScanVal s_prefix;
+
+    BatchState *bs = p.state;
+    if (threadIdx.x == 0) {
+        s_tile = atomicAdd(&bs->ticket, 1u);
+        if (s_tile == gridDim.x - 1) bs->ticket = 0;  // every ticket of this launch is taken
+    }
+    __syncthreads();
+    const uint32_t tile = s_tile;
+    const StageInfo si = bs->stage[stage];
+    const uint32_t count = (stage == 0) ? n_seeds : si.hop_edges;
+    const uint32_t n_tiles = max(1u, (count + kAssignThreads - 1) / kAssignThreads);
+    if (tile >= n_tiles) return;
+
+    const uint32_t item = tile * kAssignThreads + threadIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+    // First sighting?  The table holds kPending | position of the smallest
+    // position that named the vertex.
+    uint32_t slot = 0xFFFFFFFFu, id = 0;
+    bool first = false;
+    if (item < count) {
+        slot = (stage == 0) ? p.slot_of_seed[item] : p.slot_of_edge[si.n_edges + item];
+        if (slot != 0xFFFFFFFFu) {
+            const uint64_t cur = __ldcg((const unsigned long long *)&p.table.slots[slot]);
+            first = ((uint32_t)cur == (kPending | item));
+            id = (uint32_t)(cur >> 32);
+        }
+    }
+    ScanVal v{first ? 1u : 0u, 0u, 0ull};
+    uint64_t off = 0, deg = 0;
+    if (first && has_next) {
+        row_bounds(p.offsets, p.num_nodes, p.num_edges, id, off, deg);
+        if (deg > 0xFFFFFFFFull) { atomicOr(&bs->error, kErrCapacity); deg = 0; }
+        row_demand(p.mode, deg, next_k, v.take, v.draws);
+    }
+
+    // Block scan: warp scans, then the warp totals.
+    const ScanVal incl = warp_inclusive_scan(v, lane);
+    if (lane == 31) s_warp[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        ScanVal w = (lane < kAssignThreads / 32) ? s_warp[lane] : ScanVal{0, 0, 0};
+        const ScanVal wi = warp_inclusive_scan(w, lane);
+        const ScanVal block_total = ScanVal{__shfl_sync(0xffffffffu, wi.flags, 31),
+                                            __shfl_sync(0xffffffffu, wi.take, 31),
+                                            __shfl_sync(0xffffffffu, wi.draws, 31)};
+        if (lane < kAssignThreads / 32) s_warp[lane] = ScanVal{wi.flags - w.flags, wi.take - w.take, wi.draws - w.draws};
+        const ScanVal prefix = lookback_exclusive(p.tiles, tile, p.epoch, block_total, lane, &bs->error);
+        if (lane == 0) {
+            s_prefix = prefix;
+            if (tile == n_tiles - 1) {
+                // Totals of the stage: hand over to the next one.
+                const ScanVal tot = prefix + block_total;
+                StageInfo nx;
+                nx.n_nodes = si.n_nodes + tot.flags;
+                nx.n_edges = si.n_edges + ((stage == 0) ? 0u : count);
+                nx.frontier_n = tot.flags;
+                nx.hop_edges = tot.take;
+                nx.draws = si.draws + si.hop_draws;
+                nx.hop_draws = tot.draws;
+                bs->stage[stage + 1] = nx;
+                bs->nodes_per_stage[stage] = tot.flags;
+            }
+        }
+    }
+    __syncthreads();
+    if (!first) return;
+
+    const ScanVal base = s_prefix + s_warp[warp];
+    const ScanVal excl = ScanVal{base.flags + incl.flags - v.flags, base.take + incl.take - v.take,
+                                 base.draws + incl.draws - v.draws};
+    const uint32_t rank = excl.flags;
+    const uint32_t local = si.n_nodes + rank;
+    if ((uint64_t)local >= p.cap_nodes || (uint64_t)rank >= p.frontier_cap) {
+        atomicOr(&bs->error, kErrCapacity);
+        return;
+    }
+    p.nodes[local] = id;
+    p.table.slots[slot] = ((uint64_t)id << 32) | local;  // final: readers accept either form
+    if (has_next) {
+        FrontierEntry fe;
+        fe.off = off;
+        fe.dbase = si.draws + si.hop_draws + excl.draws;
+        fe.id = id;
+        fe.local = local;
+        fe.deg = (uint32_t)deg;
+        fe.ebase = excl.take;
+        p.frontier_out[rank] = fe;
+    }
+}
+
+// ------------------------------------------------------------------- pick --
+__device__ __forceinline__ uint32_t draw_u32(const SampleParams &p, uint32_t hop, uint32_t vertex,
+                                             uint64_t dbase, uint32_t slot) {
+    if (p.rng_mode == AG_RNG_PHILOX) return philox_u32(p.seed, hop, vertex, slot);
+    return (uint32_t)wyrand_at(p.seed, dbase + slot);  // next_u32: genstamp.rs:199-201
+}
+
+__device__ __forceinline__ void emit_edge(const SampleParams &p, const StageInfo &si,
+                                          const FrontierEntry &fe, uint32_t t, uint64_t pos) {
+    const uint32_t e_rel = fe.ebase + t;
+    const uint64_t e = (uint64_t)si.n_edges + e_rel;
+    if (e >= p.cap_edges) { atomicOr(&p.state->error, kErrCapacity); return; }
+    const uint32_t d = ld_stream_u32(p.dst + pos);
+    if (p.edge_src) p.edge_src[e] = fe.id;
+    p.edge_dst[e] = d;
+    if (p.edge_ids) p.edge_ids[e] = pos;
+    p.src_local[e] = fe.local;
+    if ((uint64_t)d >= p.num_nodes) {
+        // Only reachable on a graph that skipped validation; the reference drops
+        // such an edge (sampler.rs:736-739), which a slot-scanned layout cannot.
+        atomicOr(&p.state->error, kErrBadDst);
+        p.slot_of_edge[e] = 0xFFFFFFFFu;
+        return;
+    }
+    p.slot_of_edge[e] = table_insert_min(p.table, d, kPending | e_rel, &p.state->error);
+}
+
+// Fanout <= G <= 32: G lanes per frontier vertex, lane t owns edge slot t.
+template <int G>
+__global__ void __launch_bounds__(kPickThreads)
+k_pick_small(SampleParams p, uint32_t stage, uint32_t hop, uint32_t k) {
+    const StageInfo si = p.state->stage[stage];
+    const uint32_t node = (blockIdx.x * kPickThreads + threadIdx.x) / G;
+    const uint32_t t = threadIdx.x % G;
+    const bool active = node < si.frontier_n;
+    FrontierEntry fe{};
+    if (active) fe = p.frontier_in[node];
+    const uint32_t deg = fe.deg;
+    const bool sampled = active && p.mode != kModeReplace && deg > k;  // Floyd row
+    uint32_t pick = t;                                                  // take-all: row order
+    uint32_t ip = 0;
+    if (active && p.mode == kModeReplace && deg > 0 && t < k) {
+        // sampler.rs:1298-1300: k independent draws over the whole row
+        pick = (uint32_t)(((uint64_t)draw_u32(p, hop, fe.id, fe.dbase, t) * deg) >> 32);
+    } else if (sampled && t < k) {
+        // sampler.rs:1345-1346: i runs over deg-k .. deg-1, j = rand_below(i + 1)
+        ip = deg - k + t;
+        pick = (uint32_t)(((uint64_t)draw_u32(p, hop, fe.id, fe.dbase, t) * ((uint64_t)ip + 1)) >> 32);
+    }
+    // Floyd's "already taken?" is sequential in t (sampler.rs:1347-1352):
+    // resolve slot s against the finished slots below it, one ballot per s.
+    const uint32_t gshift = (threadIdx.x & 31) & ~(G - 1);
+    const uint32_t gmask = (G == 32) ? 0xffffffffu : ((1u << G) - 1u);
+    for (uint32_t s = 1; s < k; ++s) {
+        const uint32_t js = __shfl_sync(0xffffffffu, pick, s, G);
+        const bool hit = sampled && t < s && pick == js;
+        const uint32_t m = (__ballot_sync(0xffffffffu, hit) >> gshift) & gmask;
+        if (sampled && t == s && m) pick = ip;
+    }
+    if (!active) return;
+    uint32_t take;
+    uint64_t draws;
+    row_demand(p.mode, deg, k, take, draws);
+    if (t < take) emit_edge(p, si, fe, t, fe.off + pick);
+}
+
+// Fanout > 32: one warp per frontier vertex; finished picks live in shared
+// memory so later slots can be checked against all earlier ones.
+__global__ void __launch_bounds__(128)
+k_pick_large(SampleParams p, uint32_t stage, uint32_t hop, uint32_t k) {
+    __shared__ uint32_t s_picks[4][kLargeK];
+    const StageInfo si = p.state->stage[stage];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t node = blockIdx.x * 4 + warp;
+    if (node >= si.frontier_n) return;
+    const FrontierEntry fe = p.frontier_in[node];
+    const uint32_t deg = fe.deg;
+    uint32_t take;
+    uint64_t draws;
+    row_demand(p.mode, deg, k, take, draws);
+    const bool sampled = p.mode != kModeReplace && deg > k;
+    uint32_t *picks = s_picks[warp];
+    for (uint32_t c = 0; c < take; c += 32) {
+        const uint32_t t = c + lane;
+        const bool in = t < take;
+        uint32_t pick = t, ip = 0;
+        bool hit_prev = false;
+        if (in && p.mode == kModeReplace) {
+            pick = (uint32_t)(((uint64_t)draw_u32(p, hop, fe.id, fe.dbase, t) * deg) >> 32);
+        } else if (in && sampled) {
+            ip = deg - k + t;
+            pick = (uint32_t)(((uint64_t)draw_u32(p, hop, fe.id, fe.dbase, t) * ((uint64_t)ip + 1)) >> 32);
+            for (uint32_t q = 0; q < c; ++q) hit_prev |= (picks[q] == pick);
+        }
+        if (sampled) {
+            for (uint32_t s = 0; s < 32; ++s) {
+                const uint32_t js = __shfl_sync(0xffffffffu, pick, s);
+                const bool hit = in && (uint32_t)lane < s && pick == js;
+                const uint32_t m = __ballot_sync(0xffffffffu, hit);
+                if (in && (uint32_t)lane == s && (m || hit_prev)) pick = ip;
+            }
+            if (in) picks[t] = pick;
+            __syncwarp();
+        }
+        if (in) emit_edge(p, si, fe, t, fe.off + pick);
+    }
+}
+
+// Weighted sampling without replacement, fanout <= 32, one warp per vertex.
+// Selection follows sampler.rs:1418-1469: one 64-bit draw per row position in
+// row order, key = -ln(u) / w in f64 with u = ((bits >> 11) + 1) * 2^-53
+// (sampler.rs:52-55), +inf for a weight that is not finite and positive; the k
+// smallest keys win.  The winners are emitted in ascending (key, position)
+// order; the reference's own order comes from Rust's select_nth_unstable_by and
+// is not defined by its source tree.  The warp streams the row 32 positions at a
+// time and keeps the k best so far sorted across its lanes.
+__device__ __forceinline__ bool key_less(double ka, uint32_t pa, double kb, uint32_t pb) {
+    return ka < kb || (ka == kb && pa < pb);
+}
+
+__global__ void __launch_bounds__(kPickThreads)
+k_pick_weighted(SampleParams p, uint32_t stage, uint32_t hop, uint32_t k) {
+    const StageInfo si = p.state->stage[stage];
+    const int lane = threadIdx.x & 31;
+    const uint32_t node = (blockIdx.x * kPickThreads + threadIdx.x) >> 5;
+    if (node >= si.frontier_n) return;
+    const FrontierEntry fe = p.frontier_in[node];
+    const uint32_t deg = fe.deg;
+    if (deg == 0 || k == 0) return;
+    if (k >= deg) {
+        for (uint32_t t = lane; t < deg; t += 32) emit_edge(p, si, fe, t, fe.off + t);
+        return;
+    }
+    const double inf = __longlong_as_double(0x7FF0000000000000ll);
+    double best_key = inf;
+    uint32_t best_pos = 0xFFFFFFFFu;  // sentinel: sorts after every real (key, position)
+    for (uint32_t c = 0; c < deg; c += 32) {
+        const uint32_t pos = c + lane;
+        double key = inf;
+        uint32_t cpos = 0xFFFFFFFFu;
+        if (pos < deg) {
+            const uint64_t bits = (p.rng_mode == AG_RNG_PHILOX)
+                ? (((uint64_t)philox_u32(p.seed, hop, fe.id, 2 * pos) << 32) | philox_u32(p.seed, hop, fe.id, 2 * pos + 1))
+                : wyrand_at(p.seed, fe.dbase + pos);
+            const double w = (double)__ldg(p.weights + fe.off + pos);
+            if (isfinite(w) && w > 0.0) {
+                const double u = ((double)(bits >> 11) + 1.0) * (1.0 / 9007199254740992.0);
+                key = -log(u) / w;
+            }
+            cpos = pos;
+        }
+        for (;;) {
+            const double tk = __shfl_sync(0xffffffffu, best_key, k - 1);
+            const uint32_t tp = __shfl_sync(0xffffffffu, best_pos, k - 1);
+            const uint32_t m = __ballot_sync(0xffffffffu, cpos != 0xFFFFFFFFu && key_less(key, cpos, tk, tp));
+            if (!m) break;
+            const int src = __ffs(m) - 1;
+            const double ck = __shfl_sync(0xffffffffu, key, src);
+            const uint32_t cp = __shfl_sync(0xffffffffu, cpos, src);
+            // Insert (ck, cp) into the sorted lanes: it lands after every entry
+            // that is smaller, the rest shift up by one.
+            const uint32_t smaller = __ballot_sync(0xffffffffu, key_less(best_key, best_pos, ck, cp));
+            const int at = __popc(smaller);
+            const double up_k = __shfl_up_sync(0xffffffffu, best_key, 1);
+            const uint32_t up_p = __shfl_up_sync(0xffffffffu, best_pos, 1);
+            if (lane == at) { best_key = ck; best_pos = cp; }
+            else if (lane > at) { best_key = up_k; best_pos = up_p; }
+            if (lane == src) cpos = 0xFFFFFFFFu;
+        }
+    }
+    if ((uint32_t)lane < k) emit_edge(p, si, fe, lane, fe.off + best_pos);
+}
+
+// --------------------------------------------------------------- finalize --
+struct FinalizeArgs {
+    int64_t *n_id, *edge_index_local, *e_id, *seed_index;
+    ag_sample_counts *counts;
+    uint32_t n_seeds, num_hops, final_stage;
+};
+
+__global__ void k_finalize(SampleParams p, FinalizeArgs f) {
+    BatchState *bs = p.state;
+    const StageInfo fin = bs->stage[f.final_stage];
+    const uint32_t n_nodes = min((uint64_t)fin.n_nodes, p.cap_nodes);
+    const uint32_t n_edges = min((uint64_t)fin.n_edges, p.cap_edges);
+    const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t e = tid; e < n_edges; e += stride) {
+        const uint32_t slot = p.slot_of_edge[e];
+        const uint32_t dl = (slot == 0xFFFFFFFFu) ? 0xFFFFFFFFu
+                          : (uint32_t)__ldcg((const unsigned long long *)&p.table.slots[slot]);
+        p.dst_local[e] = dl;
+        if (f.edge_index_local) {
+            f.edge_index_local[e] = (int64_t)dl;                       // row 0: sampled neighbor
+            f.edge_index_local[(uint64_t)n_edges + e] = (int64_t)p.src_local[e];  // row 1: expanded node
+        }
+        if (f.e_id && p.edge_ids) f.e_id[e] = (int64_t)p.edge_ids[e];
+    }
+    for (uint64_t i = tid; i < f.n_seeds; i += stride) {
+        const uint32_t slot = p.slot_of_seed[i];
+        const uint32_t sl = (slot == 0xFFFFFFFFu) ? 0xFFFFFFFFu
+                          : (uint32_t)__ldcg((const unsigned long long *)&p.table.slots[slot]);
+        p.seed_locals[i] = sl;
+        if (f.seed_index) f.seed_index[i] = (int64_t)sl;
+    }
+    if (f.n_id)
+        for (uint64_t i = tid; i < n_nodes; i += stride) f.n_id[i] = (int64_t)p.nodes[i];
+    if (tid == 0) {
+        ag_sample_counts c{};
+        c.num_nodes = n_nodes;
+        c.num_edges = n_edges;
+        c.num_seeds = f.n_seeds;
+        c.num_hops = f.num_hops;
+        for (uint32_t s = 0; s <= f.num_hops; ++s) c.nodes_per_hop[s] = bs->nodes_per_stage[s];
+        for (uint32_t h = 0; h < f.num_hops; ++h) c.edges_per_hop[h] = bs->stage[h + 1].hop_edges;
+        c.draws = fin.draws - bs->stage[0].draws;
+        c.error = bs->error;
+        if ((uint64_t)fin.n_nodes > p.cap_nodes || (uint64_t)fin.n_edges > p.cap_edges) c.error |= kErrCapacity;
+        *f.counts = c;
+        bs->stream_pos = fin.draws;  // a bare sampler keeps consuming the same stream
+    }
+}
+
+// Stage 0 bookkeeping at the head of a batch.
+__global__ void k_begin(BatchState *bs, int reset_pos) {
+    if (reset_pos) bs->stream_pos = 0;
+    StageInfo s0{};
+    s0.draws = bs->stream_pos;
+    bs->stage[0] = s0;
+    bs->error = 0;
+    bs->ticket = 0;
+}
+
+uint64_t next_pow2(uint64_t v) {
+    uint64_t p = 1;
+    while (p < v) p <<= 1;
+    return p;
+}
+
+}  // namespace
+}  // namespace ag
+
+using namespace ag;
+
+struct ag_sampler {
+    const ag_graph *g = nullptr;
+    ag_sampling_config cfg{};
+    int device = 0;
+    int mode = kModeUniform;
+    uint64_t seed = 0;
+    bool reset_pos = true;
+    uint32_t epoch = 0;
+    // sizing
+    uint64_t cap_seeds = 0, max_nodes = 0, max_edges = 0, max_frontier = 0, max_hop_edges = 0;
+    // scratch (device)
+    uint64_t *table = nullptr;
+    uint64_t table_cap = 0;
+    FrontierEntry *frontier[2] = {nullptr, nullptr};
+    uint32_t *slot_of_seed = nullptr, *slot_of_edge = nullptr;
+    TileDesc *tiles = nullptr;
+    uint64_t n_tiles = 0;
+    BatchState *state = nullptr;
+    uint32_t *seeds_dev = nullptr;
+    ag_sample_counts *counts_dev = nullptr;
+    // pinned host
+    uint32_t *seeds_pinned = nullptr;
+    ag_sample_counts *counts_host = nullptr;
+    cudaEvent_t done = nullptr;
+    bool in_flight = false;
+    // buffers handed out by ag_sample (library-allocated variant)
+    std::vector<void *> owned;
+};
+
+namespace {
+
+void compute_bounds(const ag_sampler *s, uint64_t n_seeds, uint64_t *max_nodes, uint64_t *max_edges,
+                    uint64_t *max_frontier, uint64_t *max_hop_edges) {
+    const uint64_t N = s->g->num_nodes;
+    uint64_t f = std::min<uint64_t>(n_seeds, N), nodes = f, edges = 0, mf = f, mhe = 0;
+    for (uint32_t h = 0; h < s->cfg.num_hops; ++h) {
+        const uint64_t e = f * s->cfg.fanout[h];
+        edges += e;
+        mhe = std::max(mhe, e);
+        f = std::min<uint64_t>(e, N);
+        if (h + 1 < s->cfg.num_hops) mf = std::max(mf, f);
+        nodes += f;
+    }
+    if (max_nodes) *max_nodes = std::min<uint64_t>(nodes, N);
+    if (max_edges) *max_edges = edges;
+    if (max_frontier) *max_frontier = mf;
+    if (max_hop_edges) *max_hop_edges = mhe;
+}
+
+void free_scratch(ag_sampler *s) {
+    cudaFree(s->table); cudaFree(s->frontier[0]); cudaFree(s->frontier[1]);
+    cudaFree(s->slot_of_seed); cudaFree(s->slot_of_edge); cudaFree(s->tiles);
+    cudaFree(s->seeds_dev);
+    if (s->seeds_pinned) cudaFreeHost(s->seeds_pinned);
+    s->table = nullptr; s->frontier[0] = s->frontier[1] = nullptr;
+    s->slot_of_seed = s->slot_of_edge = nullptr; s->tiles = nullptr;
+    s->seeds_dev = nullptr; s->seeds_pinned = nullptr;
+}
+
+int32_t ensure_scratch(ag_sampler *s, uint64_t n_seeds) {
+    if (n_seeds <= s->cap_seeds && s->table) return AG_OK;
+    if (s->in_flight) { AG_CUDA(cudaEventSynchronize(s->done)); }
+    free_scratch(s);
+    const uint64_t cap = std::max<uint64_t>(n_seeds, 1);
+    compute_bounds(s, cap, &s->max_nodes, &s->max_edges, &s->max_frontier, &s->max_hop_edges);
+    if (s->max_nodes >= 0x7FFFFFFFull || s->max_hop_edges >= 0x7FFFFFFFull || s->max_edges >= 0xFFFFFFFFull)
+        return fail(AG_ERR_VALUE, "batch too large: %llu seeds with this fanout can emit %llu edges "
+                    "(limit 2^31 per hop)", (unsigned long long)n_seeds, (unsigned long long)s->max_edges);
+    s->table_cap = std::max<uint64_t>(1024, next_pow2(2 * s->max_nodes));
+    AG_CUDA(cudaMalloc(&s->table, s->table_cap * 8));
+    const uint64_t fcap = std::max<uint64_t>(s->max_frontier, 1);
+    AG_CUDA(cudaMalloc(&s->frontier[0], fcap * sizeof(FrontierEntry)));
+    AG_CUDA(cudaMalloc(&s->frontier[1], fcap * sizeof(FrontierEntry)));
+    AG_CUDA(cudaMalloc(&s->slot_of_seed, cap * 4));
+    AG_CUDA(cudaMalloc(&s->slot_of_edge, std::max<uint64_t>(s->max_edges, 1) * 4));
+    s->n_tiles = std::max<uint64_t>(std::max(cap, s->max_hop_edges) / kAssignThreads + 2, 2);
+    AG_CUDA(cudaMalloc(&s->tiles, s->n_tiles * sizeof(TileDesc)));
+    AG_CUDA(cudaMemset(s->tiles, 0, s->n_tiles * sizeof(TileDesc)));
+    AG_CUDA(cudaMalloc(&s->seeds_dev, cap * 4));
+    AG_CUDA(cudaHostAlloc(&s->seeds_pinned, cap * 4, cudaHostAllocDefault));
+    s->cap_seeds = cap;
+    s->epoch = 0;
+    return AG_OK;
+}
+
+}  // namespace
+
+extern "C" int32_t ag_sampler_create(const ag_graph *g, const ag_sampling_config *cfg, ag_sampler **out) {
+    if (!g || !cfg || !out) return fail(AG_ERR_VALUE, "ag_sampler_create: null argument");
+    if (cfg->num_hops == 0 || cfg->num_hops > AG_MAX_HOPS)
+        return fail(AG_ERR_VALUE, "num_neighbors must list between 1 and %d hops (got %u)", AG_MAX_HOPS, cfg->num_hops);
+    // SamplerConfigError::WeightsMissing (sampler.rs:331-337)
+    if (cfg->weighted && !g->weights)
+        return fail(AG_ERR_VALUE, "weighted sampling requested, but the graph has no edge weights");
+    if (cfg->weighted && cfg->replace)
+        return fail(AG_ERR_VALUE, "weighted sampling with replacement is not supported on the GPU path");
+    if (cfg->rng_mode != AG_RNG_WYRAND_EXACT && cfg->rng_mode != AG_RNG_PHILOX)
+        return fail(AG_ERR_VALUE, "unknown rng_mode %d", cfg->rng_mode);
+    for (uint32_t h = 0; h < cfg->num_hops; ++h) {
+        if (cfg->weighted && cfg->fanout[h] > 32)
+            return fail(AG_ERR_VALUE, "weighted sampling supports a fanout of at most 32 per hop (hop %u asks %u)", h, cfg->fanout[h]);
+        if (cfg->fanout[h] > (uint32_t)kLargeK)
+            return fail(AG_ERR_VALUE, "fanout of at most %d per hop is supported (hop %u asks %u)", kLargeK, h, cfg->fanout[h]);
+    }
+    DeviceGuard guard(g->device);
+    if (!guard.ok) return AG_ERR_CUDA;
+    ag_sampler *s = new ag_sampler();
+    s->g = g;
+    s->cfg = *cfg;
+    s->device = g->device;
+    s->mode = cfg->weighted ? kModeWeighted : (cfg->replace ? kModeReplace : kModeUniform);
+    s->seed = cfg->seed;
+    int32_t st = AG_OK;
+    do {
+        if (cudaMalloc(&s->state, sizeof(BatchState)) != cudaSuccess ||
+            cudaMemset(s->state, 0, sizeof(BatchState)) != cudaSuccess ||
+            cudaMalloc(&s->counts_dev, sizeof(ag_sample_counts)) != cudaSuccess ||
+            cudaHostAlloc(&s->counts_host, sizeof(ag_sample_counts), cudaHostAllocDefault) != cudaSuccess ||
+            cudaEventCreateWithFlags(&s->done, cudaEventDisableTiming) != cudaSuccess) {
+            st = fail(AG_ERR_CUDA, "sampler allocation failed: %s", cudaGetErrorString(cudaGetLastError()));
+            break;
+        }
+        st = ensure_scratch(s, std::max<uint32_t>(cfg->max_seeds, 1));
+    } while (0);
+    if (st != AG_OK) { ag_sampler_free(s); return st; }
+    *out = s;
+    return AG_OK;
+}
+
+extern "C" void ag_sampler_free(ag_sampler *s) {
+    if (!s) return;
+    DeviceGuard guard(s->device);
+    if (s->in_flight && s->done) cudaEventSynchronize(s->done);
+    free_scratch(s);
+    for (void *p : s->owned) cudaFree(p);
+    cudaFree(s->state); cudaFree(s->counts_dev);
+    if (s->counts_host) cudaFreeHost(s->counts_host);
+    if (s->done) cudaEventDestroy(s->done);
+    delete s;
+}
+
+extern "C" int32_t ag_sampler_reseed(ag_sampler *s, uint64_t seed) {
+    if (!s) return fail(AG_ERR_VALUE, "ag_sampler_reseed: null sampler");
+    s->seed = seed;
+    s->reset_pos = true;
+    return AG_OK;
+}
+
+extern "C" int32_t ag_sampler_bounds(const ag_sampler *s, uint64_t n_seeds, uint64_t *max_nodes, uint64_t *max_edges) {
+    if (!s) return fail(AG_ERR_VALUE, "ag_sampler_bounds: null sampler");
+    compute_bounds(s, n_seeds, max_nodes, max_edges, nullptr, nullptr);
+    return AG_OK;
+}
+
+extern "C" int32_t ag_sample_into(ag_sampler *s, const uint32_t *seeds, uint64_t n_seeds, int32_t seeds_mem,
+                                  const ag_features *feats, ag_subgraph_buffers *buf, void *stream) {
+    if (!s || !buf || (!seeds && n_seeds)) return fail(AG_ERR_VALUE, "ag_sample_into: null argument");
+    if (!buf->nodes || !buf->edge_dst || !buf->src_local || !buf->dst_local || !buf->seed_locals)
+        return fail(AG_ERR_VALUE, "ag_sample_into: nodes, edge_dst, src_local, dst_local and seed_locals are required");
+    if (buf->cap_seeds < n_seeds) return fail(AG_ERR_VALUE, "seed_locals capacity %llu < %llu seeds",
+                                              (unsigned long long)buf->cap_seeds, (unsigned long long)n_seeds);
+    if (feats && buf->x && feats->device != s->device)
+        return fail(AG_ERR_VALUE, "feature store lives on device %d, sampler on %d", feats->device, s->device);
+    if (n_seeds >= 0x7FFFFFFFull) return fail(AG_ERR_VALUE, "too many seeds");
+    const ag_graph *g = s->g;
+    // Seeds::new (sampler.rs:230-239): name the first id at or past num_nodes.
+    if (seeds_mem == AG_MEM_HOST) {
+        for (uint64_t i = 0; i < n_seeds; ++i)
+            if ((uint64_t)seeds[i] >= g->num_nodes)
+                return fail(AG_ERR_SAMPLING, "seed node %u (position %llu) is out of range for %llu nodes",
+                            seeds[i], (unsigned long long)i, (unsigned long long)g->num_nodes);
+    }
+    DeviceGuard guard(s->device);
+    if (!guard.ok) return AG_ERR_CUDA;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (s->in_flight) { AG_CUDA(cudaEventSynchronize(s->done)); s->in_flight = false; }
+    AG_TRY(ensure_scratch(s, n_seeds));
+
+    const uint32_t n = (uint32_t)n_seeds;
+    const uint32_t *seeds_dev = seeds;
+    if (seeds_mem == AG_MEM_HOST && n) {
+        memcpy(s->seeds_pinned, seeds, (size_t)n * 4);
+        AG_CUDA(cudaMemcpyAsync(s->seeds_dev, s->seeds_pinned, (size_t)n * 4, cudaMemcpyHostToDevice, st));
+        seeds_dev = s->seeds_dev;
+    }
+
+    // Size the table for this batch (cleared per batch; it stays L2-resident).
+    uint64_t b_nodes, b_edges, b_front, b_hop;
+    compute_bounds(s, n, &b_nodes, &b_edges, &b_front, &b_hop);
+    const uint64_t tcap = std::min(s->table_cap, std::max<uint64_t>(1024, next_pow2(2 * b_nodes)));
+    uint32_t log2cap = 0;
+    while ((1ull << log2cap) < tcap) ++log2cap;
+    AG_CUDA(cudaMemsetAsync(s->table, 0xFF, tcap * 8, st));
+
+    SampleParams p{};
+    p.offsets = g->offsets; p.dst = g->dst; p.weights = g->weights;
+    p.num_nodes = g->num_nodes; p.num_edges = g->num_edges;
+    p.table = DedupTable{s->table, (uint32_t)(tcap - 1), 32u - log2cap};
+    p.state = s->state; p.tiles = s->tiles;
+    p.seed = s->seed; p.rng_mode = s->cfg.rng_mode; p.mode = s->mode;
+    p.nodes = buf->nodes; p.edge_src = buf->edge_src; p.edge_dst = buf->edge_dst;
+    p.src_local = buf->src_local; p.dst_local = buf->dst_local; p.seed_locals = buf->seed_locals;
+    p.edge_ids = s->cfg.track_edge_ids ? buf->edge_ids : nullptr;
+    p.cap_nodes = buf->cap_nodes; p.cap_edges = buf->cap_edges;
+    p.slot_of_seed = s->slot_of_seed; p.slot_of_edge = s->slot_of_edge;
+    p.frontier_cap = std::max<uint64_t>(s->max_frontier, 1);
+
+    k_begin<<<1, 1, 0, st>>>(s->state, s->reset_pos ? 1 : 0);
+    s->reset_pos = false;
+    if (n) k_insert_seeds<<<(n + 255) / 256, 256, 0, st>>>(p, seeds_dev, n);
+
+    const uint32_t H = s->cfg.num_hops;
+    // stage 0: seeds -> frontier[0]
+    p.epoch = ++s->epoch;
+    p.frontier_in = nullptr; p.frontier_out = s->frontier[0];
+    k_assign<<<std::max(1u, (n + kAssignThreads - 1) / kAssignThreads), kAssignThreads, 0, st>>>(
+        p, 0, n, s->cfg.fanout[0], 1);
+
+    uint64_t f_bound = std::min<uint64_t>(n, g->num_nodes);
+    for (uint32_t h = 0; h < H; ++h) {
+        const uint32_t k = s->cfg.fanout[h];
+        const uint64_t e_bound = f_bound * k;
+        p.frontier_in = s->frontier[h & 1];
+        p.frontier_out = s->frontier[(h + 1) & 1];
+        if (f_bound && k) {
+            if (s->mode == kModeWeighted) {
+                const uint32_t blocks = (uint32_t)((f_bound * 32 + kPickThreads - 1) / kPickThreads);
+                k_pick_weighted<<<blocks, kPickThreads, 0, st>>>(p, h + 1, h, k);
+            } else if (k > 32) {
+                k_pick_large<<<(uint32_t)((f_bound + 3) / 4), 128, 0, st>>>(p, h + 1, h, k);
+            } else {
+                const uint32_t G = k <= 4 ? 4 : k <= 8 ? 8 : k <= 16 ? 16 : 32;
+                const uint32_t blocks = (uint32_t)((f_bound * G + kPickThreads - 1) / kPickThreads);
+                switch (G) {
+                    case 4: k_pick_small<4><<<blocks, kPickThreads, 0, st>>>(p, h + 1, h, k); break;
+                    case 8: k_pick_small<8><<<blocks, kPickThreads, 0, st>>>(p, h + 1, h, k); break;
+                    case 16: k_pick_small<16><<<blocks, kPickThreads, 0, st>>>(p, h + 1, h, k); break;
+                    default: k_pick_small<32><<<blocks, kPickThreads, 0, st>>>(p, h + 1, h, k); break;
+                }
+            }
+        }
+        p.epoch = ++s->epoch;
+        const bool has_next = h + 1 < H;
+        k_assign<<<(uint32_t)std::max<uint64_t>(1, (e_bound + kAssignThreads - 1) / kAssignThreads),
+                   kAssignThreads, 0, st>>>(p, h + 1, n, has_next ? s->cfg.fanout[h + 1] : 0, has_next ? 1 : 0);
+        f_bound = std::min<uint64_t>(e_bound, g->num_nodes);
+    }
+    if (s->epoch > 0x3FFFFF00u) {  // epoch lives in 30 bits of the tile status
+        AG_CUDA(cudaMemsetAsync(s->tiles, 0, s->n_tiles * sizeof(TileDesc), st));
+        s->epoch = 0;
+    }
+
+    FinalizeArgs f{};
+    f.n_id = buf->n_id; f.edge_index_local = buf->edge_index_local; f.e_id = buf->e_id;
+    f.seed_index = buf->seed_index; f.counts = s->counts_dev;
+    f.n_seeds = n; f.num_hops = H; f.final_stage = H + 1;
+    const uint64_t work = std::max<uint64_t>(std::max(b_edges, b_nodes), std::max<uint64_t>(n, 1));
+    const uint32_t fblocks = (uint32_t)std::min<uint64_t>((work + 255) / 256, (uint64_t)kSMs * 8);
+    k_finalize<<<fblocks, 256, 0, st>>>(p, f);
+    AG_CUDA(cudaGetLastError());
+
+    if (feats && buf->x) {
+        GatherArgs ga{};
+        ga.payload = feats->payload; ga.row_begin = feats->row_begin; ga.rows = feats->rows;
+        ga.row_bytes = (uint32_t)(feats->dim * elem_size(feats->dtype)); ga.dim = (uint32_t)feats->dim;
+        ga.ids = buf->nodes; ga.ids64 = 0;
+        ga.n = std::min<uint64_t>(b_nodes, buf->cap_nodes);
+        ga.n_dev = &s->counts_dev->num_nodes;
+        ga.out = buf->x; ga.err = feats->err;
+        AG_CUDA(launch_gather(ga, feats->dtype, st));
+    }
+    AG_CUDA(cudaMemcpyAsync(s->counts_host, s->counts_dev, sizeof(ag_sample_counts), cudaMemcpyDeviceToHost, st));
+    AG_CUDA(cudaEventRecord(s->done, st));
+    s->in_flight = true;
+    return AG_OK;
+}
+
+extern "C" int32_t ag_sample_wait(ag_sampler *s, ag_sample_counts *counts) {
+    if (!s) return fail(AG_ERR_VALUE, "ag_sample_wait: null sampler");
+    if (!s->in_flight) return fail(AG_ERR_VALUE, "ag_sample_wait: no batch in flight");
+    DeviceGuard guard(s->device);
+    if (!guard.ok) return AG_ERR_CUDA;
+    AG_CUDA(cudaEventSynchronize(s->done));
+    s->in_flight = false;
+    const ag_sample_counts c = *s->counts_host;
+    if (counts) *counts = c;
+    if (c.error & kErrBadSeed) return fail(AG_ERR_SAMPLING, "a seed node is out of range for %llu nodes",
+                                           (unsigned long long)s->g->num_nodes);
+    if (c.error & kErrCapacity) return fail(AG_ERR_VALUE, "output buffers too small for the sampled subgraph");
+    if (c.error & kErrBadDst) return fail(AG_ERR_LOAD, "graph holds a destination outside [0, num_nodes); load it with full validation");
+    if (c.error) return fail(AG_ERR_WORKER, "sampler kernels reported error bits 0x%x", c.error);
+    return AG_OK;
+}
+
+extern "C" int32_t ag_sample(ag_sampler *s, const uint32_t *seeds, uint64_t n_seeds, const ag_features *feats,
+                             int32_t want_int64, ag_subgraph_buffers *buf, void *stream) {
+    if (!s || !buf) return fail(AG_ERR_VALUE, "ag_sample: null argument");
+    DeviceGuard guard(s->device);
+    if (!guard.ok) return AG_ERR_CUDA;
+    uint64_t mn, me;
+    compute_bounds(s, n_seeds, &mn, &me, nullptr, nullptr);
+    ag_subgraph_buffers b{};
+    b.cap_nodes = std::max<uint64_t>(mn, 1); b.cap_edges = std::max<uint64_t>(me, 1);
+    b.cap_seeds = std::max<uint64_t>(n_seeds, 1);
+    std::vector<void *> mine;
+    auto alloc = [&](void **ptr, uint64_t bytes) -> bool {
+        if (cudaMalloc(ptr, bytes) != cudaSuccess) return false;
+        mine.push_back(*ptr);
+        return true;
+    };
+    bool ok = alloc((void **)&b.nodes, b.cap_nodes * 4) && alloc((void **)&b.edge_src, b.cap_edges * 4) &&
+              alloc((void **)&b.edge_dst, b.cap_edges * 4) && alloc((void **)&b.src_local, b.cap_edges * 4) &&
+              alloc((void **)&b.dst_local, b.cap_edges * 4) && alloc((void **)&b.seed_locals, b.cap_seeds * 4);
+    if (ok && s->cfg.track_edge_ids) ok = alloc((void **)&b.edge_ids, b.cap_edges * 8);
+    if (ok && want_int64) {
+        ok = alloc((void **)&b.n_id, b.cap_nodes * 8) && alloc((void **)&b.edge_index_local, b.cap_edges * 16) &&
+             alloc((void **)&b.seed_index, b.cap_seeds * 8);
+        if (ok && s->cfg.track_edge_ids) ok = alloc((void **)&b.e_id, b.cap_edges * 8);
+    }
+    if (ok && feats) ok = alloc((void **)&b.x, b.cap_nodes * feats->dim * 4);
+    if (!ok) {
+        for (void *q : mine) cudaFree(q);
+        return fail(AG_ERR_CUDA, "ag_sample: out of device memory: %s", cudaGetErrorString(cudaGetLastError()));
+    }
+    const int32_t st = ag_sample_into(s, seeds, n_seeds, AG_MEM_HOST, feats, &b, stream);
+    if (st != AG_OK) { for (void *q : mine) cudaFree(q); return st; }
+    s->owned.insert(s->owned.end(), mine.begin(), mine.end());
+    *buf = b;
+    return AG_OK;
+}
+
+extern "C" int32_t ag_subgraph_release(ag_sampler *s, ag_subgraph_buffers *buf) {
+    if (!s || !buf) return fail(AG_ERR_VALUE, "ag_subgraph_release: null argument");
+    DeviceGuard guard(s->device);
+    if (s->in_flight) { cudaEventSynchronize(s->done); }
+    void *ptrs[] = {buf->nodes, buf->edge_src, buf->edge_dst, buf->edge_ids, buf->src_local, buf->dst_local,
+                    buf->seed_locals, buf->n_id, buf->edge_index_local, buf->e_id, buf->seed_index, buf->x};
+    for (void *q : ptrs) {
+        if (!q) continue;
+        auto it = std::find(s->owned.begin(), s->owned.end(), q);
+        if (it != s->owned.end()) { cudaFree(q); s->owned.erase(it); }
+    }
+    *buf = ag_subgraph_buffers{};
+    return AG_OK;
+}

@@ -1,0 +1,210 @@
+"""`CsrGraph` / `Graph`: a static CSR graph resident in GPU memory.
+
+Mirrors the reference's `aethergraph._core.CsrGraph` (python/aethergraph/_core.pyi:68-131;
+crates/aethergraph-py/src/graph.rs) for the methods the minibatch path uses.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Any
+
+import numpy as np
+
+from . import _lib
+from ._ids import to_uint32_ids
+
+__all__ = ["CsrGraph", "Graph"]
+
+
+def _current_device() -> int:
+    import torch
+
+    if not torch.cuda.is_available():
+        raise RuntimeError("aethergraph_b200 needs a CUDA device; there is no CPU path")
+    return torch.cuda.current_device()
+
+
+class CsrGraph:
+    """Compressed-sparse-row graph (u64 offsets, u32 destinations, optional f32
+    weights) held in HBM.  Construct with `load`, `from_edges` or `from_csr`."""
+
+    def __init__(self, handle: int):
+        self._h = C.c_void_p(handle)
+        n, e, w, d = C.c_uint64(), C.c_uint64(), C.c_int32(), C.c_int32()
+        _lib.check(_lib.lib().ag_graph_info(self._h, C.byref(n), C.byref(e), C.byref(w), C.byref(d)))
+        self._n, self._e, self._w, self._device = n.value, e.value, bool(w.value), d.value
+
+    def __del__(self):
+        h = getattr(self, "_h", None)
+        if h:
+            try:
+                _lib.lib().ag_graph_free(h)
+            except Exception:
+                pass
+            self._h = None
+
+    # -- constructors ------------------------------------------------------
+    @staticmethod
+    def load(path, *, storage: str = "auto", validation: str = "auto", device: int | None = None) -> "CsrGraph":
+        """Load an AETH v1 file into GPU memory.
+
+        `storage` is accepted for signature compatibility; the CSR always
+        lives in HBM.  `validation` picks whether the body checksum is
+        verified ("full", or "auto" below 512 MiB); destinations are always
+        proven in range because the sampler indexes by them.
+        """
+        if storage not in ("auto", "mmap", "owned"):
+            raise ValueError(f"Invalid storage '{storage}'. Must be 'auto', 'mmap', or 'owned'")
+        if validation not in _lib.VALIDATION:
+            raise ValueError(f"Invalid validation '{validation}'. Must be 'auto', 'header_only', "
+                             "'offsets_only', or 'full'")
+        dev = _current_device() if device is None else device
+        out = C.c_void_p()
+        _lib.check(_lib.lib().ag_graph_load(os.fspath(path).encode(), _lib.VALIDATION[validation], dev,
+                                            C.byref(out)))
+        return CsrGraph(out.value)
+
+    @staticmethod
+    def from_edges(num_nodes: int, src, dst, weights=None, *, device: int | None = None) -> "CsrGraph":
+        """Build from an edge list; edges keep their input order within a row."""
+        s = np.ascontiguousarray(to_uint32_ids(np.asarray(src), "src"))
+        d = np.ascontiguousarray(to_uint32_ids(np.asarray(dst), "dst"))
+        if s.shape != d.shape or s.ndim != 1:
+            raise ValueError(f"src and dst must be 1-d arrays of equal length, got {s.shape} and {d.shape}")
+        w = None
+        if weights is not None:
+            w = np.ascontiguousarray(weights, dtype=np.float32)
+            if w.shape != s.shape:
+                raise ValueError(f"weights length {w.shape} does not match the edge count {s.shape}")
+        dev = _current_device() if device is None else device
+        out = C.c_void_p()
+        _lib.check(_lib.lib().ag_graph_from_edges(num_nodes, s.ctypes.data, d.ctypes.data,
+                                                  w.ctypes.data if w is not None else None, len(s), dev,
+                                                  C.byref(out)))
+        return CsrGraph(out.value)
+
+    @staticmethod
+    def from_csr(offsets, dst, weights=None, *, device: int | None = None) -> "CsrGraph":
+        """Build from CSR arrays (numpy, or CUDA torch tensors of dtype int64 / int32 /
+        float32 holding the u64 / u32 / f32 bit patterns)."""
+        import torch
+
+        dev = _current_device() if device is None else device
+        out = C.c_void_p()
+        if isinstance(offsets, torch.Tensor):
+            if not (offsets.is_cuda and dst.is_cuda and offsets.is_contiguous() and dst.is_contiguous()):
+                raise ValueError("tensor CSR arrays must be contiguous CUDA tensors")
+            if offsets.dtype != torch.int64 or dst.dtype != torch.int32:
+                raise ValueError("tensor CSR: offsets must be int64 and dst int32 (bit patterns of u64 / u32)")
+            n, e = offsets.numel() - 1, dst.numel()
+            wp = None
+            if weights is not None:
+                if weights.dtype != torch.float32 or not weights.is_cuda or weights.numel() != e:
+                    raise ValueError("tensor CSR: weights must be a float32 CUDA tensor with one entry per edge")
+                wp = weights.data_ptr()
+            _lib.check(_lib.lib().ag_graph_from_csr(n, e, offsets.data_ptr(), dst.data_ptr() if e else None, wp,
+                                                    _lib.AG_MEM_DEVICE, dev, C.byref(out)))
+            return CsrGraph(out.value)
+        off = np.ascontiguousarray(offsets, dtype=np.uint64)
+        d = np.ascontiguousarray(dst, dtype=np.uint32)
+        w = np.ascontiguousarray(weights, dtype=np.float32) if weights is not None else None
+        _lib.check(_lib.lib().ag_graph_from_csr(len(off) - 1, len(d), off.ctypes.data, d.ctypes.data if len(d) else None,
+                                                w.ctypes.data if w is not None else None, _lib.AG_MEM_HOST, dev,
+                                                C.byref(out)))
+        return CsrGraph(out.value)
+
+    def save(self, path, *, compressed: bool = False) -> None:
+        if compressed:
+            raise ValueError("the compressed (version 2) graph format is not supported on this path")
+        _lib.check(_lib.lib().ag_graph_save(self._h, os.fspath(path).encode()))
+
+    # -- properties --------------------------------------------------------
+    @property
+    def num_nodes(self) -> int:
+        return self._n
+
+    @property
+    def num_edges(self) -> int:
+        return self._e
+
+    @property
+    def has_weights(self) -> bool:
+        return self._w
+
+    @property
+    def has_timestamps(self) -> bool:
+        return False
+
+    @property
+    def device(self) -> int:
+        return self._device
+
+    def device_ptrs(self) -> tuple[int, int, int]:
+        """(offsets, destinations, weights) device addresses; weights is 0 if absent."""
+        a, b, c = C.c_void_p(), C.c_void_p(), C.c_void_p()
+        _lib.check(_lib.lib().ag_graph_device_ptrs(self._h, C.byref(a), C.byref(b), C.byref(c)))
+        return a.value or 0, b.value or 0, c.value or 0
+
+    # -- row access --------------------------------------------------------
+    def degrees(self) -> np.ndarray:
+        out = np.empty(self._n, dtype=np.uint32)
+        _lib.check(_lib.lib().ag_graph_degrees(self._h, None, self._n, out.ctypes.data))
+        return out
+
+    def degrees_of(self, nodes) -> np.ndarray:
+        ids = np.ascontiguousarray(to_uint32_ids(np.asarray(nodes), "nodes"))
+        out = np.empty(len(ids), dtype=np.uint32)
+        _lib.check(_lib.lib().ag_graph_degrees(self._h, ids.ctypes.data, len(ids), out.ctypes.data))
+        return out
+
+    def degree(self, node: int) -> int:
+        if node < 0 or node >= self._n:
+            return 0
+        return int(self.degrees_of(np.array([node], dtype=np.uint32))[0])
+
+    def _row(self, node: int, want_weights: bool):
+        if node < 0 or node >= 2**32:
+            return np.empty(0, dtype=np.uint32), (np.empty(0, dtype=np.float32) if want_weights else None)
+        deg = C.c_uint64()
+        _lib.check(_lib.lib().ag_graph_neighbors(self._h, node, None, None, 0, C.byref(deg)))
+        out = np.empty(deg.value, dtype=np.uint32)
+        w = np.empty(deg.value, dtype=np.float32) if (want_weights and self._w) else None
+        if deg.value:
+            _lib.check(_lib.lib().ag_graph_neighbors(self._h, node, out.ctypes.data,
+                                                     w.ctypes.data if w is not None else None, deg.value,
+                                                     C.byref(deg)))
+        return out, w
+
+    def neighbors(self, node: int) -> np.ndarray:
+        return self._row(int(node), False)[0]
+
+    def neighbor_weights(self, node: int):
+        if not self._w:
+            return None
+        return self._row(int(node), True)[1]
+
+    def batch_neighbors(self, nodes) -> list[np.ndarray]:
+        return [self.neighbors(int(v)) for v in nodes]
+
+    def stats(self) -> dict[str, Any]:
+        deg = self.degrees()
+        return {
+            "num_nodes": self._n, "num_edges": self._e,
+            "avg_degree": float(self._e) / self._n if self._n else 0.0,
+            "max_degree": int(deg.max()) if self._n else 0,
+            "min_degree": int(deg.min()) if self._n else 0,
+            "has_weights": self._w,
+        }
+
+    def __len__(self) -> int:
+        return self._n
+
+    def __getitem__(self, node: int) -> np.ndarray:
+        return self.neighbors(node)
+
+    def __repr__(self) -> str:
+        return f"CsrGraph(num_nodes={self._n}, num_edges={self._e}, device=cuda:{self._device})"
+
+
+Graph = CsrGraph

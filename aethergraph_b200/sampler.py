@@ -1,0 +1,446 @@
+"""Neighbor sampling on the GPU behind the reference's sampler API.
+
+Mirrors `SamplingConfig`, `NeighborSampler` (alias `Sampler`), `SampledSubgraph`
+and `ParallelBatchSampler` of the reference (python/aethergraph/sampler.py,
+python/aethergraph/_core.pyi:152-288).  Sampling, dedup, relabel and the int64
+widening all run in CUDA kernels; results stay in GPU memory (`*_t` tensor
+accessors, `x`) and are copied to host numpy arrays only when the numpy
+accessors of the reference API are read.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import secrets
+from dataclasses import dataclass
+from typing import Any, Sequence
+
+import numpy as np
+
+from . import _lib
+from ._lib import SamplingError
+from .features import FeatureStore
+from .graph import CsrGraph
+
+__all__ = ["NeighborSampler", "ParallelBatchSampler", "SampledSubgraph", "Sampler", "SamplingConfig",
+           "SamplingError"]
+
+_SUBGRAPH_TYPES = ("directional", "induced", "bidirectional")
+_TEMPORAL = ("uniform", "last")
+
+
+@dataclass
+class SamplingConfig:
+    """Configuration for neighborhood sampling (same fields and validation as the
+    reference, crates/aethergraph-py/src/sampler.rs:116-194), plus `rng_mode`:
+
+    - ``"wyrand_exact"`` (default) reproduces the reference CPU sampler's output
+      bit for bit for a given seed.
+    - ``"philox"`` keys every draw on (seed, hop, vertex, slot) with
+      Philox4x32-10: the same sampling distribution, different samples.
+    """
+
+    num_neighbors: list[int]
+    replace: bool = False
+    seed: int | None = None
+    max_degree: int | None = None
+    cumulative: bool = False
+    weighted: bool = False
+    subgraph_type: str = "directional"
+    track_edge_ids: bool = True
+    temporal_strategy: str | None = None
+    disjoint: bool = False
+    deterministic: bool = False
+    telemetry: Any = None
+    rng_mode: str = "wyrand_exact"
+
+    def __post_init__(self) -> None:
+        nn = list(self.num_neighbors)
+        if len(nn) == 0:
+            raise ValueError("num_neighbors must be a non-empty list")
+        if any(int(v) < 0 for v in nn):
+            raise ValueError(f"num_neighbors values must be non-negative, got {nn}")
+        self.num_neighbors = [int(v) for v in nn]
+        if self.max_degree is not None and self.max_degree <= 0:
+            raise ValueError(f"max_degree must be > 0 if specified, got {self.max_degree}")
+        if self.subgraph_type not in _SUBGRAPH_TYPES:
+            raise ValueError(f"Invalid subgraph_type '{self.subgraph_type}'. Must be 'directional', "
+                             "'induced', or 'bidirectional'")
+        if self.temporal_strategy is not None and self.temporal_strategy not in _TEMPORAL:
+            raise ValueError(f"Invalid temporal_strategy '{self.temporal_strategy}'. Must be 'uniform' or 'last'")
+        if self.seed is not None and not (0 <= int(self.seed) < 2**64):
+            raise ValueError(f"seed must fit an unsigned 64-bit integer, got {self.seed}")
+        if self.rng_mode not in _lib.RNG_MODE:
+            raise ValueError(f"Invalid rng_mode '{self.rng_mode}'. Must be 'wyrand_exact' or 'philox'")
+
+    def _unsupported(self) -> str | None:
+        """Modes of the reference this GPU path does not implement."""
+        if self.temporal_strategy is not None:
+            return "temporal sampling"
+        if self.disjoint:
+            return "disjoint sampling"
+        if self.subgraph_type != "directional":
+            return f"subgraph_type='{self.subgraph_type}'"
+        if self.cumulative:
+            return "cumulative sampling"
+        if self.max_degree is not None and self.weighted:
+            return "max_degree with weighted sampling"
+        if len(self.num_neighbors) > _lib.AG_MAX_HOPS:
+            return f"more than {_lib.AG_MAX_HOPS} hops"
+        return None
+
+    def _to_c(self, seed: int, max_seeds: int = 0) -> _lib.SamplingConfigC:
+        c = _lib.SamplingConfigC()
+        c.num_hops = len(self.num_neighbors)
+        for i, k in enumerate(self.num_neighbors):
+            c.fanout[i] = k
+        c.replace, c.weighted, c.track_edge_ids = int(self.replace), int(self.weighted), int(self.track_edge_ids)
+        c.seed = seed
+        c.rng_mode = _lib.RNG_MODE[self.rng_mode]
+        c.max_seeds = max_seeds
+        return c
+
+
+def _align4(n: int) -> int:
+    return (max(n, 1) + 3) & ~3
+
+
+def coerce_seeds(seeds, num_nodes: int) -> np.ndarray:
+    """Seed argument -> contiguous uint32 array (crates/aethergraph-py/src/error.rs:115-153):
+    uint32 arrays pass through, int64 arrays and sequences are range-checked, and
+    an id outside [0, num_nodes) raises SamplingError naming it."""
+    a = np.asarray(seeds)
+    if a.ndim != 1:
+        a = a.reshape(-1)
+    if a.dtype != np.uint32:
+        if a.size and a.dtype.kind not in "iu":
+            raise TypeError(f"seeds must be integers, got dtype {a.dtype}")
+        if a.size:
+            lo, hi = int(a.min()), int(a.max())
+            bad = lo if lo < 0 else (hi if hi > 0xFFFFFFFF else None)
+            if bad is not None:
+                raise SamplingError(f"seed node {bad} out of u32 range [0, {0xFFFFFFFF}]")
+        a = a.astype(np.uint32)
+    a = np.ascontiguousarray(a)
+    if a.size:
+        bad = np.nonzero(a >= num_nodes)[0] if num_nodes < 2**32 else []
+        if len(bad):
+            p = int(bad[0])
+            raise SamplingError(f"seed node {int(a[p])} (position {p}) is out of range for {num_nodes} nodes")
+    return a
+
+
+class _Buffers:
+    """Device output buffers of one batch, carved from three torch allocations."""
+
+    def __init__(self, device, cap_nodes: int, cap_edges: int, cap_seeds: int, track_eids: bool,
+                 feature_dim: int | None):
+        import torch
+
+        self.cap_nodes, self.cap_edges, self.cap_seeds = cap_nodes, cap_edges, cap_seeds
+        cn, ce, cs = _align4(cap_nodes), _align4(cap_edges), _align4(cap_seeds)
+        self.a32 = torch.empty(cn + 4 * ce + cs, dtype=torch.int32, device=device)
+        o = 0
+        self.nodes = self.a32[o:o + cn]; o += cn
+        self.edge_src = self.a32[o:o + ce]; o += ce
+        self.edge_dst = self.a32[o:o + ce]; o += ce
+        self.src_local = self.a32[o:o + ce]; o += ce
+        self.dst_local = self.a32[o:o + ce]; o += ce
+        self.seed_locals = self.a32[o:o + cs]
+        n64 = cn + 2 * ce + cs + (ce if track_eids else 0)
+        self.a64 = torch.empty(n64, dtype=torch.int64, device=device)
+        o = 0
+        self.n_id = self.a64[o:o + cn]; o += cn
+        self.edge_index_local = self.a64[o:o + 2 * ce]; o += 2 * ce
+        self.seed_index = self.a64[o:o + cs]; o += cs
+        self.edge_ids = self.a64[o:o + ce] if track_eids else None
+        self.x = (torch.empty((max(cap_nodes, 1), feature_dim), dtype=torch.float32, device=device)
+                  if feature_dim is not None else None)
+        b = _lib.SubgraphBuffers()
+        b.cap_nodes, b.cap_edges, b.cap_seeds = max(cap_nodes, 1), max(cap_edges, 1), max(cap_seeds, 1)
+        b.nodes, b.edge_src, b.edge_dst = self.nodes.data_ptr(), self.edge_src.data_ptr(), self.edge_dst.data_ptr()
+        b.src_local, b.dst_local = self.src_local.data_ptr(), self.dst_local.data_ptr()
+        b.seed_locals = self.seed_locals.data_ptr()
+        b.edge_ids = self.edge_ids.data_ptr() if track_eids else None
+        b.n_id, b.edge_index_local = self.n_id.data_ptr(), self.edge_index_local.data_ptr()
+        b.e_id = None  # int64(edge id) has the same bits as the u64 the kernel writes
+        b.seed_index = self.seed_index.data_ptr()
+        b.x = self.x.data_ptr() if self.x is not None else None
+        self.c = b
+
+
+def _u32_to_i64(t):
+    """int32 tensor holding u32 bit patterns -> int64 values."""
+    return t.to(dtype=__import__("torch").int64) & 0xFFFFFFFF
+
+
+class SampledSubgraph:
+    """One sampled subgraph.  numpy accessors follow the reference
+    (_core.pyi:207-261): all int64; row 0 of `edge_index` / `edge_index_local` is
+    the sampled neighbor and row 1 the node whose row was expanded; `edge_ids[i]`
+    is the CSR position of the stored edge row1 -> row0.  The `*_t` accessors
+    return the same data as CUDA tensors without a copy."""
+
+    def __init__(self, bufs: _Buffers, counts: _lib.SampleCounts, seeds: np.ndarray):
+        self._b = bufs
+        self._n, self._e, self._s = counts.num_nodes, counts.num_edges, counts.num_seeds
+        h = counts.num_hops
+        self._nodes_per_hop = [int(counts.nodes_per_hop[i]) for i in range(h + 1)]
+        self._edges_per_hop = [int(counts.edges_per_hop[i]) for i in range(h)]
+        self.draws = int(counts.draws)
+        self._seeds = seeds
+        self._cache: dict[str, Any] = {}
+
+    # counts
+    @property
+    def num_nodes(self) -> int:
+        return self._n
+
+    @property
+    def num_edges(self) -> int:
+        return self._e
+
+    @property
+    def num_seeds(self) -> int:
+        return self._s
+
+    def __len__(self) -> int:
+        return self._n
+
+    # device tensors
+    @property
+    def nodes_t(self):
+        return self._b.n_id[:self._n]
+
+    @property
+    def edge_index_local_t(self):
+        return self._b.edge_index_local[:2 * self._e].view(2, self._e)
+
+    @property
+    def edge_index_t(self):
+        import torch
+
+        return torch.stack([_u32_to_i64(self._b.edge_dst[:self._e]), _u32_to_i64(self._b.edge_src[:self._e])])
+
+    @property
+    def edge_ids_t(self):
+        return None if self._b.edge_ids is None else self._b.edge_ids[:self._e]
+
+    @property
+    def seed_indices_t(self):
+        return self._b.seed_index[:self._s]
+
+    @property
+    def x(self):
+        """Gathered feature rows [num_nodes, dim] (CUDA float32), or None."""
+        return None if self._b.x is None else self._b.x[:self._n]
+
+    def raw_u32(self) -> dict[str, np.ndarray]:
+        """The core arrays in the reference's native widths (SampledSubgraph,
+        crates/aethergraph-core/src/loader/sampler.rs:1512-1543), as host numpy."""
+        b, n, e, s = self._b, self._n, self._e, self._s
+        a32 = b.a32.cpu().numpy().view(np.uint32)
+        cn, ce = _align4(b.cap_nodes), _align4(b.cap_edges)
+        o = 0
+        out = {"nodes": a32[o:o + n].copy()}; o += cn
+        for name in ("edge_src", "edge_dst", "src_local", "dst_local"):
+            out[name] = a32[o:o + e].copy(); o += ce
+        out["seed_locals"] = a32[o:o + s].copy()
+        out["edge_ids"] = (b.edge_ids[:e].cpu().numpy().view(np.uint64).copy()
+                           if b.edge_ids is not None else None)
+        out["num_sampled_nodes"] = np.array(self._nodes_per_hop, dtype=np.uint64)
+        out["num_sampled_edges"] = np.array(self._edges_per_hop, dtype=np.uint64)
+        out["draws"] = self.draws
+        return out
+
+    # numpy accessors of the reference API
+    def _np(self, key, make):
+        if key not in self._cache:
+            self._cache[key] = make()
+        return self._cache[key]
+
+    @property
+    def nodes(self) -> np.ndarray:
+        return self._np("nodes", lambda: self.nodes_t.cpu().numpy())
+
+    @property
+    def seeds(self) -> np.ndarray:
+        return self._np("seeds", lambda: self._seeds.astype(np.int64))
+
+    @property
+    def edge_index(self) -> np.ndarray:
+        return self._np("edge_index", lambda: self.edge_index_t.cpu().numpy())
+
+    @property
+    def edge_index_local(self) -> np.ndarray:
+        return self._np("edge_index_local", lambda: self.edge_index_local_t.cpu().numpy())
+
+    @property
+    def edge_ids(self) -> np.ndarray:
+        def make():
+            t = self.edge_ids_t
+            return np.empty(0, dtype=np.int64) if t is None else t.cpu().numpy()
+        return self._np("edge_ids", make)
+
+    @property
+    def seed_indices(self) -> np.ndarray:
+        return self._np("seed_indices", lambda: self.seed_indices_t.cpu().numpy())
+
+    @property
+    def batch(self):
+        return None
+
+    @property
+    def num_sampled_nodes_per_hop(self) -> list[int]:
+        return list(self._nodes_per_hop)
+
+    @property
+    def num_sampled_edges_per_hop(self) -> list[int]:
+        return list(self._edges_per_hop)
+
+    def to_dict(self) -> dict[str, Any]:
+        return {
+            "nodes": self.nodes, "seeds": self.seeds, "edge_index": self.edge_index,
+            "edge_index_local": self.edge_index_local, "edge_ids": self.edge_ids,
+            "seed_indices": self.seed_indices, "batch": None,
+            "num_sampled_nodes_per_hop": self.num_sampled_nodes_per_hop,
+            "num_sampled_edges_per_hop": self.num_sampled_edges_per_hop,
+        }
+
+    def __repr__(self) -> str:
+        return f"SampledSubgraph(num_nodes={self._n}, num_edges={self._e}, num_seeds={self._s})"
+
+
+class _Pending:
+    """A batch queued on the GPU; `result()` waits for it."""
+
+    def __init__(self, handle: "_Handle", bufs: _Buffers, seeds: np.ndarray):
+        self._handle, self._bufs, self._seeds = handle, bufs, seeds
+        self._done: SampledSubgraph | None = None
+
+    def result(self) -> SampledSubgraph:
+        if self._done is None:
+            counts = _lib.SampleCounts()
+            _lib.check(_lib.lib().ag_sample_wait(self._handle.h, C.byref(counts)))
+            self._done = SampledSubgraph(self._bufs, counts, self._seeds)
+        return self._done
+
+
+class _Handle:
+    """One ag_sampler: scratch for one batch in flight."""
+
+    def __init__(self, graph: CsrGraph, config: SamplingConfig, seed: int, max_seeds: int = 0):
+        self.graph, self.config = graph, config
+        self.h = C.c_void_p()
+        cfg = config._to_c(seed, max_seeds)
+        _lib.check(_lib.lib().ag_sampler_create(graph._h, C.byref(cfg), C.byref(self.h)))
+
+    def __del__(self):
+        h = getattr(self, "h", None)
+        if h:
+            try:
+                _lib.lib().ag_sampler_free(h)
+            except Exception:
+                pass
+            self.h = None
+
+    def reseed(self, seed: int) -> None:
+        _lib.check(_lib.lib().ag_sampler_reseed(self.h, seed & (2**64 - 1)))
+
+    def bounds(self, n_seeds: int) -> tuple[int, int]:
+        mn, me = C.c_uint64(), C.c_uint64()
+        _lib.check(_lib.lib().ag_sampler_bounds(self.h, n_seeds, C.byref(mn), C.byref(me)))
+        return mn.value, me.value
+
+    def submit(self, seeds: np.ndarray, features: FeatureStore | None, stream=None) -> _Pending:
+        import torch
+
+        dev = torch.device("cuda", self.graph.device)
+        mn, me = self.bounds(len(seeds))
+        bufs = _Buffers(dev, mn, me, len(seeds), self.config.track_edge_ids,
+                        features.feature_dim if features is not None else None)
+        st = stream if stream is not None else torch.cuda.current_stream(dev).cuda_stream
+        _lib.check(_lib.lib().ag_sample_into(self.h, seeds.ctypes.data if len(seeds) else None, len(seeds),
+                                             _lib.AG_MEM_HOST, features._h if features is not None else None,
+                                             C.byref(bufs.c), st))
+        return _Pending(self, bufs, seeds)
+
+
+def _check_config(graph: CsrGraph, config: SamplingConfig) -> None:
+    if not isinstance(config, SamplingConfig):
+        raise TypeError("config must be a SamplingConfig")
+    bad = config._unsupported()
+    if bad:
+        raise ValueError(f"{bad} is not supported by the GPU minibatch path")
+    if config.weighted and not graph.has_weights:
+        raise ValueError("weighted sampling requested, but the graph has no edge weights")
+
+
+class NeighborSampler:
+    """Single-graph neighborhood sampler.  The RNG stream advances across
+    `sample()` calls, so consecutive batches differ and a fresh sampler with the
+    same seed replays the sequence (crates/aethergraph-py/src/sampler.rs:782-785).
+    `features` (optional) gathers `x` for every batch in the same launch chain."""
+
+    def __init__(self, graph: CsrGraph, config: SamplingConfig, features: FeatureStore | None = None):
+        _check_config(graph, config)
+        self.graph, self.config, self.features = graph, config, features
+        seed = config.seed if config.seed is not None else secrets.randbits(64)
+        self._handle = _Handle(graph, config, seed)
+
+    def sample(self, seeds, input_times=None) -> SampledSubgraph:
+        if input_times is not None:
+            raise SamplingError("temporal sampling: SamplingConfig::temporal_strategy is None")
+        s = coerce_seeds(seeds, self.graph.num_nodes)
+        return self._handle.submit(s, self.features).result()
+
+    def __repr__(self) -> str:
+        return f"NeighborSampler(num_neighbors={self.config.num_neighbors}, replace={self.config.replace})"
+
+
+Sampler = NeighborSampler
+
+
+class ParallelBatchSampler:
+    """Samples many batches concurrently.  The batch at stream position p (counted
+    over every batch this sampler has handled) draws from
+    `batch_seed(config.seed, p)`, so a fixed seed gives the same output however
+    the batches are scheduled (crates/aethergraph-core/src/loader/sampler.rs:1726-1751).
+    Here the parallelism is `streams` sampler handles, each with its own CUDA stream."""
+
+    def __init__(self, graph: CsrGraph, config: SamplingConfig, features: FeatureStore | None = None,
+                 streams: int = 4):
+        import torch
+
+        _check_config(graph, config)
+        self.graph, self.config, self.features = graph, config, features
+        self._base = config.seed if config.seed is not None else secrets.randbits(64)
+        self._next = 0
+        dev = torch.device("cuda", graph.device)
+        self._handles = [_Handle(graph, config, self._base) for _ in range(max(1, streams))]
+        self._streams = [torch.cuda.Stream(dev) for _ in self._handles]
+
+    def sample_batches(self, batches: Sequence) -> list[SampledSubgraph]:
+        import torch
+
+        seeds = [coerce_seeds(b, self.graph.num_nodes) for b in batches]
+        first = self._next
+        self._next += len(seeds)
+        out: list[SampledSubgraph | None] = [None] * len(seeds)
+        pending: list[tuple[int, _Pending] | None] = [None] * len(self._handles)
+        cur = torch.cuda.current_stream()
+        for j, s in enumerate(seeds):
+            k = j % len(self._handles)
+            if pending[k] is not None:
+                i, p = pending[k]
+                out[i] = p.result()
+            h, st = self._handles[k], self._streams[k]
+            h.reseed(_lib.lib().ag_batch_seed(self._base, first + j))
+            st.wait_stream(cur)
+            with torch.cuda.stream(st):
+                pending[k] = (j, h.submit(s, self.features, st.cuda_stream))
+        for slot in pending:
+            if slot is not None:
+                out[slot[0]] = slot[1].result()
+        for st in self._streams:
+            cur.wait_stream(st)
+        return out  # type: ignore[return-value]

@@ -1,0 +1,232 @@
+/*
+ * aethergpu.h — C ABI of the B200 minibatch path.
+ *
+ * One shared library (libaethergpu.so) implements, on the GPU, the path the
+ * reference runs on the CPU: k-hop neighbor sampling over a static CSR graph,
+ * frontier dedup + relabel into a local edge index, and the feature-row
+ * gather with fused f16/bf16 -> f32 upcast.  The reference exposes this path
+ * through its PyO3 extension module `aethergraph._core`
+ * (python/aethergraph/_core.pyi is the contract); it has no C ABI of its own.
+ * Each entry point below names the reference interface it stands in for
+ * (file:line relative to the reference project root).
+ *
+ * Conventions
+ *   - Every function returns an ag_status (0 = OK).  On failure a
+ *     thread-local, NUL-terminated message is available from ag_last_error().
+ *     Status classes map onto the reference's Python exceptions
+ *     (crates/aethergraph-py/src/error.rs:29-70, prefetch.rs:35-55):
+ *       AG_ERR_VALUE -> ValueError,  AG_ERR_LOAD -> GraphLoadError,
+ *       AG_ERR_SAMPLING -> SamplingError,  AG_ERR_TIMEOUT -> TimeoutError,
+ *       AG_ERR_WORKER -> RuntimeError,  AG_ERR_CUDA -> RuntimeError.
+ *   - Host input arrays are borrowed for the duration of the call only.
+ *   - Pointers named *_dev are device pointers on the handle's device.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = default stream).
+ *   - There is no CPU fallback: every compute entry point launches CUDA
+ *     kernels and fails with AG_ERR_CUDA when no device is usable.
+ *   - Handles may be used from any thread; a sampler handle is not
+ *     re-entrant (the reference's samplers are `&mut self`, one per worker:
+ *     crates/aethergraph-core/src/loader/prefetch.rs:918,959).
+ */
+#ifndef AETHERGPU_H
+#define AETHERGPU_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    AG_OK = 0,
+    AG_ERR_VALUE = 1,
+    AG_ERR_LOAD = 2,
+    AG_ERR_SAMPLING = 3,
+    AG_ERR_TIMEOUT = 4,
+    AG_ERR_WORKER = 5,
+    AG_ERR_CUDA = 6,
+    AG_ERR_SHUTDOWN = 7
+} ag_status;
+
+typedef struct ag_graph ag_graph;
+typedef struct ag_features ag_features;
+typedef struct ag_sampler ag_sampler;
+typedef struct ag_hetero_graph ag_hetero_graph;
+typedef struct ag_hetero_sampler ag_hetero_sampler;
+typedef struct ag_loader ag_loader;
+
+const char *ag_last_error(void);
+/* ABI version of this header; bumped on any incompatible change. */
+int32_t ag_abi_version(void);
+
+/* ------------------------------------------------------------------ RNG --
+ * crates/aethergraph-core/src/loader/sampler.rs:69-75 (batch_seed). */
+uint64_t ag_batch_seed(uint64_t base, uint64_t batch_idx);
+
+/* ---------------------------------------------------------------- graph --
+ * Stands in for CsrGraph.load / CsrGraph.from_edges / CsrGraph.save and the
+ * row accessors (_core.pyi:68-131; crates/aethergraph-py/src/graph.rs:51-88;
+ * file format crates/aethergraph-core/src/internal/mmap.rs:114-121).
+ * The CSR (u64 offsets, u32 destinations, optional f32 weights) lives in HBM.
+ */
+enum { AG_VALIDATE_AUTO = 0, AG_VALIDATE_HEADER = 1, AG_VALIDATE_OFFSETS = 2, AG_VALIDATE_FULL = 3 };
+enum { AG_MEM_HOST = 0, AG_MEM_DEVICE = 1 };
+
+int32_t ag_graph_load(const char *path, int32_t validation, int32_t device, ag_graph **out);
+/* Copies a CSR from host or device memory (mem_kind) into library-owned HBM.
+ * Offsets must be non-decreasing with offsets[n] == num_edges, and every
+ * destination < num_nodes (checked on the device; AG_ERR_LOAD otherwise). */
+int32_t ag_graph_from_csr(uint64_t num_nodes, uint64_t num_edges, const uint64_t *offsets,
+                          const uint32_t *dst, const float *weights, int32_t mem_kind,
+                          int32_t device, ag_graph **out);
+/* Takes ownership of device arrays produced by this library's generators or
+ * allocated with cudaMalloc on `device`; validates like ag_graph_from_csr. */
+int32_t ag_graph_adopt_device_csr(uint64_t num_nodes, uint64_t num_edges, uint64_t *offsets_dev,
+                                  uint32_t *dst_dev, float *weights_dev, int32_t device,
+                                  ag_graph **out);
+/* Counting-sort CSR build that keeps input order within each row
+ * (crates/aethergraph-core/src/graph/csr.rs:568-571, 631-750). */
+int32_t ag_graph_from_edges(uint64_t num_nodes, const uint32_t *src, const uint32_t *dst,
+                            const float *weights, uint64_t num_edges, int32_t device,
+                            ag_graph **out);
+int32_t ag_graph_save(const ag_graph *g, const char *path);
+int32_t ag_graph_info(const ag_graph *g, uint64_t *num_nodes, uint64_t *num_edges,
+                      int32_t *has_weights, int32_t *device);
+int32_t ag_graph_device_ptrs(const ag_graph *g, const uint64_t **offsets_dev,
+                             const uint32_t **dst_dev, const float **weights_dev);
+/* degrees_of (out-of-range id -> 0); ids == NULL means all nodes in order. */
+int32_t ag_graph_degrees(const ag_graph *g, const uint32_t *ids, uint64_t n, uint32_t *out);
+/* neighbors(node): copies up to cap destinations (and weights when
+ * weights_out != NULL) to host; *degree receives the full row length. */
+int32_t ag_graph_neighbors(const ag_graph *g, uint32_t node, uint32_t *out, float *weights_out,
+                           uint64_t cap, uint64_t *degree);
+void ag_graph_free(ag_graph *g);
+
+/* ------------------------------------------------------------- features --
+ * Stands in for save_features / FeatureStore (_core.pyi:136-148, 482-516;
+ * crates/aethergraph-core/src/features/store.rs:384-440, 691-838;
+ * header crates/aethergraph-core/src/features/header.rs:165-244).
+ * The payload (num_nodes x dim elements of f32 / f16 / bf16) lives in HBM.
+ */
+enum { AG_F32 = 0, AG_F16 = 1, AG_BF16 = 2 };
+
+int32_t ag_features_save(const char *path, const float *features, uint64_t num_nodes,
+                         uint64_t dim, int32_t dtype);
+int32_t ag_features_load(const char *path, int32_t device, ag_features **out);
+/* Loads rows [row_begin, row_end) only (a vertex-range shard). */
+int32_t ag_features_load_range(const char *path, int32_t device, uint64_t row_begin,
+                               uint64_t row_end, ag_features **out);
+/* payload holds stored elements (not f32 unless dtype == AG_F32). */
+int32_t ag_features_from_memory(const void *payload, uint64_t num_nodes, uint64_t dim,
+                                int32_t dtype, int32_t mem_kind, int32_t device,
+                                ag_features **out);
+/* Encodes f32 rows on the device into `dtype` (RNE for f16; the reference's
+ * bf16 rule, store.rs:1094-1104) and keeps the encoded payload. */
+int32_t ag_features_from_f32(const float *features, uint64_t num_nodes, uint64_t dim,
+                             int32_t dtype, int32_t mem_kind, int32_t device, ag_features **out);
+int32_t ag_features_adopt_device(void *payload_dev, uint64_t num_nodes, uint64_t dim,
+                                 int32_t dtype, int32_t device, ag_features **out);
+int32_t ag_features_info(const ag_features *f, uint64_t *num_nodes, uint64_t *dim,
+                         int32_t *dtype, int32_t *device, uint64_t *row_begin);
+int32_t ag_features_device_ptr(const ag_features *f, const void **payload_dev);
+
+/* FeatureStore.get_batch on host ids (store.rs:691-769): range-checks every
+ * id first (AG_ERR_VALUE "node N out of bounds"), gathers on the device and
+ * copies the [n, dim] f32 result to `out` (host).  Synchronous. */
+int32_t ag_features_get_batch(const ag_features *f, const int64_t *ids, uint64_t n, float *out);
+
+/* Device gather (store.rs:777-838 get_batch_into): out_dev[i, :] =
+ * upcast(row ids[i]).  ids are u32 (ids_are_i64 == 0) or i64 device arrays.
+ * The row count is `n`, or *n_dev (a device u32) clamped to n when n_dev is
+ * not NULL.  An id outside the store writes a zero row and raises a sticky
+ * error reported by ag_features_check. */
+int32_t ag_gather(const ag_features *f, const void *ids_dev, int32_t ids_are_i64, uint64_t n,
+                  const uint32_t *n_dev, float *out_dev, void *stream);
+/* Returns AG_ERR_VALUE if any device gather since the last check saw an
+ * out-of-range id (synchronises the device). */
+int32_t ag_features_check(const ag_features *f);
+void ag_features_free(ag_features *f);
+
+/* -------------------------------------------------------------- sampler --
+ * Stands in for SamplingConfig / NeighborSampler / ParallelBatchSampler
+ * (_core.pyi:152-198, 263-288; crates/aethergraph-core/src/loader/sampler.rs:
+ * 78-158 config, 525-557 sample, 845-961 sample_neighbors_inner).
+ */
+enum { AG_RNG_WYRAND_EXACT = 0, AG_RNG_PHILOX = 1 };
+#define AG_MAX_HOPS 8
+
+typedef struct {
+    uint32_t num_hops;
+    uint32_t fanout[AG_MAX_HOPS];
+    int32_t replace;        /* sampler.rs:85 */
+    int32_t weighted;       /* sampler.rs:112; needs graph weights */
+    int32_t track_edge_ids; /* sampler.rs:120 */
+    uint64_t seed;          /* sampler.rs:88 (the caller resolves None) */
+    /* AG_RNG_WYRAND_EXACT replays the reference's sequential WyRand stream
+     * (internal/genstamp.rs:181-202) draw for draw.  AG_RNG_PHILOX keys every
+     * draw on (seed, hop, vertex, slot) with Philox4x32-10
+     * (internal/philox.rs:15-52): same distribution, different samples. */
+    int32_t rng_mode;
+    uint32_t max_seeds;     /* sizing hint for scratch; grows on demand */
+} ag_sampling_config;
+
+/* Output buffers of one sampled batch, all device memory.  Arrays marked
+ * "optional" may be NULL in a caller-supplied struct and are then skipped.
+ * Layout follows SampledSubgraph (sampler.rs:1512-1543) and the Python view
+ * (crates/aethergraph-py/src/sampler.rs:329-370): edge_index_local is
+ * [2, num_edges] row-major int64, row 0 = sampled neighbor (dst_local),
+ * row 1 = expanded node (src_local). */
+typedef struct {
+    uint64_t cap_nodes, cap_edges, cap_seeds; /* capacities of the arrays below */
+    uint32_t *nodes;        /* [cap_nodes] global ids in discovery order */
+    uint32_t *edge_src;     /* [cap_edges] expanded node                (optional) */
+    uint32_t *edge_dst;     /* [cap_edges] sampled neighbor */
+    uint64_t *edge_ids;     /* [cap_edges] CSR position                 (optional) */
+    uint32_t *src_local;    /* [cap_edges] */
+    uint32_t *dst_local;    /* [cap_edges] */
+    uint32_t *seed_locals;  /* [cap_seeds] */
+    int64_t *n_id;          /* [cap_nodes] int64(nodes)                 (optional) */
+    int64_t *edge_index_local; /* [2 * num_edges] packed at the final count (optional) */
+    int64_t *e_id;          /* [cap_edges] int64(edge_ids)              (optional) */
+    int64_t *seed_index;    /* [cap_seeds] int64(seed_locals)           (optional) */
+    float *x;               /* [cap_nodes, dim] gathered rows           (optional) */
+} ag_subgraph_buffers;
+
+typedef struct {
+    uint32_t num_nodes, num_edges, num_seeds, num_hops;
+    uint32_t nodes_per_hop[AG_MAX_HOPS + 1]; /* [distinct seeds, new@hop1, ...] sampler.rs:876-883 */
+    uint32_t edges_per_hop[AG_MAX_HOPS];
+    uint64_t draws;          /* RNG draws consumed by this batch */
+    uint32_t error;          /* device-side error bits, 0 = none */
+    uint32_t reserved;
+} ag_sample_counts;
+
+int32_t ag_sampler_create(const ag_graph *g, const ag_sampling_config *cfg, ag_sampler **out);
+/* NeighborSampler::reseed (sampler.rs:509-511): restarts the stream at draw 0. */
+int32_t ag_sampler_reseed(ag_sampler *s, uint64_t seed);
+/* Upper bounds on nodes / edges for a batch of n_seeds (for sizing buffers). */
+int32_t ag_sampler_bounds(const ag_sampler *s, uint64_t n_seeds, uint64_t *max_nodes,
+                          uint64_t *max_edges);
+/* Enqueues one batch on `stream`.  seeds: host array (range-checked here like
+ * Seeds::new, sampler.rs:230-239 -> AG_ERR_SAMPLING) when seeds_mem ==
+ * AG_MEM_HOST, else a device array (checked on the device, reported through
+ * counts.error).  When `feats` is not NULL and buf->x is set, the gather of
+ * the batch's nodes is enqueued right behind the sampler.  Returns as soon as
+ * the work is queued; ag_sample_wait blocks until it is done and returns the
+ * counts.  A bare sampler keeps consuming one RNG stream across calls
+ * (crates/aethergraph-py/src/sampler.rs:782-785). */
+int32_t ag_sample_into(ag_sampler *s, const uint32_t *seeds, uint64_t n_seeds, int32_t seeds_mem,
+                       const ag_features *feats, ag_subgraph_buffers *buf, void *stream);
+int32_t ag_sample_wait(ag_sampler *s, ag_sample_counts *counts);
+/* Library-allocated variant: fills *buf with buffers sized by
+ * ag_sampler_bounds; release them with ag_subgraph_release. */
+int32_t ag_sample(ag_sampler *s, const uint32_t *seeds, uint64_t n_seeds,
+                  const ag_features *feats, int32_t want_int64, ag_subgraph_buffers *buf,
+                  void *stream);
+int32_t ag_subgraph_release(ag_sampler *s, ag_subgraph_buffers *buf);
+void ag_sampler_free(ag_sampler *s);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AETHERGPU_H */

@@ -1,0 +1,391 @@
+"""ctypes binding of the CPU oracle (liboracle.so) — TEST INFRASTRUCTURE.
+
+The oracle restates the reference's CPU minibatch path in plain C (see
+oracle.h).  Only tests, the smoke check and the bench's CPU-baseline legs may
+import this module; the shipped package never does.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "liboracle.so")
+
+F32, F16, BF16 = 0, 1, 2
+DTYPE_TAG = {"f32": F32, "f16": F16, "bf16": BF16}
+
+
+def build(force: bool = False) -> str:
+    """Compile liboracle.so with the Makefile beside this file."""
+    src = os.path.join(_HERE, "oracle.c")
+    stale = (not os.path.exists(_LIB_PATH)
+             or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src)
+             or os.path.getmtime(_LIB_PATH) < os.path.getmtime(os.path.join(_HERE, "oracle.h")))
+    if force or stale:
+        subprocess.run(["make", "-C", _HERE, "-B", "liboracle.so"], check=True,
+                       stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+    return _LIB_PATH
+
+
+class _Csr(C.Structure):
+    _fields_ = [("offsets", C.c_void_p), ("edges", C.c_void_p), ("weights", C.c_void_p),
+                ("num_nodes", C.c_uint64), ("num_edges", C.c_uint64)]
+
+
+class _Config(C.Structure):
+    _fields_ = [("fanout", C.c_void_p), ("num_hops", C.c_uint32), ("replace", C.c_int),
+                ("weighted", C.c_int), ("track_edge_ids", C.c_int), ("seed", C.c_uint64),
+                ("dense_dedup_max_nodes", C.c_uint64)]
+
+
+class _Subgraph(C.Structure):
+    _fields_ = [("nodes", C.POINTER(C.c_uint32)), ("num_nodes", C.c_size_t),
+                ("edge_src", C.POINTER(C.c_uint32)), ("edge_dst", C.POINTER(C.c_uint32)),
+                ("edge_ids", C.POINTER(C.c_uint64)),
+                ("src_local", C.POINTER(C.c_uint32)), ("dst_local", C.POINTER(C.c_uint32)),
+                ("num_edges", C.c_size_t),
+                ("seed_locals", C.POINTER(C.c_uint32)), ("num_seeds", C.c_size_t),
+                ("num_sampled_nodes", C.POINTER(C.c_uint64)),
+                ("num_sampled_edges", C.POINTER(C.c_uint64)),
+                ("num_hops", C.c_uint32), ("draws", C.c_uint64)]
+
+
+class _Relation(C.Structure):
+    _fields_ = [("src_type", C.c_uint32), ("dst_type", C.c_uint32), ("csr", _Csr)]
+
+
+class _InAdj(C.Structure):
+    _fields_ = [("offsets", C.POINTER(C.c_uint64)), ("sources", C.POINTER(C.c_uint32)),
+                ("num_dst", C.c_uint64)]
+
+
+class _HeteroConfig(C.Structure):
+    _fields_ = [("num_node_types", C.c_uint32), ("num_nodes", C.c_void_p),
+                ("num_edge_types", C.c_uint32), ("relations", C.POINTER(_Relation)),
+                ("fanout", C.c_void_p), ("num_hops", C.c_uint32), ("replace", C.c_int),
+                ("seed", C.c_uint64), ("dense_dedup_max_nodes", C.c_uint64)]
+
+
+class _HeteroSubgraph(C.Structure):
+    _fields_ = [("num_node_types", C.c_uint32), ("num_edge_types", C.c_uint32),
+                ("nodes", C.POINTER(C.POINTER(C.c_uint32))), ("num_nodes", C.POINTER(C.c_size_t)),
+                ("edge_src_local", C.POINTER(C.POINTER(C.c_uint32))),
+                ("edge_dst_local", C.POINTER(C.POINTER(C.c_uint32))),
+                ("num_edges", C.POINTER(C.c_size_t)),
+                ("seed_indices", C.POINTER(C.c_uint32)), ("num_seeds", C.c_size_t),
+                ("draws", C.c_uint64)]
+
+
+class _BenchResult(C.Structure):
+    _fields_ = [("batches", C.c_uint64), ("edges", C.c_uint64), ("nodes", C.c_uint64),
+                ("seconds", C.c_double), ("threads", C.c_int), ("checksum", C.c_uint64)]
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            build()
+        L = C.CDLL(_LIB_PATH)
+        L.ago_batch_seed.restype = C.c_uint64
+        L.ago_batch_seed.argtypes = [C.c_uint64, C.c_uint64]
+        L.ago_wyrand_at.restype = C.c_uint64
+        L.ago_wyrand_at.argtypes = [C.c_uint64, C.c_uint64]
+        L.ago_wyrand_next_u64.restype = C.c_uint64
+        L.ago_wyrand_next_u64.argtypes = [C.POINTER(C.c_uint64)]
+        L.ago_philox4x32_10.restype = None
+        L.ago_philox4x32_10.argtypes = [C.c_uint64, C.c_uint32, C.c_uint64, C.c_uint32,
+                                        C.POINTER(C.c_uint32)]
+        L.ago_philox_u32.restype = C.c_uint32
+        L.ago_philox_u32.argtypes = [C.c_uint64, C.c_uint32, C.c_uint64, C.c_uint32]
+        L.ago_reservoir_sample.restype = C.c_size_t
+        L.ago_reservoir_sample.argtypes = [C.c_void_p, C.c_size_t, C.c_size_t, C.c_uint64,
+                                           C.c_uint32, C.c_uint64, C.c_void_p]
+        L.ago_neg_ln_u64.restype = C.c_double
+        L.ago_neg_ln_u64.argtypes = [C.c_uint64]
+        L.ago_f32_to_bf16.restype = C.c_uint16
+        L.ago_f32_to_bf16.argtypes = [C.c_float]
+        L.ago_f32_to_f16.restype = C.c_uint16
+        L.ago_f32_to_f16.argtypes = [C.c_float]
+        L.ago_bf16_to_f32.restype = C.c_float
+        L.ago_bf16_to_f32.argtypes = [C.c_uint16]
+        L.ago_f16_to_f32.restype = C.c_float
+        L.ago_f16_to_f32.argtypes = [C.c_uint16]
+        L.ago_encode_rows.restype = None
+        L.ago_encode_rows.argtypes = [C.c_void_p, C.c_size_t, C.c_int, C.c_void_p]
+        L.ago_decode_rows.restype = None
+        L.ago_decode_rows.argtypes = [C.c_void_p, C.c_size_t, C.c_int, C.c_void_p]
+        L.ago_gather.restype = C.c_int64
+        L.ago_gather.argtypes = [C.c_void_p, C.c_uint64, C.c_uint64, C.c_int, C.c_void_p,
+                                 C.c_size_t, C.c_void_p]
+        L.ago_crc32.restype = C.c_uint32
+        L.ago_crc32.argtypes = [C.c_uint32, C.c_void_p, C.c_size_t]
+        L.ago_sampler_new.restype = C.c_void_p
+        L.ago_sampler_new.argtypes = [C.POINTER(_Csr), C.POINTER(_Config)]
+        L.ago_sampler_free.restype = None
+        L.ago_sampler_free.argtypes = [C.c_void_p]
+        L.ago_sampler_reseed.restype = None
+        L.ago_sampler_reseed.argtypes = [C.c_void_p, C.c_uint64]
+        L.ago_sample.restype = C.c_int64
+        L.ago_sample.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.POINTER(_Subgraph)]
+        L.ago_subgraph_free.restype = None
+        L.ago_subgraph_free.argtypes = [C.POINTER(_Subgraph)]
+        L.ago_transpose.restype = None
+        L.ago_transpose.argtypes = [C.POINTER(_Csr), C.c_uint64, C.c_uint64, C.POINTER(_InAdj)]
+        L.ago_in_adjacency_free.restype = None
+        L.ago_in_adjacency_free.argtypes = [C.POINTER(_InAdj)]
+        L.ago_hetero_sampler_new.restype = C.c_void_p
+        L.ago_hetero_sampler_new.argtypes = [C.POINTER(_HeteroConfig)]
+        L.ago_hetero_sampler_free.restype = None
+        L.ago_hetero_sampler_free.argtypes = [C.c_void_p]
+        L.ago_hetero_sampler_reseed.restype = None
+        L.ago_hetero_sampler_reseed.argtypes = [C.c_void_p, C.c_uint64]
+        L.ago_hetero_sample.restype = C.c_int64
+        L.ago_hetero_sample.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_size_t,
+                                        C.POINTER(_HeteroSubgraph)]
+        L.ago_hetero_subgraph_free.restype = None
+        L.ago_hetero_subgraph_free.argtypes = [C.POINTER(_HeteroSubgraph)]
+        L.ago_hetero_in_adjacency.restype = C.POINTER(_InAdj)
+        L.ago_hetero_in_adjacency.argtypes = [C.c_void_p, C.c_uint32]
+        L.ago_bench_run.restype = C.c_int
+        L.ago_bench_run.argtypes = [C.POINTER(_Csr), C.POINTER(_Config), C.c_void_p, C.c_uint64,
+                                    C.c_int, C.c_void_p, C.c_size_t, C.c_size_t, C.c_uint64,
+                                    C.c_int, C.POINTER(_BenchResult)]
+        _lib = L
+    return _lib
+
+
+# ---------------------------------------------------------------- scalars --
+def batch_seed(base: int, idx: int) -> int:
+    return lib().ago_batch_seed(base & (2**64 - 1), idx)
+
+
+def wyrand_at(seed: int, d: int) -> int:
+    return lib().ago_wyrand_at(seed & (2**64 - 1), d)
+
+
+def wyrand_stream(seed: int, n: int) -> np.ndarray:
+    """The first n next_u64() values of a generator created with `seed`."""
+    st = C.c_uint64(seed & (2**64 - 1))
+    return np.array([lib().ago_wyrand_next_u64(C.byref(st)) for _ in range(n)], dtype=np.uint64)
+
+
+def philox4x32_10(seed: int, layer: int, node: int, draw_group: int = 0):
+    out = (C.c_uint32 * 4)()
+    lib().ago_philox4x32_10(seed, layer, node, draw_group, out)
+    return [int(x) for x in out]
+
+
+def philox_u32(seed: int, layer: int, node: int, draw_index: int) -> int:
+    return lib().ago_philox_u32(seed, layer, node, draw_index)
+
+
+def reservoir_sample(neighbors, fanout: int, seed: int, layer: int, node: int) -> np.ndarray:
+    nb = np.ascontiguousarray(neighbors, dtype=np.uint32)
+    out = np.empty(max(len(nb), fanout, 1), dtype=np.uint32)
+    n = lib().ago_reservoir_sample(nb.ctypes.data, len(nb), fanout, seed, layer, node,
+                                   out.ctypes.data)
+    return out[:n].copy()
+
+
+def neg_ln_u64(bits: int) -> float:
+    return lib().ago_neg_ln_u64(bits)
+
+
+def crc32(data: bytes | np.ndarray, crc: int = 0) -> int:
+    a = np.frombuffer(data, dtype=np.uint8) if isinstance(data, (bytes, bytearray)) else \
+        np.ascontiguousarray(data).view(np.uint8).reshape(-1)
+    return lib().ago_crc32(crc, a.ctypes.data, a.size)
+
+
+# ----------------------------------------------------------------- codecs --
+def encode(features: np.ndarray, dtype: str) -> np.ndarray:
+    """f32 array -> stored payload (uint8 view of f32 / f16 bits / bf16 bits)."""
+    f = np.ascontiguousarray(features, dtype=np.float32)
+    tag = DTYPE_TAG[dtype]
+    out = np.empty(f.size * (4 if tag == F32 else 2), dtype=np.uint8)
+    lib().ago_encode_rows(f.ctypes.data, f.size, tag, out.ctypes.data)
+    return out
+
+
+def decode(payload: np.ndarray, dtype: str) -> np.ndarray:
+    """Stored payload (any integer/float array viewed as bytes) -> f32, bit-preserving."""
+    raw = np.ascontiguousarray(payload).view(np.uint8).reshape(-1)
+    tag = DTYPE_TAG[dtype]
+    n = raw.size // (4 if tag == F32 else 2)
+    out = np.empty(n, dtype=np.float32)
+    lib().ago_decode_rows(raw.ctypes.data, n, tag, out.ctypes.data)
+    return out
+
+
+def gather(payload: np.ndarray, num_nodes: int, dim: int, dtype: str, ids) -> np.ndarray:
+    ids = np.ascontiguousarray(ids, dtype=np.uint32)
+    payload = np.ascontiguousarray(payload)
+    out = np.empty((len(ids), dim), dtype=np.float32)
+    rc = lib().ago_gather(payload.ctypes.data, num_nodes, dim, DTYPE_TAG[dtype],
+                          ids.ctypes.data, len(ids), out.ctypes.data)
+    if rc != 0:
+        raise ValueError(f"node {int(ids[-1 - rc])} out of bounds")
+    return out
+
+
+# ---------------------------------------------------------------- sampler --
+def _csr_struct(offsets, edges, weights, keep):
+    offsets = np.ascontiguousarray(offsets, dtype=np.uint64)
+    edges = np.ascontiguousarray(edges, dtype=np.uint32)
+    keep += [offsets, edges]
+    w = None
+    if weights is not None:
+        w = np.ascontiguousarray(weights, dtype=np.float32)
+        keep.append(w)
+    return _Csr(offsets.ctypes.data, edges.ctypes.data if edges.size else None,
+                w.ctypes.data if w is not None else None, len(offsets) - 1, len(edges))
+
+
+def _np(ptr, n, dtype):
+    if n == 0:
+        return np.empty(0, dtype=dtype)
+    return np.ctypeslib.as_array(ptr, shape=(n,)).astype(dtype, copy=True)
+
+
+class Sampler:
+    """Oracle NeighborSampler (loader/sampler.rs)."""
+
+    def __init__(self, offsets, edges, fanout, *, weights=None, replace=False, weighted=False,
+                 track_edge_ids=True, seed=0, dense_dedup_max_nodes=0):
+        self._keep = []
+        self._csr = _csr_struct(offsets, edges, weights, self._keep)
+        fan = np.ascontiguousarray(fanout, dtype=np.uint32)
+        self._keep.append(fan)
+        self._cfg = _Config(fan.ctypes.data, len(fan), int(replace), int(weighted),
+                            int(track_edge_ids), seed & (2**64 - 1), dense_dedup_max_nodes)
+        self.seed = seed & (2**64 - 1)
+        self.num_hops = len(fan)
+        self._h = lib().ago_sampler_new(C.byref(self._csr), C.byref(self._cfg))
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            lib().ago_sampler_free(self._h)
+            self._h = None
+
+    def reseed(self, seed: int):
+        lib().ago_sampler_reseed(self._h, seed & (2**64 - 1))
+
+    def sample(self, seeds) -> dict:
+        seeds = np.ascontiguousarray(seeds, dtype=np.uint32)
+        sg = _Subgraph()
+        rc = lib().ago_sample(self._h, seeds.ctypes.data, len(seeds), C.byref(sg))
+        if rc != 0:
+            pos = -1 - rc
+            raise IndexError(f"seed node {int(seeds[pos])} (position {pos}) is out of range "
+                             f"for {self._csr.num_nodes} nodes")
+        try:
+            e = sg.num_edges
+            out = {
+                "nodes": _np(sg.nodes, sg.num_nodes, np.uint32),
+                "edge_src": _np(sg.edge_src, e, np.uint32),
+                "edge_dst": _np(sg.edge_dst, e, np.uint32),
+                "edge_ids": _np(sg.edge_ids, e, np.uint64) if sg.edge_ids else None,
+                "src_local": _np(sg.src_local, e, np.uint32),
+                "dst_local": _np(sg.dst_local, e, np.uint32),
+                "seed_locals": _np(sg.seed_locals, sg.num_seeds, np.uint32),
+                "num_sampled_nodes": _np(sg.num_sampled_nodes, sg.num_hops + 1, np.uint64),
+                "num_sampled_edges": _np(sg.num_sampled_edges, sg.num_hops, np.uint64),
+                "draws": int(sg.draws),
+            }
+        finally:
+            lib().ago_subgraph_free(C.byref(sg))
+        return out
+
+    def bench(self, payload, dim, dtype, seeds, batch_size, first_position=0, threads=1) -> dict:
+        seeds = np.ascontiguousarray(seeds, dtype=np.uint32)
+        nb = len(seeds) // batch_size
+        res = _BenchResult()
+        ptr = None
+        if payload is not None:
+            payload = np.ascontiguousarray(payload)
+            ptr = payload.ctypes.data
+        rc = lib().ago_bench_run(C.byref(self._csr), C.byref(self._cfg), ptr, dim,
+                                 DTYPE_TAG[dtype] if dtype else 0, seeds.ctypes.data,
+                                 batch_size, nb, first_position, threads, C.byref(res))
+        if rc != 0:
+            raise RuntimeError("oracle bench run failed (bad seed or node id)")
+        return {"batches": res.batches, "edges": res.edges, "nodes": res.nodes,
+                "seconds": res.seconds, "threads": res.threads, "checksum": res.checksum}
+
+
+def transpose(offsets, edges, num_src: int, num_dst: int):
+    keep = []
+    csr = _csr_struct(offsets, edges, None, keep)
+    adj = _InAdj()
+    lib().ago_transpose(C.byref(csr), num_src, num_dst, C.byref(adj))
+    off = _np(adj.offsets, num_dst + 1, np.uint64)
+    src = _np(adj.sources, int(off[-1]), np.uint32)
+    lib().ago_in_adjacency_free(C.byref(adj))
+    return off, src
+
+
+class HeteroSampler:
+    """Oracle HeteroNeighborSampler (loader/hetero_sampler.rs).
+
+    num_nodes: list per node type; relations: list of (src_type, dst_type,
+    offsets, edges); fanout: [edge_type][hop].
+    """
+
+    def __init__(self, num_nodes, relations, fanout, *, replace=False, seed=0,
+                 dense_dedup_max_nodes=0):
+        self._keep = []
+        nn = np.ascontiguousarray(num_nodes, dtype=np.uint64)
+        fan = np.ascontiguousarray(fanout, dtype=np.uint32).reshape(len(relations), -1)
+        rel = (_Relation * max(len(relations), 1))()
+        for i, (st, dt, off, edg) in enumerate(relations):
+            rel[i] = _Relation(st, dt, _csr_struct(off, edg, None, self._keep))
+        self._keep += [nn, fan, rel]
+        self.num_node_types, self.num_edge_types = len(nn), len(relations)
+        self._num_nodes = nn
+        cfg = _HeteroConfig(len(nn), nn.ctypes.data, len(relations), rel, fan.ctypes.data,
+                            fan.shape[1], int(replace), seed & (2**64 - 1), dense_dedup_max_nodes)
+        self._h = lib().ago_hetero_sampler_new(C.byref(cfg))
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            lib().ago_hetero_sampler_free(self._h)
+            self._h = None
+
+    def reseed(self, seed: int):
+        lib().ago_hetero_sampler_reseed(self._h, seed & (2**64 - 1))
+
+    def in_adjacency(self, edge_type: int):
+        a = lib().ago_hetero_in_adjacency(self._h, edge_type).contents
+        off = _np(a.offsets, a.num_dst + 1, np.uint64)
+        return off, _np(a.sources, int(off[-1]), np.uint32)
+
+    def sample(self, seed_type: int, seeds) -> dict:
+        seeds = np.ascontiguousarray(seeds, dtype=np.uint32)
+        sg = _HeteroSubgraph()
+        rc = lib().ago_hetero_sample(self._h, seed_type, seeds.ctypes.data, len(seeds), C.byref(sg))
+        if rc != 0:
+            pos = -1 - rc
+            raise IndexError(f"seed node {int(seeds[pos])} (position {pos}) is out of range "
+                             f"for {int(self._num_nodes[seed_type])} nodes")
+        try:
+            out = {
+                "nodes": [_np(sg.nodes[t], sg.num_nodes[t], np.uint32)
+                          for t in range(sg.num_node_types)],
+                "edge_src_local": [_np(sg.edge_src_local[e], sg.num_edges[e], np.uint32)
+                                   for e in range(sg.num_edge_types)],
+                "edge_dst_local": [_np(sg.edge_dst_local[e], sg.num_edges[e], np.uint32)
+                                   for e in range(sg.num_edge_types)],
+                "seed_indices": _np(sg.seed_indices, sg.num_seeds, np.uint32),
+                "draws": int(sg.draws),
+            }
+        finally:
+            lib().ago_hetero_subgraph_free(C.byref(sg))
+        return out
