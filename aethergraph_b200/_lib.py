@@ -52,7 +52,20 @@ class SampleCounts(C.Structure):
     _fields_ = [("num_nodes", C.c_uint32), ("num_edges", C.c_uint32), ("num_seeds", C.c_uint32),
                 ("num_hops", C.c_uint32), ("nodes_per_hop", C.c_uint32 * (AG_MAX_HOPS + 1)),
                 ("edges_per_hop", C.c_uint32 * AG_MAX_HOPS), ("draws", C.c_uint64),
-                ("error", C.c_uint32), ("reserved", C.c_uint32)]
+                ("error", C.c_uint32), ("reserved", C.c_uint32),
+                ("sample_ms", C.c_float), ("gather_ms", C.c_float)]
+
+
+class Batch(C.Structure):
+    _fields_ = [("batch_idx", C.c_int64), ("seq", C.c_uint64), ("bufs", SubgraphBuffers),
+                ("counts", SampleCounts), ("owned", C.c_int32), ("reserved", C.c_int32)]
+
+
+class LoaderStats(C.Structure):
+    _fields_ = [("hits", C.c_uint64), ("misses", C.c_uint64), ("total", C.c_uint64),
+                ("sample_time_ns", C.c_uint64), ("feature_load_time_ns", C.c_uint64),
+                ("submitted", C.c_uint64), ("edges", C.c_uint64), ("nodes", C.c_uint64),
+                ("gather_ms", C.c_double), ("sample_ms", C.c_double)]
 
 
 _P = C.c_void_p
@@ -74,6 +87,9 @@ SIGNATURES = {
     "ag_graph_device_ptrs": (C.c_int32, [_P, _PP, _PP, _PP]),
     "ag_graph_degrees": (C.c_int32, [_P, _P, C.c_uint64, _P]),
     "ag_graph_neighbors": (C.c_int32, [_P, C.c_uint32, _P, _P, C.c_uint64, _U64P]),
+    "ag_graph_copy_to_host": (C.c_int32, [_P, _P, _P, _P]),
+    "ag_features_copy_to_host": (C.c_int32, [_P, _P]),
+    "ag_features_shard": (C.c_int32, [_P, _U64P, _U64P]),
     "ag_graph_free": (None, [_P]),
     "ag_features_save": (C.c_int32, [C.c_char_p, _P, C.c_uint64, C.c_uint64, C.c_int32]),
     "ag_features_load": (C.c_int32, [C.c_char_p, C.c_int32, _PP]),
@@ -95,6 +111,25 @@ SIGNATURES = {
     "ag_sample": (C.c_int32, [_P, _P, C.c_uint64, _P, C.c_int32, C.POINTER(SubgraphBuffers), _P]),
     "ag_subgraph_release": (C.c_int32, [_P, C.POINTER(SubgraphBuffers)]),
     "ag_sampler_free": (None, [_P]),
+    "ag_sampler_set_profiling": (C.c_int32, [_P, C.c_int32]),
+    "ag_loader_create": (C.c_int32, [_P, _P, C.POINTER(SamplingConfigC), C.c_int32, C.c_uint32, C.c_uint32,
+                                     C.c_int32, _PP]),
+    "ag_loader_bounds": (C.c_int32, [_P, C.c_uint64, _U64P, _U64P]),
+    "ag_loader_submit": (C.c_int32, [_P, C.c_int64, _P, C.c_uint64, C.c_int32, C.POINTER(SubgraphBuffers), _P]),
+    "ag_loader_next": (C.c_int32, [_P, C.c_int64, C.POINTER(Batch)]),
+    "ag_loader_try_next": (C.c_int32, [_P, C.POINTER(Batch)]),
+    "ag_loader_release_batch": (C.c_int32, [_P, C.POINTER(Batch)]),
+    "ag_loader_stats_get": (C.c_int32, [_P, C.POINTER(LoaderStats)]),
+    "ag_loader_shutdown": (C.c_int32, [_P]),
+    "ag_loader_free": (None, [_P]),
+    "ag_synth_rmat_graph": (C.c_int32, [C.c_uint64, C.c_uint64, C.c_float, C.c_float, C.c_float, C.c_uint64,
+                                        C.c_float, C.c_int32, _PP]),
+    "ag_synth_rmat_csr": (C.c_int32, [C.c_uint64, C.c_uint64, C.c_uint64, C.c_float, C.c_float, C.c_float,
+                                      C.c_uint64, C.c_float, C.c_int32, _PP, _PP, _PP]),
+    "ag_synth_fixed_degree_csr": (C.c_int32, [C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint64, C.c_int32, _PP, _PP]),
+    "ag_synth_free_device": (C.c_int32, [_P, C.c_int32]),
+    "ag_synth_features": (C.c_int32, [C.c_uint64, C.c_uint64, C.c_int32, C.c_uint64, C.c_int32, C.c_uint64,
+                                      C.c_uint64, _PP]),
 }
 
 _lib = None

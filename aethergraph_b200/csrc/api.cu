@@ -399,6 +399,26 @@ extern "C" int32_t ag_graph_device_ptrs(const ag_graph *g, const uint64_t **offs
     return AG_OK;
 }
 
+extern "C" int32_t ag_graph_copy_to_host(const ag_graph *g, uint64_t *offsets, uint32_t *dst, float *weights) {
+    if (!g) return fail(AG_ERR_VALUE, "ag_graph_copy_to_host: null graph");
+    DeviceGuard guard(g->device);
+    if (!guard.ok) return AG_ERR_CUDA;
+    if (offsets) AG_CUDA(cudaMemcpy(offsets, g->offsets, (g->num_nodes + 1) * 8, cudaMemcpyDeviceToHost));
+    if (dst && g->num_edges) AG_CUDA(cudaMemcpy(dst, g->dst, g->num_edges * 4, cudaMemcpyDeviceToHost));
+    if (weights && g->weights && g->num_edges)
+        AG_CUDA(cudaMemcpy(weights, g->weights, g->num_edges * 4, cudaMemcpyDeviceToHost));
+    return AG_OK;
+}
+
+extern "C" int32_t ag_features_copy_to_host(const ag_features *f, void *payload) {
+    if (!f || !payload) return fail(AG_ERR_VALUE, "ag_features_copy_to_host: null argument");
+    DeviceGuard guard(f->device);
+    if (!guard.ok) return AG_ERR_CUDA;
+    const uint64_t bytes = f->rows * f->dim * elem_size(f->dtype);
+    if (bytes) AG_CUDA(cudaMemcpy(payload, f->payload, bytes, cudaMemcpyDeviceToHost));
+    return AG_OK;
+}
+
 extern "C" int32_t ag_graph_degrees(const ag_graph *g, const uint32_t *ids, uint64_t n, uint32_t *out) {
     if (!g || (!out && n)) return fail(AG_ERR_VALUE, "ag_graph_degrees: null argument");
     if (n == 0) return AG_OK;
@@ -649,6 +669,13 @@ extern "C" int32_t ag_features_info(const ag_features *f, uint64_t *num_nodes, u
     if (dtype) *dtype = f->dtype;
     if (device) *device = f->device;
     if (row_begin) *row_begin = f->row_begin;
+    return AG_OK;
+}
+
+extern "C" int32_t ag_features_shard(const ag_features *f, uint64_t *row_begin, uint64_t *rows) {
+    if (!f) return fail(AG_ERR_VALUE, "ag_features_shard: null store");
+    if (row_begin) *row_begin = f->row_begin;
+    if (rows) *rows = f->rows;
     return AG_OK;
 }
 

@@ -188,7 +188,7 @@ k_assign(SampleParams p, uint32_t stage, uint32_t n_seeds, uint32_t next_k, int 
                                  base.draws + incl.draws - v.draws};
     const uint32_t rank = excl.flags;
     const uint32_t local = si.n_nodes + rank;
-    if ((uint64_t)local >= p.cap_nodes || (uint64_t)rank >= p.frontier_cap) {
+    if ((uint64_t)local >= p.cap_nodes || (has_next && (uint64_t)rank >= p.frontier_cap)) {
         atomicOr(&bs->error, kErrCapacity);
         return;
     }
@@ -475,6 +475,9 @@ struct ag_sampler {
     ag_sample_counts *counts_host = nullptr;
     cudaEvent_t done = nullptr;
     bool in_flight = false;
+    // optional per-batch device timing
+    bool profile = false, gathered = false;
+    cudaEvent_t ev[3] = {nullptr, nullptr, nullptr};
     // buffers handed out by ag_sample (library-allocated variant)
     std::vector<void *> owned;
 };
@@ -588,6 +591,7 @@ extern "C" void ag_sampler_free(ag_sampler *s) {
     cudaFree(s->state); cudaFree(s->counts_dev);
     if (s->counts_host) cudaFreeHost(s->counts_host);
     if (s->done) cudaEventDestroy(s->done);
+    for (auto &e : s->ev) if (e) cudaEventDestroy(e);
     delete s;
 }
 
@@ -595,6 +599,16 @@ extern "C" int32_t ag_sampler_reseed(ag_sampler *s, uint64_t seed) {
     if (!s) return fail(AG_ERR_VALUE, "ag_sampler_reseed: null sampler");
     s->seed = seed;
     s->reset_pos = true;
+    return AG_OK;
+}
+
+extern "C" int32_t ag_sampler_set_profiling(ag_sampler *s, int32_t on) {
+    if (!s) return fail(AG_ERR_VALUE, "ag_sampler_set_profiling: null sampler");
+    DeviceGuard guard(s->device);
+    if (!guard.ok) return AG_ERR_CUDA;
+    if (on && !s->ev[0])
+        for (auto &e : s->ev) AG_CUDA(cudaEventCreate(&e));
+    s->profile = on != 0;
     return AG_OK;
 }
 
@@ -642,6 +656,7 @@ extern "C" int32_t ag_sample_into(ag_sampler *s, const uint32_t *seeds, uint64_t
     const uint64_t tcap = std::min(s->table_cap, std::max<uint64_t>(1024, next_pow2(2 * b_nodes)));
     uint32_t log2cap = 0;
     while ((1ull << log2cap) < tcap) ++log2cap;
+    if (s->profile) AG_CUDA(cudaEventRecord(s->ev[0], st));
     AG_CUDA(cudaMemsetAsync(s->table, 0xFF, tcap * 8, st));
 
     SampleParams p{};
@@ -710,6 +725,8 @@ extern "C" int32_t ag_sample_into(ag_sampler *s, const uint32_t *seeds, uint64_t
     const uint32_t fblocks = (uint32_t)std::min<uint64_t>((work + 255) / 256, (uint64_t)kSMs * 8);
     k_finalize<<<fblocks, 256, 0, st>>>(p, f);
     AG_CUDA(cudaGetLastError());
+    if (s->profile) AG_CUDA(cudaEventRecord(s->ev[1], st));
+    s->gathered = false;
 
     if (feats && buf->x) {
         GatherArgs ga{};
@@ -720,6 +737,8 @@ extern "C" int32_t ag_sample_into(ag_sampler *s, const uint32_t *seeds, uint64_t
         ga.n_dev = &s->counts_dev->num_nodes;
         ga.out = buf->x; ga.err = feats->err;
         AG_CUDA(launch_gather(ga, feats->dtype, st));
+        if (s->profile) AG_CUDA(cudaEventRecord(s->ev[2], st));
+        s->gathered = true;
     }
     AG_CUDA(cudaMemcpyAsync(s->counts_host, s->counts_dev, sizeof(ag_sample_counts), cudaMemcpyDeviceToHost, st));
     AG_CUDA(cudaEventRecord(s->done, st));
@@ -734,7 +753,12 @@ extern "C" int32_t ag_sample_wait(ag_sampler *s, ag_sample_counts *counts) {
     if (!guard.ok) return AG_ERR_CUDA;
     AG_CUDA(cudaEventSynchronize(s->done));
     s->in_flight = false;
-    const ag_sample_counts c = *s->counts_host;
+    ag_sample_counts c = *s->counts_host;
+    c.sample_ms = c.gather_ms = 0.f;
+    if (s->profile) {
+        cudaEventElapsedTime(&c.sample_ms, s->ev[0], s->ev[1]);
+        if (s->gathered) cudaEventElapsedTime(&c.gather_ms, s->ev[1], s->ev[2]);
+    }
     if (counts) *counts = c;
     if (c.error & kErrBadSeed) return fail(AG_ERR_SAMPLING, "a seed node is out of range for %llu nodes",
                                            (unsigned long long)s->g->num_nodes);

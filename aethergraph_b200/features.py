@@ -39,6 +39,9 @@ class FeatureStore:
         _lib.check(_lib.lib().ag_features_info(self._h, C.byref(n), C.byref(d), C.byref(t), C.byref(dev),
                                                C.byref(rb)))
         self._n, self._dim, self._dtype, self._device, self._row_begin = n.value, d.value, t.value, dev.value, rb.value
+        rows = C.c_uint64()
+        _lib.check(_lib.lib().ag_features_shard(self._h, None, C.byref(rows)))
+        self._rows = rows.value
 
     def __del__(self):
         h = getattr(self, "_h", None)
@@ -137,7 +140,15 @@ class FeatureStore:
 
     def features(self) -> np.ndarray:
         """The whole store decoded to f32 (host)."""
-        return self.get_batch(np.arange(self._row_begin, self._row_begin + self._n, dtype=np.int64))
+        return self.get_batch(np.arange(self._row_begin, self._row_begin + self._rows, dtype=np.int64))
+
+    def payload_to_host(self) -> np.ndarray:
+        """The stored (encoded) rows held by this handle as a flat host array
+        (float32 for f32 stores, uint16 bit patterns for f16 / bf16)."""
+        out = np.empty(self._rows * self._dim, dtype=np.float32 if self._dtype == _lib.AG_F32 else np.uint16)
+        if out.size:
+            _lib.check(_lib.lib().ag_features_copy_to_host(self._h, out.ctypes.data))
+        return out
 
     def gather(self, ids, out=None, stream=None):
         """Device gather: `ids` is a CUDA tensor (int64, or int32 holding u32 ids);

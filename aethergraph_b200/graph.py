@@ -146,6 +146,15 @@ class CsrGraph:
         _lib.check(_lib.lib().ag_graph_device_ptrs(self._h, C.byref(a), C.byref(b), C.byref(c)))
         return a.value or 0, b.value or 0, c.value or 0
 
+    def to_host(self):
+        """(offsets u64, destinations u32, weights f32 | None) copied back to host numpy arrays."""
+        off = np.empty(self._n + 1, dtype=np.uint64)
+        dst = np.empty(self._e, dtype=np.uint32)
+        w = np.empty(self._e, dtype=np.float32) if self._w else None
+        _lib.check(_lib.lib().ag_graph_copy_to_host(self._h, off.ctypes.data, dst.ctypes.data if self._e else None,
+                                                    w.ctypes.data if (w is not None and self._e) else None))
+        return off, dst, w
+
     # -- row access --------------------------------------------------------
     def degrees(self) -> np.ndarray:
         out = np.empty(self._n, dtype=np.uint32)

@@ -1,0 +1,189 @@
+"""Prefetching `NeighborLoader` over the native GPU pipeline.
+
+Mirrors `aethergraph._core.NeighborLoader` / `PrefetchStats`
+(python/aethergraph/_core.pyi:352-464): `submit(batch_idx, seeds)` queues a
+batch, `next_batch()` returns `(batch_idx, subgraph, features)`.  With a config
+seed, batches come back in submission order and batch number `seq` is sampled
+from `batch_seed(seed, seq)` whatever the number of sampler threads; without a
+seed they come back as they finish.  `None` is returned only after `shutdown()`;
+a worker failure raises RuntimeError, a 30 s wait TimeoutError.
+
+The batches are born in GPU memory: `subgraph.*_t` and `features` are CUDA
+tensors.  Pass `host_features=True` to get the feature block as a host numpy
+array the way the reference returns it.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import secrets
+import threading
+from typing import Any
+
+import numpy as np
+
+from . import _lib
+from .features import FeatureStore
+from .graph import CsrGraph
+from .sampler import SampledSubgraph, SamplingConfig, _Buffers, _check_config, coerce_seeds
+
+__all__ = ["NeighborLoader", "PrefetchStats"]
+
+
+class PrefetchStats:
+    """Snapshot of the loader's counters (crates/aethergraph-core/src/loader/prefetch.rs:853-899)."""
+
+    def __init__(self, s: _lib.LoaderStats):
+        self.hits, self.misses, self.total = s.hits, s.misses, s.total
+        self.sample_time_ns, self.feature_load_time_ns = s.sample_time_ns, s.feature_load_time_ns
+        self.submitted, self.edges, self.nodes = s.submitted, s.edges, s.nodes
+        self.gather_ms, self.sample_ms = s.gather_ms, s.sample_ms
+
+    @property
+    def hit_rate(self) -> float:
+        return 1.0 if self.total == 0 else self.hits / self.total
+
+    def to_dict(self) -> dict[str, Any]:
+        return {"hits": self.hits, "misses": self.misses, "total": self.total, "hit_rate": self.hit_rate,
+                "sample_time_ns": self.sample_time_ns, "feature_load_time_ns": self.feature_load_time_ns}
+
+
+class NeighborLoader:
+    def __init__(self, graph: CsrGraph, config: SamplingConfig, prefetch_depth: int = 2,
+                 sampler_threads: int = 1, *, features: FeatureStore | None = None,
+                 host_features: bool = False, profiling: bool = False):
+        _check_config(graph, config)
+        if prefetch_depth < 1:
+            raise ValueError("prefetch_depth must be >= 1")
+        if sampler_threads < 1:
+            raise ValueError("sampler_threads must be >= 1")
+        self.graph, self.config, self.features = graph, config, features
+        self._depth, self._host_features = prefetch_depth, host_features
+        self._seeded = config.seed is not None
+        seed = config.seed if self._seeded else secrets.randbits(64)
+        cfg = config._to_c(seed)
+        self._h = C.c_void_p()
+        _lib.check(_lib.lib().ag_loader_create(graph._h, features._h if features is not None else None,
+                                               C.byref(cfg), int(self._seeded), prefetch_depth, sampler_threads,
+                                               int(profiling), C.byref(self._h)))
+        self._lock = threading.Lock()
+        self._next_seq = 0
+        self._inflight: dict[int, tuple[_Buffers, np.ndarray]] = {}
+        self._closed = False
+
+    @staticmethod
+    def with_features(graph: CsrGraph, config: SamplingConfig, feature_path, prefetch_depth: int = 2,
+                      sampler_threads: int = 1, **kw) -> "NeighborLoader":
+        store = FeatureStore.load(os.fspath(feature_path), device=graph.device)
+        if store.num_nodes < graph.num_nodes:
+            raise ValueError(f"feature file has {store.num_nodes} rows but the graph has {graph.num_nodes} nodes")
+        return NeighborLoader(graph, config, prefetch_depth, sampler_threads, features=store, **kw)
+
+    # -- properties --------------------------------------------------------
+    @property
+    def feature_dim(self) -> int | None:
+        return self.features.feature_dim if self.features is not None else None
+
+    @property
+    def has_features(self) -> bool:
+        return self.features is not None
+
+    @property
+    def num_nodes(self) -> int:
+        return self.graph.num_nodes
+
+    @property
+    def prefetch_depth(self) -> int:
+        return self._depth
+
+    # -- producer side -----------------------------------------------------
+    def submit(self, batch_idx: int, seeds) -> None:
+        """Queue a batch.  `batch_idx` is echoed back by `next_batch()`; any value is accepted."""
+        import torch
+
+        s = coerce_seeds(seeds, self.graph.num_nodes)
+        dev = torch.device("cuda", self.graph.device)
+        mn, me = C.c_uint64(), C.c_uint64()
+        _lib.check(_lib.lib().ag_loader_bounds(self._h, len(s), C.byref(mn), C.byref(me)))
+        with torch.cuda.device(dev):
+            bufs = _Buffers(dev, mn.value, me.value, len(s), self.config.track_edge_ids, self.feature_dim)
+            after = torch.cuda.current_stream(dev).cuda_stream
+        with self._lock:
+            # The C call blocks while the work queue is full; the lock keeps the
+            # Python-side sequence counter in step with the library's.
+            seq = self._next_seq
+            self._inflight[seq] = (bufs, s)  # in place before a worker can finish the batch
+            rc = _lib.lib().ag_loader_submit(self._h, int(batch_idx), s.ctypes.data if len(s) else None,
+                                             len(s), _lib.AG_MEM_HOST, C.byref(bufs.c), after)
+            if rc != _lib.AG_OK:
+                del self._inflight[seq]
+                _lib.check(rc)
+            self._next_seq += 1
+
+    def submit_epoch(self, batches) -> None:
+        for i, b in enumerate(batches):
+            self.submit(i, b)
+
+    # -- consumer side -----------------------------------------------------
+    def _take(self, blocking: bool):
+        if self._closed:
+            return None
+        b = _lib.Batch()
+        rc = (_lib.lib().ag_loader_next(self._h, -1, C.byref(b)) if blocking
+              else _lib.lib().ag_loader_try_next(self._h, C.byref(b)))
+        if rc == _lib.AG_ERR_SHUTDOWN:
+            return None
+        if rc == _lib.AG_ERR_TIMEOUT and not blocking:
+            return None
+        _lib.check(rc)
+        bufs, seeds = self._inflight.pop(b.seq)
+        sg = SampledSubgraph(bufs, b.counts, seeds)
+        return int(b.batch_idx), sg
+
+    def next_batch(self):
+        """`(batch_idx, subgraph, features)`, or None after `shutdown()`."""
+        got = self._take(True)
+        if got is None:
+            return None
+        idx, sg = got
+        x = sg.x
+        if x is not None and self._host_features:
+            x = x.cpu().numpy()
+        return idx, sg, x
+
+    def next(self):
+        got = self._take(True)
+        return None if got is None else got[1]
+
+    def try_next(self):
+        got = self._take(False)
+        return None if got is None else got[1]
+
+    def next_with_features(self):
+        got = self.next_batch()
+        return None if got is None else (got[1], got[2])
+
+    def stats(self) -> PrefetchStats:
+        s = _lib.LoaderStats()
+        _lib.check(_lib.lib().ag_loader_stats_get(self._h, C.byref(s)))
+        return PrefetchStats(s)
+
+    def shutdown(self) -> None:
+        if self._h:
+            _lib.lib().ag_loader_shutdown(self._h)
+        self._closed = True
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc) -> None:
+        self.shutdown()
+
+    def __del__(self):
+        h = getattr(self, "_h", None)
+        if h:
+            try:
+                _lib.lib().ag_loader_free(h)
+            except Exception:
+                pass
+            self._h = None

@@ -138,34 +138,67 @@ class _Buffers:
 
         self.cap_nodes, self.cap_edges, self.cap_seeds = cap_nodes, cap_edges, cap_seeds
         cn, ce, cs = _align4(cap_nodes), _align4(cap_edges), _align4(cap_seeds)
-        self.a32 = torch.empty(cn + 4 * ce + cs, dtype=torch.int32, device=device)
-        o = 0
-        self.nodes = self.a32[o:o + cn]; o += cn
-        self.edge_src = self.a32[o:o + ce]; o += ce
-        self.edge_dst = self.a32[o:o + ce]; o += ce
-        self.src_local = self.a32[o:o + ce]; o += ce
-        self.dst_local = self.a32[o:o + ce]; o += ce
-        self.seed_locals = self.a32[o:o + cs]
+        self._cn, self._ce, self._cs = cn, ce, cs
+        # One allocation per batch: the int64 arrays first (8-byte aligned), the
+        # 32-bit arrays behind them.  Views are made only when an accessor asks.
         n64 = cn + 2 * ce + cs + (ce if track_eids else 0)
-        self.a64 = torch.empty(n64, dtype=torch.int64, device=device)
-        o = 0
-        self.n_id = self.a64[o:o + cn]; o += cn
-        self.edge_index_local = self.a64[o:o + 2 * ce]; o += 2 * ce
-        self.seed_index = self.a64[o:o + cs]; o += cs
-        self.edge_ids = self.a64[o:o + ce] if track_eids else None
+        n32 = cn + 4 * ce + cs
+        self.arena = torch.empty(n64 + (n32 + 1) // 2, dtype=torch.int64, device=device)
+        self.a64 = self.arena[:n64]
+        self.a32 = self.arena[n64:].view(torch.int32)[:n32]
+        self.track_eids = track_eids
         self.x = (torch.empty((max(cap_nodes, 1), feature_dim), dtype=torch.float32, device=device)
                   if feature_dim is not None else None)
+        base64 = self.arena.data_ptr()
+        base32 = base64 + 8 * n64
         b = _lib.SubgraphBuffers()
         b.cap_nodes, b.cap_edges, b.cap_seeds = max(cap_nodes, 1), max(cap_edges, 1), max(cap_seeds, 1)
-        b.nodes, b.edge_src, b.edge_dst = self.nodes.data_ptr(), self.edge_src.data_ptr(), self.edge_dst.data_ptr()
-        b.src_local, b.dst_local = self.src_local.data_ptr(), self.dst_local.data_ptr()
-        b.seed_locals = self.seed_locals.data_ptr()
-        b.edge_ids = self.edge_ids.data_ptr() if track_eids else None
-        b.n_id, b.edge_index_local = self.n_id.data_ptr(), self.edge_index_local.data_ptr()
+        b.nodes = base32
+        b.edge_src = base32 + 4 * cn
+        b.edge_dst = base32 + 4 * (cn + ce)
+        b.src_local = base32 + 4 * (cn + 2 * ce)
+        b.dst_local = base32 + 4 * (cn + 3 * ce)
+        b.seed_locals = base32 + 4 * (cn + 4 * ce)
+        b.n_id = base64
+        b.edge_index_local = base64 + 8 * cn
+        b.seed_index = base64 + 8 * (cn + 2 * ce)
+        b.edge_ids = base64 + 8 * (cn + 2 * ce + cs) if track_eids else None
         b.e_id = None  # int64(edge id) has the same bits as the u64 the kernel writes
-        b.seed_index = self.seed_index.data_ptr()
         b.x = self.x.data_ptr() if self.x is not None else None
         self.c = b
+
+    # lazily built views of the arena
+    @property
+    def nodes(self):
+        return self.a32[:self._cn]
+
+    @property
+    def edge_src(self):
+        return self.a32[self._cn:self._cn + self._ce]
+
+    @property
+    def edge_dst(self):
+        return self.a32[self._cn + self._ce:self._cn + 2 * self._ce]
+
+    @property
+    def n_id(self):
+        return self.a64[:self._cn]
+
+    @property
+    def edge_index_local(self):
+        return self.a64[self._cn:self._cn + 2 * self._ce]
+
+    @property
+    def seed_index(self):
+        o = self._cn + 2 * self._ce
+        return self.a64[o:o + self._cs]
+
+    @property
+    def edge_ids(self):
+        if not self.track_eids:
+            return None
+        o = self._cn + 2 * self._ce + self._cs
+        return self.a64[o:o + self._ce]
 
 
 def _u32_to_i64(t):
@@ -443,4 +476,10 @@ class ParallelBatchSampler:
                 out[slot[0]] = slot[1].result()
         for st in self._streams:
             cur.wait_stream(st)
+        for sg in out:
+            # The buffers were allocated on a side stream; tell the allocator the
+            # caller's stream uses them too before it may recycle them.
+            sg._b.arena.record_stream(cur)  # type: ignore[union-attr]
+            if sg._b.x is not None:  # type: ignore[union-attr]
+                sg._b.x.record_stream(cur)  # type: ignore[union-attr]
         return out  # type: ignore[return-value]

@@ -1,0 +1,454 @@
+#!/usr/bin/env python
+"""Benchmark of the minibatch hot path: k-hop neighbor sampling + feature gather.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2] [--impl reference]
+
+One step = one `sample_batches`-sized round of BATCHES_PER_STEP seed batches
+(batch size, fanout, graph and feature shape from the workload), each batch
+sampled, deduplicated, relabelled and its feature rows gathered.  Prints ONE
+JSON line (rank 0).  Inputs are seeded synthetic stand-ins generated in place
+(R-MAT graph, ~N(0,1) features); no dataset is read.
+
+  value   sampled edges/s with the graph, features and seed batches resident in
+          HBM, driven through the C ABI (ag_loader_*), whole job over all GPUs.
+  e2e     the same metric through the public Python API (NeighborLoader.submit /
+          next_batch) with host seed arrays copied to the device and the batch
+          counts read back every batch; the sampled batch itself stays in GPU
+          memory, where the training step consumes it.
+  --impl reference   the CPU restatement of the reference's sampler + gather
+          (oracle/, C + OpenMP) on the host cores, same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+BATCHES_PER_STEP = 16
+METRIC = "sampled edges/s (k-hop sampling + dedup/relabel + feature gather)"
+
+WORKLOADS = {
+    # 100M-vertex R-MAT, 2B edges, 256-dim bf16 features, batch 1024, fanout [25, 10]
+    "c2": dict(nodes=100_000_000, edges=2_000_000_000, dim=256, dtype="bf16", batch=1024, fanout=[25, 10],
+               weighted=False, label="C2: R-MAT 100M vertices / 2B edges, 256-dim bf16, batch 1024, fanout [25,10]"),
+    # 1M-vertex R-MAT, 16M edges, 128-dim f32, batch 128, fanout [15, 10]
+    "c1": dict(nodes=1 << 20, edges=16 << 20, dim=128, dtype="f32", batch=128, fanout=[15, 10], weighted=False,
+               label="C1: R-MAT 1M vertices / 16M edges, 128-dim f32, batch 128, fanout [15,10]"),
+    # 10M-vertex weighted R-MAT, 200M edges, 128-dim f16, batch 512, fanout [15, 10, 5]
+    "c3": dict(nodes=10_000_000, edges=200_000_000, dim=128, dtype="f16", batch=512, fanout=[15, 10, 5],
+               weighted=True, label="C3: weighted R-MAT 10M vertices / 200M edges, 128-dim f16, batch 512, fanout [15,10,5]"),
+    "tiny": dict(nodes=1 << 16, edges=1 << 20, dim=64, dtype="bf16", batch=256, fanout=[10, 5], weighted=False,
+                 label="tiny: R-MAT 64K vertices / 1M edges, 64-dim bf16, batch 256, fanout [10,5]"),
+}
+GRAPH_SEED, FEATURE_SEED, SEEDS_SEED, SAMPLER_SEED = 1, 2, 3, 42
+
+
+def sector(x: int) -> int:
+    return (x + 31) // 32 * 32
+
+
+def gather_bytes_per_row(w) -> int:
+    esize = 4 if w["dtype"] == "f32" else 2
+    return sector(w["dim"] * esize) + w["dim"] * 4
+
+
+def sampling_bytes(edges: int, nodes: int, frontier: int) -> int:
+    """Algorithmic bytes of the sampling kernels: per frontier vertex one offsets
+    sector; per emitted edge one destination sector (upper bound: picks of a
+    sampled row are scattered), 24 B of edge outputs and a dedup probe sector read
+    and written; per new vertex 4 B (nodes) + 32 B (frontier entry)."""
+    return frontier * 32 + edges * (32 + 24 + 64) + nodes * 36
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+        except Exception:
+            pass
+    return 6650.0, "fallback (earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def stop(self, t0: float, t1: float) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, smax, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        rows = [l for (t, l) in self.lines if t0 - 0.05 <= t <= t1 + 0.15] or [l for (_, l) in self.lines]
+        for l in rows:
+            f = [x.strip() for x in l.split(",")]
+            try:
+                sm.append(float(f[0])); smax = float(f[1])
+            except Exception:
+                continue
+            for name, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": smax,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- #
+#  reference arm: the CPU restatement on the host cores                        #
+# --------------------------------------------------------------------------- #
+def cpu_threads() -> int:
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def host_seed_batches(w, first_batch: int, count: int) -> np.ndarray:
+    from aethergraph_b200 import synth
+
+    return np.concatenate([synth.seed_batch(w["nodes"], w["batch"], SEEDS_SEED, first_batch + i)
+                           for i in range(count)]) if count else np.empty(0, dtype=np.uint32)
+
+
+def run_reference(args, w):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return  # one CPU, one measurement: the other ranks exit without work
+    from oracle import ago
+
+    ago.build()
+    threads = cpu_threads()
+    t_setup = time.time()
+    offsets, dst = ago.synth_rmat_csr(w["nodes"], w["nodes"], w["edges"], GRAPH_SEED, threads=threads)
+    payload = ago.synth_features(w["nodes"], w["dim"], w["dtype"], FEATURE_SEED, threads=threads)
+    if w["weighted"]:
+        raise SystemExit(json.dumps({"impl": "reference", "unavailable":
+                                     "weighted workloads take their weights from the GPU generator"}))
+    t_setup = time.time() - t_setup
+    s = ago.Sampler(offsets, dst, w["fanout"], seed=SAMPLER_SEED)
+    per_step = BATCHES_PER_STEP
+    total = (args.warmup + args.steps) * per_step
+    seeds = host_seed_batches(w, 0, total)
+    bs = w["batch"]
+    if args.warmup:
+        s.bench(payload, w["dim"], w["dtype"], seeds[:args.warmup * per_step * bs], bs, 0, threads)
+    t0 = time.time()
+    r = s.bench(payload, w["dim"], w["dtype"], seeds[args.warmup * per_step * bs:], bs,
+                args.warmup * per_step, threads)
+    wall = time.time() - t0
+    secs = r["seconds"]
+    value = r["edges"] / secs
+    gbs = r["nodes"] * gather_bytes_per_row(w) / secs / 1e9
+    sample = f"{args.steps} steps x {per_step} batches of {bs} seeds (the full step, all {threads} host threads)"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "edges/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs * 1e3 / max(args.steps, 1),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u32 ids / " + w["dtype"] + "->f32",
+        "data": "synthetic (seeded R-MAT graph + ~N(0,1) features generated on the host by the generator's CPU twin)",
+        "config": {"workload": w["label"], "batches_per_step": per_step, "rng_mode": "wyrand_exact",
+                   "inputs_larger_than_l2": True, "implementation":
+                   "C restatement of the reference's Rust CPU sampler + gather (no Rust toolchain on this image)"},
+        "gather_gbs": gbs, "edges": r["edges"], "nodes": r["nodes"], "checksum": f"{r['checksum']:016x}",
+        "setup_s": round(t_setup, 1), "wall_s": round(wall, 3),
+        "cpu_baseline": {"value": value, "unit": "edges/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- #
+#  device arm                                                                  #
+# --------------------------------------------------------------------------- #
+def run_device(args, w):
+    import torch
+    import torch.distributed as dist
+
+    import aethergraph_b200 as ag
+    from aethergraph_b200 import _lib, synth
+    from aethergraph_b200.loader import NeighborLoader
+    from aethergraph_b200.sampler import _Buffers
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: aethergraph_b200 has no CPU path "
+                         "(use --impl reference for the CPU baseline)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    L = _lib.lib()
+
+    # ---- inputs, resident in HBM (CSR and features replicated per GPU) ------
+    t_setup = time.time()
+    g = synth.rmat_graph(w["nodes"], w["edges"], GRAPH_SEED, weight_sigma=1.0 if w["weighted"] else 0.0)
+    feats = synth.features(w["nodes"], w["dim"], w["dtype"], FEATURE_SEED)
+    torch.cuda.synchronize()
+    t_setup = time.time() - t_setup
+    cfg = ag.SamplingConfig(num_neighbors=w["fanout"], seed=SAMPLER_SEED, weighted=w["weighted"])
+    per_step, bs = BATCHES_PER_STEP, w["batch"]
+    n_batches = (args.warmup + args.steps) * per_step
+    # rank r handles global batches r, r + world, ... (weak scaling: every rank does K steps)
+    gidx = [rank + world * i for i in range(n_batches)]
+    seeds_host = [synth.seed_batch(w["nodes"], bs, SEEDS_SEED, b) for b in gidx]
+    seeds_dev = torch.from_numpy(np.concatenate(seeds_host).view(np.int32)).to(dev)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def sum_over_ranks(v: float) -> float:
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(t.item())
+
+    # ---- value: C ABI, inputs resident, recycled output buffers ------------
+    threads, depth = args.threads, args.depth
+    h = C.c_void_p()
+    ccfg = cfg._to_c(SAMPLER_SEED, bs)
+    _lib.check(L.ag_loader_create(g._h, feats._h, C.byref(ccfg), 1, depth, threads, 1, C.byref(h)))
+    mn, me = C.c_uint64(), C.c_uint64()
+    _lib.check(L.ag_loader_bounds(h, bs, C.byref(mn), C.byref(me)))
+    ring = [_Buffers(dev, mn.value, me.value, bs, True, w["dim"]) for _ in range(depth + threads + 2)]
+    R = len(ring)
+    batch = _lib.Batch()
+    stats0 = _lib.LoaderStats()
+    stats1 = _lib.LoaderStats()
+
+    def run_resident(first: int, count: int):
+        """Submit batches [first, first+count) with device seeds; returns (edges, nodes)."""
+        edges = nodes = 0
+        submitted = delivered = 0
+        base = seeds_dev.data_ptr()
+        while delivered < count:
+            while submitted < count and submitted - delivered < R:
+                i = first + submitted
+                _lib.check(L.ag_loader_submit(h, gidx[i], base + 4 * bs * i, bs, _lib.AG_MEM_DEVICE,
+                                              C.byref(ring[i % R].c), None))
+                submitted += 1
+            _lib.check(L.ag_loader_next(h, -1, C.byref(batch)))
+            edges += batch.counts.num_edges
+            nodes += batch.counts.num_nodes
+            delivered += 1
+        return edges, nodes
+
+    # NOTE: seeded loaders number batches by submission; to keep every rank's
+    # batch b on ag_batch_seed(seed, b) the loader is fed consecutive positions
+    # and the global batch index only picks the seed ids.
+    run_resident(0, args.warmup * per_step)
+    clocks = ClockSampler(local)
+    clocks.start()
+    barrier()
+    _lib.check(L.ag_loader_stats_get(h, C.byref(stats0)))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    wall0 = time.time()
+    e0.record()
+    edges, nodes = run_resident(args.warmup * per_step, args.steps * per_step)
+    e1.record()
+    barrier()
+    wall1 = time.time()
+    ms = max_over_ranks(e0.elapsed_time(e1))
+    _lib.check(L.ag_loader_stats_get(h, C.byref(stats1)))
+    clk = clocks.stop(wall0, wall1)
+    tot_edges, tot_nodes = sum_over_ranks(edges), sum_over_ranks(nodes)
+    value = tot_edges / (ms * 1e-3)
+    row_bytes = gather_bytes_per_row(w)
+    gather_gbs = tot_nodes * row_bytes / (ms * 1e-3) / 1e9
+    g_ms = stats1.gather_ms - stats0.gather_ms
+    s_ms = stats1.sample_ms - stats0.sample_ms
+    n_timed = args.steps * per_step
+    peak, peak_src = peaks()
+    achieved = nodes * row_bytes / (g_ms * 1e-3) / 1e9 if g_ms > 0 else None
+    traffic = None
+    tp = os.path.join(ROOT, "profiles", "gather_traffic.json")
+    if os.path.exists(tp):
+        try:
+            t = json.load(open(tp))
+            traffic = t["dram_bytes_per_row"][w["dtype"] + str(w["dim"])] * nodes / n_timed
+        except Exception:
+            traffic = None
+    roofline = {
+        "kernel": "k_gather_vec (feature-row gather + upcast)", "bound": "hbm",
+        "achieved": achieved, "peak": peak, "unit": "GB/s",
+        "frac": (achieved / peak) if achieved else None, "peak_source": peak_src,
+        "bytes_per_launch": nodes * row_bytes / n_timed, "ms_per_launch": g_ms / n_timed,
+        "launches": n_timed, "traffic": traffic,
+        "note": "per-launch time from CUDA events on the launching stream while the other "
+                "streams' sampling kernels run beside it",
+        "pipeline": {"algorithmic_gbs": (tot_nodes * row_bytes + sampling_bytes(tot_edges, tot_nodes, tot_nodes))
+                     / (ms * 1e-3) / 1e9,
+                     "frac_of_peak": ((tot_nodes * row_bytes + sampling_bytes(tot_edges, tot_nodes, tot_nodes))
+                                      / (ms * 1e-3) / 1e9) / (peak * world),
+                     "sample_ms_per_batch": s_ms / n_timed},
+    }
+    L.ag_loader_free(h)
+    del ring
+
+    # ---- e2e: public Python API, host seeds in, counts back -----------------
+    loader = NeighborLoader(g, cfg, prefetch_depth=depth, sampler_threads=threads, features=feats)
+    window = depth + threads
+
+    def run_e2e(first: int, count: int):
+        edges = submitted = delivered = 0
+        while delivered < count:
+            while submitted < count and submitted - delivered < window:
+                loader.submit(gidx[first + submitted], seeds_host[first + submitted])
+                submitted += 1
+            _, sg, x = loader.next_batch()
+            edges += sg.num_edges
+            delivered += 1
+        return edges
+
+    run_e2e(0, args.warmup * per_step)
+    barrier()
+    e0.record()
+    edges_e2e = run_e2e(args.warmup * per_step, args.steps * per_step)
+    e1.record()
+    barrier()
+    ms_e2e = max_over_ranks(e0.elapsed_time(e1))
+    e2e_value = sum_over_ranks(edges_e2e) / (ms_e2e * 1e-3)
+    loader.shutdown()
+    del loader
+
+    # ---- CPU baseline beside it (rank 0, one GPU only) ----------------------
+    cpu = None
+    parity = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cpu, parity = cpu_baseline(g, feats, w, cfg, seeds_host, gidx)
+
+    if rank == 0:
+        hops = len(w["fanout"])
+        line = {
+            "metric": METRIC, "value": value, "unit": "edges/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / max(args.steps, 1), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "u32 ids / " + w["dtype"] + "->f32",
+            "data": "synthetic (seeded R-MAT graph + ~N(0,1) features generated in HBM)",
+            "config": {"workload": w["label"], "batches_per_step": per_step, "rng_mode": "wyrand_exact",
+                       "sampler_threads": threads, "prefetch_depth": depth, "parallelism": f"dp{world}",
+                       "features": "replicated", "inputs_larger_than_l2": True},
+            "gather_gbs": gather_gbs, "edges_per_step": tot_edges / max(args.steps, 1),
+            "rows_per_step": tot_nodes / max(args.steps, 1), "setup_s": round(t_setup, 1),
+            "clocks": clk, "roofline": roofline, "cpu_baseline": cpu, "parity_full_scale": parity,
+            "e2e": {"value": e2e_value, "unit": "edges/s", "h2d_bytes_per_step": per_step * bs * 4,
+                    "d2h_bytes_per_step": per_step * C.sizeof(_lib.SampleCounts),
+                    "ms_per_step": ms_e2e / max(args.steps, 1),
+                    "note": "host seed arrays in, per-batch counts out; the batch stays in GPU memory"},
+            "gpu_launches": n_timed * (2 + (hops + 1) + hops + 1 + 1),
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def cpu_baseline(g, feats, w, cfg, seeds_host, gidx):
+    """Times the CPU restatement on a bounded sample of the same workload (graph and
+    features copied back from the GPU) and checks two full-size batches bit for bit."""
+    import torch
+
+    import aethergraph_b200 as ag
+    from aethergraph_b200 import _lib
+    from oracle import ago
+
+    ago.build()
+    if w["nodes"] * w["dim"] * (4 if w["dtype"] == "f32" else 2) + w["edges"] * 4 > 150e9:
+        return None, None
+    n = g.num_nodes
+    offsets, dst, weights = g.to_host()
+    payload = feats.payload_to_host()
+    threads = cpu_threads()
+    s = ago.Sampler(offsets, dst, w["fanout"], weights=weights, weighted=w["weighted"], seed=SAMPLER_SEED)
+    bs = w["batch"]
+    # bounded sample: grow until the timed run lasts a few seconds
+    nb = min(len(seeds_host), 2 * threads)
+    while True:
+        seeds = np.concatenate(seeds_host[:nb])
+        r = s.bench(payload, w["dim"], w["dtype"], seeds, bs, 0, threads)
+        if r["seconds"] >= 5.0 or nb >= len(seeds_host):
+            break
+        nb = min(len(seeds_host), max(nb + 1, int(nb * min(8.0, 7.0 / max(r["seconds"], 1e-3)))))
+    cpu = {"value": r["edges"] / r["seconds"], "unit": "edges/s", "cores": threads, "kind": "port",
+           "gather_gbs": r["nodes"] * gather_bytes_per_row(w) / r["seconds"] / 1e9,
+           "sample": f"{nb} batches of {bs} seeds of the same workload (graph and features copied back from "
+                     f"the GPU), {threads} threads, {r['seconds']:.2f} s"}
+    # full-size parity: batch positions 0 and 1, bit for bit
+    sampler = ag.ParallelBatchSampler(g, cfg, features=feats, streams=2)
+    ok = True
+    for pos, sg in enumerate(sampler.sample_batches(seeds_host[:2])):
+        s.reseed(ago.batch_seed(SAMPLER_SEED, pos))
+        want = s.sample(seeds_host[pos])
+        got = sg.raw_u32()
+        for k in ("nodes", "edge_src", "edge_dst", "edge_ids", "src_local", "dst_local", "seed_locals"):
+            ok = ok and np.array_equal(got[k], want[k])
+        xw = ago.gather(payload, n, w["dim"], w["dtype"], want["nodes"])
+        ok = ok and np.array_equal(sg.x.cpu().numpy().view(np.uint32), xw.view(np.uint32))
+    return cpu, bool(ok)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--workload", default=os.environ.get("AG_BENCH_WORKLOAD", "c2"), choices=sorted(WORKLOADS))
+    ap.add_argument("--threads", type=int, default=int(os.environ.get("AG_BENCH_THREADS", "6")),
+                    help="loader worker threads = batches in flight on the GPU")
+    ap.add_argument("--depth", type=int, default=4)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
+    w = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, w)
+    else:
+        run_device(args, w)
+
+
+if __name__ == "__main__":
+    main()

@@ -100,6 +100,8 @@ int32_t ag_graph_degrees(const ag_graph *g, const uint32_t *ids, uint64_t n, uin
  * weights_out != NULL) to host; *degree receives the full row length. */
 int32_t ag_graph_neighbors(const ag_graph *g, uint32_t node, uint32_t *out, float *weights_out,
                            uint64_t cap, uint64_t *degree);
+/* Copies the CSR back to host arrays sized num_nodes + 1 / num_edges (any may be NULL). */
+int32_t ag_graph_copy_to_host(const ag_graph *g, uint64_t *offsets, uint32_t *dst, float *weights);
 void ag_graph_free(ag_graph *g);
 
 /* ------------------------------------------------------------- features --
@@ -128,7 +130,11 @@ int32_t ag_features_adopt_device(void *payload_dev, uint64_t num_nodes, uint64_t
                                  int32_t dtype, int32_t device, ag_features **out);
 int32_t ag_features_info(const ag_features *f, uint64_t *num_nodes, uint64_t *dim,
                          int32_t *dtype, int32_t *device, uint64_t *row_begin);
+/* The vertex range [row_begin, row_begin + rows) this handle holds. */
+int32_t ag_features_shard(const ag_features *f, uint64_t *row_begin, uint64_t *rows);
 int32_t ag_features_device_ptr(const ag_features *f, const void **payload_dev);
+/* Copies the stored (encoded) rows held by this handle back to host memory. */
+int32_t ag_features_copy_to_host(const ag_features *f, void *payload);
 
 /* FeatureStore.get_batch on host ids (store.rs:691-769): range-checks every
  * id first (AG_ERR_VALUE "node N out of bounds"), gathers on the device and
@@ -199,6 +205,9 @@ typedef struct {
     uint64_t draws;          /* RNG draws consumed by this batch */
     uint32_t error;          /* device-side error bits, 0 = none */
     uint32_t reserved;
+    /* Device time of the sampling kernels and of the gather kernel for this
+     * batch, in milliseconds; filled only after ag_sampler_set_profiling(s, 1). */
+    float sample_ms, gather_ms;
 } ag_sample_counts;
 
 int32_t ag_sampler_create(const ag_graph *g, const ag_sampling_config *cfg, ag_sampler **out);
@@ -224,7 +233,84 @@ int32_t ag_sample(ag_sampler *s, const uint32_t *seeds, uint64_t n_seeds,
                   const ag_features *feats, int32_t want_int64, ag_subgraph_buffers *buf,
                   void *stream);
 int32_t ag_subgraph_release(ag_sampler *s, ag_subgraph_buffers *buf);
+/* When on, every batch records CUDA events around its sampling chain and its
+ * gather on the launching stream (ag_sample_counts.sample_ms / gather_ms). */
+int32_t ag_sampler_set_profiling(ag_sampler *s, int32_t on);
 void ag_sampler_free(ag_sampler *s);
+
+/* --------------------------------------------------------------- loader --
+ * Stands in for the prefetching NeighborLoader (_core.pyi:380-464;
+ * crates/aethergraph-core/src/loader/prefetch.rs:402-560 pipeline,
+ * :911-1073 workers).  `sampler_threads` host threads each own one sampler
+ * handle and one CUDA stream, so that many batches are in flight on the GPU.
+ *   - submit assigns a sequence number; the work queue holds 8 x prefetch_depth
+ *     items and submit blocks while it is full (prefetch.rs:457-477).
+ *   - With seeded = 1 batch number seq is sampled from
+ *     ag_batch_seed(cfg->seed, seq) and results are delivered in submission
+ *     order; with seeded = 0 each worker's stream simply continues and results
+ *     arrive as they finish (prefetch.rs:486-491, 926-930).
+ *   - ag_loader_next waits up to timeout_ms (the reference waits 30 s) and
+ *     returns AG_ERR_TIMEOUT, AG_ERR_SHUTDOWN after ag_loader_shutdown, or
+ *     AG_ERR_WORKER once a worker failed (prefetch.rs:479-523).
+ * Output buffers belong to the caller: pass them with the submission (device
+ * memory, sized with ag_loader_bounds) and get the same pointers back in the
+ * ag_batch.  With bufs == NULL the library allocates them and
+ * ag_loader_release_batch frees them.  `after_stream`, when not NULL, is a
+ * stream whose already-queued work must finish before the batch's kernels
+ * may write the buffers (the stream that last used recycled memory). */
+typedef struct {
+    int64_t batch_idx;
+    uint64_t seq;
+    ag_subgraph_buffers bufs;
+    ag_sample_counts counts;
+    int32_t owned;      /* 1 when bufs were allocated by the library */
+    int32_t reserved;
+} ag_batch;
+
+typedef struct {
+    uint64_t hits, misses, total;            /* prefetch.rs:853-899 */
+    uint64_t sample_time_ns, feature_load_time_ns;
+    uint64_t submitted, edges, nodes;        /* totals over delivered batches */
+    double gather_ms, sample_ms;             /* device time, when profiling is on */
+} ag_loader_stats;
+
+int32_t ag_loader_create(const ag_graph *g, const ag_features *f, const ag_sampling_config *cfg,
+                         int32_t seeded, uint32_t prefetch_depth, uint32_t sampler_threads,
+                         int32_t profiling, ag_loader **out);
+int32_t ag_loader_bounds(const ag_loader *l, uint64_t n_seeds, uint64_t *max_nodes,
+                         uint64_t *max_edges);
+int32_t ag_loader_submit(ag_loader *l, int64_t batch_idx, const uint32_t *seeds, uint64_t n_seeds,
+                         int32_t seeds_mem, const ag_subgraph_buffers *bufs, void *after_stream);
+int32_t ag_loader_next(ag_loader *l, int64_t timeout_ms, ag_batch *out);
+/* Non-blocking: AG_ERR_TIMEOUT when nothing is ready. */
+int32_t ag_loader_try_next(ag_loader *l, ag_batch *out);
+int32_t ag_loader_release_batch(ag_loader *l, ag_batch *batch);
+int32_t ag_loader_stats_get(const ag_loader *l, ag_loader_stats *stats);
+int32_t ag_loader_shutdown(ag_loader *l);
+void ag_loader_free(ag_loader *l);
+
+/* ------------------------------------------------------ synthetic inputs --
+ * Seeded generators that build test and benchmark inputs directly in HBM
+ * (no counterpart in the reference library; its benches generate synthetic
+ * graphs on the host: crates/aethergraph-core/benches/sampling_scale.rs:29-49).
+ * R-MAT over num_src x num_dst ids with quadrant probabilities a, b, c
+ * (d = 1 - a - b - c); rows sorted by (source, destination); duplicates and
+ * self-loops kept.  weight_sigma > 0 adds lognormal(0, sigma) f32 weights. */
+int32_t ag_synth_rmat_graph(uint64_t num_nodes, uint64_t num_edges, float a, float b, float c,
+                            uint64_t seed, float weight_sigma, int32_t device, ag_graph **out);
+int32_t ag_synth_rmat_csr(uint64_t num_src, uint64_t num_dst, uint64_t num_edges, float a, float b,
+                          float c, uint64_t seed, float weight_sigma, int32_t device,
+                          uint64_t **offsets_dev, uint32_t **dst_dev, float **weights_dev);
+/* Every source gets exactly `degree` destinations drawn uniformly. */
+int32_t ag_synth_fixed_degree_csr(uint64_t num_src, uint64_t num_dst, uint32_t degree,
+                                  uint64_t seed, int32_t device, uint64_t **offsets_dev,
+                                  uint32_t **dst_dev);
+int32_t ag_synth_free_device(void *ptr, int32_t device);
+/* Rows [row_begin, row_end) of a num_nodes x dim table of ~N(0,1) values
+ * (8-term Irwin-Hall), encoded as `dtype`. */
+int32_t ag_synth_features(uint64_t num_nodes, uint64_t dim, int32_t dtype, uint64_t seed,
+                          int32_t device, uint64_t row_begin, uint64_t row_end,
+                          ag_features **out);
 
 #ifdef __cplusplus
 }

@@ -158,8 +158,35 @@ def lib():
         L.ago_bench_run.argtypes = [C.POINTER(_Csr), C.POINTER(_Config), C.c_void_p, C.c_uint64,
                                     C.c_int, C.c_void_p, C.c_size_t, C.c_size_t, C.c_uint64,
                                     C.c_int, C.POINTER(_BenchResult)]
+        L.ago_synth_rmat_csr.restype = C.c_int
+        L.ago_synth_rmat_csr.argtypes = [C.c_uint64, C.c_uint64, C.c_uint64, C.c_float, C.c_float, C.c_float,
+                                         C.c_uint64, C.c_int, C.c_void_p, C.c_void_p]
+        L.ago_synth_features.restype = C.c_int
+        L.ago_synth_features.argtypes = [C.c_uint64, C.c_int, C.c_uint64, C.c_uint64, C.c_uint64, C.c_int,
+                                         C.c_void_p]
         _lib = L
     return _lib
+
+
+def synth_rmat_csr(num_src: int, num_dst: int, num_edges: int, seed: int, abc=(0.57, 0.19, 0.19),
+                   threads: int = 1):
+    """CPU twin of the library's R-MAT generator: (offsets u64, dst u32), rows sorted."""
+    offsets = np.empty(num_src + 1, dtype=np.uint64)
+    dst = np.empty(max(num_edges, 1), dtype=np.uint32)
+    rc = lib().ago_synth_rmat_csr(num_src, num_dst, num_edges, abc[0], abc[1], abc[2], seed & (2**64 - 1),
+                                  threads, offsets.ctypes.data, dst.ctypes.data)
+    if rc != 0:
+        raise RuntimeError(f"ago_synth_rmat_csr failed ({rc})")
+    return offsets, dst[:num_edges]
+
+
+def synth_features(num_nodes: int, dim: int, dtype: str, seed: int, row_range=None, threads: int = 1):
+    """CPU twin of the library's feature generator: encoded payload as a flat array."""
+    lo, hi = row_range if row_range is not None else (0, num_nodes)
+    tag = DTYPE_TAG[dtype]
+    out = np.empty((hi - lo) * dim, dtype=np.float32 if tag == F32 else np.uint16)
+    lib().ago_synth_features(dim, tag, seed & (2**64 - 1), lo, hi, threads, out.ctypes.data)
+    return out
 
 
 # ---------------------------------------------------------------- scalars --
