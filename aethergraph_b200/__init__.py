@@ -8,11 +8,13 @@ the reference's Python sampler / feature-store / loader surface.
 from ._lib import GraphLoadError, SamplingError
 from .features import FeatureStore, save_features
 from .graph import CsrGraph, Graph
+from .loader import NeighborLoader, PrefetchStats
 from .sampler import NeighborSampler, ParallelBatchSampler, SampledSubgraph, Sampler, SamplingConfig
 
 __version__ = "0.1.0"
 
 __all__ = [
-    "CsrGraph", "FeatureStore", "Graph", "GraphLoadError", "NeighborSampler", "ParallelBatchSampler",
+    "CsrGraph", "FeatureStore", "Graph", "GraphLoadError", "NeighborLoader", "NeighborSampler",
+    "ParallelBatchSampler", "PrefetchStats",
     "SampledSubgraph", "Sampler", "SamplingConfig", "SamplingError", "__version__", "save_features",
 ]
