@@ -112,8 +112,11 @@ SIGNATURES = {
     "ag_subgraph_release": (C.c_int32, [_P, C.POINTER(SubgraphBuffers)]),
     "ag_sampler_free": (None, [_P]),
     "ag_sampler_set_profiling": (C.c_int32, [_P, C.c_int32]),
+    "ag_sampler_create_group": (C.c_int32, [_P, C.POINTER(SamplingConfigC), C.c_uint32, _PP]),
+    "ag_sample_group_into": (C.c_int32, [_P, C.c_uint32, _P, _P, C.c_int32, _P, _P, C.POINTER(SubgraphBuffers), _P]),
+    "ag_sample_group_wait": (C.c_int32, [_P, C.POINTER(SampleCounts), _I32P]),
     "ag_loader_create": (C.c_int32, [_P, _P, C.POINTER(SamplingConfigC), C.c_int32, C.c_uint32, C.c_uint32,
-                                     C.c_int32, _PP]),
+                                     C.c_uint32, C.c_int32, _PP]),
     "ag_loader_bounds": (C.c_int32, [_P, C.c_uint64, _U64P, _U64P]),
     "ag_loader_submit": (C.c_int32, [_P, C.c_int64, _P, C.c_uint64, C.c_int32, C.POINTER(SubgraphBuffers), _P]),
     "ag_loader_next": (C.c_int32, [_P, C.c_int64, C.POINTER(Batch)]),

@@ -16,6 +16,8 @@
 // evict-first.  The grid is a whole number of waves of the 148 SMs and strides
 // over the rows, so the row count may live on the device (the sampler's node
 // count) without a host round trip.
+#include <algorithm>
+
 #include "common.cuh"
 #include "internal.h"
 
@@ -74,8 +76,10 @@ __device__ __forceinline__ uint64_t load_id(const void *ids, int ids64, uint64_t
 // LPR lanes share a row; vecs = row_bytes / 16.
 template <int DTYPE, int LPR>
 __global__ void __launch_bounds__(kThreads)
-k_gather_vec(GatherArgs a) {
+k_gather_vec(GatherArgs a, const GatherArgs *__restrict__ group) {
     constexpr int kRowsPerBlock = kThreads / LPR;
+    if (group) a = group[blockIdx.y];  // one batch of a group per grid row
+    if (!a.payload) return;
     const uint64_t n = a.n_dev ? min((uint64_t)*a.n_dev, a.n) : a.n;
     const int lane = threadIdx.x % LPR;
     const int sub = threadIdx.x / LPR;
@@ -118,7 +122,9 @@ k_gather_vec(GatherArgs a) {
 // Element path for rows that are not a whole number of 16-byte vectors.
 template <int DTYPE>
 __global__ void __launch_bounds__(kThreads)
-k_gather_elem(GatherArgs a) {
+k_gather_elem(GatherArgs a, const GatherArgs *__restrict__ group) {
+    if (group) a = group[blockIdx.y];
+    if (!a.payload) return;
     const uint64_t n = a.n_dev ? min((uint64_t)*a.n_dev, a.n) : a.n;
     const uint64_t total = n * a.dim;
     for (uint64_t g = (uint64_t)blockIdx.x * kThreads + threadIdx.x; g < total;
@@ -141,12 +147,12 @@ k_gather_elem(GatherArgs a) {
 }
 
 template <int DTYPE>
-cudaError_t launch_vec(const GatherArgs &a, int blocks, cudaStream_t st) {
-    const uint32_t vecs = a.row_bytes >> 4;
-    if (vecs <= 4) k_gather_vec<DTYPE, 4><<<blocks, kThreads, 0, st>>>(a);
-    else if (vecs <= 8) k_gather_vec<DTYPE, 8><<<blocks, kThreads, 0, st>>>(a);
-    else if (vecs <= 16) k_gather_vec<DTYPE, 16><<<blocks, kThreads, 0, st>>>(a);
-    else k_gather_vec<DTYPE, 32><<<blocks, kThreads, 0, st>>>(a);
+cudaError_t launch_vec(const GatherArgs &a, const GatherArgs *group, uint32_t row_bytes, dim3 grid, cudaStream_t st) {
+    const uint32_t vecs = row_bytes >> 4;
+    if (vecs <= 4) k_gather_vec<DTYPE, 4><<<grid, kThreads, 0, st>>>(a, group);
+    else if (vecs <= 8) k_gather_vec<DTYPE, 8><<<grid, kThreads, 0, st>>>(a, group);
+    else if (vecs <= 16) k_gather_vec<DTYPE, 16><<<grid, kThreads, 0, st>>>(a, group);
+    else k_gather_vec<DTYPE, 32><<<grid, kThreads, 0, st>>>(a, group);
     return cudaGetLastError();
 }
 
@@ -212,20 +218,52 @@ cudaError_t launch_gather(const GatherArgs &a, int dtype, cudaStream_t st) {
     const bool vec_ok = (a.row_bytes % 16 == 0) && (((uintptr_t)a.payload) % 16 == 0) &&
                         (((uintptr_t)a.out) % 16 == 0);
     if (vec_ok) {
-        const int blocks = gather_grid_blocks(a.n, a.row_bytes);
+        const dim3 grid(gather_grid_blocks(a.n, a.row_bytes), 1);
         switch (dtype) {
-            case AG_F32: return launch_vec<AG_F32>(a, blocks, st);
-            case AG_F16: return launch_vec<AG_F16>(a, blocks, st);
-            default: return launch_vec<AG_BF16>(a, blocks, st);
+            case AG_F32: return launch_vec<AG_F32>(a, nullptr, a.row_bytes, grid, st);
+            case AG_F16: return launch_vec<AG_F16>(a, nullptr, a.row_bytes, grid, st);
+            default: return launch_vec<AG_BF16>(a, nullptr, a.row_bytes, grid, st);
         }
     }
     const uint64_t total = a.n * a.dim;
     uint64_t blocks = (total + kThreads - 1) / kThreads;
     if (blocks > (uint64_t)kSMs * 8) blocks = (uint64_t)kSMs * 8;
     switch (dtype) {
-        case AG_F32: k_gather_elem<AG_F32><<<(int)blocks, kThreads, 0, st>>>(a); break;
-        case AG_F16: k_gather_elem<AG_F16><<<(int)blocks, kThreads, 0, st>>>(a); break;
-        default: k_gather_elem<AG_BF16><<<(int)blocks, kThreads, 0, st>>>(a); break;
+        case AG_F32: k_gather_elem<AG_F32><<<(int)blocks, kThreads, 0, st>>>(a, nullptr); break;
+        case AG_F16: k_gather_elem<AG_F16><<<(int)blocks, kThreads, 0, st>>>(a, nullptr); break;
+        default: k_gather_elem<AG_BF16><<<(int)blocks, kThreads, 0, st>>>(a, nullptr); break;
+    }
+    return cudaGetLastError();
+}
+
+// One launch for a group of batches: grid row b gathers the batch described by
+// group_dev[b].  The output buffers come from cudaMalloc / the torch allocator
+// (256- / 512-byte aligned) and the payload base is checked by the caller's
+// store, so only the row size decides between the vector and the element path.
+cudaError_t launch_gather_group(const GatherArgs *group_dev, uint32_t n_batches, uint32_t row_bytes,
+                                uint32_t dim, uint64_t n_bound, bool aligned, int dtype, cudaStream_t st) {
+    if (n_batches == 0 || n_bound == 0) return cudaSuccess;
+    GatherArgs none{};
+    if (row_bytes % 16 == 0 && aligned) {
+        // the whole group shares whole waves of the 148 SMs
+        int per = gather_grid_blocks(n_bound, row_bytes);
+        const int cap = std::max(1, (kSMs * 8 + (int)n_batches - 1) / (int)n_batches);
+        per = std::min(per, cap);
+        const dim3 grid(per, n_batches);
+        switch (dtype) {
+            case AG_F32: return launch_vec<AG_F32>(none, group_dev, row_bytes, grid, st);
+            case AG_F16: return launch_vec<AG_F16>(none, group_dev, row_bytes, grid, st);
+            default: return launch_vec<AG_BF16>(none, group_dev, row_bytes, grid, st);
+        }
+    }
+    const uint64_t total = n_bound * dim;
+    uint64_t blocks = (total + kThreads - 1) / kThreads;
+    blocks = std::max<uint64_t>(1, std::min<uint64_t>(blocks, (uint64_t)kSMs * 8 / n_batches + 1));
+    const dim3 grid((uint32_t)blocks, n_batches);
+    switch (dtype) {
+        case AG_F32: k_gather_elem<AG_F32><<<grid, kThreads, 0, st>>>(none, group_dev); break;
+        case AG_F16: k_gather_elem<AG_F16><<<grid, kThreads, 0, st>>>(none, group_dev); break;
+        default: k_gather_elem<AG_BF16><<<grid, kThreads, 0, st>>>(none, group_dev); break;
     }
     return cudaGetLastError();
 }

@@ -45,6 +45,8 @@ struct GatherArgs {
 };
 
 cudaError_t launch_gather(const GatherArgs &a, int dtype, cudaStream_t st);
+cudaError_t launch_gather_group(const GatherArgs *group_dev, uint32_t n_batches, uint32_t row_bytes,
+                                uint32_t dim, uint64_t n_bound, bool aligned, int dtype, cudaStream_t st);
 cudaError_t launch_encode(const float *src, void *dst, uint64_t count, int dtype, cudaStream_t st);
 int gather_grid_blocks(uint64_t n, uint32_t row_bytes);
 

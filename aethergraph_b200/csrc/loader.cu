@@ -50,7 +50,7 @@ struct ag_loader {
     const ag_features *f = nullptr;
     ag_sampling_config cfg{};
     bool seeded = true, profiling = false;
-    uint32_t depth = 2, threads = 1;
+    uint32_t depth = 2, threads = 1, group = 1;
     int device = 0;
 
     std::mutex m;
@@ -98,41 +98,88 @@ void worker_main(ag_loader *l, uint32_t idx) {
     cudaSetDevice(l->device);
     ag_sampler *s = l->samplers[idx];
     cudaStream_t st = l->streams[idx];
+    const uint32_t G = l->group;
+    std::vector<Work> ws;
+    std::vector<const uint32_t *> seed_ptrs(G);
+    std::vector<uint64_t> n_seeds(G), batch_seeds(G);
+    std::vector<ag_subgraph_buffers> bufs(G);
+    std::vector<ag_sample_counts> counts(G);
+    std::vector<int32_t> statuses(G);
     for (;;) {
-        Work w;
+        ws.clear();
         {
             std::unique_lock<std::mutex> lk(l->m);
             l->cv_work.wait(lk, [&] { return l->stop || !l->queue.empty(); });
             if (l->stop) return;
-            w = std::move(l->queue.front());
-            l->queue.pop_front();
-            l->cv_space.notify_one();
+            // Take a fair share of what is queued, up to one group: the batches of
+            // a group ride one launch chain, so a deep queue costs few launches,
+            // while a shallow one is still spread over the workers.  A group is
+            // homogeneous in where its seeds live.
+            const size_t share = std::max<size_t>(1, (l->queue.size() + l->threads - 1) / l->threads);
+            const size_t take = std::min<size_t>(G, share);
+            const bool dev_seeds = l->queue.front().seeds_dev != nullptr;
+            while (ws.size() < take && !l->queue.empty() && (l->queue.front().seeds_dev != nullptr) == dev_seeds) {
+                ws.push_back(std::move(l->queue.front()));
+                l->queue.pop_front();
+            }
+            l->cv_space.notify_all();
         }
-        Done d;
-        d.batch.batch_idx = w.batch_idx; d.batch.seq = w.seq; d.batch.bufs = w.bufs; d.batch.owned = w.owned ? 1 : 0;
+        const uint32_t nb = (uint32_t)ws.size();
         const auto t0 = Clock::now();
         int32_t rc = AG_OK;
-        if (w.after) {
-            if (cudaStreamWaitEvent(st, w.after, 0) != cudaSuccess) rc = fail(AG_ERR_CUDA, "cudaStreamWaitEvent failed");
-            cudaEventDestroy(w.after);
+        for (uint32_t b = 0; b < nb; ++b) {
+            Work &w = ws[b];
+            if (w.after) {
+                if (cudaStreamWaitEvent(st, w.after, 0) != cudaSuccess) rc = fail(AG_ERR_CUDA, "cudaStreamWaitEvent failed");
+                cudaEventDestroy(w.after);
+                w.after = nullptr;
+            }
+            seed_ptrs[b] = w.seeds_dev ? w.seeds_dev : w.seeds.data();
+            n_seeds[b] = w.n_seeds;
+            bufs[b] = w.bufs;
+            // Seeded loaders restart the stream per batch from its submission number
+            // (prefetch.rs:926-930), so any pool size or grouping yields the same results.
+            batch_seeds[b] = ag_batch_seed(l->cfg.seed, w.seq);
+            statuses[b] = AG_OK;
         }
-        // Seeded loaders restart the stream per batch from its submission number
-        // (prefetch.rs:926-930), so any pool size yields the same results.
-        if (rc == AG_OK && l->seeded) rc = ag_sampler_reseed(s, ag_batch_seed(l->cfg.seed, w.seq));
-        if (rc == AG_OK)
-            rc = ag_sample_into(s, w.seeds_dev ? w.seeds_dev : w.seeds.data(), w.n_seeds,
-                                w.seeds_dev ? AG_MEM_DEVICE : AG_MEM_HOST, l->f, &d.batch.bufs, st);
-        if (rc == AG_OK) rc = ag_sample_wait(s, &d.batch.counts);
-        if (rc != AG_OK) { d.status = rc; d.error = ag_last_error(); }
+        // Unseeded: a worker's own stream continues across its batches, which needs
+        // the batches one at a time.
+        std::string err;
+        if (rc == AG_OK && (l->seeded || nb == 1)) {
+            rc = ag_sample_group_into(s, nb, seed_ptrs.data(), n_seeds.data(),
+                                      ws[0].seeds_dev ? AG_MEM_DEVICE : AG_MEM_HOST,
+                                      l->seeded ? batch_seeds.data() : nullptr, l->f, bufs.data(), st);
+            if (rc == AG_OK) rc = ag_sample_group_wait(s, counts.data(), statuses.data());
+            if (rc != AG_OK) err = ag_last_error();
+        } else if (rc == AG_OK) {
+            for (uint32_t b = 0; b < nb; ++b) {
+                int32_t r1 = ag_sample_group_into(s, 1, &seed_ptrs[b], &n_seeds[b],
+                                                  ws[b].seeds_dev ? AG_MEM_DEVICE : AG_MEM_HOST, nullptr, l->f,
+                                                  &bufs[b], st);
+                if (r1 == AG_OK) r1 = ag_sample_group_wait(s, &counts[b], &statuses[b]);
+                if (r1 != AG_OK) { statuses[b] = r1; rc = r1; err = ag_last_error(); }
+            }
+        } else {
+            err = ag_last_error();
+        }
         const uint64_t ns = (uint64_t)std::chrono::duration_cast<std::chrono::nanoseconds>(Clock::now() - t0).count();
-        {
+        for (uint32_t b = 0; b < nb; ++b) {
+            Work &w = ws[b];
+            Done d;
+            d.batch.batch_idx = w.batch_idx; d.batch.seq = w.seq; d.batch.bufs = w.bufs; d.batch.owned = w.owned ? 1 : 0;
+            d.batch.counts = counts[b];
+            // A failure of the whole launch chain fails every batch of the group; a
+            // per-batch error (bad seed, small buffer) fails only that batch.
+            const bool chain_failed = rc != AG_OK && statuses[b] == AG_OK &&
+                                      !(rc == AG_ERR_SAMPLING || rc == AG_ERR_VALUE || rc == AG_ERR_LOAD);
+            if (statuses[b] != AG_OK || chain_failed) { d.status = statuses[b] != AG_OK ? statuses[b] : rc; d.error = err; }
             std::unique_lock<std::mutex> lk(l->m);
             // Results channel holds `depth` batches: wait for room (prefetch.rs:1135-1143),
             // except for the batch the consumer is waiting on — holding it back could
             // stall an ordered loader whose later batches filled the channel first.
             l->cv_room.wait(lk, [&] { return l->stop || l->in_ready < l->depth || w.seq == l->next_deliver; });
-            if (l->stop) { if (w.owned) free_owned(&d.batch.bufs); return; }
-            l->stats.sample_time_ns += ns;
+            if (l->stop) { for (uint32_t r = b; r < nb; ++r) if (ws[r].owned) free_owned(&ws[r].bufs); return; }
+            if (b == 0) l->stats.sample_time_ns += ns;
             if (d.status != AG_OK && l->fault.empty() && d.status != AG_ERR_SAMPLING && d.status != AG_ERR_VALUE)
                 l->fault = d.error;  // a broken worker poisons the loader; a bad batch does not
             l->ready.emplace(w.seq, std::move(d));
@@ -182,8 +229,10 @@ bool has_deliverable(ag_loader *l) {
 
 extern "C" int32_t ag_loader_create(const ag_graph *g, const ag_features *f, const ag_sampling_config *cfg,
                                     int32_t seeded, uint32_t prefetch_depth, uint32_t sampler_threads,
-                                    int32_t profiling, ag_loader **out) {
+                                    uint32_t group, int32_t profiling, ag_loader **out) {
     if (!g || !cfg || !out) return fail(AG_ERR_VALUE, "ag_loader_create: null argument");
+    if (group == 0) group = 1;
+    if (group > 256) return fail(AG_ERR_VALUE, "group must be <= 256");
     if (prefetch_depth == 0) return fail(AG_ERR_VALUE, "prefetch_depth must be >= 1");
     if (sampler_threads == 0) return fail(AG_ERR_VALUE, "sampler_threads must be >= 1");
     if (sampler_threads > 64) return fail(AG_ERR_VALUE, "sampler_threads must be <= 64");
@@ -193,13 +242,14 @@ extern "C" int32_t ag_loader_create(const ag_graph *g, const ag_features *f, con
     ag_loader *l = new ag_loader();
     l->g = g; l->f = f; l->cfg = *cfg; l->seeded = seeded != 0; l->profiling = profiling != 0;
     l->depth = prefetch_depth; l->threads = sampler_threads; l->device = g->device;
+    l->group = seeded ? group : 1;
     int32_t st = AG_OK;
     for (uint32_t i = 0; i < sampler_threads && st == AG_OK; ++i) {
         ag_sampler *s = nullptr;
         ag_sampling_config c = *cfg;
         // Unseeded workers must not replay one another (the reference seeds each from entropy).
         if (!l->seeded) c.seed = ag_batch_seed(cfg->seed, 0x5eed0000ull + i);
-        st = ag_sampler_create(g, &c, &s);
+        st = ag_sampler_create_group(g, &c, l->group, &s);
         if (st != AG_OK) break;
         l->samplers.push_back(s);
         if (profiling) st = ag_sampler_set_profiling(s, 1);

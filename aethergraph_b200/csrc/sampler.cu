@@ -3,7 +3,7 @@
 // Computes exactly what the reference's NeighborSampler::sample computes
 // (crates/aethergraph-core/src/loader/sampler.rs:845-961 with the hop loop at
 // :754-842 and the per-node dispatch at :1178-1235), but as a short chain of
-// data-parallel kernels per batch instead of one sequential loop:
+// data-parallel kernels instead of one sequential loop:
 //
 //   insert   every seed (or every edge of a hop) is inserted into a hash table
 //            keyed by vertex id with atomicMin(position): the smallest position
@@ -26,6 +26,11 @@
 // state is an additive counter, so draw d is a pure function of (seed, d); the
 // scan of per-vertex draw counts gives every vertex the index of its first
 // draw, and the parallel picks are bit-identical to the sequential ones.
+//
+// Batches are independent, so one launch chain serves a whole GROUP of them:
+// every kernel's grid has the batch as its y dimension and each batch brings
+// its own parameter block, dedup table, scan descriptors and output buffers.
+// A group of 16 batches of 1024 seeds costs the same dozen launches as one.
 #include <string.h>
 
 #include <algorithm>
@@ -45,6 +50,8 @@ constexpr int kLargeK = 1024;        // largest fanout the k > 32 path keeps in 
 
 enum : int { kModeUniform = 0, kModeReplace = 1, kModeWeighted = 2 };
 
+// Parameter block of one batch; a group's blocks sit in one device array that
+// the kernels index with blockIdx.y.
 struct SampleParams {
     const uint64_t *offsets;
     const uint32_t *dst;
@@ -53,20 +60,26 @@ struct SampleParams {
     DedupTable table;
     BatchState *state;
     TileDesc *tiles;
-    uint32_t epoch;
+    uint32_t epoch_base;  // stage s scans under epoch_base + s
+    uint32_t n_seeds;
+    const uint32_t *seeds;
     uint64_t seed;
     int rng_mode;
     int mode;
+    int reset_pos;
     // outputs
     uint32_t *nodes;
     uint32_t *edge_src, *edge_dst, *src_local, *dst_local, *seed_locals;
     uint64_t *edge_ids;
     uint64_t cap_nodes, cap_edges;
+    int64_t *n_id, *edge_index_local, *e_id, *seed_index;
+    ag_sample_counts *counts;
     // scratch
     uint32_t *slot_of_seed;
     uint32_t *slot_of_edge;
-    FrontierEntry *frontier_in, *frontier_out;
+    FrontierEntry *frontier[2];
     uint64_t frontier_cap;
+    uint32_t num_hops;
 };
 
 // Row bounds with the reference's guard (graph/csr.rs:318-335): an inverted
@@ -93,11 +106,38 @@ __device__ __forceinline__ void row_demand(int mode, uint64_t deg, uint32_t k, u
     draws = (mode == kModeWeighted) ? deg : (uint64_t)k;
 }
 
+// ------------------------------------------------------------------ begin --
+// Empties the table slots the handle's previous batch touched (so the table is
+// never memset between batches) and resets the per-batch bookkeeping.
+__global__ void k_begin(const SampleParams *__restrict__ pa) {
+    const SampleParams &p = pa[blockIdx.y];
+    BatchState *bs = p.state;
+    const uint32_t pe = bs->prev_edges, ps = bs->prev_seeds;
+    const uint32_t tid = blockIdx.x * blockDim.x + threadIdx.x, stride = gridDim.x * blockDim.x;
+    for (uint32_t e = tid; e < pe; e += stride) {
+        const uint32_t slot = p.slot_of_edge[e];
+        if (slot != 0xFFFFFFFFu) p.table.slots[slot] = kSlotEmpty;
+    }
+    for (uint32_t i = tid; i < ps; i += stride) {
+        const uint32_t slot = p.slot_of_seed[i];
+        if (slot != 0xFFFFFFFFu) p.table.slots[slot] = kSlotEmpty;
+    }
+    if (tid == 0) {
+        if (p.reset_pos) bs->stream_pos = 0;
+        StageInfo s0{};
+        s0.draws = bs->stream_pos;
+        bs->stage[0] = s0;
+        bs->error = 0;
+        bs->ticket = 0;
+    }
+}
+
 // ------------------------------------------------------------ seed insert --
-__global__ void k_insert_seeds(SampleParams p, const uint32_t *seeds, uint32_t n_seeds) {
+__global__ void k_insert_seeds(const SampleParams *__restrict__ pa) {
+    const SampleParams &p = pa[blockIdx.y];
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n_seeds) return;
-    const uint32_t id = seeds[i];
+    if (i >= p.n_seeds) return;
+    const uint32_t id = p.seeds[i];
     if ((uint64_t)id >= p.num_nodes) {
         atomicOr(&p.state->error, kErrBadSeed);
         p.slot_of_seed[i] = 0xFFFFFFFFu;
@@ -109,13 +149,14 @@ __global__ void k_insert_seeds(SampleParams p, const uint32_t *seeds, uint32_t n
 // ----------------------------------------------------------------- assign --
 // Items of stage s in position order: the seeds (s == 0) or the edges of hop
 // s - 1.  next_k is the fanout of the hop the new vertices will be expanded
-// at, or 0 after the last hop.
+// at; has_next is 0 after the last hop.
 __global__ void __launch_bounds__(kAssignThreads)
-k_assign(SampleParams p, uint32_t stage, uint32_t n_seeds, uint32_t next_k, int has_next) {
+k_assign(const SampleParams *__restrict__ pa, uint32_t stage, uint32_t next_k, int has_next) {
     __shared__ uint32_t s_tile;
     __shared__ ScanVal s_warp[kAssignThreads / 32];
     __shared__ ScanVal s_prefix;
 
+    const SampleParams &p = pa[blockIdx.y];
     BatchState *bs = p.state;
     if (threadIdx.x == 0) {
         s_tile = atomicAdd(&bs->ticket, 1u);
@@ -124,7 +165,7 @@ k_assign(SampleParams p, uint32_t stage, uint32_t n_seeds, uint32_t next_k, int 
     __syncthreads();
     const uint32_t tile = s_tile;
     const StageInfo si = bs->stage[stage];
-    const uint32_t count = (stage == 0) ? n_seeds : si.hop_edges;
+    const uint32_t count = (stage == 0) ? p.n_seeds : si.hop_edges;
     const uint32_t n_tiles = max(1u, (count + kAssignThreads - 1) / kAssignThreads);
     if (tile >= n_tiles) return;
 
@@ -162,7 +203,7 @@ k_assign(SampleParams p, uint32_t stage, uint32_t n_seeds, uint32_t next_k, int 
                                             __shfl_sync(0xffffffffu, wi.take, 31),
                                             __shfl_sync(0xffffffffu, wi.draws, 31)};
         if (lane < kAssignThreads / 32) s_warp[lane] = ScanVal{wi.flags - w.flags, wi.take - w.take, wi.draws - w.draws};
-        const ScanVal prefix = lookback_exclusive(p.tiles, tile, p.epoch, block_total, lane, &bs->error);
+        const ScanVal prefix = lookback_exclusive(p.tiles, tile, p.epoch_base + stage, block_total, lane, &bs->error);
         if (lane == 0) {
             s_prefix = prefix;
             if (tile == n_tiles - 1) {
@@ -202,7 +243,7 @@ k_assign(SampleParams p, uint32_t stage, uint32_t n_seeds, uint32_t next_k, int 
         fe.local = local;
         fe.deg = (uint32_t)deg;
         fe.ebase = excl.take;
-        p.frontier_out[rank] = fe;
+        p.frontier[stage & 1][rank] = fe;
     }
 }
 
@@ -234,15 +275,19 @@ __device__ __forceinline__ void emit_edge(const SampleParams &p, const StageInfo
 }
 
 // Fanout <= G <= 32: G lanes per frontier vertex, lane t owns edge slot t.
+// The frontier of hop h was written by stage h into frontier[h & 1].
 template <int G>
 __global__ void __launch_bounds__(kPickThreads)
-k_pick_small(SampleParams p, uint32_t stage, uint32_t hop, uint32_t k) {
+k_pick_small(const SampleParams *__restrict__ pa, uint32_t hop, uint32_t k) {
+    const SampleParams &p = pa[blockIdx.y];
+    const uint32_t stage = hop + 1;
     const StageInfo si = p.state->stage[stage];
     const uint32_t node = (blockIdx.x * kPickThreads + threadIdx.x) / G;
+    if ((node & ~(32u / G - 1u)) >= si.frontier_n) return;  // the whole warp is past the frontier
     const uint32_t t = threadIdx.x % G;
     const bool active = node < si.frontier_n;
     FrontierEntry fe{};
-    if (active) fe = p.frontier_in[node];
+    if (active) fe = p.frontier[hop & 1][node];
     const uint32_t deg = fe.deg;
     const bool sampled = active && p.mode != kModeReplace && deg > k;  // Floyd row
     uint32_t pick = t;                                                  // take-all: row order
@@ -259,11 +304,13 @@ k_pick_small(SampleParams p, uint32_t stage, uint32_t hop, uint32_t k) {
     // resolve slot s against the finished slots below it, one ballot per s.
     const uint32_t gshift = (threadIdx.x & 31) & ~(G - 1);
     const uint32_t gmask = (G == 32) ? 0xffffffffu : ((1u << G) - 1u);
-    for (uint32_t s = 1; s < k; ++s) {
-        const uint32_t js = __shfl_sync(0xffffffffu, pick, s, G);
-        const bool hit = sampled && t < s && pick == js;
-        const uint32_t m = (__ballot_sync(0xffffffffu, hit) >> gshift) & gmask;
-        if (sampled && t == s && m) pick = ip;
+    if (__any_sync(0xffffffffu, sampled)) {
+        for (uint32_t s = 1; s < k; ++s) {
+            const uint32_t js = __shfl_sync(0xffffffffu, pick, s, G);
+            const bool hit = sampled && t < s && pick == js;
+            const uint32_t m = (__ballot_sync(0xffffffffu, hit) >> gshift) & gmask;
+            if (sampled && t == s && m) pick = ip;
+        }
     }
     if (!active) return;
     uint32_t take;
@@ -275,13 +322,14 @@ k_pick_small(SampleParams p, uint32_t stage, uint32_t hop, uint32_t k) {
 // Fanout > 32: one warp per frontier vertex; finished picks live in shared
 // memory so later slots can be checked against all earlier ones.
 __global__ void __launch_bounds__(128)
-k_pick_large(SampleParams p, uint32_t stage, uint32_t hop, uint32_t k) {
+k_pick_large(const SampleParams *__restrict__ pa, uint32_t hop, uint32_t k) {
     __shared__ uint32_t s_picks[4][kLargeK];
-    const StageInfo si = p.state->stage[stage];
+    const SampleParams &p = pa[blockIdx.y];
+    const StageInfo si = p.state->stage[hop + 1];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t node = blockIdx.x * 4 + warp;
     if (node >= si.frontier_n) return;
-    const FrontierEntry fe = p.frontier_in[node];
+    const FrontierEntry fe = p.frontier[hop & 1][node];
     const uint32_t deg = fe.deg;
     uint32_t take;
     uint64_t draws;
@@ -327,12 +375,13 @@ __device__ __forceinline__ bool key_less(double ka, uint32_t pa, double kb, uint
 }
 
 __global__ void __launch_bounds__(kPickThreads)
-k_pick_weighted(SampleParams p, uint32_t stage, uint32_t hop, uint32_t k) {
-    const StageInfo si = p.state->stage[stage];
+k_pick_weighted(const SampleParams *__restrict__ pa, uint32_t hop, uint32_t k) {
+    const SampleParams &p = pa[blockIdx.y];
+    const StageInfo si = p.state->stage[hop + 1];
     const int lane = threadIdx.x & 31;
     const uint32_t node = (blockIdx.x * kPickThreads + threadIdx.x) >> 5;
     if (node >= si.frontier_n) return;
-    const FrontierEntry fe = p.frontier_in[node];
+    const FrontierEntry fe = p.frontier[hop & 1][node];
     const uint32_t deg = fe.deg;
     if (deg == 0 || k == 0) return;
     if (k >= deg) {
@@ -380,15 +429,10 @@ k_pick_weighted(SampleParams p, uint32_t stage, uint32_t hop, uint32_t k) {
 }
 
 // --------------------------------------------------------------- finalize --
-struct FinalizeArgs {
-    int64_t *n_id, *edge_index_local, *e_id, *seed_index;
-    ag_sample_counts *counts;
-    uint32_t n_seeds, num_hops, final_stage;
-};
-
-__global__ void k_finalize(SampleParams p, FinalizeArgs f) {
+__global__ void k_finalize(const SampleParams *__restrict__ pa) {
+    const SampleParams &p = pa[blockIdx.y];
     BatchState *bs = p.state;
-    const StageInfo fin = bs->stage[f.final_stage];
+    const StageInfo fin = bs->stage[p.num_hops + 1];
     const uint32_t n_nodes = min((uint64_t)fin.n_nodes, p.cap_nodes);
     const uint32_t n_edges = min((uint64_t)fin.n_edges, p.cap_edges);
     const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -398,45 +442,37 @@ __global__ void k_finalize(SampleParams p, FinalizeArgs f) {
         const uint32_t dl = (slot == 0xFFFFFFFFu) ? 0xFFFFFFFFu
                           : (uint32_t)__ldcg((const unsigned long long *)&p.table.slots[slot]);
         p.dst_local[e] = dl;
-        if (f.edge_index_local) {
-            f.edge_index_local[e] = (int64_t)dl;                       // row 0: sampled neighbor
-            f.edge_index_local[(uint64_t)n_edges + e] = (int64_t)p.src_local[e];  // row 1: expanded node
+        if (p.edge_index_local) {
+            p.edge_index_local[e] = (int64_t)dl;                                   // row 0: sampled neighbor
+            p.edge_index_local[(uint64_t)n_edges + e] = (int64_t)p.src_local[e];   // row 1: expanded node
         }
-        if (f.e_id && p.edge_ids) f.e_id[e] = (int64_t)p.edge_ids[e];
+        if (p.e_id && p.edge_ids) p.e_id[e] = (int64_t)p.edge_ids[e];
     }
-    for (uint64_t i = tid; i < f.n_seeds; i += stride) {
+    for (uint64_t i = tid; i < p.n_seeds; i += stride) {
         const uint32_t slot = p.slot_of_seed[i];
         const uint32_t sl = (slot == 0xFFFFFFFFu) ? 0xFFFFFFFFu
                           : (uint32_t)__ldcg((const unsigned long long *)&p.table.slots[slot]);
         p.seed_locals[i] = sl;
-        if (f.seed_index) f.seed_index[i] = (int64_t)sl;
+        if (p.seed_index) p.seed_index[i] = (int64_t)sl;
     }
-    if (f.n_id)
-        for (uint64_t i = tid; i < n_nodes; i += stride) f.n_id[i] = (int64_t)p.nodes[i];
+    if (p.n_id)
+        for (uint64_t i = tid; i < n_nodes; i += stride) p.n_id[i] = (int64_t)p.nodes[i];
     if (tid == 0) {
         ag_sample_counts c{};
         c.num_nodes = n_nodes;
         c.num_edges = n_edges;
-        c.num_seeds = f.n_seeds;
-        c.num_hops = f.num_hops;
-        for (uint32_t s = 0; s <= f.num_hops; ++s) c.nodes_per_hop[s] = bs->nodes_per_stage[s];
-        for (uint32_t h = 0; h < f.num_hops; ++h) c.edges_per_hop[h] = bs->stage[h + 1].hop_edges;
+        c.num_seeds = p.n_seeds;
+        c.num_hops = p.num_hops;
+        for (uint32_t s = 0; s <= p.num_hops; ++s) c.nodes_per_hop[s] = bs->nodes_per_stage[s];
+        for (uint32_t h = 0; h < p.num_hops; ++h) c.edges_per_hop[h] = bs->stage[h + 1].hop_edges;
         c.draws = fin.draws - bs->stage[0].draws;
         c.error = bs->error;
         if ((uint64_t)fin.n_nodes > p.cap_nodes || (uint64_t)fin.n_edges > p.cap_edges) c.error |= kErrCapacity;
-        *f.counts = c;
+        *p.counts = c;
         bs->stream_pos = fin.draws;  // a bare sampler keeps consuming the same stream
+        bs->prev_edges = n_edges;    // what the next batch's k_begin has to wipe from the table
+        bs->prev_seeds = p.n_seeds;
     }
-}
-
-// Stage 0 bookkeeping at the head of a batch.
-__global__ void k_begin(BatchState *bs, int reset_pos) {
-    if (reset_pos) bs->stream_pos = 0;
-    StageInfo s0{};
-    s0.draws = bs->stream_pos;
-    bs->stage[0] = s0;
-    bs->error = 0;
-    bs->ticket = 0;
 }
 
 uint64_t next_pow2(uint64_t v) {
@@ -458,24 +494,29 @@ struct ag_sampler {
     uint64_t seed = 0;
     bool reset_pos = true;
     uint32_t epoch = 0;
-    // sizing
+    uint32_t group = 1;  // batches one launch chain can carry
+    // sizing (per batch)
     uint64_t cap_seeds = 0, max_nodes = 0, max_edges = 0, max_frontier = 0, max_hop_edges = 0;
-    // scratch (device)
+    uint64_t table_cap = 0, n_tiles = 0;
+    // scratch (device), each `group` times the per-batch size
     uint64_t *table = nullptr;
-    uint64_t table_cap = 0;
     FrontierEntry *frontier[2] = {nullptr, nullptr};
     uint32_t *slot_of_seed = nullptr, *slot_of_edge = nullptr;
     TileDesc *tiles = nullptr;
-    uint64_t n_tiles = 0;
     BatchState *state = nullptr;
     uint32_t *seeds_dev = nullptr;
     ag_sample_counts *counts_dev = nullptr;
+    SampleParams *params_dev = nullptr;
+    GatherArgs *gather_dev = nullptr;
     // pinned host
     uint32_t *seeds_pinned = nullptr;
     ag_sample_counts *counts_host = nullptr;
+    SampleParams *params_host = nullptr;
+    GatherArgs *gather_host = nullptr;
     cudaEvent_t done = nullptr;
-    bool in_flight = false;
-    // optional per-batch device timing
+    bool in_flight = false, dirty = true;
+    uint32_t in_flight_n = 0;
+    // optional per-group device timing
     bool profile = false, gathered = false;
     cudaEvent_t ev[3] = {nullptr, nullptr, nullptr};
     // buffers handed out by ag_sample (library-allocated variant)
@@ -512,36 +553,40 @@ void free_scratch(ag_sampler *s) {
     s->seeds_dev = nullptr; s->seeds_pinned = nullptr;
 }
 
+// Scratch for `group` batches of up to n_seeds seeds each.
 int32_t ensure_scratch(ag_sampler *s, uint64_t n_seeds) {
     if (n_seeds <= s->cap_seeds && s->table) return AG_OK;
     if (s->in_flight) { AG_CUDA(cudaEventSynchronize(s->done)); }
     free_scratch(s);
-    const uint64_t cap = std::max<uint64_t>(n_seeds, 1);
+    const uint64_t cap = std::max<uint64_t>(n_seeds, 1), G = s->group;
     compute_bounds(s, cap, &s->max_nodes, &s->max_edges, &s->max_frontier, &s->max_hop_edges);
     if (s->max_nodes >= 0x7FFFFFFFull || s->max_hop_edges >= 0x7FFFFFFFull || s->max_edges >= 0xFFFFFFFFull)
         return fail(AG_ERR_VALUE, "batch too large: %llu seeds with this fanout can emit %llu edges "
                     "(limit 2^31 per hop)", (unsigned long long)n_seeds, (unsigned long long)s->max_edges);
     s->table_cap = std::max<uint64_t>(1024, next_pow2(2 * s->max_nodes));
-    AG_CUDA(cudaMalloc(&s->table, s->table_cap * 8));
+    AG_CUDA(cudaMalloc(&s->table, G * s->table_cap * 8));
     const uint64_t fcap = std::max<uint64_t>(s->max_frontier, 1);
-    AG_CUDA(cudaMalloc(&s->frontier[0], fcap * sizeof(FrontierEntry)));
-    AG_CUDA(cudaMalloc(&s->frontier[1], fcap * sizeof(FrontierEntry)));
-    AG_CUDA(cudaMalloc(&s->slot_of_seed, cap * 4));
-    AG_CUDA(cudaMalloc(&s->slot_of_edge, std::max<uint64_t>(s->max_edges, 1) * 4));
+    AG_CUDA(cudaMalloc(&s->frontier[0], G * fcap * sizeof(FrontierEntry)));
+    AG_CUDA(cudaMalloc(&s->frontier[1], G * fcap * sizeof(FrontierEntry)));
+    AG_CUDA(cudaMalloc(&s->slot_of_seed, G * cap * 4));
+    AG_CUDA(cudaMalloc(&s->slot_of_edge, G * std::max<uint64_t>(s->max_edges, 1) * 4));
     s->n_tiles = std::max<uint64_t>(std::max(cap, s->max_hop_edges) / kAssignThreads + 2, 2);
-    AG_CUDA(cudaMalloc(&s->tiles, s->n_tiles * sizeof(TileDesc)));
-    AG_CUDA(cudaMemset(s->tiles, 0, s->n_tiles * sizeof(TileDesc)));
-    AG_CUDA(cudaMalloc(&s->seeds_dev, cap * 4));
-    AG_CUDA(cudaHostAlloc(&s->seeds_pinned, cap * 4, cudaHostAllocDefault));
+    AG_CUDA(cudaMalloc(&s->tiles, G * s->n_tiles * sizeof(TileDesc)));
+    AG_CUDA(cudaMemset(s->tiles, 0, G * s->n_tiles * sizeof(TileDesc)));
+    AG_CUDA(cudaMalloc(&s->seeds_dev, G * cap * 4));
+    AG_CUDA(cudaHostAlloc(&s->seeds_pinned, G * cap * 4, cudaHostAllocDefault));
     s->cap_seeds = cap;
     s->epoch = 0;
+    s->dirty = true;
     return AG_OK;
 }
 
 }  // namespace
 
-extern "C" int32_t ag_sampler_create(const ag_graph *g, const ag_sampling_config *cfg, ag_sampler **out) {
+extern "C" int32_t ag_sampler_create_group(const ag_graph *g, const ag_sampling_config *cfg, uint32_t group,
+                                           ag_sampler **out) {
     if (!g || !cfg || !out) return fail(AG_ERR_VALUE, "ag_sampler_create: null argument");
+    if (group == 0 || group > 256) return fail(AG_ERR_VALUE, "group size must be between 1 and 256 (got %u)", group);
     if (cfg->num_hops == 0 || cfg->num_hops > AG_MAX_HOPS)
         return fail(AG_ERR_VALUE, "num_neighbors must list between 1 and %d hops (got %u)", AG_MAX_HOPS, cfg->num_hops);
     // SamplerConfigError::WeightsMissing (sampler.rs:331-337)
@@ -563,14 +608,19 @@ extern "C" int32_t ag_sampler_create(const ag_graph *g, const ag_sampling_config
     s->g = g;
     s->cfg = *cfg;
     s->device = g->device;
+    s->group = group;
     s->mode = cfg->weighted ? kModeWeighted : (cfg->replace ? kModeReplace : kModeUniform);
     s->seed = cfg->seed;
     int32_t st = AG_OK;
     do {
-        if (cudaMalloc(&s->state, sizeof(BatchState)) != cudaSuccess ||
-            cudaMemset(s->state, 0, sizeof(BatchState)) != cudaSuccess ||
-            cudaMalloc(&s->counts_dev, sizeof(ag_sample_counts)) != cudaSuccess ||
-            cudaHostAlloc(&s->counts_host, sizeof(ag_sample_counts), cudaHostAllocDefault) != cudaSuccess ||
+        if (cudaMalloc(&s->state, group * sizeof(BatchState)) != cudaSuccess ||
+            cudaMemset(s->state, 0, group * sizeof(BatchState)) != cudaSuccess ||
+            cudaMalloc(&s->counts_dev, group * sizeof(ag_sample_counts)) != cudaSuccess ||
+            cudaMalloc(&s->params_dev, group * sizeof(SampleParams)) != cudaSuccess ||
+            cudaMalloc(&s->gather_dev, group * sizeof(GatherArgs)) != cudaSuccess ||
+            cudaHostAlloc(&s->counts_host, group * sizeof(ag_sample_counts), cudaHostAllocDefault) != cudaSuccess ||
+            cudaHostAlloc(&s->params_host, group * sizeof(SampleParams), cudaHostAllocDefault) != cudaSuccess ||
+            cudaHostAlloc(&s->gather_host, group * sizeof(GatherArgs), cudaHostAllocDefault) != cudaSuccess ||
             cudaEventCreateWithFlags(&s->done, cudaEventDisableTiming) != cudaSuccess) {
             st = fail(AG_ERR_CUDA, "sampler allocation failed: %s", cudaGetErrorString(cudaGetLastError()));
             break;
@@ -582,14 +632,20 @@ extern "C" int32_t ag_sampler_create(const ag_graph *g, const ag_sampling_config
     return AG_OK;
 }
 
+extern "C" int32_t ag_sampler_create(const ag_graph *g, const ag_sampling_config *cfg, ag_sampler **out) {
+    return ag_sampler_create_group(g, cfg, 1, out);
+}
+
 extern "C" void ag_sampler_free(ag_sampler *s) {
     if (!s) return;
     DeviceGuard guard(s->device);
     if (s->in_flight && s->done) cudaEventSynchronize(s->done);
     free_scratch(s);
     for (void *p : s->owned) cudaFree(p);
-    cudaFree(s->state); cudaFree(s->counts_dev);
+    cudaFree(s->state); cudaFree(s->counts_dev); cudaFree(s->params_dev); cudaFree(s->gather_dev);
     if (s->counts_host) cudaFreeHost(s->counts_host);
+    if (s->params_host) cudaFreeHost(s->params_host);
+    if (s->gather_host) cudaFreeHost(s->gather_host);
     if (s->done) cudaEventDestroy(s->done);
     for (auto &e : s->ev) if (e) cudaEventDestroy(e);
     delete s;
@@ -618,154 +674,226 @@ extern "C" int32_t ag_sampler_bounds(const ag_sampler *s, uint64_t n_seeds, uint
     return AG_OK;
 }
 
-extern "C" int32_t ag_sample_into(ag_sampler *s, const uint32_t *seeds, uint64_t n_seeds, int32_t seeds_mem,
-                                  const ag_features *feats, ag_subgraph_buffers *buf, void *stream) {
-    if (!s || !buf || (!seeds && n_seeds)) return fail(AG_ERR_VALUE, "ag_sample_into: null argument");
-    if (!buf->nodes || !buf->edge_dst || !buf->src_local || !buf->dst_local || !buf->seed_locals)
-        return fail(AG_ERR_VALUE, "ag_sample_into: nodes, edge_dst, src_local, dst_local and seed_locals are required");
-    if (buf->cap_seeds < n_seeds) return fail(AG_ERR_VALUE, "seed_locals capacity %llu < %llu seeds",
-                                              (unsigned long long)buf->cap_seeds, (unsigned long long)n_seeds);
-    if (feats && buf->x && feats->device != s->device)
-        return fail(AG_ERR_VALUE, "feature store lives on device %d, sampler on %d", feats->device, s->device);
-    if (n_seeds >= 0x7FFFFFFFull) return fail(AG_ERR_VALUE, "too many seeds");
+// One launch chain for `n_batches` independent batches.  batch b uses
+// seeds[b] / n_seeds[b] / bufs[b] and, when batch_seeds != NULL, restarts its
+// RNG stream at draw 0 of batch_seeds[b]; with batch_seeds == NULL the handle's
+// own stream continues (only meaningful for a single batch).
+extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const uint32_t *const *seeds,
+                                        const uint64_t *n_seeds, int32_t seeds_mem, const uint64_t *batch_seeds,
+                                        const ag_features *feats, ag_subgraph_buffers *bufs, void *stream) {
+    if (!s || !bufs || !seeds || !n_seeds) return fail(AG_ERR_VALUE, "ag_sample_group_into: null argument");
+    if (n_batches == 0 || n_batches > s->group)
+        return fail(AG_ERR_VALUE, "group of %u batches does not fit a sampler created for %u", n_batches, s->group);
     const ag_graph *g = s->g;
-    // Seeds::new (sampler.rs:230-239): name the first id at or past num_nodes.
-    if (seeds_mem == AG_MEM_HOST) {
-        for (uint64_t i = 0; i < n_seeds; ++i)
-            if ((uint64_t)seeds[i] >= g->num_nodes)
-                return fail(AG_ERR_SAMPLING, "seed node %u (position %llu) is out of range for %llu nodes",
-                            seeds[i], (unsigned long long)i, (unsigned long long)g->num_nodes);
+    uint64_t max_n = 0;
+    bool want_x = false;
+    for (uint32_t b = 0; b < n_batches; ++b) {
+        const ag_subgraph_buffers &B = bufs[b];
+        if (!seeds[b] && n_seeds[b]) return fail(AG_ERR_VALUE, "ag_sample_group_into: null seeds");
+        if (!B.nodes || !B.edge_dst || !B.src_local || !B.dst_local || !B.seed_locals)
+            return fail(AG_ERR_VALUE, "nodes, edge_dst, src_local, dst_local and seed_locals buffers are required");
+        if (B.cap_seeds < n_seeds[b]) return fail(AG_ERR_VALUE, "seed_locals capacity %llu < %llu seeds",
+                                                  (unsigned long long)B.cap_seeds, (unsigned long long)n_seeds[b]);
+        if (n_seeds[b] >= 0x7FFFFFFFull) return fail(AG_ERR_VALUE, "too many seeds");
+        max_n = std::max(max_n, n_seeds[b]);
+        want_x = want_x || (feats && B.x);
+        // Seeds::new (sampler.rs:230-239): name the first id at or past num_nodes.
+        if (seeds_mem == AG_MEM_HOST)
+            for (uint64_t i = 0; i < n_seeds[b]; ++i)
+                if ((uint64_t)seeds[b][i] >= g->num_nodes)
+                    return fail(AG_ERR_SAMPLING, "seed node %u (position %llu) is out of range for %llu nodes",
+                                seeds[b][i], (unsigned long long)i, (unsigned long long)g->num_nodes);
     }
+    if (feats && want_x && feats->device != s->device)
+        return fail(AG_ERR_VALUE, "feature store lives on device %d, sampler on %d", feats->device, s->device);
     DeviceGuard guard(s->device);
     if (!guard.ok) return AG_ERR_CUDA;
     cudaStream_t st = (cudaStream_t)stream;
     if (s->in_flight) { AG_CUDA(cudaEventSynchronize(s->done)); s->in_flight = false; }
-    AG_TRY(ensure_scratch(s, n_seeds));
-
-    const uint32_t n = (uint32_t)n_seeds;
-    const uint32_t *seeds_dev = seeds;
-    if (seeds_mem == AG_MEM_HOST && n) {
-        memcpy(s->seeds_pinned, seeds, (size_t)n * 4);
-        AG_CUDA(cudaMemcpyAsync(s->seeds_dev, s->seeds_pinned, (size_t)n * 4, cudaMemcpyHostToDevice, st));
-        seeds_dev = s->seeds_dev;
-    }
-
-    // Size the table for this batch (cleared per batch; it stays L2-resident).
-    uint64_t b_nodes, b_edges, b_front, b_hop;
-    compute_bounds(s, n, &b_nodes, &b_edges, &b_front, &b_hop);
-    const uint64_t tcap = std::min(s->table_cap, std::max<uint64_t>(1024, next_pow2(2 * b_nodes)));
-    uint32_t log2cap = 0;
-    while ((1ull << log2cap) < tcap) ++log2cap;
+    AG_TRY(ensure_scratch(s, max_n));
     if (s->profile) AG_CUDA(cudaEventRecord(s->ev[0], st));
-    AG_CUDA(cudaMemsetAsync(s->table, 0xFF, tcap * 8, st));
-
-    SampleParams p{};
-    p.offsets = g->offsets; p.dst = g->dst; p.weights = g->weights;
-    p.num_nodes = g->num_nodes; p.num_edges = g->num_edges;
-    p.table = DedupTable{s->table, (uint32_t)(tcap - 1), 32u - log2cap};
-    p.state = s->state; p.tiles = s->tiles;
-    p.seed = s->seed; p.rng_mode = s->cfg.rng_mode; p.mode = s->mode;
-    p.nodes = buf->nodes; p.edge_src = buf->edge_src; p.edge_dst = buf->edge_dst;
-    p.src_local = buf->src_local; p.dst_local = buf->dst_local; p.seed_locals = buf->seed_locals;
-    p.edge_ids = s->cfg.track_edge_ids ? buf->edge_ids : nullptr;
-    p.cap_nodes = buf->cap_nodes; p.cap_edges = buf->cap_edges;
-    p.slot_of_seed = s->slot_of_seed; p.slot_of_edge = s->slot_of_edge;
-    p.frontier_cap = std::max<uint64_t>(s->max_frontier, 1);
-
-    k_begin<<<1, 1, 0, st>>>(s->state, s->reset_pos ? 1 : 0);
-    s->reset_pos = false;
-    if (n) k_insert_seeds<<<(n + 255) / 256, 256, 0, st>>>(p, seeds_dev, n);
-
+    if (s->dirty) {
+        // First use (or after a failed batch): the whole table starts empty.  From
+        // here on each batch wipes exactly the slots its predecessor touched.
+        AG_CUDA(cudaMemsetAsync(s->table, 0xFF, (uint64_t)s->group * s->table_cap * 8, st));
+        AG_CUDA(cudaMemsetAsync(s->state, 0, s->group * sizeof(BatchState), st));
+        s->dirty = false;
+        s->reset_pos = true;
+    }
     const uint32_t H = s->cfg.num_hops;
-    // stage 0: seeds -> frontier[0]
-    p.epoch = ++s->epoch;
-    p.frontier_in = nullptr; p.frontier_out = s->frontier[0];
-    k_assign<<<std::max(1u, (n + kAssignThreads - 1) / kAssignThreads), kAssignThreads, 0, st>>>(
-        p, 0, n, s->cfg.fanout[0], 1);
+    if (s->epoch + (H + 2) > 0x3FFFFF00u) {  // the epoch lives in 30 bits of the tile status
+        AG_CUDA(cudaMemsetAsync(s->tiles, 0, (uint64_t)s->group * s->n_tiles * sizeof(TileDesc), st));
+        s->epoch = 0;
+    }
+    uint32_t log2cap = 0;
+    while ((1ull << log2cap) < s->table_cap) ++log2cap;
+    const uint64_t fcap = std::max<uint64_t>(s->max_frontier, 1), ecap = std::max<uint64_t>(s->max_edges, 1);
 
-    uint64_t f_bound = std::min<uint64_t>(n, g->num_nodes);
+    uint64_t b_nodes = 0, b_edges = 0;
+    for (uint32_t b = 0; b < n_batches; ++b) {
+        const ag_subgraph_buffers &B = bufs[b];
+        const uint32_t n = (uint32_t)n_seeds[b];
+        SampleParams p{};
+        p.offsets = g->offsets; p.dst = g->dst; p.weights = g->weights;
+        p.num_nodes = g->num_nodes; p.num_edges = g->num_edges;
+        p.table = DedupTable{s->table + (uint64_t)b * s->table_cap, (uint32_t)(s->table_cap - 1), 32u - log2cap};
+        p.state = s->state + b;
+        p.tiles = s->tiles + (uint64_t)b * s->n_tiles;
+        p.epoch_base = s->epoch + 1;
+        p.n_seeds = n;
+        if (seeds_mem == AG_MEM_HOST) {
+            if (n) memcpy(s->seeds_pinned + (uint64_t)b * s->cap_seeds, seeds[b], (size_t)n * 4);
+            p.seeds = s->seeds_dev + (uint64_t)b * s->cap_seeds;
+        } else {
+            p.seeds = seeds[b];
+        }
+        p.seed = batch_seeds ? batch_seeds[b] : s->seed;
+        p.rng_mode = s->cfg.rng_mode; p.mode = s->mode;
+        p.reset_pos = (batch_seeds || s->reset_pos) ? 1 : 0;
+        p.nodes = B.nodes; p.edge_src = B.edge_src; p.edge_dst = B.edge_dst;
+        p.src_local = B.src_local; p.dst_local = B.dst_local; p.seed_locals = B.seed_locals;
+        p.edge_ids = s->cfg.track_edge_ids ? B.edge_ids : nullptr;
+        p.cap_nodes = B.cap_nodes; p.cap_edges = B.cap_edges;
+        p.n_id = B.n_id; p.edge_index_local = B.edge_index_local; p.e_id = B.e_id; p.seed_index = B.seed_index;
+        p.counts = s->counts_dev + b;
+        p.slot_of_seed = s->slot_of_seed + (uint64_t)b * s->cap_seeds;
+        p.slot_of_edge = s->slot_of_edge + (uint64_t)b * ecap;
+        p.frontier[0] = s->frontier[0] + (uint64_t)b * fcap;
+        p.frontier[1] = s->frontier[1] + (uint64_t)b * fcap;
+        p.frontier_cap = fcap;
+        p.num_hops = H;
+        s->params_host[b] = p;
+        uint64_t bn, be;
+        compute_bounds(s, n, &bn, &be, nullptr, nullptr);
+        b_nodes = std::max(b_nodes, bn); b_edges = std::max(b_edges, be);
+        if (want_x) {
+            GatherArgs ga{};
+            if (feats && B.x) {
+                ga.payload = feats->payload; ga.row_begin = feats->row_begin; ga.rows = feats->rows;
+                ga.row_bytes = (uint32_t)(feats->dim * elem_size(feats->dtype)); ga.dim = (uint32_t)feats->dim;
+                ga.ids = B.nodes; ga.ids64 = 0;
+                ga.n = std::min<uint64_t>(bn, B.cap_nodes);
+                ga.n_dev = &s->counts_dev[b].num_nodes;
+                ga.out = B.x; ga.err = feats->err;
+            }
+            s->gather_host[b] = ga;
+        }
+    }
+    s->reset_pos = false;
+    s->epoch += H + 2;
+    if (seeds_mem == AG_MEM_HOST)
+        AG_CUDA(cudaMemcpyAsync(s->seeds_dev, s->seeds_pinned, (uint64_t)n_batches * s->cap_seeds * 4, cudaMemcpyHostToDevice, st));
+    AG_CUDA(cudaMemcpyAsync(s->params_dev, s->params_host, n_batches * sizeof(SampleParams), cudaMemcpyHostToDevice, st));
+
+    const SampleParams *pa = s->params_dev;
+    const uint32_t nmax = (uint32_t)max_n;
+    {
+        // enough blocks to wipe a typical batch's slots in one pass
+        const uint32_t bx = (uint32_t)std::min<uint64_t>(std::max<uint64_t>((b_edges + nmax) / 1024, 1), 64);
+        k_begin<<<dim3(bx, n_batches), 256, 0, st>>>(pa);
+    }
+    if (nmax) k_insert_seeds<<<dim3((nmax + 255) / 256, n_batches), 256, 0, st>>>(pa);
+    // stage 0: seeds -> frontier[0]
+    k_assign<<<dim3(std::max(1u, (nmax + kAssignThreads - 1) / kAssignThreads), n_batches), kAssignThreads, 0, st>>>(
+        pa, 0, s->cfg.fanout[0], 1);
+
+    uint64_t f_bound = std::min<uint64_t>(nmax, g->num_nodes);
     for (uint32_t h = 0; h < H; ++h) {
         const uint32_t k = s->cfg.fanout[h];
         const uint64_t e_bound = f_bound * k;
-        p.frontier_in = s->frontier[h & 1];
-        p.frontier_out = s->frontier[(h + 1) & 1];
         if (f_bound && k) {
             if (s->mode == kModeWeighted) {
                 const uint32_t blocks = (uint32_t)((f_bound * 32 + kPickThreads - 1) / kPickThreads);
-                k_pick_weighted<<<blocks, kPickThreads, 0, st>>>(p, h + 1, h, k);
+                k_pick_weighted<<<dim3(blocks, n_batches), kPickThreads, 0, st>>>(pa, h, k);
             } else if (k > 32) {
-                k_pick_large<<<(uint32_t)((f_bound + 3) / 4), 128, 0, st>>>(p, h + 1, h, k);
+                k_pick_large<<<dim3((uint32_t)((f_bound + 3) / 4), n_batches), 128, 0, st>>>(pa, h, k);
             } else {
                 const uint32_t G = k <= 4 ? 4 : k <= 8 ? 8 : k <= 16 ? 16 : 32;
-                const uint32_t blocks = (uint32_t)((f_bound * G + kPickThreads - 1) / kPickThreads);
+                const dim3 grid((uint32_t)((f_bound * G + kPickThreads - 1) / kPickThreads), n_batches);
                 switch (G) {
-                    case 4: k_pick_small<4><<<blocks, kPickThreads, 0, st>>>(p, h + 1, h, k); break;
-                    case 8: k_pick_small<8><<<blocks, kPickThreads, 0, st>>>(p, h + 1, h, k); break;
-                    case 16: k_pick_small<16><<<blocks, kPickThreads, 0, st>>>(p, h + 1, h, k); break;
-                    default: k_pick_small<32><<<blocks, kPickThreads, 0, st>>>(p, h + 1, h, k); break;
+                    case 4: k_pick_small<4><<<grid, kPickThreads, 0, st>>>(pa, h, k); break;
+                    case 8: k_pick_small<8><<<grid, kPickThreads, 0, st>>>(pa, h, k); break;
+                    case 16: k_pick_small<16><<<grid, kPickThreads, 0, st>>>(pa, h, k); break;
+                    default: k_pick_small<32><<<grid, kPickThreads, 0, st>>>(pa, h, k); break;
                 }
             }
         }
-        p.epoch = ++s->epoch;
         const bool has_next = h + 1 < H;
-        k_assign<<<(uint32_t)std::max<uint64_t>(1, (e_bound + kAssignThreads - 1) / kAssignThreads),
-                   kAssignThreads, 0, st>>>(p, h + 1, n, has_next ? s->cfg.fanout[h + 1] : 0, has_next ? 1 : 0);
+        k_assign<<<dim3((uint32_t)std::max<uint64_t>(1, (e_bound + kAssignThreads - 1) / kAssignThreads), n_batches),
+                   kAssignThreads, 0, st>>>(pa, h + 1, has_next ? s->cfg.fanout[h + 1] : 0, has_next ? 1 : 0);
         f_bound = std::min<uint64_t>(e_bound, g->num_nodes);
     }
-    if (s->epoch > 0x3FFFFF00u) {  // epoch lives in 30 bits of the tile status
-        AG_CUDA(cudaMemsetAsync(s->tiles, 0, s->n_tiles * sizeof(TileDesc), st));
-        s->epoch = 0;
+    {
+        const uint64_t work = std::max<uint64_t>(std::max(b_edges, b_nodes), std::max<uint64_t>(nmax, 1));
+        const uint32_t fx = (uint32_t)std::min<uint64_t>((work + 255) / 256, std::max<uint64_t>((uint64_t)kSMs * 8 / n_batches, 1));
+        k_finalize<<<dim3(fx, n_batches), 256, 0, st>>>(pa);
     }
-
-    FinalizeArgs f{};
-    f.n_id = buf->n_id; f.edge_index_local = buf->edge_index_local; f.e_id = buf->e_id;
-    f.seed_index = buf->seed_index; f.counts = s->counts_dev;
-    f.n_seeds = n; f.num_hops = H; f.final_stage = H + 1;
-    const uint64_t work = std::max<uint64_t>(std::max(b_edges, b_nodes), std::max<uint64_t>(n, 1));
-    const uint32_t fblocks = (uint32_t)std::min<uint64_t>((work + 255) / 256, (uint64_t)kSMs * 8);
-    k_finalize<<<fblocks, 256, 0, st>>>(p, f);
     AG_CUDA(cudaGetLastError());
     if (s->profile) AG_CUDA(cudaEventRecord(s->ev[1], st));
     s->gathered = false;
-
-    if (feats && buf->x) {
-        GatherArgs ga{};
-        ga.payload = feats->payload; ga.row_begin = feats->row_begin; ga.rows = feats->rows;
-        ga.row_bytes = (uint32_t)(feats->dim * elem_size(feats->dtype)); ga.dim = (uint32_t)feats->dim;
-        ga.ids = buf->nodes; ga.ids64 = 0;
-        ga.n = std::min<uint64_t>(b_nodes, buf->cap_nodes);
-        ga.n_dev = &s->counts_dev->num_nodes;
-        ga.out = buf->x; ga.err = feats->err;
-        AG_CUDA(launch_gather(ga, feats->dtype, st));
+    if (want_x) {
+        AG_CUDA(cudaMemcpyAsync(s->gather_dev, s->gather_host, n_batches * sizeof(GatherArgs), cudaMemcpyHostToDevice, st));
+        bool aligned = ((uintptr_t)feats->payload % 16) == 0;
+        for (uint32_t b = 0; b < n_batches; ++b) aligned = aligned && ((uintptr_t)bufs[b].x % 16) == 0;
+        AG_CUDA(launch_gather_group(s->gather_dev, n_batches, (uint32_t)(feats->dim * elem_size(feats->dtype)),
+                                    (uint32_t)feats->dim, b_nodes, aligned, feats->dtype, st));
         if (s->profile) AG_CUDA(cudaEventRecord(s->ev[2], st));
         s->gathered = true;
     }
-    AG_CUDA(cudaMemcpyAsync(s->counts_host, s->counts_dev, sizeof(ag_sample_counts), cudaMemcpyDeviceToHost, st));
+    AG_CUDA(cudaMemcpyAsync(s->counts_host, s->counts_dev, n_batches * sizeof(ag_sample_counts), cudaMemcpyDeviceToHost, st));
     AG_CUDA(cudaEventRecord(s->done, st));
     s->in_flight = true;
+    s->in_flight_n = n_batches;
     return AG_OK;
 }
 
-extern "C" int32_t ag_sample_wait(ag_sampler *s, ag_sample_counts *counts) {
+// Waits for the group queued last; counts[b] receives batch b's counts.  Returns
+// the first batch error (the other batches' counts are still valid).
+extern "C" int32_t ag_sample_group_wait(ag_sampler *s, ag_sample_counts *counts, int32_t *statuses) {
     if (!s) return fail(AG_ERR_VALUE, "ag_sample_wait: null sampler");
     if (!s->in_flight) return fail(AG_ERR_VALUE, "ag_sample_wait: no batch in flight");
     DeviceGuard guard(s->device);
     if (!guard.ok) return AG_ERR_CUDA;
-    AG_CUDA(cudaEventSynchronize(s->done));
+    const cudaError_t e = cudaEventSynchronize(s->done);
     s->in_flight = false;
-    ag_sample_counts c = *s->counts_host;
-    c.sample_ms = c.gather_ms = 0.f;
-    if (s->profile) {
-        cudaEventElapsedTime(&c.sample_ms, s->ev[0], s->ev[1]);
-        if (s->gathered) cudaEventElapsedTime(&c.gather_ms, s->ev[1], s->ev[2]);
+    if (e != cudaSuccess) {
+        s->dirty = true;
+        return fail(AG_ERR_CUDA, "sampling kernels failed: %s", cudaGetErrorString(e));
     }
-    if (counts) *counts = c;
-    if (c.error & kErrBadSeed) return fail(AG_ERR_SAMPLING, "a seed node is out of range for %llu nodes",
-                                           (unsigned long long)s->g->num_nodes);
-    if (c.error & kErrCapacity) return fail(AG_ERR_VALUE, "output buffers too small for the sampled subgraph");
-    if (c.error & kErrBadDst) return fail(AG_ERR_LOAD, "graph holds a destination outside [0, num_nodes); load it with full validation");
-    if (c.error) return fail(AG_ERR_WORKER, "sampler kernels reported error bits 0x%x", c.error);
-    return AG_OK;
+    float sample_ms = 0.f, gather_ms = 0.f;
+    if (s->profile) {
+        cudaEventElapsedTime(&sample_ms, s->ev[0], s->ev[1]);
+        if (s->gathered) cudaEventElapsedTime(&gather_ms, s->ev[1], s->ev[2]);
+    }
+    int32_t first = AG_OK;
+    for (uint32_t b = 0; b < s->in_flight_n; ++b) {
+        ag_sample_counts c = s->counts_host[b];
+        c.sample_ms = sample_ms / s->in_flight_n;
+        c.gather_ms = gather_ms / s->in_flight_n;
+        if (counts) counts[b] = c;
+        int32_t st = AG_OK;
+        if (c.error & kErrBadSeed) st = fail(AG_ERR_SAMPLING, "a seed node is out of range for %llu nodes", (unsigned long long)s->g->num_nodes);
+        else if (c.error & kErrCapacity) st = fail(AG_ERR_VALUE, "output buffers too small for the sampled subgraph");
+        else if (c.error & kErrBadDst) st = fail(AG_ERR_LOAD, "graph holds a destination outside [0, num_nodes); load it with full validation");
+        else if (c.error) st = fail(AG_ERR_WORKER, "sampler kernels reported error bits 0x%x", c.error);
+        if (st != AG_OK && (c.error & (kErrSpinTimeout | kErrTableFull))) s->dirty = true;
+        if (statuses) statuses[b] = st;
+        if (st != AG_OK && first == AG_OK) first = st;
+    }
+    return first;
+}
+
+extern "C" int32_t ag_sample_into(ag_sampler *s, const uint32_t *seeds, uint64_t n_seeds, int32_t seeds_mem,
+                                  const ag_features *feats, ag_subgraph_buffers *buf, void *stream) {
+    if (!s || !buf || (!seeds && n_seeds)) return fail(AG_ERR_VALUE, "ag_sample_into: null argument");
+    const uint32_t *sp[1] = {seeds};
+    const uint64_t ns[1] = {n_seeds};
+    return ag_sample_group_into(s, 1, sp, ns, seeds_mem, nullptr, feats, buf, stream);
+}
+
+extern "C" int32_t ag_sample_wait(ag_sampler *s, ag_sample_counts *counts) {
+    if (s && s->in_flight && s->in_flight_n != 1) return fail(AG_ERR_VALUE, "ag_sample_wait: a group is in flight; use ag_sample_group_wait");
+    return ag_sample_group_wait(s, counts, nullptr);
 }
 
 extern "C" int32_t ag_sample(ag_sampler *s, const uint32_t *seeds, uint64_t n_seeds, const ag_features *feats,

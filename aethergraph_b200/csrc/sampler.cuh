@@ -55,6 +55,8 @@ struct BatchState {
     uint32_t error;
     uint32_t ticket;
     uint64_t stream_pos;  // draws consumed by earlier batches of this handle
+    uint32_t prev_edges;  // edges / seeds of the batch that last used this slot: the
+    uint32_t prev_seeds;  // table entries the next batch has to wipe
 };
 
 constexpr uint64_t kSlotEmpty = 0xFFFFFFFFFFFFFFFFull;

@@ -51,7 +51,7 @@ class PrefetchStats:
 class NeighborLoader:
     def __init__(self, graph: CsrGraph, config: SamplingConfig, prefetch_depth: int = 2,
                  sampler_threads: int = 1, *, features: FeatureStore | None = None,
-                 host_features: bool = False, profiling: bool = False):
+                 host_features: bool = False, profiling: bool = False, group: int = 8):
         _check_config(graph, config)
         if prefetch_depth < 1:
             raise ValueError("prefetch_depth must be >= 1")
@@ -65,7 +65,7 @@ class NeighborLoader:
         self._h = C.c_void_p()
         _lib.check(_lib.lib().ag_loader_create(graph._h, features._h if features is not None else None,
                                                C.byref(cfg), int(self._seeded), prefetch_depth, sampler_threads,
-                                               int(profiling), C.byref(self._h)))
+                                               max(1, int(group)), int(profiling), C.byref(self._h)))
         self._lock = threading.Lock()
         self._next_seq = 0
         self._inflight: dict[int, tuple[_Buffers, np.ndarray]] = {}

@@ -361,11 +361,11 @@ class _Pending:
 class _Handle:
     """One ag_sampler: scratch for one batch in flight."""
 
-    def __init__(self, graph: CsrGraph, config: SamplingConfig, seed: int, max_seeds: int = 0):
-        self.graph, self.config = graph, config
+    def __init__(self, graph: CsrGraph, config: SamplingConfig, seed: int, max_seeds: int = 0, group: int = 1):
+        self.graph, self.config, self.group = graph, config, group
         self.h = C.c_void_p()
         cfg = config._to_c(seed, max_seeds)
-        _lib.check(_lib.lib().ag_sampler_create(graph._h, C.byref(cfg), C.byref(self.h)))
+        _lib.check(_lib.lib().ag_sampler_create_group(graph._h, C.byref(cfg), group, C.byref(self.h)))
 
     def __del__(self):
         h = getattr(self, "h", None)
@@ -396,6 +396,48 @@ class _Handle:
                                              _lib.AG_MEM_HOST, features._h if features is not None else None,
                                              C.byref(bufs.c), st))
         return _Pending(self, bufs, seeds)
+
+
+class _PendingGroup:
+    """A group of batches queued as one launch chain; `results()` waits for it."""
+
+    def __init__(self, handle: _Handle, bufs: list[_Buffers], seeds: list[np.ndarray], keep):
+        self._handle, self._bufs, self._seeds, self._keep = handle, bufs, seeds, keep
+        self._done: list[SampledSubgraph] | None = None
+
+    def results(self) -> list[SampledSubgraph]:
+        if self._done is None:
+            n = len(self._bufs)
+            counts = (_lib.SampleCounts * n)()
+            _lib.check(_lib.lib().ag_sample_group_wait(self._handle.h, counts, None))
+            self._done = [SampledSubgraph(b, c, s) for b, c, s in zip(self._bufs, counts, self._seeds)]
+            self._keep = None
+        return self._done
+
+
+def _submit_group(handle: _Handle, seeds: list[np.ndarray], batch_seeds: list[int],
+                  features: FeatureStore | None, stream=None) -> _PendingGroup:
+    import torch
+
+    n = len(seeds)
+    dev = torch.device("cuda", handle.graph.device)
+    dim = features.feature_dim if features is not None else None
+    bufs = []
+    cbufs = (_lib.SubgraphBuffers * n)()
+    ptrs = (C.c_void_p * n)()
+    lens = (C.c_uint64 * n)()
+    bseeds = (C.c_uint64 * n)(*[s & (2**64 - 1) for s in batch_seeds])
+    for i, s in enumerate(seeds):
+        mn, me = handle.bounds(len(s))
+        b = _Buffers(dev, mn, me, len(s), handle.config.track_edge_ids, dim)
+        bufs.append(b)
+        cbufs[i] = b.c
+        ptrs[i] = s.ctypes.data if len(s) else None
+        lens[i] = len(s)
+    st = stream if stream is not None else torch.cuda.current_stream(dev).cuda_stream
+    _lib.check(_lib.lib().ag_sample_group_into(handle.h, n, ptrs, lens, _lib.AG_MEM_HOST, bseeds,
+                                               features._h if features is not None else None, cbufs, st))
+    return _PendingGroup(handle, bufs, seeds, (cbufs, ptrs, lens, bseeds))
 
 
 def _check_config(graph: CsrGraph, config: SamplingConfig) -> None:
@@ -438,18 +480,21 @@ class ParallelBatchSampler:
     over every batch this sampler has handled) draws from
     `batch_seed(config.seed, p)`, so a fixed seed gives the same output however
     the batches are scheduled (crates/aethergraph-core/src/loader/sampler.rs:1726-1751).
-    Here the parallelism is `streams` sampler handles, each with its own CUDA stream."""
+    Here the parallelism is on the device: up to `group` batches ride one launch
+    chain (each kernel's grid has the batch as a second dimension), and `streams`
+    such chains overlap on their own CUDA streams."""
 
     def __init__(self, graph: CsrGraph, config: SamplingConfig, features: FeatureStore | None = None,
-                 streams: int = 4):
+                 streams: int = 2, group: int = 16):
         import torch
 
         _check_config(graph, config)
         self.graph, self.config, self.features = graph, config, features
         self._base = config.seed if config.seed is not None else secrets.randbits(64)
         self._next = 0
+        self._group = max(1, int(group))
         dev = torch.device("cuda", graph.device)
-        self._handles = [_Handle(graph, config, self._base) for _ in range(max(1, streams))]
+        self._handles = [_Handle(graph, config, self._base, group=self._group) for _ in range(max(1, streams))]
         self._streams = [torch.cuda.Stream(dev) for _ in self._handles]
 
     def sample_batches(self, batches: Sequence) -> list[SampledSubgraph]:
@@ -459,21 +504,24 @@ class ParallelBatchSampler:
         first = self._next
         self._next += len(seeds)
         out: list[SampledSubgraph | None] = [None] * len(seeds)
-        pending: list[tuple[int, _Pending] | None] = [None] * len(self._handles)
+        pending: list[tuple[int, _PendingGroup] | None] = [None] * len(self._handles)
         cur = torch.cuda.current_stream()
-        for j, s in enumerate(seeds):
-            k = j % len(self._handles)
+        G = self._group
+        for c, lo in enumerate(range(0, len(seeds), G)):
+            k = c % len(self._handles)
             if pending[k] is not None:
                 i, p = pending[k]
-                out[i] = p.result()
+                out[i:i + len(p._bufs)] = p.results()
             h, st = self._handles[k], self._streams[k]
-            h.reseed(_lib.lib().ag_batch_seed(self._base, first + j))
+            chunk = seeds[lo:lo + G]
+            bseeds = [_lib.lib().ag_batch_seed(self._base, first + lo + j) for j in range(len(chunk))]
             st.wait_stream(cur)
             with torch.cuda.stream(st):
-                pending[k] = (j, h.submit(s, self.features, st.cuda_stream))
+                pending[k] = (lo, _submit_group(h, chunk, bseeds, self.features, st.cuda_stream))
         for slot in pending:
             if slot is not None:
-                out[slot[0]] = slot[1].result()
+                i, p = slot
+                out[i:i + len(p._bufs)] = p.results()
         for st in self._streams:
             cur.wait_stream(st)
         for sg in out:

@@ -252,10 +252,11 @@ def run_device(args, w):
     threads, depth = args.threads, args.depth
     h = C.c_void_p()
     ccfg = cfg._to_c(SAMPLER_SEED, bs)
-    _lib.check(L.ag_loader_create(g._h, feats._h, C.byref(ccfg), 1, depth, threads, 1, C.byref(h)))
+    group = args.group
+    _lib.check(L.ag_loader_create(g._h, feats._h, C.byref(ccfg), 1, depth, threads, group, 1, C.byref(h)))
     mn, me = C.c_uint64(), C.c_uint64()
     _lib.check(L.ag_loader_bounds(h, bs, C.byref(mn), C.byref(me)))
-    ring = [_Buffers(dev, mn.value, me.value, bs, True, w["dim"]) for _ in range(depth + threads + 2)]
+    ring = [_Buffers(dev, mn.value, me.value, bs, True, w["dim"]) for _ in range(depth + threads * group + group)]
     R = len(ring)
     batch = _lib.Batch()
     stats0 = _lib.LoaderStats()
@@ -331,8 +332,8 @@ def run_device(args, w):
     del ring
 
     # ---- e2e: public Python API, host seeds in, counts back -----------------
-    loader = NeighborLoader(g, cfg, prefetch_depth=depth, sampler_threads=threads, features=feats)
-    window = depth + threads
+    loader = NeighborLoader(g, cfg, prefetch_depth=depth, sampler_threads=threads, features=feats, group=group)
+    window = depth + threads * group
 
     def run_e2e(first: int, count: int):
         edges = submitted = delivered = 0
@@ -370,7 +371,7 @@ def run_device(args, w):
             "scaling": "weak", "vs_baseline": None, "dtype": "u32 ids / " + w["dtype"] + "->f32",
             "data": "synthetic (seeded R-MAT graph + ~N(0,1) features generated in HBM)",
             "config": {"workload": w["label"], "batches_per_step": per_step, "rng_mode": "wyrand_exact",
-                       "sampler_threads": threads, "prefetch_depth": depth, "parallelism": f"dp{world}",
+                       "sampler_threads": threads, "group": group, "prefetch_depth": depth, "parallelism": f"dp{world}",
                        "features": "replicated", "inputs_larger_than_l2": True},
             "gather_gbs": gather_gbs, "edges_per_step": tot_edges / max(args.steps, 1),
             "rows_per_step": tot_nodes / max(args.steps, 1), "setup_s": round(t_setup, 1),
@@ -437,9 +438,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--workload", default=os.environ.get("AG_BENCH_WORKLOAD", "c2"), choices=sorted(WORKLOADS))
-    ap.add_argument("--threads", type=int, default=int(os.environ.get("AG_BENCH_THREADS", "6")),
-                    help="loader worker threads = batches in flight on the GPU")
-    ap.add_argument("--depth", type=int, default=4)
+    ap.add_argument("--threads", type=int, default=int(os.environ.get("AG_BENCH_THREADS", "3")),
+                    help="loader worker threads, each with its own CUDA stream")
+    ap.add_argument("--depth", type=int, default=8)
+    ap.add_argument("--group", type=int, default=int(os.environ.get("AG_BENCH_GROUP", "16")),
+                    help="batches a worker runs as one launch chain")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup

@@ -233,6 +233,25 @@ int32_t ag_sample(ag_sampler *s, const uint32_t *seeds, uint64_t n_seeds,
                   const ag_features *feats, int32_t want_int64, ag_subgraph_buffers *buf,
                   void *stream);
 int32_t ag_subgraph_release(ag_sampler *s, ag_subgraph_buffers *buf);
+
+/* Groups.  Batches are independent, so one launch chain can serve several of
+ * them: every kernel's grid gets the batch as a second dimension and a group
+ * of 16 batches costs the same dozen launches as one.  This is the device form
+ * of ParallelBatchSampler::sample_batches (sampler.rs:1726-1751): with
+ * batch_seeds[b] = ag_batch_seed(seed, position of batch b) it reproduces it
+ * bit for bit.  A sampler created with ag_sampler_create_group(.., group, ..)
+ * holds scratch for `group` batches; n_batches may be anything up to that.
+ * seeds[b] / n_seeds[b] / bufs[b] describe batch b; batch_seeds == NULL lets
+ * the handle's own RNG stream continue (single batch only makes sense).
+ * ag_sample_group_wait fills counts[b] and statuses[b] (either may be NULL)
+ * and returns the first failing status. */
+int32_t ag_sampler_create_group(const ag_graph *g, const ag_sampling_config *cfg, uint32_t group,
+                                ag_sampler **out);
+int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const uint32_t *const *seeds,
+                             const uint64_t *n_seeds, int32_t seeds_mem,
+                             const uint64_t *batch_seeds, const ag_features *feats,
+                             ag_subgraph_buffers *bufs, void *stream);
+int32_t ag_sample_group_wait(ag_sampler *s, ag_sample_counts *counts, int32_t *statuses);
 /* When on, every batch records CUDA events around its sampling chain and its
  * gather on the launching stream (ag_sample_counts.sample_ms / gather_ms). */
 int32_t ag_sampler_set_profiling(ag_sampler *s, int32_t on);
@@ -242,7 +261,9 @@ void ag_sampler_free(ag_sampler *s);
  * Stands in for the prefetching NeighborLoader (_core.pyi:380-464;
  * crates/aethergraph-core/src/loader/prefetch.rs:402-560 pipeline,
  * :911-1073 workers).  `sampler_threads` host threads each own one sampler
- * handle and one CUDA stream, so that many batches are in flight on the GPU.
+ * handle and one CUDA stream; a worker takes up to `group` queued batches at a
+ * time and runs them as one launch chain (see "Groups" above), so up to
+ * sampler_threads x group batches are in flight on the GPU.
  *   - submit assigns a sequence number; the work queue holds 8 x prefetch_depth
  *     items and submit blocks while it is full (prefetch.rs:457-477).
  *   - With seeded = 1 batch number seq is sampled from
@@ -276,7 +297,7 @@ typedef struct {
 
 int32_t ag_loader_create(const ag_graph *g, const ag_features *f, const ag_sampling_config *cfg,
                          int32_t seeded, uint32_t prefetch_depth, uint32_t sampler_threads,
-                         int32_t profiling, ag_loader **out);
+                         uint32_t group, int32_t profiling, ag_loader **out);
 int32_t ag_loader_bounds(const ag_loader *l, uint64_t n_seeds, uint64_t *max_nodes,
                          uint64_t *max_edges);
 int32_t ag_loader_submit(ag_loader *l, int64_t batch_idx, const uint32_t *seeds, uint64_t n_seeds,
