@@ -299,7 +299,19 @@ extern "C" int32_t ag_loader_submit(ag_loader *l, int64_t batch_idx, const uint3
         }
     }
     std::unique_lock<std::mutex> lk(l->m);
-    l->cv_space.wait(lk, [&] { return l->stop || !l->fault.empty() || l->queue.size() < (size_t)8 * l->depth; });
+    // Blocks while the work queue is full, like the reference's bounded channel; gives
+    // up after the same 30 s the consumer side waits, so a caller that submits and
+    // consumes on one thread and overfills the queue gets an error, not a hang.
+    const bool room = l->cv_space.wait_for(lk, std::chrono::seconds(30), [&] {
+        return l->stop || !l->fault.empty() || l->queue.size() < (size_t)8 * l->depth;
+    });
+    if (!room) {
+        lk.unlock();
+        if (w.after) cudaEventDestroy(w.after);
+        if (w.owned) free_owned(&w.bufs);
+        return fail(AG_ERR_TIMEOUT, "timed out waiting for room in the work queue (%u batches queued; is anything "
+                    "consuming results?)", 8 * l->depth);
+    }
     if (l->stop || !l->fault.empty()) {
         const std::string msg = l->stop ? "loader is shut down" : ("sampler worker failed: " + l->fault);
         const int32_t code = l->stop ? AG_ERR_SHUTDOWN : AG_ERR_WORKER;

@@ -158,19 +158,25 @@ k_assign(const SampleParams *__restrict__ pa, uint32_t stage, uint32_t next_k, i
 
     const SampleParams &p = pa[blockIdx.y];
     BatchState *bs = p.state;
-    if (threadIdx.x == 0) {
-        s_tile = atomicAdd(&bs->ticket, 1u);
-        if (s_tile == gridDim.x - 1) bs->ticket = 0;  // every ticket of this launch is taken
-    }
-    __syncthreads();
-    const uint32_t tile = s_tile;
     const StageInfo si = bs->stage[stage];
     const uint32_t count = (stage == 0) ? p.n_seeds : si.hop_edges;
     const uint32_t n_tiles = max(1u, (count + kAssignThreads - 1) / kAssignThreads);
-    if (tile >= n_tiles) return;
-
-    const uint32_t item = tile * kAssignThreads + threadIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+    // The grid is sized for a typical batch, not for the worst case: a block
+    // keeps drawing tile tickets until they run out.  Tickets are handed out in
+    // order, so the tiles a look-back waits for are always already running.
+    for (;;) {
+    __syncthreads();
+    if (threadIdx.x == 0) s_tile = atomicAdd(&bs->ticket, 1u);
+    __syncthreads();
+    const uint32_t tile = s_tile;
+    if (tile >= n_tiles) {
+        // n_tiles + gridDim.x tickets are drawn in all; the last one resets the counter.
+        if (threadIdx.x == 0 && tile == n_tiles + gridDim.x - 1) bs->ticket = 0;
+        return;
+    }
+    const uint32_t item = tile * kAssignThreads + threadIdx.x;
 
     // First sighting?  The table holds kPending | position of the smallest
     // position that named the vertex.
@@ -222,29 +228,30 @@ k_assign(const SampleParams *__restrict__ pa, uint32_t stage, uint32_t next_k, i
         }
     }
     __syncthreads();
-    if (!first) return;
-
-    const ScanVal base = s_prefix + s_warp[warp];
-    const ScanVal excl = ScanVal{base.flags + incl.flags - v.flags, base.take + incl.take - v.take,
-                                 base.draws + incl.draws - v.draws};
-    const uint32_t rank = excl.flags;
-    const uint32_t local = si.n_nodes + rank;
-    if ((uint64_t)local >= p.cap_nodes || (has_next && (uint64_t)rank >= p.frontier_cap)) {
-        atomicOr(&bs->error, kErrCapacity);
-        return;
+    if (first) {
+        const ScanVal base = s_prefix + s_warp[warp];
+        const ScanVal excl = ScanVal{base.flags + incl.flags - v.flags, base.take + incl.take - v.take,
+                                     base.draws + incl.draws - v.draws};
+        const uint32_t rank = excl.flags;
+        const uint32_t local = si.n_nodes + rank;
+        if ((uint64_t)local >= p.cap_nodes || (has_next && (uint64_t)rank >= p.frontier_cap)) {
+            atomicOr(&bs->error, kErrCapacity);
+        } else {
+            p.nodes[local] = id;
+            p.table.slots[slot] = ((uint64_t)id << 32) | local;  // final: readers accept either form
+            if (has_next) {
+                FrontierEntry fe;
+                fe.off = off;
+                fe.dbase = si.draws + si.hop_draws + excl.draws;
+                fe.id = id;
+                fe.local = local;
+                fe.deg = (uint32_t)deg;
+                fe.ebase = excl.take;
+                p.frontier[stage & 1][rank] = fe;
+            }
+        }
     }
-    p.nodes[local] = id;
-    p.table.slots[slot] = ((uint64_t)id << 32) | local;  // final: readers accept either form
-    if (has_next) {
-        FrontierEntry fe;
-        fe.off = off;
-        fe.dbase = si.draws + si.hop_draws + excl.draws;
-        fe.id = id;
-        fe.local = local;
-        fe.deg = (uint32_t)deg;
-        fe.ebase = excl.take;
-        p.frontier[stage & 1][rank] = fe;
-    }
+    }  // next ticket
 }
 
 // ------------------------------------------------------------------- pick --
@@ -282,9 +289,11 @@ k_pick_small(const SampleParams *__restrict__ pa, uint32_t hop, uint32_t k) {
     const SampleParams &p = pa[blockIdx.y];
     const uint32_t stage = hop + 1;
     const StageInfo si = p.state->stage[stage];
-    const uint32_t node = (blockIdx.x * kPickThreads + threadIdx.x) / G;
-    if ((node & ~(32u / G - 1u)) >= si.frontier_n) return;  // the whole warp is past the frontier
     const uint32_t t = threadIdx.x % G;
+    // Grid-stride over the frontier (the grid is sized for a typical batch); a
+    // warp leaves the loop together, when its first vertex is past the frontier.
+    for (uint32_t node = (blockIdx.x * kPickThreads + threadIdx.x) / G; (node & ~(32u / G - 1u)) < si.frontier_n;
+         node += gridDim.x * (kPickThreads / G)) {
     const bool active = node < si.frontier_n;
     FrontierEntry fe{};
     if (active) fe = p.frontier[hop & 1][node];
@@ -312,11 +321,13 @@ k_pick_small(const SampleParams *__restrict__ pa, uint32_t hop, uint32_t k) {
             if (sampled && t == s && m) pick = ip;
         }
     }
-    if (!active) return;
-    uint32_t take;
-    uint64_t draws;
-    row_demand(p.mode, deg, k, take, draws);
-    if (t < take) emit_edge(p, si, fe, t, fe.off + pick);
+    if (active) {
+        uint32_t take;
+        uint64_t draws;
+        row_demand(p.mode, deg, k, take, draws);
+        if (t < take) emit_edge(p, si, fe, t, fe.off + pick);
+    }
+    }  // next vertex
 }
 
 // Fanout > 32: one warp per frontier vertex; finished picks live in shared
@@ -327,15 +338,15 @@ k_pick_large(const SampleParams *__restrict__ pa, uint32_t hop, uint32_t k) {
     const SampleParams &p = pa[blockIdx.y];
     const StageInfo si = p.state->stage[hop + 1];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t node = blockIdx.x * 4 + warp;
-    if (node >= si.frontier_n) return;
+    uint32_t *picks = s_picks[warp];
+    for (uint32_t node = blockIdx.x * 4 + warp; node < si.frontier_n; node += gridDim.x * 4) {
     const FrontierEntry fe = p.frontier[hop & 1][node];
     const uint32_t deg = fe.deg;
     uint32_t take;
     uint64_t draws;
     row_demand(p.mode, deg, k, take, draws);
     const bool sampled = p.mode != kModeReplace && deg > k;
-    uint32_t *picks = s_picks[warp];
+    __syncwarp();
     for (uint32_t c = 0; c < take; c += 32) {
         const uint32_t t = c + lane;
         const bool in = t < take;
@@ -360,6 +371,7 @@ k_pick_large(const SampleParams *__restrict__ pa, uint32_t hop, uint32_t k) {
         }
         if (in) emit_edge(p, si, fe, t, fe.off + pick);
     }
+    }  // next vertex
 }
 
 // Weighted sampling without replacement, fanout <= 32, one warp per vertex.
@@ -379,16 +391,17 @@ k_pick_weighted(const SampleParams *__restrict__ pa, uint32_t hop, uint32_t k) {
     const SampleParams &p = pa[blockIdx.y];
     const StageInfo si = p.state->stage[hop + 1];
     const int lane = threadIdx.x & 31;
-    const uint32_t node = (blockIdx.x * kPickThreads + threadIdx.x) >> 5;
-    if (node >= si.frontier_n) return;
+    if (k == 0) return;
+    const double inf = __longlong_as_double(0x7FF0000000000000ll);
+    for (uint32_t node = (blockIdx.x * kPickThreads + threadIdx.x) >> 5; node < si.frontier_n;
+         node += gridDim.x * (kPickThreads / 32)) {
     const FrontierEntry fe = p.frontier[hop & 1][node];
     const uint32_t deg = fe.deg;
-    if (deg == 0 || k == 0) return;
+    if (deg == 0) continue;
     if (k >= deg) {
         for (uint32_t t = lane; t < deg; t += 32) emit_edge(p, si, fe, t, fe.off + t);
-        return;
+        continue;
     }
-    const double inf = __longlong_as_double(0x7FF0000000000000ll);
     double best_key = inf;
     uint32_t best_pos = 0xFFFFFFFFu;  // sentinel: sorts after every real (key, position)
     for (uint32_t c = 0; c < deg; c += 32) {
@@ -426,6 +439,7 @@ k_pick_weighted(const SampleParams *__restrict__ pa, uint32_t hop, uint32_t k) {
         }
     }
     if ((uint32_t)lane < k) emit_edge(p, si, fe, lane, fe.off + best_pos);
+    }  // next vertex
 }
 
 // --------------------------------------------------------------- finalize --
@@ -787,6 +801,15 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
 
     const SampleParams *pa = s->params_dev;
     const uint32_t nmax = (uint32_t)max_n;
+    // Grids cover the worst case only up to about two waves of resident blocks
+    // over the whole group; the kernels stride (or draw tickets) beyond that, so
+    // a batch far below its bound does not pay for thousands of empty blocks.
+    auto cap_assign = [&](uint64_t blocks) {
+        return (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>(blocks, std::max<uint64_t>(1, (uint64_t)kSMs * 8 / n_batches)));
+    };
+    auto cap_pick = [&](uint64_t blocks) {
+        return (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>(blocks, std::max<uint64_t>(1, (uint64_t)kSMs * 16 / n_batches)));
+    };
     {
         // enough blocks to wipe a typical batch's slots in one pass
         const uint32_t bx = (uint32_t)std::min<uint64_t>(std::max<uint64_t>((b_edges + nmax) / 1024, 1), 64);
@@ -794,7 +817,7 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
     }
     if (nmax) k_insert_seeds<<<dim3((nmax + 255) / 256, n_batches), 256, 0, st>>>(pa);
     // stage 0: seeds -> frontier[0]
-    k_assign<<<dim3(std::max(1u, (nmax + kAssignThreads - 1) / kAssignThreads), n_batches), kAssignThreads, 0, st>>>(
+    k_assign<<<dim3(cap_assign((nmax + kAssignThreads - 1) / kAssignThreads), n_batches), kAssignThreads, 0, st>>>(
         pa, 0, s->cfg.fanout[0], 1);
 
     uint64_t f_bound = std::min<uint64_t>(nmax, g->num_nodes);
@@ -803,13 +826,13 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
         const uint64_t e_bound = f_bound * k;
         if (f_bound && k) {
             if (s->mode == kModeWeighted) {
-                const uint32_t blocks = (uint32_t)((f_bound * 32 + kPickThreads - 1) / kPickThreads);
+                const uint32_t blocks = cap_pick((f_bound * 32 + kPickThreads - 1) / kPickThreads);
                 k_pick_weighted<<<dim3(blocks, n_batches), kPickThreads, 0, st>>>(pa, h, k);
             } else if (k > 32) {
-                k_pick_large<<<dim3((uint32_t)((f_bound + 3) / 4), n_batches), 128, 0, st>>>(pa, h, k);
+                k_pick_large<<<dim3(cap_pick((f_bound + 3) / 4), n_batches), 128, 0, st>>>(pa, h, k);
             } else {
                 const uint32_t G = k <= 4 ? 4 : k <= 8 ? 8 : k <= 16 ? 16 : 32;
-                const dim3 grid((uint32_t)((f_bound * G + kPickThreads - 1) / kPickThreads), n_batches);
+                const dim3 grid(cap_pick((f_bound * G + kPickThreads - 1) / kPickThreads), n_batches);
                 switch (G) {
                     case 4: k_pick_small<4><<<grid, kPickThreads, 0, st>>>(pa, h, k); break;
                     case 8: k_pick_small<8><<<grid, kPickThreads, 0, st>>>(pa, h, k); break;
@@ -819,7 +842,7 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
             }
         }
         const bool has_next = h + 1 < H;
-        k_assign<<<dim3((uint32_t)std::max<uint64_t>(1, (e_bound + kAssignThreads - 1) / kAssignThreads), n_batches),
+        k_assign<<<dim3(cap_assign((e_bound + kAssignThreads - 1) / kAssignThreads), n_batches),
                    kAssignThreads, 0, st>>>(pa, h + 1, has_next ? s->cfg.fanout[h + 1] : 0, has_next ? 1 : 0);
         f_bound = std::min<uint64_t>(e_bound, g->num_nodes);
     }

@@ -66,6 +66,10 @@ class NeighborLoader:
         _lib.check(_lib.lib().ag_loader_create(graph._h, features._h if features is not None else None,
                                                C.byref(cfg), int(self._seeded), prefetch_depth, sampler_threads,
                                                max(1, int(group)), int(profiling), C.byref(self._h)))
+        import torch
+
+        self._dev = torch.device("cuda", graph.device)
+        self._bounds: dict[int, tuple[int, int]] = {}
         self._lock = threading.Lock()
         self._next_seq = 0
         self._inflight: dict[int, tuple[_Buffers, np.ndarray]] = {}
@@ -102,12 +106,14 @@ class NeighborLoader:
         import torch
 
         s = coerce_seeds(seeds, self.graph.num_nodes)
-        dev = torch.device("cuda", self.graph.device)
-        mn, me = C.c_uint64(), C.c_uint64()
-        _lib.check(_lib.lib().ag_loader_bounds(self._h, len(s), C.byref(mn), C.byref(me)))
-        with torch.cuda.device(dev):
-            bufs = _Buffers(dev, mn.value, me.value, len(s), self.config.track_edge_ids, self.feature_dim)
-            after = torch.cuda.current_stream(dev).cuda_stream
+        bound = self._bounds.get(len(s))
+        if bound is None:
+            mn, me = C.c_uint64(), C.c_uint64()
+            _lib.check(_lib.lib().ag_loader_bounds(self._h, len(s), C.byref(mn), C.byref(me)))
+            bound = self._bounds[len(s)] = (mn.value, me.value)
+        dev = self._dev
+        bufs = _Buffers(dev, bound[0], bound[1], len(s), self.config.track_edge_ids, self.feature_dim)
+        after = torch.cuda.current_stream(dev).cuda_stream
         with self._lock:
             # The C call blocks while the work queue is full; the lock keeps the
             # Python-side sequence counter in step with the library's.

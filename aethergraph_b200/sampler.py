@@ -120,12 +120,11 @@ def coerce_seeds(seeds, num_nodes: int) -> np.ndarray:
             if bad is not None:
                 raise SamplingError(f"seed node {bad} out of u32 range [0, {0xFFFFFFFF}]")
         a = a.astype(np.uint32)
-    a = np.ascontiguousarray(a)
-    if a.size:
-        bad = np.nonzero(a >= num_nodes)[0] if num_nodes < 2**32 else []
-        if len(bad):
-            p = int(bad[0])
-            raise SamplingError(f"seed node {int(a[p])} (position {p}) is out of range for {num_nodes} nodes")
+    if not a.flags.c_contiguous:
+        a = np.ascontiguousarray(a)
+    if a.size and num_nodes < 2**32 and int(a.max()) >= num_nodes:
+        p = int(np.nonzero(a >= num_nodes)[0][0])
+        raise SamplingError(f"seed node {int(a[p])} (position {p}) is out of range for {num_nodes} nodes")
     return a
 
 

@@ -256,7 +256,10 @@ def run_device(args, w):
     _lib.check(L.ag_loader_create(g._h, feats._h, C.byref(ccfg), 1, depth, threads, group, 1, C.byref(h)))
     mn, me = C.c_uint64(), C.c_uint64()
     _lib.check(L.ag_loader_bounds(h, bs, C.byref(mn), C.byref(me)))
-    ring = [_Buffers(dev, mn.value, me.value, bs, True, w["dim"]) for _ in range(depth + threads * group + group)]
+    # One thread both submits and consumes here, so it must never block in submit:
+    # keep no more batches outstanding than the loader's work queue (8 x depth) holds.
+    window = min(8 * depth, depth + threads * group + group)
+    ring = [_Buffers(dev, mn.value, me.value, bs, True, w["dim"]) for _ in range(window)]
     R = len(ring)
     batch = _lib.Batch()
     stats0 = _lib.LoaderStats()
@@ -333,7 +336,6 @@ def run_device(args, w):
 
     # ---- e2e: public Python API, host seeds in, counts back -----------------
     loader = NeighborLoader(g, cfg, prefetch_depth=depth, sampler_threads=threads, features=feats, group=group)
-    window = depth + threads * group
 
     def run_e2e(first: int, count: int):
         edges = submitted = delivered = 0
