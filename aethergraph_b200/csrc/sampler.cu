@@ -3,24 +3,28 @@
 // Computes exactly what the reference's NeighborSampler::sample computes
 // (crates/aethergraph-core/src/loader/sampler.rs:845-961 with the hop loop at
 // :754-842 and the per-node dispatch at :1178-1235), but as a short chain of
-// data-parallel kernels instead of one sequential loop:
+// data-parallel kernels instead of one sequential loop.  A batch with H hops
+// is H + 3 launches:
 //
-//   insert   every seed (or every edge of a hop) is inserted into a hash table
-//            keyed by vertex id with atomicMin(position): the smallest position
-//            that names a vertex is its first sighting.
-//   assign   one single-pass scan over the items in position order turns the
-//            first-sighting flags into local ids (= discovery order, exactly
-//            the order the sequential reference assigns them in), appends the
-//            new vertices to `nodes` and to the next frontier, and in the same
-//            pass reads each new vertex's CSR row bounds and scans how many
-//            edges and how many RNG draws it will need in the next hop.
-//   pick     a group of lanes per frontier vertex reproduces the reference's
-//            choice of row positions — take-all (:1312-1328), Floyd
-//            (:1332-1380), with replacement (:1289-1308) or the weighted
-//            Efraimidis-Spirakis keys (:1418-1469) — writes the edges at their
-//            scanned slots and inserts the destinations for the next assign.
-//   finalize every edge and seed reads its endpoint's final local id from the
-//            table; the int64 views the Python API exposes are written here.
+//   insert_seeds   every seed is inserted into a hash table keyed by vertex id
+//                  with atomicMin(position): the smallest position that names a
+//                  vertex is its first sighting.
+//   expand(s)      s = 0 .. H.  The items of stage s are the seeds (s = 0) or
+//                  the edges hop s - 1 emitted, in position order.  One
+//                  single-pass scan over them turns the first-sighting flags
+//                  into local ids (= discovery order, exactly the order the
+//                  sequential reference assigns them in) and appends the new
+//                  vertices to `nodes`; the same scan carries how many edges and
+//                  how many RNG draws each new vertex needs at hop s.  The tile
+//                  then expands its own new vertices straight away: a group of
+//                  lanes per vertex reproduces the reference's choice of row
+//                  positions — take-all (:1312-1328), Floyd (:1332-1380), with
+//                  replacement (:1289-1308) or the weighted Efraimidis-Spirakis
+//                  keys (:1418-1469) — writes the edges of hop s at their
+//                  scanned slots and inserts the destinations into the table as
+//                  the items of stage s + 1.
+//   finalize       every edge and seed reads its endpoint's final local id from
+//                  the table; the int64 views the Python API exposes are written.
 //
 // The reference draws from one sequential WyRand stream per batch.  WyRand's
 // state is an additive counter, so draw d is a pure function of (seed, d); the
@@ -30,7 +34,7 @@
 // Batches are independent, so one launch chain serves a whole GROUP of them:
 // every kernel's grid has the batch as its y dimension and each batch brings
 // its own parameter block, dedup table, scan descriptors and output buffers.
-// A group of 16 batches of 1024 seeds costs the same dozen launches as one.
+// A group of 16 batches of 1024 seeds costs the same few launches as one.
 #include <string.h>
 
 #include <algorithm>
@@ -44,11 +48,11 @@ namespace ag {
 
 namespace {
 
-constexpr int kAssignThreads = 512;  // one item per thread, one tile per block
-constexpr int kPickThreads = 256;
-constexpr int kLargeK = 1024;        // largest fanout the k > 32 path keeps in shared memory
+constexpr int kTile = 512;      // items per tile = threads per block of the expand kernel
+constexpr int kLargeK = 1024;   // largest fanout the k > 32 path keeps in shared memory
 
 enum : int { kModeUniform = 0, kModeReplace = 1, kModeWeighted = 2 };
+enum : int { kPickSmall = 0, kPickLarge = 1, kPickWeighted = 2 };
 
 // Parameter block of one batch; a group's blocks sit in one device array that
 // the kernels index with blockIdx.y.
@@ -67,6 +71,7 @@ struct SampleParams {
     int rng_mode;
     int mode;
     int reset_pos;
+    uint32_t num_hops;
     // outputs
     uint32_t *nodes;
     uint32_t *edge_src, *edge_dst, *src_local, *dst_local, *seed_locals;
@@ -77,9 +82,6 @@ struct SampleParams {
     // scratch
     uint32_t *slot_of_seed;
     uint32_t *slot_of_edge;
-    FrontierEntry *frontier[2];
-    uint64_t frontier_cap;
-    uint32_t num_hops;
 };
 
 // Row bounds with the reference's guard (graph/csr.rs:318-335): an inverted
@@ -106,32 +108,6 @@ __device__ __forceinline__ void row_demand(int mode, uint64_t deg, uint32_t k, u
     draws = (mode == kModeWeighted) ? deg : (uint64_t)k;
 }
 
-// ------------------------------------------------------------------ begin --
-// Empties the table slots the handle's previous batch touched (so the table is
-// never memset between batches) and resets the per-batch bookkeeping.
-__global__ void k_begin(const SampleParams *__restrict__ pa) {
-    const SampleParams &p = pa[blockIdx.y];
-    BatchState *bs = p.state;
-    const uint32_t pe = bs->prev_edges, ps = bs->prev_seeds;
-    const uint32_t tid = blockIdx.x * blockDim.x + threadIdx.x, stride = gridDim.x * blockDim.x;
-    for (uint32_t e = tid; e < pe; e += stride) {
-        const uint32_t slot = p.slot_of_edge[e];
-        if (slot != 0xFFFFFFFFu) p.table.slots[slot] = kSlotEmpty;
-    }
-    for (uint32_t i = tid; i < ps; i += stride) {
-        const uint32_t slot = p.slot_of_seed[i];
-        if (slot != 0xFFFFFFFFu) p.table.slots[slot] = kSlotEmpty;
-    }
-    if (tid == 0) {
-        if (p.reset_pos) bs->stream_pos = 0;
-        StageInfo s0{};
-        s0.draws = bs->stream_pos;
-        bs->stage[0] = s0;
-        bs->error = 0;
-        bs->ticket = 0;
-    }
-}
-
 // ------------------------------------------------------------ seed insert --
 __global__ void k_insert_seeds(const SampleParams *__restrict__ pa) {
     const SampleParams &p = pa[blockIdx.y];
@@ -143,129 +119,22 @@ __global__ void k_insert_seeds(const SampleParams *__restrict__ pa) {
         p.slot_of_seed[i] = 0xFFFFFFFFu;
         return;
     }
-    p.slot_of_seed[i] = table_insert_min(p.table, id, kPending | i, &p.state->error);
+    p.slot_of_seed[i] = table_insert_min(p.table, id, enc_pending(p.table.gen, 0, i), &p.state->error);
 }
 
-// ----------------------------------------------------------------- assign --
-// Items of stage s in position order: the seeds (s == 0) or the edges of hop
-// s - 1.  next_k is the fanout of the hop the new vertices will be expanded
-// at; has_next is 0 after the last hop.
-__global__ void __launch_bounds__(kAssignThreads)
-k_assign(const SampleParams *__restrict__ pa, uint32_t stage, uint32_t next_k, int has_next) {
-    __shared__ uint32_t s_tile;
-    __shared__ ScanVal s_warp[kAssignThreads / 32];
-    __shared__ ScanVal s_prefix;
-
-    const SampleParams &p = pa[blockIdx.y];
-    BatchState *bs = p.state;
-    const StageInfo si = bs->stage[stage];
-    const uint32_t count = (stage == 0) ? p.n_seeds : si.hop_edges;
-    const uint32_t n_tiles = max(1u, (count + kAssignThreads - 1) / kAssignThreads);
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-
-    // The grid is sized for a typical batch, not for the worst case: a block
-    // keeps drawing tile tickets until they run out.  Tickets are handed out in
-    // order, so the tiles a look-back waits for are always already running.
-    for (;;) {
-    __syncthreads();
-    if (threadIdx.x == 0) s_tile = atomicAdd(&bs->ticket, 1u);
-    __syncthreads();
-    const uint32_t tile = s_tile;
-    if (tile >= n_tiles) {
-        // n_tiles + gridDim.x tickets are drawn in all; the last one resets the counter.
-        if (threadIdx.x == 0 && tile == n_tiles + gridDim.x - 1) bs->ticket = 0;
-        return;
-    }
-    const uint32_t item = tile * kAssignThreads + threadIdx.x;
-
-    // First sighting?  The table holds kPending | position of the smallest
-    // position that named the vertex.
-    uint32_t slot = 0xFFFFFFFFu, id = 0;
-    bool first = false;
-    if (item < count) {
-        slot = (stage == 0) ? p.slot_of_seed[item] : p.slot_of_edge[si.n_edges + item];
-        if (slot != 0xFFFFFFFFu) {
-            const uint64_t cur = __ldcg((const unsigned long long *)&p.table.slots[slot]);
-            first = ((uint32_t)cur == (kPending | item));
-            id = (uint32_t)(cur >> 32);
-        }
-    }
-    ScanVal v{first ? 1u : 0u, 0u, 0ull};
-    uint64_t off = 0, deg = 0;
-    if (first && has_next) {
-        row_bounds(p.offsets, p.num_nodes, p.num_edges, id, off, deg);
-        if (deg > 0xFFFFFFFFull) { atomicOr(&bs->error, kErrCapacity); deg = 0; }
-        row_demand(p.mode, deg, next_k, v.take, v.draws);
-    }
-
-    // Block scan: warp scans, then the warp totals.
-    const ScanVal incl = warp_inclusive_scan(v, lane);
-    if (lane == 31) s_warp[warp] = incl;
-    __syncthreads();
-    if (warp == 0) {
-        ScanVal w = (lane < kAssignThreads / 32) ? s_warp[lane] : ScanVal{0, 0, 0};
-        const ScanVal wi = warp_inclusive_scan(w, lane);
-        const ScanVal block_total = ScanVal{__shfl_sync(0xffffffffu, wi.flags, 31),
-                                            __shfl_sync(0xffffffffu, wi.take, 31),
-                                            __shfl_sync(0xffffffffu, wi.draws, 31)};
-        if (lane < kAssignThreads / 32) s_warp[lane] = ScanVal{wi.flags - w.flags, wi.take - w.take, wi.draws - w.draws};
-        const ScanVal prefix = lookback_exclusive(p.tiles, tile, p.epoch_base + stage, block_total, lane, &bs->error);
-        if (lane == 0) {
-            s_prefix = prefix;
-            if (tile == n_tiles - 1) {
-                // Totals of the stage: hand over to the next one.
-                const ScanVal tot = prefix + block_total;
-                StageInfo nx;
-                nx.n_nodes = si.n_nodes + tot.flags;
-                nx.n_edges = si.n_edges + ((stage == 0) ? 0u : count);
-                nx.frontier_n = tot.flags;
-                nx.hop_edges = tot.take;
-                nx.draws = si.draws + si.hop_draws;
-                nx.hop_draws = tot.draws;
-                bs->stage[stage + 1] = nx;
-                bs->nodes_per_stage[stage] = tot.flags;
-            }
-        }
-    }
-    __syncthreads();
-    if (first) {
-        const ScanVal base = s_prefix + s_warp[warp];
-        const ScanVal excl = ScanVal{base.flags + incl.flags - v.flags, base.take + incl.take - v.take,
-                                     base.draws + incl.draws - v.draws};
-        const uint32_t rank = excl.flags;
-        const uint32_t local = si.n_nodes + rank;
-        if ((uint64_t)local >= p.cap_nodes || (has_next && (uint64_t)rank >= p.frontier_cap)) {
-            atomicOr(&bs->error, kErrCapacity);
-        } else {
-            p.nodes[local] = id;
-            p.table.slots[slot] = ((uint64_t)id << 32) | local;  // final: readers accept either form
-            if (has_next) {
-                FrontierEntry fe;
-                fe.off = off;
-                fe.dbase = si.draws + si.hop_draws + excl.draws;
-                fe.id = id;
-                fe.local = local;
-                fe.deg = (uint32_t)deg;
-                fe.ebase = excl.take;
-                p.frontier[stage & 1][rank] = fe;
-            }
-        }
-    }
-    }  // next ticket
-}
-
-// ------------------------------------------------------------------- pick --
+// ----------------------------------------------------------------- expand --
 __device__ __forceinline__ uint32_t draw_u32(const SampleParams &p, uint32_t hop, uint32_t vertex,
                                              uint64_t dbase, uint32_t slot) {
     if (p.rng_mode == AG_RNG_PHILOX) return philox_u32(p.seed, hop, vertex, slot);
     return (uint32_t)wyrand_at(p.seed, dbase + slot);  // next_u32: genstamp.rs:199-201
 }
 
-__device__ __forceinline__ void emit_edge(const SampleParams &p, const StageInfo &si,
+// Edge t of vertex fe at hop `hop` (= item fe.ebase + t of stage hop + 1).
+__device__ __forceinline__ void emit_edge(const SampleParams &p, uint32_t hop, uint32_t edges_before,
                                           const FrontierEntry &fe, uint32_t t, uint64_t pos) {
     const uint32_t e_rel = fe.ebase + t;
-    const uint64_t e = (uint64_t)si.n_edges + e_rel;
-    if (e >= p.cap_edges) { atomicOr(&p.state->error, kErrCapacity); return; }
+    const uint64_t e = (uint64_t)edges_before + e_rel;
+    if (e >= p.cap_edges || e_rel >= kMaxPos) { atomicOr(&p.state->error, kErrCapacity); return; }
     const uint32_t d = ld_stream_u32(p.dst + pos);
     if (p.edge_src) p.edge_src[e] = fe.id;
     p.edge_dst[e] = d;
@@ -278,100 +147,96 @@ __device__ __forceinline__ void emit_edge(const SampleParams &p, const StageInfo
         p.slot_of_edge[e] = 0xFFFFFFFFu;
         return;
     }
-    p.slot_of_edge[e] = table_insert_min(p.table, d, kPending | e_rel, &p.state->error);
+    p.slot_of_edge[e] = table_insert_min(p.table, d, enc_pending(p.table.gen, hop + 1, e_rel), &p.state->error);
 }
 
-// Fanout <= G <= 32: G lanes per frontier vertex, lane t owns edge slot t.
-// The frontier of hop h was written by stage h into frontier[h & 1].
+__device__ __forceinline__ bool key_less(double ka, uint32_t pa, double kb, uint32_t pb) {
+    return ka < kb || (ka == kb && pa < pb);
+}
+
+// Fanout <= G <= 32: G lanes per vertex, lane t owns edge slot t.
 template <int G>
-__global__ void __launch_bounds__(kPickThreads)
-k_pick_small(const SampleParams *__restrict__ pa, uint32_t hop, uint32_t k) {
-    const SampleParams &p = pa[blockIdx.y];
-    const uint32_t stage = hop + 1;
-    const StageInfo si = p.state->stage[stage];
+__device__ __forceinline__ void pick_small(const SampleParams &p, uint32_t hop, uint32_t k, uint32_t edges_before,
+                                           const FrontierEntry *fes, uint32_t n) {
     const uint32_t t = threadIdx.x % G;
-    // Grid-stride over the frontier (the grid is sized for a typical batch); a
-    // warp leaves the loop together, when its first vertex is past the frontier.
-    for (uint32_t node = (blockIdx.x * kPickThreads + threadIdx.x) / G; (node & ~(32u / G - 1u)) < si.frontier_n;
-         node += gridDim.x * (kPickThreads / G)) {
-    const bool active = node < si.frontier_n;
-    FrontierEntry fe{};
-    if (active) fe = p.frontier[hop & 1][node];
-    const uint32_t deg = fe.deg;
-    const bool sampled = active && p.mode != kModeReplace && deg > k;  // Floyd row
-    uint32_t pick = t;                                                  // take-all: row order
-    uint32_t ip = 0;
-    if (active && p.mode == kModeReplace && deg > 0 && t < k) {
-        // sampler.rs:1298-1300: k independent draws over the whole row
-        pick = (uint32_t)(((uint64_t)draw_u32(p, hop, fe.id, fe.dbase, t) * deg) >> 32);
-    } else if (sampled && t < k) {
-        // sampler.rs:1345-1346: i runs over deg-k .. deg-1, j = rand_below(i + 1)
-        ip = deg - k + t;
-        pick = (uint32_t)(((uint64_t)draw_u32(p, hop, fe.id, fe.dbase, t) * ((uint64_t)ip + 1)) >> 32);
-    }
-    // Floyd's "already taken?" is sequential in t (sampler.rs:1347-1352):
-    // resolve slot s against the finished slots below it, one ballot per s.
     const uint32_t gshift = (threadIdx.x & 31) & ~(G - 1);
     const uint32_t gmask = (G == 32) ? 0xffffffffu : ((1u << G) - 1u);
-    if (__any_sync(0xffffffffu, sampled)) {
-        for (uint32_t s = 1; s < k; ++s) {
-            const uint32_t js = __shfl_sync(0xffffffffu, pick, s, G);
-            const bool hit = sampled && t < s && pick == js;
-            const uint32_t m = (__ballot_sync(0xffffffffu, hit) >> gshift) & gmask;
-            if (sampled && t == s && m) pick = ip;
+    for (uint32_t base = 0; base < n; base += kTile / G) {
+        const uint32_t j = base + threadIdx.x / G;
+        const bool active = j < n;
+        FrontierEntry fe{};
+        if (active) fe = fes[j];
+        const uint32_t deg = fe.deg;
+        const bool sampled = active && p.mode != kModeReplace && deg > k;  // Floyd row
+        uint32_t pick = t;                                                  // take-all: row order
+        uint32_t ip = 0;
+        if (active && p.mode == kModeReplace && deg > 0 && t < k) {
+            // sampler.rs:1298-1300: k independent draws over the whole row
+            pick = (uint32_t)(((uint64_t)draw_u32(p, hop, fe.id, fe.dbase, t) * deg) >> 32);
+        } else if (sampled && t < k) {
+            // sampler.rs:1345-1346: i runs over deg-k .. deg-1, j = rand_below(i + 1)
+            ip = deg - k + t;
+            pick = (uint32_t)(((uint64_t)draw_u32(p, hop, fe.id, fe.dbase, t) * ((uint64_t)ip + 1)) >> 32);
+        }
+        // Floyd's "already taken?" is sequential in t (sampler.rs:1347-1352):
+        // resolve slot s against the finished slots below it, one ballot per s.
+        if (__any_sync(0xffffffffu, sampled)) {
+            for (uint32_t s = 1; s < k; ++s) {
+                const uint32_t js = __shfl_sync(0xffffffffu, pick, s, G);
+                const bool hit = sampled && t < s && pick == js;
+                const uint32_t m = (__ballot_sync(0xffffffffu, hit) >> gshift) & gmask;
+                if (sampled && t == s && m) pick = ip;
+            }
+        }
+        if (active) {
+            uint32_t take;
+            uint64_t draws;
+            row_demand(p.mode, deg, k, take, draws);
+            if (t < take) emit_edge(p, hop, edges_before, fe, t, fe.off + pick);
         }
     }
-    if (active) {
+}
+
+// Fanout > 32: one warp per vertex (the first four warps of the tile); finished
+// picks live in shared memory so later slots can be checked against all earlier ones.
+__device__ __forceinline__ void pick_large(const SampleParams &p, uint32_t hop, uint32_t k, uint32_t edges_before,
+                                           const FrontierEntry *fes, uint32_t n, uint32_t (*s_picks)[kLargeK]) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (warp >= 4) return;
+    uint32_t *picks = s_picks[warp];
+    for (uint32_t j = warp; j < n; j += 4) {
+        const FrontierEntry fe = fes[j];
+        const uint32_t deg = fe.deg;
         uint32_t take;
         uint64_t draws;
         row_demand(p.mode, deg, k, take, draws);
-        if (t < take) emit_edge(p, si, fe, t, fe.off + pick);
-    }
-    }  // next vertex
-}
-
-// Fanout > 32: one warp per frontier vertex; finished picks live in shared
-// memory so later slots can be checked against all earlier ones.
-__global__ void __launch_bounds__(128)
-k_pick_large(const SampleParams *__restrict__ pa, uint32_t hop, uint32_t k) {
-    __shared__ uint32_t s_picks[4][kLargeK];
-    const SampleParams &p = pa[blockIdx.y];
-    const StageInfo si = p.state->stage[hop + 1];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    uint32_t *picks = s_picks[warp];
-    for (uint32_t node = blockIdx.x * 4 + warp; node < si.frontier_n; node += gridDim.x * 4) {
-    const FrontierEntry fe = p.frontier[hop & 1][node];
-    const uint32_t deg = fe.deg;
-    uint32_t take;
-    uint64_t draws;
-    row_demand(p.mode, deg, k, take, draws);
-    const bool sampled = p.mode != kModeReplace && deg > k;
-    __syncwarp();
-    for (uint32_t c = 0; c < take; c += 32) {
-        const uint32_t t = c + lane;
-        const bool in = t < take;
-        uint32_t pick = t, ip = 0;
-        bool hit_prev = false;
-        if (in && p.mode == kModeReplace) {
-            pick = (uint32_t)(((uint64_t)draw_u32(p, hop, fe.id, fe.dbase, t) * deg) >> 32);
-        } else if (in && sampled) {
-            ip = deg - k + t;
-            pick = (uint32_t)(((uint64_t)draw_u32(p, hop, fe.id, fe.dbase, t) * ((uint64_t)ip + 1)) >> 32);
-            for (uint32_t q = 0; q < c; ++q) hit_prev |= (picks[q] == pick);
-        }
-        if (sampled) {
-            for (uint32_t s = 0; s < 32; ++s) {
-                const uint32_t js = __shfl_sync(0xffffffffu, pick, s);
-                const bool hit = in && (uint32_t)lane < s && pick == js;
-                const uint32_t m = __ballot_sync(0xffffffffu, hit);
-                if (in && (uint32_t)lane == s && (m || hit_prev)) pick = ip;
+        const bool sampled = p.mode != kModeReplace && deg > k;
+        __syncwarp();
+        for (uint32_t c = 0; c < take; c += 32) {
+            const uint32_t t = c + lane;
+            const bool in = t < take;
+            uint32_t pick = t, ip = 0;
+            bool hit_prev = false;
+            if (in && p.mode == kModeReplace) {
+                pick = (uint32_t)(((uint64_t)draw_u32(p, hop, fe.id, fe.dbase, t) * deg) >> 32);
+            } else if (in && sampled) {
+                ip = deg - k + t;
+                pick = (uint32_t)(((uint64_t)draw_u32(p, hop, fe.id, fe.dbase, t) * ((uint64_t)ip + 1)) >> 32);
+                for (uint32_t q = 0; q < c; ++q) hit_prev |= (picks[q] == pick);
             }
-            if (in) picks[t] = pick;
-            __syncwarp();
+            if (sampled) {
+                for (uint32_t s = 0; s < 32; ++s) {
+                    const uint32_t js = __shfl_sync(0xffffffffu, pick, s);
+                    const bool hit = in && (uint32_t)lane < s && pick == js;
+                    const uint32_t m = __ballot_sync(0xffffffffu, hit);
+                    if (in && (uint32_t)lane == s && (m || hit_prev)) pick = ip;
+                }
+                if (in) picks[t] = pick;
+                __syncwarp();
+            }
+            if (in) emit_edge(p, hop, edges_before, fe, t, fe.off + pick);
         }
-        if (in) emit_edge(p, si, fe, t, fe.off + pick);
     }
-    }  // next vertex
 }
 
 // Weighted sampling without replacement, fanout <= 32, one warp per vertex.
@@ -382,64 +247,182 @@ k_pick_large(const SampleParams *__restrict__ pa, uint32_t hop, uint32_t k) {
 // order; the reference's own order comes from Rust's select_nth_unstable_by and
 // is not defined by its source tree.  The warp streams the row 32 positions at a
 // time and keeps the k best so far sorted across its lanes.
-__device__ __forceinline__ bool key_less(double ka, uint32_t pa, double kb, uint32_t pb) {
-    return ka < kb || (ka == kb && pa < pb);
-}
-
-__global__ void __launch_bounds__(kPickThreads)
-k_pick_weighted(const SampleParams *__restrict__ pa, uint32_t hop, uint32_t k) {
-    const SampleParams &p = pa[blockIdx.y];
-    const StageInfo si = p.state->stage[hop + 1];
-    const int lane = threadIdx.x & 31;
+__device__ __forceinline__ void pick_weighted(const SampleParams &p, uint32_t hop, uint32_t k, uint32_t edges_before,
+                                              const FrontierEntry *fes, uint32_t n) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (k == 0) return;
     const double inf = __longlong_as_double(0x7FF0000000000000ll);
-    for (uint32_t node = (blockIdx.x * kPickThreads + threadIdx.x) >> 5; node < si.frontier_n;
-         node += gridDim.x * (kPickThreads / 32)) {
-    const FrontierEntry fe = p.frontier[hop & 1][node];
-    const uint32_t deg = fe.deg;
-    if (deg == 0) continue;
-    if (k >= deg) {
-        for (uint32_t t = lane; t < deg; t += 32) emit_edge(p, si, fe, t, fe.off + t);
-        continue;
-    }
-    double best_key = inf;
-    uint32_t best_pos = 0xFFFFFFFFu;  // sentinel: sorts after every real (key, position)
-    for (uint32_t c = 0; c < deg; c += 32) {
-        const uint32_t pos = c + lane;
-        double key = inf;
-        uint32_t cpos = 0xFFFFFFFFu;
-        if (pos < deg) {
-            const uint64_t bits = (p.rng_mode == AG_RNG_PHILOX)
-                ? (((uint64_t)philox_u32(p.seed, hop, fe.id, 2 * pos) << 32) | philox_u32(p.seed, hop, fe.id, 2 * pos + 1))
-                : wyrand_at(p.seed, fe.dbase + pos);
-            const double w = (double)__ldg(p.weights + fe.off + pos);
-            if (isfinite(w) && w > 0.0) {
-                const double u = ((double)(bits >> 11) + 1.0) * (1.0 / 9007199254740992.0);
-                key = -log(u) / w;
+    for (uint32_t j = warp; j < n; j += kTile / 32) {
+        const FrontierEntry fe = fes[j];
+        const uint32_t deg = fe.deg;
+        if (deg == 0) continue;
+        if (k >= deg) {
+            for (uint32_t t = lane; t < deg; t += 32) emit_edge(p, hop, edges_before, fe, t, fe.off + t);
+            continue;
+        }
+        double best_key = inf;
+        uint32_t best_pos = 0xFFFFFFFFu;  // sentinel: sorts after every real (key, position)
+        for (uint32_t c = 0; c < deg; c += 32) {
+            const uint32_t pos = c + lane;
+            double key = inf;
+            uint32_t cpos = 0xFFFFFFFFu;
+            if (pos < deg) {
+                const uint64_t bits = (p.rng_mode == AG_RNG_PHILOX)
+                    ? (((uint64_t)philox_u32(p.seed, hop, fe.id, 2 * pos) << 32) | philox_u32(p.seed, hop, fe.id, 2 * pos + 1))
+                    : wyrand_at(p.seed, fe.dbase + pos);
+                const double w = (double)__ldg(p.weights + fe.off + pos);
+                if (isfinite(w) && w > 0.0) {
+                    const double u = ((double)(bits >> 11) + 1.0) * (1.0 / 9007199254740992.0);
+                    key = -log(u) / w;
+                }
+                cpos = pos;
             }
-            cpos = pos;
+            for (;;) {
+                const double tk = __shfl_sync(0xffffffffu, best_key, k - 1);
+                const uint32_t tp = __shfl_sync(0xffffffffu, best_pos, k - 1);
+                const uint32_t m = __ballot_sync(0xffffffffu, cpos != 0xFFFFFFFFu && key_less(key, cpos, tk, tp));
+                if (!m) break;
+                const int src = __ffs(m) - 1;
+                const double ck = __shfl_sync(0xffffffffu, key, src);
+                const uint32_t cp = __shfl_sync(0xffffffffu, cpos, src);
+                // Insert (ck, cp) into the sorted lanes: it lands after every entry
+                // that is smaller, the rest shift up by one.
+                const uint32_t smaller = __ballot_sync(0xffffffffu, key_less(best_key, best_pos, ck, cp));
+                const int at = __popc(smaller);
+                const double up_k = __shfl_up_sync(0xffffffffu, best_key, 1);
+                const uint32_t up_p = __shfl_up_sync(0xffffffffu, best_pos, 1);
+                if (lane == at) { best_key = ck; best_pos = cp; }
+                else if (lane > at) { best_key = up_k; best_pos = up_p; }
+                if (lane == src) cpos = 0xFFFFFFFFu;
+            }
         }
-        for (;;) {
-            const double tk = __shfl_sync(0xffffffffu, best_key, k - 1);
-            const uint32_t tp = __shfl_sync(0xffffffffu, best_pos, k - 1);
-            const uint32_t m = __ballot_sync(0xffffffffu, cpos != 0xFFFFFFFFu && key_less(key, cpos, tk, tp));
-            if (!m) break;
-            const int src = __ffs(m) - 1;
-            const double ck = __shfl_sync(0xffffffffu, key, src);
-            const uint32_t cp = __shfl_sync(0xffffffffu, cpos, src);
-            // Insert (ck, cp) into the sorted lanes: it lands after every entry
-            // that is smaller, the rest shift up by one.
-            const uint32_t smaller = __ballot_sync(0xffffffffu, key_less(best_key, best_pos, ck, cp));
-            const int at = __popc(smaller);
-            const double up_k = __shfl_up_sync(0xffffffffu, best_key, 1);
-            const uint32_t up_p = __shfl_up_sync(0xffffffffu, best_pos, 1);
-            if (lane == at) { best_key = ck; best_pos = cp; }
-            else if (lane > at) { best_key = up_k; best_pos = up_p; }
-            if (lane == src) cpos = 0xFFFFFFFFu;
-        }
+        if ((uint32_t)lane < k) emit_edge(p, hop, edges_before, fe, lane, fe.off + best_pos);
     }
-    if ((uint32_t)lane < k) emit_edge(p, si, fe, lane, fe.off + best_pos);
-    }  // next vertex
+}
+
+// One stage: assign local ids to the first sightings among the stage's items,
+// then (has_next) expand the new vertices at hop `stage` with fanout k.
+template <int G, int PICK>
+__global__ void __launch_bounds__(kTile)
+k_expand(const SampleParams *__restrict__ pa, uint32_t stage, uint32_t k, int has_next) {
+    __shared__ uint32_t s_tile;
+    __shared__ ScanVal s_warp[kTile / 32];
+    __shared__ ScanVal s_prefix, s_total;
+    __shared__ FrontierEntry s_fe[kTile];
+    __shared__ uint32_t s_picks[PICK == kPickLarge ? 4 : 1][PICK == kPickLarge ? kLargeK : 1];
+
+    const SampleParams &p = pa[blockIdx.y];
+    BatchState *bs = p.state;
+    StageInfo si = bs->stage[stage];
+    if (stage == 0) {
+        // A reseeded batch restarts its stream at draw 0; otherwise the handle's
+        // stream continues where its previous batch stopped.
+        si = StageInfo{};
+        si.draws = p.reset_pos ? 0ull : bs->stream_pos;
+    }
+    const uint32_t count = (stage == 0) ? p.n_seeds : si.hop_edges;
+    const uint32_t n_tiles = max(1u, (count + kTile - 1) / kTile);
+    const uint32_t edges_before_next = si.n_edges + ((stage == 0) ? 0u : count);  // where hop `stage` starts
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t gen = p.table.gen;
+
+    // The grid is sized for a typical batch, not for the worst case: a block
+    // keeps drawing tile tickets until they run out.  Tickets are handed out in
+    // order, so the tiles a look-back waits for are always already running.
+    for (;;) {
+        __syncthreads();
+        if (threadIdx.x == 0) s_tile = atomicAdd(&bs->ticket, 1u);
+        __syncthreads();
+        const uint32_t tile = s_tile;
+        if (tile >= n_tiles) {
+            // n_tiles + gridDim.x tickets are drawn in all; the last one resets the counter.
+            if (threadIdx.x == 0 && tile == n_tiles + gridDim.x - 1) bs->ticket = 0;
+            return;
+        }
+        const uint32_t item = tile * kTile + threadIdx.x;
+
+        // First sighting?  The table holds the pending mark of the smallest
+        // position that named the vertex.
+        uint32_t slot = 0xFFFFFFFFu, id = 0;
+        bool first = false;
+        if (item < count) {
+            slot = (stage == 0) ? p.slot_of_seed[item] : p.slot_of_edge[si.n_edges + item];
+            if (slot != 0xFFFFFFFFu) {
+                const uint64_t cur = __ldcg((const unsigned long long *)&p.table.slots[slot]);
+                first = ((uint32_t)cur == enc_pending(gen, stage, item));
+                id = (uint32_t)(cur >> 32);
+            }
+        }
+        ScanVal v{first ? 1u : 0u, 0u, 0ull};
+        uint64_t off = 0, deg = 0;
+        if (first && has_next) {
+            row_bounds(p.offsets, p.num_nodes, p.num_edges, id, off, deg);
+            if (deg > 0xFFFFFFFFull) { atomicOr(&bs->error, kErrCapacity); deg = 0; }
+            row_demand(p.mode, deg, k, v.take, v.draws);
+        }
+
+        // Block scan: warp scans, then the warp totals.
+        const ScanVal incl = warp_inclusive_scan(v, lane);
+        if (lane == 31) s_warp[warp] = incl;
+        __syncthreads();
+        if (warp == 0) {
+            ScanVal w = (lane < kTile / 32) ? s_warp[lane] : ScanVal{0, 0, 0};
+            const ScanVal wi = warp_inclusive_scan(w, lane);
+            const ScanVal block_total = ScanVal{__shfl_sync(0xffffffffu, wi.flags, 31),
+                                                __shfl_sync(0xffffffffu, wi.take, 31),
+                                                __shfl_sync(0xffffffffu, wi.draws, 31)};
+            if (lane < kTile / 32) s_warp[lane] = ScanVal{wi.flags - w.flags, wi.take - w.take, wi.draws - w.draws};
+            const ScanVal prefix = lookback_exclusive(p.tiles, tile, p.epoch_base + stage, block_total, lane, &bs->error);
+            if (lane == 0) {
+                s_prefix = prefix;
+                s_total = block_total;
+                if (tile == n_tiles - 1) {
+                    // Totals of the stage: hand over to the next one.
+                    const ScanVal tot = prefix + block_total;
+                    StageInfo nx;
+                    nx.n_nodes = si.n_nodes + tot.flags;
+                    nx.n_edges = edges_before_next;
+                    nx.frontier_n = tot.flags;
+                    nx.hop_edges = tot.take;
+                    nx.draws = si.draws + tot.draws;
+                    nx.hop_draws = 0;
+                    bs->stage[stage + 1] = nx;
+                    bs->nodes_per_stage[stage] = tot.flags;
+                    if (stage == 0) bs->stage[0] = si;  // what finalize measures the draws against
+                }
+            }
+        }
+        __syncthreads();
+        if (first) {
+            const ScanVal base = s_prefix + s_warp[warp];
+            const ScanVal excl = ScanVal{base.flags + incl.flags - v.flags, base.take + incl.take - v.take,
+                                         base.draws + incl.draws - v.draws};
+            const uint32_t local = si.n_nodes + excl.flags;
+            if ((uint64_t)local >= p.cap_nodes || (uint64_t)local >= kMaxPos) {
+                atomicOr(&bs->error, kErrCapacity);
+                if (has_next) s_fe[excl.flags - s_prefix.flags] = FrontierEntry{};  // deg 0: expands to nothing
+            } else {
+                p.nodes[local] = id;
+                p.table.slots[slot] = ((uint64_t)id << 32) | enc_final(gen, local);  // readers accept either form
+                if (has_next) {
+                    FrontierEntry fe;
+                    fe.off = off;
+                    fe.dbase = si.draws + excl.draws;
+                    fe.id = id;
+                    fe.local = local;
+                    fe.deg = (uint32_t)deg;
+                    fe.ebase = excl.take;
+                    s_fe[excl.flags - s_prefix.flags] = fe;
+                }
+            }
+        }
+        if (!has_next) continue;
+        __syncthreads();
+        const uint32_t n_new = s_total.flags;
+        if (PICK == kPickWeighted) pick_weighted(p, stage, k, edges_before_next, s_fe, n_new);
+        else if (PICK == kPickLarge) pick_large(p, stage, k, edges_before_next, s_fe, n_new, s_picks);
+        else pick_small<G>(p, stage, k, edges_before_next, s_fe, n_new);
+    }
 }
 
 // --------------------------------------------------------------- finalize --
@@ -454,7 +437,7 @@ __global__ void k_finalize(const SampleParams *__restrict__ pa) {
     for (uint64_t e = tid; e < n_edges; e += stride) {
         const uint32_t slot = p.slot_of_edge[e];
         const uint32_t dl = (slot == 0xFFFFFFFFu) ? 0xFFFFFFFFu
-                          : (uint32_t)__ldcg((const unsigned long long *)&p.table.slots[slot]);
+                          : ((uint32_t)__ldcg((const unsigned long long *)&p.table.slots[slot]) & kPosMask);
         p.dst_local[e] = dl;
         if (p.edge_index_local) {
             p.edge_index_local[e] = (int64_t)dl;                                   // row 0: sampled neighbor
@@ -465,7 +448,7 @@ __global__ void k_finalize(const SampleParams *__restrict__ pa) {
     for (uint64_t i = tid; i < p.n_seeds; i += stride) {
         const uint32_t slot = p.slot_of_seed[i];
         const uint32_t sl = (slot == 0xFFFFFFFFu) ? 0xFFFFFFFFu
-                          : (uint32_t)__ldcg((const unsigned long long *)&p.table.slots[slot]);
+                          : ((uint32_t)__ldcg((const unsigned long long *)&p.table.slots[slot]) & kPosMask);
         p.seed_locals[i] = sl;
         if (p.seed_index) p.seed_index[i] = (int64_t)sl;
     }
@@ -484,8 +467,8 @@ __global__ void k_finalize(const SampleParams *__restrict__ pa) {
         if ((uint64_t)fin.n_nodes > p.cap_nodes || (uint64_t)fin.n_edges > p.cap_edges) c.error |= kErrCapacity;
         *p.counts = c;
         bs->stream_pos = fin.draws;  // a bare sampler keeps consuming the same stream
-        bs->prev_edges = n_edges;    // what the next batch's k_begin has to wipe from the table
-        bs->prev_seeds = p.n_seeds;
+        bs->error = 0;               // ready for the handle's next batch
+        bs->ticket = 0;
     }
 }
 
@@ -493,6 +476,18 @@ uint64_t next_pow2(uint64_t v) {
     uint64_t p = 1;
     while (p < v) p <<= 1;
     return p;
+}
+
+template <int PICK>
+void launch_expand(uint32_t G, dim3 grid, cudaStream_t st, const SampleParams *pa, uint32_t stage, uint32_t k,
+                   int has_next) {
+    if (PICK != kPickSmall) { k_expand<32, PICK><<<grid, kTile, 0, st>>>(pa, stage, k, has_next); return; }
+    switch (G) {
+        case 4: k_expand<4, kPickSmall><<<grid, kTile, 0, st>>>(pa, stage, k, has_next); break;
+        case 8: k_expand<8, kPickSmall><<<grid, kTile, 0, st>>>(pa, stage, k, has_next); break;
+        case 16: k_expand<16, kPickSmall><<<grid, kTile, 0, st>>>(pa, stage, k, has_next); break;
+        default: k_expand<32, kPickSmall><<<grid, kTile, 0, st>>>(pa, stage, k, has_next); break;
+    }
 }
 
 }  // namespace
@@ -508,13 +503,13 @@ struct ag_sampler {
     uint64_t seed = 0;
     bool reset_pos = true;
     uint32_t epoch = 0;
+    uint32_t gen = 0;    // table generation of the next launch
     uint32_t group = 1;  // batches one launch chain can carry
     // sizing (per batch)
-    uint64_t cap_seeds = 0, max_nodes = 0, max_edges = 0, max_frontier = 0, max_hop_edges = 0;
+    uint64_t cap_seeds = 0, max_nodes = 0, max_edges = 0, max_hop_edges = 0;
     uint64_t table_cap = 0, n_tiles = 0;
     // scratch (device), each `group` times the per-batch size
     uint64_t *table = nullptr;
-    FrontierEntry *frontier[2] = {nullptr, nullptr};
     uint32_t *slot_of_seed = nullptr, *slot_of_edge = nullptr;
     TileDesc *tiles = nullptr;
     BatchState *state = nullptr;
@@ -540,29 +535,27 @@ struct ag_sampler {
 namespace {
 
 void compute_bounds(const ag_sampler *s, uint64_t n_seeds, uint64_t *max_nodes, uint64_t *max_edges,
-                    uint64_t *max_frontier, uint64_t *max_hop_edges) {
+                    uint64_t *max_hop_edges) {
     const uint64_t N = s->g->num_nodes;
-    uint64_t f = std::min<uint64_t>(n_seeds, N), nodes = f, edges = 0, mf = f, mhe = 0;
+    uint64_t f = std::min<uint64_t>(n_seeds, N), nodes = f, edges = 0, mhe = 0;
     for (uint32_t h = 0; h < s->cfg.num_hops; ++h) {
         const uint64_t e = f * s->cfg.fanout[h];
         edges += e;
         mhe = std::max(mhe, e);
         f = std::min<uint64_t>(e, N);
-        if (h + 1 < s->cfg.num_hops) mf = std::max(mf, f);
         nodes += f;
     }
     if (max_nodes) *max_nodes = std::min<uint64_t>(nodes, N);
     if (max_edges) *max_edges = edges;
-    if (max_frontier) *max_frontier = mf;
     if (max_hop_edges) *max_hop_edges = mhe;
 }
 
 void free_scratch(ag_sampler *s) {
-    cudaFree(s->table); cudaFree(s->frontier[0]); cudaFree(s->frontier[1]);
+    cudaFree(s->table);
     cudaFree(s->slot_of_seed); cudaFree(s->slot_of_edge); cudaFree(s->tiles);
     cudaFree(s->seeds_dev);
     if (s->seeds_pinned) cudaFreeHost(s->seeds_pinned);
-    s->table = nullptr; s->frontier[0] = s->frontier[1] = nullptr;
+    s->table = nullptr;
     s->slot_of_seed = s->slot_of_edge = nullptr; s->tiles = nullptr;
     s->seeds_dev = nullptr; s->seeds_pinned = nullptr;
 }
@@ -572,19 +565,18 @@ int32_t ensure_scratch(ag_sampler *s, uint64_t n_seeds) {
     if (n_seeds <= s->cap_seeds && s->table) return AG_OK;
     if (s->in_flight) { AG_CUDA(cudaEventSynchronize(s->done)); }
     free_scratch(s);
+    s->cap_seeds = 0;
     const uint64_t cap = std::max<uint64_t>(n_seeds, 1), G = s->group;
-    compute_bounds(s, cap, &s->max_nodes, &s->max_edges, &s->max_frontier, &s->max_hop_edges);
-    if (s->max_nodes >= 0x7FFFFFFFull || s->max_hop_edges >= 0x7FFFFFFFull || s->max_edges >= 0xFFFFFFFFull)
-        return fail(AG_ERR_VALUE, "batch too large: %llu seeds with this fanout can emit %llu edges "
-                    "(limit 2^31 per hop)", (unsigned long long)n_seeds, (unsigned long long)s->max_edges);
+    compute_bounds(s, cap, &s->max_nodes, &s->max_edges, &s->max_hop_edges);
+    if (s->max_nodes >= kMaxPos || s->max_hop_edges >= kMaxPos || cap >= kMaxPos || s->max_edges >= 0xFFFFFFFFull)
+        return fail(AG_ERR_VALUE, "batch too large: %llu seeds with this fanout can reach %llu nodes and %llu edges "
+                    "in a hop (limit %llu each)", (unsigned long long)n_seeds, (unsigned long long)s->max_nodes,
+                    (unsigned long long)s->max_hop_edges, (unsigned long long)kMaxPos - 1);
     s->table_cap = std::max<uint64_t>(1024, next_pow2(2 * s->max_nodes));
     AG_CUDA(cudaMalloc(&s->table, G * s->table_cap * 8));
-    const uint64_t fcap = std::max<uint64_t>(s->max_frontier, 1);
-    AG_CUDA(cudaMalloc(&s->frontier[0], G * fcap * sizeof(FrontierEntry)));
-    AG_CUDA(cudaMalloc(&s->frontier[1], G * fcap * sizeof(FrontierEntry)));
     AG_CUDA(cudaMalloc(&s->slot_of_seed, G * cap * 4));
     AG_CUDA(cudaMalloc(&s->slot_of_edge, G * std::max<uint64_t>(s->max_edges, 1) * 4));
-    s->n_tiles = std::max<uint64_t>(std::max(cap, s->max_hop_edges) / kAssignThreads + 2, 2);
+    s->n_tiles = std::max<uint64_t>(std::max(cap, s->max_hop_edges) / kTile + 2, 2);
     AG_CUDA(cudaMalloc(&s->tiles, G * s->n_tiles * sizeof(TileDesc)));
     AG_CUDA(cudaMemset(s->tiles, 0, G * s->n_tiles * sizeof(TileDesc)));
     AG_CUDA(cudaMalloc(&s->seeds_dev, G * cap * 4));
@@ -684,7 +676,7 @@ extern "C" int32_t ag_sampler_set_profiling(ag_sampler *s, int32_t on) {
 
 extern "C" int32_t ag_sampler_bounds(const ag_sampler *s, uint64_t n_seeds, uint64_t *max_nodes, uint64_t *max_edges) {
     if (!s) return fail(AG_ERR_VALUE, "ag_sampler_bounds: null sampler");
-    compute_bounds(s, n_seeds, max_nodes, max_edges, nullptr, nullptr);
+    compute_bounds(s, n_seeds, max_nodes, max_edges, nullptr);
     return AG_OK;
 }
 
@@ -708,7 +700,7 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
             return fail(AG_ERR_VALUE, "nodes, edge_dst, src_local, dst_local and seed_locals buffers are required");
         if (B.cap_seeds < n_seeds[b]) return fail(AG_ERR_VALUE, "seed_locals capacity %llu < %llu seeds",
                                                   (unsigned long long)B.cap_seeds, (unsigned long long)n_seeds[b]);
-        if (n_seeds[b] >= 0x7FFFFFFFull) return fail(AG_ERR_VALUE, "too many seeds");
+        if (n_seeds[b] >= kMaxPos) return fail(AG_ERR_VALUE, "too many seeds");
         max_n = std::max(max_n, n_seeds[b]);
         want_x = want_x || (feats && B.x);
         // Seeds::new (sampler.rs:230-239): name the first id at or past num_nodes.
@@ -726,10 +718,14 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
     if (s->in_flight) { AG_CUDA(cudaEventSynchronize(s->done)); s->in_flight = false; }
     AG_TRY(ensure_scratch(s, max_n));
     if (s->profile) AG_CUDA(cudaEventRecord(s->ev[0], st));
-    if (s->dirty) {
-        // First use (or after a failed batch): the whole table starts empty.  From
-        // here on each batch wipes exactly the slots its predecessor touched.
+    if (s->dirty || s->gen >= kGens) {
+        // Every slot free again.  A launch marks its entries with its generation,
+        // so this real clear is only needed once the generations have cycled (or
+        // after a failed launch left the table in an unknown state).
         AG_CUDA(cudaMemsetAsync(s->table, 0xFF, (uint64_t)s->group * s->table_cap * 8, st));
+        s->gen = 0;
+    }
+    if (s->dirty) {
         AG_CUDA(cudaMemsetAsync(s->state, 0, s->group * sizeof(BatchState), st));
         s->dirty = false;
         s->reset_pos = true;
@@ -741,7 +737,7 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
     }
     uint32_t log2cap = 0;
     while ((1ull << log2cap) < s->table_cap) ++log2cap;
-    const uint64_t fcap = std::max<uint64_t>(s->max_frontier, 1), ecap = std::max<uint64_t>(s->max_edges, 1);
+    const uint64_t ecap = std::max<uint64_t>(s->max_edges, 1);
 
     uint64_t b_nodes = 0, b_edges = 0;
     for (uint32_t b = 0; b < n_batches; ++b) {
@@ -750,7 +746,7 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
         SampleParams p{};
         p.offsets = g->offsets; p.dst = g->dst; p.weights = g->weights;
         p.num_nodes = g->num_nodes; p.num_edges = g->num_edges;
-        p.table = DedupTable{s->table + (uint64_t)b * s->table_cap, (uint32_t)(s->table_cap - 1), 32u - log2cap};
+        p.table = DedupTable{s->table + (uint64_t)b * s->table_cap, (uint32_t)(s->table_cap - 1), 32u - log2cap, s->gen};
         p.state = s->state + b;
         p.tiles = s->tiles + (uint64_t)b * s->n_tiles;
         p.epoch_base = s->epoch + 1;
@@ -764,6 +760,7 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
         p.seed = batch_seeds ? batch_seeds[b] : s->seed;
         p.rng_mode = s->cfg.rng_mode; p.mode = s->mode;
         p.reset_pos = (batch_seeds || s->reset_pos) ? 1 : 0;
+        p.num_hops = H;
         p.nodes = B.nodes; p.edge_src = B.edge_src; p.edge_dst = B.edge_dst;
         p.src_local = B.src_local; p.dst_local = B.dst_local; p.seed_locals = B.seed_locals;
         p.edge_ids = s->cfg.track_edge_ids ? B.edge_ids : nullptr;
@@ -772,13 +769,9 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
         p.counts = s->counts_dev + b;
         p.slot_of_seed = s->slot_of_seed + (uint64_t)b * s->cap_seeds;
         p.slot_of_edge = s->slot_of_edge + (uint64_t)b * ecap;
-        p.frontier[0] = s->frontier[0] + (uint64_t)b * fcap;
-        p.frontier[1] = s->frontier[1] + (uint64_t)b * fcap;
-        p.frontier_cap = fcap;
-        p.num_hops = H;
         s->params_host[b] = p;
         uint64_t bn, be;
-        compute_bounds(s, n, &bn, &be, nullptr, nullptr);
+        compute_bounds(s, n, &bn, &be, nullptr);
         b_nodes = std::max(b_nodes, bn); b_edges = std::max(b_edges, be);
         if (want_x) {
             GatherArgs ga{};
@@ -787,7 +780,8 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
                 ga.row_bytes = (uint32_t)(feats->dim * elem_size(feats->dtype)); ga.dim = (uint32_t)feats->dim;
                 ga.ids = B.nodes; ga.ids64 = 0;
                 ga.n = std::min<uint64_t>(bn, B.cap_nodes);
-                ga.n_dev = &s->counts_dev[b].num_nodes;
+                // rows to gather = nodes registered by the last stage (read on the device)
+                ga.n_dev = &s->state[b].stage[H + 1].n_nodes;
                 ga.out = B.x; ga.err = feats->err;
             }
             s->gather_host[b] = ga;
@@ -795,56 +789,32 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
     }
     s->reset_pos = false;
     s->epoch += H + 2;
+    s->gen += 1;
     if (seeds_mem == AG_MEM_HOST)
         AG_CUDA(cudaMemcpyAsync(s->seeds_dev, s->seeds_pinned, (uint64_t)n_batches * s->cap_seeds * 4, cudaMemcpyHostToDevice, st));
     AG_CUDA(cudaMemcpyAsync(s->params_dev, s->params_host, n_batches * sizeof(SampleParams), cudaMemcpyHostToDevice, st));
+    if (want_x)
+        AG_CUDA(cudaMemcpyAsync(s->gather_dev, s->gather_host, n_batches * sizeof(GatherArgs), cudaMemcpyHostToDevice, st));
 
     const SampleParams *pa = s->params_dev;
     const uint32_t nmax = (uint32_t)max_n;
     // Grids cover the worst case only up to about two waves of resident blocks
-    // over the whole group; the kernels stride (or draw tickets) beyond that, so
+    // over the whole group; the expand kernel draws tile tickets beyond that, so
     // a batch far below its bound does not pay for thousands of empty blocks.
-    auto cap_assign = [&](uint64_t blocks) {
+    auto tiles_for = [&](uint64_t items) {
+        const uint64_t blocks = (items + kTile - 1) / kTile;
         return (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>(blocks, std::max<uint64_t>(1, (uint64_t)kSMs * 8 / n_batches)));
     };
-    auto cap_pick = [&](uint64_t blocks) {
-        return (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>(blocks, std::max<uint64_t>(1, (uint64_t)kSMs * 16 / n_batches)));
-    };
-    {
-        // enough blocks to wipe a typical batch's slots in one pass
-        const uint32_t bx = (uint32_t)std::min<uint64_t>(std::max<uint64_t>((b_edges + nmax) / 1024, 1), 64);
-        k_begin<<<dim3(bx, n_batches), 256, 0, st>>>(pa);
-    }
     if (nmax) k_insert_seeds<<<dim3((nmax + 255) / 256, n_batches), 256, 0, st>>>(pa);
-    // stage 0: seeds -> frontier[0]
-    k_assign<<<dim3(cap_assign((nmax + kAssignThreads - 1) / kAssignThreads), n_batches), kAssignThreads, 0, st>>>(
-        pa, 0, s->cfg.fanout[0], 1);
-
-    uint64_t f_bound = std::min<uint64_t>(nmax, g->num_nodes);
-    for (uint32_t h = 0; h < H; ++h) {
-        const uint32_t k = s->cfg.fanout[h];
-        const uint64_t e_bound = f_bound * k;
-        if (f_bound && k) {
-            if (s->mode == kModeWeighted) {
-                const uint32_t blocks = cap_pick((f_bound * 32 + kPickThreads - 1) / kPickThreads);
-                k_pick_weighted<<<dim3(blocks, n_batches), kPickThreads, 0, st>>>(pa, h, k);
-            } else if (k > 32) {
-                k_pick_large<<<dim3(cap_pick((f_bound + 3) / 4), n_batches), 128, 0, st>>>(pa, h, k);
-            } else {
-                const uint32_t G = k <= 4 ? 4 : k <= 8 ? 8 : k <= 16 ? 16 : 32;
-                const dim3 grid(cap_pick((f_bound * G + kPickThreads - 1) / kPickThreads), n_batches);
-                switch (G) {
-                    case 4: k_pick_small<4><<<grid, kPickThreads, 0, st>>>(pa, h, k); break;
-                    case 8: k_pick_small<8><<<grid, kPickThreads, 0, st>>>(pa, h, k); break;
-                    case 16: k_pick_small<16><<<grid, kPickThreads, 0, st>>>(pa, h, k); break;
-                    default: k_pick_small<32><<<grid, kPickThreads, 0, st>>>(pa, h, k); break;
-                }
-            }
-        }
-        const bool has_next = h + 1 < H;
-        k_assign<<<dim3(cap_assign((e_bound + kAssignThreads - 1) / kAssignThreads), n_batches),
-                   kAssignThreads, 0, st>>>(pa, h + 1, has_next ? s->cfg.fanout[h + 1] : 0, has_next ? 1 : 0);
-        f_bound = std::min<uint64_t>(e_bound, g->num_nodes);
+    uint64_t items = nmax;  // bound on the items of the stage being launched
+    for (uint32_t stage = 0; stage <= H; ++stage) {
+        const bool has_next = stage < H;
+        const uint32_t k = has_next ? s->cfg.fanout[stage] : 0;
+        const dim3 grid(tiles_for(items), n_batches);
+        if (s->mode == kModeWeighted) launch_expand<kPickWeighted>(32, grid, st, pa, stage, k, has_next);
+        else if (k > 32) launch_expand<kPickLarge>(32, grid, st, pa, stage, k, has_next);
+        else launch_expand<kPickSmall>(k <= 4 ? 4 : k <= 8 ? 8 : k <= 16 ? 16 : 32, grid, st, pa, stage, k, has_next);
+        items = std::min<uint64_t>(items, g->num_nodes) * k;
     }
     {
         const uint64_t work = std::max<uint64_t>(std::max(b_edges, b_nodes), std::max<uint64_t>(nmax, 1));
@@ -855,7 +825,6 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
     if (s->profile) AG_CUDA(cudaEventRecord(s->ev[1], st));
     s->gathered = false;
     if (want_x) {
-        AG_CUDA(cudaMemcpyAsync(s->gather_dev, s->gather_host, n_batches * sizeof(GatherArgs), cudaMemcpyHostToDevice, st));
         bool aligned = ((uintptr_t)feats->payload % 16) == 0;
         for (uint32_t b = 0; b < n_batches; ++b) aligned = aligned && ((uintptr_t)bufs[b].x % 16) == 0;
         AG_CUDA(launch_gather_group(s->gather_dev, n_batches, (uint32_t)(feats->dim * elem_size(feats->dtype)),
@@ -925,7 +894,7 @@ extern "C" int32_t ag_sample(ag_sampler *s, const uint32_t *seeds, uint64_t n_se
     DeviceGuard guard(s->device);
     if (!guard.ok) return AG_ERR_CUDA;
     uint64_t mn, me;
-    compute_bounds(s, n_seeds, &mn, &me, nullptr, nullptr);
+    compute_bounds(s, n_seeds, &mn, &me, nullptr);
     ag_subgraph_buffers b{};
     b.cap_nodes = std::max<uint64_t>(mn, 1); b.cap_edges = std::max<uint64_t>(me, 1);
     b.cap_seeds = std::max<uint64_t>(n_seeds, 1);

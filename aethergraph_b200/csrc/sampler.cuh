@@ -1,32 +1,33 @@
-// Device-side state shared by the sampling kernels (homogeneous and hetero).
+// Device-side building blocks of the sampling kernels: the dedup table, the
+// single-pass scan and the per-batch bookkeeping they share.
 #pragma once
 
 #include "common.cuh"
 
 namespace ag {
 
-// One frontier entry: everything the pick kernel needs for a node, in one
-// 32-byte record (two 16-byte loads).
+// A vertex discovered in one stage and expanded in the next: everything the
+// picks need, kept in shared memory between the two halves of the expand kernel.
 struct __align__(16) FrontierEntry {
     uint64_t off;    // first CSR position of the row
-    uint64_t dbase;  // absolute index of the node's first RNG draw
-    uint32_t id;     // global id (hetero: id within its node type)
+    uint64_t dbase;  // absolute index of the vertex's first RNG draw
+    uint32_t id;     // vertex id
     uint32_t local;  // local index assigned at discovery
-    uint32_t deg;    // row length (hetero: unused, rows are re-read per edge type)
-    uint32_t ebase;  // first edge slot of the node within its hop
+    uint32_t deg;    // row length
+    uint32_t ebase;  // first edge slot of the vertex within its hop
 };
 
 // Running totals handed from one stage to the next.  Stage 0 is the seed
-// registration, stage h + 1 the edges of hop h.  A stage's kernels only read
-// stage[s] and only the last tile of its assign kernel writes stage[s + 1], so
-// nothing is read and written concurrently.
+// registration, stage h + 1 the edges of hop h.  A stage's kernel only reads
+// stage[s] and only the last tile writes stage[s + 1], so nothing is read and
+// written concurrently.
 struct StageInfo {
     uint32_t n_nodes;     // nodes registered before this stage
     uint32_t n_edges;     // edges emitted before this stage
-    uint32_t frontier_n;  // entries in the frontier this stage expands
-    uint32_t hop_edges;   // edges this stage emits (sum of take over the frontier)
-    uint64_t draws;       // RNG draws consumed before this stage
-    uint64_t hop_draws;   // draws this stage consumes
+    uint32_t frontier_n;  // vertices this stage discovered (expanded by the next)
+    uint32_t hop_edges;   // items of this stage (edges the previous stage emitted)
+    uint64_t draws;       // RNG draws consumed before this stage's picks
+    uint64_t hop_draws;   // draws this stage's picks consume
 };
 
 struct ScanVal {
@@ -55,12 +56,31 @@ struct BatchState {
     uint32_t error;
     uint32_t ticket;
     uint64_t stream_pos;  // draws consumed by earlier batches of this handle
-    uint32_t prev_edges;  // edges / seeds of the batch that last used this slot: the
-    uint32_t prev_seeds;  // table entries the next batch has to wipe
 };
 
+// ------------------------------------------------------------ dedup table --
+// Open addressing, linear probing, one 64-bit slot per vertex:
+//   key (32) | generation (4) | pending (1) | stage (4) | position (23)
+// A pending value says "first named at this position of this stage"; once the
+// vertex has its local index the value becomes generation | local.  For one key
+// and generation the integer order of the value is exactly the order the
+// sequential reference meets the vertex in: assigned < pending of an earlier
+// stage < pending of a later stage, then by position.  atomicMin therefore
+// keeps the first sighting.  A slot whose generation is not the current one is
+// free: a handle bumps the generation per launch instead of clearing the table
+// and clears it for real once per 15 launches (generation 15 is the empty mark).
 constexpr uint64_t kSlotEmpty = 0xFFFFFFFFFFFFFFFFull;
-constexpr uint32_t kPending = 0x80000000u;
+constexpr uint32_t kGenShift = 28, kPendingBit = 1u << 27, kStageShift = 23;
+constexpr uint32_t kPosMask = (1u << 23) - 1u;
+constexpr uint32_t kGens = 15;
+constexpr uint64_t kMaxPos = 1ull << 23;  // items per stage and nodes per batch
+
+__host__ __device__ __forceinline__ uint32_t enc_pending(uint32_t gen, uint32_t stage, uint32_t pos) {
+    return (gen << kGenShift) | kPendingBit | (stage << kStageShift) | pos;
+}
+__host__ __device__ __forceinline__ uint32_t enc_final(uint32_t gen, uint32_t local) {
+    return (gen << kGenShift) | local;
+}
 
 // Bounded polling: ~2^20 polls with a short sleep is on the order of 100 ms,
 // far beyond any legitimate wait between tiles of one launch.
@@ -72,6 +92,7 @@ struct DedupTable {
     uint64_t *slots;
     uint32_t mask;
     uint32_t shift;  // 32 - log2(capacity)
+    uint32_t gen;
 };
 
 __device__ __forceinline__ uint32_t table_hash(uint32_t key, uint32_t shift) {
@@ -79,27 +100,27 @@ __device__ __forceinline__ uint32_t table_hash(uint32_t key, uint32_t shift) {
 }
 
 // Inserts (key, val) keeping the minimum val per key; returns the slot index.
-// Slot layout: key in the high word, value in the low word.  A value below
-// kPending is a final local index and is never replaced (min keeps it).
 __device__ __forceinline__ uint32_t table_insert_min(const DedupTable &t, uint32_t key,
                                                      uint32_t val, uint32_t *err) {
-    const uint64_t mine = ((uint64_t)key << 32) | val;
+    const unsigned long long mine = ((unsigned long long)key << 32) | val;
     uint32_t h = table_hash(key, t.shift);
     for (uint32_t probe = 0; probe <= t.mask; ++probe) {
-        unsigned long long cur = __ldcg((const unsigned long long *)&t.slots[h]);
-        if (cur == kSlotEmpty) {
-            cur = atomicCAS((unsigned long long *)&t.slots[h], (unsigned long long)kSlotEmpty,
-                            (unsigned long long)mine);
-            if (cur == kSlotEmpty) return h;
+        unsigned long long *slot = (unsigned long long *)&t.slots[h];
+        unsigned long long cur = __ldcg(slot);
+        // free (never used, or left over from an older generation): claim it
+        while (((uint32_t)cur >> kGenShift) != t.gen) {
+            const unsigned long long prev = atomicCAS(slot, cur, mine);
+            if (prev == cur) return h;
+            cur = prev;
         }
         if ((uint32_t)(cur >> 32) == key) {
-            if ((uint32_t)cur > val) atomicMin((unsigned long long *)&t.slots[h], (unsigned long long)mine);
+            if ((uint32_t)cur > val) atomicMin(slot, mine);
             return h;
         }
         h = (h + 1) & t.mask;
     }
     atomicOr(err, kErrTableFull);
-    return 0;
+    return 0xFFFFFFFFu;
 }
 
 __device__ __forceinline__ ScanVal warp_inclusive_scan(ScanVal v, int lane) {
@@ -155,7 +176,7 @@ __device__ __forceinline__ ScanVal lookback_exclusive(TileDesc *tiles, uint32_t 
                 st = ld_acquire_u32(&tiles[t].status);
                 if ((st >> 2) == epoch && (st & 3u) != 0) break;
                 if (++spins > kSpinLimit) { atomicOr(err, kErrSpinTimeout); st = (epoch << 2) | kTileIncl; break; }
-                __nanosleep(64);
+                __nanosleep(32);
             }
             state = st & 3u;
             if (spins <= kSpinLimit) v = (state == kTileIncl) ? tiles[t].incl : tiles[t].agg;
