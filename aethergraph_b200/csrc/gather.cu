@@ -85,9 +85,13 @@ k_gather_vec(GatherArgs a, const GatherArgs *__restrict__ group) {
     const int sub = threadIdx.x / LPR;
     const uint32_t vecs = a.row_bytes >> 4;
     const uint32_t out_per_vec = (DTYPE == AG_F32) ? 4u : 8u;  // floats per 16-byte vector
-    const uint64_t stride = (uint64_t)gridDim.x * kRowsPerBlock;
+    // A block owns chunks of kRowsPerBlock * kInFlight consecutive rows.  With a
+    // grid of about one chunk per block the blocks are short-lived, so blocks of
+    // a concurrent (higher-priority) kernel get SM slots as they retire.
+    constexpr uint64_t kChunk = (uint64_t)kRowsPerBlock * kInFlight;
+    const uint64_t stride = kRowsPerBlock;
 
-    for (uint64_t base = (uint64_t)blockIdx.x * kRowsPerBlock + sub; base < n; base += stride * kInFlight) {
+    for (uint64_t base = (uint64_t)blockIdx.x * kChunk + sub; base < n; base += (uint64_t)gridDim.x * kChunk) {
         for (uint32_t v0 = 0; v0 < vecs; v0 += LPR) {
             const uint32_t v = v0 + lane;
             uint4 val[kInFlight];
@@ -201,16 +205,13 @@ __global__ void k_encode(const float *src, uint16_t *dst, uint64_t count, int dt
 }  // namespace
 
 int gather_grid_blocks(uint64_t n, uint32_t row_bytes) {
-    // Whole waves of 148 SMs x 8 resident 256-thread blocks; fewer blocks when
-    // the batch is small enough that one pass covers it.
+    // One chunk of rows per block, up to 64 blocks per SM's worth of grid; past
+    // that the blocks stride over further chunks.
     const uint32_t vecs = row_bytes >> 4;
     const int lpr = vecs <= 4 ? 4 : vecs <= 8 ? 8 : vecs <= 16 ? 16 : 32;
     const uint64_t rows_per_block = (uint64_t)(kThreads / lpr) * kInFlight;
-    const uint64_t need = (n + rows_per_block - 1) / rows_per_block;
-    const uint64_t full = (uint64_t)kSMs * 8;
-    if (need >= full) return (int)full;
-    const uint64_t waves = (need + kSMs - 1) / kSMs;
-    return (int)(waves ? waves * kSMs : kSMs);
+    const uint64_t need = std::max<uint64_t>(1, (n + rows_per_block - 1) / rows_per_block);
+    return (int)std::min<uint64_t>(need, (uint64_t)kSMs * 64);
 }
 
 cudaError_t launch_gather(const GatherArgs &a, int dtype, cudaStream_t st) {
@@ -245,9 +246,10 @@ cudaError_t launch_gather_group(const GatherArgs *group_dev, uint32_t n_batches,
     if (n_batches == 0 || n_bound == 0) return cudaSuccess;
     GatherArgs none{};
     if (row_bytes % 16 == 0 && aligned) {
-        // the whole group shares whole waves of the 148 SMs
+        // n_bound is the caller's estimate of the rows per batch (the true count is
+        // read on the device); a batch with more rows strides over extra chunks.
         int per = gather_grid_blocks(n_bound, row_bytes);
-        const int cap = std::max(1, (kSMs * 8 + (int)n_batches - 1) / (int)n_batches);
+        const int cap = std::max(1, (kSMs * 64 + (int)n_batches - 1) / (int)n_batches);
         per = std::min(per, cap);
         const dim3 grid(per, n_batches);
         switch (dtype) {

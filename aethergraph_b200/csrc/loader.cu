@@ -254,7 +254,11 @@ extern "C" int32_t ag_loader_create(const ag_graph *g, const ag_features *f, con
         l->samplers.push_back(s);
         if (profiling) st = ag_sampler_set_profiling(s, 1);
         cudaStream_t stream = nullptr;
-        if (st == AG_OK && cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking) != cudaSuccess)
+        // Sampling chains run at the highest priority; each handle's gather runs on
+        // its own lowest-priority stream, so chains of other workers cut in.
+        int lo = 0, hi = 0;
+        cudaDeviceGetStreamPriorityRange(&lo, &hi);
+        if (st == AG_OK && cudaStreamCreateWithPriority(&stream, cudaStreamNonBlocking, hi) != cudaSuccess)
             st = fail(AG_ERR_CUDA, "cudaStreamCreate failed: %s", cudaGetErrorString(cudaGetLastError()));
         if (st == AG_OK) l->streams.push_back(stream);
     }

@@ -200,10 +200,10 @@ __device__ __forceinline__ void pick_small(const SampleParams &p, uint32_t hop, 
 // Fanout > 32: one warp per vertex (the first four warps of the tile); finished
 // picks live in shared memory so later slots can be checked against all earlier ones.
 __device__ __forceinline__ void pick_large(const SampleParams &p, uint32_t hop, uint32_t k, uint32_t edges_before,
-                                           const FrontierEntry *fes, uint32_t n, uint32_t (*s_picks)[kLargeK]) {
+                                           const FrontierEntry *fes, uint32_t n, uint32_t *s_picks) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (warp >= 4) return;
-    uint32_t *picks = s_picks[warp];
+    uint32_t *picks = s_picks + warp * kLargeK;
     for (uint32_t j = warp; j < n; j += 4) {
         const FrontierEntry fe = fes[j];
         const uint32_t deg = fe.deg;
@@ -419,8 +419,8 @@ k_expand(const SampleParams *__restrict__ pa, uint32_t stage, uint32_t k, int ha
         if (!has_next) continue;
         __syncthreads();
         const uint32_t n_new = s_total.flags;
-        if (PICK == kPickWeighted) pick_weighted(p, stage, k, edges_before_next, s_fe, n_new);
-        else if (PICK == kPickLarge) pick_large(p, stage, k, edges_before_next, s_fe, n_new, s_picks);
+        if constexpr (PICK == kPickWeighted) pick_weighted(p, stage, k, edges_before_next, s_fe, n_new);
+        else if constexpr (PICK == kPickLarge) pick_large(p, stage, k, edges_before_next, s_fe, n_new, &s_picks[0][0]);
         else pick_small<G>(p, stage, k, edges_before_next, s_fe, n_new);
     }
 }
@@ -525,9 +525,18 @@ struct ag_sampler {
     cudaEvent_t done = nullptr;
     bool in_flight = false, dirty = true;
     uint32_t in_flight_n = 0;
+    // The gather runs on the handle's own low-priority stream, behind an event:
+    // sampling kernels of other handles (latency-bound, few resources) then slip
+    // in between the short-lived blocks of a running gather (bandwidth-bound).
+    cudaStream_t gstream = nullptr;
+    cudaEvent_t sampled = nullptr;
+    // Grid-size estimates from the last group's real counts (the bounds before
+    // the first one); kernels stride past an estimate that turns out too small.
+    uint64_t est_nodes = 0;
+    uint64_t est_items[AG_MAX_HOPS + 2] = {0};
     // optional per-group device timing
     bool profile = false, gathered = false;
-    cudaEvent_t ev[3] = {nullptr, nullptr, nullptr};
+    cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
     // buffers handed out by ag_sample (library-allocated variant)
     std::vector<void *> owned;
 };
@@ -627,8 +636,15 @@ extern "C" int32_t ag_sampler_create_group(const ag_graph *g, const ag_sampling_
             cudaHostAlloc(&s->counts_host, group * sizeof(ag_sample_counts), cudaHostAllocDefault) != cudaSuccess ||
             cudaHostAlloc(&s->params_host, group * sizeof(SampleParams), cudaHostAllocDefault) != cudaSuccess ||
             cudaHostAlloc(&s->gather_host, group * sizeof(GatherArgs), cudaHostAllocDefault) != cudaSuccess ||
-            cudaEventCreateWithFlags(&s->done, cudaEventDisableTiming) != cudaSuccess) {
+            cudaEventCreateWithFlags(&s->done, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&s->sampled, cudaEventDisableTiming) != cudaSuccess) {
             st = fail(AG_ERR_CUDA, "sampler allocation failed: %s", cudaGetErrorString(cudaGetLastError()));
+            break;
+        }
+        int lo = 0, hi = 0;
+        cudaDeviceGetStreamPriorityRange(&lo, &hi);  // lo = least urgent
+        if (cudaStreamCreateWithPriority(&s->gstream, cudaStreamNonBlocking, lo) != cudaSuccess) {
+            st = fail(AG_ERR_CUDA, "cudaStreamCreateWithPriority failed: %s", cudaGetErrorString(cudaGetLastError()));
             break;
         }
         st = ensure_scratch(s, std::max<uint32_t>(cfg->max_seeds, 1));
@@ -653,6 +669,8 @@ extern "C" void ag_sampler_free(ag_sampler *s) {
     if (s->params_host) cudaFreeHost(s->params_host);
     if (s->gather_host) cudaFreeHost(s->gather_host);
     if (s->done) cudaEventDestroy(s->done);
+    if (s->sampled) cudaEventDestroy(s->sampled);
+    if (s->gstream) cudaStreamDestroy(s->gstream);
     for (auto &e : s->ev) if (e) cudaEventDestroy(e);
     delete s;
 }
@@ -810,30 +828,42 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
     for (uint32_t stage = 0; stage <= H; ++stage) {
         const bool has_next = stage < H;
         const uint32_t k = has_next ? s->cfg.fanout[stage] : 0;
-        const dim3 grid(tiles_for(items), n_batches);
+        const uint64_t expect = (stage && s->est_items[stage]) ? std::min(items, s->est_items[stage]) : items;
+        const dim3 grid(tiles_for(expect), n_batches);
         if (s->mode == kModeWeighted) launch_expand<kPickWeighted>(32, grid, st, pa, stage, k, has_next);
         else if (k > 32) launch_expand<kPickLarge>(32, grid, st, pa, stage, k, has_next);
         else launch_expand<kPickSmall>(k <= 4 ? 4 : k <= 8 ? 8 : k <= 16 ? 16 : 32, grid, st, pa, stage, k, has_next);
         items = std::min<uint64_t>(items, g->num_nodes) * k;
     }
     {
-        const uint64_t work = std::max<uint64_t>(std::max(b_edges, b_nodes), std::max<uint64_t>(nmax, 1));
-        const uint32_t fx = (uint32_t)std::min<uint64_t>((work + 255) / 256, std::max<uint64_t>((uint64_t)kSMs * 8 / n_batches, 1));
+        uint64_t est_edges = 0;
+        for (uint32_t h = 1; h <= H; ++h) est_edges += s->est_items[h];
+        const uint64_t bound = std::max<uint64_t>(std::max(b_edges, b_nodes), std::max<uint64_t>(nmax, 1));
+        const uint64_t work = est_edges ? std::min(bound, std::max<uint64_t>(est_edges, nmax)) : bound;
+        const uint32_t fx = (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>((work + 255) / 256, std::max<uint64_t>((uint64_t)kSMs * 8 / n_batches, 1)));
         k_finalize<<<dim3(fx, n_batches), 256, 0, st>>>(pa);
     }
     AG_CUDA(cudaGetLastError());
     if (s->profile) AG_CUDA(cudaEventRecord(s->ev[1], st));
+    AG_CUDA(cudaMemcpyAsync(s->counts_host, s->counts_dev, n_batches * sizeof(ag_sample_counts), cudaMemcpyDeviceToHost, st));
     s->gathered = false;
     if (want_x) {
         bool aligned = ((uintptr_t)feats->payload % 16) == 0;
         for (uint32_t b = 0; b < n_batches; ++b) aligned = aligned && ((uintptr_t)bufs[b].x % 16) == 0;
+        // sampling chain -> event -> gather on the low-priority stream -> event -> caller's stream
+        AG_CUDA(cudaEventRecord(s->sampled, st));
+        AG_CUDA(cudaStreamWaitEvent(s->gstream, s->sampled, 0));
+        if (s->profile) AG_CUDA(cudaEventRecord(s->ev[2], s->gstream));
+        const uint64_t rows = s->est_nodes ? std::min(b_nodes, s->est_nodes) : b_nodes;
         AG_CUDA(launch_gather_group(s->gather_dev, n_batches, (uint32_t)(feats->dim * elem_size(feats->dtype)),
-                                    (uint32_t)feats->dim, b_nodes, aligned, feats->dtype, st));
-        if (s->profile) AG_CUDA(cudaEventRecord(s->ev[2], st));
+                                    (uint32_t)feats->dim, rows, aligned, feats->dtype, s->gstream));
+        if (s->profile) AG_CUDA(cudaEventRecord(s->ev[3], s->gstream));
+        AG_CUDA(cudaEventRecord(s->done, s->gstream));
+        AG_CUDA(cudaStreamWaitEvent(st, s->done, 0));  // the caller's stream stays ordered behind the gather
         s->gathered = true;
+    } else {
+        AG_CUDA(cudaEventRecord(s->done, st));
     }
-    AG_CUDA(cudaMemcpyAsync(s->counts_host, s->counts_dev, n_batches * sizeof(ag_sample_counts), cudaMemcpyDeviceToHost, st));
-    AG_CUDA(cudaEventRecord(s->done, st));
     s->in_flight = true;
     s->in_flight_n = n_batches;
     return AG_OK;
@@ -855,8 +885,18 @@ extern "C" int32_t ag_sample_group_wait(ag_sampler *s, ag_sample_counts *counts,
     float sample_ms = 0.f, gather_ms = 0.f;
     if (s->profile) {
         cudaEventElapsedTime(&sample_ms, s->ev[0], s->ev[1]);
-        if (s->gathered) cudaEventElapsedTime(&gather_ms, s->ev[1], s->ev[2]);
+        if (s->gathered) cudaEventElapsedTime(&gather_ms, s->ev[2], s->ev[3]);
     }
+    // Next group's grids follow what this one really produced (with headroom).
+    uint64_t mx_nodes = 0, mx_items[AG_MAX_HOPS + 2] = {0};
+    for (uint32_t b = 0; b < s->in_flight_n; ++b) {
+        const ag_sample_counts &c = s->counts_host[b];
+        mx_nodes = std::max<uint64_t>(mx_nodes, c.num_nodes);
+        for (uint32_t h = 0; h < c.num_hops && h < AG_MAX_HOPS; ++h)
+            mx_items[h + 1] = std::max<uint64_t>(mx_items[h + 1], c.edges_per_hop[h]);
+    }
+    s->est_nodes = mx_nodes + mx_nodes / 4 + 256;
+    for (uint32_t h = 1; h <= s->cfg.num_hops; ++h) s->est_items[h] = mx_items[h] + mx_items[h] / 4 + 512;
     int32_t first = AG_OK;
     for (uint32_t b = 0; b < s->in_flight_n; ++b) {
         ag_sample_counts c = s->counts_host[b];
