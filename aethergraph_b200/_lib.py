@@ -121,7 +121,9 @@ SIGNATURES = {
     "ag_loader_submit": (C.c_int32, [_P, C.c_int64, _P, C.c_uint64, C.c_int32, C.POINTER(SubgraphBuffers), _P]),
     "ag_loader_next": (C.c_int32, [_P, C.c_int64, C.POINTER(Batch)]),
     "ag_loader_try_next": (C.c_int32, [_P, C.POINTER(Batch)]),
-    "ag_loader_release_batch": (C.c_int32, [_P, C.POINTER(Batch)]),
+    "ag_loader_release_batch": (C.c_int32, [_P, C.POINTER(Batch), _P]),
+    "ag_loader_submit_many": (C.c_int32, [_P, C.c_uint32, _P, _P, _P, C.c_int32, _P, _P, C.POINTER(C.c_uint32)]),
+    "ag_loader_next_many": (C.c_int32, [_P, C.c_int64, C.c_uint32, C.POINTER(Batch), C.POINTER(C.c_uint32)]),
     "ag_loader_stats_get": (C.c_int32, [_P, C.POINTER(LoaderStats)]),
     "ag_loader_shutdown": (C.c_int32, [_P]),
     "ag_loader_free": (None, [_P]),

@@ -3,10 +3,16 @@
 // contract of the reference pipeline
 // (crates/aethergraph-core/src/loader/prefetch.rs:402-560, 911-1073).
 //
-// Each worker thread owns one sampler handle and one CUDA stream.  A batch is
-// one launch chain (sample -> dedup/relabel -> gather) on the worker's stream;
-// with T workers, T chains overlap on the device, which is what hides the
-// latency-bound sampling kernels behind the bandwidth-bound gather.
+// Each worker thread owns one sampler handle and one high-priority CUDA stream.
+// A worker takes up to `group` queued batches at a time and runs them as ONE
+// launch chain (sample -> dedup/relabel -> gather); with T workers, T chains
+// overlap on the device, which is what hides the latency-bound sampling kernels
+// behind the bandwidth-bound gather.
+//
+// Output buffers either come with the submission (caller-owned) or from the
+// loader's pool: one device allocation per batch shape, recycled when the
+// consumer releases the batch.  A recycled set remembers the event that marks
+// the consumer's last use, and the next batch's kernels wait for it.
 #include <atomic>
 #include <chrono>
 #include <condition_variable>
@@ -15,6 +21,7 @@
 #include <mutex>
 #include <string>
 #include <thread>
+#include <unordered_map>
 #include <vector>
 
 #include "common.cuh"
@@ -24,6 +31,12 @@ using namespace ag;
 
 namespace {
 
+struct PoolSet {
+    void *base = nullptr;              // one cudaMalloc
+    ag_subgraph_buffers bufs{};
+    cudaEvent_t last_use = nullptr;    // consumer's last use of the memory, if any
+};
+
 struct Work {
     uint64_t seq = 0;
     int64_t batch_idx = 0;
@@ -32,7 +45,7 @@ struct Work {
     uint64_t n_seeds = 0;
     ag_subgraph_buffers bufs{};
     bool owned = false;
-    cudaEvent_t after = nullptr;       // work the buffers' previous user still has queued
+    cudaEvent_t after[2] = {nullptr, nullptr};  // work that must finish before the buffers are written
 };
 
 struct Done {
@@ -42,6 +55,8 @@ struct Done {
 };
 
 using Clock = std::chrono::steady_clock;
+
+uint64_t align256(uint64_t v) { return (v + 255) & ~255ull; }
 
 }  // namespace
 
@@ -65,33 +80,90 @@ struct ag_loader {
     std::vector<ag_sampler *> samplers;
     std::vector<cudaStream_t> streams;
     ag_loader_stats stats{};
+
+    std::mutex pool_m;
+    std::vector<PoolSet> pool_free;
+    std::unordered_map<void *, PoolSet> pool_live;  // keyed by bufs.nodes
 };
 
 namespace {
 
-int32_t alloc_owned(ag_loader *l, uint64_t n_seeds, ag_subgraph_buffers *b) {
+// A buffer set for a batch of n_seeds seeds, from the pool or freshly allocated.
+// *last_use receives the event the next writer has to wait for (may be null).
+int32_t pool_take(ag_loader *l, uint64_t n_seeds, ag_subgraph_buffers *out, cudaEvent_t *last_use) {
     uint64_t mn = 0, me = 0;
     AG_TRY(ag_sampler_bounds(l->samplers[0], n_seeds, &mn, &me));
-    *b = ag_subgraph_buffers{};
-    b->cap_nodes = std::max<uint64_t>(mn, 1); b->cap_edges = std::max<uint64_t>(me, 1);
-    b->cap_seeds = std::max<uint64_t>(n_seeds, 1);
-    bool ok = cudaMalloc(&b->nodes, b->cap_nodes * 4) == cudaSuccess &&
-              cudaMalloc(&b->edge_src, b->cap_edges * 4) == cudaSuccess &&
-              cudaMalloc(&b->edge_dst, b->cap_edges * 4) == cudaSuccess &&
-              cudaMalloc(&b->src_local, b->cap_edges * 4) == cudaSuccess &&
-              cudaMalloc(&b->dst_local, b->cap_edges * 4) == cudaSuccess &&
-              cudaMalloc(&b->seed_locals, b->cap_seeds * 4) == cudaSuccess;
-    if (ok && l->cfg.track_edge_ids) ok = cudaMalloc(&b->edge_ids, b->cap_edges * 8) == cudaSuccess;
-    if (ok && l->f) ok = cudaMalloc(&b->x, b->cap_nodes * l->f->dim * 4) == cudaSuccess;
-    if (!ok) return fail(AG_ERR_CUDA, "loader: out of device memory: %s", cudaGetErrorString(cudaGetLastError()));
+    const uint64_t cn = std::max<uint64_t>(mn, 1), ce = std::max<uint64_t>(me, 1), cs = std::max<uint64_t>(n_seeds, 1);
+    *last_use = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(l->pool_m);
+        for (size_t i = 0; i < l->pool_free.size(); ++i) {
+            PoolSet &p = l->pool_free[i];
+            if (p.bufs.cap_nodes == cn && p.bufs.cap_edges == ce && p.bufs.cap_seeds == cs) {
+                PoolSet s = p;
+                l->pool_free[i] = l->pool_free.back();
+                l->pool_free.pop_back();
+                *last_use = s.last_use;
+                s.last_use = nullptr;
+                *out = s.bufs;
+                l->pool_live.emplace(s.bufs.nodes, s);
+                return AG_OK;
+            }
+        }
+    }
+    const bool eids = l->cfg.track_edge_ids != 0;
+    const uint64_t dim = l->f ? l->f->dim : 0;
+    uint64_t off = 0;
+    auto carve = [&](uint64_t bytes) { const uint64_t o = off; off += align256(bytes); return o; };
+    const uint64_t o_nodes = carve(cn * 4), o_esrc = carve(ce * 4), o_edst = carve(ce * 4), o_sl = carve(ce * 4),
+                   o_dl = carve(ce * 4), o_seedl = carve(cs * 4), o_eid = eids ? carve(ce * 8) : 0,
+                   o_nid = carve(cn * 8), o_eil = carve(ce * 16), o_sidx = carve(cs * 8),
+                   o_x = dim ? carve(cn * dim * 4) : 0;
+    uint8_t *base = nullptr;
+    if (cudaMalloc(&base, std::max<uint64_t>(off, 256)) != cudaSuccess)
+        return fail(AG_ERR_CUDA, "loader: out of device memory for a %llu-byte batch buffer: %s",
+                    (unsigned long long)off, cudaGetErrorString(cudaGetLastError()));
+    PoolSet s;
+    s.base = base;
+    ag_subgraph_buffers &b = s.bufs;
+    b.cap_nodes = cn; b.cap_edges = ce; b.cap_seeds = cs;
+    b.nodes = (uint32_t *)(base + o_nodes); b.edge_src = (uint32_t *)(base + o_esrc);
+    b.edge_dst = (uint32_t *)(base + o_edst); b.src_local = (uint32_t *)(base + o_sl);
+    b.dst_local = (uint32_t *)(base + o_dl); b.seed_locals = (uint32_t *)(base + o_seedl);
+    b.edge_ids = eids ? (uint64_t *)(base + o_eid) : nullptr;
+    b.n_id = (int64_t *)(base + o_nid); b.edge_index_local = (int64_t *)(base + o_eil);
+    b.e_id = nullptr;  // int64(edge id) shares its bits with the u64 edge_ids
+    b.seed_index = (int64_t *)(base + o_sidx);
+    b.x = dim ? (float *)(base + o_x) : nullptr;
+    *out = b;
+    std::lock_guard<std::mutex> lk(l->pool_m);
+    l->pool_live.emplace(b.nodes, s);
     return AG_OK;
 }
 
-void free_owned(ag_subgraph_buffers *b) {
-    void *ptrs[] = {b->nodes, b->edge_src, b->edge_dst, b->edge_ids, b->src_local, b->dst_local,
-                    b->seed_locals, b->n_id, b->edge_index_local, b->e_id, b->seed_index, b->x};
-    for (void *p : ptrs) cudaFree(p);
-    *b = ag_subgraph_buffers{};
+// Returns a set to the pool; `stream`'s queued work (when record is true) is the
+// consumer's last use of it.
+void pool_give(ag_loader *l, const ag_subgraph_buffers &bufs, bool record, cudaStream_t stream) {
+    std::lock_guard<std::mutex> lk(l->pool_m);
+    auto it = l->pool_live.find(bufs.nodes);
+    if (it == l->pool_live.end()) return;
+    PoolSet s = it->second;
+    l->pool_live.erase(it);
+    if (record) {
+        if (cudaEventCreateWithFlags(&s.last_use, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventRecord(s.last_use, stream) != cudaSuccess) {
+            // Cannot order the reuse: do not reuse.
+            if (s.last_use) cudaEventDestroy(s.last_use);
+            cudaFree(s.base);
+            return;
+        }
+    }
+    l->pool_free.push_back(s);
+}
+
+void drop_work(ag_loader *l, Work &w) {
+    for (cudaEvent_t &e : w.after) if (e) { cudaEventDestroy(e); e = nullptr; }
+    if (w.owned) pool_give(l, w.bufs, false, nullptr);
 }
 
 void worker_main(ag_loader *l, uint32_t idx) {
@@ -129,10 +201,11 @@ void worker_main(ag_loader *l, uint32_t idx) {
         int32_t rc = AG_OK;
         for (uint32_t b = 0; b < nb; ++b) {
             Work &w = ws[b];
-            if (w.after) {
-                if (cudaStreamWaitEvent(st, w.after, 0) != cudaSuccess) rc = fail(AG_ERR_CUDA, "cudaStreamWaitEvent failed");
-                cudaEventDestroy(w.after);
-                w.after = nullptr;
+            for (cudaEvent_t &e : w.after) {
+                if (!e) continue;
+                if (cudaStreamWaitEvent(st, e, 0) != cudaSuccess) rc = fail(AG_ERR_CUDA, "cudaStreamWaitEvent failed");
+                cudaEventDestroy(e);
+                e = nullptr;
             }
             seed_ptrs[b] = w.seeds_dev ? w.seeds_dev : w.seeds.data();
             n_seeds[b] = w.n_seeds;
@@ -163,6 +236,7 @@ void worker_main(ag_loader *l, uint32_t idx) {
             err = ag_last_error();
         }
         const uint64_t ns = (uint64_t)std::chrono::duration_cast<std::chrono::nanoseconds>(Clock::now() - t0).count();
+        std::unique_lock<std::mutex> lk(l->m);
         for (uint32_t b = 0; b < nb; ++b) {
             Work &w = ws[b];
             Done d;
@@ -173,12 +247,15 @@ void worker_main(ag_loader *l, uint32_t idx) {
             const bool chain_failed = rc != AG_OK && statuses[b] == AG_OK &&
                                       !(rc == AG_ERR_SAMPLING || rc == AG_ERR_VALUE || rc == AG_ERR_LOAD);
             if (statuses[b] != AG_OK || chain_failed) { d.status = statuses[b] != AG_OK ? statuses[b] : rc; d.error = err; }
-            std::unique_lock<std::mutex> lk(l->m);
             // Results channel holds `depth` batches: wait for room (prefetch.rs:1135-1143),
             // except for the batch the consumer is waiting on — holding it back could
             // stall an ordered loader whose later batches filled the channel first.
             l->cv_room.wait(lk, [&] { return l->stop || l->in_ready < l->depth || w.seq == l->next_deliver; });
-            if (l->stop) { for (uint32_t r = b; r < nb; ++r) if (ws[r].owned) free_owned(&ws[r].bufs); return; }
+            if (l->stop) {
+                lk.unlock();
+                for (uint32_t r = b; r < nb; ++r) drop_work(l, ws[r]);
+                return;
+            }
             if (b == 0) l->stats.sample_time_ns += ns;
             if (d.status != AG_OK && l->fault.empty() && d.status != AG_ERR_SAMPLING && d.status != AG_ERR_VALUE)
                 l->fault = d.error;  // a broken worker poisons the loader; a bad batch does not
@@ -190,13 +267,14 @@ void worker_main(ag_loader *l, uint32_t idx) {
     }
 }
 
-int32_t deliver(ag_loader *l, std::unique_lock<std::mutex> &lk, ag_batch *out, bool waited) {
-    std::map<uint64_t, Done>::iterator it;
-    if (l->seeded) {
-        it = l->ready.find(l->next_deliver);
-    } else {
-        it = l->ready.find(l->arrival.front());
-    }
+bool has_deliverable(ag_loader *l) {
+    if (l->seeded) return l->ready.count(l->next_deliver) != 0;
+    return !l->arrival.empty();
+}
+
+// Caller holds l->m and has_deliverable(l) is true.
+int32_t deliver(ag_loader *l, ag_batch *out, bool waited) {
+    std::map<uint64_t, Done>::iterator it = l->seeded ? l->ready.find(l->next_deliver) : l->ready.find(l->arrival.front());
     Done d = std::move(it->second);
     const uint64_t seq = it->first;
     l->ready.erase(it);
@@ -208,7 +286,7 @@ int32_t deliver(ag_loader *l, std::unique_lock<std::mutex> &lk, ag_batch *out, b
     l->stats.total++;
     (waited ? l->stats.misses : l->stats.hits)++;
     if (d.status != AG_OK) {
-        if (d.batch.owned) free_owned(&d.batch.bufs);
+        if (d.batch.owned) pool_give(l, d.batch.bufs, false, nullptr);
         set_error("%s", d.error.c_str());
         return d.status;
     }
@@ -220,9 +298,50 @@ int32_t deliver(ag_loader *l, std::unique_lock<std::mutex> &lk, ag_batch *out, b
     return AG_OK;
 }
 
-bool has_deliverable(ag_loader *l) {
-    if (l->seeded) return l->ready.count(l->next_deliver) != 0;
-    return !l->arrival.empty();
+// Builds one work item (no locking); on failure nothing is left allocated.
+int32_t make_work(ag_loader *l, int64_t batch_idx, const uint32_t *seeds, uint64_t n_seeds, int32_t seeds_mem,
+                  const ag_subgraph_buffers *bufs, void *after_stream, Work *w) {
+    if (!seeds && n_seeds) return fail(AG_ERR_VALUE, "ag_loader_submit: null seeds");
+    // Range-check where seeds enter (Seeds::new, sampler.rs:230-239).
+    if (seeds_mem == AG_MEM_HOST)
+        for (uint64_t i = 0; i < n_seeds; ++i)
+            if ((uint64_t)seeds[i] >= l->g->num_nodes)
+                return fail(AG_ERR_SAMPLING, "seed node %u (position %llu) is out of range for %llu nodes",
+                            seeds[i], (unsigned long long)i, (unsigned long long)l->g->num_nodes);
+    w->batch_idx = batch_idx; w->n_seeds = n_seeds;
+    if (seeds_mem == AG_MEM_HOST) w->seeds.assign(seeds, seeds + n_seeds); else w->seeds_dev = seeds;
+    if (bufs) {
+        w->bufs = *bufs;
+        // Order the batch's kernels after whatever the caller's stream has queued
+        // (the previous user of recycled memory).
+        if (cudaEventCreateWithFlags(&w->after[0], cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventRecord(w->after[0], (cudaStream_t)after_stream) != cudaSuccess) {
+            if (w->after[0]) cudaEventDestroy(w->after[0]);
+            w->after[0] = nullptr;
+            return fail(AG_ERR_CUDA, "loader: event record failed: %s", cudaGetErrorString(cudaGetLastError()));
+        }
+    } else {
+        AG_TRY(pool_take(l, n_seeds, &w->bufs, &w->after[1]));
+        w->owned = true;
+    }
+    return AG_OK;
+}
+
+// Caller holds lk.  Waits for queue room like the reference's bounded channel;
+// gives up after the same 30 s the consumer side waits.
+int32_t enqueue(ag_loader *l, std::unique_lock<std::mutex> &lk, Work &w) {
+    const bool room = l->cv_space.wait_for(lk, std::chrono::seconds(30), [&] {
+        return l->stop || !l->fault.empty() || l->queue.size() < (size_t)8 * l->depth;
+    });
+    if (!room)
+        return fail(AG_ERR_TIMEOUT, "timed out waiting for room in the work queue (%u batches queued; is anything "
+                    "consuming results?)", 8 * l->depth);
+    if (l->stop) return fail(AG_ERR_SHUTDOWN, "loader is shut down");
+    if (!l->fault.empty()) return fail(AG_ERR_WORKER, "sampler worker failed: %s", l->fault.c_str());
+    w.seq = l->next_seq++;
+    l->stats.submitted++;
+    l->queue.push_back(std::move(w));
+    return AG_OK;
 }
 
 }  // namespace
@@ -280,54 +399,40 @@ extern "C" int32_t ag_loader_bounds(const ag_loader *l, uint64_t n_seeds, uint64
 
 extern "C" int32_t ag_loader_submit(ag_loader *l, int64_t batch_idx, const uint32_t *seeds, uint64_t n_seeds,
                                     int32_t seeds_mem, const ag_subgraph_buffers *bufs, void *after_stream) {
-    if (!l || (!seeds && n_seeds)) return fail(AG_ERR_VALUE, "ag_loader_submit: null argument");
-    // Range-check where seeds enter (Seeds::new, sampler.rs:230-239; prefetch.rs:389-397 of the bindings).
-    if (seeds_mem == AG_MEM_HOST)
-        for (uint64_t i = 0; i < n_seeds; ++i)
-            if ((uint64_t)seeds[i] >= l->g->num_nodes)
-                return fail(AG_ERR_SAMPLING, "seed node %u (position %llu) is out of range for %llu nodes",
-                            seeds[i], (unsigned long long)i, (unsigned long long)l->g->num_nodes);
-    Work w;
-    w.batch_idx = batch_idx; w.n_seeds = n_seeds;
-    if (seeds_mem == AG_MEM_HOST) w.seeds.assign(seeds, seeds + n_seeds); else w.seeds_dev = seeds;
+    if (!l) return fail(AG_ERR_VALUE, "ag_loader_submit: null loader");
     DeviceGuard guard(l->device);
     if (!guard.ok) return AG_ERR_CUDA;
-    if (bufs) w.bufs = *bufs;
-    else { AG_TRY(alloc_owned(l, n_seeds, &w.bufs)); w.owned = true; }
-    if (after_stream || bufs) {
-        // Order the batch's kernels after whatever the caller's stream has queued.
-        if (cudaEventCreateWithFlags(&w.after, cudaEventDisableTiming) != cudaSuccess ||
-            cudaEventRecord(w.after, (cudaStream_t)after_stream) != cudaSuccess) {
-            if (w.owned) free_owned(&w.bufs);
-            return fail(AG_ERR_CUDA, "loader: event record failed: %s", cudaGetErrorString(cudaGetLastError()));
-        }
-    }
+    Work w;
+    AG_TRY(make_work(l, batch_idx, seeds, n_seeds, seeds_mem, bufs, after_stream, &w));
     std::unique_lock<std::mutex> lk(l->m);
-    // Blocks while the work queue is full, like the reference's bounded channel; gives
-    // up after the same 30 s the consumer side waits, so a caller that submits and
-    // consumes on one thread and overfills the queue gets an error, not a hang.
-    const bool room = l->cv_space.wait_for(lk, std::chrono::seconds(30), [&] {
-        return l->stop || !l->fault.empty() || l->queue.size() < (size_t)8 * l->depth;
-    });
-    if (!room) {
-        lk.unlock();
-        if (w.after) cudaEventDestroy(w.after);
-        if (w.owned) free_owned(&w.bufs);
-        return fail(AG_ERR_TIMEOUT, "timed out waiting for room in the work queue (%u batches queued; is anything "
-                    "consuming results?)", 8 * l->depth);
-    }
-    if (l->stop || !l->fault.empty()) {
-        const std::string msg = l->stop ? "loader is shut down" : ("sampler worker failed: " + l->fault);
-        const int32_t code = l->stop ? AG_ERR_SHUTDOWN : AG_ERR_WORKER;
-        lk.unlock();
-        if (w.after) cudaEventDestroy(w.after);
-        if (w.owned) free_owned(&w.bufs);
-        return fail(code, "%s", msg.c_str());
-    }
-    w.seq = l->next_seq++;
-    l->stats.submitted++;
-    l->queue.push_back(std::move(w));
+    const int32_t rc = enqueue(l, lk, w);
+    lk.unlock();
+    if (rc != AG_OK) { drop_work(l, w); return rc; }
     l->cv_work.notify_one();
+    return AG_OK;
+}
+
+// Submits n batches in one call (submit_epoch of the reference loader,
+// _core.pyi:425).  batch b uses batch_idx[b], seeds[b], n_seeds[b] and bufs[b]
+// (bufs == NULL: pooled buffers).  *n_done receives how many were queued before
+// an error, if any.
+extern "C" int32_t ag_loader_submit_many(ag_loader *l, uint32_t n, const int64_t *batch_idx,
+                                         const uint32_t *const *seeds, const uint64_t *n_seeds, int32_t seeds_mem,
+                                         const ag_subgraph_buffers *bufs, void *after_stream, uint32_t *n_done) {
+    if (n_done) *n_done = 0;
+    if (!l || (n && (!batch_idx || !seeds || !n_seeds))) return fail(AG_ERR_VALUE, "ag_loader_submit_many: null argument");
+    DeviceGuard guard(l->device);
+    if (!guard.ok) return AG_ERR_CUDA;
+    for (uint32_t b = 0; b < n; ++b) {
+        Work w;
+        AG_TRY(make_work(l, batch_idx[b], seeds[b], n_seeds[b], seeds_mem, bufs ? &bufs[b] : nullptr, after_stream, &w));
+        std::unique_lock<std::mutex> lk(l->m);
+        const int32_t rc = enqueue(l, lk, w);
+        lk.unlock();
+        if (rc != AG_OK) { drop_work(l, w); return rc; }
+        if (n_done) *n_done = b + 1;
+        if ((b + 1) % l->group == 0 || b + 1 == n) l->cv_work.notify_all();
+    }
     return AG_OK;
 }
 
@@ -345,7 +450,38 @@ extern "C" int32_t ag_loader_next(ag_loader *l, int64_t timeout_ms, ag_batch *ou
             return fail(AG_ERR_TIMEOUT, "timed out waiting for a sampled batch");
         }
     }
-    return deliver(l, lk, out, waited);
+    return deliver(l, out, waited);
+}
+
+// Waits like ag_loader_next for the first batch, then also hands over every
+// further batch that is already deliverable, up to max_n.  A batch that failed
+// ends the call: the batches before it are returned (*n_out) with AG_OK, and
+// the failure is reported by the next call.
+extern "C" int32_t ag_loader_next_many(ag_loader *l, int64_t timeout_ms, uint32_t max_n, ag_batch *out,
+                                       uint32_t *n_out) {
+    if (!l || !out || !n_out || max_n == 0) return fail(AG_ERR_VALUE, "ag_loader_next_many: bad argument");
+    *n_out = 0;
+    std::unique_lock<std::mutex> lk(l->m);
+    bool waited = false;
+    const auto deadline = Clock::now() + std::chrono::milliseconds(timeout_ms < 0 ? 30000 : timeout_ms);
+    while (!has_deliverable(l)) {
+        if (l->stop) return fail(AG_ERR_SHUTDOWN, "loader is shut down");
+        if (!l->fault.empty()) return fail(AG_ERR_WORKER, "sampler worker failed: %s", l->fault.c_str());
+        waited = true;
+        if (l->cv_done.wait_until(lk, deadline) == std::cv_status::timeout && !has_deliverable(l)) {
+            if (l->stop) return fail(AG_ERR_SHUTDOWN, "loader is shut down");
+            return fail(AG_ERR_TIMEOUT, "timed out waiting for a sampled batch");
+        }
+    }
+    while (*n_out < max_n && has_deliverable(l)) {
+        // peek: a failed batch is only consumed when it is the first of the call
+        const auto it = l->seeded ? l->ready.find(l->next_deliver) : l->ready.find(l->arrival.front());
+        if (it->second.status != AG_OK && *n_out > 0) break;
+        const int32_t rc = deliver(l, &out[*n_out], waited && *n_out == 0);
+        if (rc != AG_OK) return rc;
+        ++*n_out;
+    }
+    return AG_OK;
 }
 
 extern "C" int32_t ag_loader_try_next(ag_loader *l, ag_batch *out) {
@@ -356,15 +492,19 @@ extern "C" int32_t ag_loader_try_next(ag_loader *l, ag_batch *out) {
         if (!l->fault.empty()) return fail(AG_ERR_WORKER, "sampler worker failed: %s", l->fault.c_str());
         return fail(AG_ERR_TIMEOUT, "no batch is ready");
     }
-    return deliver(l, lk, out, false);
+    return deliver(l, out, false);
 }
 
-extern "C" int32_t ag_loader_release_batch(ag_loader *l, ag_batch *batch) {
+// Hands a pooled batch back.  `stream` is the stream whose already-queued work
+// is the consumer's last use of the batch's memory; the next batch that gets the
+// buffers waits for it.
+extern "C" int32_t ag_loader_release_batch(ag_loader *l, ag_batch *batch, void *stream) {
     if (!l || !batch) return fail(AG_ERR_VALUE, "ag_loader_release_batch: null argument");
     if (batch->owned) {
         DeviceGuard guard(l->device);
-        free_owned(&batch->bufs);
+        pool_give(l, batch->bufs, true, (cudaStream_t)stream);
         batch->owned = 0;
+        batch->bufs = ag_subgraph_buffers{};
     }
     return AG_OK;
 }
@@ -391,9 +531,13 @@ extern "C" void ag_loader_free(ag_loader *l) {
     ag_loader_shutdown(l);
     for (std::thread &t : l->workers) if (t.joinable()) t.join();
     DeviceGuard guard(l->device);
-    for (Work &w : l->queue) { if (w.after) cudaEventDestroy(w.after); if (w.owned) free_owned(&w.bufs); }
-    for (auto &kv : l->ready) if (kv.second.batch.owned) free_owned(&kv.second.batch.bufs);
+    cudaDeviceSynchronize();
+    for (Work &w : l->queue) drop_work(l, w);
+    for (auto &kv : l->ready) if (kv.second.batch.owned) pool_give(l, kv.second.batch.bufs, false, nullptr);
     for (ag_sampler *s : l->samplers) ag_sampler_free(s);
     for (cudaStream_t s : l->streams) cudaStreamDestroy(s);
+    // Batches still held by a consumer keep their memory valid until now.
+    for (PoolSet &p : l->pool_free) { if (p.last_use) cudaEventDestroy(p.last_use); cudaFree(p.base); }
+    for (auto &kv : l->pool_live) cudaFree(kv.second.base);
     delete l;
 }

@@ -4,25 +4,27 @@
 // (crates/aethergraph-core/src/loader/sampler.rs:845-961 with the hop loop at
 // :754-842 and the per-node dispatch at :1178-1235), but as a short chain of
 // data-parallel kernels instead of one sequential loop.  A batch with H hops
-// is H + 3 launches:
+// is 2H + 3 launches:
 //
 //   insert_seeds   every seed is inserted into a hash table keyed by vertex id
 //                  with atomicMin(position): the smallest position that names a
 //                  vertex is its first sighting.
-//   expand(s)      s = 0 .. H.  The items of stage s are the seeds (s = 0) or
+//   assign(s)      s = 0 .. H.  The items of stage s are the seeds (s = 0) or
 //                  the edges hop s - 1 emitted, in position order.  One
 //                  single-pass scan over them turns the first-sighting flags
 //                  into local ids (= discovery order, exactly the order the
 //                  sequential reference assigns them in) and appends the new
 //                  vertices to `nodes`; the same scan carries how many edges and
-//                  how many RNG draws each new vertex needs at hop s.  The tile
-//                  then expands its own new vertices straight away: a group of
-//                  lanes per vertex reproduces the reference's choice of row
-//                  positions — take-all (:1312-1328), Floyd (:1332-1380), with
-//                  replacement (:1289-1308) or the weighted Efraimidis-Spirakis
-//                  keys (:1418-1469) — writes the edges of hop s at their
-//                  scanned slots and inserts the destinations into the table as
-//                  the items of stage s + 1.
+//                  how many RNG draws each new vertex needs at hop s, so the new
+//                  vertices leave the kernel as a frontier with their row
+//                  bounds, edge slots and draw offsets attached.
+//   pick(s)        s = 0 .. H - 1.  A group of lanes per frontier vertex
+//                  reproduces the reference's choice of row positions — take-all
+//                  (:1312-1328), Floyd (:1332-1380), with replacement
+//                  (:1289-1308) or the weighted Efraimidis-Spirakis keys
+//                  (:1418-1469) — writes the edges of hop s at their scanned
+//                  slots and inserts the destinations into the table as the
+//                  items of stage s + 1.
 //   finalize       every edge and seed reads its endpoint's final local id from
 //                  the table; the int64 views the Python API exposes are written.
 //
@@ -48,7 +50,8 @@ namespace ag {
 
 namespace {
 
-constexpr int kTile = 512;      // items per tile = threads per block of the expand kernel
+constexpr int kTile = 512;      // items per tile = threads per block of the assign kernel
+constexpr int kPickThreads = 256;
 constexpr int kLargeK = 1024;   // largest fanout the k > 32 path keeps in shared memory
 
 enum : int { kModeUniform = 0, kModeReplace = 1, kModeWeighted = 2 };
@@ -82,6 +85,8 @@ struct SampleParams {
     // scratch
     uint32_t *slot_of_seed;
     uint32_t *slot_of_edge;
+    FrontierEntry *frontier;
+    uint64_t frontier_cap;
 };
 
 // Row bounds with the reference's guard (graph/csr.rs:318-335): an inverted
@@ -161,7 +166,8 @@ __device__ __forceinline__ void pick_small(const SampleParams &p, uint32_t hop, 
     const uint32_t t = threadIdx.x % G;
     const uint32_t gshift = (threadIdx.x & 31) & ~(G - 1);
     const uint32_t gmask = (G == 32) ? 0xffffffffu : ((1u << G) - 1u);
-    for (uint32_t base = 0; base < n; base += kTile / G) {
+    // Grid-stride over the frontier; the loop bound is block-uniform.
+    for (uint32_t base = blockIdx.x * (kPickThreads / G); base < n; base += gridDim.x * (kPickThreads / G)) {
         const uint32_t j = base + threadIdx.x / G;
         const bool active = j < n;
         FrontierEntry fe{};
@@ -197,14 +203,13 @@ __device__ __forceinline__ void pick_small(const SampleParams &p, uint32_t hop, 
     }
 }
 
-// Fanout > 32: one warp per vertex (the first four warps of the tile); finished
-// picks live in shared memory so later slots can be checked against all earlier ones.
+// Fanout > 32: one warp per vertex (four warps per block); finished picks live
+// in shared memory so later slots can be checked against all earlier ones.
 __device__ __forceinline__ void pick_large(const SampleParams &p, uint32_t hop, uint32_t k, uint32_t edges_before,
                                            const FrontierEntry *fes, uint32_t n, uint32_t *s_picks) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (warp >= 4) return;
     uint32_t *picks = s_picks + warp * kLargeK;
-    for (uint32_t j = warp; j < n; j += 4) {
+    for (uint32_t j = blockIdx.x * 4 + warp; j < n; j += gridDim.x * 4) {
         const FrontierEntry fe = fes[j];
         const uint32_t deg = fe.deg;
         uint32_t take;
@@ -252,7 +257,7 @@ __device__ __forceinline__ void pick_weighted(const SampleParams &p, uint32_t ho
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (k == 0) return;
     const double inf = __longlong_as_double(0x7FF0000000000000ll);
-    for (uint32_t j = warp; j < n; j += kTile / 32) {
+    for (uint32_t j = blockIdx.x * (kPickThreads / 32) + warp; j < n; j += gridDim.x * (kPickThreads / 32)) {
         const FrontierEntry fe = fes[j];
         const uint32_t deg = fe.deg;
         if (deg == 0) continue;
@@ -300,16 +305,14 @@ __device__ __forceinline__ void pick_weighted(const SampleParams &p, uint32_t ho
     }
 }
 
-// One stage: assign local ids to the first sightings among the stage's items,
-// then (has_next) expand the new vertices at hop `stage` with fanout k.
-template <int G, int PICK>
+// One stage: assign local ids to the first sightings among the stage's items
+// and (has_next) queue the new vertices, with their row bounds, edge slots and
+// draw offsets, as the frontier the pick kernel of hop `stage` expands.
 __global__ void __launch_bounds__(kTile)
-k_expand(const SampleParams *__restrict__ pa, uint32_t stage, uint32_t k, int has_next) {
+k_assign(const SampleParams *__restrict__ pa, uint32_t stage, uint32_t k, int has_next) {
     __shared__ uint32_t s_tile;
     __shared__ ScanVal s_warp[kTile / 32];
-    __shared__ ScanVal s_prefix, s_total;
-    __shared__ FrontierEntry s_fe[kTile];
-    __shared__ uint32_t s_picks[PICK == kPickLarge ? 4 : 1][PICK == kPickLarge ? kLargeK : 1];
+    __shared__ ScanVal s_prefix;
 
     const SampleParams &p = pa[blockIdx.y];
     BatchState *bs = p.state;
@@ -375,7 +378,6 @@ k_expand(const SampleParams *__restrict__ pa, uint32_t stage, uint32_t k, int ha
             const ScanVal prefix = lookback_exclusive(p.tiles, tile, p.epoch_base + stage, block_total, lane, &bs->error);
             if (lane == 0) {
                 s_prefix = prefix;
-                s_total = block_total;
                 if (tile == n_tiles - 1) {
                     // Totals of the stage: hand over to the next one.
                     const ScanVal tot = prefix + block_total;
@@ -398,9 +400,10 @@ k_expand(const SampleParams *__restrict__ pa, uint32_t stage, uint32_t k, int ha
             const ScanVal excl = ScanVal{base.flags + incl.flags - v.flags, base.take + incl.take - v.take,
                                          base.draws + incl.draws - v.draws};
             const uint32_t local = si.n_nodes + excl.flags;
-            if ((uint64_t)local >= p.cap_nodes || (uint64_t)local >= kMaxPos) {
+            if ((uint64_t)local >= p.cap_nodes || (uint64_t)local >= kMaxPos ||
+                (has_next && (uint64_t)excl.flags >= p.frontier_cap)) {
                 atomicOr(&bs->error, kErrCapacity);
-                if (has_next) s_fe[excl.flags - s_prefix.flags] = FrontierEntry{};  // deg 0: expands to nothing
+                if (has_next && (uint64_t)excl.flags < p.frontier_cap) p.frontier[excl.flags] = FrontierEntry{};
             } else {
                 p.nodes[local] = id;
                 p.table.slots[slot] = ((uint64_t)id << 32) | enc_final(gen, local);  // readers accept either form
@@ -412,17 +415,25 @@ k_expand(const SampleParams *__restrict__ pa, uint32_t stage, uint32_t k, int ha
                     fe.local = local;
                     fe.deg = (uint32_t)deg;
                     fe.ebase = excl.take;
-                    s_fe[excl.flags - s_prefix.flags] = fe;
+                    p.frontier[excl.flags] = fe;
                 }
             }
         }
-        if (!has_next) continue;
-        __syncthreads();
-        const uint32_t n_new = s_total.flags;
-        if constexpr (PICK == kPickWeighted) pick_weighted(p, stage, k, edges_before_next, s_fe, n_new);
-        else if constexpr (PICK == kPickLarge) pick_large(p, stage, k, edges_before_next, s_fe, n_new, &s_picks[0][0]);
-        else pick_small<G>(p, stage, k, edges_before_next, s_fe, n_new);
     }
+}
+
+// Hop `hop`: expand the frontier stage `hop` queued (stage[hop + 1] holds its
+// size and where the hop's edges start).  The lanes of the whole grid share the
+// frontier, so even a hop with few vertices spreads over the GPU.
+template <int G, int PICK>
+__global__ void __launch_bounds__(PICK == kPickLarge ? 128 : kPickThreads)
+k_pick(const SampleParams *__restrict__ pa, uint32_t hop, uint32_t k) {
+    __shared__ uint32_t s_picks[PICK == kPickLarge ? 4 : 1][PICK == kPickLarge ? kLargeK : 1];
+    const SampleParams &p = pa[blockIdx.y];
+    const StageInfo nx = p.state->stage[hop + 1];
+    if constexpr (PICK == kPickWeighted) pick_weighted(p, hop, k, nx.n_edges, p.frontier, nx.frontier_n);
+    else if constexpr (PICK == kPickLarge) pick_large(p, hop, k, nx.n_edges, p.frontier, nx.frontier_n, &s_picks[0][0]);
+    else pick_small<G>(p, hop, k, nx.n_edges, p.frontier, nx.frontier_n);
 }
 
 // --------------------------------------------------------------- finalize --
@@ -478,15 +489,26 @@ uint64_t next_pow2(uint64_t v) {
     return p;
 }
 
-template <int PICK>
-void launch_expand(uint32_t G, dim3 grid, cudaStream_t st, const SampleParams *pa, uint32_t stage, uint32_t k,
-                   int has_next) {
-    if (PICK != kPickSmall) { k_expand<32, PICK><<<grid, kTile, 0, st>>>(pa, stage, k, has_next); return; }
-    switch (G) {
-        case 4: k_expand<4, kPickSmall><<<grid, kTile, 0, st>>>(pa, stage, k, has_next); break;
-        case 8: k_expand<8, kPickSmall><<<grid, kTile, 0, st>>>(pa, stage, k, has_next); break;
-        case 16: k_expand<16, kPickSmall><<<grid, kTile, 0, st>>>(pa, stage, k, has_next); break;
-        default: k_expand<32, kPickSmall><<<grid, kTile, 0, st>>>(pa, stage, k, has_next); break;
+void launch_pick(int mode, uint32_t k, uint64_t frontier_est, uint32_t n_batches, cudaStream_t st,
+                 const SampleParams *pa, uint32_t hop) {
+    // About two waves of resident blocks over the whole group; the lanes stride beyond.
+    auto blocks_for = [&](uint64_t vertices, uint64_t per_block) {
+        const uint64_t b = (vertices + per_block - 1) / per_block;
+        return (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>(b, std::max<uint64_t>(1, (uint64_t)kSMs * 16 / n_batches)));
+    };
+    if (mode == kModeWeighted) {
+        k_pick<32, kPickWeighted><<<dim3(blocks_for(frontier_est, kPickThreads / 32), n_batches), kPickThreads, 0, st>>>(pa, hop, k);
+    } else if (k > 32) {
+        k_pick<32, kPickLarge><<<dim3(blocks_for(frontier_est, 4), n_batches), 128, 0, st>>>(pa, hop, k);
+    } else {
+        const uint32_t G = k <= 4 ? 4 : k <= 8 ? 8 : k <= 16 ? 16 : 32;
+        const dim3 grid(blocks_for(frontier_est, kPickThreads / G), n_batches);
+        switch (G) {
+            case 4: k_pick<4, kPickSmall><<<grid, kPickThreads, 0, st>>>(pa, hop, k); break;
+            case 8: k_pick<8, kPickSmall><<<grid, kPickThreads, 0, st>>>(pa, hop, k); break;
+            case 16: k_pick<16, kPickSmall><<<grid, kPickThreads, 0, st>>>(pa, hop, k); break;
+            default: k_pick<32, kPickSmall><<<grid, kPickThreads, 0, st>>>(pa, hop, k); break;
+        }
     }
 }
 
@@ -510,6 +532,8 @@ struct ag_sampler {
     uint64_t table_cap = 0, n_tiles = 0;
     // scratch (device), each `group` times the per-batch size
     uint64_t *table = nullptr;
+    FrontierEntry *frontier = nullptr;
+    uint64_t max_frontier = 0;
     uint32_t *slot_of_seed = nullptr, *slot_of_edge = nullptr;
     TileDesc *tiles = nullptr;
     BatchState *state = nullptr;
@@ -560,7 +584,8 @@ void compute_bounds(const ag_sampler *s, uint64_t n_seeds, uint64_t *max_nodes, 
 }
 
 void free_scratch(ag_sampler *s) {
-    cudaFree(s->table);
+    cudaFree(s->table); cudaFree(s->frontier);
+    s->frontier = nullptr;
     cudaFree(s->slot_of_seed); cudaFree(s->slot_of_edge); cudaFree(s->tiles);
     cudaFree(s->seeds_dev);
     if (s->seeds_pinned) cudaFreeHost(s->seeds_pinned);
@@ -583,6 +608,9 @@ int32_t ensure_scratch(ag_sampler *s, uint64_t n_seeds) {
                     (unsigned long long)s->max_hop_edges, (unsigned long long)kMaxPos - 1);
     s->table_cap = std::max<uint64_t>(1024, next_pow2(2 * s->max_nodes));
     AG_CUDA(cudaMalloc(&s->table, G * s->table_cap * 8));
+    // the frontier of a hop holds at most the vertices the previous stage found
+    s->max_frontier = std::max<uint64_t>(std::min<uint64_t>(std::max(cap, s->max_hop_edges), s->g->num_nodes), 1);
+    AG_CUDA(cudaMalloc(&s->frontier, G * s->max_frontier * sizeof(FrontierEntry)));
     AG_CUDA(cudaMalloc(&s->slot_of_seed, G * cap * 4));
     AG_CUDA(cudaMalloc(&s->slot_of_edge, G * std::max<uint64_t>(s->max_edges, 1) * 4));
     s->n_tiles = std::max<uint64_t>(std::max(cap, s->max_hop_edges) / kTile + 2, 2);
@@ -787,6 +815,8 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
         p.counts = s->counts_dev + b;
         p.slot_of_seed = s->slot_of_seed + (uint64_t)b * s->cap_seeds;
         p.slot_of_edge = s->slot_of_edge + (uint64_t)b * ecap;
+        p.frontier = s->frontier + (uint64_t)b * s->max_frontier;
+        p.frontier_cap = s->max_frontier;
         s->params_host[b] = p;
         uint64_t bn, be;
         compute_bounds(s, n, &bn, &be, nullptr);
@@ -829,10 +859,11 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
         const bool has_next = stage < H;
         const uint32_t k = has_next ? s->cfg.fanout[stage] : 0;
         const uint64_t expect = (stage && s->est_items[stage]) ? std::min(items, s->est_items[stage]) : items;
-        const dim3 grid(tiles_for(expect), n_batches);
-        if (s->mode == kModeWeighted) launch_expand<kPickWeighted>(32, grid, st, pa, stage, k, has_next);
-        else if (k > 32) launch_expand<kPickLarge>(32, grid, st, pa, stage, k, has_next);
-        else launch_expand<kPickSmall>(k <= 4 ? 4 : k <= 8 ? 8 : k <= 16 ? 16 : 32, grid, st, pa, stage, k, has_next);
+        k_assign<<<dim3(tiles_for(expect), n_batches), kTile, 0, st>>>(pa, stage, k, has_next ? 1 : 0);
+        if (has_next && k) {
+            // the new vertices of this stage are at most its items
+            launch_pick(s->mode, k, std::min<uint64_t>(expect, g->num_nodes), n_batches, st, pa, stage);
+        }
         items = std::min<uint64_t>(items, g->num_nodes) * k;
     }
     {

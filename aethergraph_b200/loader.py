@@ -9,8 +9,10 @@ seed they come back as they finish.  `None` is returned only after `shutdown()`;
 a worker failure raises RuntimeError, a 30 s wait TimeoutError.
 
 The batches are born in GPU memory: `subgraph.*_t` and `features` are CUDA
-tensors.  Pass `host_features=True` to get the feature block as a host numpy
-array the way the reference returns it.
+tensors that view one pooled device allocation per batch.  The allocation goes
+back to the loader's pool when the last tensor or subgraph object that refers
+to it is dropped.  Pass `host_features=True` to get the feature block as a host
+numpy array the way the reference returns it.
 """
 from __future__ import annotations
 
@@ -28,6 +30,8 @@ from .graph import CsrGraph
 from .sampler import SampledSubgraph, SamplingConfig, _Buffers, _check_config, coerce_seeds
 
 __all__ = ["NeighborLoader", "PrefetchStats"]
+
+_FETCH = 32  # batches taken from the native queue per call
 
 
 class PrefetchStats:
@@ -48,10 +52,35 @@ class PrefetchStats:
                 "sample_time_ns": self.sample_time_ns, "feature_load_time_ns": self.feature_load_time_ns}
 
 
+class _Lease:
+    """Holds one pooled batch; gives it back to the loader when nothing refers to it
+    any more.  The release records the consumer's current stream, so kernels
+    already queued on it finish before the memory is written again."""
+
+    __slots__ = ("loader", "batch")
+
+    def __init__(self, loader: "NeighborLoader", batch: _lib.Batch):
+        self.loader, self.batch = loader, batch
+
+    def __del__(self):
+        ld = self.loader
+        if ld is None or not ld._h:
+            return
+        try:
+            import torch
+
+            st = torch.cuda.current_stream(ld._dev).cuda_stream
+            _lib.lib().ag_loader_release_batch(ld._h, C.byref(self.batch), st)
+        except Exception:
+            pass
+
+
 class NeighborLoader:
     def __init__(self, graph: CsrGraph, config: SamplingConfig, prefetch_depth: int = 2,
                  sampler_threads: int = 1, *, features: FeatureStore | None = None,
                  host_features: bool = False, profiling: bool = False, group: int = 8):
+        import torch
+
         _check_config(graph, config)
         if prefetch_depth < 1:
             raise ValueError("prefetch_depth must be >= 1")
@@ -66,13 +95,13 @@ class NeighborLoader:
         _lib.check(_lib.lib().ag_loader_create(graph._h, features._h if features is not None else None,
                                                C.byref(cfg), int(self._seeded), prefetch_depth, sampler_threads,
                                                max(1, int(group)), int(profiling), C.byref(self._h)))
-        import torch
-
         self._dev = torch.device("cuda", graph.device)
-        self._bounds: dict[int, tuple[int, int]] = {}
+        self._dim = features.feature_dim if features is not None else None
         self._lock = threading.Lock()
         self._next_seq = 0
-        self._inflight: dict[int, tuple[_Buffers, np.ndarray]] = {}
+        self._seeds: dict[int, np.ndarray] = {}
+        self._fetched: list = []          # batches already taken from the native queue
+        self._fetch_buf = (_lib.Batch * _FETCH)()
         self._closed = False
 
     @staticmethod
@@ -86,7 +115,7 @@ class NeighborLoader:
     # -- properties --------------------------------------------------------
     @property
     def feature_dim(self) -> int | None:
-        return self.features.feature_dim if self.features is not None else None
+        return self._dim
 
     @property
     def has_features(self) -> bool:
@@ -103,48 +132,63 @@ class NeighborLoader:
     # -- producer side -----------------------------------------------------
     def submit(self, batch_idx: int, seeds) -> None:
         """Queue a batch.  `batch_idx` is echoed back by `next_batch()`; any value is accepted."""
-        import torch
-
         s = coerce_seeds(seeds, self.graph.num_nodes)
-        bound = self._bounds.get(len(s))
-        if bound is None:
-            mn, me = C.c_uint64(), C.c_uint64()
-            _lib.check(_lib.lib().ag_loader_bounds(self._h, len(s), C.byref(mn), C.byref(me)))
-            bound = self._bounds[len(s)] = (mn.value, me.value)
-        dev = self._dev
-        bufs = _Buffers(dev, bound[0], bound[1], len(s), self.config.track_edge_ids, self.feature_dim)
-        after = torch.cuda.current_stream(dev).cuda_stream
         with self._lock:
             # The C call blocks while the work queue is full; the lock keeps the
             # Python-side sequence counter in step with the library's.
             seq = self._next_seq
-            self._inflight[seq] = (bufs, s)  # in place before a worker can finish the batch
+            self._seeds[seq] = s  # in place before a worker can finish the batch
             rc = _lib.lib().ag_loader_submit(self._h, int(batch_idx), s.ctypes.data if len(s) else None,
-                                             len(s), _lib.AG_MEM_HOST, C.byref(bufs.c), after)
+                                             len(s), _lib.AG_MEM_HOST, None, None)
             if rc != _lib.AG_OK:
-                del self._inflight[seq]
+                del self._seeds[seq]
                 _lib.check(rc)
             self._next_seq += 1
 
     def submit_epoch(self, batches) -> None:
-        for i, b in enumerate(batches):
-            self.submit(i, b)
+        """Queue batches 0 .. len(batches) - 1 in one native call."""
+        seeds = [coerce_seeds(b, self.graph.num_nodes) for b in batches]
+        n = len(seeds)
+        if n == 0:
+            return
+        idx = (C.c_int64 * n)(*range(n))
+        ptrs = (C.c_void_p * n)(*[s.ctypes.data if len(s) else None for s in seeds])
+        lens = (C.c_uint64 * n)(*[len(s) for s in seeds])
+        done = C.c_uint32()
+        with self._lock:
+            first = self._next_seq
+            for i, s in enumerate(seeds):
+                self._seeds[first + i] = s
+            rc = _lib.lib().ag_loader_submit_many(self._h, n, idx, ptrs, lens, _lib.AG_MEM_HOST, None, None,
+                                                  C.byref(done))
+            self._next_seq += done.value
+            for i in range(done.value, n):
+                del self._seeds[first + i]
+            _lib.check(rc)
 
     # -- consumer side -----------------------------------------------------
     def _take(self, blocking: bool):
-        if self._closed:
-            return None
-        b = _lib.Batch()
-        rc = (_lib.lib().ag_loader_next(self._h, -1, C.byref(b)) if blocking
-              else _lib.lib().ag_loader_try_next(self._h, C.byref(b)))
-        if rc == _lib.AG_ERR_SHUTDOWN:
-            return None
-        if rc == _lib.AG_ERR_TIMEOUT and not blocking:
-            return None
-        _lib.check(rc)
-        bufs, seeds = self._inflight.pop(b.seq)
-        sg = SampledSubgraph(bufs, b.counts, seeds)
-        return int(b.batch_idx), sg
+        if not self._fetched:
+            if self._closed:
+                return None
+            got = C.c_uint32()
+            if blocking:
+                rc = _lib.lib().ag_loader_next_many(self._h, -1, _FETCH, self._fetch_buf, C.byref(got))
+            else:
+                rc = _lib.lib().ag_loader_try_next(self._h, self._fetch_buf)
+                got.value = 1 if rc == _lib.AG_OK else 0
+            if rc == _lib.AG_ERR_SHUTDOWN:
+                return None
+            if rc == _lib.AG_ERR_TIMEOUT and not blocking:
+                return None
+            _lib.check(rc)
+            for i in range(got.value - 1, -1, -1):  # reversed: pop() hands them out in order
+                b = _lib.Batch.from_buffer_copy(self._fetch_buf[i])
+                self._fetched.append(b)
+        b = self._fetched.pop()
+        seeds = self._seeds.pop(b.seq)
+        bufs = _Buffers(b.bufs, _Lease(self, b), self._dev, self._dim)
+        return int(b.batch_idx), SampledSubgraph(bufs, b.counts, seeds)
 
     def next_batch(self):
         """`(batch_idx, subgraph, features)`, or None after `shutdown()`."""
@@ -189,6 +233,7 @@ class NeighborLoader:
         h = getattr(self, "_h", None)
         if h:
             try:
+                self._fetched = []
                 _lib.lib().ag_loader_free(h)
             except Exception:
                 pass

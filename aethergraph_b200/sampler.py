@@ -128,27 +128,42 @@ def coerce_seeds(seeds, num_nodes: int) -> np.ndarray:
     return a
 
 
-class _Buffers:
-    """Device output buffers of one batch, carved from three torch allocations."""
+class _DevArray:
+    """A window of device memory for `torch.as_tensor` (CUDA array interface).  The
+    tensor made from it keeps this object — and through `owner` the allocation —
+    alive, so a view may outlive the batch object it came from."""
 
-    def __init__(self, device, cap_nodes: int, cap_edges: int, cap_seeds: int, track_eids: bool,
-                 feature_dim: int | None):
+    __slots__ = ("__cuda_array_interface__", "owner")
+
+    def __init__(self, ptr: int, shape: tuple, typestr: str, owner):
+        self.__cuda_array_interface__ = {"shape": shape, "typestr": typestr, "data": (ptr, False), "version": 2}
+        self.owner = owner
+
+
+class _Buffers:
+    """Device output buffers of one batch: the pointer block handed to the C ABI
+    plus whatever keeps the memory alive (torch tensors allocated here, or a lease
+    on one of the loader's pooled sets).  Tensor views are made on demand."""
+
+    __slots__ = ("c", "owner", "device", "dim")
+
+    def __init__(self, c: _lib.SubgraphBuffers, owner, device, dim: int | None):
+        self.c, self.owner, self.device, self.dim = c, owner, device, dim
+
+    @staticmethod
+    def alloc(device, cap_nodes: int, cap_edges: int, cap_seeds: int, track_eids: bool,
+              feature_dim: int | None) -> "_Buffers":
         import torch
 
-        self.cap_nodes, self.cap_edges, self.cap_seeds = cap_nodes, cap_edges, cap_seeds
         cn, ce, cs = _align4(cap_nodes), _align4(cap_edges), _align4(cap_seeds)
-        self._cn, self._ce, self._cs = cn, ce, cs
         # One allocation per batch: the int64 arrays first (8-byte aligned), the
-        # 32-bit arrays behind them.  Views are made only when an accessor asks.
+        # 32-bit arrays behind them.
         n64 = cn + 2 * ce + cs + (ce if track_eids else 0)
         n32 = cn + 4 * ce + cs
-        self.arena = torch.empty(n64 + (n32 + 1) // 2, dtype=torch.int64, device=device)
-        self.a64 = self.arena[:n64]
-        self.a32 = self.arena[n64:].view(torch.int32)[:n32]
-        self.track_eids = track_eids
-        self.x = (torch.empty((max(cap_nodes, 1), feature_dim), dtype=torch.float32, device=device)
-                  if feature_dim is not None else None)
-        base64 = self.arena.data_ptr()
+        arena = torch.empty(n64 + (n32 + 1) // 2, dtype=torch.int64, device=device)
+        x = (torch.empty((max(cap_nodes, 1), feature_dim), dtype=torch.float32, device=device)
+             if feature_dim is not None else None)
+        base64 = arena.data_ptr()
         base32 = base64 + 8 * n64
         b = _lib.SubgraphBuffers()
         b.cap_nodes, b.cap_edges, b.cap_seeds = max(cap_nodes, 1), max(cap_edges, 1), max(cap_seeds, 1)
@@ -163,46 +178,33 @@ class _Buffers:
         b.seed_index = base64 + 8 * (cn + 2 * ce)
         b.edge_ids = base64 + 8 * (cn + 2 * ce + cs) if track_eids else None
         b.e_id = None  # int64(edge id) has the same bits as the u64 the kernel writes
-        b.x = self.x.data_ptr() if self.x is not None else None
-        self.c = b
+        b.x = x.data_ptr() if x is not None else None
+        return _Buffers(b, (arena, x), device, feature_dim)
 
-    # lazily built views of the arena
-    @property
-    def nodes(self):
-        return self.a32[:self._cn]
+    def view(self, ptr, shape: tuple, typestr: str):
+        import torch
 
-    @property
-    def edge_src(self):
-        return self.a32[self._cn:self._cn + self._ce]
+        n = 1
+        for s in shape:
+            n *= s
+        if not ptr or n == 0:
+            dt = {"<i4": torch.int32, "<i8": torch.int64, "<f4": torch.float32}[typestr]
+            return torch.empty(shape, dtype=dt, device=self.device)
+        return torch.as_tensor(_DevArray(ptr, shape, typestr, self.owner), device=self.device)
 
-    @property
-    def edge_dst(self):
-        return self.a32[self._cn + self._ce:self._cn + 2 * self._ce]
-
-    @property
-    def n_id(self):
-        return self.a64[:self._cn]
-
-    @property
-    def edge_index_local(self):
-        return self.a64[self._cn:self._cn + 2 * self._ce]
-
-    @property
-    def seed_index(self):
-        o = self._cn + 2 * self._ce
-        return self.a64[o:o + self._cs]
-
-    @property
-    def edge_ids(self):
-        if not self.track_eids:
-            return None
-        o = self._cn + 2 * self._ce + self._cs
-        return self.a64[o:o + self._ce]
+    def record_stream(self, stream) -> None:
+        """Torch-allocated buffers only: mark `stream` as a user of the memory."""
+        if isinstance(self.owner, tuple):
+            for t in self.owner:
+                if t is not None:
+                    t.record_stream(stream)
 
 
 def _u32_to_i64(t):
     """int32 tensor holding u32 bit patterns -> int64 values."""
-    return t.to(dtype=__import__("torch").int64) & 0xFFFFFFFF
+    import torch
+
+    return t.to(dtype=torch.int64) & 0xFFFFFFFF
 
 
 class SampledSubgraph:
@@ -212,15 +214,17 @@ class SampledSubgraph:
     is the CSR position of the stored edge row1 -> row0.  The `*_t` accessors
     return the same data as CUDA tensors without a copy."""
 
+    __slots__ = ("_b", "_n", "_e", "_s", "_nodes_per_hop", "_edges_per_hop", "draws", "_seeds", "_cache")
+
     def __init__(self, bufs: _Buffers, counts: _lib.SampleCounts, seeds: np.ndarray):
         self._b = bufs
         self._n, self._e, self._s = counts.num_nodes, counts.num_edges, counts.num_seeds
         h = counts.num_hops
-        self._nodes_per_hop = [int(counts.nodes_per_hop[i]) for i in range(h + 1)]
-        self._edges_per_hop = [int(counts.edges_per_hop[i]) for i in range(h)]
-        self.draws = int(counts.draws)
+        self._nodes_per_hop = counts.nodes_per_hop[:h + 1]
+        self._edges_per_hop = counts.edges_per_hop[:h]
+        self.draws = counts.draws
         self._seeds = seeds
-        self._cache: dict[str, Any] = {}
+        self._cache = None
 
     # counts
     @property
@@ -241,51 +245,59 @@ class SampledSubgraph:
     # device tensors
     @property
     def nodes_t(self):
-        return self._b.n_id[:self._n]
+        return self._b.view(self._b.c.n_id, (self._n,), "<i8")
 
     @property
     def edge_index_local_t(self):
-        return self._b.edge_index_local[:2 * self._e].view(2, self._e)
+        return self._b.view(self._b.c.edge_index_local, (2, self._e), "<i8")
 
     @property
     def edge_index_t(self):
         import torch
 
-        return torch.stack([_u32_to_i64(self._b.edge_dst[:self._e]), _u32_to_i64(self._b.edge_src[:self._e])])
+        b = self._b
+        return torch.stack([_u32_to_i64(b.view(b.c.edge_dst, (self._e,), "<i4")),
+                            _u32_to_i64(b.view(b.c.edge_src, (self._e,), "<i4"))])
 
     @property
     def edge_ids_t(self):
-        return None if self._b.edge_ids is None else self._b.edge_ids[:self._e]
+        if not self._b.c.edge_ids:
+            return None
+        return self._b.view(self._b.c.edge_ids, (self._e,), "<i8")
 
     @property
     def seed_indices_t(self):
-        return self._b.seed_index[:self._s]
+        return self._b.view(self._b.c.seed_index, (self._s,), "<i8")
 
     @property
     def x(self):
         """Gathered feature rows [num_nodes, dim] (CUDA float32), or None."""
-        return None if self._b.x is None else self._b.x[:self._n]
+        if not self._b.c.x:
+            return None
+        return self._b.view(self._b.c.x, (self._n, self._b.dim), "<f4")
 
-    def raw_u32(self) -> dict[str, np.ndarray]:
+    def raw_u32(self) -> dict[str, Any]:
         """The core arrays in the reference's native widths (SampledSubgraph,
         crates/aethergraph-core/src/loader/sampler.rs:1512-1543), as host numpy."""
         b, n, e, s = self._b, self._n, self._e, self._s
-        a32 = b.a32.cpu().numpy().view(np.uint32)
-        cn, ce = _align4(b.cap_nodes), _align4(b.cap_edges)
-        o = 0
-        out = {"nodes": a32[o:o + n].copy()}; o += cn
-        for name in ("edge_src", "edge_dst", "src_local", "dst_local"):
-            out[name] = a32[o:o + e].copy(); o += ce
-        out["seed_locals"] = a32[o:o + s].copy()
-        out["edge_ids"] = (b.edge_ids[:e].cpu().numpy().view(np.uint64).copy()
-                           if b.edge_ids is not None else None)
+
+        def u32(ptr, count):
+            return b.view(ptr, (count,), "<i4").cpu().numpy().view(np.uint32)
+
+        out = {"nodes": u32(b.c.nodes, n), "edge_src": u32(b.c.edge_src, e), "edge_dst": u32(b.c.edge_dst, e),
+               "src_local": u32(b.c.src_local, e), "dst_local": u32(b.c.dst_local, e),
+               "seed_locals": u32(b.c.seed_locals, s)}
+        t = self.edge_ids_t
+        out["edge_ids"] = t.cpu().numpy().view(np.uint64) if t is not None else None
         out["num_sampled_nodes"] = np.array(self._nodes_per_hop, dtype=np.uint64)
         out["num_sampled_edges"] = np.array(self._edges_per_hop, dtype=np.uint64)
-        out["draws"] = self.draws
+        out["draws"] = int(self.draws)
         return out
 
-    # numpy accessors of the reference API
+    # numpy accessors of the reference API (cached: the same array on every access)
     def _np(self, key, make):
+        if self._cache is None:
+            self._cache = {}
         if key not in self._cache:
             self._cache[key] = make()
         return self._cache[key]
@@ -342,27 +354,16 @@ class SampledSubgraph:
         return f"SampledSubgraph(num_nodes={self._n}, num_edges={self._e}, num_seeds={self._s})"
 
 
-class _Pending:
-    """A batch queued on the GPU; `result()` waits for it."""
-
-    def __init__(self, handle: "_Handle", bufs: _Buffers, seeds: np.ndarray):
-        self._handle, self._bufs, self._seeds = handle, bufs, seeds
-        self._done: SampledSubgraph | None = None
-
-    def result(self) -> SampledSubgraph:
-        if self._done is None:
-            counts = _lib.SampleCounts()
-            _lib.check(_lib.lib().ag_sample_wait(self._handle.h, C.byref(counts)))
-            self._done = SampledSubgraph(self._bufs, counts, self._seeds)
-        return self._done
-
-
 class _Handle:
-    """One ag_sampler: scratch for one batch in flight."""
+    """One ag_sampler: scratch for one group of batches in flight."""
 
     def __init__(self, graph: CsrGraph, config: SamplingConfig, seed: int, max_seeds: int = 0, group: int = 1):
+        import torch
+
         self.graph, self.config, self.group = graph, config, group
+        self.device = torch.device("cuda", graph.device)
         self.h = C.c_void_p()
+        self._bounds: dict[int, tuple[int, int]] = {}
         cfg = config._to_c(seed, max_seeds)
         _lib.check(_lib.lib().ag_sampler_create_group(graph._h, C.byref(cfg), group, C.byref(self.h)))
 
@@ -379,22 +380,12 @@ class _Handle:
         _lib.check(_lib.lib().ag_sampler_reseed(self.h, seed & (2**64 - 1)))
 
     def bounds(self, n_seeds: int) -> tuple[int, int]:
-        mn, me = C.c_uint64(), C.c_uint64()
-        _lib.check(_lib.lib().ag_sampler_bounds(self.h, n_seeds, C.byref(mn), C.byref(me)))
-        return mn.value, me.value
-
-    def submit(self, seeds: np.ndarray, features: FeatureStore | None, stream=None) -> _Pending:
-        import torch
-
-        dev = torch.device("cuda", self.graph.device)
-        mn, me = self.bounds(len(seeds))
-        bufs = _Buffers(dev, mn, me, len(seeds), self.config.track_edge_ids,
-                        features.feature_dim if features is not None else None)
-        st = stream if stream is not None else torch.cuda.current_stream(dev).cuda_stream
-        _lib.check(_lib.lib().ag_sample_into(self.h, seeds.ctypes.data if len(seeds) else None, len(seeds),
-                                             _lib.AG_MEM_HOST, features._h if features is not None else None,
-                                             C.byref(bufs.c), st))
-        return _Pending(self, bufs, seeds)
+        b = self._bounds.get(n_seeds)
+        if b is None:
+            mn, me = C.c_uint64(), C.c_uint64()
+            _lib.check(_lib.lib().ag_sampler_bounds(self.h, n_seeds, C.byref(mn), C.byref(me)))
+            b = self._bounds[n_seeds] = (mn.value, me.value)
+        return b
 
 
 class _PendingGroup:
@@ -403,6 +394,9 @@ class _PendingGroup:
     def __init__(self, handle: _Handle, bufs: list[_Buffers], seeds: list[np.ndarray], keep):
         self._handle, self._bufs, self._seeds, self._keep = handle, bufs, seeds, keep
         self._done: list[SampledSubgraph] | None = None
+
+    def __len__(self) -> int:
+        return len(self._bufs)
 
     def results(self) -> list[SampledSubgraph]:
         if self._done is None:
@@ -414,21 +408,21 @@ class _PendingGroup:
         return self._done
 
 
-def _submit_group(handle: _Handle, seeds: list[np.ndarray], batch_seeds: list[int],
+def _submit_group(handle: _Handle, seeds: list[np.ndarray], batch_seeds: list[int] | None,
                   features: FeatureStore | None, stream=None) -> _PendingGroup:
     import torch
 
     n = len(seeds)
-    dev = torch.device("cuda", handle.graph.device)
+    dev = handle.device
     dim = features.feature_dim if features is not None else None
     bufs = []
     cbufs = (_lib.SubgraphBuffers * n)()
     ptrs = (C.c_void_p * n)()
     lens = (C.c_uint64 * n)()
-    bseeds = (C.c_uint64 * n)(*[s & (2**64 - 1) for s in batch_seeds])
+    bseeds = (C.c_uint64 * n)(*[s & (2**64 - 1) for s in batch_seeds]) if batch_seeds is not None else None
     for i, s in enumerate(seeds):
         mn, me = handle.bounds(len(s))
-        b = _Buffers(dev, mn, me, len(s), handle.config.track_edge_ids, dim)
+        b = _Buffers.alloc(dev, mn, me, len(s), handle.config.track_edge_ids, dim)
         bufs.append(b)
         cbufs[i] = b.c
         ptrs[i] = s.ctypes.data if len(s) else None
@@ -465,7 +459,7 @@ class NeighborSampler:
         if input_times is not None:
             raise SamplingError("temporal sampling: SamplingConfig::temporal_strategy is None")
         s = coerce_seeds(seeds, self.graph.num_nodes)
-        return self._handle.submit(s, self.features).result()
+        return _submit_group(self._handle, [s], None, self.features).results()[0]
 
     def __repr__(self) -> str:
         return f"NeighborSampler(num_neighbors={self.config.num_neighbors}, replace={self.config.replace})"
@@ -510,7 +504,7 @@ class ParallelBatchSampler:
             k = c % len(self._handles)
             if pending[k] is not None:
                 i, p = pending[k]
-                out[i:i + len(p._bufs)] = p.results()
+                out[i:i + len(p)] = p.results()
             h, st = self._handles[k], self._streams[k]
             chunk = seeds[lo:lo + G]
             bseeds = [_lib.lib().ag_batch_seed(self._base, first + lo + j) for j in range(len(chunk))]
@@ -520,13 +514,11 @@ class ParallelBatchSampler:
         for slot in pending:
             if slot is not None:
                 i, p = slot
-                out[i:i + len(p._bufs)] = p.results()
+                out[i:i + len(p)] = p.results()
         for st in self._streams:
             cur.wait_stream(st)
         for sg in out:
             # The buffers were allocated on a side stream; tell the allocator the
             # caller's stream uses them too before it may recycle them.
-            sg._b.arena.record_stream(cur)  # type: ignore[union-attr]
-            if sg._b.x is not None:  # type: ignore[union-attr]
-                sg._b.x.record_stream(cur)  # type: ignore[union-attr]
+            sg._b.record_stream(cur)  # type: ignore[union-attr]
         return out  # type: ignore[return-value]

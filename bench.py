@@ -259,27 +259,40 @@ def run_device(args, w):
     # One thread both submits and consumes here, so it must never block in submit:
     # keep no more batches outstanding than the loader's work queue (8 x depth) holds.
     window = min(8 * depth, depth + threads * group + group)
-    ring = [_Buffers(dev, mn.value, me.value, bs, True, w["dim"]) for _ in range(window)]
+    ring = [_Buffers.alloc(dev, mn.value, me.value, bs, True, w["dim"]) for _ in range(window)]
     R = len(ring)
     batch = _lib.Batch()
     stats0 = _lib.LoaderStats()
     stats1 = _lib.LoaderStats()
 
+    # Argument arrays for ag_loader_submit_many / ag_loader_next_many, built once.
+    base = seeds_dev.data_ptr()
+    idx_all = (C.c_int64 * n_batches)(*gidx)
+    ptr_all = (C.c_void_p * n_batches)(*[base + 4 * bs * i for i in range(n_batches)])
+    len_all = (C.c_uint64 * n_batches)(*([bs] * n_batches))
+    ring_c = (_lib.SubgraphBuffers * (R + group))(*[ring[j % R].c for j in range(R + group)])
+    out_batches = (_lib.Batch * 64)()
+    n_out = C.c_uint32()
+    sz_i64, sz_ptr, sz_u64, sz_buf = C.sizeof(C.c_int64), C.sizeof(C.c_void_p), C.sizeof(C.c_uint64), \
+        C.sizeof(_lib.SubgraphBuffers)
+
     def run_resident(first: int, count: int):
         """Submit batches [first, first+count) with device seeds; returns (edges, nodes)."""
         edges = nodes = 0
         submitted = delivered = 0
-        base = seeds_dev.data_ptr()
         while delivered < count:
-            while submitted < count and submitted - delivered < R:
+            while submitted < count and submitted - delivered + min(group, count - submitted) <= R:
                 i = first + submitted
-                _lib.check(L.ag_loader_submit(h, gidx[i], base + 4 * bs * i, bs, _lib.AG_MEM_DEVICE,
-                                              C.byref(ring[i % R].c), None))
-                submitted += 1
-            _lib.check(L.ag_loader_next(h, -1, C.byref(batch)))
-            edges += batch.counts.num_edges
-            nodes += batch.counts.num_nodes
-            delivered += 1
+                n = min(group, count - submitted)
+                _lib.check(L.ag_loader_submit_many(
+                    h, n, C.byref(idx_all, i * sz_i64), C.byref(ptr_all, i * sz_ptr), C.byref(len_all, i * sz_u64),
+                    _lib.AG_MEM_DEVICE, C.byref(ring_c, (i % R) * sz_buf), None, None))
+                submitted += n
+            _lib.check(L.ag_loader_next_many(h, -1, 64, out_batches, C.byref(n_out)))
+            for j in range(n_out.value):
+                edges += out_batches[j].counts.num_edges
+                nodes += out_batches[j].counts.num_nodes
+            delivered += n_out.value
         return edges, nodes
 
     # NOTE: seeded loaders number batches by submission; to keep every rank's

@@ -273,10 +273,11 @@ void ag_sampler_free(ag_sampler *s);
  *   - ag_loader_next waits up to timeout_ms (the reference waits 30 s) and
  *     returns AG_ERR_TIMEOUT, AG_ERR_SHUTDOWN after ag_loader_shutdown, or
  *     AG_ERR_WORKER once a worker failed (prefetch.rs:479-523).
- * Output buffers belong to the caller: pass them with the submission (device
- * memory, sized with ag_loader_bounds) and get the same pointers back in the
- * ag_batch.  With bufs == NULL the library allocates them and
- * ag_loader_release_batch frees them.  `after_stream`, when not NULL, is a
+ * Output buffers: pass your own with the submission (device memory, sized with
+ * ag_loader_bounds) and get the same pointers back in the ag_batch; or pass
+ * bufs == NULL and the loader takes a set from its pool (one device allocation
+ * per batch, with the int64 views and, when a feature store is attached, x),
+ * which ag_loader_release_batch hands back for reuse. `after_stream`, when not NULL, is a
  * stream whose already-queued work must finish before the batch's kernels
  * may write the buffers (the stream that last used recycled memory). */
 typedef struct {
@@ -302,10 +303,23 @@ int32_t ag_loader_bounds(const ag_loader *l, uint64_t n_seeds, uint64_t *max_nod
                          uint64_t *max_edges);
 int32_t ag_loader_submit(ag_loader *l, int64_t batch_idx, const uint32_t *seeds, uint64_t n_seeds,
                          int32_t seeds_mem, const ag_subgraph_buffers *bufs, void *after_stream);
+/* submit_epoch (_core.pyi:425): n submissions in one call; bufs == NULL means
+ * pooled buffers for all of them.  *n_done = how many were queued. */
+int32_t ag_loader_submit_many(ag_loader *l, uint32_t n, const int64_t *batch_idx,
+                              const uint32_t *const *seeds, const uint64_t *n_seeds,
+                              int32_t seeds_mem, const ag_subgraph_buffers *bufs,
+                              void *after_stream, uint32_t *n_done);
 int32_t ag_loader_next(ag_loader *l, int64_t timeout_ms, ag_batch *out);
+/* Like ag_loader_next for the first batch, then also returns every further
+ * batch that is already deliverable (up to max_n) without waiting. */
+int32_t ag_loader_next_many(ag_loader *l, int64_t timeout_ms, uint32_t max_n, ag_batch *out,
+                            uint32_t *n_out);
 /* Non-blocking: AG_ERR_TIMEOUT when nothing is ready. */
 int32_t ag_loader_try_next(ag_loader *l, ag_batch *out);
-int32_t ag_loader_release_batch(ag_loader *l, ag_batch *batch);
+/* Returns a pooled batch (owned == 1).  `stream` is the stream whose queued
+ * work is the consumer's last use of the batch; the buffers' next batch waits
+ * for it.  The memory stays valid until then or until ag_loader_free. */
+int32_t ag_loader_release_batch(ag_loader *l, ag_batch *batch, void *stream);
 int32_t ag_loader_stats_get(const ag_loader *l, ag_loader_stats *stats);
 int32_t ag_loader_shutdown(ag_loader *l);
 void ag_loader_free(ag_loader *l);
