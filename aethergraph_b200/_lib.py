@@ -112,6 +112,8 @@ SIGNATURES = {
     "ag_subgraph_release": (C.c_int32, [_P, C.POINTER(SubgraphBuffers)]),
     "ag_sampler_free": (None, [_P]),
     "ag_sampler_set_profiling": (C.c_int32, [_P, C.c_int32]),
+    "ag_register_seeds_static_max": (C.c_uint32, []),
+    "ag_register_seeds_static": (C.c_int32, [C.c_int32, _P, C.c_uint32, C.c_uint64, _P, _P, _P, _P]),
     "ag_sampler_create_group": (C.c_int32, [_P, C.POINTER(SamplingConfigC), C.c_uint32, _PP]),
     "ag_sample_group_into": (C.c_int32, [_P, C.c_uint32, _P, _P, C.c_int32, _P, _P, C.POINTER(SubgraphBuffers), _P]),
     "ag_sample_group_wait": (C.c_int32, [_P, C.POINTER(SampleCounts), _I32P]),

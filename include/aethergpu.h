@@ -257,6 +257,29 @@ int32_t ag_sample_group_wait(ag_sampler *s, ag_sample_counts *counts, int32_t *s
 int32_t ag_sampler_set_profiling(ag_sampler *s, int32_t on);
 void ag_sampler_free(ag_sampler *s);
 
+/* ------------------------------------------------ allocation-free entry --
+ * No counterpart in the reference.  For callers that must not allocate device
+ * memory while they run (a memory-pool or stream callback, a process whose
+ * device memory is fully budgeted to another allocator, a loop that cannot
+ * afford the device-wide synchronisation of cudaMalloc / cudaFree): the first
+ * step of the sampling path, seed registration, with its scratch in a fixed
+ * 160 KiB `static __device__` array inside the library instead of an
+ * allocation.  Collapses duplicate seeds in first-sighting order into
+ * nodes_out_dev and writes each input seed's local index to
+ * seed_locals_out_dev; count_err_out_dev[0] receives the distinct count,
+ * count_err_out_dev[1] error bits (8 = a seed >= num_nodes).  All buffers are
+ * the caller's device memory (capacity n_seeds each).  At most
+ * ag_register_seeds_static_max() (8192) seeds per call; more is AG_ERR_VALUE.
+ * The call allocates nothing.  Every call on a device shares the one scratch
+ * array, so calls that may overlap on the GPU must be ordered by the caller
+ * (same stream, or events).  The first call on a device resolves the array's
+ * device address (cudaGetSymbolAddress): make it before any stream capture. */
+uint32_t ag_register_seeds_static_max(void);
+int32_t ag_register_seeds_static(int32_t device, const uint32_t *seeds_dev, uint32_t n_seeds,
+                                 uint64_t num_nodes, uint32_t *nodes_out_dev,
+                                 uint32_t *seed_locals_out_dev, uint32_t *count_err_out_dev,
+                                 void *stream);
+
 /* --------------------------------------------------------------- loader --
  * Stands in for the prefetching NeighborLoader (_core.pyi:380-464;
  * crates/aethergraph-core/src/loader/prefetch.rs:402-560 pipeline,
