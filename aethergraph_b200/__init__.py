@@ -9,12 +9,15 @@ from ._lib import GraphLoadError, SamplingError
 from .features import FeatureStore, save_features
 from .graph import CsrGraph, Graph
 from .loader import NeighborLoader, PrefetchStats
+from .hetero import (HeteroCsrGraph, HeteroNeighborLoader, HeteroNeighborSampler, HeteroSampledSubgraph,
+                     HeteroSamplingConfig)
 from .sampler import NeighborSampler, ParallelBatchSampler, SampledSubgraph, Sampler, SamplingConfig
 
 __version__ = "0.1.0"
 
 __all__ = [
-    "CsrGraph", "FeatureStore", "Graph", "GraphLoadError", "NeighborLoader", "NeighborSampler",
+    "CsrGraph", "FeatureStore", "Graph", "GraphLoadError", "HeteroCsrGraph", "HeteroNeighborLoader",
+    "HeteroNeighborSampler", "HeteroSampledSubgraph", "HeteroSamplingConfig", "NeighborLoader", "NeighborSampler",
     "ParallelBatchSampler", "PrefetchStats",
     "SampledSubgraph", "Sampler", "SamplingConfig", "SamplingError", "__version__", "save_features",
 ]

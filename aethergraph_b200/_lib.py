@@ -68,6 +68,22 @@ class LoaderStats(C.Structure):
                 ("gather_ms", C.c_double), ("sample_ms", C.c_double)]
 
 
+AG_MAX_NODE_TYPES, AG_MAX_EDGE_TYPES = 8, 16
+
+
+class HeteroBuffers(C.Structure):
+    _fields_ = [("cap_nodes", C.c_uint64), ("cap_edges", C.c_uint64), ("cap_seeds", C.c_uint64)] + \
+               [(n, C.c_void_p) for n in ("nodes", "edge_src_local", "edge_dst_local", "seed_indices",
+                                          "n_id", "edge_index_local", "seed_index")]
+
+
+class HeteroCounts(C.Structure):
+    _fields_ = [("num_node_types", C.c_uint32), ("num_edge_types", C.c_uint32), ("num_seeds", C.c_uint32),
+                ("error", C.c_uint32), ("nodes", C.c_uint32 * AG_MAX_NODE_TYPES),
+                ("edges", C.c_uint32 * AG_MAX_EDGE_TYPES), ("total_nodes", C.c_uint32),
+                ("total_edges", C.c_uint32), ("draws", C.c_uint64)]
+
+
 _P = C.c_void_p
 _PP = C.POINTER(C.c_void_p)
 _U64P = C.POINTER(C.c_uint64)
@@ -117,6 +133,16 @@ SIGNATURES = {
     "ag_sampler_create_group": (C.c_int32, [_P, C.POINTER(SamplingConfigC), C.c_uint32, _PP]),
     "ag_sample_group_into": (C.c_int32, [_P, C.c_uint32, _P, _P, C.c_int32, _P, _P, C.POINTER(SubgraphBuffers), _P]),
     "ag_sample_group_wait": (C.c_int32, [_P, C.POINTER(SampleCounts), _I32P]),
+    "ag_hetero_create": (C.c_int32, [C.c_uint32, _P, C.c_uint32, _P, _P, _P, _P, _P, _P, C.c_int32, C.c_int32, _PP]),
+    "ag_hetero_info": (C.c_int32, [_P, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32), _P, _P, _I32P]),
+    "ag_hetero_in_adjacency": (C.c_int32, [_P, C.c_uint32, _P, _P]),
+    "ag_hetero_free": (None, [_P]),
+    "ag_hetero_sampler_create": (C.c_int32, [_P, _P, C.c_uint32, C.c_int32, C.c_uint64, C.c_int32, _PP]),
+    "ag_hetero_sampler_reseed": (C.c_int32, [_P, C.c_uint64]),
+    "ag_hetero_sampler_bounds": (C.c_int32, [_P, C.c_uint64, _U64P, _U64P]),
+    "ag_hetero_sample_into": (C.c_int32, [_P, C.c_uint32, _P, C.c_uint64, C.POINTER(HeteroBuffers), _P]),
+    "ag_hetero_sample_wait": (C.c_int32, [_P, C.POINTER(HeteroCounts)]),
+    "ag_hetero_sampler_free": (None, [_P]),
     "ag_loader_create": (C.c_int32, [_P, _P, C.POINTER(SamplingConfigC), C.c_int32, C.c_uint32, C.c_uint32,
                                      C.c_uint32, C.c_int32, _PP]),
     "ag_loader_bounds": (C.c_int32, [_P, C.c_uint64, _U64P, _U64P]),

@@ -58,4 +58,9 @@ cudaError_t launch_validate_csr(const uint64_t *offsets, const uint32_t *dst, ui
 cudaError_t launch_degrees(const uint64_t *offsets, uint64_t num_nodes, const uint32_t *ids,
                            uint64_t n, uint32_t *out, cudaStream_t st);
 
+// Sorts n keys (row << 32 | value) and builds the CSR over num_rows rows from them
+// (rows ascending, values ascending within a row).  Consumes (frees) keys.
+int32_t keys_to_sorted_csr(uint64_t *keys, uint64_t n, uint64_t num_rows, uint64_t **offsets_out,
+                           uint32_t **vals_out);
+
 }  // namespace ag

@@ -191,6 +191,46 @@ int32_t build_relation(uint64_t num_src, uint64_t num_dst, uint64_t num_edges, c
 }
 
 }  // namespace
+
+// Sorts `n` 64-bit keys (row << 32 | value) by their low `32 + bits_row` bits and
+// turns them into a CSR over `num_rows` rows: offsets[num_rows + 1] and the values
+// in sorted order.  keys is consumed (freed); offsets / vals are cudaMalloc'ed.
+int32_t keys_to_sorted_csr(uint64_t *keys, uint64_t n, uint64_t num_rows, uint64_t **offsets_out, uint32_t **vals_out) {
+    uint64_t *alt = nullptr, *offsets = nullptr;
+    uint32_t *vals = nullptr;
+    void *temp = nullptr;
+    int32_t st = AG_OK;
+    auto ok = [&](cudaError_t e, const char *what) {
+        if (e != cudaSuccess && st == AG_OK) st = fail(AG_ERR_CUDA, "%s failed: %s", what, cudaGetErrorString(e));
+        return e == cudaSuccess;
+    };
+    uint64_t *sorted = keys;
+    do {
+        if (n) {
+            if (!ok(cudaMalloc(&alt, n * 8), "cudaMalloc(sort buffer)")) break;
+            cub::DoubleBuffer<uint64_t> buf(keys, alt);
+            size_t temp_bytes = 0;
+            const int end_bit = 32 + (int)bits_for(std::max<uint64_t>(num_rows, 2));
+            if (!ok(cub::DeviceRadixSort::SortKeys(nullptr, temp_bytes, buf, n, 0, end_bit), "sort sizing")) break;
+            if (!ok(cudaMalloc(&temp, std::max<size_t>(temp_bytes, 16)), "cudaMalloc(sort temp)")) break;
+            if (!ok(cub::DeviceRadixSort::SortKeys(temp, temp_bytes, buf, n, 0, end_bit), "radix sort")) break;
+            if (!ok(cudaDeviceSynchronize(), "radix sort")) break;
+            sorted = buf.Current();
+            cudaFree(temp); temp = nullptr;
+            if (sorted == keys) { cudaFree(alt); alt = nullptr; } else { cudaFree(keys); keys = nullptr; }
+        }
+        if (!ok(cudaMalloc(&offsets, (num_rows + 1) * 8), "cudaMalloc(offsets)")) break;
+        if (!ok(cudaMalloc(&vals, std::max<uint64_t>(n, 1) * 4), "cudaMalloc(values)")) break;
+        k_keys_to_csr<<<grid_for(std::max<uint64_t>(n, num_rows + 1)), 256>>>(sorted, n, num_rows, offsets, vals);
+        if (!ok(cudaGetLastError(), "k_keys_to_csr")) break;
+        ok(cudaDeviceSynchronize(), "k_keys_to_csr");
+    } while (0);
+    cudaFree(temp); cudaFree(keys); cudaFree(alt);
+    if (st != AG_OK) { cudaFree(offsets); cudaFree(vals); return st; }
+    *offsets_out = offsets; *vals_out = vals;
+    return AG_OK;
+}
+
 }  // namespace ag
 
 using namespace ag;

@@ -1,0 +1,532 @@
+"""Heterogeneous neighbor sampling on the GPU behind the reference's API.
+
+Mirrors `HeteroCsrGraph`, `HeteroSamplingConfig`, `HeteroSampledSubgraph`,
+`HeteroNeighborSampler` and `HeteroNeighborLoader`
+(python/aethergraph/_core.pyi:609-720, crates/aethergraph-py/src/hetero.rs).
+The transposed adjacency is built and kept in GPU memory; sampling, per-type
+dedup, relabel and the int64 widening run in CUDA kernels.  For the same seed
+the arrays are the reference CPU sampler's, bit for bit.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import queue
+import secrets
+import threading
+import time
+from typing import Sequence
+
+import numpy as np
+
+from . import _lib
+from ._lib import SamplingError
+from .loader import PrefetchStats
+from .sampler import _DevArray, coerce_seeds
+
+__all__ = ["HeteroCsrGraph", "HeteroNeighborLoader", "HeteroNeighborSampler", "HeteroSampledSubgraph",
+           "HeteroSamplingConfig"]
+
+EdgeType = tuple[str, str, str]
+
+
+def _ptr_array(arrays: Sequence[np.ndarray | None]):
+    out = (C.c_void_p * max(len(arrays), 1))()
+    for i, a in enumerate(arrays):
+        out[i] = a.ctypes.data if a is not None and a.size else None
+    return out
+
+
+class HeteroCsrGraph:
+    """Heterogeneous graph: several node types and edge types, resident in GPU memory
+    as one transposed adjacency per edge type (crates/aethergraph-core/src/graph/hetero.rs:70-97)."""
+
+    def __init__(self, handle: int, node_types: list[tuple[str, int]], edge_types: list[EdgeType],
+                 num_edges: list[int], device: int):
+        self._h = handle
+        self._node_types = node_types
+        self._edge_types = edge_types
+        self._num_edges = num_edges
+        self.device = device
+        self._nt_id = {name: i for i, (name, _) in enumerate(node_types)}
+        self._et_id = {et: i for i, et in enumerate(edge_types)}
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            try:
+                _lib.lib().ag_hetero_free(h)
+            except Exception:
+                pass
+
+    @staticmethod
+    def from_edge_arrays(node_types: dict[str, int], edge_types: list[tuple], device: int | None = None) -> "HeteroCsrGraph":
+        """Build from per-edge-type COO arrays `(src_type, rel, dst_type, src_ids, dst_ids)`.
+
+        Raises ValueError for mismatched array lengths, an unknown node type, an
+        endpoint outside its type's node count or a repeated edge type
+        (crates/aethergraph-py/src/hetero.rs:56-134), and for more node / edge
+        types than the GPU sampler supports (8 / 16)."""
+        import torch
+
+        if device is None:
+            device = torch.cuda.current_device() if torch.cuda.is_available() else 0
+        nt = [(str(k), int(v)) for k, v in node_types.items()]
+        nt_id = {name: i for i, (name, _) in enumerate(nt)}
+        names: list[EdgeType] = []
+        src_t, dst_t, srcs, dsts = [], [], [], []
+        for (s, rel, d, src_ids, dst_ids) in edge_types:
+            a = np.ascontiguousarray(np.asarray(src_ids), dtype=np.uint32).reshape(-1)
+            b = np.ascontiguousarray(np.asarray(dst_ids), dtype=np.uint32).reshape(-1)
+            if a.size != b.size:
+                raise ValueError(f"src and dst arrays must have the same length for ({s}, {rel}, {d})")
+            if s not in nt_id:
+                raise ValueError(f"unknown source type '{s}' in ({s}, {rel}, {d})")
+            if d not in nt_id:
+                raise ValueError(f"unknown dest type '{d}' in ({s}, {rel}, {d})")
+            if (s, rel, d) in names:
+                raise ValueError(f"duplicate edge type ({s}, {rel}, {d})")
+            names.append((s, rel, d))
+            src_t.append(nt_id[s]); dst_t.append(nt_id[d]); srcs.append(a); dsts.append(b)
+        for (s, rel, d), a, b, si, di in zip(names, srcs, dsts, src_t, dst_t):
+            # the reference's bipartite builder names the relation in its error
+            if a.size and (int(a.max()) >= nt[si][1] or int(b.max()) >= nt[di][1]):
+                raise ValueError(f"failed to build CSR for ({s}, {rel}, {d}): endpoint outside the node range")
+        num_nodes = np.array([c for _, c in nt], dtype=np.uint64)
+        st = np.array(src_t, dtype=np.uint32)
+        dt = np.array(dst_t, dtype=np.uint32)
+        ne = np.array([a.size for a in srcs], dtype=np.uint64)
+        out = C.c_void_p()
+        _lib.check(_lib.lib().ag_hetero_create(len(nt), num_nodes.ctypes.data, len(names), st.ctypes.data,
+                                               dt.ctypes.data, None, _ptr_array(srcs), _ptr_array(dsts),
+                                               ne.ctypes.data, _lib.AG_MEM_HOST, device, C.byref(out)))
+        return HeteroCsrGraph(out.value, nt, names, [int(v) for v in ne], device)
+
+    def node_types(self) -> list[str]:
+        return [n for n, _ in self._node_types]
+
+    def edge_types(self) -> list[EdgeType]:
+        return list(self._edge_types)
+
+    def num_nodes(self, node_type: str) -> int:
+        if node_type not in self._nt_id:
+            raise KeyError(f"unknown node type '{node_type}'")
+        return self._node_types[self._nt_id[node_type]][1]
+
+    def num_edges(self, src_type: str, rel: str, dst_type: str) -> int:
+        if (src_type, rel, dst_type) not in self._et_id:
+            raise KeyError(f"unknown edge type ('{src_type}', '{rel}', '{dst_type}')")
+        return self._num_edges[self._et_id[(src_type, rel, dst_type)]]
+
+    def total_nodes(self) -> int:
+        return sum(c for _, c in self._node_types)
+
+    def total_edges(self) -> int:
+        return sum(self._num_edges)
+
+    def in_adjacency(self, src_type: str, rel: str, dst_type: str) -> tuple[np.ndarray, np.ndarray]:
+        """Host copy of the transposed adjacency of one edge type: `(offsets, sources)`
+        over the destination type's nodes."""
+        if (src_type, rel, dst_type) not in self._et_id:
+            raise KeyError(f"unknown edge type ('{src_type}', '{rel}', '{dst_type}')")
+        e = self._et_id[(src_type, rel, dst_type)]
+        offsets = np.zeros(self.num_nodes(dst_type) + 1, dtype=np.uint64)
+        sources = np.zeros(self._num_edges[e], dtype=np.uint32)
+        _lib.check(_lib.lib().ag_hetero_in_adjacency(self._h, e, offsets.ctypes.data,
+                                                     sources.ctypes.data if sources.size else None))
+        return offsets, sources
+
+    def __repr__(self) -> str:
+        return (f"HeteroCsrGraph(node_types={len(self._node_types)}, edge_types={len(self._edge_types)}, "
+                f"total_nodes={self.total_nodes()}, total_edges={self.total_edges()})")
+
+
+class HeteroSamplingConfig:
+    """`num_neighbors[(src, rel, dst)]` is, per hop, how many `src` nodes with an
+    edge into each expanded `dst` node to draw; edge types left out draw nothing.
+    `max_degree` has no effect (crates/aethergraph-py/src/hetero.rs:209-262)."""
+
+    def __init__(self, num_neighbors: dict[EdgeType, list[int]], replace: bool = False, seed: int | None = None,
+                 max_degree: int | None = None, rng_mode: str = "wyrand_exact"):
+        if not num_neighbors:
+            raise ValueError("num_neighbors must not be empty")
+        hops = [len(v) for v in num_neighbors.values()]
+        if hops[0] == 0:
+            raise ValueError("num_neighbors hop lists must be non-empty")
+        if any(h != hops[0] for h in hops):
+            raise ValueError("all edge types must have the same number of hops")
+        if max_degree is not None and max_degree == 0:
+            raise ValueError("max_degree must be > 0 if specified")
+        if seed is not None and not (0 <= int(seed) < 2**64):
+            raise ValueError(f"seed must fit an unsigned 64-bit integer, got {seed}")
+        if rng_mode not in _lib.RNG_MODE:
+            raise ValueError(f"Invalid rng_mode '{rng_mode}'. Must be 'wyrand_exact' or 'philox'")
+        self._nn = {tuple(k): [int(x) for x in v] for k, v in num_neighbors.items()}
+        if any(x < 0 for v in self._nn.values() for x in v):
+            raise ValueError("num_neighbors values must be non-negative")
+        self._replace, self._seed, self._max_degree, self.rng_mode = bool(replace), seed, max_degree, rng_mode
+
+    num_neighbors = property(lambda self: {k: list(v) for k, v in self._nn.items()})
+    replace = property(lambda self: self._replace)
+    seed = property(lambda self: self._seed)
+    max_degree = property(lambda self: self._max_degree)
+    num_hops = property(lambda self: len(next(iter(self._nn.values()))))
+
+    def _fanout(self, graph: HeteroCsrGraph) -> np.ndarray:
+        """[edge types][hops], zeros for edge types left out (hetero.rs:309-328)."""
+        f = np.zeros((len(graph._edge_types), self.num_hops), dtype=np.uint32)
+        for et, hops in self._nn.items():
+            if et not in graph._et_id:
+                raise SamplingError(f"unknown edge type ('{et[0]}', '{et[1]}', '{et[2]}')")
+            f[graph._et_id[et]] = hops
+        return f
+
+    def __repr__(self) -> str:
+        return f"HeteroSamplingConfig(edge_types={len(self._nn)}, num_hops={self.num_hops}, replace={self._replace})"
+
+
+class HeteroSampledSubgraph:
+    """One heterogeneous batch.  The arrays live in GPU memory; `*_t` accessors
+    return CUDA tensors over it without a copy, the reference's accessors
+    (`nodes`, `nodes_u32`, `edge_index_local`, `seeds`, `seed_indices`) return
+    fresh host numpy arrays (crates/aethergraph-py/src/hetero.rs:349-470)."""
+
+    def __init__(self, graph: HeteroCsrGraph, seed_type: int, seeds: np.ndarray, counts: _lib.HeteroCounts,
+                 bufs: _lib.HeteroBuffers, owner):
+        self._g, self._seed_type, self._seeds, self._c, self._b, self._owner = graph, seed_type, seeds, counts, bufs, owner
+        self._n = [int(counts.nodes[t]) for t in range(len(graph._node_types))]
+        self._e = [int(counts.edges[e]) for e in range(len(graph._edge_types))]
+        self._n_start = np.concatenate([[0], np.cumsum(self._n)]).astype(np.int64)
+        self._e_start = np.concatenate([[0], np.cumsum(self._e)]).astype(np.int64)
+
+    # -- reference API ------------------------------------------------------
+    @property
+    def node_types(self) -> list[str]:
+        return [name for (name, _), n in zip(self._g._node_types, self._n) if n]
+
+    @property
+    def edge_types(self) -> list[EdgeType]:
+        return [et for et, n in zip(self._g._edge_types, self._e) if n]
+
+    @property
+    def seed_type(self) -> str:
+        return self._g._node_types[self._seed_type][0]
+
+    @property
+    def seeds(self) -> np.ndarray:
+        return self._seeds.astype(np.int64)
+
+    @property
+    def seed_indices(self) -> np.ndarray:
+        return self.seed_indices_t.cpu().numpy()
+
+    def nodes(self, node_type: str) -> np.ndarray:
+        return self.nodes_t(node_type).cpu().numpy()
+
+    def nodes_u32(self, node_type: str) -> np.ndarray:
+        import torch
+
+        t = self._nt(node_type)
+        v = torch.as_tensor(_DevArray(self._b.nodes + 4 * int(self._n_start[t]), (self._n[t],), "<i4", self._owner),
+                            device=self._dev()) if self._n[t] else torch.empty(0, dtype=torch.int32)
+        return v.cpu().numpy().view(np.uint32)
+
+    def edge_index_local(self, src: str, rel: str, dst: str) -> np.ndarray:
+        return self.edge_index_local_t(src, rel, dst).cpu().numpy()
+
+    # -- device views -------------------------------------------------------
+    def _dev(self):
+        import torch
+
+        return torch.device("cuda", self._g.device)
+
+    def _nt(self, node_type: str) -> int:
+        if node_type not in self._g._nt_id:
+            raise KeyError(f"unknown node type '{node_type}'")
+        return self._g._nt_id[node_type]
+
+    def nodes_t(self, node_type: str):
+        """int64 CUDA tensor of the sampled ids of `node_type`, in discovery order."""
+        import torch
+
+        t = self._nt(node_type)
+        if not self._n[t]:
+            return torch.empty(0, dtype=torch.int64, device=self._dev())
+        return torch.as_tensor(_DevArray(self._b.n_id + 8 * int(self._n_start[t]), (self._n[t],), "<i8", self._owner),
+                               device=self._dev())
+
+    def edge_index_local_t(self, src: str, rel: str, dst: str):
+        """int64 CUDA tensor [2, E]: row 0 indexes `nodes(src)`, row 1 `nodes(dst)`."""
+        import torch
+
+        if (src, rel, dst) not in self._g._et_id:
+            raise KeyError(f"unknown edge type ('{src}', '{rel}', '{dst}')")
+        e = self._g._et_id[(src, rel, dst)]
+        if not self._e[e]:
+            return torch.empty((2, 0), dtype=torch.int64, device=self._dev())
+        return torch.as_tensor(_DevArray(self._b.edge_index_local + 16 * int(self._e_start[e]), (2, self._e[e]), "<i8",
+                                         self._owner), device=self._dev())
+
+    @property
+    def seed_indices_t(self):
+        import torch
+
+        n = int(self._c.num_seeds)
+        if not n:
+            return torch.empty(0, dtype=torch.int64, device=self._dev())
+        return torch.as_tensor(_DevArray(self._b.seed_index, (n,), "<i8", self._owner), device=self._dev())
+
+    def raw_u32(self) -> dict:
+        """The u32 arrays the C ABI wrote, per type, as host numpy (parity tests)."""
+        import torch
+
+        def u32(ptr, start, n):
+            if not n:
+                return np.zeros(0, dtype=np.uint32)
+            t = torch.as_tensor(_DevArray(ptr + 4 * int(start), (n,), "<i4", self._owner), device=self._dev())
+            return t.cpu().numpy().view(np.uint32)
+
+        return {
+            "nodes": [u32(self._b.nodes, self._n_start[t], self._n[t]) for t in range(len(self._n))],
+            "edge_src_local": [u32(self._b.edge_src_local, self._e_start[e], self._e[e]) for e in range(len(self._e))],
+            "edge_dst_local": [u32(self._b.edge_dst_local, self._e_start[e], self._e[e]) for e in range(len(self._e))],
+            "seed_indices": u32(self._b.seed_indices, 0, int(self._c.num_seeds)),
+            "draws": int(self._c.draws),
+        }
+
+    def __repr__(self) -> str:
+        return (f"HeteroSampledSubgraph(node_types={len(self.node_types)}, edge_types={len(self.edge_types)}, "
+                f"seed_type='{self.seed_type}')")
+
+
+def _align(n: int, a: int = 256) -> int:
+    return (n + a - 1) // a * a
+
+
+class _HeteroHandle:
+    """One native hetero sampler handle plus the allocation of its output buffers."""
+
+    def __init__(self, graph: HeteroCsrGraph, config: HeteroSamplingConfig, seed: int):
+        self.graph, self.config = graph, config
+        fan = np.ascontiguousarray(config._fanout(graph))
+        out = C.c_void_p()
+        _lib.check(_lib.lib().ag_hetero_sampler_create(graph._h, fan.ctypes.data, config.num_hops, int(config.replace),
+                                                       seed, _lib.RNG_MODE[config.rng_mode], C.byref(out)))
+        self._h = out.value
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            try:
+                _lib.lib().ag_hetero_sampler_free(h)
+            except Exception:
+                pass
+
+    def reseed(self, seed: int) -> None:
+        _lib.check(_lib.lib().ag_hetero_sampler_reseed(self._h, seed))
+
+    def sample(self, seed_type: int, seeds: np.ndarray, stream=None) -> HeteroSampledSubgraph:
+        import torch
+
+        L = _lib.lib()
+        n = int(seeds.size)
+        mn, me = C.c_uint64(), C.c_uint64()
+        _lib.check(L.ag_hetero_sampler_bounds(self._h, n, C.byref(mn), C.byref(me)))
+        cap_n, cap_e, cap_s = max(int(mn.value), 1), max(int(me.value), 1), max(n, 1)
+        sizes = [4 * cap_n, 4 * cap_e, 4 * cap_e, 4 * cap_s, 8 * cap_n, 16 * cap_e, 8 * cap_s]
+        offs = np.concatenate([[0], np.cumsum([_align(s) for s in sizes])])
+        dev = torch.device("cuda", self.graph.device)
+        block = torch.empty(int(offs[-1]), dtype=torch.uint8, device=dev)
+        base = block.data_ptr()
+        b = _lib.HeteroBuffers()
+        b.cap_nodes, b.cap_edges, b.cap_seeds = cap_n, cap_e, cap_s
+        (b.nodes, b.edge_src_local, b.edge_dst_local, b.seed_indices, b.n_id, b.edge_index_local,
+         b.seed_index) = (base + int(o) for o in offs[:-1])
+        st = stream if stream is not None else torch.cuda.current_stream(dev)
+        _lib.check(L.ag_hetero_sample_into(self._h, seed_type, seeds.ctypes.data if n else None, n, C.byref(b),
+                                           st.cuda_stream))
+        counts = _lib.HeteroCounts()
+        _lib.check(L.ag_hetero_sample_wait(self._h, C.byref(counts)))
+        return HeteroSampledSubgraph(self.graph, seed_type, seeds, counts, b, block)
+
+
+class HeteroNeighborSampler:
+    """Heterogeneous neighborhood sampler; `sample` raises SamplingError for an
+    unknown seed type or a seed outside the seed type's node range
+    (crates/aethergraph-py/src/hetero.rs:544-581)."""
+
+    def __init__(self, graph: HeteroCsrGraph, config: HeteroSamplingConfig):
+        self._graph = graph
+        seed = config.seed if config.seed is not None else secrets.randbits(64)
+        self._handle = _HeteroHandle(graph, config, int(seed))
+
+    def sample(self, seed_type: str, seeds) -> HeteroSampledSubgraph:
+        if seed_type not in self._graph._nt_id:
+            raise SamplingError(f"unknown seed type '{seed_type}'")
+        t = self._graph._nt_id[seed_type]
+        return self._handle.sample(t, coerce_seeds(seeds, self._graph._node_types[t][1]))
+
+    def __repr__(self) -> str:
+        return f"HeteroNeighborSampler(edge_types={len(self._graph._edge_types)})"
+
+
+class HeteroNeighborLoader:
+    """Prefetching heterogeneous loader: `sampler_threads` workers, each with its own
+    sampler handle and CUDA stream, over a bounded work queue; the same ordering,
+    per-batch reseed (`batch_seed(seed, seq)` when the config has a seed), timeout
+    and shutdown contract as `NeighborLoader`
+    (crates/aethergraph-core/src/loader/prefetch.rs:984-1022, 1940-2060)."""
+
+    _TIMEOUT_S = 30.0
+
+    def __init__(self, graph: HeteroCsrGraph, config: HeteroSamplingConfig, seed_type: str, prefetch_depth: int = 2,
+                 sampler_threads: int = 1):
+        import torch
+
+        if prefetch_depth < 1:
+            raise RuntimeError("Failed to create HeteroNeighborLoader: prefetch_depth must be >= 1")
+        if seed_type not in graph._nt_id:
+            raise SamplingError(f"unknown seed type '{seed_type}'")
+        self._graph, self._config = graph, config
+        self._seed_type = graph._nt_id[seed_type]
+        self._seed_nodes = graph._node_types[self._seed_type][1]
+        self._depth = prefetch_depth
+        threads = max(1, int(sampler_threads))
+        self._seeded = config.seed is not None
+        self._work: queue.Queue = queue.Queue(maxsize=8 * prefetch_depth)
+        self._lock = threading.Condition()
+        self._ready: dict[int, tuple] = {}     # seq -> (batch_idx, subgraph)
+        self._unordered: list[tuple] = []
+        self._next_seq = 0      # next sequence number to hand out at submit
+        self._deliver_seq = 0   # next sequence number to deliver (seeded)
+        self._failed: str | None = None
+        self._stop = False
+        self._stats = {"hits": 0, "misses": 0, "total": 0, "sample_ns": 0}
+        base = config.seed if self._seeded else secrets.randbits(64)
+        self._threads = []
+        for t in range(threads):
+            h = _HeteroHandle(graph, config, int(base) if self._seeded else (int(base) + t) % 2**64)
+            stream = torch.cuda.Stream(device=graph.device)
+            th = threading.Thread(target=self._worker, args=(h, stream), name=f"aethergraph-hetero-sampler-{t}",
+                                  daemon=True)
+            th.start()
+            self._threads.append(th)
+
+    def _worker(self, handle: _HeteroHandle, stream) -> None:
+        L = _lib.lib()
+        try:
+            while True:
+                item = self._work.get()
+                if item is None or self._stop:
+                    return
+                seq, batch_idx, seeds = item
+                if self._seeded:
+                    handle.reseed(int(L.ag_batch_seed(self._config.seed, seq)))
+                t0 = time.perf_counter_ns()
+                sg = handle.sample(self._seed_type, seeds, stream)
+                dt = time.perf_counter_ns() - t0
+                with self._lock:
+                    self._stats["sample_ns"] += dt
+                    # the result channel holds max(depth, threads) finished batches
+                    cap = max(self._depth, len(self._threads))
+                    while not self._stop and self._seeded and seq - self._deliver_seq >= cap + len(self._threads):
+                        self._lock.wait(0.1)
+                    if self._seeded:
+                        self._ready[seq] = (batch_idx, sg)
+                    else:
+                        self._unordered.append((batch_idx, sg))
+                    self._lock.notify_all()
+        except Exception as e:  # a worker that dies fails the loader, as in the reference
+            with self._lock:
+                self._failed = f"{type(e).__name__}: {e}"
+                self._lock.notify_all()
+
+    def submit(self, batch_idx: int, seeds) -> None:
+        if self._stop:
+            raise SamplingError("Submit failed: loader is shut down")
+        s = coerce_seeds(seeds, self._seed_nodes).copy()
+        with self._lock:
+            seq = self._next_seq
+            self._next_seq += 1
+        try:
+            self._work.put((seq, int(batch_idx), s), timeout=self._TIMEOUT_S)
+        except queue.Full:
+            raise SamplingError("Submit failed: work queue full for 30 s") from None
+
+    def _take(self):
+        if self._seeded:
+            if self._deliver_seq in self._ready:
+                r = self._ready.pop(self._deliver_seq)
+                self._deliver_seq += 1
+                self._lock.notify_all()
+                return r
+            return None
+        return self._unordered.pop(0) if self._unordered else None
+
+    def next_batch(self):
+        """`(batch_idx, subgraph)`, or None after `shutdown()`; TimeoutError when
+        nothing arrived within 30 s; RuntimeError once a worker failed."""
+        deadline = time.monotonic() + self._TIMEOUT_S
+        with self._lock:
+            first = True
+            while True:
+                r = self._take()
+                if r is not None:
+                    self._stats["total"] += 1
+                    self._stats["hits" if first else "misses"] += 1
+                    return r
+                if self._failed:
+                    raise RuntimeError(f"sampler worker exited: {self._failed}")
+                if self._stop:
+                    return None
+                first = False
+                left = deadline - time.monotonic()
+                if left <= 0:
+                    raise TimeoutError("no batch arrived within 30 s")
+                self._lock.wait(min(left, 0.5))
+
+    def next(self):
+        r = self.next_batch()
+        return None if r is None else r[1]
+
+    @property
+    def prefetch_depth(self) -> int:
+        return self._depth
+
+    def stats(self) -> PrefetchStats:
+        c = _lib.LoaderStats()
+        c.hits, c.misses, c.total = self._stats["hits"], self._stats["misses"], self._stats["total"]
+        c.sample_time_ns, c.submitted = self._stats["sample_ns"], self._next_seq
+        return PrefetchStats(c)
+
+    def shutdown(self) -> None:
+        with self._lock:
+            if self._stop:
+                return
+            self._stop = True
+            self._lock.notify_all()
+        for _ in self._threads:
+            try:
+                self._work.put_nowait(None)
+            except queue.Full:
+                try:
+                    self._work.get_nowait()
+                    self._work.put_nowait(None)
+                except Exception:
+                    pass
+        for th in self._threads:
+            th.join(timeout=5)
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc) -> None:
+        self.shutdown()
+
+    def __del__(self):
+        try:
+            self.shutdown()
+        except Exception:
+            pass
+
+    def __repr__(self) -> str:
+        return f"HeteroNeighborLoader(prefetch_depth={self._depth})"

@@ -280,6 +280,77 @@ int32_t ag_register_seeds_static(int32_t device, const uint32_t *seeds_dev, uint
                                  uint32_t *seed_locals_out_dev, uint32_t *count_err_out_dev,
                                  void *stream);
 
+/* --------------------------------------------------- heterogeneous path --
+ * Stands in for HeteroCsrGraph + HeteroNeighborSampler (_core.pyi:609-720;
+ * crates/aethergraph-core/src/graph/hetero.rs:312-423 from_relations,
+ * crates/aethergraph-core/src/loader/hetero_sampler.rs:174-330 sample_neighbors).
+ * Node and edge types are dense ids in the caller's order (the Python layer
+ * maps names).  A node of type T is expanded along every edge type whose
+ * destination type is T, in ascending edge type id, over the transposed
+ * adjacency (hetero.rs:70-97); nodes are deduplicated per node type; an edge is
+ * (source local, destination local) in its edge type's arrays, the locals
+ * indexing the source / destination TYPE's nodes.  One WyRand stream per batch;
+ * same picks, same order as the reference for the same seed.
+ * Limits: <= 8 node types, <= 16 edge types, fewer than 2^32 nodes over all
+ * types, fanout <= 32 per (edge type, hop). */
+#define AG_MAX_NODE_TYPES 8
+#define AG_MAX_EDGE_TYPES 16
+
+/* Relation e is an edge list (rel_offsets == NULL or rel_offsets[e] == NULL:
+ * rel_a[e] = sources, rel_b[e] = destinations, num_edges[e] each) or a CSR over
+ * its source type (rel_offsets[e] = num_nodes[src_type[e]] + 1 offsets,
+ * rel_b[e] = destinations); all arrays of one call in host or all in device
+ * memory (mem_kind).  An endpoint outside its node type's range is
+ * AG_ERR_VALUE (hetero.rs:346-379). */
+int32_t ag_hetero_create(uint32_t num_node_types, const uint64_t *num_nodes, uint32_t num_edge_types,
+                         const uint32_t *src_type, const uint32_t *dst_type,
+                         const uint64_t *const *rel_offsets, const uint32_t *const *rel_a,
+                         const uint32_t *const *rel_b, const uint64_t *num_edges, int32_t mem_kind,
+                         int32_t device, ag_hetero_graph **out);
+int32_t ag_hetero_info(const ag_hetero_graph *h, uint32_t *num_node_types, uint32_t *num_edge_types,
+                       uint64_t *num_nodes /* [types] */, uint64_t *num_edges /* [edge types] */,
+                       int32_t *device);
+/* Host copy of one edge type's transposed adjacency (hetero.rs:70-97):
+ * offsets[num_nodes[dst_type] + 1], sources[num_edges]. */
+int32_t ag_hetero_in_adjacency(const ag_hetero_graph *h, uint32_t edge_type, uint64_t *offsets,
+                               uint32_t *sources);
+void ag_hetero_free(ag_hetero_graph *h);
+
+/* Device output buffers of one heterogeneous batch.  Node type t's nodes are
+ * nodes[node_start(t) .. +counts.nodes[t]) with node_start(t) = sum of the
+ * counts of the types before it; edge type e's edges likewise in
+ * edge_src_local / edge_dst_local.  edge_index_local (optional) holds, per edge
+ * type, a contiguous int64 [2, E_e] block at element offset 2 * edge_start(e):
+ * row 0 sources, row 1 destinations (aethergraph-py/src/hetero.rs:178-200). */
+typedef struct {
+    uint64_t cap_nodes, cap_edges, cap_seeds;
+    uint32_t *nodes, *edge_src_local, *edge_dst_local, *seed_indices;
+    int64_t *n_id, *edge_index_local, *seed_index;   /* optional int64 views */
+} ag_hetero_buffers;
+
+typedef struct {
+    uint32_t num_node_types, num_edge_types, num_seeds, error;
+    uint32_t nodes[AG_MAX_NODE_TYPES];
+    uint32_t edges[AG_MAX_EDGE_TYPES];
+    uint32_t total_nodes, total_edges;
+    uint64_t draws;
+} ag_hetero_counts;
+
+/* fanout: [num_edge_types][num_hops] row-major, 0 = do not follow that edge
+ * type at that hop (hetero_sampler.rs:25-60). */
+int32_t ag_hetero_sampler_create(const ag_hetero_graph *h, const uint32_t *fanout, uint32_t num_hops,
+                                 int32_t replace, uint64_t seed, int32_t rng_mode,
+                                 ag_hetero_sampler **out);
+int32_t ag_hetero_sampler_reseed(ag_hetero_sampler *s, uint64_t seed);
+int32_t ag_hetero_sampler_bounds(const ag_hetero_sampler *s, uint64_t n_seeds, uint64_t *max_nodes,
+                                 uint64_t *max_edges);
+/* Seeds are host ids of node type seed_type, checked before anything is
+ * launched (hetero_sampler.rs:174-187: AG_ERR_SAMPLING names the seed). */
+int32_t ag_hetero_sample_into(ag_hetero_sampler *s, uint32_t seed_type, const uint32_t *seeds,
+                              uint64_t n_seeds, ag_hetero_buffers *buf, void *stream);
+int32_t ag_hetero_sample_wait(ag_hetero_sampler *s, ag_hetero_counts *counts);
+void ag_hetero_sampler_free(ag_hetero_sampler *s);
+
 /* --------------------------------------------------------------- loader --
  * Stands in for the prefetching NeighborLoader (_core.pyi:380-464;
  * crates/aethergraph-core/src/loader/prefetch.rs:402-560 pipeline,
