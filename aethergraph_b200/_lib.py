@@ -65,7 +65,7 @@ class LoaderStats(C.Structure):
     _fields_ = [("hits", C.c_uint64), ("misses", C.c_uint64), ("total", C.c_uint64),
                 ("sample_time_ns", C.c_uint64), ("feature_load_time_ns", C.c_uint64),
                 ("submitted", C.c_uint64), ("edges", C.c_uint64), ("nodes", C.c_uint64),
-                ("gather_ms", C.c_double), ("sample_ms", C.c_double)]
+                ("gather_ms", C.c_double), ("sample_ms", C.c_double), ("chains", C.c_uint64)]
 
 
 AG_MAX_NODE_TYPES, AG_MAX_EDGE_TYPES = 8, 16

@@ -256,7 +256,7 @@ void worker_main(ag_loader *l, uint32_t idx) {
                 for (uint32_t r = b; r < nb; ++r) drop_work(l, ws[r]);
                 return;
             }
-            if (b == 0) l->stats.sample_time_ns += ns;
+            if (b == 0) { l->stats.sample_time_ns += ns; l->stats.chains += (l->seeded || nb == 1) ? 1 : nb; }
             if (d.status != AG_OK && l->fault.empty() && d.status != AG_ERR_SAMPLING && d.status != AG_ERR_VALUE)
                 l->fault = d.error;  // a broken worker poisons the loader; a bad batch does not
             l->ready.emplace(w.seq, std::move(d));

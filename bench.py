@@ -48,10 +48,19 @@ WORKLOADS = {
     # 10M-vertex weighted R-MAT, 200M edges, 128-dim f16, batch 512, fanout [15, 10, 5]
     "c3": dict(nodes=10_000_000, edges=200_000_000, dim=128, dtype="f16", batch=512, fanout=[15, 10, 5],
                weighted=True, label="C3: weighted R-MAT 10M vertices / 200M edges, 128-dim f16, batch 512, fanout [15,10,5]"),
+    # C2's batch shape and feature rows on a graph small enough to profile (features 2 GB, CSR 0.3 GB)
+    "c2s": dict(nodes=4_000_000, edges=64_000_000, dim=256, dtype="bf16", batch=1024, fanout=[25, 10],
+                weighted=False, label="C2-small: R-MAT 4M vertices / 64M edges, 256-dim bf16, batch 1024, fanout [25,10]"),
     "tiny": dict(nodes=1 << 16, edges=1 << 20, dim=64, dtype="bf16", batch=256, fanout=[10, 5], weighted=False,
                  label="tiny: R-MAT 64K vertices / 1M edges, 64-dim bf16, batch 256, fanout [10,5]"),
 }
 GRAPH_SEED, FEATURE_SEED, SEEDS_SEED, SAMPLER_SEED = 1, 2, 3, 42
+
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per gathered row of
+# k_gather_vec, from the ncu capture summarised in
+# profiles/k_gather_vec_c2small_ncu_full.md: 647.6 MB for a launch over 495,171 rows
+# of 256 bf16 -> f32 (1536 algorithmic bytes per row).
+NCU_DRAM_BYTES_PER_ROW = {"bf16256": 1308}
 
 
 def sector(x: int) -> int:
@@ -322,20 +331,16 @@ def run_device(args, w):
     n_timed = args.steps * per_step
     peak, peak_src = peaks()
     achieved = nodes * row_bytes / (g_ms * 1e-3) / 1e9 if g_ms > 0 else None
-    traffic = None
-    tp = os.path.join(ROOT, "profiles", "gather_traffic.json")
-    if os.path.exists(tp):
-        try:
-            t = json.load(open(tp))
-            traffic = t["dram_bytes_per_row"][w["dtype"] + str(w["dim"])] * nodes / n_timed
-        except Exception:
-            traffic = None
+    # one gather launch per chain (a chain covers up to `group` batches, the batch is blockIdx.y)
+    launches = max(int(stats1.chains - stats0.chains), 1)
+    per_row = NCU_DRAM_BYTES_PER_ROW.get(w["dtype"] + str(w["dim"]))
     roofline = {
         "kernel": "k_gather_vec (feature-row gather + upcast)", "bound": "hbm",
         "achieved": achieved, "peak": peak, "unit": "GB/s",
         "frac": (achieved / peak) if achieved else None, "peak_source": peak_src,
-        "bytes_per_launch": nodes * row_bytes / n_timed, "ms_per_launch": g_ms / n_timed,
-        "launches": n_timed, "traffic": traffic,
+        "bytes_per_launch": nodes * row_bytes / launches, "ms_per_launch": g_ms / launches,
+        "launches": launches, "traffic": (per_row * nodes / launches) if per_row else None,
+        "traffic_note": "ncu dram bytes per gathered row on the C2-small capture x rows per launch",
         "note": "per-launch time from CUDA events on the launching stream while the other "
                 "streams' sampling kernels run beside it",
         "pipeline": {"algorithmic_gbs": (tot_nodes * row_bytes + sampling_bytes(tot_edges, tot_nodes, tot_nodes))
@@ -348,35 +353,64 @@ def run_device(args, w):
     del ring
 
     # ---- e2e: public Python API, host seeds in, counts back -----------------
-    loader = NeighborLoader(g, cfg, prefetch_depth=depth, sampler_threads=threads, features=feats, group=group)
+    e2e_value = ms_e2e = host_value = host_ms = None
+    d2h_host = 0
+    if not args.only_value:
+        loader = NeighborLoader(g, cfg, prefetch_depth=depth, sampler_threads=threads, features=feats, group=group)
+        pinned = None
 
-    def run_e2e(first: int, count: int):
-        edges = submitted = delivered = 0
-        while delivered < count:
-            while submitted < count and submitted - delivered < window:
-                loader.submit(gidx[first + submitted], seeds_host[first + submitted])
-                submitted += 1
-            _, sg, x = loader.next_batch()
-            edges += sg.num_edges
-            delivered += 1
-        return edges
+        def run_e2e(first: int, count: int, to_host: bool = False):
+            """Host seed arrays in through the public API; `to_host` also copies every
+            batch (ids, local edge index, feature rows) into pinned host memory."""
+            nonlocal d2h_host
+            edges = submitted = delivered = 0
+            while delivered < count:
+                while submitted < count and submitted - delivered < window:
+                    b = (first + submitted) % n_batches
+                    loader.submit(gidx[b], seeds_host[b])
+                    submitted += 1
+                _, sg, x = loader.next_batch()
+                if to_host:
+                    nn, ne = sg.num_nodes, sg.num_edges
+                    pinned["n_id"][:nn].copy_(sg.nodes_t, non_blocking=True)
+                    pinned["ei"][:, :ne].copy_(sg.edge_index_local_t, non_blocking=True)
+                    pinned["x"][:nn].copy_(x, non_blocking=True)
+                    torch.cuda.current_stream().synchronize()
+                    d2h_host += nn * 8 + ne * 16 + nn * w["dim"] * 4
+                edges += sg.num_edges
+                delivered += 1
+            return edges
 
-    run_e2e(0, args.warmup * per_step)
-    barrier()
-    e0.record()
-    edges_e2e = run_e2e(args.warmup * per_step, args.steps * per_step)
-    e1.record()
-    barrier()
-    ms_e2e = max_over_ranks(e0.elapsed_time(e1))
-    e2e_value = sum_over_ranks(edges_e2e) / (ms_e2e * 1e-3)
-    loader.shutdown()
-    del loader
+        # warm-up long enough for the loader's buffer pool to reach its working size
+        run_e2e(0, max(args.warmup * per_step, 2 * window))
+        barrier()
+        e0.record()
+        edges_e2e = run_e2e(args.warmup * per_step, args.steps * per_step)
+        e1.record()
+        barrier()
+        ms_e2e = max_over_ranks(e0.elapsed_time(e1))
+        e2e_value = sum_over_ranks(edges_e2e) / (ms_e2e * 1e-3)
+        # the same with every batch also copied to pinned host memory (what a host-side consumer sees)
+        pinned = {"n_id": torch.empty(mn.value, dtype=torch.int64).pin_memory(),
+                  "ei": torch.empty((2, me.value), dtype=torch.int64).pin_memory(),
+                  "x": torch.empty((mn.value, w["dim"]), dtype=torch.float32).pin_memory()}
+        run_e2e(0, per_step, True)
+        d2h_host = 0
+        barrier()
+        e0.record()
+        edges_host = run_e2e(args.warmup * per_step, args.steps * per_step, True)
+        e1.record()
+        barrier()
+        host_ms = max_over_ranks(e0.elapsed_time(e1))
+        host_value = sum_over_ranks(edges_host) / (host_ms * 1e-3)
+        loader.shutdown()
+        del loader
 
     # ---- CPU baseline beside it (rank 0, one GPU only) ----------------------
     cpu = None
     parity = None
-    if rank == 0 and world == 1 and not args.no_cpu:
-        cpu, parity = cpu_baseline(g, feats, w, cfg, seeds_host, gidx)
+    if rank == 0 and world == 1 and not args.no_cpu and not args.only_value:
+        cpu, parity = cpu_baseline(g, feats, w, cfg)
 
     if rank == 0:
         hops = len(w["fanout"])
@@ -391,24 +425,30 @@ def run_device(args, w):
             "gather_gbs": gather_gbs, "edges_per_step": tot_edges / max(args.steps, 1),
             "rows_per_step": tot_nodes / max(args.steps, 1), "setup_s": round(t_setup, 1),
             "clocks": clk, "roofline": roofline, "cpu_baseline": cpu, "parity_full_scale": parity,
-            "e2e": {"value": e2e_value, "unit": "edges/s", "h2d_bytes_per_step": per_step * bs * 4,
-                    "d2h_bytes_per_step": per_step * C.sizeof(_lib.SampleCounts),
-                    "ms_per_step": ms_e2e / max(args.steps, 1),
-                    "note": "host seed arrays in, per-batch counts out; the batch stays in GPU memory"},
-            "gpu_launches": n_timed * (2 + (hops + 1) + hops + 1 + 1),
+            "e2e": None if e2e_value is None else {
+                "value": e2e_value, "unit": "edges/s", "h2d_bytes_per_step": per_step * bs * 4,
+                "d2h_bytes_per_step": per_step * C.sizeof(_lib.SampleCounts),
+                "ms_per_step": ms_e2e / max(args.steps, 1),
+                "note": "public Python API: host seed arrays in, per-batch counts out; the sampled batch and "
+                        "its feature rows stay in GPU memory, where the training step reads them",
+                "host_results": {"value": host_value, "unit": "edges/s", "ms_per_step": host_ms / max(args.steps, 1),
+                                 "d2h_bytes_per_step": d2h_host / max(args.steps, 1),
+                                 "note": "same calls, every batch (int64 ids, local edge index, f32 feature rows) "
+                                         "also copied to pinned host memory: PCIe-bound"}},
+            # one launch chain per group of batches (the batch is blockIdx.y): seed insert,
+            # hops + 1 assign, hops pick, finalize, gather
+            "gpu_launches": world * -(-n_timed // group) * (2 * hops + 4),
         }
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
 
-def cpu_baseline(g, feats, w, cfg, seeds_host, gidx):
+def cpu_baseline(g, feats, w, cfg):
     """Times the CPU restatement on a bounded sample of the same workload (graph and
     features copied back from the GPU) and checks two full-size batches bit for bit."""
-    import torch
-
     import aethergraph_b200 as ag
-    from aethergraph_b200 import _lib
+    from aethergraph_b200 import synth
     from oracle import ago
 
     ago.build()
@@ -420,14 +460,17 @@ def cpu_baseline(g, feats, w, cfg, seeds_host, gidx):
     threads = cpu_threads()
     s = ago.Sampler(offsets, dst, w["fanout"], weights=weights, weighted=w["weighted"], seed=SAMPLER_SEED)
     bs = w["batch"]
-    # bounded sample: grow until the timed run lasts a few seconds
-    nb = min(len(seeds_host), 2 * threads)
+    # bounded sample: batches 0, 1, ... of the workload's seed stream, grown until
+    # the timed run lasts about ten seconds
+    seeds_host = [synth.seed_batch(w["nodes"], bs, SEEDS_SEED, b) for b in range(4 * threads)]
+    nb, cap = len(seeds_host), 1 << 16
     while True:
         seeds = np.concatenate(seeds_host[:nb])
         r = s.bench(payload, w["dim"], w["dtype"], seeds, bs, 0, threads)
-        if r["seconds"] >= 5.0 or nb >= len(seeds_host):
+        if r["seconds"] >= 8.0 or nb >= cap:
             break
-        nb = min(len(seeds_host), max(nb + 1, int(nb * min(8.0, 7.0 / max(r["seconds"], 1e-3)))))
+        nb = min(cap, max(nb + 1, int(nb * min(16.0, 12.0 / max(r["seconds"], 1e-3)))))
+        seeds_host += [synth.seed_batch(w["nodes"], bs, SEEDS_SEED, b) for b in range(len(seeds_host), nb)]
     cpu = {"value": r["edges"] / r["seconds"], "unit": "edges/s", "cores": threads, "kind": "port",
            "gather_gbs": r["nodes"] * gather_bytes_per_row(w) / r["seconds"] / 1e9,
            "sample": f"{nb} batches of {bs} seeds of the same workload (graph and features copied back from "
@@ -459,6 +502,8 @@ def main():
     ap.add_argument("--group", type=int, default=int(os.environ.get("AG_BENCH_GROUP", "16")),
                     help="batches a worker runs as one launch chain")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--only-value", action="store_true",
+                    help="run the resident (C ABI) leg only: no e2e, no CPU baseline (profiling runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
     w = WORKLOADS[args.workload]

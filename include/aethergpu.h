@@ -388,6 +388,7 @@ typedef struct {
     uint64_t sample_time_ns, feature_load_time_ns;
     uint64_t submitted, edges, nodes;        /* totals over delivered batches */
     double gather_ms, sample_ms;             /* device time, when profiling is on */
+    uint64_t chains;                         /* launch chains run (a chain covers up to `group` batches) */
 } ag_loader_stats;
 
 int32_t ag_loader_create(const ag_graph *g, const ag_features *f, const ag_sampling_config *cfg,
