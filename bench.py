@@ -426,8 +426,8 @@ def run_device(args, w):
             "rows_per_step": tot_nodes / max(args.steps, 1), "setup_s": round(t_setup, 1),
             "clocks": clk, "roofline": roofline, "cpu_baseline": cpu, "parity_full_scale": parity,
             "e2e": None if e2e_value is None else {
-                "value": e2e_value, "unit": "edges/s", "h2d_bytes_per_step": per_step * bs * 4,
-                "d2h_bytes_per_step": per_step * C.sizeof(_lib.SampleCounts),
+                "value": e2e_value, "unit": "edges/s", "h2d_bytes_per_step": world * per_step * bs * 4,
+                "d2h_bytes_per_step": world * per_step * C.sizeof(_lib.SampleCounts),
                 "ms_per_step": ms_e2e / max(args.steps, 1),
                 "note": "public Python API: host seed arrays in, per-batch counts out; the sampled batch and "
                         "its feature rows stay in GPU memory, where the training step reads them",

@@ -1,0 +1,135 @@
+"""Epoch driver (`aethergraph_b200.pytorch.NeighborLoader`) against the CPU oracle.
+
+Every batch of an epoch must be what the reference produces for the same
+arguments: seeds from the same batch getter, sampled from
+batch_seed(epoch seed, batch number) (python/aethergraph/pytorch/loader.py:195-205,
+crates/aethergraph-core/src/loader/prefetch.rs:926-930), delivered in order, with
+the feature rows of `n_id`.  Bit-exact.
+"""
+import numpy as np
+import pytest
+
+from helpers import rmat_csr
+
+pytestmark = pytest.mark.gpu
+
+
+def _graph_and_features(ag, scale=12, dim=24):
+    n, off, dst, _ = rmat_csr(scale, 10, seed=17)
+    g = ag.Graph.from_csr(off, dst)
+    feats = np.random.default_rng(5).standard_normal((n, dim)).astype(np.float32)
+    return n, off, dst, g, feats
+
+
+def _expect(ago, off, dst, fanout, epoch_seed, b, seeds, **kw):
+    s = ago.Sampler(off, dst, fanout, seed=ago.batch_seed(epoch_seed, b), **kw)
+    return s.sample(np.asarray(seeds, dtype=np.uint32))
+
+
+def _check_batch(data, want, feats, seeds, input_id):
+    n_id = data.n_id.cpu().numpy()
+    assert np.array_equal(n_id, want["nodes"].astype(np.int64))
+    ei = data.edge_index.cpu().numpy()
+    assert ei.shape == (2, len(want["dst_local"]))
+    assert np.array_equal(ei[0], want["dst_local"]) and np.array_equal(ei[1], want["src_local"])
+    assert np.array_equal(data.e_id.cpu().numpy(), want["edge_ids"].astype(np.int64))
+    assert np.array_equal(data.seed_index.cpu().numpy(), want["seed_locals"].astype(np.int64))
+    assert np.array_equal(data.input_id.cpu().numpy(), input_id)
+    assert data.batch_size == len(seeds) and data.num_nodes == len(n_id)
+    assert np.array_equal(n_id[data.seed_index.cpu().numpy()], seeds)
+    assert list(data.num_sampled_nodes) == want["num_sampled_nodes"].tolist()
+    assert list(data.num_sampled_edges) == want["num_sampled_edges"].tolist()
+    if feats is not None:
+        assert data.x.is_cuda and np.array_equal(data.x.cpu().numpy().view(np.uint32), feats[n_id].view(np.uint32))
+
+
+def test_all_nodes_in_order_matches_the_oracle_and_epochs_resample():
+    import aethergraph_b200 as ag
+    from aethergraph_b200.pytorch import NeighborLoader
+    from aethergraph_b200.pytorch.loader import epoch_sampling_seed
+    from oracle import ago
+
+    n, off, dst, g, feats = _graph_and_features(ag)
+    fanout, bs = [6, 4], 500
+    loader = NeighborLoader(g, fanout, batch_size=bs, shuffle=False, seed=7, features=feats, num_workers=2,
+                            prefetch_factor=3)
+    assert len(loader) == (n + bs - 1) // bs
+    ss = np.random.SeedSequence(7)
+    first_epoch = None
+    for epoch in range(2):
+        es = epoch_sampling_seed(ss)
+        count = 0
+        for b, data in enumerate(loader):
+            seeds = np.arange(b * bs, min((b + 1) * bs, n), dtype=np.int64)
+            _check_batch(data, _expect(ago, off, dst, fanout, es, b, seeds), feats, seeds, seeds)
+            if b == 0:
+                if epoch == 0:
+                    first_epoch = data.edge_index.cpu().numpy()
+                else:  # a new epoch draws new neighborhoods for the same seeds
+                    assert not np.array_equal(first_epoch, data.edge_index.cpu().numpy())
+            count += 1
+        assert count == len(loader)
+        m = loader.metrics
+        assert m.batches_processed == count and m.total_time_ms > 0 and 0.0 <= m.prefetch_hit_rate <= 1.0
+        assert m.prefetch_hits + m.prefetch_misses == count
+    # a loader built with the same seed replays the same epochs
+    again = NeighborLoader(g, fanout, batch_size=bs, shuffle=False, seed=7, features=feats)
+    assert np.array_equal(next(iter(again)).edge_index.cpu().numpy(), first_epoch)
+
+
+def test_shuffled_input_nodes_mask_and_strided_permutation():
+    import aethergraph_b200 as ag
+    from aethergraph_b200.pytorch import NeighborLoader
+    from aethergraph_b200.pytorch.loader import epoch_sampling_seed
+    from oracle import ago
+
+    n, off, dst, g, feats = _graph_and_features(ag, scale=11)
+    fanout, bs = [5, 3], 128
+    mask = np.zeros(n, dtype=bool)
+    mask[::3] = True
+    nodes = np.nonzero(mask)[0].astype(np.int64)
+    loader = NeighborLoader(g, fanout, input_nodes=mask, batch_size=bs, shuffle=True, seed=11, features=feats,
+                            transform=lambda d: d)
+    order = np.random.default_rng(11).spawn(1)[0].permutation(len(nodes))   # loader.py:155-156
+    es = epoch_sampling_seed(np.random.SeedSequence(11))
+    seen = []
+    for b, data in enumerate(loader):
+        pos = order[b * bs:(b + 1) * bs]
+        _check_batch(data, _expect(ago, off, dst, fanout, es, b, nodes[pos]), feats, nodes[pos], pos)
+        seen.append(nodes[pos])
+    assert np.array_equal(np.sort(np.concatenate(seen)), nodes)
+    # all nodes + shuffle: the coprime-stride walk visits every node exactly once (loader.py:169-184)
+    loader = NeighborLoader(g, [2], batch_size=200, shuffle=True, seed=3, track_edge_ids=False)
+    got = [d for d in loader]
+    assert all(d.e_id is None and d.x is None for d in got)
+    ids = np.concatenate([d.n_id.cpu().numpy()[d.seed_index.cpu().numpy()] for d in got])
+    assert np.array_equal(np.sort(ids), np.arange(n))
+    assert not np.array_equal(ids, np.arange(n))
+
+
+def test_early_break_custom_sampler_and_argument_errors():
+    import aethergraph_b200 as ag
+    from aethergraph_b200.pytorch import NeighborLoader
+
+    n, off, dst, g, feats = _graph_and_features(ag, scale=10)
+    loader = NeighborLoader(g, [3, 2], batch_size=64, seed=1)
+    for i, data in enumerate(loader):
+        if i == 2:
+            break  # the generator's cleanup shuts the native loader down
+    assert loader.metrics.batches_processed == 3
+    calls = []
+    custom = NeighborLoader(g, [3], batch_size=256, shuffle=False,
+                            neighbor_sampler=lambda graph, seeds: calls.append(len(seeds)) or len(seeds))
+    assert list(custom) == calls and sum(calls) == n
+    with pytest.raises(ValueError, match="float32"):
+        NeighborLoader(g, [3], features=feats.astype(np.float64))
+    with pytest.raises(ValueError, match="does not match graph num_nodes"):
+        NeighborLoader(g, [3], features=feats[:-1])
+    with pytest.raises(ValueError, match="out-of-range node IDs"):
+        NeighborLoader(g, [3], input_nodes=[0, n])
+    with pytest.raises(ValueError, match="unrecognized feature_source"):
+        NeighborLoader(g, [3], feature_source="http://x")
+    with pytest.raises(NotImplementedError):
+        NeighborLoader(g, [3], input_time=np.zeros(4))
+    with pytest.raises(ValueError, match="not both"):
+        NeighborLoader(g, [3], features=feats, feature_path="x.bin")
