@@ -128,6 +128,7 @@ SIGNATURES = {
     "ag_subgraph_release": (C.c_int32, [_P, C.POINTER(SubgraphBuffers)]),
     "ag_sampler_free": (None, [_P]),
     "ag_sampler_set_profiling": (C.c_int32, [_P, C.c_int32]),
+    "ag_sample_hop_reservoir": (C.c_int32, [_P, _P, C.c_uint64, C.c_uint32, C.c_uint64, C.c_uint32, _P, _P, _P]),
     "ag_register_seeds_static_max": (C.c_uint32, []),
     "ag_register_seeds_static": (C.c_int32, [C.c_int32, _P, C.c_uint32, C.c_uint64, _P, _P, _P, _P]),
     "ag_sampler_create_group": (C.c_int32, [_P, C.POINTER(SamplingConfigC), C.c_uint32, _PP]),

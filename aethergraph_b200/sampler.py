@@ -522,3 +522,27 @@ class ParallelBatchSampler:
             # caller's stream uses them too before it may recycle them.
             sg._b.record_stream(cur)  # type: ignore[union-attr]
         return out  # type: ignore[return-value]
+
+
+SAMPLE_PAD = 0xFFFFFFFF
+
+
+def reservoir_hop(graph: CsrGraph, nodes, fanout: int, seed: int, layer: int = 0):
+    """One hop of the reference's Philox fast mode for a list of nodes: returns
+    `(neighbors [n, fanout] int32 CUDA tensor holding u32 ids, counts [n])`, bit for
+    bit what `reservoir_sample` (crates/aethergraph-core/src/internal/philox.rs:59-82)
+    and the `warp_sample_neighbors` kernel give; unused slots hold SAMPLE_PAD."""
+    import torch
+
+    dev = torch.device("cuda", graph.device)
+    if isinstance(nodes, torch.Tensor):
+        ids = nodes.to(device=dev, dtype=torch.int64).contiguous()
+    else:
+        ids = torch.from_numpy(np.ascontiguousarray(np.asarray(nodes).astype(np.uint64)).view(np.int64)).to(dev)
+    n = int(ids.numel())
+    out = torch.empty((n, int(fanout)), dtype=torch.int32, device=dev)
+    counts = torch.empty((n,), dtype=torch.int32, device=dev)
+    _lib.check(_lib.lib().ag_sample_hop_reservoir(graph._h, ids.data_ptr() if n else None, n, int(fanout),
+                                                  int(seed) & (2**64 - 1), int(layer), out.data_ptr(),
+                                                  counts.data_ptr(), torch.cuda.current_stream(dev).cuda_stream))
+    return out, counts

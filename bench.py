@@ -145,6 +145,19 @@ def cpu_threads() -> int:
         return os.cpu_count() or 1
 
 
+def host_description() -> str:
+    """`nproc` and the CPU model name of the box the CPU legs ran on."""
+    model = "unknown CPU"
+    try:
+        for line in open("/proc/cpuinfo"):
+            if line.startswith("model name"):
+                model = line.split(":", 1)[1].strip()
+                break
+    except OSError:
+        pass
+    return f"{cpu_threads()} logical CPUs, {model}"
+
+
 def host_seed_batches(w, first_batch: int, count: int) -> np.ndarray:
     from aethergraph_b200 import synth
 
@@ -192,7 +205,8 @@ def run_reference(args, w):
                    "C restatement of the reference's Rust CPU sampler + gather (no Rust toolchain on this image)"},
         "gather_gbs": gbs, "edges": r["edges"], "nodes": r["nodes"], "checksum": f"{r['checksum']:016x}",
         "setup_s": round(t_setup, 1), "wall_s": round(wall, 3),
-        "cpu_baseline": {"value": value, "unit": "edges/s", "cores": threads, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "edges/s", "cores": threads, "kind": "port", "sample": sample,
+                         "host": host_description()},
         "e2e": {"value": value, "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -338,6 +352,7 @@ def run_device(args, w):
         "kernel": "k_gather_vec (feature-row gather + upcast)", "bound": "hbm",
         "achieved": achieved, "peak": peak, "unit": "GB/s",
         "frac": (achieved / peak) if achieved else None, "peak_source": peak_src,
+        "frac_of_nominal_8tbs": (achieved / 8000.0) if achieved else None,
         "bytes_per_launch": nodes * row_bytes / launches, "ms_per_launch": g_ms / launches,
         "launches": launches, "traffic": (per_row * nodes / launches) if per_row else None,
         "traffic_note": "ncu dram bytes per gathered row on the C2-small capture x rows per launch",
@@ -471,8 +486,14 @@ def cpu_baseline(g, feats, w, cfg):
             break
         nb = min(cap, max(nb + 1, int(nb * min(16.0, 12.0 / max(r["seconds"], 1e-3)))))
         seeds_host += [synth.seed_batch(w["nodes"], bs, SEEDS_SEED, b) for b in range(len(seeds_host), nb)]
+    # one thread, one persistent sampler reused across batches (the reference's NeighborSampler reuse)
+    n1 = max(4, min(nb, int(4.0 * nb / max(r["seconds"], 1e-3) / threads)))
+    r1 = s.bench(payload, w["dim"], w["dtype"], np.concatenate(seeds_host[:n1]), bs, 0, 1)
     cpu = {"value": r["edges"] / r["seconds"], "unit": "edges/s", "cores": threads, "kind": "port",
            "gather_gbs": r["nodes"] * gather_bytes_per_row(w) / r["seconds"] / 1e9,
+           "single_thread": {"value": r1["edges"] / r1["seconds"], "unit": "edges/s",
+                             "sample": f"{n1} batches, 1 thread, {r1['seconds']:.2f} s"},
+           "host": host_description(),
            "sample": f"{nb} batches of {bs} seeds of the same workload (graph and features copied back from "
                      f"the GPU), {threads} threads, {r['seconds']:.2f} s"}
     # full-size parity: batch positions 0 and 1, bit for bit

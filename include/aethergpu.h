@@ -257,6 +257,22 @@ int32_t ag_sample_group_wait(ag_sampler *s, ag_sample_counts *counts, int32_t *s
 int32_t ag_sampler_set_profiling(ag_sampler *s, int32_t on);
 void ag_sampler_free(ag_sampler *s);
 
+/* ------------------------------------------- fast mode: one-hop reservoir --
+ * Stands in for the reference's Philox fast-mode sampler, bit for bit: CPU
+ * `reservoir_sample` (crates/aethergraph-core/src/internal/philox.rs:59-82) and
+ * its GPU kernel `warp_sample_neighbors`
+ * (crates/aether-stream/src/gpu/kernels/sampler/sampler.cu, launched by
+ * sampler/mod.rs:180-230).  For each of node_count nodes (u64 ids, device
+ * array; an id outside the graph gives an empty row) writes `fanout` slots to
+ * neighbors_out_dev[row * fanout ..] and the number of real ones to
+ * counts_out_dev[row]; unused slots hold AG_SAMPLE_PAD.  fanout >= degree
+ * copies the row; fanout <= 32 runs Algorithm R keyed on (seed, layer, node, t);
+ * fanout > 32 draws with replacement, slot d = row[philox(d) % degree]. */
+#define AG_SAMPLE_PAD 0xffffffffu
+int32_t ag_sample_hop_reservoir(const ag_graph *g, const uint64_t *nodes_dev, uint64_t node_count,
+                                uint32_t fanout, uint64_t seed, uint32_t layer,
+                                uint32_t *neighbors_out_dev, uint32_t *counts_out_dev, void *stream);
+
 /* ------------------------------------------------ allocation-free entry --
  * No counterpart in the reference.  For callers that must not allocate device
  * memory while they run (a memory-pool or stream callback, a process whose

@@ -31,6 +31,41 @@ def build(force: bool = False) -> str:
     return _LIB_PATH
 
 
+REF_WARP_SAMPLER = os.path.join(_HERE, "_ref", "libref_warp_sampler.so")
+_REF_ROOT = "/root/reference"
+
+
+def build_ref() -> str | None:
+    """Compile the reference's own CUDA sampler kernel (from the reference checkout,
+    where one is present) into oracle/_ref/.  Returns the library path, or None
+    when neither a checkout nor a previously built library exists."""
+    src = os.path.join(_REF_ROOT, "crates", "aether-stream", "src", "gpu", "kernels", "sampler", "sampler.cu")
+    if os.path.exists(src):
+        subprocess.run(["make", "-C", _HERE, "ref", f"REF={_REF_ROOT}"], check=True,
+                       stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+    return REF_WARP_SAMPLER if os.path.exists(REF_WARP_SAMPLER) else None
+
+
+_ref_lib = None
+
+
+def ref_warp_sample(offsets_ptr: int, neighbors_ptr: int, num_nodes: int, nodes_ptr: int, output_ptr: int,
+                    counts_ptr: int, node_count: int, fanout: int, seed: int, layer: int, stream: int = 0) -> None:
+    """Launch the reference's `warp_sample_neighbors` on device arrays (raw pointers)."""
+    global _ref_lib
+    if _ref_lib is None:
+        if not os.path.exists(REF_WARP_SAMPLER):
+            raise FileNotFoundError(REF_WARP_SAMPLER)
+        _ref_lib = C.CDLL(REF_WARP_SAMPLER)
+        _ref_lib.ref_warp_sample_launch.restype = C.c_int
+        _ref_lib.ref_warp_sample_launch.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p,
+                                                    C.c_void_p, C.c_int, C.c_int, C.c_uint64, C.c_uint32, C.c_void_p]
+    rc = _ref_lib.ref_warp_sample_launch(offsets_ptr, neighbors_ptr, num_nodes, nodes_ptr, output_ptr, counts_ptr,
+                                         node_count, fanout, seed & (2**64 - 1), layer, stream or None)
+    if rc != 0:
+        raise RuntimeError(f"reference warp_sample_neighbors launch failed: cudaError {rc}")
+
+
 class _Csr(C.Structure):
     _fields_ = [("offsets", C.c_void_p), ("edges", C.c_void_p), ("weights", C.c_void_p),
                 ("num_nodes", C.c_uint64), ("num_edges", C.c_uint64)]
