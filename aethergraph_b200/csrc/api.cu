@@ -412,6 +412,7 @@ extern "C" int32_t ag_graph_copy_to_host(const ag_graph *g, uint64_t *offsets, u
 
 extern "C" int32_t ag_features_copy_to_host(const ag_features *f, void *payload) {
     if (!f || !payload) return fail(AG_ERR_VALUE, "ag_features_copy_to_host: null argument");
+    if (f->shards) return fail(AG_ERR_VALUE, "ag_features_copy_to_host: a sharded view holds no rows of its own; copy each shard");
     DeviceGuard guard(f->device);
     if (!guard.ok) return AG_ERR_CUDA;
     const uint64_t bytes = f->rows * f->dim * elem_size(f->dtype);
@@ -568,6 +569,8 @@ extern "C" void ag_features_free(ag_features *f) {
     if (!f) return;
     DeviceGuard guard(f->device);
     if (f->owns_payload) cudaFree(f->payload);
+    for (void *p : f->ipc_opened) if (p) cudaIpcCloseMemHandle(p);
+    cudaFree(f->shards);
     cudaFree(f->err);
     delete f;
 }
@@ -692,9 +695,8 @@ extern "C" int32_t ag_gather(const ag_features *f, const void *ids_dev, int32_t 
     DeviceGuard guard(f->device);
     if (!guard.ok) return AG_ERR_CUDA;
     GatherArgs a{};
-    a.payload = f->payload; a.row_begin = f->row_begin; a.rows = f->rows;
-    a.row_bytes = (uint32_t)(f->dim * elem_size(f->dtype)); a.dim = (uint32_t)f->dim;
-    a.ids = ids_dev; a.ids64 = ids_are_i64; a.n = n; a.n_dev = n_dev; a.out = out_dev; a.err = f->err;
+    set_gather_source(a, f);
+    a.ids = ids_dev; a.ids64 = ids_are_i64; a.n = n; a.n_dev = n_dev; a.out = out_dev;
     AG_CUDA(launch_gather(a, f->dtype, (cudaStream_t)stream));
     return AG_OK;
 }

@@ -72,9 +72,27 @@ __device__ __forceinline__ uint64_t load_id(const void *ids, int ids64, uint64_t
     return ids64 ? (uint64_t)((const int64_t *)ids)[i] : (uint64_t)((const uint32_t *)ids)[i];
 }
 
+// Plain (coherent) 16-byte load that does not allocate in L1: rows of a peer
+// GPU's shard arrive over NVLink through this.
+__device__ __forceinline__ uint4 ld_peer_v4(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+// Where row `id` of a sharded store lives: shard id / shard_rows, which is this
+// GPU's own memory or a peer's (vertex-range shards of equal size).
+__device__ __forceinline__ const uint8_t *shard_row(const ag_shard_table *t, uint64_t id, uint32_t row_bytes) {
+    const uint64_t s = id / t->shard_rows;
+    return t->base[s] + (id - s * t->shard_rows) * row_bytes;
+}
+
 // Vector path: row_bytes % 16 == 0 and the payload base is 16-byte aligned.
-// LPR lanes share a row; vecs = row_bytes / 16.
-template <int DTYPE, int LPR>
+// LPR lanes share a row; vecs = row_bytes / 16.  SHARDED: the store is split by
+// vertex range over several GPUs and every row is fetched straight from its
+// owner's memory (local HBM or a peer over NVLink), upcast at the reader.
+template <int DTYPE, int LPR, bool SHARDED>
 __global__ void __launch_bounds__(kThreads)
 k_gather_vec(GatherArgs a, const GatherArgs *__restrict__ group) {
     constexpr int kRowsPerBlock = kThreads / LPR;
@@ -106,7 +124,8 @@ k_gather_vec(GatherArgs a, const GatherArgs *__restrict__ group) {
                     const uint64_t local = id - a.row_begin;
                     ok[u] = true;
                     if (id >= a.row_begin && local < a.rows) {
-                        val[u] = ld_stream_v4(a.payload + local * a.row_bytes + ((uint64_t)v << 4));
+                        if (SHARDED) val[u] = ld_peer_v4(shard_row(a.shards, id, a.row_bytes) + ((uint64_t)v << 4));
+                        else val[u] = ld_stream_v4(a.payload + local * a.row_bytes + ((uint64_t)v << 4));
                     } else if (lane == 0) {
                         atomicOr(a.err, kErrBadId);
                     }
@@ -139,10 +158,17 @@ k_gather_elem(GatherArgs a, const GatherArgs *__restrict__ group) {
         const uint64_t local = id - a.row_begin;
         float f = 0.f;
         if (id >= a.row_begin && local < a.rows) {
-            const uint8_t *row = a.payload + local * a.row_bytes;
-            if (DTYPE == AG_F32) f = __uint_as_float(ld_stream_u32(row + 4ull * j));
-            else if (DTYPE == AG_BF16) f = bf16lo(ld_stream_u16(row + 2ull * j));
-            else f = f16_to_f32_bits(ld_stream_u16(row + 2ull * j));
+            if (a.shards) {  // sharded store: plain loads from the owner's memory
+                const uint8_t *row = shard_row(a.shards, id, a.row_bytes);
+                if (DTYPE == AG_F32) f = __uint_as_float(*(const volatile uint32_t *)(row + 4ull * j));
+                else if (DTYPE == AG_BF16) f = bf16lo(*(const volatile uint16_t *)(row + 2ull * j));
+                else f = f16_to_f32_bits(*(const volatile uint16_t *)(row + 2ull * j));
+            } else {
+                const uint8_t *row = a.payload + local * a.row_bytes;
+                if (DTYPE == AG_F32) f = __uint_as_float(ld_stream_u32(row + 4ull * j));
+                else if (DTYPE == AG_BF16) f = bf16lo(ld_stream_u16(row + 2ull * j));
+                else f = f16_to_f32_bits(ld_stream_u16(row + 2ull * j));
+            }
         } else if (j == 0) {
             atomicOr(a.err, kErrBadId);
         }
@@ -150,14 +176,21 @@ k_gather_elem(GatherArgs a, const GatherArgs *__restrict__ group) {
     }
 }
 
-template <int DTYPE>
-cudaError_t launch_vec(const GatherArgs &a, const GatherArgs *group, uint32_t row_bytes, dim3 grid, cudaStream_t st) {
+template <int DTYPE, bool SHARDED>
+cudaError_t launch_vec_s(const GatherArgs &a, const GatherArgs *group, uint32_t row_bytes, dim3 grid, cudaStream_t st) {
     const uint32_t vecs = row_bytes >> 4;
-    if (vecs <= 4) k_gather_vec<DTYPE, 4><<<grid, kThreads, 0, st>>>(a, group);
-    else if (vecs <= 8) k_gather_vec<DTYPE, 8><<<grid, kThreads, 0, st>>>(a, group);
-    else if (vecs <= 16) k_gather_vec<DTYPE, 16><<<grid, kThreads, 0, st>>>(a, group);
-    else k_gather_vec<DTYPE, 32><<<grid, kThreads, 0, st>>>(a, group);
+    if (vecs <= 4) k_gather_vec<DTYPE, 4, SHARDED><<<grid, kThreads, 0, st>>>(a, group);
+    else if (vecs <= 8) k_gather_vec<DTYPE, 8, SHARDED><<<grid, kThreads, 0, st>>>(a, group);
+    else if (vecs <= 16) k_gather_vec<DTYPE, 16, SHARDED><<<grid, kThreads, 0, st>>>(a, group);
+    else k_gather_vec<DTYPE, 32, SHARDED><<<grid, kThreads, 0, st>>>(a, group);
     return cudaGetLastError();
+}
+
+template <int DTYPE>
+cudaError_t launch_vec(const GatherArgs &a, const GatherArgs *group, uint32_t row_bytes, dim3 grid, bool sharded,
+                       cudaStream_t st) {
+    return sharded ? launch_vec_s<DTYPE, true>(a, group, row_bytes, grid, st)
+                   : launch_vec_s<DTYPE, false>(a, group, row_bytes, grid, st);
 }
 
 // f32 -> stored dtype, used to build a store from f32 rows on the device.
@@ -221,9 +254,9 @@ cudaError_t launch_gather(const GatherArgs &a, int dtype, cudaStream_t st) {
     if (vec_ok) {
         const dim3 grid(gather_grid_blocks(a.n, a.row_bytes), 1);
         switch (dtype) {
-            case AG_F32: return launch_vec<AG_F32>(a, nullptr, a.row_bytes, grid, st);
-            case AG_F16: return launch_vec<AG_F16>(a, nullptr, a.row_bytes, grid, st);
-            default: return launch_vec<AG_BF16>(a, nullptr, a.row_bytes, grid, st);
+            case AG_F32: return launch_vec<AG_F32>(a, nullptr, a.row_bytes, grid, a.shards != nullptr, st);
+            case AG_F16: return launch_vec<AG_F16>(a, nullptr, a.row_bytes, grid, a.shards != nullptr, st);
+            default: return launch_vec<AG_BF16>(a, nullptr, a.row_bytes, grid, a.shards != nullptr, st);
         }
     }
     const uint64_t total = a.n * a.dim;
@@ -242,7 +275,8 @@ cudaError_t launch_gather(const GatherArgs &a, int dtype, cudaStream_t st) {
 // (256- / 512-byte aligned) and the payload base is checked by the caller's
 // store, so only the row size decides between the vector and the element path.
 cudaError_t launch_gather_group(const GatherArgs *group_dev, uint32_t n_batches, uint32_t row_bytes,
-                                uint32_t dim, uint64_t n_bound, bool aligned, int dtype, cudaStream_t st) {
+                                uint32_t dim, uint64_t n_bound, bool aligned, int dtype, bool sharded,
+                                cudaStream_t st) {
     if (n_batches == 0 || n_bound == 0) return cudaSuccess;
     GatherArgs none{};
     if (row_bytes % 16 == 0 && aligned) {
@@ -253,9 +287,9 @@ cudaError_t launch_gather_group(const GatherArgs *group_dev, uint32_t n_batches,
         per = std::min(per, cap);
         const dim3 grid(per, n_batches);
         switch (dtype) {
-            case AG_F32: return launch_vec<AG_F32>(none, group_dev, row_bytes, grid, st);
-            case AG_F16: return launch_vec<AG_F16>(none, group_dev, row_bytes, grid, st);
-            default: return launch_vec<AG_BF16>(none, group_dev, row_bytes, grid, st);
+            case AG_F32: return launch_vec<AG_F32>(none, group_dev, row_bytes, grid, sharded, st);
+            case AG_F16: return launch_vec<AG_F16>(none, group_dev, row_bytes, grid, sharded, st);
+            default: return launch_vec<AG_BF16>(none, group_dev, row_bytes, grid, sharded, st);
         }
     }
     const uint64_t total = n_bound * dim;

@@ -26,6 +26,19 @@ struct ag_features {
     uint8_t *payload = nullptr;  // device, rows * dim * elem_size
     uint32_t *err = nullptr;     // device, sticky error bits
     bool owns_payload = true;
+    // A sharded view (ag_features_open_sharded / ag_features_view_sharded): rows
+    // [r * shard_rows, (r + 1) * shard_rows) live in shard r's memory, this GPU's
+    // own shard or a peer's mapped into this process.
+    struct ag_shard_table *shards = nullptr;  // device copy of the table, or null
+    uint32_t n_shards = 0;
+    void *ipc_opened[8] = {nullptr};          // peer mappings this view opened (closed on free)
+};
+
+// Device-visible table of a sharded feature store.
+struct ag_shard_table {
+    const uint8_t *base[8];
+    uint64_t shard_rows;
+    uint32_t n_shards;
 };
 
 namespace ag {
@@ -42,11 +55,20 @@ struct GatherArgs {
     const uint32_t *n_dev;
     float *out;
     uint32_t *err;
+    const ag_shard_table *shards;  // non-null: rows are looked up through the shard table
 };
+
+// The source half of a gather's arguments, from a feature store handle.
+inline void set_gather_source(GatherArgs &a, const ag_features *f) {
+    a.payload = f->payload; a.row_begin = f->row_begin; a.rows = f->rows;
+    a.row_bytes = (uint32_t)(f->dim * elem_size(f->dtype)); a.dim = (uint32_t)f->dim;
+    a.err = f->err; a.shards = f->shards;
+}
 
 cudaError_t launch_gather(const GatherArgs &a, int dtype, cudaStream_t st);
 cudaError_t launch_gather_group(const GatherArgs *group_dev, uint32_t n_batches, uint32_t row_bytes,
-                                uint32_t dim, uint64_t n_bound, bool aligned, int dtype, cudaStream_t st);
+                                uint32_t dim, uint64_t n_bound, bool aligned, int dtype, bool sharded,
+                                cudaStream_t st);
 cudaError_t launch_encode(const float *src, void *dst, uint64_t count, int dtype, cudaStream_t st);
 int gather_grid_blocks(uint64_t n, uint32_t row_bytes);
 

@@ -824,13 +824,12 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
         if (want_x) {
             GatherArgs ga{};
             if (feats && B.x) {
-                ga.payload = feats->payload; ga.row_begin = feats->row_begin; ga.rows = feats->rows;
-                ga.row_bytes = (uint32_t)(feats->dim * elem_size(feats->dtype)); ga.dim = (uint32_t)feats->dim;
+                set_gather_source(ga, feats);
                 ga.ids = B.nodes; ga.ids64 = 0;
                 ga.n = std::min<uint64_t>(bn, B.cap_nodes);
                 // rows to gather = nodes registered by the last stage (read on the device)
                 ga.n_dev = &s->state[b].stage[H + 1].n_nodes;
-                ga.out = B.x; ga.err = feats->err;
+                ga.out = B.x;
             }
             s->gather_host[b] = ga;
         }
@@ -887,7 +886,7 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
         if (s->profile) AG_CUDA(cudaEventRecord(s->ev[2], s->gstream));
         const uint64_t rows = s->est_nodes ? std::min(b_nodes, s->est_nodes) : b_nodes;
         AG_CUDA(launch_gather_group(s->gather_dev, n_batches, (uint32_t)(feats->dim * elem_size(feats->dtype)),
-                                    (uint32_t)feats->dim, rows, aligned, feats->dtype, s->gstream));
+                                    (uint32_t)feats->dim, rows, aligned, feats->dtype, feats->shards != nullptr, s->gstream));
         if (s->profile) AG_CUDA(cudaEventRecord(s->ev[3], s->gstream));
         AG_CUDA(cudaEventRecord(s->done, s->gstream));
         AG_CUDA(cudaStreamWaitEvent(st, s->done, 0));  // the caller's stream stays ordered behind the gather

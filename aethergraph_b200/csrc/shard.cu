@@ -1,0 +1,128 @@
+// Feature stores sharded by vertex range over the GPUs of one node.
+//
+// The reference scales past one machine's memory by partitioning the feature
+// matrix by contiguous vertex ranges and fetching remote rows over the fabric
+// (python/aethergraph/ray/datasource.py:6-10 keeps the topology replicated and
+// the features partitioned; crates/aether-stream's RDMA gather is its transport).
+// On one NVSwitch node the transport is a plain load: every GPU maps its peers'
+// shards (CUDA IPC across processes, peer access inside one process) and the
+// gather kernel reads row v straight out of HBM of GPU v / shard_rows.  The
+// stored (bf16 / f16) row crosses NVLink; the upcast happens at the reader.
+// There is no staging buffer, no collective, and nothing here uses TMA.
+#include <string.h>
+
+#include <algorithm>
+
+#include "common.cuh"
+#include "internal.h"
+
+using namespace ag;
+
+namespace {
+
+int32_t make_view(const ag_features *local, uint32_t world, const uint8_t *const *bases, void *const *opened,
+                  ag_features **out) {
+    const uint64_t n = local->num_nodes;
+    const uint64_t shard_rows = (n + world - 1) / world;
+    ag_features *v = new ag_features();
+    v->device = local->device;
+    v->num_nodes = n; v->row_begin = 0; v->rows = n; v->dim = local->dim; v->dtype = local->dtype;
+    v->payload = local->payload;  // borrowed: the view must not outlive the local shard
+    for (uint32_t r = 0; r < world && !v->payload; ++r) v->payload = const_cast<uint8_t *>(bases[r]);
+    v->owns_payload = false;
+    v->n_shards = world;
+    for (uint32_t r = 0; r < world && opened; ++r) v->ipc_opened[r] = opened[r];
+    ag_shard_table t{};
+    for (uint32_t r = 0; r < world; ++r) t.base[r] = bases[r];
+    t.shard_rows = std::max<uint64_t>(shard_rows, 1);
+    t.n_shards = world;
+    if (cudaMalloc(&v->err, 4) != cudaSuccess || cudaMemset(v->err, 0, 4) != cudaSuccess ||
+        cudaMalloc(&v->shards, sizeof(ag_shard_table)) != cudaSuccess ||
+        cudaMemcpy(v->shards, &t, sizeof(t), cudaMemcpyHostToDevice) != cudaSuccess) {
+        const int32_t st = fail(AG_ERR_CUDA, "sharded view allocation failed: %s", cudaGetErrorString(cudaGetLastError()));
+        ag_features_free(v);
+        return st;
+    }
+    *out = v;
+    return AG_OK;
+}
+
+int32_t check_local(const ag_features *local, uint32_t world, uint32_t rank, const char *who) {
+    if (world == 0 || world > 8 || rank >= world) return fail(AG_ERR_VALUE, "%s: bad rank %u of %u (at most 8 shards)", who, rank, world);
+    if (local->shards) return fail(AG_ERR_VALUE, "%s: the local store is already a sharded view", who);
+    const uint64_t n = local->num_nodes, shard_rows = (n + world - 1) / world;
+    const uint64_t begin = std::min<uint64_t>((uint64_t)rank * shard_rows, n), end = std::min<uint64_t>(begin + shard_rows, n);
+    if (local->row_begin != begin || local->rows != end - begin)
+        return fail(AG_ERR_VALUE, "%s: rank %u of %u must hold rows [%llu, %llu) of %llu, the store holds [%llu, %llu)", who,
+                    rank, world, (unsigned long long)begin, (unsigned long long)end, (unsigned long long)n,
+                    (unsigned long long)local->row_begin, (unsigned long long)(local->row_begin + local->rows));
+    return AG_OK;
+}
+
+}  // namespace
+
+extern "C" int32_t ag_features_ipc_export(const ag_features *f, void *handle_out) {
+    if (!f || !handle_out) return fail(AG_ERR_VALUE, "ag_features_ipc_export: null argument");
+    static_assert(sizeof(cudaIpcMemHandle_t) == AG_IPC_HANDLE_BYTES, "IPC handle size");
+    DeviceGuard guard(f->device);
+    if (!guard.ok) return AG_ERR_CUDA;
+    memset(handle_out, 0, AG_IPC_HANDLE_BYTES);
+    if (!f->payload || f->rows == 0) return AG_OK;  // an empty shard has nothing to map
+    cudaIpcMemHandle_t h;
+    AG_CUDA(cudaIpcGetMemHandle(&h, f->payload));
+    memcpy(handle_out, &h, sizeof(h));
+    return AG_OK;
+}
+
+extern "C" int32_t ag_features_open_sharded(const ag_features *local, uint32_t world, uint32_t rank, const void *handles,
+                                            ag_features **out) {
+    if (!local || !handles || !out) return fail(AG_ERR_VALUE, "ag_features_open_sharded: null argument");
+    AG_TRY(check_local(local, world, rank, "ag_features_open_sharded"));
+    DeviceGuard guard(local->device);
+    if (!guard.ok) return AG_ERR_CUDA;
+    const uint8_t *bases[8] = {nullptr};
+    void *opened[8] = {nullptr};
+    const uint64_t n = local->num_nodes, shard_rows = (n + world - 1) / world;
+    for (uint32_t r = 0; r < world; ++r) {
+        if (r == rank) { bases[r] = local->payload; continue; }
+        if ((uint64_t)r * shard_rows >= n) continue;  // empty tail shard
+        cudaIpcMemHandle_t h;
+        memcpy(&h, (const uint8_t *)handles + (size_t)r * AG_IPC_HANDLE_BYTES, sizeof(h));
+        void *p = nullptr;
+        const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) {
+            for (void *q : opened) if (q) cudaIpcCloseMemHandle(q);
+            return fail(AG_ERR_CUDA, "cannot map the feature shard of rank %u: %s", r, cudaGetErrorString(e));
+        }
+        opened[r] = p; bases[r] = (const uint8_t *)p;
+    }
+    const int32_t st = make_view(local, world, bases, opened, out);
+    if (st != AG_OK) for (void *q : opened) if (q) cudaIpcCloseMemHandle(q);
+    return st;
+}
+
+extern "C" int32_t ag_features_view_sharded(const ag_features *const *shards, uint32_t world, uint32_t rank,
+                                            ag_features **out) {
+    if (!shards || !out || world == 0 || world > 8 || rank >= world) return fail(AG_ERR_VALUE, "ag_features_view_sharded: bad argument");
+    for (uint32_t r = 0; r < world; ++r) {
+        if (!shards[r]) return fail(AG_ERR_VALUE, "ag_features_view_sharded: shard %u is null", r);
+        if (shards[r]->num_nodes != shards[0]->num_nodes || shards[r]->dim != shards[0]->dim || shards[r]->dtype != shards[0]->dtype)
+            return fail(AG_ERR_VALUE, "ag_features_view_sharded: shard %u disagrees on shape or dtype", r);
+        AG_TRY(check_local(shards[r], world, r, "ag_features_view_sharded"));
+    }
+    const ag_features *local = shards[rank];
+    DeviceGuard guard(local->device);
+    if (!guard.ok) return AG_ERR_CUDA;
+    const uint8_t *bases[8] = {nullptr};
+    for (uint32_t r = 0; r < world; ++r) {
+        bases[r] = shards[r]->payload;
+        if (shards[r]->device == local->device || shards[r]->rows == 0) continue;
+        int can = 0;
+        AG_CUDA(cudaDeviceCanAccessPeer(&can, local->device, shards[r]->device));
+        if (!can) return fail(AG_ERR_CUDA, "GPU %d cannot access GPU %d's memory", local->device, shards[r]->device);
+        const cudaError_t e = cudaDeviceEnablePeerAccess(shards[r]->device, 0);
+        if (e == cudaErrorPeerAccessAlreadyEnabled) cudaGetLastError();
+        else if (e != cudaSuccess) return fail(AG_ERR_CUDA, "enabling peer access to GPU %d failed: %s", shards[r]->device, cudaGetErrorString(e));
+    }
+    return make_view(local, world, bases, nullptr, out);
+}

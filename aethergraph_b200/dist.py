@@ -48,3 +48,22 @@ def sum_over_ranks(value: float, device=None) -> float:
     t = torch.tensor([value], dtype=torch.float64, device=device)
     dist.all_reduce(t, op=dist.ReduceOp.SUM)
     return float(t.item())
+
+
+def open_sharded_features(local):
+    """Every rank passes the FeatureStore holding ITS vertex range
+    (`shard_range(rank, num_nodes, world)`); returns a store over all rows whose
+    remote rows are read from the owning rank's GPU memory over NVLink.  The only
+    communication is the one-off exchange of 64-byte IPC handles."""
+    import torch.distributed as dist
+
+    from .features import FeatureStore
+
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        return FeatureStore.open_sharded(local, [local.ipc_handle()], 0)
+    world, rank = dist.get_world_size(), dist.get_rank()
+    handles: list = [None] * world
+    dist.all_gather_object(handles, local.ipc_handle())
+    view = FeatureStore.open_sharded(local, handles, rank)
+    dist.barrier()  # every rank has mapped its peers before anyone may free a shard
+    return view

@@ -111,6 +111,37 @@ class FeatureStore:
                                                       FeatureStore._dev(device), C.byref(out)))
         return FeatureStore(out.value)
 
+    # -- vertex-range shards over the GPUs of one node -----------------------
+    def ipc_handle(self) -> bytes:
+        """64-byte CUDA IPC handle of this shard's rows, for the other ranks of the node."""
+        buf = C.create_string_buffer(_lib.AG_IPC_HANDLE_BYTES)
+        _lib.check(_lib.lib().ag_features_ipc_export(self._h, buf))
+        return buf.raw
+
+    @staticmethod
+    def open_sharded(local: "FeatureStore", handles: list[bytes], rank: int) -> "FeatureStore":
+        """A store over ALL rows whose shard `r` lives in rank r's GPU memory: `local`
+        is this rank's shard (rows `dist.shard_range(rank, n, world)`), `handles` the
+        `ipc_handle()` of every rank in rank order.  Remote rows are read over NVLink
+        by the gather kernel itself."""
+        world = len(handles)
+        blob = b"".join(h if len(h) == _lib.AG_IPC_HANDLE_BYTES else b"\0" * _lib.AG_IPC_HANDLE_BYTES for h in handles)
+        out = C.c_void_p()
+        _lib.check(_lib.lib().ag_features_open_sharded(local._h, world, rank, blob, C.byref(out)))
+        view = FeatureStore(out.value)
+        view._keep = local  # the view borrows the local shard's memory
+        return view
+
+    @staticmethod
+    def view_sharded(shards: list["FeatureStore"], rank: int) -> "FeatureStore":
+        """The same view inside ONE process that holds every shard (one per GPU, peer access)."""
+        arr = (C.c_void_p * len(shards))(*[s._h for s in shards])
+        out = C.c_void_p()
+        _lib.check(_lib.lib().ag_features_view_sharded(arr, len(shards), rank, C.byref(out)))
+        view = FeatureStore(out.value)
+        view._keep = list(shards)
+        return view
+
     @property
     def num_nodes(self) -> int:
         return self._n

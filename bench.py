@@ -240,7 +240,15 @@ def run_device(args, w):
     # ---- inputs, resident in HBM (CSR and features replicated per GPU) ------
     t_setup = time.time()
     g = synth.rmat_graph(w["nodes"], w["edges"], GRAPH_SEED, weight_sigma=1.0 if w["weighted"] else 0.0)
-    feats = synth.features(w["nodes"], w["dim"], w["dtype"], FEATURE_SEED)
+    if args.features == "sharded" and world > 1:
+        # vertex-range shards: rank r holds rows shard_range(r); remote rows cross NVLink inside the gather kernel
+        from aethergraph_b200 import dist as agd
+
+        local_shard = synth.features(w["nodes"], w["dim"], w["dtype"], FEATURE_SEED,
+                                     row_range=agd.shard_range(rank, w["nodes"], world))
+        feats = agd.open_sharded_features(local_shard)
+    else:
+        feats = synth.features(w["nodes"], w["dim"], w["dtype"], FEATURE_SEED)
     torch.cuda.synchronize()
     t_setup = time.time() - t_setup
     cfg = ag.SamplingConfig(num_neighbors=w["fanout"], seed=SAMPLER_SEED, weighted=w["weighted"])
@@ -436,7 +444,9 @@ def run_device(args, w):
             "data": "synthetic (seeded R-MAT graph + ~N(0,1) features generated in HBM)",
             "config": {"workload": w["label"], "batches_per_step": per_step, "rng_mode": "wyrand_exact",
                        "sampler_threads": threads, "group": group, "prefetch_depth": depth, "parallelism": f"dp{world}",
-                       "features": "replicated", "inputs_larger_than_l2": True},
+                       "features": ("sharded by vertex range, remote rows over NVLink (%d/%d of the reads)"
+                                    % (world - 1, world)) if (args.features == "sharded" and world > 1)
+                       else "replicated", "inputs_larger_than_l2": True},
             "gather_gbs": gather_gbs, "edges_per_step": tot_edges / max(args.steps, 1),
             "rows_per_step": tot_nodes / max(args.steps, 1), "setup_s": round(t_setup, 1),
             "clocks": clk, "roofline": roofline, "cpu_baseline": cpu, "parity_full_scale": parity,
@@ -456,6 +466,9 @@ def run_device(args, w):
         }
         print(json.dumps(line), flush=True)
     if world > 1:
+        barrier()  # no rank frees its feature shard while a peer may still be reading it
+        del feats
+        barrier()
         dist.destroy_process_group()
 
 
@@ -522,6 +535,8 @@ def main():
     ap.add_argument("--depth", type=int, default=8)
     ap.add_argument("--group", type=int, default=int(os.environ.get("AG_BENCH_GROUP", "16")),
                     help="batches a worker runs as one launch chain")
+    ap.add_argument("--features", default="replicated", choices=["replicated", "sharded"],
+                    help="with more than one GPU: every GPU holds all feature rows, or a vertex-range shard each")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--only-value", action="store_true",
                     help="run the resident (C ABI) leg only: no e2e, no CPU baseline (profiling runs)")

@@ -133,6 +133,26 @@ int32_t ag_features_info(const ag_features *f, uint64_t *num_nodes, uint64_t *di
 /* The vertex range [row_begin, row_begin + rows) this handle holds. */
 int32_t ag_features_shard(const ag_features *f, uint64_t *row_begin, uint64_t *rows);
 int32_t ag_features_device_ptr(const ag_features *f, const void **payload_dev);
+
+/* Vertex-range shards over the GPUs of one node (the partitioned-features
+ * layout of python/aethergraph/ray/datasource.py:6-10; the reference fetches
+ * remote rows through its RDMA gather, here a remote row is a plain load over
+ * NVLink from the owner's HBM, upcast at the reader).  Shard r of `world` holds
+ * rows [r * S, min((r + 1) * S, num_nodes)) with S = ceil(num_nodes / world)
+ * (load it with ag_features_load_range or build it with ag_synth_features).
+ * One process per GPU: every rank exports its shard's 64-byte IPC handle,
+ * exchanges the handles by any means (the Python layer uses
+ * torch.distributed.all_gather_object) and opens the view with all of them
+ * (`handles` = world x 64 bytes, own entry ignored).  One process driving
+ * several GPUs: ag_features_view_sharded over the shard handles themselves.
+ * The view gathers any row in [0, num_nodes); it borrows the local shard,
+ * which must outlive it, and is freed with ag_features_free. */
+#define AG_IPC_HANDLE_BYTES 64
+int32_t ag_features_ipc_export(const ag_features *f, void *handle_out);
+int32_t ag_features_open_sharded(const ag_features *local, uint32_t world, uint32_t rank,
+                                 const void *handles, ag_features **out);
+int32_t ag_features_view_sharded(const ag_features *const *shards, uint32_t world, uint32_t rank,
+                                 ag_features **out);
 /* Copies the stored (encoded) rows held by this handle back to host memory. */
 int32_t ag_features_copy_to_host(const ag_features *f, void *payload);
 

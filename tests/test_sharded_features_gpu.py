@@ -1,0 +1,140 @@
+"""Feature stores sharded by vertex range: the gather must return exactly the rows
+of the unsharded store (bit-exact), whichever GPU's memory a row lives in.
+
+- one GPU: the shards all live on device 0 and are joined with view_sharded —
+  covers the kernel's shard lookup, every dtype, the loader path and the errors;
+- two or more GPUs (skipped on a one-GPU box): one process per GPU, shards
+  exchanged as CUDA IPC handles, remote rows read over NVLink by the gather kernel.
+"""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from helpers import rmat_csr
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.mark.parametrize("dtype,dim", [("bf16", 256), ("f16", 64), ("f32", 24), ("bf16", 5)])
+@pytest.mark.parametrize("world", [2, 3])
+def test_sharded_view_on_one_gpu_matches_the_unsharded_store(dtype, dim, world, tmp_path):
+    import torch
+
+    import aethergraph_b200 as ag
+    from aethergraph_b200 import dist
+    from oracle import ago
+
+    n = 5003
+    feats = np.random.default_rng(dim).standard_normal((n, dim)).astype(np.float32)
+    path = tmp_path / "f.bin"
+    ag.save_features(str(path), feats, dtype=dtype)
+    shards = [ag.FeatureStore.load(str(path), row_range=dist.shard_range(r, n, world)) for r in range(world)]
+    payload = ago.encode(feats, dtype)
+    ids = np.concatenate([np.random.default_rng(1).integers(0, n, 4000), [0, n - 1], np.arange(n - 40, n)])
+    want = ago.gather(payload, n, dim, dtype, ids.astype(np.uint32))
+    for rank in range(world):
+        view = ag.FeatureStore.view_sharded(shards, rank)
+        assert view.num_nodes == n and view.feature_dim == dim
+        got = view.gather(torch.from_numpy(ids).cuda())
+        assert np.array_equal(got.cpu().numpy().view(np.uint32), want.view(np.uint32))
+        assert np.array_equal(view.get_batch(ids[:100]).view(np.uint32), want[:100].view(np.uint32))
+        with pytest.raises(ValueError, match="out of bounds"):
+            view.get_batch([n])
+    with pytest.raises(ValueError, match="must hold rows"):
+        ag.FeatureStore.view_sharded(shards[::-1], 0)
+
+
+def test_loader_with_sharded_features_matches_the_oracle():
+    import aethergraph_b200 as ag
+    from aethergraph_b200 import dist, synth
+    from oracle import ago
+
+    n, off, dst, _ = rmat_csr(12, 12, seed=3)
+    g = ag.Graph.from_csr(off, dst)
+    dim, world = 128, 4
+    shards = [synth.features(n, dim, "bf16", 9, row_range=dist.shard_range(r, n, world)) for r in range(world)]
+    view = ag.FeatureStore.view_sharded(shards, 1)
+    payload = ago.synth_features(n, dim, "bf16", 9)
+    cfg = ag.SamplingConfig(num_neighbors=[8, 4], seed=5)
+    s = ago.Sampler(off, dst, [8, 4], seed=5)
+    rng = np.random.default_rng(0)
+    batches = [rng.integers(0, n, 200).astype(np.uint32) for _ in range(12)]
+    with ag.NeighborLoader(g, cfg, prefetch_depth=4, sampler_threads=2, features=view) as ld:
+        for i, b in enumerate(batches):
+            ld.submit(i, b)
+        for i, b in enumerate(batches):
+            idx, sg, x = ld.next_batch()
+            s.reseed(ago.batch_seed(5, i))
+            want = s.sample(b)
+            assert idx == i and np.array_equal(sg.raw_u32()["nodes"], want["nodes"])
+            xw = ago.gather(payload, n, dim, "bf16", want["nodes"])
+            assert np.array_equal(x.cpu().numpy().view(np.uint32), xw.view(np.uint32))
+
+
+_WORKER = r"""
+import os, sys
+import numpy as np
+import torch
+import torch.distributed as dist
+sys.path.insert(0, os.environ["AG_ROOT"]); sys.path.insert(0, os.path.join(os.environ["AG_ROOT"], "tests"))
+import aethergraph_b200 as ag
+from aethergraph_b200 import synth
+from aethergraph_b200 import dist as agd
+from oracle import ago
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("gloo")
+n, dim, dtype = 200_003, 256, "bf16"
+local = synth.features(n, dim, dtype, 21, row_range=agd.shard_range(rank, n, world))
+view = agd.open_sharded_features(local)
+payload = ago.synth_features(n, dim, dtype, 21)
+ids = np.random.default_rng(100 + rank).integers(0, n, 50_000)
+got = view.gather(torch.from_numpy(ids).cuda())
+want = ago.gather(payload, n, dim, dtype, ids.astype(np.uint32))
+ok = np.array_equal(got.cpu().numpy().view(np.uint32), want.view(np.uint32))
+remote = float(np.mean(np.array([agd.owner_of_row(int(i), n, world) for i in ids[:2000]]) != rank))
+# the loader path over the sharded view
+from helpers import rmat_csr
+nn, off, dst, _ = rmat_csr(14, 8, seed=2)
+g = ag.Graph.from_csr(off, dst)
+loc2 = synth.features(nn, 64, "f16", 4, row_range=agd.shard_range(rank, nn, world))
+v2 = agd.open_sharded_features(loc2)
+p2 = ago.synth_features(nn, 64, "f16", 4)
+s = ago.Sampler(off, dst, [6, 3], seed=8)
+with ag.NeighborLoader(g, ag.SamplingConfig(num_neighbors=[6, 3], seed=8), 2, 2, features=v2) as ld:
+    seeds = np.random.default_rng(rank).integers(0, nn, 300).astype(np.uint32)
+    ld.submit(0, seeds)
+    _, sg, x = ld.next_batch()
+    s.reseed(ago.batch_seed(8, 0))
+    w = s.sample(seeds)
+    ok = ok and np.array_equal(sg.raw_u32()["nodes"], w["nodes"])
+    ok = ok and np.array_equal(x.cpu().numpy().view(np.uint32), ago.gather(p2, nn, 64, "f16", w["nodes"]).view(np.uint32))
+torch.cuda.synchronize()
+dist.barrier()   # nobody frees a shard while a peer may still read it
+print(f"RANK{rank} ok={ok} remote_share={remote:.2f}", flush=True)
+del view, v2
+dist.barrier()
+dist.destroy_process_group()
+sys.exit(0 if ok else 1)
+"""
+
+
+def test_ipc_shards_across_processes_and_gpus(tmp_path):
+    import torch
+
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    script = tmp_path / "worker.py"
+    script.write_text(_WORKER)
+    env = dict(os.environ, AG_ROOT=ROOT, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+                        "--master-addr", "127.0.0.1", "--master-port", "29533", str(script)],
+                       env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    for k in range(world):
+        assert f"RANK{k} ok=True" in r.stdout
