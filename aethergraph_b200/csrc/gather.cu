@@ -72,6 +72,22 @@ __device__ __forceinline__ uint64_t load_id(const void *ids, int ids64, uint64_t
     return ids64 ? (uint64_t)((const int64_t *)ids)[i] : (uint64_t)((const uint32_t *)ids)[i];
 }
 
+// Feature rows are read once per batch and there are tens of gigabytes of them:
+// mark their lines evict-first in L2 as well, so the stream of rows does not push
+// out what the sampling kernels of the neighbouring chains keep there (dedup
+// tables, scan descriptors, CSR offsets).
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ uint4 ld_stream_v4_l2ef(const void *p, uint64_t pol) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p), "l"(pol));
+    return v;
+}
+
 // Plain (coherent) 16-byte load that does not allocate in L1: rows of a peer
 // GPU's shard arrive over NVLink through this.
 __device__ __forceinline__ uint4 ld_peer_v4(const void *p) {
@@ -108,6 +124,7 @@ k_gather_vec(GatherArgs a, const GatherArgs *__restrict__ group) {
     // a concurrent (higher-priority) kernel get SM slots as they retire.
     constexpr uint64_t kChunk = (uint64_t)kRowsPerBlock * kInFlight;
     const uint64_t stride = kRowsPerBlock;
+    const uint64_t pol = l2_evict_first_policy();
 
     for (uint64_t base = (uint64_t)blockIdx.x * kChunk + sub; base < n; base += (uint64_t)gridDim.x * kChunk) {
         for (uint32_t v0 = 0; v0 < vecs; v0 += LPR) {
@@ -125,7 +142,7 @@ k_gather_vec(GatherArgs a, const GatherArgs *__restrict__ group) {
                     ok[u] = true;
                     if (id >= a.row_begin && local < a.rows) {
                         if (SHARDED) val[u] = ld_peer_v4(shard_row(a.shards, id, a.row_bytes) + ((uint64_t)v << 4));
-                        else val[u] = ld_stream_v4(a.payload + local * a.row_bytes + ((uint64_t)v << 4));
+                        else val[u] = ld_stream_v4_l2ef(a.payload + local * a.row_bytes + ((uint64_t)v << 4), pol);
                     } else if (lane == 0) {
                         atomicOr(a.err, kErrBadId);
                     }

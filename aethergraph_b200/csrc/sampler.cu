@@ -308,8 +308,10 @@ __device__ __forceinline__ void pick_weighted(const SampleParams &p, uint32_t ho
 // One stage: assign local ids to the first sightings among the stage's items
 // and (has_next) queue the new vertices, with their row bounds, edge slots and
 // draw offsets, as the frontier the pick kernel of hop `stage` expands.
-__global__ void __launch_bounds__(kTile)
-k_assign(const SampleParams *__restrict__ pa, uint32_t stage, uint32_t k, int has_next) {
+template <bool HAS_NEXT>
+__global__ void __launch_bounds__(kTile, HAS_NEXT ? 2 : 3)
+k_assign(const SampleParams *__restrict__ pa, uint32_t stage, uint32_t k) {
+    constexpr bool has_next = HAS_NEXT;  // the last stage queues no frontier and needs fewer registers
     __shared__ uint32_t s_tile;
     __shared__ ScanVal s_warp[kTile / 32];
     __shared__ ScanVal s_prefix;
@@ -858,7 +860,8 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
         const bool has_next = stage < H;
         const uint32_t k = has_next ? s->cfg.fanout[stage] : 0;
         const uint64_t expect = (stage && s->est_items[stage]) ? std::min(items, s->est_items[stage]) : items;
-        k_assign<<<dim3(tiles_for(expect), n_batches), kTile, 0, st>>>(pa, stage, k, has_next ? 1 : 0);
+        if (has_next) k_assign<true><<<dim3(tiles_for(expect), n_batches), kTile, 0, st>>>(pa, stage, k);
+        else k_assign<false><<<dim3(tiles_for(expect), n_batches), kTile, 0, st>>>(pa, stage, k);
         if (has_next && k) {
             // the new vertices of this stage are at most its items
             launch_pick(s->mode, k, std::min<uint64_t>(expect, g->num_nodes), n_batches, st, pa, stage);
@@ -870,7 +873,8 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
         for (uint32_t h = 1; h <= H; ++h) est_edges += s->est_items[h];
         const uint64_t bound = std::max<uint64_t>(std::max(b_edges, b_nodes), std::max<uint64_t>(nmax, 1));
         const uint64_t work = est_edges ? std::min(bound, std::max<uint64_t>(est_edges, nmax)) : bound;
-        const uint32_t fx = (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>((work + 255) / 256, std::max<uint64_t>((uint64_t)kSMs * 8 / n_batches, 1)));
+        // one edge per thread where the GPU can hold them: every table lookup in flight at once
+        const uint32_t fx = (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>((work + 255) / 256, std::max<uint64_t>((uint64_t)kSMs * 16 / n_batches, 1)));
         k_finalize<<<dim3(fx, n_batches), 256, 0, st>>>(pa);
     }
     AG_CUDA(cudaGetLastError());

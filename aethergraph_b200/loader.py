@@ -67,12 +67,20 @@ class _Lease:
         if ld is None or not ld._h:
             return
         try:
-            import torch
-
-            st = torch.cuda.current_stream(ld._dev).cuda_stream
-            _lib.lib().ag_loader_release_batch(ld._h, C.byref(self.batch), st)
+            ld._release(ld._h, C.byref(self.batch), _raw_current_stream(ld._dev_index))
         except Exception:
             pass
+
+
+def _raw_current_stream(device_index: int) -> int:
+    """cudaStream_t of torch's current stream on the device (the cheap accessor; the
+    Stream object `torch.cuda.current_stream` builds costs several microseconds)."""
+    import torch
+
+    try:
+        return torch._C._cuda_getCurrentRawStream(device_index)
+    except AttributeError:
+        return torch.cuda.current_stream(device_index).cuda_stream
 
 
 class NeighborLoader:
@@ -96,6 +104,8 @@ class NeighborLoader:
                                                C.byref(cfg), int(self._seeded), prefetch_depth, sampler_threads,
                                                max(1, int(group)), int(profiling), C.byref(self._h)))
         self._dev = torch.device("cuda", graph.device)
+        self._dev_index = int(graph.device)
+        self._release = _lib.lib().ag_loader_release_batch
         self._dim = features.feature_dim if features is not None else None
         self._lock = threading.Lock()
         self._next_seq = 0

@@ -280,10 +280,17 @@ def run_device(args, w):
         return float(t.item())
 
     # ---- value: C ABI, inputs resident, recycled output buffers ------------
-    threads, depth = args.threads, args.depth
+    threads = args.threads
+    # Batches per launch chain: large chains amortise the per-kernel latency of the
+    # sampling stages, but every worker should still see several chains in the timed region.
+    if args.group:
+        group = args.group
+    else:
+        per_worker = args.steps * per_step // (3 * threads)
+        group = 32 if per_worker >= 32 else 16 if per_worker >= 16 else 8
+    depth = args.depth if args.depth else max(8, group // 2)
     h = C.c_void_p()
     ccfg = cfg._to_c(SAMPLER_SEED, bs)
-    group = args.group
     _lib.check(L.ag_loader_create(g._h, feats._h, C.byref(ccfg), 1, depth, threads, group, 1, C.byref(h)))
     mn, me = C.c_uint64(), C.c_uint64()
     _lib.check(L.ag_loader_bounds(h, bs, C.byref(mn), C.byref(me)))
@@ -532,9 +539,9 @@ def main():
     ap.add_argument("--workload", default=os.environ.get("AG_BENCH_WORKLOAD", "c2"), choices=sorted(WORKLOADS))
     ap.add_argument("--threads", type=int, default=int(os.environ.get("AG_BENCH_THREADS", "3")),
                     help="loader worker threads, each with its own CUDA stream")
-    ap.add_argument("--depth", type=int, default=8)
-    ap.add_argument("--group", type=int, default=int(os.environ.get("AG_BENCH_GROUP", "16")),
-                    help="batches a worker runs as one launch chain")
+    ap.add_argument("--depth", type=int, default=0, help="prefetch depth (0: max(8, group / 2))")
+    ap.add_argument("--group", type=int, default=int(os.environ.get("AG_BENCH_GROUP", "0")),
+                    help="batches a worker runs as one launch chain (0: chosen from --steps)")
     ap.add_argument("--features", default="replicated", choices=["replicated", "sharded"],
                     help="with more than one GPU: every GPU holds all feature rows, or a vertex-range shard each")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
