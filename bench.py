@@ -527,7 +527,56 @@ def cpu_baseline(g, feats, w, cfg):
             ok = ok and np.array_equal(got[k], want[k])
         xw = ago.gather(payload, n, w["dim"], w["dtype"], want["nodes"])
         ok = ok and np.array_equal(sg.x.cpu().numpy().view(np.uint32), xw.view(np.uint32))
+    cpu["reference_gpu_hop1"] = reference_gpu_hop1(g, w, seeds_host)
     return cpu, bool(ok)
+
+
+def reference_gpu_hop1(g, w, seeds_host):
+    """Secondary baseline: hop 1 of the workload (Philox fast mode, fanout = first
+    hop) through the reference's OWN CUDA kernel `warp_sample_neighbors` — compiled
+    from the reference checkout into oracle/_ref/ — against this library's
+    ag_sample_hop_reservoir, same device arrays, outputs compared bit for bit."""
+    import torch
+
+    from aethergraph_b200 import _lib
+    from aethergraph_b200.sampler import reservoir_hop
+    from oracle import ago
+
+    if not os.path.exists(ago.REF_WARP_SAMPLER):
+        return None
+    fanout = int(w["fanout"][0])
+    nodes = np.concatenate(seeds_host[:64]).astype(np.uint64)  # 64 batches' seeds in one launch
+    nodes_dev = torch.from_numpy(nodes.view(np.int64)).cuda()
+    po, pd, pw = C.c_void_p(), C.c_void_p(), C.c_void_p()
+    _lib.check(_lib.lib().ag_graph_device_ptrs(g._h, C.byref(po), C.byref(pd), C.byref(pw)))
+    out = torch.empty((len(nodes), fanout), dtype=torch.int32, device="cuda")
+    cnt = torch.empty((len(nodes),), dtype=torch.int32, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+
+    def timed(fn, reps=20):
+        for _ in range(3):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / reps
+
+    ref_us = timed(lambda: ago.ref_warp_sample(po.value, pd.value, g.num_nodes, nodes_dev.data_ptr(), out.data_ptr(),
+                                               cnt.data_ptr(), len(nodes), fanout, SAMPLER_SEED, 0, st))
+    mine = [None]
+
+    def run_mine():
+        mine[0] = reservoir_hop(g, nodes_dev, fanout, SAMPLER_SEED, 0)
+
+    own_us = timed(run_mine)
+    same = bool(torch.equal(mine[0][0], out) and torch.equal(mine[0][1], cnt))
+    return {"nodes": int(len(nodes)), "fanout": fanout, "reference_kernel_us": ref_us, "this_library_us": own_us,
+            "identical_output": same,
+            "note": "warp_sample_neighbors compiled unmodified from the reference checkout vs ag_sample_hop_reservoir"}
 
 
 def main():

@@ -133,3 +133,55 @@ def test_early_break_custom_sampler_and_argument_errors():
         NeighborLoader(g, [3], input_time=np.zeros(4))
     with pytest.raises(ValueError, match="not both"):
         NeighborLoader(g, [3], features=feats, feature_path="x.bin")
+
+
+def test_hetero_epoch_loader_matches_the_oracle():
+    """python/aethergraph/pytorch/hetero_loader.py:289-404: per-type n_id / x, per-edge-type
+    edge_index, seed_index / input_id / batch_size on the seed type, batches in order."""
+    import aethergraph_b200 as ag
+    from aethergraph_b200.pytorch import HeteroNeighborLoader
+    from aethergraph_b200.pytorch.loader import epoch_sampling_seed
+    from helpers import csr_from_edges
+    from oracle import ago
+
+    rng = np.random.default_rng(6)
+    nn = {"user": 3000, "item": 1500}
+    buys = (rng.integers(0, 3000, 20_000).astype(np.uint32), (rng.zipf(1.5, 20_000) % 1500).astype(np.uint32))
+    ets = [("user", "buys", "item"), ("item", "rev_buys", "user")]
+    edges = [buys, buys[::-1]]
+    g = ag.HeteroCsrGraph.from_edge_arrays(nn, [(*et, *e) for et, e in zip(ets, edges)])
+    fan = {ets[0]: [4, 3], ets[1]: [6, 2]}
+    feats = {"user": rng.standard_normal((3000, 16)).astype(np.float32),
+             "item": rng.standard_normal((1500, 8)).astype(np.float32)}
+    ids = np.arange(0, 3000, 2)
+    loader = HeteroNeighborLoader(g, fan, input_nodes=("user", ids), batch_size=256, shuffle=True, seed=5,
+                                  num_workers=2, prefetch_factor=3, features=feats)
+    assert len(loader) == (len(ids) + 255) // 256
+    order = np.random.default_rng(5).spawn(1)[0].permutation(len(ids))
+    es = epoch_sampling_seed(np.random.SeedSequence(5))
+    rels = []
+    for (st, _, dt), (src, dst) in zip(ets, edges):
+        off, dd, _ = csr_from_edges(nn[st], src, dst)
+        rels.append((["user", "item"].index(st), ["user", "item"].index(dt), off, dd))
+    o = ago.HeteroSampler([3000, 1500], rels, [fan[ets[0]], fan[ets[1]]], seed=0)
+    count = 0
+    for b, data in enumerate(loader):
+        pos = order[b * 256:(b + 1) * 256]
+        o.reseed(ago.batch_seed(es, b))
+        want = o.sample(0, ids[pos].astype(np.uint32))
+        for t, nt in enumerate(["user", "item"]):
+            n_id = data[nt].n_id.cpu().numpy()
+            assert np.array_equal(n_id, want["nodes"][t].astype(np.int64)) and data[nt].num_nodes == len(n_id)
+            assert np.array_equal(data[nt].x.cpu().numpy().view(np.uint32), feats[nt][n_id].view(np.uint32))
+        for e, et in enumerate(ets):
+            ei = data[et].edge_index.cpu().numpy()
+            assert np.array_equal(ei[0], want["edge_src_local"][e]) and np.array_equal(ei[1], want["edge_dst_local"][e])
+        u = data["user"]
+        assert u.batch_size == len(pos) and np.array_equal(u.input_id.cpu().numpy(), pos)
+        assert np.array_equal(u.seed_index.cpu().numpy(), want["seed_indices"].astype(np.int64))
+        count += 1
+    assert count == len(loader) and loader.metrics.batches_processed == count
+    with pytest.raises(ValueError, match="input_nodes is required"):
+        HeteroNeighborLoader(g, fan)
+    with pytest.raises(ValueError, match="same number of hops"):
+        HeteroNeighborLoader(g, {ets[0]: [1], ets[1]: [1, 2]}, input_nodes=("user", None))

@@ -258,3 +258,39 @@ def test_loader_delivers_in_order_with_per_batch_seeds():
         with pytest.raises(ag.SamplingError, match="out of range"):
             ld.submit(0, [100])  # test_hetero.py: a seed past its type fails at submit
     assert ld.next_batch() is None  # after shutdown
+
+
+def test_c4_shaped_schema_down_scaled_matches_the_oracle():
+    """The heterogeneous benchmark configuration at 1/1000 scale: user / post /
+    comment / subreddit, three stored relations plus their reverses, fanouts
+    votes [15,10], writes [10,5], belongs_to [3,2], user seeds."""
+    import aethergraph_b200 as ag
+    from oracle import ago
+
+    rng = np.random.default_rng(44)
+    nn = {"user": 50_000, "post": 20_000, "comment": 100_000, "subreddit": 100}
+
+    def skewed(n_src, n_dst, e):
+        return ((rng.zipf(1.4, e) % n_src).astype(np.uint32), (rng.zipf(1.6, e) % n_dst).astype(np.uint32))
+
+    votes = skewed(nn["user"], nn["post"], 30 * nn["user"])
+    writes = skewed(nn["user"], nn["comment"], 8 * nn["user"])
+    belongs = (np.arange(nn["post"], dtype=np.uint32), rng.integers(0, nn["subreddit"], nn["post"]).astype(np.uint32))
+    ets = [("user", "votes", "post"), ("user", "writes", "comment"), ("post", "belongs_to", "subreddit"),
+           ("post", "rev_votes", "user"), ("comment", "rev_writes", "user"), ("subreddit", "rev_belongs_to", "post")]
+    edges = [votes, writes, belongs, votes[::-1], writes[::-1], belongs[::-1]]
+    fan = [[15, 10], [10, 5], [3, 2], [15, 10], [10, 5], [3, 2]]
+    g = ag.HeteroCsrGraph.from_edge_arrays(nn, [(*et, *e) for et, e in zip(ets, edges)])
+    s = ag.HeteroNeighborSampler(g, ag.HeteroSamplingConfig(dict(zip(ets, fan)), seed=42))
+    names = list(nn)
+    rels = []
+    for (st, _, dt), (src, dst) in zip(ets, edges):
+        off, dd, _ = csr_from_edges(nn[st], src, dst)
+        rels.append((names.index(st), names.index(dt), off, dd))
+    o = ago.HeteroSampler([nn[k] for k in names], rels, fan, seed=42)
+    for i in range(3):
+        seeds = rng.integers(0, nn["user"], 1024).astype(np.uint32)
+        sg = s.sample("user", seeds)
+        want = o.sample(0, seeds)
+        _same(sg.raw_u32(), want)
+        assert sum(len(x) for x in want["nodes"]) > 5000 and all(len(x) for x in want["nodes"])

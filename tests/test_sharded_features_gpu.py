@@ -138,3 +138,26 @@ def test_ipc_shards_across_processes_and_gpus(tmp_path):
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     for k in range(world):
         assert f"RANK{k} ok=True" in r.stdout
+
+
+def test_c5_shaped_batch_over_eight_shards():
+    """The sharded-feature configuration at small scale: 4096 seeds, fanout [15,10,5],
+    128-dim bf16 rows split into 8 vertex-range shards (all on this GPU)."""
+    import aethergraph_b200 as ag
+    from aethergraph_b200 import dist, synth
+    from oracle import ago
+
+    n, off, dst, _ = rmat_csr(16, 12, seed=12)
+    g = ag.Graph.from_csr(off, dst)
+    shards = [synth.features(n, 128, "bf16", 6, row_range=dist.shard_range(r, n, 8)) for r in range(8)]
+    view = ag.FeatureStore.view_sharded(shards, 5)
+    payload = ago.synth_features(n, 128, "bf16", 6)
+    seeds = np.random.default_rng(3).integers(0, n, 4096).astype(np.uint32)
+    sg = ag.NeighborSampler(g, ag.SamplingConfig(num_neighbors=[15, 10, 5], seed=9), features=view).sample(seeds)
+    want = ago.Sampler(off, dst, [15, 10, 5], seed=9).sample(seeds)
+    got = sg.raw_u32()
+    for k in ("nodes", "edge_src", "edge_dst", "src_local", "dst_local", "seed_locals"):
+        assert np.array_equal(got[k], want[k]), k
+    xw = ago.gather(payload, n, 128, "bf16", want["nodes"])
+    assert np.array_equal(sg.x.cpu().numpy().view(np.uint32), xw.view(np.uint32))
+    assert len(want["nodes"]) > 20_000
