@@ -785,6 +785,7 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
     }
     uint32_t log2cap = 0;
     while ((1ull << log2cap) < s->table_cap) ++log2cap;
+    const uint64_t used_cap = s->table_cap;
     const uint64_t ecap = std::max<uint64_t>(s->max_edges, 1);
 
     uint64_t b_nodes = 0, b_edges = 0;
@@ -794,7 +795,7 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
         SampleParams p{};
         p.offsets = g->offsets; p.dst = g->dst; p.weights = g->weights;
         p.num_nodes = g->num_nodes; p.num_edges = g->num_edges;
-        p.table = DedupTable{s->table + (uint64_t)b * s->table_cap, (uint32_t)(s->table_cap - 1), 32u - log2cap, s->gen};
+        p.table = DedupTable{s->table + (uint64_t)b * used_cap, (uint32_t)(used_cap - 1), 32u - log2cap, s->gen};
         p.state = s->state + b;
         p.tiles = s->tiles + (uint64_t)b * s->n_tiles;
         p.epoch_base = s->epoch + 1;
