@@ -24,6 +24,7 @@ RNG_MODE = {"wyrand_exact": AG_RNG_WYRAND_EXACT, "philox": AG_RNG_PHILOX,
             "philox_fast": AG_RNG_PHILOX}
 AG_MAX_HOPS = 8
 AG_IPC_HANDLE_BYTES = 64
+SHARD_LAYOUT = {"range": 0, "cyclic": 1}
 
 
 class GraphLoadError(Exception):
@@ -119,6 +120,9 @@ SIGNATURES = {
     "ag_features_get_batch": (C.c_int32, [_P, _P, C.c_uint64, _P]),
     "ag_gather": (C.c_int32, [_P, _P, C.c_int32, C.c_uint64, _P, _P, _P]),
     "ag_features_check": (C.c_int32, [_P]),
+    "ag_features_load_shard": (C.c_int32, [C.c_char_p, C.c_int32, C.c_uint32, C.c_uint32, C.c_int32, _PP]),
+    "ag_synth_features_shard": (C.c_int32, [C.c_uint64, C.c_uint64, C.c_int32, C.c_uint64, C.c_int32, C.c_uint32,
+                                            C.c_uint32, C.c_int32, _PP]),
     "ag_features_ipc_export": (C.c_int32, [_P, _P]),
     "ag_features_open_sharded": (C.c_int32, [_P, C.c_uint32, C.c_uint32, _P, _PP]),
     "ag_features_view_sharded": (C.c_int32, [_P, C.c_uint32, C.c_uint32, _PP]),

@@ -602,6 +602,56 @@ extern "C" int32_t ag_features_load(const char *path, int32_t device, ag_feature
     return ag_features_load_range(path, device, 0, 0xFFFFFFFFFFFFFFFFull, out);
 }
 
+// Shard `rank` of `world` of a feature file.  Range layout: a contiguous block of
+// rows.  Cyclic layout: rows rank, rank + world, ...: the file is streamed through
+// the pinned bounce buffer in whole multiples of `world` rows and every world-th
+// row is picked by a strided copy (cudaMemcpy2D with the host pitch = world rows).
+extern "C" int32_t ag_features_load_shard(const char *path, int32_t device, uint32_t rank, uint32_t world, int32_t layout,
+                                          ag_features **out) {
+    if (!path || !out) return fail(AG_ERR_VALUE, "ag_features_load_shard: null argument");
+    if (world == 0 || rank >= world) return fail(AG_ERR_VALUE, "ag_features_load_shard: bad rank %u of %u", rank, world);
+    if (layout != AG_SHARD_RANGE && layout != AG_SHARD_CYCLIC) return fail(AG_ERR_VALUE, "unknown shard layout %d", layout);
+    const int fd = open(path, O_RDONLY);
+    if (fd < 0) return fail(AG_ERR_LOAD, "failed to open feature file %s: %s", path, strerror(errno));
+    struct stat sb;
+    if (fstat(fd, &sb) != 0) { close(fd); return fail(AG_ERR_LOAD, "failed to stat feature file"); }
+    FeatHeader h{};
+    int32_t st = parse_feature_header(fd, (uint64_t)sb.st_size, &h);
+    if (st != AG_OK) { close(fd); return st; }
+    if (layout == AG_SHARD_RANGE || world == 1) {
+        close(fd);
+        const uint64_t per = (h.n + world - 1) / world;
+        return ag_features_load_range(path, device, (uint64_t)rank * per, (uint64_t)rank * per + per, out);
+    }
+    DeviceGuard guard(device);
+    if (!guard.ok) { close(fd); return AG_ERR_CUDA; }
+    const uint64_t rows = h.n > rank ? (h.n - rank + world - 1) / world : 0;
+    ag_features *f = new_features(device, h.n, rank, rows, h.dim, h.dtype);
+    f->row_stride = world;
+    st = alloc_features(f, true);
+    const uint64_t row = h.dim * elem_size(h.dtype);
+    void *pinned = nullptr;
+    // rows per chunk: a whole number of `world`-row groups, about 64 MiB
+    const uint64_t groups = std::max<uint64_t>(1, (64ull << 20) / std::max<uint64_t>(row * world, 1));
+    if (st == AG_OK && rows && row &&
+        cudaHostAlloc(&pinned, (size_t)(groups * world * row), cudaHostAllocDefault) != cudaSuccess)
+        st = fail(AG_ERR_CUDA, "pinned buffer allocation failed: %s", cudaGetErrorString(cudaGetLastError()));
+    for (uint64_t done = 0; st == AG_OK && row && done < rows; done += groups) {
+        const uint64_t take = std::min(groups, rows - done);            // shard rows in this chunk
+        const uint64_t first = done * world;                            // first file row of the chunk
+        const uint64_t file_rows = std::min<uint64_t>(take * world, h.n - first);
+        if (!read_exact(fd, pinned, file_rows * row, h.offset + first * row)) { st = fail(AG_ERR_LOAD, "short read in feature payload"); break; }
+        if (cudaMemcpy2D(f->payload + done * row, row, (const uint8_t *)pinned + (uint64_t)rank * row, row * world, row, take,
+                         cudaMemcpyHostToDevice) != cudaSuccess)
+            st = fail(AG_ERR_CUDA, "copy to device failed: %s", cudaGetErrorString(cudaGetLastError()));
+    }
+    if (pinned) cudaFreeHost(pinned);
+    close(fd);
+    if (st != AG_OK) { ag_features_free(f); return st; }
+    *out = f;
+    return AG_OK;
+}
+
 extern "C" int32_t ag_features_from_memory(const void *payload, uint64_t num_nodes, uint64_t dim, int32_t dtype,
                                            int32_t mem_kind, int32_t device, ag_features **out) {
     if ((!payload && num_nodes * dim) || !out) return fail(AG_ERR_VALUE, "ag_features_from_memory: null argument");
@@ -691,6 +741,8 @@ extern "C" int32_t ag_features_device_ptr(const ag_features *f, const void **pay
 extern "C" int32_t ag_gather(const ag_features *f, const void *ids_dev, int32_t ids_are_i64, uint64_t n,
                              const uint32_t *n_dev, float *out_dev, void *stream) {
     if (!f || (!ids_dev && n) || (!out_dev && n)) return fail(AG_ERR_VALUE, "ag_gather: null argument");
+    if (f->row_stride != 1 && !f->shards)
+        return fail(AG_ERR_VALUE, "a cyclic shard is read through a sharded view (ag_features_open_sharded / ag_features_view_sharded)");
     if (n == 0) return AG_OK;
     DeviceGuard guard(f->device);
     if (!guard.ok) return AG_ERR_CUDA;
@@ -718,6 +770,8 @@ extern "C" int32_t ag_features_check(const ag_features *f) {
 // reference: features/store.rs:691-769 — every id is checked before any row is read.
 extern "C" int32_t ag_features_get_batch(const ag_features *f, const int64_t *ids, uint64_t n, float *out) {
     if (!f || (!ids && n) || (!out && n)) return fail(AG_ERR_VALUE, "ag_features_get_batch: null argument");
+    if (f->row_stride != 1 && !f->shards)
+        return fail(AG_ERR_VALUE, "a cyclic shard is read through a sharded view (ag_features_open_sharded / ag_features_view_sharded)");
     for (uint64_t i = 0; i < n; ++i) {
         if (ids[i] < 0 || (uint64_t)ids[i] > 0xFFFFFFFFull) return fail(AG_ERR_VALUE, "invalid node id: %lld", (long long)ids[i]);
         if ((uint64_t)ids[i] >= f->num_nodes) return fail(AG_ERR_VALUE, "node %lld out of bounds", (long long)ids[i]);

@@ -100,6 +100,10 @@ __device__ __forceinline__ uint4 ld_peer_v4(const void *p) {
 // Where row `id` of a sharded store lives: shard id / shard_rows, which is this
 // GPU's own memory or a peer's (vertex-range shards of equal size).
 __device__ __forceinline__ const uint8_t *shard_row(const ag_shard_table *t, uint64_t id, uint32_t row_bytes) {
+    if (t->cyclic) {  // rows dealt round-robin: hot vertex ranges spread over all GPUs
+        const uint64_t s = id % t->n_shards;
+        return t->base[s] + (id / t->n_shards) * row_bytes;
+    }
     const uint64_t s = id / t->shard_rows;
     return t->base[s] + (id - s * t->shard_rows) * row_bytes;
 }

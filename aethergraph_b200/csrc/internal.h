@@ -21,6 +21,7 @@ struct ag_features {
     uint64_t num_nodes = 0;   // rows of the whole store
     uint64_t row_begin = 0;   // first row held here (vertex-range shard)
     uint64_t rows = 0;        // rows held here
+    uint64_t row_stride = 1;  // held row i is row row_begin + i * row_stride (cyclic shard: stride = world)
     uint64_t dim = 0;
     int dtype = AG_F32;
     uint8_t *payload = nullptr;  // device, rows * dim * elem_size
@@ -37,8 +38,9 @@ struct ag_features {
 // Device-visible table of a sharded feature store.
 struct ag_shard_table {
     const uint8_t *base[8];
-    uint64_t shard_rows;
+    uint64_t shard_rows;  // range layout: rows per shard
     uint32_t n_shards;
+    uint32_t cyclic;      // 1: row v lives in shard v % n_shards at local row v / n_shards
 };
 
 namespace ag {

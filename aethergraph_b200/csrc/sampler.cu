@@ -758,6 +758,8 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
                     return fail(AG_ERR_SAMPLING, "seed node %u (position %llu) is out of range for %llu nodes",
                                 seeds[b][i], (unsigned long long)i, (unsigned long long)g->num_nodes);
     }
+    if (feats && want_x && feats->row_stride != 1 && !feats->shards)
+        return fail(AG_ERR_VALUE, "a cyclic feature shard is read through a sharded view");
     if (feats && want_x && feats->device != s->device)
         return fail(AG_ERR_VALUE, "feature store lives on device %d, sampler on %d", feats->device, s->device);
     DeviceGuard guard(s->device);

@@ -1,14 +1,21 @@
-// Feature stores sharded by vertex range over the GPUs of one node.
+// Feature stores sharded over the GPUs of one node.
 //
 // The reference scales past one machine's memory by partitioning the feature
-// matrix by contiguous vertex ranges and fetching remote rows over the fabric
+// matrix across workers and fetching remote rows over the fabric
 // (python/aethergraph/ray/datasource.py:6-10 keeps the topology replicated and
 // the features partitioned; crates/aether-stream's RDMA gather is its transport).
 // On one NVSwitch node the transport is a plain load: every GPU maps its peers'
 // shards (CUDA IPC across processes, peer access inside one process) and the
-// gather kernel reads row v straight out of HBM of GPU v / shard_rows.  The
-// stored (bf16 / f16) row crosses NVLink; the upcast happens at the reader.
-// There is no staging buffer, no collective, and nothing here uses TMA.
+// gather kernel reads row v straight out of the owner's HBM.  The stored
+// (bf16 / f16) row crosses NVLink; the upcast happens at the reader.  There is no
+// staging buffer, no collective, and nothing here uses TMA.
+//
+// Two layouts.  AG_SHARD_RANGE is the reference's: contiguous vertex ranges,
+// owner(v) = v / ceil(N / G).  On skewed graphs the low vertex ids are the hubs,
+// so most sampled rows live in shard 0 and that GPU's NVLink egress becomes the
+// bottleneck of all the others.  AG_SHARD_CYCLIC deals the rows round-robin,
+// owner(v) = v % G, local row v / G: every vertex range, hot or cold, is spread
+// evenly over the GPUs and the exchange is a balanced all-to-all.
 #include <string.h>
 
 #include <algorithm>
@@ -20,7 +27,9 @@ using namespace ag;
 
 namespace {
 
-int32_t make_view(const ag_features *local, uint32_t world, const uint8_t *const *bases, void *const *opened,
+bool is_cyclic(const ag_features *f) { return f->row_stride > 1; }
+
+int32_t make_view(const ag_features *local, uint32_t world, bool cyclic, const uint8_t *const *bases, void *const *opened,
                   ag_features **out) {
     const uint64_t n = local->num_nodes;
     const uint64_t shard_rows = (n + world - 1) / world;
@@ -36,6 +45,7 @@ int32_t make_view(const ag_features *local, uint32_t world, const uint8_t *const
     for (uint32_t r = 0; r < world; ++r) t.base[r] = bases[r];
     t.shard_rows = std::max<uint64_t>(shard_rows, 1);
     t.n_shards = world;
+    t.cyclic = cyclic ? 1u : 0u;
     if (cudaMalloc(&v->err, 4) != cudaSuccess || cudaMemset(v->err, 0, 4) != cudaSuccess ||
         cudaMalloc(&v->shards, sizeof(ag_shard_table)) != cudaSuccess ||
         cudaMemcpy(v->shards, &t, sizeof(t), cudaMemcpyHostToDevice) != cudaSuccess) {
@@ -47,10 +57,20 @@ int32_t make_view(const ag_features *local, uint32_t world, const uint8_t *const
     return AG_OK;
 }
 
+// Does `local` hold exactly the rows shard `rank` of `world` must hold?
 int32_t check_local(const ag_features *local, uint32_t world, uint32_t rank, const char *who) {
     if (world == 0 || world > 8 || rank >= world) return fail(AG_ERR_VALUE, "%s: bad rank %u of %u (at most 8 shards)", who, rank, world);
     if (local->shards) return fail(AG_ERR_VALUE, "%s: the local store is already a sharded view", who);
-    const uint64_t n = local->num_nodes, shard_rows = (n + world - 1) / world;
+    const uint64_t n = local->num_nodes;
+    if (is_cyclic(local)) {
+        const uint64_t rows = n > rank ? (n - rank + world - 1) / world : 0;
+        if (local->row_stride != world || local->row_begin != rank || local->rows != rows)
+            return fail(AG_ERR_VALUE, "%s: rank %u of %u must hold rows %u, %u + %u, ... (%llu rows); the store holds %llu rows "
+                        "from %llu with stride %llu", who, rank, world, rank, rank, world, (unsigned long long)rows,
+                        (unsigned long long)local->rows, (unsigned long long)local->row_begin, (unsigned long long)local->row_stride);
+        return AG_OK;
+    }
+    const uint64_t shard_rows = (n + world - 1) / world;
     const uint64_t begin = std::min<uint64_t>((uint64_t)rank * shard_rows, n), end = std::min<uint64_t>(begin + shard_rows, n);
     if (local->row_begin != begin || local->rows != end - begin)
         return fail(AG_ERR_VALUE, "%s: rank %u of %u must hold rows [%llu, %llu) of %llu, the store holds [%llu, %llu)", who,
@@ -82,10 +102,12 @@ extern "C" int32_t ag_features_open_sharded(const ag_features *local, uint32_t w
     if (!guard.ok) return AG_ERR_CUDA;
     const uint8_t *bases[8] = {nullptr};
     void *opened[8] = {nullptr};
+    const bool cyclic = is_cyclic(local) || (world > 1 && local->row_stride == world);
     const uint64_t n = local->num_nodes, shard_rows = (n + world - 1) / world;
     for (uint32_t r = 0; r < world; ++r) {
         if (r == rank) { bases[r] = local->payload; continue; }
-        if ((uint64_t)r * shard_rows >= n) continue;  // empty tail shard
+        const bool empty = cyclic ? (uint64_t)r >= n : (uint64_t)r * shard_rows >= n;
+        if (empty) continue;
         cudaIpcMemHandle_t h;
         memcpy(&h, (const uint8_t *)handles + (size_t)r * AG_IPC_HANDLE_BYTES, sizeof(h));
         void *p = nullptr;
@@ -96,7 +118,7 @@ extern "C" int32_t ag_features_open_sharded(const ag_features *local, uint32_t w
         }
         opened[r] = p; bases[r] = (const uint8_t *)p;
     }
-    const int32_t st = make_view(local, world, bases, opened, out);
+    const int32_t st = make_view(local, world, cyclic, bases, opened, out);
     if (st != AG_OK) for (void *q : opened) if (q) cudaIpcCloseMemHandle(q);
     return st;
 }
@@ -106,8 +128,9 @@ extern "C" int32_t ag_features_view_sharded(const ag_features *const *shards, ui
     if (!shards || !out || world == 0 || world > 8 || rank >= world) return fail(AG_ERR_VALUE, "ag_features_view_sharded: bad argument");
     for (uint32_t r = 0; r < world; ++r) {
         if (!shards[r]) return fail(AG_ERR_VALUE, "ag_features_view_sharded: shard %u is null", r);
-        if (shards[r]->num_nodes != shards[0]->num_nodes || shards[r]->dim != shards[0]->dim || shards[r]->dtype != shards[0]->dtype)
-            return fail(AG_ERR_VALUE, "ag_features_view_sharded: shard %u disagrees on shape or dtype", r);
+        if (shards[r]->num_nodes != shards[0]->num_nodes || shards[r]->dim != shards[0]->dim ||
+            shards[r]->dtype != shards[0]->dtype || is_cyclic(shards[r]) != is_cyclic(shards[0]))
+            return fail(AG_ERR_VALUE, "ag_features_view_sharded: shard %u disagrees on shape, dtype or layout", r);
         AG_TRY(check_local(shards[r], world, r, "ag_features_view_sharded"));
     }
     const ag_features *local = shards[rank];
@@ -124,5 +147,5 @@ extern "C" int32_t ag_features_view_sharded(const ag_features *const *shards, ui
         if (e == cudaErrorPeerAccessAlreadyEnabled) cudaGetLastError();
         else if (e != cudaSuccess) return fail(AG_ERR_CUDA, "enabling peer access to GPU %d failed: %s", shards[r]->device, cudaGetErrorString(e));
     }
-    return make_view(local, world, bases, nullptr, out);
+    return make_view(local, world, is_cyclic(local), bases, nullptr, out);
 }

@@ -115,11 +115,19 @@ __device__ __forceinline__ uint16_t enc_bf16(float v) {
     return (uint16_t)((bits + 0x7FFFu + ((bits >> 16) & 1u)) >> 16);  // values are finite
 }
 
-__global__ void k_features(uint8_t *payload, uint64_t row_begin, uint64_t rows, uint64_t dim, int dtype, uint64_t seed) {
+// Held row i is row row_begin + i * row_stride of the whole table; a value depends
+// only on (seed, row, column), so any shard of the table has the whole table's bits.
+__global__ void k_features(uint8_t *payload, uint64_t row_begin, uint64_t row_stride, uint64_t rows, uint64_t dim,
+                           int dtype, uint64_t seed) {
     const uint64_t total = rows * dim;
     for (uint64_t g = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; g < total;
          g += (uint64_t)gridDim.x * blockDim.x) {
-        const float f = unit_normal(seed, row_begin * dim + g);
+        uint64_t index = row_begin * dim + g;
+        if (row_stride != 1) {
+            const uint64_t i = g / dim;
+            index = (row_begin + i * row_stride) * dim + (g - i * dim);
+        }
+        const float f = unit_normal(seed, index);
         if (dtype == AG_F32) ((float *)payload)[g] = f;
         else if (dtype == AG_BF16) ((uint16_t *)payload)[g] = enc_bf16(f);
         else ((uint16_t *)payload)[g] = __half_as_ushort(__float2half_rn(f));
@@ -284,24 +292,43 @@ extern "C" int32_t ag_synth_free_device(void *ptr, int32_t device) {
     return AG_OK;
 }
 
-extern "C" int32_t ag_synth_features(uint64_t num_nodes, uint64_t dim, int32_t dtype, uint64_t seed, int32_t device,
-                                     uint64_t row_begin, uint64_t row_end, ag_features **out) {
+namespace {
+int32_t synth_feature_rows(uint64_t num_nodes, uint64_t dim, int32_t dtype, uint64_t seed, int32_t device,
+                           uint64_t row_begin, uint64_t row_stride, uint64_t rows, ag_features **out) {
     if (!out) return fail(AG_ERR_VALUE, "ag_synth_features: null argument");
     if (dtype < 0 || dtype > 2) return fail(AG_ERR_VALUE, "unknown feature dtype tag: %d", dtype);
-    row_end = std::min(row_end, num_nodes);
-    row_begin = std::min(row_begin, row_end);
     DeviceGuard guard(device);
     if (!guard.ok) return AG_ERR_CUDA;
-    const uint64_t rows = row_end - row_begin;
     uint8_t *payload = nullptr;
     AG_CUDA(cudaMalloc(&payload, std::max<uint64_t>(rows * dim * elem_size(dtype), 16)));
-    k_features<<<grid_for(rows * dim), 256>>>(payload, row_begin, rows, dim, dtype, seed);
+    k_features<<<grid_for(rows * dim), 256>>>(payload, row_begin, row_stride, rows, dim, dtype, seed);
     const cudaError_t e = cudaDeviceSynchronize();
     if (e != cudaSuccess) { cudaFree(payload); return fail(AG_ERR_CUDA, "k_features: %s", cudaGetErrorString(e)); }
     ag_features *f = nullptr;
     const int32_t st = ag_features_adopt_device(payload, rows, dim, dtype, device, &f);
     if (st != AG_OK) { cudaFree(payload); return st; }
-    f->num_nodes = num_nodes; f->row_begin = row_begin; f->rows = rows; f->owns_payload = true;
+    f->num_nodes = num_nodes; f->row_begin = row_begin; f->rows = rows; f->row_stride = row_stride; f->owns_payload = true;
     *out = f;
     return AG_OK;
+}
+}  // namespace
+
+extern "C" int32_t ag_synth_features(uint64_t num_nodes, uint64_t dim, int32_t dtype, uint64_t seed, int32_t device,
+                                     uint64_t row_begin, uint64_t row_end, ag_features **out) {
+    row_end = std::min(row_end, num_nodes);
+    row_begin = std::min(row_begin, row_end);
+    return synth_feature_rows(num_nodes, dim, dtype, seed, device, row_begin, 1, row_end - row_begin, out);
+}
+
+extern "C" int32_t ag_synth_features_shard(uint64_t num_nodes, uint64_t dim, int32_t dtype, uint64_t seed, int32_t device,
+                                           uint32_t rank, uint32_t world, int32_t layout, ag_features **out) {
+    if (world == 0 || rank >= world) return fail(AG_ERR_VALUE, "ag_synth_features_shard: bad rank %u of %u", rank, world);
+    if (layout == AG_SHARD_CYCLIC && world > 1) {
+        const uint64_t rows = num_nodes > rank ? (num_nodes - rank + world - 1) / world : 0;
+        return synth_feature_rows(num_nodes, dim, dtype, seed, device, rank, world, rows, out);
+    }
+    if (layout != AG_SHARD_RANGE && layout != AG_SHARD_CYCLIC) return fail(AG_ERR_VALUE, "unknown shard layout %d", layout);
+    const uint64_t per = (num_nodes + world - 1) / world;
+    const uint64_t begin = std::min<uint64_t>((uint64_t)rank * per, num_nodes), end = std::min<uint64_t>(begin + per, num_nodes);
+    return synth_feature_rows(num_nodes, dim, dtype, seed, device, begin, 1, end - begin, out);
 }

@@ -111,7 +111,16 @@ class FeatureStore:
                                                       FeatureStore._dev(device), C.byref(out)))
         return FeatureStore(out.value)
 
-    # -- vertex-range shards over the GPUs of one node -----------------------
+    # -- shards over the GPUs of one node --------------------------------------
+    @staticmethod
+    def load_shard(path, rank: int, world: int, layout: str = "cyclic", *, device: int | None = None) -> "FeatureStore":
+        """Shard `rank` of `world` of a feature file: `layout="range"` is a contiguous
+        block of rows, `"cyclic"` rows rank, rank + world, ... (balanced on skewed graphs)."""
+        out = C.c_void_p()
+        _lib.check(_lib.lib().ag_features_load_shard(os.fspath(path).encode(), FeatureStore._dev(device), rank, world,
+                                                     _lib.SHARD_LAYOUT[layout], C.byref(out)))
+        return FeatureStore(out.value)
+
     def ipc_handle(self) -> bytes:
         """64-byte CUDA IPC handle of this shard's rows, for the other ranks of the node."""
         buf = C.create_string_buffer(_lib.AG_IPC_HANDLE_BYTES)

@@ -62,3 +62,12 @@ def seed_batch(num_nodes: int, batch_size: int, seed: int, batch_idx: int) -> np
     with np.errstate(over="ignore"):
         r = _mix(base + np.arange(batch_size, dtype=np.uint64))
     return (r % np.uint64(num_nodes)).astype(np.uint32)
+
+
+def features_shard(num_nodes: int, dim: int, dtype: str, seed: int, rank: int, world: int, layout: str = "cyclic", *,
+                   device: int | None = None) -> FeatureStore:
+    """Shard `rank` of `world` of the same table as `features()`, generated in place."""
+    out = C.c_void_p()
+    _lib.check(_lib.lib().ag_synth_features_shard(num_nodes, dim, _lib.DTYPE_TAG[dtype], seed & (2**64 - 1),
+                                                  _device(device), rank, world, _lib.SHARD_LAYOUT[layout], C.byref(out)))
+    return FeatureStore(out.value)

@@ -240,12 +240,13 @@ def run_device(args, w):
     # ---- inputs, resident in HBM (CSR and features replicated per GPU) ------
     t_setup = time.time()
     g = synth.rmat_graph(w["nodes"], w["edges"], GRAPH_SEED, weight_sigma=1.0 if w["weighted"] else 0.0)
-    if args.features == "sharded" and world > 1:
-        # vertex-range shards: rank r holds rows shard_range(r); remote rows cross NVLink inside the gather kernel
+    if args.features != "replicated" and world > 1:
+        # every rank holds 1/world of the rows; remote rows cross NVLink inside the gather kernel.
+        # "sharded": rows dealt round-robin (balanced); "sharded-range": contiguous vertex ranges.
         from aethergraph_b200 import dist as agd
 
-        local_shard = synth.features(w["nodes"], w["dim"], w["dtype"], FEATURE_SEED,
-                                     row_range=agd.shard_range(rank, w["nodes"], world))
+        layout = "range" if args.features == "sharded-range" else "cyclic"
+        local_shard = synth.features_shard(w["nodes"], w["dim"], w["dtype"], FEATURE_SEED, rank, world, layout)
         feats = agd.open_sharded_features(local_shard)
     else:
         feats = synth.features(w["nodes"], w["dim"], w["dtype"], FEATURE_SEED)
@@ -451,9 +452,11 @@ def run_device(args, w):
             "data": "synthetic (seeded R-MAT graph + ~N(0,1) features generated in HBM)",
             "config": {"workload": w["label"], "batches_per_step": per_step, "rng_mode": "wyrand_exact",
                        "sampler_threads": threads, "group": group, "prefetch_depth": depth, "parallelism": f"dp{world}",
-                       "features": ("sharded by vertex range, remote rows over NVLink (%d/%d of the reads)"
-                                    % (world - 1, world)) if (args.features == "sharded" and world > 1)
-                       else "replicated", "inputs_larger_than_l2": True},
+                       "features": ("%s, remote rows over NVLink (%d/%d of the rows)"
+                                    % ("sharded by contiguous vertex range" if args.features == "sharded-range"
+                                       else "sharded round-robin by vertex id", world - 1, world))
+                       if (args.features != "replicated" and world > 1) else "replicated",
+                       "inputs_larger_than_l2": True},
             "gather_gbs": gather_gbs, "edges_per_step": tot_edges / max(args.steps, 1),
             "rows_per_step": tot_nodes / max(args.steps, 1), "setup_s": round(t_setup, 1),
             "clocks": clk, "roofline": roofline, "cpu_baseline": cpu, "parity_full_scale": parity,
@@ -591,8 +594,9 @@ def main():
     ap.add_argument("--depth", type=int, default=0, help="prefetch depth (0: max(8, group / 2))")
     ap.add_argument("--group", type=int, default=int(os.environ.get("AG_BENCH_GROUP", "0")),
                     help="batches a worker runs as one launch chain (0: chosen from --steps)")
-    ap.add_argument("--features", default="replicated", choices=["replicated", "sharded"],
-                    help="with more than one GPU: every GPU holds all feature rows, or a vertex-range shard each")
+    ap.add_argument("--features", default="replicated", choices=["replicated", "sharded", "sharded-range"],
+                    help="with more than one GPU: every GPU holds all feature rows, or 1/N of them "
+                         "(dealt round-robin, or as contiguous vertex ranges)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--only-value", action="store_true",
                     help="run the resident (C ABI) leg only: no e2e, no CPU baseline (profiling runs)")

@@ -146,7 +146,18 @@ int32_t ag_features_device_ptr(const ag_features *f, const void **payload_dev);
  * (`handles` = world x 64 bytes, own entry ignored).  One process driving
  * several GPUs: ag_features_view_sharded over the shard handles themselves.
  * The view gathers any row in [0, num_nodes); it borrows the local shard,
- * which must outlive it, and is freed with ag_features_free. */
+ * which must outlive it, and is freed with ag_features_free.
+ *
+ * Layouts.  AG_SHARD_RANGE is the contiguous layout above (the reference's).
+ * AG_SHARD_CYCLIC deals rows round-robin: shard r holds rows r, r + world, ...
+ * and row v lives in shard v % world at local row v / world.  On skewed graphs
+ * the hub vertices sit in the low id range, so under the range layout most
+ * gathered rows come from shard 0 and that GPU's NVLink egress throttles every
+ * reader; the cyclic layout spreads any id range evenly over the GPUs.  A
+ * cyclic shard can only be read through a view. */
+enum { AG_SHARD_RANGE = 0, AG_SHARD_CYCLIC = 1 };
+int32_t ag_features_load_shard(const char *path, int32_t device, uint32_t rank, uint32_t world,
+                               int32_t layout, ag_features **out);
 #define AG_IPC_HANDLE_BYTES 64
 int32_t ag_features_ipc_export(const ag_features *f, void *handle_out);
 int32_t ag_features_open_sharded(const ag_features *local, uint32_t world, uint32_t rank,
@@ -477,6 +488,11 @@ int32_t ag_synth_free_device(void *ptr, int32_t device);
 int32_t ag_synth_features(uint64_t num_nodes, uint64_t dim, int32_t dtype, uint64_t seed,
                           int32_t device, uint64_t row_begin, uint64_t row_end,
                           ag_features **out);
+/* Shard `rank` of `world` of the same table in either layout (same bits as the
+ * corresponding rows of the whole table). */
+int32_t ag_synth_features_shard(uint64_t num_nodes, uint64_t dim, int32_t dtype, uint64_t seed,
+                                int32_t device, uint32_t rank, uint32_t world, int32_t layout,
+                                ag_features **out);
 
 #ifdef __cplusplus
 }

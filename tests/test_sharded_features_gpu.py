@@ -48,6 +48,38 @@ def test_sharded_view_on_one_gpu_matches_the_unsharded_store(dtype, dim, world, 
         ag.FeatureStore.view_sharded(shards[::-1], 0)
 
 
+@pytest.mark.parametrize("dtype,dim", [("bf16", 256), ("f32", 24), ("f16", 7)])
+@pytest.mark.parametrize("world", [2, 3, 8])
+def test_cyclic_shards_from_file_and_generator(dtype, dim, world, tmp_path):
+    """Rows dealt round-robin (row v in shard v % world): the view returns the rows of
+    the whole table; a bare cyclic shard refuses to be read by global id."""
+    import torch
+
+    import aethergraph_b200 as ag
+    from aethergraph_b200 import synth
+    from oracle import ago
+
+    n = 5003
+    payload = ago.synth_features(n, dim, dtype, 31)
+    feats = ago.decode(payload, dtype).reshape(n, dim)
+    path = tmp_path / "f.bin"
+    ag.save_features(str(path), feats, dtype=dtype)   # re-encoding decoded values is exact
+    ids = np.concatenate([np.random.default_rng(2).integers(0, n, 4000), np.arange(0, 3 * world), np.arange(n - 20, n)])
+    want = ago.gather(payload, n, dim, dtype, ids.astype(np.uint32))
+    from_file = [ag.FeatureStore.load_shard(str(path), r, world, "cyclic") for r in range(world)]
+    generated = [synth.features_shard(n, dim, dtype, 31, r, world, "cyclic") for r in range(world)]
+    for shards in (from_file, generated):
+        assert sum(s.payload_to_host().size for s in shards) == payload.size
+        view = ag.FeatureStore.view_sharded(shards, world - 1)
+        got = view.gather(torch.from_numpy(ids).cuda())
+        assert np.array_equal(got.cpu().numpy().view(np.uint32), want.view(np.uint32))
+    with pytest.raises(ValueError, match="sharded view"):
+        generated[0].gather(torch.from_numpy(ids).cuda())
+    with pytest.raises(ValueError, match="layout"):
+        ag.FeatureStore.view_sharded([generated[0]] + [synth.features_shard(n, dim, dtype, 31, r, world, "range")
+                                                       for r in range(1, world)], 0)
+
+
 def test_loader_with_sharded_features_matches_the_oracle():
     import aethergraph_b200 as ag
     from aethergraph_b200 import dist, synth
@@ -89,14 +121,14 @@ rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
 torch.cuda.set_device(rank)
 dist.init_process_group("gloo")
 n, dim, dtype = 200_003, 256, "bf16"
-local = synth.features(n, dim, dtype, 21, row_range=agd.shard_range(rank, n, world))
+local = synth.features_shard(n, dim, dtype, 21, rank, world, "cyclic")   # rows dealt round-robin
 view = agd.open_sharded_features(local)
 payload = ago.synth_features(n, dim, dtype, 21)
 ids = np.random.default_rng(100 + rank).integers(0, n, 50_000)
 got = view.gather(torch.from_numpy(ids).cuda())
 want = ago.gather(payload, n, dim, dtype, ids.astype(np.uint32))
 ok = np.array_equal(got.cpu().numpy().view(np.uint32), want.view(np.uint32))
-remote = float(np.mean(np.array([agd.owner_of_row(int(i), n, world) for i in ids[:2000]]) != rank))
+remote = float(np.mean(ids[:2000] % world != rank))
 # the loader path over the sharded view
 from helpers import rmat_csr
 nn, off, dst, _ = rmat_csr(14, 8, seed=2)
