@@ -114,7 +114,20 @@ __device__ __forceinline__ void row_demand(int mode, uint64_t deg, uint32_t k, u
 }
 
 // ------------------------------------------------------------ seed insert --
+// Programmatic dependent launch: the kernels of a chain are launched with
+// cudaLaunchAttributeProgrammaticStreamSerialization, so the next kernel's blocks
+// are scheduled as this one's blocks exit, without waiting for the grid's
+// completion to be reported first.  Every kernel starts by waiting for its
+// predecessor's results (griddepcontrol.wait; a no-op for a plain launch).  The
+// kernels do NOT release their successor early (no griddepcontrol.launch_dependents
+// before the work): measured, successor blocks parked in SM slots take those slots
+// from the gather of a neighbouring chain and the whole pipeline gets slower.
+__device__ __forceinline__ void chain_sync() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 __global__ void k_insert_seeds(const SampleParams *__restrict__ pa) {
+    chain_sync();
     const SampleParams &p = pa[blockIdx.y];
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= p.n_seeds) return;
@@ -312,6 +325,7 @@ template <bool HAS_NEXT>
 __global__ void __launch_bounds__(kTile, HAS_NEXT ? 2 : 3)
 k_assign(const SampleParams *__restrict__ pa, uint32_t stage, uint32_t k) {
     constexpr bool has_next = HAS_NEXT;  // the last stage queues no frontier and needs fewer registers
+    chain_sync();
     __shared__ uint32_t s_tile;
     __shared__ ScanVal s_warp[kTile / 32];
     __shared__ ScanVal s_prefix;
@@ -431,6 +445,7 @@ template <int G, int PICK>
 __global__ void __launch_bounds__(PICK == kPickLarge ? 128 : kPickThreads)
 k_pick(const SampleParams *__restrict__ pa, uint32_t hop, uint32_t k) {
     __shared__ uint32_t s_picks[PICK == kPickLarge ? 4 : 1][PICK == kPickLarge ? kLargeK : 1];
+    chain_sync();
     const SampleParams &p = pa[blockIdx.y];
     const StageInfo nx = p.state->stage[hop + 1];
     if constexpr (PICK == kPickWeighted) pick_weighted(p, hop, k, nx.n_edges, p.frontier, nx.frontier_n);
@@ -440,6 +455,7 @@ k_pick(const SampleParams *__restrict__ pa, uint32_t hop, uint32_t k) {
 
 // --------------------------------------------------------------- finalize --
 __global__ void k_finalize(const SampleParams *__restrict__ pa) {
+    chain_sync();
     const SampleParams &p = pa[blockIdx.y];
     BatchState *bs = p.state;
     const StageInfo fin = bs->stage[p.num_hops + 1];
@@ -485,6 +501,18 @@ __global__ void k_finalize(const SampleParams *__restrict__ pa) {
     }
 }
 
+// Launches `kern` as a programmatic dependent of the previous kernel on the stream.
+template <typename... KArgs, typename... Args>
+void launch_chained(void (*kern)(KArgs...), dim3 grid, dim3 block, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = 0; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
 uint64_t next_pow2(uint64_t v) {
     uint64_t p = 1;
     while (p < v) p <<= 1;
@@ -499,17 +527,17 @@ void launch_pick(int mode, uint32_t k, uint64_t frontier_est, uint32_t n_batches
         return (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>(b, std::max<uint64_t>(1, (uint64_t)kSMs * 16 / n_batches)));
     };
     if (mode == kModeWeighted) {
-        k_pick<32, kPickWeighted><<<dim3(blocks_for(frontier_est, kPickThreads / 32), n_batches), kPickThreads, 0, st>>>(pa, hop, k);
+        launch_chained(k_pick<32, kPickWeighted>, dim3(blocks_for(frontier_est, kPickThreads / 32), n_batches), dim3(kPickThreads), st, pa, hop, k);
     } else if (k > 32) {
-        k_pick<32, kPickLarge><<<dim3(blocks_for(frontier_est, 4), n_batches), 128, 0, st>>>(pa, hop, k);
+        launch_chained(k_pick<32, kPickLarge>, dim3(blocks_for(frontier_est, 4), n_batches), dim3(128), st, pa, hop, k);
     } else {
         const uint32_t G = k <= 4 ? 4 : k <= 8 ? 8 : k <= 16 ? 16 : 32;
         const dim3 grid(blocks_for(frontier_est, kPickThreads / G), n_batches);
         switch (G) {
-            case 4: k_pick<4, kPickSmall><<<grid, kPickThreads, 0, st>>>(pa, hop, k); break;
-            case 8: k_pick<8, kPickSmall><<<grid, kPickThreads, 0, st>>>(pa, hop, k); break;
-            case 16: k_pick<16, kPickSmall><<<grid, kPickThreads, 0, st>>>(pa, hop, k); break;
-            default: k_pick<32, kPickSmall><<<grid, kPickThreads, 0, st>>>(pa, hop, k); break;
+            case 4: launch_chained(k_pick<4, kPickSmall>, grid, dim3(kPickThreads), st, pa, hop, k); break;
+            case 8: launch_chained(k_pick<8, kPickSmall>, grid, dim3(kPickThreads), st, pa, hop, k); break;
+            case 16: launch_chained(k_pick<16, kPickSmall>, grid, dim3(kPickThreads), st, pa, hop, k); break;
+            default: launch_chained(k_pick<32, kPickSmall>, grid, dim3(kPickThreads), st, pa, hop, k); break;
         }
     }
 }
@@ -863,8 +891,8 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
         const bool has_next = stage < H;
         const uint32_t k = has_next ? s->cfg.fanout[stage] : 0;
         const uint64_t expect = (stage && s->est_items[stage]) ? std::min(items, s->est_items[stage]) : items;
-        if (has_next) k_assign<true><<<dim3(tiles_for(expect), n_batches), kTile, 0, st>>>(pa, stage, k);
-        else k_assign<false><<<dim3(tiles_for(expect), n_batches), kTile, 0, st>>>(pa, stage, k);
+        if (has_next) launch_chained(k_assign<true>, dim3(tiles_for(expect), n_batches), dim3(kTile), st, pa, stage, k);
+        else launch_chained(k_assign<false>, dim3(tiles_for(expect), n_batches), dim3(kTile), st, pa, stage, k);
         if (has_next && k) {
             // the new vertices of this stage are at most its items
             launch_pick(s->mode, k, std::min<uint64_t>(expect, g->num_nodes), n_batches, st, pa, stage);
@@ -878,7 +906,7 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
         const uint64_t work = est_edges ? std::min(bound, std::max<uint64_t>(est_edges, nmax)) : bound;
         // one edge per thread where the GPU can hold them: every table lookup in flight at once
         const uint32_t fx = (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>((work + 255) / 256, std::max<uint64_t>((uint64_t)kSMs * 16 / n_batches, 1)));
-        k_finalize<<<dim3(fx, n_batches), 256, 0, st>>>(pa);
+        launch_chained(k_finalize, dim3(fx, n_batches), dim3(256), st, pa);
     }
     AG_CUDA(cudaGetLastError());
     if (s->profile) AG_CUDA(cudaEventRecord(s->ev[1], st));
