@@ -101,6 +101,39 @@ class HeteroCsrGraph:
                                                ne.ctypes.data, _lib.AG_MEM_HOST, device, C.byref(out)))
         return HeteroCsrGraph(out.value, nt, names, [int(v) for v in ne], device)
 
+    @staticmethod
+    def from_device_edges(node_types: dict[str, int], edge_types: list[tuple], device: int | None = None) -> "HeteroCsrGraph":
+        """Like `from_edge_arrays` with the COO arrays already in GPU memory: every
+        `src_ids` / `dst_ids` is a contiguous int32 CUDA tensor holding u32 ids."""
+        import torch
+
+        if device is None:
+            device = torch.cuda.current_device()
+        nt = [(str(k), int(v)) for k, v in node_types.items()]
+        nt_id = {name: i for i, (name, _) in enumerate(nt)}
+        names, src_t, dst_t, srcs, dsts = [], [], [], [], []
+        for (s, rel, d, a, b) in edge_types:
+            if s not in nt_id or d not in nt_id:
+                raise ValueError(f"unknown node type in ({s}, {rel}, {d})")
+            if (s, rel, d) in names:
+                raise ValueError(f"duplicate edge type ({s}, {rel}, {d})")
+            for t in (a, b):
+                if not (t.is_cuda and t.is_contiguous() and t.dtype == torch.int32 and t.dim() == 1):
+                    raise ValueError("edge arrays must be contiguous 1-d int32 CUDA tensors")
+            if a.numel() != b.numel():
+                raise ValueError(f"src and dst arrays must have the same length for ({s}, {rel}, {d})")
+            names.append((s, rel, d)); src_t.append(nt_id[s]); dst_t.append(nt_id[d]); srcs.append(a); dsts.append(b)
+        num_nodes = np.array([c for _, c in nt], dtype=np.uint64)
+        st, dt = np.array(src_t, dtype=np.uint32), np.array(dst_t, dtype=np.uint32)
+        ne = np.array([a.numel() for a in srcs], dtype=np.uint64)
+        pa = (C.c_void_p * max(len(srcs), 1))(*[a.data_ptr() if a.numel() else None for a in srcs])
+        pb = (C.c_void_p * max(len(dsts), 1))(*[b.data_ptr() if b.numel() else None for b in dsts])
+        out = C.c_void_p()
+        torch.cuda.synchronize(device)
+        _lib.check(_lib.lib().ag_hetero_create(len(nt), num_nodes.ctypes.data, len(names), st.ctypes.data, dt.ctypes.data,
+                                               None, pa, pb, ne.ctypes.data, _lib.AG_MEM_DEVICE, device, C.byref(out)))
+        return HeteroCsrGraph(out.value, nt, names, [int(v) for v in ne], device)
+
     def node_types(self) -> list[str]:
         return [n for n, _ in self._node_types]
 

@@ -71,3 +71,33 @@ def features_shard(num_nodes: int, dim: int, dtype: str, seed: int, rank: int, w
     _lib.check(_lib.lib().ag_synth_features_shard(num_nodes, dim, _lib.DTYPE_TAG[dtype], seed & (2**64 - 1),
                                                   _device(device), rank, world, _lib.SHARD_LAYOUT[layout], C.byref(out)))
     return FeatureStore(out.value)
+
+
+def rmat_relation(num_src: int, num_dst: int, num_edges: int, seed: int, *, abc=RMAT_ABC, device: int | None = None):
+    """One bipartite R-MAT relation generated on the device: returns
+    `(offsets, dst)` as CUDA tensors (int64 offsets over the sources, int32 holding
+    u32 destination ids), rows sorted by (source, destination)."""
+    import torch
+
+    dev = _device(device)
+    po, pd, pw = C.c_void_p(), C.c_void_p(), C.c_void_p()
+    _lib.check(_lib.lib().ag_synth_rmat_csr(num_src, num_dst, num_edges, abc[0], abc[1], abc[2], seed & (2**64 - 1),
+                                            0.0, dev, C.byref(po), C.byref(pd), C.byref(pw)))
+    from .sampler import _DevArray
+
+    tdev = torch.device("cuda", dev)
+    try:
+        offsets = torch.as_tensor(_DevArray(po.value, (num_src + 1,), "<i8", None), device=tdev).clone()
+        dst = torch.as_tensor(_DevArray(pd.value, (max(num_edges, 1),), "<i4", None), device=tdev)[:num_edges].clone()
+    finally:
+        _lib.lib().ag_synth_free_device(po, dev)
+        _lib.lib().ag_synth_free_device(pd, dev)
+    return offsets, dst
+
+
+def relation_sources(offsets):
+    """Source id of every edge of a CSR relation (int32 CUDA tensor holding u32 ids)."""
+    import torch
+
+    deg = offsets[1:] - offsets[:-1]
+    return torch.repeat_interleave(torch.arange(deg.numel(), dtype=torch.int32, device=offsets.device), deg)

@@ -482,6 +482,123 @@ def run_device(args, w):
         dist.destroy_process_group()
 
 
+# --------------------------------------------------------------------------- #
+#  heterogeneous workload (C4): secondary, `--workload c4` / `c4s`               #
+# --------------------------------------------------------------------------- #
+HETERO = {
+    # user / post / comment / subreddit; three stored relations plus their reverses (user seeds
+    # need incoming edge types); fanouts votes [15,10], writes [10,5], belongs_to [3,2]
+    "c4": dict(scale=1, label="C4: user 50M / post 20M / comment 100M / subreddit 100K, 6 edge types, batch 1024"),
+    "c4s": dict(scale=10, label="C4 at 1/10 scale: user 5M / post 2M / comment 10M / subreddit 10K, 6 edge types, batch 1024"),
+}
+
+
+def run_hetero(args, hw):
+    """Sampled edges/s of the heterogeneous sampler + per-type feature gather on one
+    GPU, with the CPU restatement timed beside it on the same relations."""
+    import torch
+
+    import aethergraph_b200 as ag
+    from aethergraph_b200 import synth
+    from oracle import ago
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device")
+    sc = hw["scale"]
+    nn = {"user": 50_000_000 // sc, "post": 20_000_000 // sc, "comment": 100_000_000 // sc, "subreddit": 100_000 // sc}
+    t0 = time.time()
+    votes = synth.rmat_relation(nn["user"], nn["post"], 30 * nn["user"], 11)
+    writes = synth.rmat_relation(nn["user"], nn["comment"], 8 * nn["user"], 12)
+    belongs_dst = torch.from_numpy((synth._mix(np.arange(nn["post"], dtype=np.uint64) + np.uint64(13))
+                                    % np.uint64(nn["subreddit"])).astype(np.int32)).cuda()
+    belongs = (torch.arange(nn["post"] + 1, dtype=torch.int64, device="cuda"), belongs_dst)
+    rel = {"votes": votes, "writes": writes, "belongs_to": belongs}
+    src = {k: synth.relation_sources(v[0]) for k, v in rel.items()}
+    ets = [("user", "votes", "post"), ("user", "writes", "comment"), ("post", "belongs_to", "subreddit"),
+           ("post", "rev_votes", "user"), ("comment", "rev_writes", "user"), ("subreddit", "rev_belongs_to", "post")]
+    arrays = [(src["votes"], votes[1]), (src["writes"], writes[1]), (src["belongs_to"], belongs[1]),
+              (votes[1], src["votes"]), (writes[1], src["writes"]), (belongs[1], src["belongs_to"])]
+    fan = [[15, 10], [10, 5], [3, 2], [15, 10], [10, 5], [3, 2]]
+    g = ag.HeteroCsrGraph.from_device_edges(nn, [(*et, *a) for et, a in zip(ets, arrays)])
+    host_rel = {k: (v[0].cpu().numpy().astype(np.uint64), v[1].cpu().numpy().view(np.uint32)) for k, v in rel.items()}
+    del src, arrays, votes, writes, belongs, rel
+    torch.cuda.empty_cache()
+    dims = {"user": 128, "post": 128, "comment": 128, "subreddit": 64}
+    stores = {nt: synth.features(nn[nt], dims[nt], "bf16", 20 + i) for i, nt in enumerate(nn)}
+    torch.cuda.synchronize()
+    t_setup = time.time() - t0
+    cfg = ag.HeteroSamplingConfig(dict(zip(ets, fan)), seed=SAMPLER_SEED)
+    bs, per_step = 1024, BATCHES_PER_STEP
+    n_batches = (args.warmup + args.steps) * per_step
+    seeds = [synth.seed_batch(nn["user"], bs, SEEDS_SEED, b) for b in range(n_batches)]
+    loader = ag.HeteroNeighborLoader(g, cfg, "user", prefetch_depth=8, sampler_threads=args.threads)
+    row_bytes = {nt: dims[nt] * 2 + dims[nt] * 4 for nt in nn}
+
+    def run(first, count):
+        edges = rows_b = sub = got = 0
+        while got < count:
+            while sub < count and sub - got < 16:
+                loader.submit(first + sub, seeds[first + sub]); sub += 1
+            _, sg = loader.next_batch()
+            for nt in nn:
+                n_id = sg.nodes_t(nt)
+                if n_id.shape[0]:
+                    stores[nt].gather(n_id)
+                rows_b += int(n_id.shape[0]) * row_bytes[nt]
+            edges += int(sg._c.total_edges)
+            got += 1
+        return edges, rows_b
+
+    run(0, args.warmup * per_step)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    edges, gbytes = run(args.warmup * per_step, args.steps * per_step)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    loader.shutdown()
+    # CPU restatement on the same relations (reverse relation = transpose of the stored one)
+    threads = cpu_threads()
+    names = list(nn)
+    rels = []
+    for (s, r, d) in ets[:3]:
+        off, dd = host_rel[r]
+        rels.append((names.index(s), names.index(d), off, dd))
+    for (s, r, d) in ets[3:]:
+        off, dd = host_rel[r[4:]]
+        t_off, t_src = ago.transpose(off, dd, nn[d], nn[s])
+        rels.append((names.index(s), names.index(d), t_off, t_src))
+    o = ago.HeteroSampler([nn[k] for k in names], rels, fan, seed=SAMPLER_SEED)
+    ok, cpu_edges, t_cpu = True, 0, time.time()
+    nb_cpu = 0
+    while time.time() - t_cpu < 6.0 and nb_cpu < n_batches:
+        o.reseed(ago.batch_seed(SAMPLER_SEED, nb_cpu))
+        want = o.sample(0, seeds[nb_cpu])
+        cpu_edges += sum(len(x) for x in want["edge_src_local"])
+        nb_cpu += 1
+    t_cpu = time.time() - t_cpu
+    # parity of batch 0 at this scale, bit for bit
+    s1 = ag.HeteroNeighborSampler(g, ag.HeteroSamplingConfig(dict(zip(ets, fan)), seed=ago.batch_seed(SAMPLER_SEED, 0)))
+    got = s1.sample("user", seeds[0]).raw_u32()
+    o.reseed(ago.batch_seed(SAMPLER_SEED, 0))
+    want = o.sample(0, seeds[0])
+    for k in ("nodes", "edge_src_local", "edge_dst_local"):
+        ok = ok and all(np.array_equal(a, b) for a, b in zip(got[k], want[k]))
+    line = {
+        "metric": METRIC, "value": edges / (ms * 1e-3), "unit": "edges/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms / max(args.steps, 1), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "u32 ids / bf16->f32", "data": "synthetic (per-relation R-MAT generated in HBM)",
+        "config": {"workload": hw["label"], "batches_per_step": per_step, "sampler_threads": args.threads,
+                   "fanout": {"/".join(et): f for et, f in zip(ets, fan)}},
+        "gather_gbs": gbytes / (ms * 1e-3) / 1e9, "edges_per_step": edges / max(args.steps, 1), "setup_s": round(t_setup, 1),
+        "cpu_baseline": {"value": cpu_edges / t_cpu, "unit": "edges/s", "cores": 1, "kind": "port",
+                         "sample": f"{nb_cpu} batches, one thread, sampling only, {t_cpu:.1f} s", "host": host_description()},
+        "parity_full_scale": bool(ok),
+    }
+    print(json.dumps(line), flush=True)
+
+
 def cpu_baseline(g, feats, w, cfg):
     """Times the CPU restatement on a bounded sample of the same workload (graph and
     features copied back from the GPU) and checks two full-size batches bit for bit."""
@@ -588,7 +705,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--workload", default=os.environ.get("AG_BENCH_WORKLOAD", "c2"), choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=os.environ.get("AG_BENCH_WORKLOAD", "c2"),
+                    choices=sorted(WORKLOADS) + sorted(HETERO))
     ap.add_argument("--threads", type=int, default=int(os.environ.get("AG_BENCH_THREADS", "3")),
                     help="loader worker threads, each with its own CUDA stream")
     ap.add_argument("--depth", type=int, default=0, help="prefetch depth (0: max(8, group / 2))")
@@ -602,6 +720,8 @@ def main():
                     help="run the resident (C ABI) leg only: no e2e, no CPU baseline (profiling runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
+    if args.workload in HETERO:
+        return run_hetero(args, HETERO[args.workload])
     w = WORKLOADS[args.workload]
     if args.impl == "reference":
         run_reference(args, w)
