@@ -76,7 +76,8 @@ AG_MAX_NODE_TYPES, AG_MAX_EDGE_TYPES = 8, 16
 class HeteroBuffers(C.Structure):
     _fields_ = [("cap_nodes", C.c_uint64), ("cap_edges", C.c_uint64), ("cap_seeds", C.c_uint64)] + \
                [(n, C.c_void_p) for n in ("nodes", "edge_src_local", "edge_dst_local", "seed_indices",
-                                          "n_id", "edge_index_local", "seed_index")]
+                                          "n_id", "edge_index_local", "seed_index")] + \
+               [("x", C.c_void_p * AG_MAX_NODE_TYPES)]
 
 
 class HeteroCounts(C.Structure):
@@ -147,6 +148,9 @@ SIGNATURES = {
     "ag_hetero_in_adjacency": (C.c_int32, [_P, C.c_uint32, _P, _P]),
     "ag_hetero_free": (None, [_P]),
     "ag_hetero_sampler_create": (C.c_int32, [_P, _P, C.c_uint32, C.c_int32, C.c_uint64, C.c_int32, _PP]),
+    "ag_hetero_sampler_create_group": (C.c_int32, [_P, _P, C.c_uint32, C.c_int32, C.c_uint64, C.c_int32, C.c_uint32, _PP]),
+    "ag_hetero_sample_group_into": (C.c_int32, [_P, C.c_uint32, C.c_uint32, _P, _P, _P, _P, _P, _P]),
+    "ag_hetero_sample_group_wait": (C.c_int32, [_P, _P, _I32P]),
     "ag_hetero_sampler_reseed": (C.c_int32, [_P, C.c_uint64]),
     "ag_hetero_sampler_bounds": (C.c_int32, [_P, C.c_uint64, _U64P, _U64P]),
     "ag_hetero_sample_into": (C.c_int32, [_P, C.c_uint32, _P, C.c_uint64, C.POINTER(HeteroBuffers), _P]),

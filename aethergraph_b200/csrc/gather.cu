@@ -119,6 +119,7 @@ k_gather_vec(GatherArgs a, const GatherArgs *__restrict__ group) {
     if (group) a = group[blockIdx.y];  // one batch of a group per grid row
     if (!a.payload) return;
     const uint64_t n = a.n_dev ? min((uint64_t)*a.n_dev, a.n) : a.n;
+    if (a.ids_off) a.ids = (const uint32_t *)a.ids + *a.ids_off;  // a segment of a longer id array
     const int lane = threadIdx.x % LPR;
     const int sub = threadIdx.x / LPR;
     const uint32_t vecs = a.row_bytes >> 4;
@@ -170,6 +171,7 @@ k_gather_elem(GatherArgs a, const GatherArgs *__restrict__ group) {
     if (group) a = group[blockIdx.y];
     if (!a.payload) return;
     const uint64_t n = a.n_dev ? min((uint64_t)*a.n_dev, a.n) : a.n;
+    if (a.ids_off) a.ids = (const uint32_t *)a.ids + *a.ids_off;
     const uint64_t total = n * a.dim;
     for (uint64_t g = (uint64_t)blockIdx.x * kThreads + threadIdx.x; g < total;
          g += (uint64_t)gridDim.x * kThreads) {

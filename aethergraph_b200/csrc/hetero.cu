@@ -68,7 +68,11 @@ struct HParams {
     uint32_t *edge_rank;    // rank within its edge type
     uint64_t cap_nodes, cap_edges;
     uint32_t *class_tiles;  // descriptors of the class-rank scans
+    uint32_t class_epoch;   // the node scan runs under class_epoch, the edge scan under class_epoch + 1
+    uint32_t *class_ticket;
     uint32_t *type_count, *et_count;  // totals per node type / edge type (device)
+    uint32_t *type_start;   // first position of each node type's segment in `nodes`
+    int reset_pos;          // 1: the batch's RNG stream starts at draw 0
     // outputs
     uint32_t *nodes, *edge_src_local, *edge_dst_local, *seed_indices;
     int64_t *n_id, *edge_index_local, *seed_index;
@@ -96,7 +100,10 @@ __device__ __forceinline__ void in_row(const HeteroMeta &m, uint32_t et, uint32_
     if (b > m.in_edges[et]) deg = 0;
 }
 
-__global__ void k_het_insert_seeds(HParams p) {
+// Every kernel's grid has the batch as blockIdx.y; the group's parameter blocks
+// sit in one device array.
+__global__ void k_het_insert_seeds(const HParams *__restrict__ pa) {
+    const HParams &p = pa[blockIdx.y];
     const HeteroMeta &m = *p.meta;
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= p.n_seeds) return;
@@ -113,18 +120,19 @@ __global__ void k_het_insert_seeds(HParams p) {
 // Same single-pass scan as the homogeneous assign; the demand of a new node is
 // the sum over the edge types into its type.
 __global__ void __launch_bounds__(kTile)
-k_het_assign(HParams p, uint32_t stage, int has_next) {
+k_het_assign(const HParams *__restrict__ pa, uint32_t stage, int has_next) {
     __shared__ uint32_t s_tile;
     __shared__ ScanVal s_warp[kTile / 32];
     __shared__ ScanVal s_prefix;
+    const HParams &p = pa[blockIdx.y];
     const HeteroMeta &m = *p.meta;
     BatchState *bs = p.state;
     StageInfo si = bs->stage[stage];
     if (stage == 0) {
-        // The handle's stream continues where its previous batch stopped; a
-        // reseed zeroes stream_pos before the launch.
+        // A reseeded batch restarts its stream at draw 0; otherwise the handle's
+        // stream continues where its previous batch stopped.
         si = StageInfo{};
-        si.draws = bs->stream_pos;
+        si.draws = p.reset_pos ? 0ull : bs->stream_pos;
     }
     const uint32_t count = (stage == 0) ? p.n_seeds : si.hop_edges;
     const uint32_t n_tiles = max(1u, (count + kTile - 1) / kTile);
@@ -234,7 +242,8 @@ k_het_assign(HParams p, uint32_t stage, int has_next) {
 // edge type id, the lanes reproduce take-all / Floyd / replace
 // (hetero_sampler.rs:364-422) and emit the edges at consecutive slots.
 __global__ void __launch_bounds__(kPickThreads)
-k_het_pick(HParams p, uint32_t hop) {
+k_het_pick(const HParams *__restrict__ pa, uint32_t hop) {
+    const HParams &p = pa[blockIdx.y];
     const HeteroMeta &m = *p.meta;
     const StageInfo nx = p.state->stage[hop + 1];
     const int lane = threadIdx.x & 31;
@@ -301,12 +310,18 @@ constexpr int kClassThreads = 256;
 constexpr int kDescWords = 1 + 2 * kChan;
 
 __global__ void __launch_bounds__(kClassThreads)
-k_class_rank(const uint8_t *__restrict__ tags, const uint32_t *n_ptr, uint32_t n_cap, uint32_t *ranks,
-             uint32_t *totals, uint32_t *tiles, uint32_t epoch, uint32_t *ticket, uint32_t *err) {
+k_class_rank(const HParams *__restrict__ pa, int edges) {
     __shared__ uint32_t s_tile;
     __shared__ uint32_t s_cnt[kClassThreads / 32][kChan];   // per warp, per channel: count within the tile
     __shared__ uint32_t s_base[kChan];                      // exclusive prefix of the tile per channel
-    const uint32_t n = min(*n_ptr, n_cap);
+    const HParams &p = pa[blockIdx.y];
+    const StageInfo fin = p.state->stage[p.meta->num_hops + 1];
+    const uint8_t *__restrict__ tags = edges ? p.edge_tag : p.node_tag;
+    uint32_t *ranks = edges ? p.edge_rank : p.node_rank;
+    uint32_t *totals = edges ? p.et_count : p.type_count;
+    uint32_t *tiles = p.class_tiles, *ticket = p.class_ticket, *err = &p.state->error;
+    const uint32_t epoch = p.class_epoch + (edges ? 1u : 0u);
+    const uint32_t n = edges ? (uint32_t)min((uint64_t)fin.n_edges, p.cap_edges) : (uint32_t)min((uint64_t)fin.n_nodes, p.cap_nodes);
     const uint32_t n_tiles = max(1u, (n + kClassTile - 1) / kClassTile);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (;;) {
@@ -402,7 +417,8 @@ k_class_rank(const uint8_t *__restrict__ tags, const uint32_t *n_ptr, uint32_t n
 
 // Per-type arrays out of the global ones.  Segments: node type t starts at the
 // sum of the counts of the types before it; edge type likewise.
-__global__ void k_het_scatter(HParams p) {
+__global__ void k_het_scatter(const HParams *__restrict__ pa) {
+    const HParams &p = pa[blockIdx.y];
     const HeteroMeta &m = *p.meta;
     BatchState *bs = p.state;
     const StageInfo fin = bs->stage[m.num_hops + 1];
@@ -414,6 +430,7 @@ __global__ void k_het_scatter(HParams p) {
         for (uint32_t t = 0; t < kChan; ++t) { s_toff[t] = a; a += (t < m.nt) ? p.type_count[t] : 0; }
         for (uint32_t t = 0; t < kChan; ++t) { s_eoff[t] = b; b += (t < m.et) ? p.et_count[t] : 0; }
         s_toff[kChan] = a; s_eoff[kChan] = b;
+        if (blockIdx.x == 0) for (uint32_t t = 0; t < kChan; ++t) p.type_start[t] = s_toff[t];  // for the gathers
     }
     __syncthreads();
     const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (uint64_t)gridDim.x * blockDim.x;
@@ -513,12 +530,15 @@ struct ag_hetero_graph {
 struct ag_hetero_sampler {
     const ag_hetero_graph *g = nullptr;
     int device = 0;
+    uint32_t group = 1;
     HeteroMeta meta{};
     HeteroMeta *meta_dev = nullptr;
     uint64_t seed = 0;
     bool reset_pos = true, dirty = true, in_flight = false;
-    uint32_t epoch = 0, gen = 0, class_epoch = 0;
-    uint64_t cap_seeds = 0, max_nodes = 0, max_edges = 0, max_hop_edges = 0, max_frontier = 0, table_cap = 0, n_tiles = 0;
+    uint32_t epoch = 0, gen = 0, class_epoch = 0, last_batches = 0;
+    uint64_t cap_seeds = 0, max_nodes = 0, max_edges = 0, max_hop_edges = 0, max_frontier = 0, table_cap = 0, n_tiles = 0,
+             class_tiles_n = 0;
+    // scratch, each array x group
     uint64_t *table = nullptr;
     uint32_t *slot_of_seed = nullptr, *slot_of_edge = nullptr, *node_key = nullptr, *node_rank = nullptr,
              *edge_exp = nullptr, *edge_rank = nullptr, *class_tiles = nullptr, *class_misc = nullptr, *seeds_dev = nullptr;
@@ -526,11 +546,14 @@ struct ag_hetero_sampler {
     FrontierEntry *frontier = nullptr;
     TileDesc *tiles = nullptr;
     BatchState *state = nullptr;
+    HParams *params_dev = nullptr, *params_host = nullptr;
+    GatherArgs *gather_dev = nullptr, *gather_host = nullptr;  // [node type][batch]
     ag_hetero_counts *counts_dev = nullptr, *counts_host = nullptr;
     uint32_t *seeds_pinned = nullptr;
     cudaEvent_t done = nullptr;
-    uint32_t seed_type = 0;
 };
+
+constexpr int kMiscWords = 3 * kChan + 2;  // type_count, et_count, type_start, ticket (per batch)
 
 extern "C" void ag_hetero_free(ag_hetero_graph *h) {
     if (!h) return;
@@ -637,6 +660,16 @@ extern "C" int32_t ag_hetero_in_adjacency(const ag_hetero_graph *h, uint32_t edg
 
 namespace {
 
+uint64_t het_per_node(const HeteroMeta &m, uint32_t hop) {
+    uint64_t per_node = 0;  // most edges any node can emit at this hop
+    for (uint32_t t = 0; t < m.nt; ++t) {
+        uint64_t k = 0;
+        for (uint32_t i = 0; i < m.in_count[t]; ++i) k += m.fanout[m.in_list[t][i]][hop];
+        per_node = std::max(per_node, k);
+    }
+    return per_node;
+}
+
 void het_bounds(const ag_hetero_sampler *s, uint64_t n_seeds, uint64_t *nodes, uint64_t *edges, uint64_t *hop_edges,
                 uint64_t *frontier) {
     const HeteroMeta &m = s->meta;
@@ -644,13 +677,7 @@ void het_bounds(const ag_hetero_sampler *s, uint64_t n_seeds, uint64_t *nodes, u
     for (uint32_t t = 0; t < m.nt; ++t) total += m.type_nodes[t];
     uint64_t f = std::min<uint64_t>(n_seeds, total), n = f, e = 0, mhe = 0, mf = f;
     for (uint32_t h = 0; h < m.num_hops; ++h) {
-        uint64_t per_node = 0;  // most edges any node can emit at this hop
-        for (uint32_t t = 0; t < m.nt; ++t) {
-            uint64_t k = 0;
-            for (uint32_t i = 0; i < m.in_count[t]; ++i) k += m.fanout[m.in_list[t][i]][h];
-            per_node = std::max(per_node, k);
-        }
-        const uint64_t he = f * per_node;
+        const uint64_t he = f * het_per_node(m, h);
         e += he; mhe = std::max(mhe, he);
         f = std::min<uint64_t>(he, total);
         if (h + 1 < m.num_hops) mf = std::max(mf, f);
@@ -672,12 +699,13 @@ void het_free_scratch(ag_hetero_sampler *s) {
     s->seeds_pinned = nullptr;
 }
 
+// Scratch for `group` batches of up to n_seeds seeds each.
 int32_t het_ensure(ag_hetero_sampler *s, uint64_t n_seeds) {
     if (n_seeds <= s->cap_seeds && s->table) return AG_OK;
-    if (s->in_flight) AG_CUDA(cudaEventSynchronize(s->done));
+    if (s->in_flight) { AG_CUDA(cudaEventSynchronize(s->done)); s->in_flight = false; }
     het_free_scratch(s);
     s->cap_seeds = 0;
-    const uint64_t cap = std::max<uint64_t>(n_seeds, 1);
+    const uint64_t cap = std::max<uint64_t>(n_seeds, 1), G = s->group;
     het_bounds(s, cap, &s->max_nodes, &s->max_edges, &s->max_hop_edges, &s->max_frontier);
     if (s->max_nodes >= kMaxPos || s->max_hop_edges >= kMaxPos || cap >= kMaxPos || s->max_edges >= 0xFFFFFFFFull)
         return fail(AG_ERR_VALUE, "batch too large: %llu seeds with these fanouts can reach %llu nodes and %llu edges in a hop "
@@ -685,24 +713,24 @@ int32_t het_ensure(ag_hetero_sampler *s, uint64_t n_seeds) {
                     (unsigned long long)s->max_hop_edges, (unsigned long long)kMaxPos - 1);
     const uint64_t cn = std::max<uint64_t>(s->max_nodes, 1), ce = std::max<uint64_t>(s->max_edges, 1);
     s->table_cap = std::max<uint64_t>(1024, next_pow2(2 * s->max_nodes));
-    AG_CUDA(cudaMalloc(&s->table, s->table_cap * 8));
-    AG_CUDA(cudaMalloc(&s->slot_of_seed, cap * 4));
-    AG_CUDA(cudaMalloc(&s->slot_of_edge, ce * 4));
-    AG_CUDA(cudaMalloc(&s->node_key, cn * 4));
-    AG_CUDA(cudaMalloc(&s->node_rank, cn * 4));
-    AG_CUDA(cudaMalloc(&s->node_tag, cn));
-    AG_CUDA(cudaMalloc(&s->edge_exp, ce * 4));
-    AG_CUDA(cudaMalloc(&s->edge_rank, ce * 4));
-    AG_CUDA(cudaMalloc(&s->edge_tag, ce));
-    AG_CUDA(cudaMalloc(&s->frontier, std::max<uint64_t>(s->max_frontier, 1) * sizeof(FrontierEntry)));
+    AG_CUDA(cudaMalloc(&s->table, G * s->table_cap * 8));
+    AG_CUDA(cudaMalloc(&s->slot_of_seed, G * cap * 4));
+    AG_CUDA(cudaMalloc(&s->slot_of_edge, G * ce * 4));
+    AG_CUDA(cudaMalloc(&s->node_key, G * cn * 4));
+    AG_CUDA(cudaMalloc(&s->node_rank, G * cn * 4));
+    AG_CUDA(cudaMalloc(&s->node_tag, G * cn));
+    AG_CUDA(cudaMalloc(&s->edge_exp, G * ce * 4));
+    AG_CUDA(cudaMalloc(&s->edge_rank, G * ce * 4));
+    AG_CUDA(cudaMalloc(&s->edge_tag, G * ce));
+    AG_CUDA(cudaMalloc(&s->frontier, G * std::max<uint64_t>(s->max_frontier, 1) * sizeof(FrontierEntry)));
     s->n_tiles = std::max<uint64_t>(std::max(cap, s->max_hop_edges) / kTile + 2, 2);
-    AG_CUDA(cudaMalloc(&s->tiles, s->n_tiles * sizeof(TileDesc)));
-    AG_CUDA(cudaMemset(s->tiles, 0, s->n_tiles * sizeof(TileDesc)));
-    const uint64_t ctiles = std::max(cn, ce) / kClassTile + 2;
-    AG_CUDA(cudaMalloc(&s->class_tiles, ctiles * kDescWords * 4));
-    AG_CUDA(cudaMemset(s->class_tiles, 0, ctiles * kDescWords * 4));
-    AG_CUDA(cudaMalloc(&s->seeds_dev, cap * 4));
-    AG_CUDA(cudaHostAlloc(&s->seeds_pinned, cap * 4, cudaHostAllocDefault));
+    AG_CUDA(cudaMalloc(&s->tiles, G * s->n_tiles * sizeof(TileDesc)));
+    AG_CUDA(cudaMemset(s->tiles, 0, G * s->n_tiles * sizeof(TileDesc)));
+    s->class_tiles_n = std::max(cn, ce) / kClassTile + 2;
+    AG_CUDA(cudaMalloc(&s->class_tiles, G * s->class_tiles_n * kDescWords * 4));
+    AG_CUDA(cudaMemset(s->class_tiles, 0, G * s->class_tiles_n * kDescWords * 4));
+    AG_CUDA(cudaMalloc(&s->seeds_dev, G * cap * 4));
+    AG_CUDA(cudaHostAlloc(&s->seeds_pinned, G * cap * 4, cudaHostAllocDefault));
     s->cap_seeds = cap; s->epoch = 0; s->class_epoch = 0; s->dirty = true;
     return AG_OK;
 }
@@ -715,6 +743,9 @@ extern "C" void ag_hetero_sampler_free(ag_hetero_sampler *s) {
     if (s->in_flight && s->done) cudaEventSynchronize(s->done);
     het_free_scratch(s);
     cudaFree(s->meta_dev); cudaFree(s->state); cudaFree(s->counts_dev); cudaFree(s->class_misc);
+    cudaFree(s->params_dev); cudaFree(s->gather_dev);
+    if (s->params_host) cudaFreeHost(s->params_host);
+    if (s->gather_host) cudaFreeHost(s->gather_host);
     if (s->counts_host) cudaFreeHost(s->counts_host);
     if (s->done) cudaEventDestroy(s->done);
     delete s;
@@ -722,11 +753,13 @@ extern "C" void ag_hetero_sampler_free(ag_hetero_sampler *s) {
 
 // fanout: [num_edge_types][num_hops] row-major (hetero_sampler.rs:32-33; the
 // Python mapping fills zeros for edge types left out, aethergraph-py/src/hetero.rs:309-328).
-extern "C" int32_t ag_hetero_sampler_create(const ag_hetero_graph *h, const uint32_t *fanout, uint32_t num_hops,
-                                            int32_t replace, uint64_t seed, int32_t rng_mode, ag_hetero_sampler **out) {
+extern "C" int32_t ag_hetero_sampler_create_group(const ag_hetero_graph *h, const uint32_t *fanout, uint32_t num_hops,
+                                                  int32_t replace, uint64_t seed, int32_t rng_mode, uint32_t group,
+                                                  ag_hetero_sampler **out) {
     if (!h || !fanout || !out) return fail(AG_ERR_VALUE, "ag_hetero_sampler_create: null argument");
     if (num_hops == 0 || num_hops > AG_MAX_HOPS)
         return fail(AG_ERR_VALUE, "between 1 and %d hops are supported (got %u)", AG_MAX_HOPS, num_hops);
+    if (group == 0 || group > 64) return fail(AG_ERR_VALUE, "group size must be between 1 and 64 (got %u)", group);
     if (rng_mode != AG_RNG_WYRAND_EXACT && rng_mode != AG_RNG_PHILOX) return fail(AG_ERR_VALUE, "unknown rng_mode %d", rng_mode);
     for (uint32_t e = 0; e < h->et; ++e)
         for (uint32_t k = 0; k < num_hops; ++k)
@@ -736,7 +769,7 @@ extern "C" int32_t ag_hetero_sampler_create(const ag_hetero_graph *h, const uint
     DeviceGuard guard(h->device);
     if (!guard.ok) return AG_ERR_CUDA;
     ag_hetero_sampler *s = new ag_hetero_sampler();
-    s->g = h; s->device = h->device; s->seed = seed;
+    s->g = h; s->device = h->device; s->seed = seed; s->group = group;
     HeteroMeta &m = s->meta;
     m.nt = h->nt; m.et = h->et; m.num_hops = num_hops; m.replace = replace ? 1 : 0; m.rng_mode = rng_mode;
     uint32_t base = 0;
@@ -751,12 +784,19 @@ extern "C" int32_t ag_hetero_sampler_create(const ag_hetero_graph *h, const uint
     }
     int32_t st = AG_OK;
     do {
+        const size_t G = group;
         if (cudaMalloc(&s->meta_dev, sizeof(HeteroMeta)) != cudaSuccess ||
             cudaMemcpy(s->meta_dev, &m, sizeof(HeteroMeta), cudaMemcpyHostToDevice) != cudaSuccess ||
-            cudaMalloc(&s->state, sizeof(BatchState)) != cudaSuccess || cudaMemset(s->state, 0, sizeof(BatchState)) != cudaSuccess ||
-            cudaMalloc(&s->counts_dev, sizeof(ag_hetero_counts)) != cudaSuccess ||
-            cudaMalloc(&s->class_misc, (2 * kChan + 2) * 4) != cudaSuccess || cudaMemset(s->class_misc, 0, (2 * kChan + 2) * 4) != cudaSuccess ||
-            cudaHostAlloc(&s->counts_host, sizeof(ag_hetero_counts), cudaHostAllocDefault) != cudaSuccess ||
+            cudaMalloc(&s->state, G * sizeof(BatchState)) != cudaSuccess ||
+            cudaMemset(s->state, 0, G * sizeof(BatchState)) != cudaSuccess ||
+            cudaMalloc(&s->counts_dev, G * sizeof(ag_hetero_counts)) != cudaSuccess ||
+            cudaMalloc(&s->class_misc, G * kMiscWords * 4) != cudaSuccess ||
+            cudaMemset(s->class_misc, 0, G * kMiscWords * 4) != cudaSuccess ||
+            cudaMalloc(&s->params_dev, G * sizeof(HParams)) != cudaSuccess ||
+            cudaMalloc(&s->gather_dev, G * kMaxNT * sizeof(GatherArgs)) != cudaSuccess ||
+            cudaHostAlloc(&s->params_host, G * sizeof(HParams), cudaHostAllocDefault) != cudaSuccess ||
+            cudaHostAlloc(&s->gather_host, G * kMaxNT * sizeof(GatherArgs), cudaHostAllocDefault) != cudaSuccess ||
+            cudaHostAlloc(&s->counts_host, G * sizeof(ag_hetero_counts), cudaHostAllocDefault) != cudaSuccess ||
             cudaEventCreateWithFlags(&s->done, cudaEventDisableTiming) != cudaSuccess) {
             st = fail(AG_ERR_CUDA, "hetero sampler allocation failed: %s", cudaGetErrorString(cudaGetLastError()));
             break;
@@ -766,6 +806,11 @@ extern "C" int32_t ag_hetero_sampler_create(const ag_hetero_graph *h, const uint
     if (st != AG_OK) { ag_hetero_sampler_free(s); return st; }
     *out = s;
     return AG_OK;
+}
+
+extern "C" int32_t ag_hetero_sampler_create(const ag_hetero_graph *h, const uint32_t *fanout, uint32_t num_hops,
+                                            int32_t replace, uint64_t seed, int32_t rng_mode, ag_hetero_sampler **out) {
+    return ag_hetero_sampler_create_group(h, fanout, num_hops, replace, seed, rng_mode, 1, out);
 }
 
 extern "C" int32_t ag_hetero_sampler_reseed(ag_hetero_sampler *s, uint64_t seed) {
@@ -780,114 +825,185 @@ extern "C" int32_t ag_hetero_sampler_bounds(const ag_hetero_sampler *s, uint64_t
     return AG_OK;
 }
 
-extern "C" int32_t ag_hetero_sample_into(ag_hetero_sampler *s, uint32_t seed_type, const uint32_t *seeds, uint64_t n_seeds,
-                                         ag_hetero_buffers *buf, void *stream) {
-    if (!s || !buf || (!seeds && n_seeds)) return fail(AG_ERR_VALUE, "ag_hetero_sample_into: null argument");
+// One launch chain for a group of batches rooted at the same node type.  With
+// batch_seeds, batch b starts its own RNG stream at draw 0 of batch_seeds[b]
+// (the loader's per-batch reseed, prefetch.rs:1003-1005); without (single batch
+// only) the handle's stream continues.  feats: NULL, or one feature store per
+// node type (entries may be NULL); node type t's rows are gathered into
+// bufs[b].x[t] in the order of its `nodes` segment.
+extern "C" int32_t ag_hetero_sample_group_into(ag_hetero_sampler *s, uint32_t n_batches, uint32_t seed_type,
+                                               const uint32_t *const *seeds, const uint64_t *n_seeds,
+                                               const uint64_t *batch_seeds, const ag_features *const *feats,
+                                               ag_hetero_buffers *bufs, void *stream) {
+    if (!s || !bufs || !seeds || !n_seeds) return fail(AG_ERR_VALUE, "ag_hetero_sample_group_into: null argument");
+    if (n_batches == 0 || n_batches > s->group)
+        return fail(AG_ERR_VALUE, "group of %u batches does not fit a sampler created for %u", n_batches, s->group);
+    if (!batch_seeds && n_batches > 1) return fail(AG_ERR_VALUE, "a group of several batches needs batch_seeds");
     const HeteroMeta &m = s->meta;
     if (seed_type >= m.nt) return fail(AG_ERR_VALUE, "unknown seed node type %u", seed_type);
-    if (!buf->nodes || !buf->edge_src_local || !buf->edge_dst_local || !buf->seed_indices)
-        return fail(AG_ERR_VALUE, "nodes, edge_src_local, edge_dst_local and seed_indices buffers are required");
-    if (buf->cap_seeds < n_seeds) return fail(AG_ERR_VALUE, "seed_indices capacity %llu < %llu seeds",
-                                              (unsigned long long)buf->cap_seeds, (unsigned long long)n_seeds);
-    // Seeds are checked against the seed type's node count (hetero_sampler.rs:174-187).
-    for (uint64_t i = 0; i < n_seeds; ++i)
-        if ((uint64_t)seeds[i] >= m.type_nodes[seed_type])
-            return fail(AG_ERR_SAMPLING, "seed node %u (position %llu) is out of range for %llu nodes",
-                        seeds[i], (unsigned long long)i, (unsigned long long)m.type_nodes[seed_type]);
+    uint64_t max_n = 0;
+    for (uint32_t b = 0; b < n_batches; ++b) {
+        const ag_hetero_buffers &B = bufs[b];
+        if (!seeds[b] && n_seeds[b]) return fail(AG_ERR_VALUE, "ag_hetero_sample_group_into: null seeds");
+        if (!B.nodes || !B.edge_src_local || !B.edge_dst_local || !B.seed_indices)
+            return fail(AG_ERR_VALUE, "nodes, edge_src_local, edge_dst_local and seed_indices buffers are required");
+        if (B.cap_seeds < n_seeds[b]) return fail(AG_ERR_VALUE, "seed_indices capacity %llu < %llu seeds",
+                                                  (unsigned long long)B.cap_seeds, (unsigned long long)n_seeds[b]);
+        // Seeds are checked against the seed type's node count (hetero_sampler.rs:174-187).
+        for (uint64_t i = 0; i < n_seeds[b]; ++i)
+            if ((uint64_t)seeds[b][i] >= m.type_nodes[seed_type])
+                return fail(AG_ERR_SAMPLING, "seed node %u (position %llu) is out of range for %llu nodes",
+                            seeds[b][i], (unsigned long long)i, (unsigned long long)m.type_nodes[seed_type]);
+        max_n = std::max(max_n, n_seeds[b]);
+    }
+    if (feats)
+        for (uint32_t t = 0; t < m.nt; ++t)
+            if (feats[t]) {
+                if (feats[t]->device != s->device) return fail(AG_ERR_VALUE, "feature store of node type %u lives on another device", t);
+                if (feats[t]->num_nodes < m.type_nodes[t]) return fail(AG_ERR_VALUE, "feature store of node type %u has too few rows", t);
+                if (feats[t]->row_stride != 1 && !feats[t]->shards) return fail(AG_ERR_VALUE, "a cyclic feature shard is read through a sharded view");
+            }
     DeviceGuard guard(s->device);
     if (!guard.ok) return AG_ERR_CUDA;
     cudaStream_t st = (cudaStream_t)stream;
     if (s->in_flight) { AG_CUDA(cudaEventSynchronize(s->done)); s->in_flight = false; }
-    AG_TRY(het_ensure(s, n_seeds));
-    if (s->dirty || s->gen >= kGens) { AG_CUDA(cudaMemsetAsync(s->table, 0xFF, s->table_cap * 8, st)); s->gen = 0; }
-    if (s->dirty) { AG_CUDA(cudaMemsetAsync(s->state, 0, sizeof(BatchState), st)); s->dirty = false; s->reset_pos = true; }
-    if (s->reset_pos) { AG_CUDA(cudaMemsetAsync(&s->state->stream_pos, 0, 8, st)); s->reset_pos = false; }
-    const uint32_t H = m.num_hops, n = (uint32_t)n_seeds;
-    if (s->epoch + (H + 2) > 0x3FFFFF00u) { AG_CUDA(cudaMemsetAsync(s->tiles, 0, s->n_tiles * sizeof(TileDesc), st)); s->epoch = 0; }
-    if (s->class_epoch + 2 > 0x3FFFFF00u) {
-        const uint64_t ctiles = std::max(std::max<uint64_t>(s->max_nodes, 1), std::max<uint64_t>(s->max_edges, 1)) / kClassTile + 2;
-        AG_CUDA(cudaMemsetAsync(s->class_tiles, 0, ctiles * kDescWords * 4, st));
+    AG_TRY(het_ensure(s, max_n));
+    const uint64_t G = s->group;
+    if (s->dirty || s->gen >= kGens) { AG_CUDA(cudaMemsetAsync(s->table, 0xFF, G * s->table_cap * 8, st)); s->gen = 0; }
+    if (s->dirty) { AG_CUDA(cudaMemsetAsync(s->state, 0, G * sizeof(BatchState), st)); s->dirty = false; s->reset_pos = true; }
+    const uint32_t H = m.num_hops;
+    if (s->epoch + (H + 2) > 0x3FFFFF00u) { AG_CUDA(cudaMemsetAsync(s->tiles, 0, G * s->n_tiles * sizeof(TileDesc), st)); s->epoch = 0; }
+    if (s->class_epoch + 4 > 0x3FFFFF00u) {
+        AG_CUDA(cudaMemsetAsync(s->class_tiles, 0, G * s->class_tiles_n * kDescWords * 4, st));
         s->class_epoch = 0;
-    }
-    if (n) {
-        memcpy(s->seeds_pinned, seeds, (size_t)n * 4);
-        AG_CUDA(cudaMemcpyAsync(s->seeds_dev, s->seeds_pinned, (size_t)n * 4, cudaMemcpyHostToDevice, st));
     }
     uint32_t log2cap = 0;
     while ((1ull << log2cap) < s->table_cap) ++log2cap;
-    HParams p{};
-    p.meta = s->meta_dev;
-    p.table = DedupTable{s->table, (uint32_t)(s->table_cap - 1), 32u - log2cap, s->gen};
-    p.state = s->state; p.tiles = s->tiles; p.epoch_base = s->epoch + 1;
-    p.n_seeds = n; p.seed_type = seed_type; p.seeds = s->seeds_dev; p.seed = s->seed;
-    p.slot_of_seed = s->slot_of_seed; p.slot_of_edge = s->slot_of_edge;
-    p.frontier = s->frontier; p.frontier_cap = std::max<uint64_t>(s->max_frontier, 1);
-    p.node_key = s->node_key; p.node_tag = s->node_tag; p.node_rank = s->node_rank;
-    p.edge_exp = s->edge_exp; p.edge_tag = s->edge_tag; p.edge_rank = s->edge_rank;
-    p.cap_nodes = std::min<uint64_t>(buf->cap_nodes, std::max<uint64_t>(s->max_nodes, 1));
-    p.cap_edges = std::min<uint64_t>(buf->cap_edges, std::max<uint64_t>(s->max_edges, 1));
-    p.class_tiles = s->class_tiles;
-    p.type_count = s->class_misc; p.et_count = s->class_misc + kChan;
-    p.nodes = buf->nodes; p.edge_src_local = buf->edge_src_local; p.edge_dst_local = buf->edge_dst_local;
-    p.seed_indices = buf->seed_indices; p.n_id = buf->n_id; p.edge_index_local = buf->edge_index_local;
-    p.seed_index = buf->seed_index; p.counts = s->counts_dev;
-    s->epoch += H + 2; s->gen += 1; s->seed_type = seed_type;
+    const uint64_t cn = std::max<uint64_t>(s->max_nodes, 1), ce = std::max<uint64_t>(s->max_edges, 1);
+    const uint64_t fcap = std::max<uint64_t>(s->max_frontier, 1);
+    bool want_x = false;
+    for (uint32_t b = 0; b < n_batches; ++b) {
+        const ag_hetero_buffers &B = bufs[b];
+        const uint32_t n = (uint32_t)n_seeds[b];
+        HParams p{};
+        p.meta = s->meta_dev;
+        p.table = DedupTable{s->table + b * s->table_cap, (uint32_t)(s->table_cap - 1), 32u - log2cap, s->gen};
+        p.state = s->state + b; p.tiles = s->tiles + b * s->n_tiles; p.epoch_base = s->epoch + 1;
+        p.n_seeds = n; p.seed_type = seed_type;
+        if (n) memcpy(s->seeds_pinned + b * s->cap_seeds, seeds[b], (size_t)n * 4);
+        p.seeds = s->seeds_dev + b * s->cap_seeds;
+        p.seed = batch_seeds ? batch_seeds[b] : s->seed;
+        p.reset_pos = (batch_seeds || s->reset_pos) ? 1 : 0;
+        p.slot_of_seed = s->slot_of_seed + b * s->cap_seeds; p.slot_of_edge = s->slot_of_edge + b * ce;
+        p.frontier = s->frontier + b * fcap; p.frontier_cap = fcap;
+        p.node_key = s->node_key + b * cn; p.node_tag = s->node_tag + b * cn; p.node_rank = s->node_rank + b * cn;
+        p.edge_exp = s->edge_exp + b * ce; p.edge_tag = s->edge_tag + b * ce; p.edge_rank = s->edge_rank + b * ce;
+        p.cap_nodes = std::min<uint64_t>(B.cap_nodes, cn);
+        p.cap_edges = std::min<uint64_t>(B.cap_edges, ce);
+        p.class_tiles = s->class_tiles + b * s->class_tiles_n * kDescWords;
+        p.class_epoch = s->class_epoch + 1;
+        uint32_t *misc = s->class_misc + b * kMiscWords;
+        p.type_count = misc; p.et_count = misc + kChan; p.type_start = misc + 2 * kChan; p.class_ticket = misc + 3 * kChan;
+        p.nodes = B.nodes; p.edge_src_local = B.edge_src_local; p.edge_dst_local = B.edge_dst_local;
+        p.seed_indices = B.seed_indices; p.n_id = B.n_id; p.edge_index_local = B.edge_index_local;
+        p.seed_index = B.seed_index; p.counts = s->counts_dev + b;
+        s->params_host[b] = p;
+        for (uint32_t t = 0; t < m.nt; ++t) {
+            GatherArgs ga{};
+            if (feats && feats[t] && B.x[t]) {
+                set_gather_source(ga, feats[t]);
+                ga.ids = B.nodes; ga.ids64 = 0; ga.ids_off = p.type_start + t;
+                ga.n = std::min<uint64_t>(p.cap_nodes, m.type_nodes[t]);
+                ga.n_dev = p.type_count + t;
+                ga.out = B.x[t];
+                want_x = true;
+            }
+            s->gather_host[(size_t)t * G + b] = ga;
+        }
+    }
+    s->reset_pos = false;
+    s->epoch += H + 2; s->class_epoch += 2; s->gen += 1; s->last_batches = n_batches;
+    AG_CUDA(cudaMemcpyAsync(s->seeds_dev, s->seeds_pinned, (uint64_t)n_batches * s->cap_seeds * 4, cudaMemcpyHostToDevice, st));
+    AG_CUDA(cudaMemcpyAsync(s->params_dev, s->params_host, n_batches * sizeof(HParams), cudaMemcpyHostToDevice, st));
+    if (want_x) AG_CUDA(cudaMemcpyAsync(s->gather_dev, s->gather_host, G * kMaxNT * sizeof(GatherArgs), cudaMemcpyHostToDevice, st));
 
+    const HParams *pa = s->params_dev;
+    const uint32_t nmax = (uint32_t)max_n, nb = n_batches;
     auto tiles_for = [&](uint64_t items) {
-        return (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>((items + kTile - 1) / kTile, (uint64_t)kSMs * 4));
+        return (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>((items + kTile - 1) / kTile, std::max<uint64_t>(1, (uint64_t)kSMs * 8 / nb)));
     };
-    if (n) k_het_insert_seeds<<<(n + 255) / 256, 256, 0, st>>>(p);
-    uint64_t f_bound = n, items = n;
+    if (nmax) k_het_insert_seeds<<<dim3((nmax + 255) / 256, nb), 256, 0, st>>>(pa);
+    uint64_t f_bound = nmax, items = nmax;
     for (uint32_t stage = 0; stage <= H; ++stage) {
         const bool has_next = stage < H;
-        k_het_assign<<<tiles_for(items), kTile, 0, st>>>(p, stage, has_next ? 1 : 0);
+        k_het_assign<<<dim3(tiles_for(items), nb), kTile, 0, st>>>(pa, stage, has_next ? 1 : 0);
         if (has_next) {
-            const uint32_t blocks = (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>((f_bound * 32 + kPickThreads - 1) / kPickThreads, (uint64_t)kSMs * 16));
-            k_het_pick<<<blocks, kPickThreads, 0, st>>>(p, stage);
-            uint64_t per_node = 0;
-            for (uint32_t t = 0; t < m.nt; ++t) {
-                uint64_t k = 0;
-                for (uint32_t i = 0; i < m.in_count[t]; ++i) k += m.fanout[m.in_list[t][i]][stage];
-                per_node = std::max(per_node, k);
-            }
-            items = f_bound * per_node;
+            const uint32_t blocks = (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>((f_bound * 32 + kPickThreads - 1) / kPickThreads,
+                                                                                      std::max<uint64_t>(1, (uint64_t)kSMs * 16 / nb)));
+            k_het_pick<<<dim3(blocks, nb), kPickThreads, 0, st>>>(pa, stage);
+            items = f_bound * het_per_node(m, stage);
             f_bound = std::min<uint64_t>(items, s->max_nodes);
         }
     }
-    // per-type local ids and per-edge-type positions
-    uint32_t *ticket = s->class_misc + 2 * kChan;
-    const uint32_t *n_nodes_dev = &s->state->stage[H + 1].n_nodes, *n_edges_dev = &s->state->stage[H + 1].n_edges;
-    auto ctiles_for = [&](uint64_t items_) {
-        return (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>((items_ + kClassTile - 1) / kClassTile, (uint64_t)kSMs * 4));
+    auto ctiles_for = [&](uint64_t n) {
+        return (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>((n + kClassTile - 1) / kClassTile, std::max<uint64_t>(1, (uint64_t)kSMs * 4 / nb)));
     };
-    k_class_rank<<<ctiles_for(s->max_nodes), kClassThreads, 0, st>>>(s->node_tag, n_nodes_dev, (uint32_t)p.cap_nodes, s->node_rank,
-                                                                     p.type_count, s->class_tiles, ++s->class_epoch, ticket, &s->state->error);
-    k_class_rank<<<ctiles_for(s->max_edges), kClassThreads, 0, st>>>(s->edge_tag, n_edges_dev, (uint32_t)p.cap_edges, s->edge_rank,
-                                                                     p.et_count, s->class_tiles, ++s->class_epoch, ticket, &s->state->error);
+    k_class_rank<<<dim3(ctiles_for(s->max_nodes), nb), kClassThreads, 0, st>>>(pa, 0);
+    k_class_rank<<<dim3(ctiles_for(s->max_edges), nb), kClassThreads, 0, st>>>(pa, 1);
     {
-        const uint64_t work = std::max<uint64_t>(std::max(s->max_edges, s->max_nodes), std::max<uint64_t>(n, 1));
-        k_het_scatter<<<(uint32_t)std::min<uint64_t>((work + 255) / 256, (uint64_t)kSMs * 8), 256, 0, st>>>(p);
+        const uint64_t work = std::max<uint64_t>(std::max(s->max_edges, s->max_nodes), std::max<uint64_t>(nmax, 1));
+        const uint32_t fx = (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>((work + 255) / 256, std::max<uint64_t>(1, (uint64_t)kSMs * 8 / nb)));
+        k_het_scatter<<<dim3(fx, nb), 256, 0, st>>>(pa);
     }
     AG_CUDA(cudaGetLastError());
-    AG_CUDA(cudaMemcpyAsync(s->counts_host, s->counts_dev, sizeof(ag_hetero_counts), cudaMemcpyDeviceToHost, st));
+    if (want_x) {
+        for (uint32_t t = 0; t < m.nt; ++t) {
+            if (!feats[t]) continue;
+            bool any = false, aligned = ((uintptr_t)feats[t]->payload % 16) == 0;
+            for (uint32_t b = 0; b < nb; ++b)
+                if (bufs[b].x[t]) { any = true; aligned = aligned && ((uintptr_t)bufs[b].x[t] % 16) == 0; }
+            if (!any) continue;
+            const uint64_t bound = std::min<uint64_t>(s->max_nodes, m.type_nodes[t]);
+            AG_CUDA(launch_gather_group(s->gather_dev + (size_t)t * G, nb, (uint32_t)(feats[t]->dim * elem_size(feats[t]->dtype)),
+                                        (uint32_t)feats[t]->dim, std::max<uint64_t>(bound / 4, 1), aligned, feats[t]->dtype,
+                                        feats[t]->shards != nullptr, st));
+        }
+    }
+    AG_CUDA(cudaMemcpyAsync(s->counts_host, s->counts_dev, nb * sizeof(ag_hetero_counts), cudaMemcpyDeviceToHost, st));
     AG_CUDA(cudaEventRecord(s->done, st));
     s->in_flight = true;
     return AG_OK;
 }
 
-extern "C" int32_t ag_hetero_sample_wait(ag_hetero_sampler *s, ag_hetero_counts *counts) {
-    if (!s) return fail(AG_ERR_VALUE, "ag_hetero_sample_wait: null sampler");
-    if (!s->in_flight) return fail(AG_ERR_VALUE, "ag_hetero_sample_wait: no batch in flight");
+extern "C" int32_t ag_hetero_sample_group_wait(ag_hetero_sampler *s, ag_hetero_counts *counts, int32_t *statuses) {
+    if (!s) return fail(AG_ERR_VALUE, "ag_hetero_sample_group_wait: null sampler");
+    if (!s->in_flight) return fail(AG_ERR_VALUE, "ag_hetero_sample_group_wait: no batch in flight");
     DeviceGuard guard(s->device);
     if (!guard.ok) return AG_ERR_CUDA;
     const cudaError_t e = cudaEventSynchronize(s->done);
     s->in_flight = false;
     if (e != cudaSuccess) { s->dirty = true; return fail(AG_ERR_CUDA, "hetero sampling kernels failed: %s", cudaGetErrorString(e)); }
-    const ag_hetero_counts c = *s->counts_host;
-    if (counts) *counts = c;
-    if (c.error & (kErrSpinTimeout | kErrTableFull)) s->dirty = true;
-    if (c.error & kErrBadSeed) return fail(AG_ERR_SAMPLING, "a seed node is out of range for its node type");
-    if (c.error & kErrCapacity) return fail(AG_ERR_VALUE, "output buffers too small for the sampled subgraph");
-    if (c.error) return fail(AG_ERR_WORKER, "hetero sampler kernels reported error bits 0x%x", c.error);
-    return AG_OK;
+    int32_t first = AG_OK;
+    for (uint32_t b = 0; b < s->last_batches; ++b) {
+        const ag_hetero_counts c = s->counts_host[b];
+        if (counts) counts[b] = c;
+        int32_t st = AG_OK;
+        if (c.error & (kErrSpinTimeout | kErrTableFull)) s->dirty = true;
+        if (c.error & kErrBadSeed) st = fail(AG_ERR_SAMPLING, "a seed node is out of range for its node type");
+        else if (c.error & kErrCapacity) st = fail(AG_ERR_VALUE, "output buffers too small for the sampled subgraph");
+        else if (c.error & kErrBadId) st = fail(AG_ERR_VALUE, "a gathered node id is outside its feature store");
+        else if (c.error) st = fail(AG_ERR_WORKER, "hetero sampler kernels reported error bits 0x%x", c.error);
+        if (statuses) statuses[b] = st;
+        if (st != AG_OK && first == AG_OK) first = st;
+    }
+    return first;
+}
+
+extern "C" int32_t ag_hetero_sample_into(ag_hetero_sampler *s, uint32_t seed_type, const uint32_t *seeds, uint64_t n_seeds,
+                                         ag_hetero_buffers *buf, void *stream) {
+    return ag_hetero_sample_group_into(s, 1, seed_type, &seeds, &n_seeds, nullptr, nullptr, buf, stream);
+}
+
+extern "C" int32_t ag_hetero_sample_wait(ag_hetero_sampler *s, ag_hetero_counts *counts) {
+    return ag_hetero_sample_group_wait(s, counts, nullptr);
 }

@@ -58,6 +58,7 @@ struct GatherArgs {
     float *out;
     uint32_t *err;
     const ag_shard_table *shards;  // non-null: rows are looked up through the shard table
+    const uint32_t *ids_off;       // non-null (u32 ids only): the ids start at ids + *ids_off (device value)
 };
 
 // The source half of a gather's arguments, from a feature store handle.

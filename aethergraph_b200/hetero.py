@@ -224,8 +224,9 @@ class HeteroSampledSubgraph:
     fresh host numpy arrays (crates/aethergraph-py/src/hetero.rs:349-470)."""
 
     def __init__(self, graph: HeteroCsrGraph, seed_type: int, seeds: np.ndarray, counts: _lib.HeteroCounts,
-                 bufs: _lib.HeteroBuffers, owner):
+                 bufs: _lib.HeteroBuffers, owner, dims=None):
         self._g, self._seed_type, self._seeds, self._c, self._b, self._owner = graph, seed_type, seeds, counts, bufs, owner
+        self._dims = dims or [0] * len(graph._node_types)
         self._n = [int(counts.nodes[t]) for t in range(len(graph._node_types))]
         self._e = [int(counts.edges[e]) for e in range(len(graph._edge_types))]
         self._n_start = np.concatenate([[0], np.cumsum(self._n)]).astype(np.int64)
@@ -287,6 +288,19 @@ class HeteroSampledSubgraph:
         return torch.as_tensor(_DevArray(self._b.n_id + 8 * int(self._n_start[t]), (self._n[t],), "<i8", self._owner),
                                device=self._dev())
 
+    def x_t(self, node_type: str):
+        """float32 CUDA tensor [num nodes of the type, dim]: the feature rows of
+        `nodes(node_type)`, gathered in the sampling launch chain; None when the
+        sampler was built without a feature store for this type."""
+        import torch
+
+        t = self._nt(node_type)
+        if not self._dims[t] or not self._b.x[t]:
+            return None
+        if not self._n[t]:
+            return torch.empty((0, self._dims[t]), dtype=torch.float32, device=self._dev())
+        return torch.as_tensor(_DevArray(self._b.x[t], (self._n[t], self._dims[t]), "<f4", self._owner), device=self._dev())
+
     def edge_index_local_t(self, src: str, rel: str, dst: str):
         """int64 CUDA tensor [2, E]: row 0 indexes `nodes(src)`, row 1 `nodes(dst)`."""
         import torch
@@ -336,15 +350,28 @@ def _align(n: int, a: int = 256) -> int:
 
 
 class _HeteroHandle:
-    """One native hetero sampler handle plus the allocation of its output buffers."""
+    """One native hetero sampler handle (scratch for `group` batches per launch
+    chain) plus the allocation of its output buffers."""
 
-    def __init__(self, graph: HeteroCsrGraph, config: HeteroSamplingConfig, seed: int):
-        self.graph, self.config = graph, config
+    def __init__(self, graph: HeteroCsrGraph, config: HeteroSamplingConfig, seed: int, group: int = 1,
+                 features: dict | None = None):
+        self.graph, self.config, self.group = graph, config, max(1, int(group))
         fan = np.ascontiguousarray(config._fanout(graph))
         out = C.c_void_p()
-        _lib.check(_lib.lib().ag_hetero_sampler_create(graph._h, fan.ctypes.data, config.num_hops, int(config.replace),
-                                                       seed, _lib.RNG_MODE[config.rng_mode], C.byref(out)))
+        _lib.check(_lib.lib().ag_hetero_sampler_create_group(graph._h, fan.ctypes.data, config.num_hops,
+                                                             int(config.replace), seed, _lib.RNG_MODE[config.rng_mode],
+                                                             self.group, C.byref(out)))
         self._h = out.value
+        # per node type: the feature store whose rows ride along as x, or None
+        self._stores = [None] * len(graph._node_types)
+        for name, store in (features or {}).items():
+            if name not in graph._nt_id:
+                raise KeyError(f"unknown node type '{name}'")
+            self._stores[graph._nt_id[name]] = store
+        self._feat_ptrs = None
+        if any(st is not None for st in self._stores):
+            self._feat_ptrs = (C.c_void_p * len(self._stores))(*[st._h if st is not None else None for st in self._stores])
+        self._bounds: dict[int, tuple[int, int]] = {}
 
     def __del__(self):
         h, self._h = getattr(self, "_h", None), None
@@ -357,29 +384,64 @@ class _HeteroHandle:
     def reseed(self, seed: int) -> None:
         _lib.check(_lib.lib().ag_hetero_sampler_reseed(self._h, seed))
 
-    def sample(self, seed_type: int, seeds: np.ndarray, stream=None) -> HeteroSampledSubgraph:
+    def _bound(self, n: int) -> tuple[int, int]:
+        if n not in self._bounds:
+            mn, me = C.c_uint64(), C.c_uint64()
+            _lib.check(_lib.lib().ag_hetero_sampler_bounds(self._h, n, C.byref(mn), C.byref(me)))
+            self._bounds[n] = (max(int(mn.value), 1), max(int(me.value), 1))
+        return self._bounds[n]
+
+    def sample_group(self, seed_type: int, seeds: list[np.ndarray], batch_seeds: list[int] | None, stream=None,
+                     return_errors: bool = False) -> list:
+        """One launch chain for up to `group` batches; returns one HeteroSampledSubgraph per batch."""
         import torch
 
         L = _lib.lib()
-        n = int(seeds.size)
-        mn, me = C.c_uint64(), C.c_uint64()
-        _lib.check(L.ag_hetero_sampler_bounds(self._h, n, C.byref(mn), C.byref(me)))
-        cap_n, cap_e, cap_s = max(int(mn.value), 1), max(int(me.value), 1), max(n, 1)
-        sizes = [4 * cap_n, 4 * cap_e, 4 * cap_e, 4 * cap_s, 8 * cap_n, 16 * cap_e, 8 * cap_s]
-        offs = np.concatenate([[0], np.cumsum([_align(s) for s in sizes])])
+        nb = len(seeds)
         dev = torch.device("cuda", self.graph.device)
-        block = torch.empty(int(offs[-1]), dtype=torch.uint8, device=dev)
+        dims = [st.feature_dim if st is not None else 0 for st in self._stores]
+        layouts, total = [], 0
+        for sd in seeds:
+            n = int(sd.size)
+            cap_n, cap_e = self._bound(n)
+            cap_s = max(n, 1)
+            sizes = [4 * cap_n, 4 * cap_e, 4 * cap_e, 4 * cap_s, 8 * cap_n, 16 * cap_e, 8 * cap_s]
+            sizes += [4 * min(cap_n, self.graph._node_types[t][1]) * d for t, d in enumerate(dims)]
+            offs = []
+            for sz in sizes:
+                offs.append(total)
+                total += _align(sz)
+            layouts.append((cap_n, cap_e, cap_s, offs))
+        block = torch.empty(max(total, 1), dtype=torch.uint8, device=dev)
         base = block.data_ptr()
-        b = _lib.HeteroBuffers()
-        b.cap_nodes, b.cap_edges, b.cap_seeds = cap_n, cap_e, cap_s
-        (b.nodes, b.edge_src_local, b.edge_dst_local, b.seed_indices, b.n_id, b.edge_index_local,
-         b.seed_index) = (base + int(o) for o in offs[:-1])
+        bufs = (_lib.HeteroBuffers * nb)()
+        for i, (cap_n, cap_e, cap_s, offs) in enumerate(layouts):
+            b = bufs[i]
+            b.cap_nodes, b.cap_edges, b.cap_seeds = cap_n, cap_e, cap_s
+            (b.nodes, b.edge_src_local, b.edge_dst_local, b.seed_indices, b.n_id, b.edge_index_local,
+             b.seed_index) = (base + o for o in offs[:7])
+            for t, d in enumerate(dims):
+                b.x[t] = base + offs[7 + t] if d else None
+        ptrs = (C.c_void_p * nb)(*[sd.ctypes.data if sd.size else None for sd in seeds])
+        lens = (C.c_uint64 * nb)(*[int(sd.size) for sd in seeds])
+        bseeds = (C.c_uint64 * nb)(*batch_seeds) if batch_seeds is not None else None
         st = stream if stream is not None else torch.cuda.current_stream(dev)
-        _lib.check(L.ag_hetero_sample_into(self._h, seed_type, seeds.ctypes.data if n else None, n, C.byref(b),
-                                           st.cuda_stream))
-        counts = _lib.HeteroCounts()
-        _lib.check(L.ag_hetero_sample_wait(self._h, C.byref(counts)))
-        return HeteroSampledSubgraph(self.graph, seed_type, seeds, counts, b, block)
+        _lib.check(L.ag_hetero_sample_group_into(self._h, nb, seed_type, ptrs, lens, bseeds, self._feat_ptrs, bufs,
+                                                 st.cuda_stream))
+        counts = (_lib.HeteroCounts * nb)()
+        statuses = (C.c_int32 * nb)()
+        rc = L.ag_hetero_sample_group_wait(self._h, counts, statuses)
+        if rc != _lib.AG_OK and not return_errors:
+            _lib.check(rc)
+        out = []
+        for i in range(nb):
+            cb = _lib.HeteroBuffers.from_buffer_copy(bufs[i])
+            cc = _lib.HeteroCounts.from_buffer_copy(counts[i])
+            out.append(HeteroSampledSubgraph(self.graph, seed_type, seeds[i], cc, cb, block, dims))
+        return (out, list(statuses), _lib.last_error() if rc != _lib.AG_OK else "") if return_errors else out
+
+    def sample(self, seed_type: int, seeds: np.ndarray, stream=None) -> HeteroSampledSubgraph:
+        return self.sample_group(seed_type, [seeds], None, stream)[0]
 
 
 class HeteroNeighborSampler:
@@ -387,10 +449,10 @@ class HeteroNeighborSampler:
     unknown seed type or a seed outside the seed type's node range
     (crates/aethergraph-py/src/hetero.rs:544-581)."""
 
-    def __init__(self, graph: HeteroCsrGraph, config: HeteroSamplingConfig):
+    def __init__(self, graph: HeteroCsrGraph, config: HeteroSamplingConfig, features: dict | None = None):
         self._graph = graph
         seed = config.seed if config.seed is not None else secrets.randbits(64)
-        self._handle = _HeteroHandle(graph, config, int(seed))
+        self._handle = _HeteroHandle(graph, config, int(seed), 1, features)
 
     def sample(self, seed_type: str, seeds) -> HeteroSampledSubgraph:
         if seed_type not in self._graph._nt_id:
@@ -412,7 +474,7 @@ class HeteroNeighborLoader:
     _TIMEOUT_S = 30.0
 
     def __init__(self, graph: HeteroCsrGraph, config: HeteroSamplingConfig, seed_type: str, prefetch_depth: int = 2,
-                 sampler_threads: int = 1):
+                 sampler_threads: int = 1, *, features: dict | None = None, group: int = 8):
         import torch
 
         if prefetch_depth < 1:
@@ -425,6 +487,10 @@ class HeteroNeighborLoader:
         self._depth = prefetch_depth
         threads = max(1, int(sampler_threads))
         self._seeded = config.seed is not None
+        # A seeded loader runs up to `group` queued batches as one launch chain (every
+        # batch has its own seed); an unseeded worker's stream simply continues, which
+        # needs its batches one at a time.
+        self._group = max(1, int(group)) if self._seeded else 1
         self._work: queue.Queue = queue.Queue(maxsize=8 * prefetch_depth)
         self._lock = threading.Condition()
         self._ready: dict[int, tuple] = {}     # seq -> (batch_idx, subgraph)
@@ -437,7 +503,7 @@ class HeteroNeighborLoader:
         base = config.seed if self._seeded else secrets.randbits(64)
         self._threads = []
         for t in range(threads):
-            h = _HeteroHandle(graph, config, int(base) if self._seeded else (int(base) + t) % 2**64)
+            h = _HeteroHandle(graph, config, int(base) if self._seeded else (int(base) + t) % 2**64, self._group, features)
             stream = torch.cuda.Stream(device=graph.device)
             th = threading.Thread(target=self._worker, args=(h, stream), name=f"aethergraph-hetero-sampler-{t}",
                                   daemon=True)
@@ -448,26 +514,43 @@ class HeteroNeighborLoader:
         L = _lib.lib()
         try:
             while True:
-                item = self._work.get()
-                if item is None or self._stop:
+                items = [self._work.get()]
+                while len(items) < self._group and items[-1] is not None:  # whatever else is queued, up to a group
+                    try:
+                        items.append(self._work.get_nowait())
+                    except queue.Empty:
+                        break
+                if items[-1] is None:
+                    stop_seen, items = True, items[:-1]
+                else:
+                    stop_seen = False
+                if self._stop or (stop_seen and not items):
                     return
-                seq, batch_idx, seeds = item
-                if self._seeded:
-                    handle.reseed(int(L.ag_batch_seed(self._config.seed, seq)))
                 t0 = time.perf_counter_ns()
-                sg = handle.sample(self._seed_type, seeds, stream)
+                if self._seeded:
+                    bseeds = [int(L.ag_batch_seed(self._config.seed, seq)) for seq, _, _ in items]
+                    sgs, statuses, err = handle.sample_group(self._seed_type, [sd for _, _, sd in items], bseeds, stream,
+                                                             return_errors=True)
+                    bad = [st for st in statuses if st != _lib.AG_OK]
+                    if bad:
+                        raise RuntimeError(err or f"hetero sampling failed with status {bad[0]}")
+                else:
+                    sgs = [handle.sample(self._seed_type, items[0][2], stream)]
                 dt = time.perf_counter_ns() - t0
                 with self._lock:
                     self._stats["sample_ns"] += dt
-                    # the result channel holds max(depth, threads) finished batches
-                    cap = max(self._depth, len(self._threads))
-                    while not self._stop and self._seeded and seq - self._deliver_seq >= cap + len(self._threads):
-                        self._lock.wait(0.1)
-                    if self._seeded:
-                        self._ready[seq] = (batch_idx, sg)
-                    else:
-                        self._unordered.append((batch_idx, sg))
-                    self._lock.notify_all()
+                    # the result channel holds max(depth, threads) finished batches per worker group
+                    cap = max(self._depth, len(self._threads)) + len(self._threads) * self._group
+                    for (seq, batch_idx, _), sg in zip(items, sgs):
+                        while not self._stop and self._seeded and seq - self._deliver_seq >= cap:
+                            self._lock.wait(0.1)
+                        if self._seeded:
+                            self._ready[seq] = (batch_idx, sg)
+                        else:
+                            self._unordered.append((batch_idx, sg))
+                        self._lock.notify_all()
+                if stop_seen:
+                    return
         except Exception as e:  # a worker that dies fails the loader, as in the reference
             with self._lock:
                 self._failed = f"{type(e).__name__}: {e}"

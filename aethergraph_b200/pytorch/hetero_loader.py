@@ -162,7 +162,7 @@ class HeteroNeighborLoader:
         cfg = HeteroSamplingConfig(self.num_neighbors, replace=self.replace,
                                    seed=epoch_sampling_seed(self._sampling_seeds), max_degree=self._max_degree)
         native = NativeHeteroLoader(self.graph, cfg, self._seed_type, prefetch_depth=self.prefetch_factor,
-                                    sampler_threads=self._threads)
+                                    sampler_threads=self._threads, features=self._stores or None)
         dev = torch.device("cuda", self.graph.device)
         submitted = received = 0
         input_ids: dict[int, np.ndarray] = {}
@@ -186,8 +186,7 @@ class HeteroNeighborLoader:
                     store.n_id = n_id
                     store.num_nodes = int(n_id.shape[0])
                     if nt in self._stores:
-                        store.x = self._stores[nt].gather(n_id) if n_id.shape[0] else \
-                            torch.empty((0, self._stores[nt].feature_dim), dtype=torch.float32, device=dev)
+                        store.x = sg.x_t(nt)  # gathered on the GPU in the sampling launch chain
                 for et in self._edge_types:
                     data[et].edge_index = sg.edge_index_local_t(*et)
                 seed_store = data[self._seed_type]

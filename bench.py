@@ -531,20 +531,20 @@ def run_hetero(args, hw):
     bs, per_step = 1024, BATCHES_PER_STEP
     n_batches = (args.warmup + args.steps) * per_step
     seeds = [synth.seed_batch(nn["user"], bs, SEEDS_SEED, b) for b in range(n_batches)]
-    loader = ag.HeteroNeighborLoader(g, cfg, "user", prefetch_depth=8, sampler_threads=args.threads)
+    group = args.group if args.group else 16
+    loader = ag.HeteroNeighborLoader(g, cfg, "user", prefetch_depth=max(8, group), sampler_threads=args.threads,
+                                     features=stores, group=group)
     row_bytes = {nt: dims[nt] * 2 + dims[nt] * 4 for nt in nn}
+    window = min(8 * max(8, group) - 1, args.threads * group + group)
 
     def run(first, count):
         edges = rows_b = sub = got = 0
         while got < count:
-            while sub < count and sub - got < 16:
+            while sub < count and sub - got < window:
                 loader.submit(first + sub, seeds[first + sub]); sub += 1
             _, sg = loader.next_batch()
-            for nt in nn:
-                n_id = sg.nodes_t(nt)
-                if n_id.shape[0]:
-                    stores[nt].gather(n_id)
-                rows_b += int(n_id.shape[0]) * row_bytes[nt]
+            for t, nt in enumerate(nn):  # the rows of every type were gathered in the batch's launch chain
+                rows_b += int(sg._c.nodes[t]) * row_bytes[nt]
             edges += int(sg._c.total_edges)
             got += 1
         return edges, rows_b
@@ -585,11 +585,18 @@ def run_hetero(args, hw):
     want = o.sample(0, seeds[0])
     for k in ("nodes", "edge_src_local", "edge_dst_local"):
         ok = ok and all(np.array_equal(a, b) for a, b in zip(got[k], want[k]))
+    # ... and the rows gathered for it: x of a type == the type's stored rows at its node ids
+    s2 = ag.HeteroNeighborSampler(g, ag.HeteroSamplingConfig(dict(zip(ets, fan)), seed=7), features=stores)
+    sg2 = s2.sample("user", seeds[1])
+    for nt in nn:
+        ids = sg2.nodes_t(nt)
+        if ids.shape[0]:
+            ok = ok and bool(torch.equal(sg2.x_t(nt), stores[nt].gather(ids)))
     line = {
         "metric": METRIC, "value": edges / (ms * 1e-3), "unit": "edges/s", "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms / max(args.steps, 1), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "u32 ids / bf16->f32", "data": "synthetic (per-relation R-MAT generated in HBM)",
-        "config": {"workload": hw["label"], "batches_per_step": per_step, "sampler_threads": args.threads,
+        "config": {"workload": hw["label"], "batches_per_step": per_step, "sampler_threads": args.threads, "group": group,
                    "fanout": {"/".join(et): f for et, f in zip(ets, fan)}},
         "gather_gbs": gbytes / (ms * 1e-3) / 1e9, "edges_per_step": edges / max(args.steps, 1), "setup_s": round(t_setup, 1),
         "cpu_baseline": {"value": cpu_edges / t_cpu, "unit": "edges/s", "cores": 1, "kind": "port",

@@ -373,6 +373,9 @@ typedef struct {
     uint64_t cap_nodes, cap_edges, cap_seeds;
     uint32_t *nodes, *edge_src_local, *edge_dst_local, *seed_indices;
     int64_t *n_id, *edge_index_local, *seed_index;   /* optional int64 views */
+    /* optional, per node type: f32 [cap_nodes, dim of that type's feature store]
+     * rows of the type's `nodes` segment, filled when feature stores are passed */
+    float *x[AG_MAX_NODE_TYPES];
 } ag_hetero_buffers;
 
 typedef struct {
@@ -388,6 +391,10 @@ typedef struct {
 int32_t ag_hetero_sampler_create(const ag_hetero_graph *h, const uint32_t *fanout, uint32_t num_hops,
                                  int32_t replace, uint64_t seed, int32_t rng_mode,
                                  ag_hetero_sampler **out);
+/* A handle with scratch for `group` (<= 64) batches per launch chain. */
+int32_t ag_hetero_sampler_create_group(const ag_hetero_graph *h, const uint32_t *fanout,
+                                       uint32_t num_hops, int32_t replace, uint64_t seed,
+                                       int32_t rng_mode, uint32_t group, ag_hetero_sampler **out);
 int32_t ag_hetero_sampler_reseed(ag_hetero_sampler *s, uint64_t seed);
 int32_t ag_hetero_sampler_bounds(const ag_hetero_sampler *s, uint64_t n_seeds, uint64_t *max_nodes,
                                  uint64_t *max_edges);
@@ -396,6 +403,18 @@ int32_t ag_hetero_sampler_bounds(const ag_hetero_sampler *s, uint64_t n_seeds, u
 int32_t ag_hetero_sample_into(ag_hetero_sampler *s, uint32_t seed_type, const uint32_t *seeds,
                               uint64_t n_seeds, ag_hetero_buffers *buf, void *stream);
 int32_t ag_hetero_sample_wait(ag_hetero_sampler *s, ag_hetero_counts *counts);
+/* One launch chain for n_batches batches rooted at the same node type (the batch
+ * is blockIdx.y of every kernel).  batch_seeds[b] starts batch b's own RNG stream
+ * (the loader's per-batch reseed, prefetch.rs:1003-1005); NULL (one batch only)
+ * continues the handle's stream.  feats: NULL, or num_node_types feature stores
+ * (entries may be NULL): node type t's rows are gathered into bufs[b].x[t] in the
+ * same chain.  The wait returns per-batch counts and statuses. */
+int32_t ag_hetero_sample_group_into(ag_hetero_sampler *s, uint32_t n_batches, uint32_t seed_type,
+                                    const uint32_t *const *seeds, const uint64_t *n_seeds,
+                                    const uint64_t *batch_seeds, const ag_features *const *feats,
+                                    ag_hetero_buffers *bufs, void *stream);
+int32_t ag_hetero_sample_group_wait(ag_hetero_sampler *s, ag_hetero_counts *counts,
+                                    int32_t *statuses);
 void ag_hetero_sampler_free(ag_hetero_sampler *s);
 
 /* --------------------------------------------------------------- loader --
