@@ -77,7 +77,7 @@ class HeteroBuffers(C.Structure):
     _fields_ = [("cap_nodes", C.c_uint64), ("cap_edges", C.c_uint64), ("cap_seeds", C.c_uint64)] + \
                [(n, C.c_void_p) for n in ("nodes", "edge_src_local", "edge_dst_local", "seed_indices",
                                           "n_id", "edge_index_local", "seed_index")] + \
-               [("x", C.c_void_p * AG_MAX_NODE_TYPES)]
+               [("x", C.c_void_p * AG_MAX_NODE_TYPES), ("cap_x", C.c_uint64 * AG_MAX_NODE_TYPES)]
 
 
 class HeteroCounts(C.Structure):

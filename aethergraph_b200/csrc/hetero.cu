@@ -914,6 +914,7 @@ extern "C" int32_t ag_hetero_sample_group_into(ag_hetero_sampler *s, uint32_t n_
                 set_gather_source(ga, feats[t]);
                 ga.ids = B.nodes; ga.ids64 = 0; ga.ids_off = p.type_start + t;
                 ga.n = std::min<uint64_t>(p.cap_nodes, m.type_nodes[t]);
+                if (B.cap_x[t]) ga.n = std::min<uint64_t>(ga.n, B.cap_x[t]);
                 ga.n_dev = p.type_count + t;
                 ga.out = B.x[t];
                 want_x = true;

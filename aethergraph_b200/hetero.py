@@ -227,6 +227,7 @@ class HeteroSampledSubgraph:
                  bufs: _lib.HeteroBuffers, owner, dims=None):
         self._g, self._seed_type, self._seeds, self._c, self._b, self._owner = graph, seed_type, seeds, counts, bufs, owner
         self._dims = dims or [0] * len(graph._node_types)
+        self._x_override: dict[int, object] = {}
         self._n = [int(counts.nodes[t]) for t in range(len(graph._node_types))]
         self._e = [int(counts.edges[e]) for e in range(len(graph._edge_types))]
         self._n_start = np.concatenate([[0], np.cumsum(self._n)]).astype(np.int64)
@@ -295,6 +296,8 @@ class HeteroSampledSubgraph:
         import torch
 
         t = self._nt(node_type)
+        if t in self._x_override:
+            return self._x_override[t]
         if not self._dims[t] or not self._b.x[t]:
             return None
         if not self._n[t]:
@@ -372,6 +375,10 @@ class _HeteroHandle:
         if any(st is not None for st in self._stores):
             self._feat_ptrs = (C.c_void_p * len(self._stores))(*[st._h if st is not None else None for st in self._stores])
         self._bounds: dict[int, tuple[int, int]] = {}
+        # rows of x reserved per node type: the worst-case bound until batches have been
+        # seen, then 1.5 x the largest count observed (a batch that outgrows it is
+        # gathered again at its exact size)
+        self._x_rows: list[int | None] = [None] * len(self._stores)
 
     def __del__(self):
         h, self._h = getattr(self, "_h", None), None
@@ -406,22 +413,25 @@ class _HeteroHandle:
             cap_n, cap_e = self._bound(n)
             cap_s = max(n, 1)
             sizes = [4 * cap_n, 4 * cap_e, 4 * cap_e, 4 * cap_s, 8 * cap_n, 16 * cap_e, 8 * cap_s]
-            sizes += [4 * min(cap_n, self.graph._node_types[t][1]) * d for t, d in enumerate(dims)]
+            x_caps = [min(cap_n, self.graph._node_types[t][1], self._x_rows[t] or cap_n) if d else 0
+                      for t, d in enumerate(dims)]
+            sizes += [4 * c * d for c, d in zip(x_caps, dims)]
             offs = []
             for sz in sizes:
                 offs.append(total)
                 total += _align(sz)
-            layouts.append((cap_n, cap_e, cap_s, offs))
+            layouts.append((cap_n, cap_e, cap_s, offs, x_caps))
         block = torch.empty(max(total, 1), dtype=torch.uint8, device=dev)
         base = block.data_ptr()
         bufs = (_lib.HeteroBuffers * nb)()
-        for i, (cap_n, cap_e, cap_s, offs) in enumerate(layouts):
+        for i, (cap_n, cap_e, cap_s, offs, x_caps) in enumerate(layouts):
             b = bufs[i]
             b.cap_nodes, b.cap_edges, b.cap_seeds = cap_n, cap_e, cap_s
             (b.nodes, b.edge_src_local, b.edge_dst_local, b.seed_indices, b.n_id, b.edge_index_local,
              b.seed_index) = (base + o for o in offs[:7])
             for t, d in enumerate(dims):
                 b.x[t] = base + offs[7 + t] if d else None
+                b.cap_x[t] = x_caps[t]
         ptrs = (C.c_void_p * nb)(*[sd.ctypes.data if sd.size else None for sd in seeds])
         lens = (C.c_uint64 * nb)(*[int(sd.size) for sd in seeds])
         bseeds = (C.c_uint64 * nb)(*batch_seeds) if batch_seeds is not None else None
@@ -437,7 +447,15 @@ class _HeteroHandle:
         for i in range(nb):
             cb = _lib.HeteroBuffers.from_buffer_copy(bufs[i])
             cc = _lib.HeteroCounts.from_buffer_copy(counts[i])
-            out.append(HeteroSampledSubgraph(self.graph, seed_type, seeds[i], cc, cb, block, dims))
+            sg = HeteroSampledSubgraph(self.graph, seed_type, seeds[i], cc, cb, block, dims)
+            for t, d in enumerate(dims):
+                if not d:
+                    continue
+                n_t = int(cc.nodes[t])
+                if n_t > layouts[i][4][t]:  # outgrew the reserved rows: gather this type again, exactly
+                    sg._x_override[t] = self._stores[t].gather(sg.nodes_t(self.graph._node_types[t][0]))
+                self._x_rows[t] = max(self._x_rows[t] or 0, n_t + n_t // 2 + 1024)
+            out.append(sg)
         return (out, list(statuses), _lib.last_error() if rc != _lib.AG_OK else "") if return_errors else out
 
     def sample(self, seed_type: int, seeds: np.ndarray, stream=None) -> HeteroSampledSubgraph:

@@ -373,9 +373,12 @@ typedef struct {
     uint64_t cap_nodes, cap_edges, cap_seeds;
     uint32_t *nodes, *edge_src_local, *edge_dst_local, *seed_indices;
     int64_t *n_id, *edge_index_local, *seed_index;   /* optional int64 views */
-    /* optional, per node type: f32 [cap_nodes, dim of that type's feature store]
-     * rows of the type's `nodes` segment, filled when feature stores are passed */
+    /* optional, per node type: f32 [cap_x[t], dim of that type's feature store]
+     * rows of the type's `nodes` segment, filled when feature stores are passed.
+     * cap_x[t] = 0 means cap_nodes rows.  A type with more nodes than cap_x[t]
+     * gets its first cap_x[t] rows only (compare ag_hetero_counts.nodes[t]). */
     float *x[AG_MAX_NODE_TYPES];
+    uint64_t cap_x[AG_MAX_NODE_TYPES];
 } ag_hetero_buffers;
 
 typedef struct {

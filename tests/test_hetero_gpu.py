@@ -295,3 +295,29 @@ def test_c4_shaped_schema_down_scaled_matches_the_oracle():
         want = o.sample(0, seeds)
         _same(sg.raw_u32(), want)
         assert sum(len(x) for x in want["nodes"]) > 5000 and all(len(x) for x in want["nodes"])
+
+
+def test_features_ride_the_chain_and_outgrown_reservations_are_regathered():
+    """x of a node type == the type's stored rows at its node ids, both when the rows
+    fit the space reserved from earlier batches and when a batch outgrows it."""
+    import torch
+
+    import aethergraph_b200 as ag
+
+    rng = np.random.default_rng(12)
+    nn = {"a": 6000, "b": 3000}
+    e1 = (rng.integers(0, 6000, 60_000).astype(np.uint32), rng.integers(0, 3000, 60_000).astype(np.uint32))
+    ets = [("a", "to", "b"), ("b", "back", "a")]
+    g = ag.HeteroCsrGraph.from_edge_arrays(nn, [(*ets[0], *e1), (*ets[1], *e1[::-1])])
+    feats = {"a": ag.FeatureStore.from_array(rng.standard_normal((6000, 32)).astype(np.float32), dtype="bf16"),
+             "b": ag.FeatureStore.from_array(rng.standard_normal((3000, 5)).astype(np.float32), dtype="f32")}
+    s = ag.HeteroNeighborSampler(g, ag.HeteroSamplingConfig({ets[0]: [8, 8], ets[1]: [8, 8]}, seed=3), features=feats)
+    for n_seeds in (2, 1500, 40, 3000):   # small, far larger (outgrows the reservation), small, larger again
+        sg = s.sample("a", rng.integers(0, 6000, n_seeds))
+        for nt in nn:
+            ids = sg.nodes_t(nt)
+            x = sg.x_t(nt)
+            assert x.shape == (ids.shape[0], feats[nt].feature_dim)
+            assert torch.equal(x, feats[nt].gather(ids))
+    plain = ag.HeteroNeighborSampler(g, ag.HeteroSamplingConfig({ets[0]: [2]}, seed=3)).sample("a", [1, 2])
+    assert plain.x_t("a") is None
