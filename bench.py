@@ -493,6 +493,52 @@ HETERO = {
 }
 
 
+def hetero_cpu_leg(g, nn, ets, fan, host_rel, seeds, stores):
+    """The CPU restatement of the hetero sampler on the same relations (one thread,
+    sampling only) and a bit-for-bit check of one batch and its gathered rows."""
+    import torch
+
+    import aethergraph_b200 as ag
+    from oracle import ago
+
+    # reverse relation = transpose of the stored one
+    names = list(nn)
+    rels = []
+    for (s, r, d) in ets[:3]:
+        off, dd = host_rel[r]
+        rels.append((names.index(s), names.index(d), off, dd))
+    for (s, r, d) in ets[3:]:
+        off, dd = host_rel[r[4:]]
+        t_off, t_src = ago.transpose(off, dd, nn[d], nn[s])
+        rels.append((names.index(s), names.index(d), t_off, t_src))
+    o = ago.HeteroSampler([nn[k] for k in names], rels, fan, seed=SAMPLER_SEED)
+    ok, cpu_edges, t_cpu = True, 0, time.time()
+    nb_cpu = 0
+    while time.time() - t_cpu < 6.0 and nb_cpu < len(seeds):
+        o.reseed(ago.batch_seed(SAMPLER_SEED, nb_cpu))
+        want = o.sample(0, seeds[nb_cpu])
+        cpu_edges += sum(len(x) for x in want["edge_src_local"])
+        nb_cpu += 1
+    t_cpu = time.time() - t_cpu
+    # parity of batch 0 at this scale, bit for bit
+    s1 = ag.HeteroNeighborSampler(g, ag.HeteroSamplingConfig(dict(zip(ets, fan)), seed=ago.batch_seed(SAMPLER_SEED, 0)))
+    got = s1.sample("user", seeds[0]).raw_u32()
+    o.reseed(ago.batch_seed(SAMPLER_SEED, 0))
+    want = o.sample(0, seeds[0])
+    for k in ("nodes", "edge_src_local", "edge_dst_local"):
+        ok = ok and all(np.array_equal(a, b) for a, b in zip(got[k], want[k]))
+    # ... and the rows gathered for it: x of a type == the type's stored rows at its node ids
+    s2 = ag.HeteroNeighborSampler(g, ag.HeteroSamplingConfig(dict(zip(ets, fan)), seed=7), features=stores)
+    sg2 = s2.sample("user", seeds[1])
+    for nt in nn:
+        ids = sg2.nodes_t(nt)
+        if ids.shape[0]:
+            ok = ok and bool(torch.equal(sg2.x_t(nt), stores[nt].gather(ids)))
+    cpu = {"value": cpu_edges / t_cpu, "unit": "edges/s", "cores": 1, "kind": "port",
+           "sample": f"{nb_cpu} batches, one thread, sampling only, {t_cpu:.1f} s", "host": host_description()}
+    return cpu, bool(ok)
+
+
 def run_hetero(args, hw):
     """Sampled edges/s of the heterogeneous sampler + per-type feature gather on one
     GPU, with the CPU restatement timed beside it on the same relations."""
@@ -520,7 +566,9 @@ def run_hetero(args, hw):
               (votes[1], src["votes"]), (writes[1], src["writes"]), (belongs[1], src["belongs_to"])]
     fan = [[15, 10], [10, 5], [3, 2], [15, 10], [10, 5], [3, 2]]
     g = ag.HeteroCsrGraph.from_device_edges(nn, [(*et, *a) for et, a in zip(ets, arrays)])
-    host_rel = {k: (v[0].cpu().numpy().astype(np.uint64), v[1].cpu().numpy().view(np.uint32)) for k, v in rel.items()}
+    host_rel = None
+    if not args.no_cpu and sc > 1:  # the CPU leg needs the relations on the host (skipped at full scale)
+        host_rel = {k: (v[0].cpu().numpy().astype(np.uint64), v[1].cpu().numpy().view(np.uint32)) for k, v in rel.items()}
     del src, arrays, votes, writes, belongs, rel
     torch.cuda.empty_cache()
     dims = {"user": 128, "post": 128, "comment": 128, "subreddit": 64}
@@ -558,40 +606,9 @@ def run_hetero(args, hw):
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1)
     loader.shutdown()
-    # CPU restatement on the same relations (reverse relation = transpose of the stored one)
-    threads = cpu_threads()
-    names = list(nn)
-    rels = []
-    for (s, r, d) in ets[:3]:
-        off, dd = host_rel[r]
-        rels.append((names.index(s), names.index(d), off, dd))
-    for (s, r, d) in ets[3:]:
-        off, dd = host_rel[r[4:]]
-        t_off, t_src = ago.transpose(off, dd, nn[d], nn[s])
-        rels.append((names.index(s), names.index(d), t_off, t_src))
-    o = ago.HeteroSampler([nn[k] for k in names], rels, fan, seed=SAMPLER_SEED)
-    ok, cpu_edges, t_cpu = True, 0, time.time()
-    nb_cpu = 0
-    while time.time() - t_cpu < 6.0 and nb_cpu < n_batches:
-        o.reseed(ago.batch_seed(SAMPLER_SEED, nb_cpu))
-        want = o.sample(0, seeds[nb_cpu])
-        cpu_edges += sum(len(x) for x in want["edge_src_local"])
-        nb_cpu += 1
-    t_cpu = time.time() - t_cpu
-    # parity of batch 0 at this scale, bit for bit
-    s1 = ag.HeteroNeighborSampler(g, ag.HeteroSamplingConfig(dict(zip(ets, fan)), seed=ago.batch_seed(SAMPLER_SEED, 0)))
-    got = s1.sample("user", seeds[0]).raw_u32()
-    o.reseed(ago.batch_seed(SAMPLER_SEED, 0))
-    want = o.sample(0, seeds[0])
-    for k in ("nodes", "edge_src_local", "edge_dst_local"):
-        ok = ok and all(np.array_equal(a, b) for a, b in zip(got[k], want[k]))
-    # ... and the rows gathered for it: x of a type == the type's stored rows at its node ids
-    s2 = ag.HeteroNeighborSampler(g, ag.HeteroSamplingConfig(dict(zip(ets, fan)), seed=7), features=stores)
-    sg2 = s2.sample("user", seeds[1])
-    for nt in nn:
-        ids = sg2.nodes_t(nt)
-        if ids.shape[0]:
-            ok = ok and bool(torch.equal(sg2.x_t(nt), stores[nt].gather(ids)))
+    cpu, ok = None, None
+    if not args.no_cpu and sc > 1:
+        cpu, ok = hetero_cpu_leg(g, nn, ets, fan, host_rel, seeds, stores)
     line = {
         "metric": METRIC, "value": edges / (ms * 1e-3), "unit": "edges/s", "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms / max(args.steps, 1), "higher_is_better": True, "scaling": "weak",
@@ -599,9 +616,7 @@ def run_hetero(args, hw):
         "config": {"workload": hw["label"], "batches_per_step": per_step, "sampler_threads": args.threads, "group": group,
                    "fanout": {"/".join(et): f for et, f in zip(ets, fan)}},
         "gather_gbs": gbytes / (ms * 1e-3) / 1e9, "edges_per_step": edges / max(args.steps, 1), "setup_s": round(t_setup, 1),
-        "cpu_baseline": {"value": cpu_edges / t_cpu, "unit": "edges/s", "cores": 1, "kind": "port",
-                         "sample": f"{nb_cpu} batches, one thread, sampling only, {t_cpu:.1f} s", "host": host_description()},
-        "parity_full_scale": bool(ok),
+        "cpu_baseline": cpu, "parity_full_scale": ok,
     }
     print(json.dumps(line), flush=True)
 
