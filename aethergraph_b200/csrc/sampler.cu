@@ -87,6 +87,8 @@ struct SampleParams {
     uint32_t *slot_of_edge;
     FrontierEntry *frontier;
     uint64_t frontier_cap;
+    uint32_t *hub_list;   // weighted only: frontier positions of the rows left to k_pick_hubs
+    uint32_t *hub_count;
 };
 
 // Row bounds with the reference's guard (graph/csr.rs:318-335): an inverted
@@ -265,6 +267,60 @@ __device__ __forceinline__ void pick_large(const SampleParams &p, uint32_t hop, 
 // order; the reference's own order comes from Rust's select_nth_unstable_by and
 // is not defined by its source tree.  The warp streams the row 32 positions at a
 // time and keeps the k best so far sorted across its lanes.
+// Weighted picks (sampler.rs:1418-1469): every position of a row with deg > k gets
+// the key -ln(u) / w from its own draw; the k smallest (key, position) win and are
+// emitted in ascending order.  A warp streams 32 positions at a time and keeps the
+// current best k sorted across its lanes.
+
+// Inserts the chunk's candidates (one per lane, cpos == ~0 for none) that beat the
+// current k-th best into the sorted lanes.
+__device__ __forceinline__ void topk_insert_chunk(double key, uint32_t cpos, double &best_key, uint32_t &best_pos,
+                                                  uint32_t k, int lane) {
+    for (;;) {
+        const double tk = __shfl_sync(0xffffffffu, best_key, k - 1);
+        const uint32_t tp = __shfl_sync(0xffffffffu, best_pos, k - 1);
+        const uint32_t m = __ballot_sync(0xffffffffu, cpos != 0xFFFFFFFFu && key_less(key, cpos, tk, tp));
+        if (!m) break;
+        const int src = __ffs(m) - 1;
+        const double ck = __shfl_sync(0xffffffffu, key, src);
+        const uint32_t cp = __shfl_sync(0xffffffffu, cpos, src);
+        // (ck, cp) lands after every entry that is smaller, the rest shift up by one.
+        const uint32_t smaller = __ballot_sync(0xffffffffu, key_less(best_key, best_pos, ck, cp));
+        const int at = __popc(smaller);
+        const double up_k = __shfl_up_sync(0xffffffffu, best_key, 1);
+        const uint32_t up_p = __shfl_up_sync(0xffffffffu, best_pos, 1);
+        if (lane == at) { best_key = ck; best_pos = cp; }
+        else if (lane > at) { best_key = up_k; best_pos = up_p; }
+        if (lane == src) cpos = 0xFFFFFFFFu;
+    }
+}
+
+// Streams positions [begin, end) of the row of `fe` into the warp's sorted best k.
+__device__ __forceinline__ void topk_stream(const SampleParams &p, uint32_t hop, const FrontierEntry &fe, uint32_t begin,
+                                            uint32_t end, uint32_t k, int lane, double &best_key, uint32_t &best_pos) {
+    const double inf = __longlong_as_double(0x7FF0000000000000ll);
+    for (uint32_t c = begin; c < end; c += 32) {
+        const uint32_t pos = c + lane;
+        double key = inf;
+        uint32_t cpos = 0xFFFFFFFFu;
+        if (pos < end) {
+            const uint64_t bits = (p.rng_mode == AG_RNG_PHILOX)
+                ? (((uint64_t)philox_u32(p.seed, hop, fe.id, 2 * pos) << 32) | philox_u32(p.seed, hop, fe.id, 2 * pos + 1))
+                : wyrand_at(p.seed, fe.dbase + pos);
+            const double w = (double)__ldg(p.weights + fe.off + pos);
+            if (isfinite(w) && w > 0.0) {
+                const double u = ((double)(bits >> 11) + 1.0) * (1.0 / 9007199254740992.0);
+                key = -log(u) / w;
+            }
+            cpos = pos;
+        }
+        topk_insert_chunk(key, cpos, best_key, best_pos, k, lane);
+    }
+}
+
+constexpr uint32_t kHubDegree = 4096;  // rows longer than this are left to k_pick_hubs (a whole block per row)
+constexpr int kHubThreads = 512;
+
 __device__ __forceinline__ void pick_weighted(const SampleParams &p, uint32_t hop, uint32_t k, uint32_t edges_before,
                                               const FrontierEntry *fes, uint32_t n) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -278,42 +334,13 @@ __device__ __forceinline__ void pick_weighted(const SampleParams &p, uint32_t ho
             for (uint32_t t = lane; t < deg; t += 32) emit_edge(p, hop, edges_before, fe, t, fe.off + t);
             continue;
         }
+        if (deg > kHubDegree && p.hub_list) {  // queue the hub for the block-per-row kernel
+            if (lane == 0) p.hub_list[atomicAdd(p.hub_count, 1u)] = j;
+            continue;
+        }
         double best_key = inf;
         uint32_t best_pos = 0xFFFFFFFFu;  // sentinel: sorts after every real (key, position)
-        for (uint32_t c = 0; c < deg; c += 32) {
-            const uint32_t pos = c + lane;
-            double key = inf;
-            uint32_t cpos = 0xFFFFFFFFu;
-            if (pos < deg) {
-                const uint64_t bits = (p.rng_mode == AG_RNG_PHILOX)
-                    ? (((uint64_t)philox_u32(p.seed, hop, fe.id, 2 * pos) << 32) | philox_u32(p.seed, hop, fe.id, 2 * pos + 1))
-                    : wyrand_at(p.seed, fe.dbase + pos);
-                const double w = (double)__ldg(p.weights + fe.off + pos);
-                if (isfinite(w) && w > 0.0) {
-                    const double u = ((double)(bits >> 11) + 1.0) * (1.0 / 9007199254740992.0);
-                    key = -log(u) / w;
-                }
-                cpos = pos;
-            }
-            for (;;) {
-                const double tk = __shfl_sync(0xffffffffu, best_key, k - 1);
-                const uint32_t tp = __shfl_sync(0xffffffffu, best_pos, k - 1);
-                const uint32_t m = __ballot_sync(0xffffffffu, cpos != 0xFFFFFFFFu && key_less(key, cpos, tk, tp));
-                if (!m) break;
-                const int src = __ffs(m) - 1;
-                const double ck = __shfl_sync(0xffffffffu, key, src);
-                const uint32_t cp = __shfl_sync(0xffffffffu, cpos, src);
-                // Insert (ck, cp) into the sorted lanes: it lands after every entry
-                // that is smaller, the rest shift up by one.
-                const uint32_t smaller = __ballot_sync(0xffffffffu, key_less(best_key, best_pos, ck, cp));
-                const int at = __popc(smaller);
-                const double up_k = __shfl_up_sync(0xffffffffu, best_key, 1);
-                const uint32_t up_p = __shfl_up_sync(0xffffffffu, best_pos, 1);
-                if (lane == at) { best_key = ck; best_pos = cp; }
-                else if (lane > at) { best_key = up_k; best_pos = up_p; }
-                if (lane == src) cpos = 0xFFFFFFFFu;
-            }
-        }
+        topk_stream(p, hop, fe, 0, deg, k, lane, best_key, best_pos);
         if ((uint32_t)lane < k) emit_edge(p, hop, edges_before, fe, lane, fe.off + best_pos);
     }
 }
@@ -406,6 +433,7 @@ k_assign(const SampleParams *__restrict__ pa, uint32_t stage, uint32_t k) {
                     nx.hop_draws = 0;
                     bs->stage[stage + 1] = nx;
                     bs->nodes_per_stage[stage] = tot.flags;
+                    if (p.hub_count) *p.hub_count = 0;  // the hop's hub queue starts empty
                     if (stage == 0) bs->stage[0] = si;  // what finalize measures the draws against
                 }
             }
@@ -451,6 +479,42 @@ k_pick(const SampleParams *__restrict__ pa, uint32_t hop, uint32_t k) {
     if constexpr (PICK == kPickWeighted) pick_weighted(p, hop, k, nx.n_edges, p.frontier, nx.frontier_n);
     else if constexpr (PICK == kPickLarge) pick_large(p, hop, k, nx.n_edges, p.frontier, nx.frontier_n, &s_picks[0][0]);
     else pick_small<G>(p, hop, k, nx.n_edges, p.frontier, nx.frontier_n);
+}
+
+// Hub rows of a weighted hop: one block per queued row.  Every warp streams an
+// equal slice of the row into its own best k, the slices' winners meet in shared
+// memory and warp 0 merges them; (key, position) is a total order, so the k
+// smallest — and their emission order — do not depend on how the row was split.
+__global__ void __launch_bounds__(kHubThreads)
+k_pick_hubs(const SampleParams *__restrict__ pa, uint32_t hop, uint32_t k) {
+    __shared__ double s_key[kHubThreads / 32][32];
+    __shared__ uint32_t s_pos[kHubThreads / 32][32];
+    chain_sync();
+    const SampleParams &p = pa[blockIdx.y];
+    const StageInfo nx = p.state->stage[hop + 1];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int kWarps = kHubThreads / 32;
+    const double inf = __longlong_as_double(0x7FF0000000000000ll);
+    const uint32_t hubs = min(*p.hub_count, nx.frontier_n);
+    for (uint32_t h = blockIdx.x; h < hubs; h += gridDim.x) {
+        const FrontierEntry fe = p.frontier[p.hub_list[h]];
+        const uint32_t deg = fe.deg;
+        const uint32_t per = ((deg + kWarps - 1) / kWarps + 31) & ~31u;  // slice per warp, whole chunks of 32
+        const uint32_t begin = min(deg, (uint32_t)warp * per), end = min(deg, begin + per);
+        double best_key = inf;
+        uint32_t best_pos = 0xFFFFFFFFu;
+        topk_stream(p, hop, fe, begin, end, k, lane, best_key, best_pos);
+        s_key[warp][lane] = best_key; s_pos[warp][lane] = best_pos;
+        __syncthreads();
+        if (warp == 0) {
+            for (int w = 1; w < kWarps; ++w) {
+                const bool have = (uint32_t)lane < k && s_pos[w][lane] != 0xFFFFFFFFu;
+                topk_insert_chunk(have ? s_key[w][lane] : inf, have ? s_pos[w][lane] : 0xFFFFFFFFu, best_key, best_pos, k, lane);
+            }
+            if ((uint32_t)lane < k) emit_edge(p, hop, nx.n_edges, fe, lane, fe.off + best_pos);
+        }
+        __syncthreads();
+    }
 }
 
 // --------------------------------------------------------------- finalize --
@@ -528,6 +592,8 @@ void launch_pick(int mode, uint32_t k, uint64_t frontier_est, uint32_t n_batches
     };
     if (mode == kModeWeighted) {
         launch_chained(k_pick<32, kPickWeighted>, dim3(blocks_for(frontier_est, kPickThreads / 32), n_batches), dim3(kPickThreads), st, pa, hop, k);
+        // rows longer than kHubDegree were only queued: one block per queued row
+        launch_chained(k_pick_hubs, dim3(std::max<uint32_t>(1, (uint32_t)(kSMs * 2 / n_batches)), n_batches), dim3(kHubThreads), st, pa, hop, k);
     } else if (k > 32) {
         launch_chained(k_pick<32, kPickLarge>, dim3(blocks_for(frontier_est, 4), n_batches), dim3(128), st, pa, hop, k);
     } else {
@@ -565,6 +631,7 @@ struct ag_sampler {
     FrontierEntry *frontier = nullptr;
     uint64_t max_frontier = 0;
     uint32_t *slot_of_seed = nullptr, *slot_of_edge = nullptr;
+    uint32_t *hub_list = nullptr;  // weighted only: per batch max_frontier queue slots + 1 counter word
     TileDesc *tiles = nullptr;
     BatchState *state = nullptr;
     uint32_t *seeds_dev = nullptr;
@@ -617,6 +684,7 @@ void free_scratch(ag_sampler *s) {
     cudaFree(s->table); cudaFree(s->frontier);
     s->frontier = nullptr;
     cudaFree(s->slot_of_seed); cudaFree(s->slot_of_edge); cudaFree(s->tiles);
+    cudaFree(s->hub_list); s->hub_list = nullptr;
     cudaFree(s->seeds_dev);
     if (s->seeds_pinned) cudaFreeHost(s->seeds_pinned);
     s->table = nullptr;
@@ -643,6 +711,10 @@ int32_t ensure_scratch(ag_sampler *s, uint64_t n_seeds) {
     AG_CUDA(cudaMalloc(&s->frontier, G * s->max_frontier * sizeof(FrontierEntry)));
     AG_CUDA(cudaMalloc(&s->slot_of_seed, G * cap * 4));
     AG_CUDA(cudaMalloc(&s->slot_of_edge, G * std::max<uint64_t>(s->max_edges, 1) * 4));
+    if (s->mode == kModeWeighted) {
+        AG_CUDA(cudaMalloc(&s->hub_list, G * (s->max_frontier + 1) * 4));
+        AG_CUDA(cudaMemset(s->hub_list, 0, G * (s->max_frontier + 1) * 4));
+    }
     s->n_tiles = std::max<uint64_t>(std::max(cap, s->max_hop_edges) / kTile + 2, 2);
     AG_CUDA(cudaMalloc(&s->tiles, G * s->n_tiles * sizeof(TileDesc)));
     AG_CUDA(cudaMemset(s->tiles, 0, G * s->n_tiles * sizeof(TileDesc)));
@@ -850,6 +922,10 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
         p.slot_of_edge = s->slot_of_edge + (uint64_t)b * ecap;
         p.frontier = s->frontier + (uint64_t)b * s->max_frontier;
         p.frontier_cap = s->max_frontier;
+        if (s->hub_list) {
+            p.hub_count = s->hub_list + (uint64_t)b * (s->max_frontier + 1);
+            p.hub_list = p.hub_count + 1;
+        }
         s->params_host[b] = p;
         uint64_t bn, be;
         compute_bounds(s, n, &bn, &be, nullptr);

@@ -228,10 +228,13 @@ class HeteroSampledSubgraph:
         self._g, self._seed_type, self._seeds, self._c, self._b, self._owner = graph, seed_type, seeds, counts, bufs, owner
         self._dims = dims or [0] * len(graph._node_types)
         self._x_override: dict[int, object] = {}
-        self._n = [int(counts.nodes[t]) for t in range(len(graph._node_types))]
-        self._e = [int(counts.edges[e]) for e in range(len(graph._edge_types))]
-        self._n_start = np.concatenate([[0], np.cumsum(self._n)]).astype(np.int64)
-        self._e_start = np.concatenate([[0], np.cumsum(self._e)]).astype(np.int64)
+        self._n = list(counts.nodes[:len(graph._node_types)])
+        self._e = list(counts.edges[:len(graph._edge_types)])
+        self._n_start, self._e_start = [0], [0]  # segment starts: prefix sums of the per-type counts
+        for v in self._n:
+            self._n_start.append(self._n_start[-1] + v)
+        for v in self._e:
+            self._e_start.append(self._e_start[-1] + v)
 
     # -- reference API ------------------------------------------------------
     @property
