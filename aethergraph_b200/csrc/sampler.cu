@@ -303,16 +303,33 @@ __device__ __forceinline__ void topk_stream(const SampleParams &p, uint32_t hop,
         const uint32_t pos = c + lane;
         double key = inf;
         uint32_t cpos = 0xFFFFFFFFu;
+        // Once k candidates are held, almost every position loses against the k-th
+        // best key.  A single-precision test settles those without the f64 log and
+        // divide: with uf >= u (u's top 24 bits, rounded up) -ln(uf) is a LOWER bound
+        // of -ln(u); if even that bound, less the error of __logf (< 5e-7 absolute or
+        // relative), exceeds tk * w (with slack for the f32 product), the exact key
+        // cannot be below tk.  The test only ever discards certain losers, so the
+        // winners — and the output — are exactly those of the full computation.
+        const float tkf = (float)__shfl_sync(0xffffffffu, best_key, k - 1);
         if (pos < end) {
             const uint64_t bits = (p.rng_mode == AG_RNG_PHILOX)
                 ? (((uint64_t)philox_u32(p.seed, hop, fe.id, 2 * pos) << 32) | philox_u32(p.seed, hop, fe.id, 2 * pos + 1))
                 : wyrand_at(p.seed, fe.dbase + pos);
-            const double w = (double)__ldg(p.weights + fe.off + pos);
-            if (isfinite(w) && w > 0.0) {
-                const double u = ((double)(bits >> 11) + 1.0) * (1.0 / 9007199254740992.0);
-                key = -log(u) / w;
+            const float wf = __ldg(p.weights + fe.off + pos);
+            bool loser = false;
+            if (wf > 0.0f && wf <= 3.0e38f && tkf >= 1.0e-30f) {  // normal range only: no under- or overflow below
+                const float uf = (float)((uint32_t)(bits >> 40) + 1u) * 5.9604644775390625e-08f;  // 2^-24, exact
+                const float lower = -__logf(uf);
+                loser = lower * 0.999998f - 1.0e-6f > tkf * wf * 1.00001f + 1.0e-6f;
             }
-            cpos = pos;
+            if (!loser) {
+                const double w = (double)wf;
+                if (isfinite(w) && w > 0.0) {
+                    const double u = ((double)(bits >> 11) + 1.0) * (1.0 / 9007199254740992.0);
+                    key = -log(u) / w;
+                }
+                cpos = pos;
+            }
         }
         topk_insert_chunk(key, cpos, best_key, best_pos, k, lane);
     }

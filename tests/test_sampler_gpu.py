@@ -192,3 +192,33 @@ def test_philox_mode_invariants_and_uniformity(ag, rmat12):
     expected = trials * k * widths / deg
     p = stats.chisquare(bins, expected).pvalue
     assert p > 0.01, p
+
+
+def test_weighted_hub_rows_match_the_oracle():
+    """Rows far longer than the fanout (block-per-row path, with the single-precision
+    pre-filter in front of the f64 keys), next to ordinary rows, zero weights included."""
+    import aethergraph_b200 as ag
+    from oracle import ago
+
+    rng = np.random.default_rng(77)
+    n = 60_000
+    hubs = {0: 50_000, 7: 9000, 11: 4097, 13: 4096}
+    src = [np.full(d, v, dtype=np.uint32) for v, d in hubs.items()]
+    dst = [rng.integers(0, n, d).astype(np.uint32) for d in hubs.values()]
+    rest = rng.integers(0, n, 300_000).astype(np.uint32)
+    src.append(rest)
+    dst.append(rng.integers(0, n, 300_000).astype(np.uint32))
+    dst.append(np.array([0, 7, 11, 13] * 50, dtype=np.uint32))   # edges INTO the hubs, so later hops expand them
+    src.append(rng.integers(100, n, 200).astype(np.uint32))
+    src, dst = np.concatenate(src), np.concatenate(dst)
+    w = rng.lognormal(0.0, 1.0, len(src)).astype(np.float32)
+    w[rng.integers(0, len(w), 2000)] = 0.0
+    off, d2, w2 = csr_from_edges(n, src, dst, w)
+    g = ag.Graph.from_csr(off, d2, w2)
+    for fan, seeds in (([15, 10, 5], [0, 7, 11, 13, 5, 9]), ([32], [0, 0, 7]),
+                       ([8, 8], rng.integers(0, n, 700).tolist() + [0, 11])):
+        cfg = ag.SamplingConfig(num_neighbors=fan, weighted=True, seed=21)
+        got = ag.NeighborSampler(g, cfg).sample(seeds).raw_u32()
+        want = ago.Sampler(off, d2, fan, weights=w2, weighted=True, seed=21).sample(np.array(seeds, dtype=np.uint32))
+        assert_same_subgraph(got, want)
+        assert len(want["edge_dst"]) > len(seeds)
