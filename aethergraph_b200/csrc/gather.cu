@@ -29,7 +29,6 @@ constexpr int kThreads = 256;
 constexpr int kInFlight = 4;
 
 __device__ __forceinline__ float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
-__device__ __forceinline__ float bf16hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
 
 // IEEE binary16 -> binary32, exact; a NaN keeps its payload and comes out quiet
 // (what the reference's half / F16C converters produce).

@@ -296,8 +296,12 @@ __device__ __forceinline__ void topk_insert_chunk(double key, uint32_t cpos, dou
 }
 
 // Streams positions [begin, end) of the row of `fe` into the warp's sorted best k.
+// `shared_thr` (optional, shared memory): an upper bound on the row's final k-th best
+// key that several warps streaming slices of the same row keep lowering together
+// (the bit pattern of a non-negative float orders like the float).
 __device__ __forceinline__ void topk_stream(const SampleParams &p, uint32_t hop, const FrontierEntry &fe, uint32_t begin,
-                                            uint32_t end, uint32_t k, int lane, double &best_key, uint32_t &best_pos) {
+                                            uint32_t end, uint32_t k, int lane, double &best_key, uint32_t &best_pos,
+                                            uint32_t *shared_thr = nullptr) {
     const double inf = __longlong_as_double(0x7FF0000000000000ll);
     for (uint32_t c = begin; c < end; c += 32) {
         const uint32_t pos = c + lane;
@@ -310,7 +314,13 @@ __device__ __forceinline__ void topk_stream(const SampleParams &p, uint32_t hop,
         // relative), exceeds tk * w (with slack for the f32 product), the exact key
         // cannot be below tk.  The test only ever discards certain losers, so the
         // winners — and the output — are exactly those of the full computation.
-        const float tkf = (float)__shfl_sync(0xffffffffu, best_key, k - 1);
+        float tkf = (float)__shfl_sync(0xffffffffu, best_key, k - 1);
+        if (shared_thr) {
+            // publish this warp's k-th best (rounded up: still an upper bound) and adopt the lowest seen
+            const float up = __double2float_ru(__shfl_sync(0xffffffffu, best_key, k - 1));
+            if (lane == 0 && up < 3.0e38f) atomicMin(shared_thr, __float_as_uint(up));
+            tkf = fminf(tkf, __uint_as_float(*(volatile uint32_t *)shared_thr));
+        }
         if (pos < end) {
             const uint64_t bits = (p.rng_mode == AG_RNG_PHILOX)
                 ? (((uint64_t)philox_u32(p.seed, hop, fe.id, 2 * pos) << 32) | philox_u32(p.seed, hop, fe.id, 2 * pos + 1))
@@ -506,6 +516,7 @@ __global__ void __launch_bounds__(kHubThreads)
 k_pick_hubs(const SampleParams *__restrict__ pa, uint32_t hop, uint32_t k) {
     __shared__ double s_key[kHubThreads / 32][32];
     __shared__ uint32_t s_pos[kHubThreads / 32][32];
+    __shared__ uint32_t s_thr;  // float bits: lowest k-th best key any warp holds for the current row
     chain_sync();
     const SampleParams &p = pa[blockIdx.y];
     const StageInfo nx = p.state->stage[hop + 1];
@@ -520,7 +531,9 @@ k_pick_hubs(const SampleParams *__restrict__ pa, uint32_t hop, uint32_t k) {
         const uint32_t begin = min(deg, (uint32_t)warp * per), end = min(deg, begin + per);
         double best_key = inf;
         uint32_t best_pos = 0xFFFFFFFFu;
-        topk_stream(p, hop, fe, begin, end, k, lane, best_key, best_pos);
+        if (threadIdx.x == 0) s_thr = 0x7F800000u;  // +inf
+        __syncthreads();
+        topk_stream(p, hop, fe, begin, end, k, lane, best_key, best_pos, &s_thr);
         s_key[warp][lane] = best_key; s_pos[warp][lane] = best_pos;
         __syncthreads();
         if (warp == 0) {
