@@ -296,60 +296,93 @@ __device__ __forceinline__ void topk_insert_chunk(double key, uint32_t cpos, dou
 }
 
 // Streams positions [begin, end) of the row of `fe` into the warp's sorted best k.
-// `shared_thr` (optional, shared memory): an upper bound on the row's final k-th best
-// key that several warps streaming slices of the same row keep lowering together
-// (the bit pattern of a non-negative float orders like the float).
+// Exact key of position `pos` of the row (sampler.rs:1440-1452): u from the position's
+// own draw, key = -ln(u) / w, +inf for a weight that is not a positive finite number.
+__device__ __forceinline__ double weighted_key(const SampleParams &p, uint32_t hop, const FrontierEntry &fe, uint32_t pos) {
+    const uint64_t bits = (p.rng_mode == AG_RNG_PHILOX)
+        ? (((uint64_t)philox_u32(p.seed, hop, fe.id, 2 * pos) << 32) | philox_u32(p.seed, hop, fe.id, 2 * pos + 1))
+        : wyrand_at(p.seed, fe.dbase + pos);
+    const double w = (double)__ldg(p.weights + fe.off + pos);
+    if (!(isfinite(w) && w > 0.0)) return __longlong_as_double(0x7FF0000000000000ll);
+    const double u = ((double)(bits >> 11) + 1.0) * (1.0 / 9007199254740992.0);
+    return -log(u) / w;
+}
+
+// Streams positions [begin, end) of the row of `fe` into the warp's sorted best k.
+//
+// Almost every position loses against the k-th best key, and the exact key costs an
+// f64 log and divide, so the stream works in two stages.  Stage 1, all lanes, single
+// precision: with uf >= u (u's top 24 bits, rounded up) -ln(uf) is a LOWER bound of
+// -ln(u); if even that bound, less the error of __logf (< 5e-7 absolute or relative),
+// exceeds thr * w (with slack for the f32 product), the exact key cannot be below the
+// threshold and the position is dropped.  Survivors are only queued (`buf`, 64 slots
+// of the warp's shared memory).  Stage 2, whenever 32 are queued: every lane evaluates
+// one queued position exactly and the winners are inserted.  The threshold is the k-th
+// best key at the last flush (and, when several warps stream slices of one row,
+// `shared_thr`, the lowest k-th best any of them holds; the bit pattern of a
+// non-negative float orders like the float).  It is always an upper bound of the
+// row's final k-th best key, so stage 1 only ever discards certain losers and the
+// winners — and the output — are exactly those of evaluating every position.
 __device__ __forceinline__ void topk_stream(const SampleParams &p, uint32_t hop, const FrontierEntry &fe, uint32_t begin,
                                             uint32_t end, uint32_t k, int lane, double &best_key, uint32_t &best_pos,
-                                            uint32_t *shared_thr = nullptr) {
+                                            uint32_t *buf, uint32_t *shared_thr = nullptr) {
     const double inf = __longlong_as_double(0x7FF0000000000000ll);
-    for (uint32_t c = begin; c < end; c += 32) {
-        const uint32_t pos = c + lane;
+    uint32_t queued = 0;  // warp-uniform
+    float thr = (float)__shfl_sync(0xffffffffu, best_key, k - 1);
+    auto flush = [&](uint32_t count) {  // evaluate buf[0 .. count) exactly, one per lane, and insert the winners
         double key = inf;
         uint32_t cpos = 0xFFFFFFFFu;
-        // Once k candidates are held, almost every position loses against the k-th
-        // best key.  A single-precision test settles those without the f64 log and
-        // divide: with uf >= u (u's top 24 bits, rounded up) -ln(uf) is a LOWER bound
-        // of -ln(u); if even that bound, less the error of __logf (< 5e-7 absolute or
-        // relative), exceeds tk * w (with slack for the f32 product), the exact key
-        // cannot be below tk.  The test only ever discards certain losers, so the
-        // winners — and the output — are exactly those of the full computation.
-        float tkf = (float)__shfl_sync(0xffffffffu, best_key, k - 1);
-        if (shared_thr) {
-            // publish this warp's k-th best (rounded up: still an upper bound) and adopt the lowest seen
-            const float up = __double2float_ru(__shfl_sync(0xffffffffu, best_key, k - 1));
-            if (lane == 0 && up < 3.0e38f) atomicMin(shared_thr, __float_as_uint(up));
-            tkf = fminf(tkf, __uint_as_float(*(volatile uint32_t *)shared_thr));
+        if ((uint32_t)lane < count) {
+            cpos = buf[lane];
+            key = weighted_key(p, hop, fe, cpos);
         }
-        if (pos < end) {
+        topk_insert_chunk(key, cpos, best_key, best_pos, k, lane);
+        const double kth = __shfl_sync(0xffffffffu, best_key, k - 1);
+        thr = (float)kth;
+        if (shared_thr) {
+            const float up = __double2float_ru(kth);  // rounded up: still an upper bound
+            if (lane == 0 && up < 3.0e38f) atomicMin(shared_thr, __float_as_uint(up));
+        }
+    };
+    for (uint32_t c = begin; c < end; c += 32) {
+        const uint32_t pos = c + lane;
+        float t = thr;
+        if (shared_thr) t = fminf(t, __uint_as_float(*(volatile uint32_t *)shared_thr));
+        bool keep = pos < end;
+        if (keep && t >= 1.0e-30f) {  // a finite threshold in the normal range: no under- or overflow below
             const uint64_t bits = (p.rng_mode == AG_RNG_PHILOX)
                 ? (((uint64_t)philox_u32(p.seed, hop, fe.id, 2 * pos) << 32) | philox_u32(p.seed, hop, fe.id, 2 * pos + 1))
                 : wyrand_at(p.seed, fe.dbase + pos);
             const float wf = __ldg(p.weights + fe.off + pos);
-            bool loser = false;
-            if (wf > 0.0f && wf <= 3.0e38f && tkf >= 1.0e-30f) {  // normal range only: no under- or overflow below
+            if (wf > 0.0f && wf <= 3.0e38f) {
                 const float uf = (float)((uint32_t)(bits >> 40) + 1u) * 5.9604644775390625e-08f;  // 2^-24, exact
                 const float lower = -__logf(uf);
-                loser = lower * 0.999998f - 1.0e-6f > tkf * wf * 1.00001f + 1.0e-6f;
-            }
-            if (!loser) {
-                const double w = (double)wf;
-                if (isfinite(w) && w > 0.0) {
-                    const double u = ((double)(bits >> 11) + 1.0) * (1.0 / 9007199254740992.0);
-                    key = -log(u) / w;
-                }
-                cpos = pos;
+                keep = !(lower * 0.999998f - 1.0e-6f > t * wf * 1.00001f + 1.0e-6f);
             }
         }
-        topk_insert_chunk(key, cpos, best_key, best_pos, k, lane);
+        const uint32_t m = __ballot_sync(0xffffffffu, keep);
+        if (keep) buf[queued + __popc(m & ((1u << lane) - 1u))] = pos;
+        queued += __popc(m);
+        __syncwarp();
+        if (queued >= 32) {
+            flush(32);
+            __syncwarp();
+            const uint32_t rest = queued - 32;  // < 32: move the tail to the front
+            const uint32_t moved = (uint32_t)lane < rest ? buf[32 + lane] : 0;
+            __syncwarp();
+            if ((uint32_t)lane < rest) buf[lane] = moved;
+            queued = rest;
+            __syncwarp();
+        }
     }
+    if (queued) { flush(queued); __syncwarp(); }
 }
 
 constexpr uint32_t kHubDegree = 4096;  // rows longer than this are left to k_pick_hubs (a whole block per row)
 constexpr int kHubThreads = 512;
 
 __device__ __forceinline__ void pick_weighted(const SampleParams &p, uint32_t hop, uint32_t k, uint32_t edges_before,
-                                              const FrontierEntry *fes, uint32_t n) {
+                                              const FrontierEntry *fes, uint32_t n, uint32_t *queue) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (k == 0) return;
     const double inf = __longlong_as_double(0x7FF0000000000000ll);
@@ -367,7 +400,7 @@ __device__ __forceinline__ void pick_weighted(const SampleParams &p, uint32_t ho
         }
         double best_key = inf;
         uint32_t best_pos = 0xFFFFFFFFu;  // sentinel: sorts after every real (key, position)
-        topk_stream(p, hop, fe, 0, deg, k, lane, best_key, best_pos);
+        topk_stream(p, hop, fe, 0, deg, k, lane, best_key, best_pos, queue + warp * 64);
         if ((uint32_t)lane < k) emit_edge(p, hop, edges_before, fe, lane, fe.off + best_pos);
     }
 }
@@ -500,10 +533,11 @@ template <int G, int PICK>
 __global__ void __launch_bounds__(PICK == kPickLarge ? 128 : kPickThreads)
 k_pick(const SampleParams *__restrict__ pa, uint32_t hop, uint32_t k) {
     __shared__ uint32_t s_picks[PICK == kPickLarge ? 4 : 1][PICK == kPickLarge ? kLargeK : 1];
+    __shared__ uint32_t s_queue[PICK == kPickWeighted ? (kPickThreads / 32) * 64 : 1];  // weighted: 64 queued positions per warp
     chain_sync();
     const SampleParams &p = pa[blockIdx.y];
     const StageInfo nx = p.state->stage[hop + 1];
-    if constexpr (PICK == kPickWeighted) pick_weighted(p, hop, k, nx.n_edges, p.frontier, nx.frontier_n);
+    if constexpr (PICK == kPickWeighted) pick_weighted(p, hop, k, nx.n_edges, p.frontier, nx.frontier_n, s_queue);
     else if constexpr (PICK == kPickLarge) pick_large(p, hop, k, nx.n_edges, p.frontier, nx.frontier_n, &s_picks[0][0]);
     else pick_small<G>(p, hop, k, nx.n_edges, p.frontier, nx.frontier_n);
 }
@@ -517,6 +551,7 @@ k_pick_hubs(const SampleParams *__restrict__ pa, uint32_t hop, uint32_t k) {
     __shared__ double s_key[kHubThreads / 32][32];
     __shared__ uint32_t s_pos[kHubThreads / 32][32];
     __shared__ uint32_t s_thr;  // float bits: lowest k-th best key any warp holds for the current row
+    __shared__ uint32_t s_queue[(kHubThreads / 32) * 64];
     chain_sync();
     const SampleParams &p = pa[blockIdx.y];
     const StageInfo nx = p.state->stage[hop + 1];
@@ -533,7 +568,7 @@ k_pick_hubs(const SampleParams *__restrict__ pa, uint32_t hop, uint32_t k) {
         uint32_t best_pos = 0xFFFFFFFFu;
         if (threadIdx.x == 0) s_thr = 0x7F800000u;  // +inf
         __syncthreads();
-        topk_stream(p, hop, fe, begin, end, k, lane, best_key, best_pos, &s_thr);
+        topk_stream(p, hop, fe, begin, end, k, lane, best_key, best_pos, s_queue + warp * 64, &s_thr);
         s_key[warp][lane] = best_key; s_pos[warp][lane] = best_pos;
         __syncthreads();
         if (warp == 0) {
