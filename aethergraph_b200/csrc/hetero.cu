@@ -72,7 +72,7 @@ struct HParams {
     uint32_t *class_ticket;
     uint32_t *type_count, *et_count;  // totals per node type / edge type (device)
     uint32_t *type_start;   // first position of each node type's segment in `nodes`
-    int reset_pos;          // 1: the batch's RNG stream starts at draw 0
+    uint64_t start_draw;    // absolute index of the batch's first RNG draw (0 for a freshly seeded batch)
     // outputs
     uint32_t *nodes, *edge_src_local, *edge_dst_local, *seed_indices;
     int64_t *n_id, *edge_index_local, *seed_index;
@@ -129,10 +129,10 @@ k_het_assign(const HParams *__restrict__ pa, uint32_t stage, int has_next) {
     BatchState *bs = p.state;
     StageInfo si = bs->stage[stage];
     if (stage == 0) {
-        // A reseeded batch restarts its stream at draw 0; otherwise the handle's
-        // stream continues where its previous batch stopped.
+        // A reseeded batch starts its stream at draw 0; otherwise the handle's stream
+        // continues where its previous batch stopped (the host keeps that position).
         si = StageInfo{};
-        si.draws = p.reset_pos ? 0ull : bs->stream_pos;
+        si.draws = p.start_draw;
     }
     const uint32_t count = (stage == 0) ? p.n_seeds : si.hop_edges;
     const uint32_t n_tiles = max(1u, (count + kTile - 1) / kTile);
@@ -534,7 +534,9 @@ struct ag_hetero_sampler {
     HeteroMeta meta{};
     HeteroMeta *meta_dev = nullptr;
     uint64_t seed = 0;
-    bool reset_pos = true, dirty = true, in_flight = false;
+    bool dirty = true, in_flight = false;
+    uint64_t stream_pos = 0;   // draws consumed by earlier continuing batches (host-side, survives scratch growth)
+    bool pending_pos = false;  // a continuing batch was launched and not yet accounted
     uint32_t epoch = 0, gen = 0, class_epoch = 0, last_batches = 0;
     uint64_t cap_seeds = 0, max_nodes = 0, max_edges = 0, max_hop_edges = 0, max_frontier = 0, table_cap = 0, n_tiles = 0,
              class_tiles_n = 0;
@@ -699,10 +701,16 @@ void het_free_scratch(ag_hetero_sampler *s) {
     s->seeds_pinned = nullptr;
 }
 
+// A finished continuing batch moves the handle's stream on by the draws it consumed.
+void het_account(ag_hetero_sampler *s) {
+    if (s->pending_pos) s->stream_pos += s->counts_host[0].draws;
+    s->pending_pos = false;
+}
+
 // Scratch for `group` batches of up to n_seeds seeds each.
 int32_t het_ensure(ag_hetero_sampler *s, uint64_t n_seeds) {
     if (n_seeds <= s->cap_seeds && s->table) return AG_OK;
-    if (s->in_flight) { AG_CUDA(cudaEventSynchronize(s->done)); s->in_flight = false; }
+    if (s->in_flight) { AG_CUDA(cudaEventSynchronize(s->done)); s->in_flight = false; het_account(s); }
     het_free_scratch(s);
     s->cap_seeds = 0;
     const uint64_t cap = std::max<uint64_t>(n_seeds, 1), G = s->group;
@@ -815,7 +823,8 @@ extern "C" int32_t ag_hetero_sampler_create(const ag_hetero_graph *h, const uint
 
 extern "C" int32_t ag_hetero_sampler_reseed(ag_hetero_sampler *s, uint64_t seed) {
     if (!s) return fail(AG_ERR_VALUE, "ag_hetero_sampler_reseed: null sampler");
-    s->seed = seed; s->reset_pos = true;
+    if (s->in_flight) { DeviceGuard guard(s->device); cudaEventSynchronize(s->done); }
+    s->seed = seed; s->stream_pos = 0; s->pending_pos = false;
     return AG_OK;
 }
 
@@ -866,11 +875,11 @@ extern "C" int32_t ag_hetero_sample_group_into(ag_hetero_sampler *s, uint32_t n_
     DeviceGuard guard(s->device);
     if (!guard.ok) return AG_ERR_CUDA;
     cudaStream_t st = (cudaStream_t)stream;
-    if (s->in_flight) { AG_CUDA(cudaEventSynchronize(s->done)); s->in_flight = false; }
+    if (s->in_flight) { AG_CUDA(cudaEventSynchronize(s->done)); s->in_flight = false; het_account(s); }
     AG_TRY(het_ensure(s, max_n));
     const uint64_t G = s->group;
     if (s->dirty || s->gen >= kGens) { AG_CUDA(cudaMemsetAsync(s->table, 0xFF, G * s->table_cap * 8, st)); s->gen = 0; }
-    if (s->dirty) { AG_CUDA(cudaMemsetAsync(s->state, 0, G * sizeof(BatchState), st)); s->dirty = false; s->reset_pos = true; }
+    if (s->dirty) { AG_CUDA(cudaMemsetAsync(s->state, 0, G * sizeof(BatchState), st)); s->dirty = false; }
     const uint32_t H = m.num_hops;
     if (s->epoch + (H + 2) > 0x3FFFFF00u) { AG_CUDA(cudaMemsetAsync(s->tiles, 0, G * s->n_tiles * sizeof(TileDesc), st)); s->epoch = 0; }
     if (s->class_epoch + 4 > 0x3FFFFF00u) {
@@ -893,7 +902,7 @@ extern "C" int32_t ag_hetero_sample_group_into(ag_hetero_sampler *s, uint32_t n_
         if (n) memcpy(s->seeds_pinned + b * s->cap_seeds, seeds[b], (size_t)n * 4);
         p.seeds = s->seeds_dev + b * s->cap_seeds;
         p.seed = batch_seeds ? batch_seeds[b] : s->seed;
-        p.reset_pos = (batch_seeds || s->reset_pos) ? 1 : 0;
+        p.start_draw = batch_seeds ? 0ull : s->stream_pos;
         p.slot_of_seed = s->slot_of_seed + b * s->cap_seeds; p.slot_of_edge = s->slot_of_edge + b * ce;
         p.frontier = s->frontier + b * fcap; p.frontier_cap = fcap;
         p.node_key = s->node_key + b * cn; p.node_tag = s->node_tag + b * cn; p.node_rank = s->node_rank + b * cn;
@@ -922,7 +931,7 @@ extern "C" int32_t ag_hetero_sample_group_into(ag_hetero_sampler *s, uint32_t n_
             s->gather_host[(size_t)t * G + b] = ga;
         }
     }
-    s->reset_pos = false;
+    s->pending_pos = (batch_seeds == nullptr);
     s->epoch += H + 2; s->class_epoch += 2; s->gen += 1; s->last_batches = n_batches;
     AG_CUDA(cudaMemcpyAsync(s->seeds_dev, s->seeds_pinned, (uint64_t)n_batches * s->cap_seeds * 4, cudaMemcpyHostToDevice, st));
     AG_CUDA(cudaMemcpyAsync(s->params_dev, s->params_host, n_batches * sizeof(HParams), cudaMemcpyHostToDevice, st));
@@ -983,7 +992,8 @@ extern "C" int32_t ag_hetero_sample_group_wait(ag_hetero_sampler *s, ag_hetero_c
     if (!guard.ok) return AG_ERR_CUDA;
     const cudaError_t e = cudaEventSynchronize(s->done);
     s->in_flight = false;
-    if (e != cudaSuccess) { s->dirty = true; return fail(AG_ERR_CUDA, "hetero sampling kernels failed: %s", cudaGetErrorString(e)); }
+    if (e != cudaSuccess) { s->dirty = true; s->pending_pos = false; return fail(AG_ERR_CUDA, "hetero sampling kernels failed: %s", cudaGetErrorString(e)); }
+    het_account(s);
     int32_t first = AG_OK;
     for (uint32_t b = 0; b < s->last_batches; ++b) {
         const ag_hetero_counts c = s->counts_host[b];

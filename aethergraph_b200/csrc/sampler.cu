@@ -73,7 +73,7 @@ struct SampleParams {
     uint64_t seed;
     int rng_mode;
     int mode;
-    int reset_pos;
+    uint64_t start_draw;  // absolute index of the batch's first RNG draw (0 for a freshly seeded batch)
     uint32_t num_hops;
     // outputs
     uint32_t *nodes;
@@ -421,10 +421,10 @@ k_assign(const SampleParams *__restrict__ pa, uint32_t stage, uint32_t k) {
     BatchState *bs = p.state;
     StageInfo si = bs->stage[stage];
     if (stage == 0) {
-        // A reseeded batch restarts its stream at draw 0; otherwise the handle's
-        // stream continues where its previous batch stopped.
+        // A reseeded batch starts its stream at draw 0; otherwise the handle's stream
+        // continues where its previous batch stopped (the host keeps that position).
         si = StageInfo{};
-        si.draws = p.reset_pos ? 0ull : bs->stream_pos;
+        si.draws = p.start_draw;
     }
     const uint32_t count = (stage == 0) ? p.n_seeds : si.hop_edges;
     const uint32_t n_tiles = max(1u, (count + kTile - 1) / kTile);
@@ -684,7 +684,11 @@ struct ag_sampler {
     int device = 0;
     int mode = kModeUniform;
     uint64_t seed = 0;
-    bool reset_pos = true;
+    // RNG stream position of the handle (draws consumed by earlier batches).  Kept on the
+    // host from the counts of every finished continuing batch, so it survives scratch
+    // growth and state resets; `pending_pos` marks a launched batch not yet accounted.
+    uint64_t stream_pos = 0;
+    bool pending_pos = false;
     uint32_t epoch = 0;
     uint32_t gen = 0;    // table generation of the next launch
     uint32_t group = 1;  // batches one launch chain can carry
@@ -757,10 +761,17 @@ void free_scratch(ag_sampler *s) {
     s->seeds_dev = nullptr; s->seeds_pinned = nullptr;
 }
 
+// A finished continuing batch (no per-batch seed) moves the handle's stream on by
+// the draws it consumed; called wherever the host has just waited for the batch.
+void account_stream(ag_sampler *s) {
+    if (s->pending_pos) s->stream_pos += s->counts_host[0].draws;
+    s->pending_pos = false;
+}
+
 // Scratch for `group` batches of up to n_seeds seeds each.
 int32_t ensure_scratch(ag_sampler *s, uint64_t n_seeds) {
     if (n_seeds <= s->cap_seeds && s->table) return AG_OK;
-    if (s->in_flight) { AG_CUDA(cudaEventSynchronize(s->done)); }
+    if (s->in_flight) { AG_CUDA(cudaEventSynchronize(s->done)); s->in_flight = false; account_stream(s); }
     free_scratch(s);
     s->cap_seeds = 0;
     const uint64_t cap = std::max<uint64_t>(n_seeds, 1), G = s->group;
@@ -872,8 +883,13 @@ extern "C" void ag_sampler_free(ag_sampler *s) {
 
 extern "C" int32_t ag_sampler_reseed(ag_sampler *s, uint64_t seed) {
     if (!s) return fail(AG_ERR_VALUE, "ag_sampler_reseed: null sampler");
+    if (s->in_flight) {  // the batch in flight still belongs to the old stream
+        DeviceGuard guard(s->device);
+        cudaEventSynchronize(s->done);
+    }
     s->seed = seed;
-    s->reset_pos = true;
+    s->stream_pos = 0;
+    s->pending_pos = false;
     return AG_OK;
 }
 
@@ -930,7 +946,7 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
     DeviceGuard guard(s->device);
     if (!guard.ok) return AG_ERR_CUDA;
     cudaStream_t st = (cudaStream_t)stream;
-    if (s->in_flight) { AG_CUDA(cudaEventSynchronize(s->done)); s->in_flight = false; }
+    if (s->in_flight) { AG_CUDA(cudaEventSynchronize(s->done)); s->in_flight = false; account_stream(s); }
     AG_TRY(ensure_scratch(s, max_n));
     if (s->profile) AG_CUDA(cudaEventRecord(s->ev[0], st));
     if (s->dirty || s->gen >= kGens) {
@@ -943,7 +959,6 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
     if (s->dirty) {
         AG_CUDA(cudaMemsetAsync(s->state, 0, s->group * sizeof(BatchState), st));
         s->dirty = false;
-        s->reset_pos = true;
     }
     const uint32_t H = s->cfg.num_hops;
     if (s->epoch + (H + 2) > 0x3FFFFF00u) {  // the epoch lives in 30 bits of the tile status
@@ -975,7 +990,7 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
         }
         p.seed = batch_seeds ? batch_seeds[b] : s->seed;
         p.rng_mode = s->cfg.rng_mode; p.mode = s->mode;
-        p.reset_pos = (batch_seeds || s->reset_pos) ? 1 : 0;
+        p.start_draw = batch_seeds ? 0ull : s->stream_pos;
         p.num_hops = H;
         p.nodes = B.nodes; p.edge_src = B.edge_src; p.edge_dst = B.edge_dst;
         p.src_local = B.src_local; p.dst_local = B.dst_local; p.seed_locals = B.seed_locals;
@@ -1008,7 +1023,7 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
             s->gather_host[b] = ga;
         }
     }
-    s->reset_pos = false;
+    s->pending_pos = (batch_seeds == nullptr);  // a continuing batch advances the handle's stream
     s->epoch += H + 2;
     s->gen += 1;
     if (seeds_mem == AG_MEM_HOST)
@@ -1086,8 +1101,10 @@ extern "C" int32_t ag_sample_group_wait(ag_sampler *s, ag_sample_counts *counts,
     s->in_flight = false;
     if (e != cudaSuccess) {
         s->dirty = true;
+        s->pending_pos = false;
         return fail(AG_ERR_CUDA, "sampling kernels failed: %s", cudaGetErrorString(e));
     }
+    account_stream(s);
     float sample_ms = 0.f, gather_ms = 0.f;
     if (s->profile) {
         cudaEventElapsedTime(&sample_ms, s->ev[0], s->ev[1]);

@@ -321,3 +321,19 @@ def test_features_ride_the_chain_and_outgrown_reservations_are_regathered():
             assert torch.equal(x, feats[nt].gather(ids))
     plain = ag.HeteroNeighborSampler(g, ag.HeteroSamplingConfig({ets[0]: [2]}, seed=3)).sample("a", [1, 2])
     assert plain.x_t("a") is None
+
+
+def test_stream_continues_when_the_handle_grows():
+    """One RNG stream per handle across calls, also when a later batch needs more scratch."""
+    import aethergraph_b200 as ag
+    from oracle import ago
+
+    g = _reddit_graph(ag)
+    num_nodes, rels = _reddit_oracle_parts()
+    cfg = ag.HeteroSamplingConfig({et: [3, 2] for et in ETS}, seed=5)
+    s = ag.HeteroNeighborSampler(g, cfg)
+    o = ago.HeteroSampler(num_nodes, rels, [[3, 2]] * 3, seed=5)
+    rng = np.random.default_rng(1)
+    for ns in (4, 2500, 10, 6000):
+        seeds = rng.integers(0, 100, ns).astype(np.uint32)
+        _same(s.sample(USER, seeds).raw_u32(), o.sample(0, seeds))

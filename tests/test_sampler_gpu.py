@@ -222,3 +222,22 @@ def test_weighted_hub_rows_match_the_oracle():
         want = ago.Sampler(off, d2, fan, weights=w2, weighted=True, seed=21).sample(np.array(seeds, dtype=np.uint32))
         assert_same_subgraph(got, want)
         assert len(want["edge_dst"]) > len(seeds)
+
+
+def test_stream_continues_across_calls_of_any_size():
+    """Consecutive calls on one handle consume ONE RNG stream (the reference's sampler is
+    `&mut self` with a persistent generator): also when a later call is larger than any
+    before it and the handle has to grow its scratch memory in between."""
+    import aethergraph_b200 as ag
+    from oracle import ago
+
+    n, off, dst, w = rmat_csr(13, 10, seed=31, weighted=True)
+    g = ag.Graph.from_csr(off, dst, w)
+    rng = np.random.default_rng(4)
+    for kw in (dict(), dict(replace=True), dict(weighted=True)):
+        cfg = ag.SamplingConfig(num_neighbors=[6, 3], seed=99, **kw)
+        s = ag.NeighborSampler(g, cfg)
+        o = ago.Sampler(off, dst, [6, 3], weights=w if kw.get("weighted") else None, seed=99, **kw)
+        for ns in (5, 3000, 40, 7000, 1):   # 3000 and 7000 exceed the scratch sized for the call before
+            seeds = rng.integers(0, n, ns).astype(np.uint32)
+            assert_same_subgraph(s.sample(seeds).raw_u32(), o.sample(seeds))
