@@ -87,6 +87,10 @@ class HeteroCounts(C.Structure):
                 ("total_edges", C.c_uint32), ("draws", C.c_uint64)]
 
 
+class HeteroBatch(C.Structure):
+    _fields_ = [("batch_idx", C.c_int64), ("seq", C.c_uint64), ("bufs", HeteroBuffers), ("counts", HeteroCounts)]
+
+
 _P = C.c_void_p
 _PP = C.POINTER(C.c_void_p)
 _U64P = C.POINTER(C.c_uint64)
@@ -168,6 +172,15 @@ SIGNATURES = {
     "ag_loader_stats_get": (C.c_int32, [_P, C.POINTER(LoaderStats)]),
     "ag_loader_shutdown": (C.c_int32, [_P]),
     "ag_loader_free": (None, [_P]),
+    "ag_hetero_loader_create": (C.c_int32, [_P, C.c_uint32, _P, C.c_uint32, C.c_int32, C.c_uint64, C.c_int32, C.c_int32,
+                                            _P, C.c_uint32, C.c_uint32, C.c_uint32, _PP]),
+    "ag_hetero_loader_submit": (C.c_int32, [_P, C.c_int64, _P, C.c_uint64]),
+    "ag_hetero_loader_next": (C.c_int32, [_P, C.c_int64, C.POINTER(HeteroBatch)]),
+    "ag_hetero_loader_next_many": (C.c_int32, [_P, C.c_int64, C.c_uint32, C.POINTER(HeteroBatch), C.POINTER(C.c_uint32)]),
+    "ag_hetero_loader_release_batch": (C.c_int32, [_P, C.POINTER(HeteroBatch), _P]),
+    "ag_hetero_loader_stats_get": (C.c_int32, [_P, C.POINTER(LoaderStats)]),
+    "ag_hetero_loader_shutdown": (C.c_int32, [_P]),
+    "ag_hetero_loader_free": (None, [_P]),
     "ag_synth_rmat_graph": (C.c_int32, [C.c_uint64, C.c_uint64, C.c_float, C.c_float, C.c_float, C.c_uint64,
                                         C.c_float, C.c_int32, _PP]),
     "ag_synth_rmat_csr": (C.c_int32, [C.c_uint64, C.c_uint64, C.c_uint64, C.c_float, C.c_float, C.c_float,

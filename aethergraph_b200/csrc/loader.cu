@@ -218,13 +218,15 @@ void worker_main(ag_loader *l, uint32_t idx) {
         // Unseeded: a worker's own stream continues across its batches, which needs
         // the batches one at a time.
         std::string err;
+        bool launched = false;  // the chain ran, so statuses[] tells the batches apart
         if (rc == AG_OK && (l->seeded || nb == 1)) {
             rc = ag_sample_group_into(s, nb, seed_ptrs.data(), n_seeds.data(),
                                       ws[0].seeds_dev ? AG_MEM_DEVICE : AG_MEM_HOST,
                                       l->seeded ? batch_seeds.data() : nullptr, l->f, bufs.data(), st);
-            if (rc == AG_OK) rc = ag_sample_group_wait(s, counts.data(), statuses.data());
+            if (rc == AG_OK) { launched = true; rc = ag_sample_group_wait(s, counts.data(), statuses.data()); }
             if (rc != AG_OK) err = ag_last_error();
         } else if (rc == AG_OK) {
+            launched = true;
             for (uint32_t b = 0; b < nb; ++b) {
                 int32_t r1 = ag_sample_group_into(s, 1, &seed_ptrs[b], &n_seeds[b],
                                                   ws[b].seeds_dev ? AG_MEM_DEVICE : AG_MEM_HOST, nullptr, l->f,
@@ -242,10 +244,11 @@ void worker_main(ag_loader *l, uint32_t idx) {
             Done d;
             d.batch.batch_idx = w.batch_idx; d.batch.seq = w.seq; d.batch.bufs = w.bufs; d.batch.owned = w.owned ? 1 : 0;
             d.batch.counts = counts[b];
-            // A failure of the whole launch chain fails every batch of the group; a
-            // per-batch error (bad seed, small buffer) fails only that batch.
+            // A chain that was refused before launch, or that failed as a whole, fails
+            // every batch of the group; a per-batch error (bad seed, small buffer) fails
+            // only that batch.
             const bool chain_failed = rc != AG_OK && statuses[b] == AG_OK &&
-                                      !(rc == AG_ERR_SAMPLING || rc == AG_ERR_VALUE || rc == AG_ERR_LOAD);
+                                      (!launched || !(rc == AG_ERR_SAMPLING || rc == AG_ERR_VALUE || rc == AG_ERR_LOAD));
             if (statuses[b] != AG_OK || chain_failed) { d.status = statuses[b] != AG_OK ? statuses[b] : rc; d.error = err; }
             // Results channel holds `depth` batches: wait for room (prefetch.rs:1135-1143),
             // except for the batch the consumer is waiting on — holding it back could

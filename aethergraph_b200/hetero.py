@@ -10,17 +10,15 @@ the arrays are the reference CPU sampler's, bit for bit.
 from __future__ import annotations
 
 import ctypes as C
-import queue
 import secrets
 import threading
-import time
 from typing import Sequence
 
 import numpy as np
 
 from . import _lib
 from ._lib import SamplingError
-from .loader import PrefetchStats
+from .loader import _FETCH, PrefetchStats, _raw_current_stream
 from .sampler import _DevArray, coerce_seeds
 
 __all__ = ["HeteroCsrGraph", "HeteroNeighborLoader", "HeteroNeighborSampler", "HeteroSampledSubgraph",
@@ -485,19 +483,35 @@ class HeteroNeighborSampler:
         return f"HeteroNeighborSampler(edge_types={len(self._graph._edge_types)})"
 
 
-class HeteroNeighborLoader:
-    """Prefetching heterogeneous loader: `sampler_threads` workers, each with its own
-    sampler handle and CUDA stream, over a bounded work queue; the same ordering,
-    per-batch reseed (`batch_seed(seed, seq)` when the config has a seed), timeout
-    and shutdown contract as `NeighborLoader`
-    (crates/aethergraph-core/src/loader/prefetch.rs:984-1022, 1940-2060)."""
+class _HeteroLease:
+    """Holds one pooled heterogeneous batch; hands it back to the loader when nothing
+    refers to it any more, recording the consumer's current stream as its last use."""
 
-    _TIMEOUT_S = 30.0
+    __slots__ = ("loader", "batch")
+
+    def __init__(self, loader: "HeteroNeighborLoader", batch: _lib.HeteroBatch):
+        self.loader, self.batch = loader, batch
+
+    def __del__(self):
+        ld = self.loader
+        if ld is None or not ld._h:
+            return
+        try:
+            ld._release(ld._h, C.byref(self.batch), _raw_current_stream(ld._dev_index))
+        except Exception:
+            pass
+
+
+class HeteroNeighborLoader:
+    """Prefetching heterogeneous loader over the native worker pool: `sampler_threads`
+    host threads, each with its own sampler handle and CUDA stream, run up to `group`
+    queued batches as one launch chain; the same ordering, per-batch reseed
+    (`batch_seed(seed, seq)` when the config has a seed), timeout and shutdown
+    contract as `NeighborLoader`
+    (crates/aethergraph-core/src/loader/prefetch.rs:984-1022, 1940-2060)."""
 
     def __init__(self, graph: HeteroCsrGraph, config: HeteroSamplingConfig, seed_type: str, prefetch_depth: int = 2,
                  sampler_threads: int = 1, *, features: dict | None = None, group: int = 8):
-        import torch
-
         if prefetch_depth < 1:
             raise RuntimeError("Failed to create HeteroNeighborLoader: prefetch_depth must be >= 1")
         if seed_type not in graph._nt_id:
@@ -506,120 +520,69 @@ class HeteroNeighborLoader:
         self._seed_type = graph._nt_id[seed_type]
         self._seed_nodes = graph._node_types[self._seed_type][1]
         self._depth = prefetch_depth
-        threads = max(1, int(sampler_threads))
         self._seeded = config.seed is not None
-        # A seeded loader runs up to `group` queued batches as one launch chain (every
-        # batch has its own seed); an unseeded worker's stream simply continues, which
-        # needs its batches one at a time.
-        self._group = max(1, int(group)) if self._seeded else 1
-        self._work: queue.Queue = queue.Queue(maxsize=8 * prefetch_depth)
-        self._lock = threading.Condition()
-        self._ready: dict[int, tuple] = {}     # seq -> (batch_idx, subgraph)
-        self._unordered: list[tuple] = []
-        self._next_seq = 0      # next sequence number to hand out at submit
-        self._deliver_seq = 0   # next sequence number to deliver (seeded)
-        self._failed: str | None = None
-        self._stop = False
-        self._stats = {"hits": 0, "misses": 0, "total": 0, "sample_ns": 0}
-        base = config.seed if self._seeded else secrets.randbits(64)
-        self._threads = []
-        for t in range(threads):
-            h = _HeteroHandle(graph, config, int(base) if self._seeded else (int(base) + t) % 2**64, self._group, features)
-            stream = torch.cuda.Stream(device=graph.device)
-            th = threading.Thread(target=self._worker, args=(h, stream), name=f"aethergraph-hetero-sampler-{t}",
-                                  daemon=True)
-            th.start()
-            self._threads.append(th)
-
-    def _worker(self, handle: _HeteroHandle, stream) -> None:
-        L = _lib.lib()
-        try:
-            while True:
-                items = [self._work.get()]
-                while len(items) < self._group and items[-1] is not None:  # whatever else is queued, up to a group
-                    try:
-                        items.append(self._work.get_nowait())
-                    except queue.Empty:
-                        break
-                if items[-1] is None:
-                    stop_seen, items = True, items[:-1]
-                else:
-                    stop_seen = False
-                if self._stop or (stop_seen and not items):
-                    return
-                t0 = time.perf_counter_ns()
-                if self._seeded:
-                    bseeds = [int(L.ag_batch_seed(self._config.seed, seq)) for seq, _, _ in items]
-                    sgs, statuses, err = handle.sample_group(self._seed_type, [sd for _, _, sd in items], bseeds, stream,
-                                                             return_errors=True)
-                    bad = [st for st in statuses if st != _lib.AG_OK]
-                    if bad:
-                        raise RuntimeError(err or f"hetero sampling failed with status {bad[0]}")
-                else:
-                    sgs = [handle.sample(self._seed_type, items[0][2], stream)]
-                dt = time.perf_counter_ns() - t0
-                with self._lock:
-                    self._stats["sample_ns"] += dt
-                    # the result channel holds max(depth, threads) finished batches per worker group
-                    cap = max(self._depth, len(self._threads)) + len(self._threads) * self._group
-                    for (seq, batch_idx, _), sg in zip(items, sgs):
-                        while not self._stop and self._seeded and seq - self._deliver_seq >= cap:
-                            self._lock.wait(0.1)
-                        if self._seeded:
-                            self._ready[seq] = (batch_idx, sg)
-                        else:
-                            self._unordered.append((batch_idx, sg))
-                        self._lock.notify_all()
-                if stop_seen:
-                    return
-        except Exception as e:  # a worker that dies fails the loader, as in the reference
-            with self._lock:
-                self._failed = f"{type(e).__name__}: {e}"
-                self._lock.notify_all()
+        self._stores = [None] * len(graph._node_types)
+        for name, store in (features or {}).items():
+            if name not in graph._nt_id:
+                raise KeyError(f"unknown node type '{name}'")
+            self._stores[graph._nt_id[name]] = store
+        self._dims = [st.feature_dim if st is not None else 0 for st in self._stores]
+        feat_ptrs = None
+        if any(st is not None for st in self._stores):
+            feat_ptrs = (C.c_void_p * len(self._stores))(*[st._h if st is not None else None for st in self._stores])
+        fan = np.ascontiguousarray(config._fanout(graph))
+        seed = config.seed if self._seeded else secrets.randbits(64)
+        self._h = C.c_void_p()
+        _lib.check(_lib.lib().ag_hetero_loader_create(graph._h, self._seed_type, fan.ctypes.data, config.num_hops,
+                                                      int(config.replace), int(seed), _lib.RNG_MODE[config.rng_mode],
+                                                      int(self._seeded), feat_ptrs, prefetch_depth,
+                                                      max(1, int(sampler_threads)), max(1, min(int(group), 64)),
+                                                      C.byref(self._h)))
+        self._dev_index = int(graph.device)
+        self._release = _lib.lib().ag_hetero_loader_release_batch
+        self._lock = threading.Lock()
+        self._next_seq = 0
+        self._seeds: dict[int, np.ndarray] = {}
+        self._fetched: list = []
+        self._fetch_buf = (_lib.HeteroBatch * _FETCH)()
+        self._closed = False
 
     def submit(self, batch_idx: int, seeds) -> None:
-        if self._stop:
+        if self._closed:
             raise SamplingError("Submit failed: loader is shut down")
-        s = coerce_seeds(seeds, self._seed_nodes).copy()
+        s = coerce_seeds(seeds, self._seed_nodes)
         with self._lock:
+            # The C call blocks while the work queue is full; the lock keeps the
+            # Python-side sequence counter in step with the library's.
             seq = self._next_seq
+            self._seeds[seq] = s
+            rc = _lib.lib().ag_hetero_loader_submit(self._h, int(batch_idx), s.ctypes.data if len(s) else None, len(s))
+            if rc != _lib.AG_OK:
+                del self._seeds[seq]
+                _lib.check(rc)
             self._next_seq += 1
-        try:
-            self._work.put((seq, int(batch_idx), s), timeout=self._TIMEOUT_S)
-        except queue.Full:
-            raise SamplingError("Submit failed: work queue full for 30 s") from None
-
-    def _take(self):
-        if self._seeded:
-            if self._deliver_seq in self._ready:
-                r = self._ready.pop(self._deliver_seq)
-                self._deliver_seq += 1
-                self._lock.notify_all()
-                return r
-            return None
-        return self._unordered.pop(0) if self._unordered else None
 
     def next_batch(self):
         """`(batch_idx, subgraph)`, or None after `shutdown()`; TimeoutError when
         nothing arrived within 30 s; RuntimeError once a worker failed."""
-        deadline = time.monotonic() + self._TIMEOUT_S
-        with self._lock:
-            first = True
-            while True:
-                r = self._take()
-                if r is not None:
-                    self._stats["total"] += 1
-                    self._stats["hits" if first else "misses"] += 1
-                    return r
-                if self._failed:
-                    raise RuntimeError(f"sampler worker exited: {self._failed}")
-                if self._stop:
-                    return None
-                first = False
-                left = deadline - time.monotonic()
-                if left <= 0:
-                    raise TimeoutError("no batch arrived within 30 s")
-                self._lock.wait(min(left, 0.5))
+        if not self._fetched:
+            if self._closed:
+                return None
+            got = C.c_uint32()
+            rc = _lib.lib().ag_hetero_loader_next_many(self._h, -1, _FETCH, self._fetch_buf, C.byref(got))
+            if rc == _lib.AG_ERR_SHUTDOWN:
+                return None
+            _lib.check(rc)
+            for i in range(got.value - 1, -1, -1):  # reversed: pop() hands them out in order
+                self._fetched.append(_lib.HeteroBatch.from_buffer_copy(self._fetch_buf[i]))
+        b = self._fetched.pop()
+        seeds = self._seeds.pop(b.seq)
+        sg = HeteroSampledSubgraph(self._graph, self._seed_type, seeds, b.counts, b.bufs, _HeteroLease(self, b), self._dims)
+        for t, d in enumerate(self._dims):
+            # a type that outgrew the rows reserved for it is gathered again, exactly
+            if d and b.counts.nodes[t] > b.bufs.cap_x[t]:
+                sg._x_override[t] = self._stores[t].gather(sg.nodes_t(self._graph._node_types[t][0]))
+        return int(b.batch_idx), sg
 
     def next(self):
         r = self.next_batch()
@@ -630,28 +593,14 @@ class HeteroNeighborLoader:
         return self._depth
 
     def stats(self) -> PrefetchStats:
-        c = _lib.LoaderStats()
-        c.hits, c.misses, c.total = self._stats["hits"], self._stats["misses"], self._stats["total"]
-        c.sample_time_ns, c.submitted = self._stats["sample_ns"], self._next_seq
-        return PrefetchStats(c)
+        s = _lib.LoaderStats()
+        _lib.check(_lib.lib().ag_hetero_loader_stats_get(self._h, C.byref(s)))
+        return PrefetchStats(s)
 
     def shutdown(self) -> None:
-        with self._lock:
-            if self._stop:
-                return
-            self._stop = True
-            self._lock.notify_all()
-        for _ in self._threads:
-            try:
-                self._work.put_nowait(None)
-            except queue.Full:
-                try:
-                    self._work.get_nowait()
-                    self._work.put_nowait(None)
-                except Exception:
-                    pass
-        for th in self._threads:
-            th.join(timeout=5)
+        if self._h:
+            _lib.lib().ag_hetero_loader_shutdown(self._h)
+        self._closed = True
 
     def __enter__(self):
         return self
@@ -660,10 +609,14 @@ class HeteroNeighborLoader:
         self.shutdown()
 
     def __del__(self):
-        try:
-            self.shutdown()
-        except Exception:
-            pass
+        h = getattr(self, "_h", None)
+        if h:
+            try:
+                self._fetched = []
+                _lib.lib().ag_hetero_loader_free(h)
+            except Exception:
+                pass
+            self._h = None
 
     def __repr__(self) -> str:
         return f"HeteroNeighborLoader(prefetch_depth={self._depth})"

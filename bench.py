@@ -729,8 +729,8 @@ def main():
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--workload", default=os.environ.get("AG_BENCH_WORKLOAD", "c2"),
                     choices=sorted(WORKLOADS) + sorted(HETERO))
-    ap.add_argument("--threads", type=int, default=int(os.environ.get("AG_BENCH_THREADS", "3")),
-                    help="loader worker threads, each with its own CUDA stream")
+    ap.add_argument("--threads", type=int, default=int(os.environ.get("AG_BENCH_THREADS", "0")),
+                    help="loader worker threads, each with its own CUDA stream (0: 3, heterogeneous workloads 2)")
     ap.add_argument("--depth", type=int, default=0, help="prefetch depth (0: max(8, group / 2))")
     ap.add_argument("--group", type=int, default=int(os.environ.get("AG_BENCH_GROUP", "0")),
                     help="batches a worker runs as one launch chain (0: chosen from --steps)")
@@ -742,6 +742,8 @@ def main():
                     help="run the resident (C ABI) leg only: no e2e, no CPU baseline (profiling runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
+    if args.threads <= 0:
+        args.threads = 2 if args.workload in HETERO else 3
     if args.workload in HETERO:
         return run_hetero(args, HETERO[args.workload])
     w = WORKLOADS[args.workload]

@@ -488,6 +488,42 @@ int32_t ag_loader_stats_get(const ag_loader *l, ag_loader_stats *stats);
 int32_t ag_loader_shutdown(ag_loader *l);
 void ag_loader_free(ag_loader *l);
 
+/* -------------------------------------------------- heterogeneous loader --
+ * Stands in for HeteroNeighborLoader (_core.pyi:680-720;
+ * crates/aethergraph-core/src/loader/prefetch.rs:984-1022 hetero workers,
+ * :1940-2060).  The contract of the loader above (sequence numbers, a work queue
+ * of 8 x prefetch_depth, in-order delivery and ag_batch_seed(seed, seq) per batch
+ * when seeded, 30 s timeouts, a failed worker poisons the loader) over the
+ * heterogeneous sampler: every batch is rooted at seed_type; `feats` is NULL or
+ * one feature store per node type (entries may be NULL), whose rows arrive in
+ * bufs.x[t].  Buffers always come from the loader's pool.  The rows reserved for
+ * x[t] follow the counts seen so far; a batch with counts.nodes[t] > bufs.cap_x[t]
+ * holds only the first cap_x[t] rows of that type, and the caller gathers the
+ * type again from bufs.nodes. */
+typedef struct ag_hetero_loader ag_hetero_loader;
+typedef struct {
+    int64_t batch_idx;
+    uint64_t seq;
+    ag_hetero_buffers bufs;
+    ag_hetero_counts counts;
+} ag_hetero_batch;
+
+int32_t ag_hetero_loader_create(const ag_hetero_graph *g, uint32_t seed_type, const uint32_t *fanout,
+                                uint32_t num_hops, int32_t replace, uint64_t seed, int32_t rng_mode,
+                                int32_t seeded, const ag_features *const *feats,
+                                uint32_t prefetch_depth, uint32_t sampler_threads, uint32_t group,
+                                ag_hetero_loader **out);
+/* Seeds are host ids of the seed type; one outside its range is AG_ERR_SAMPLING. */
+int32_t ag_hetero_loader_submit(ag_hetero_loader *l, int64_t batch_idx, const uint32_t *seeds,
+                                uint64_t n_seeds);
+int32_t ag_hetero_loader_next(ag_hetero_loader *l, int64_t timeout_ms, ag_hetero_batch *out);
+int32_t ag_hetero_loader_next_many(ag_hetero_loader *l, int64_t timeout_ms, uint32_t max_n,
+                                   ag_hetero_batch *out, uint32_t *n_out);
+int32_t ag_hetero_loader_release_batch(ag_hetero_loader *l, ag_hetero_batch *batch, void *stream);
+int32_t ag_hetero_loader_stats_get(const ag_hetero_loader *l, ag_loader_stats *stats);
+int32_t ag_hetero_loader_shutdown(ag_hetero_loader *l);
+void ag_hetero_loader_free(ag_hetero_loader *l);
+
 /* ------------------------------------------------------ synthetic inputs --
  * Seeded generators that build test and benchmark inputs directly in HBM
  * (no counterpart in the reference library; its benches generate synthetic

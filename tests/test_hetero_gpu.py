@@ -337,3 +337,75 @@ def test_stream_continues_when_the_handle_grows():
     for ns in (4, 2500, 10, 6000):
         seeds = rng.integers(0, 100, ns).astype(np.uint32)
         _same(s.sample(USER, seeds).raw_u32(), o.sample(0, seeds))
+
+
+def test_native_loader_features_pool_reuse_and_outgrown_reservations():
+    """The native hetero loader over many batches of changing size: x of every type ==
+    the stored rows of its node ids (also for a batch that outgrows the rows reserved
+    from earlier batches), sampled arrays == the oracle, pooled buffers recycled."""
+    import torch
+
+    import aethergraph_b200 as ag
+    from oracle import ago
+
+    rng = np.random.default_rng(91)
+    nn = {"a": 6000, "b": 3000}
+    e1 = (rng.integers(0, 6000, 60_000).astype(np.uint32), rng.integers(0, 3000, 60_000).astype(np.uint32))
+    ets = [("a", "to", "b"), ("b", "back", "a")]
+    g = ag.HeteroCsrGraph.from_edge_arrays(nn, [(*ets[0], *e1), (*ets[1], *e1[::-1])])
+    feats = {"a": ag.FeatureStore.from_array(rng.standard_normal((6000, 32)).astype(np.float32), dtype="bf16"),
+             "b": ag.FeatureStore.from_array(rng.standard_normal((3000, 5)).astype(np.float32), dtype="f32")}
+    rels = []
+    for (st, _, dt), (src, dst) in zip(ets, [e1, e1[::-1]]):
+        off, dd, _ = csr_from_edges(nn[st], src, dst)
+        rels.append((list(nn).index(st), list(nn).index(dt), off, dd))
+    fan = [[6, 4], [6, 4]]
+    o = ago.HeteroSampler([6000, 3000], rels, fan, seed=19)
+    sizes = [4] * 12 + [900] + [4] * 6 + [64] * 20 + [2000] + [64] * 10
+    batches = [rng.integers(0, 6000, n).astype(np.int64) for n in sizes]
+    cfg = ag.HeteroSamplingConfig(dict(zip(ets, fan)), seed=19)
+    with ag.HeteroNeighborLoader(g, cfg, "a", prefetch_depth=3, sampler_threads=2, features=feats, group=4) as ld:
+        sub = got = 0
+        while got < len(batches):
+            while sub < len(batches) and sub - got < 9:
+                ld.submit(sub, batches[sub])
+                sub += 1
+            idx, sg = ld.next_batch()
+            assert idx == got
+            o.reseed(ago.batch_seed(19, got))
+            _same(sg.raw_u32(), o.sample(0, batches[got].astype(np.uint32)))
+            for nt in nn:
+                ids = sg.nodes_t(nt)
+                x = sg.x_t(nt)
+                assert x.shape == (ids.shape[0], feats[nt].feature_dim)
+                assert torch.equal(x, feats[nt].gather(ids)), (got, nt)
+            del sg
+            got += 1
+        st = ld.stats()
+        assert st.total == len(batches) and st.submitted == len(batches)
+
+
+def test_native_loader_unseeded_delivers_every_batch_once_and_shuts_down():
+    import aethergraph_b200 as ag
+
+    g = _reddit_graph(ag)
+    cfg = ag.HeteroSamplingConfig({et: [3, 2] for et in ETS})  # no seed: arrival order, each worker its own stream
+    rng = np.random.default_rng(5)
+    ld = ag.HeteroNeighborLoader(g, cfg, USER, prefetch_depth=2, sampler_threads=3)
+    seen = set()
+    for i in range(12):
+        ld.submit(i, rng.integers(0, 100, 8))
+    for _ in range(12):
+        idx, sg = ld.next_batch()
+        assert idx not in seen
+        seen.add(idx)
+        assert len(sg.nodes(USER)) >= 1 and sg.seed_indices.shape == (8,)
+    assert seen == set(range(12))
+    ld.shutdown()
+    assert ld.next_batch() is None
+    with pytest.raises(ag.SamplingError, match="shut down"):
+        ld.submit(99, [1])
+    with pytest.raises(RuntimeError, match="prefetch_depth"):
+        ag.HeteroNeighborLoader(g, cfg, USER, prefetch_depth=0)
+    with pytest.raises(ag.SamplingError, match="unknown seed type"):
+        ag.HeteroNeighborLoader(g, cfg, "nobody")
