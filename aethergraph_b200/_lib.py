@@ -172,6 +172,10 @@ SIGNATURES = {
     "ag_loader_stats_get": (C.c_int32, [_P, C.POINTER(LoaderStats)]),
     "ag_loader_shutdown": (C.c_int32, [_P]),
     "ag_loader_free": (None, [_P]),
+    "ag_subgraph_mirror": (C.c_int32, [C.c_int32, C.c_uint64, C.c_uint64, _P, _P, _P, _P, _P, _P, _U64P, _P]),
+    "ag_subgraph_induce_plan": (C.c_int32, [_P, _P, C.c_uint64, _P, _PP, _U64P]),
+    "ag_subgraph_induce_fill": (C.c_int32, [_P, C.c_uint64, _P, _P, _P, _P, _P, _P, _P]),
+    "ag_subgraph_induce_free": (None, [_P]),
     "ag_hetero_loader_create": (C.c_int32, [_P, C.c_uint32, _P, C.c_uint32, C.c_int32, C.c_uint64, C.c_int32, C.c_int32,
                                             _P, C.c_uint32, C.c_uint32, C.c_uint32, _PP]),
     "ag_hetero_loader_submit": (C.c_int32, [_P, C.c_int64, _P, C.c_uint64]),

@@ -27,7 +27,8 @@ import numpy as np
 from . import _lib
 from .features import FeatureStore
 from .graph import CsrGraph
-from .sampler import SampledSubgraph, SamplingConfig, _Buffers, _check_config, coerce_seeds
+from .sampler import (SampledSubgraph, SamplingConfig, _Buffers, _check_config, apply_subgraph_type,
+                      coerce_seeds)
 
 __all__ = ["NeighborLoader", "PrefetchStats"]
 
@@ -198,7 +199,10 @@ class NeighborLoader:
         b = self._fetched.pop()
         seeds = self._seeds.pop(b.seq)
         bufs = _Buffers(b.bufs, _Lease(self, b), self._dev, self._dim)
-        return int(b.batch_idx), SampledSubgraph(bufs, b.counts, seeds)
+        sg = SampledSubgraph(bufs, b.counts, seeds)
+        if self.config.subgraph_type != "directional":
+            sg = apply_subgraph_type(self.graph, self.config.subgraph_type, sg)
+        return int(b.batch_idx), sg
 
     def next_batch(self):
         """`(batch_idx, subgraph, features)`, or None after `shutdown()`."""

@@ -78,8 +78,6 @@ class SamplingConfig:
             return "temporal sampling"
         if self.disjoint:
             return "disjoint sampling"
-        if self.subgraph_type != "directional":
-            return f"subgraph_type='{self.subgraph_type}'"
         if self.cumulative:
             return "cumulative sampling"
         if self.max_degree is not None and self.weighted:
@@ -196,7 +194,7 @@ class _Buffers:
         """Torch-allocated buffers only: mark `stream` as a user of the memory."""
         if isinstance(self.owner, tuple):
             for t in self.owner:
-                if t is not None:
+                if hasattr(t, "record_stream"):  # not a pool lease
                     t.record_stream(stream)
 
 
@@ -225,6 +223,15 @@ class SampledSubgraph:
         self.draws = counts.draws
         self._seeds = seeds
         self._cache = None
+
+    def _with_edges(self, bufs: "_Buffers", num_edges: int) -> "SampledSubgraph":
+        """The same batch with rewritten edge arrays; per-hop counts keep describing
+        the sampling pass (crates/aethergraph-core/src/loader/sampler.rs:1533-1536)."""
+        out = SampledSubgraph.__new__(SampledSubgraph)
+        out._b, out._n, out._e, out._s = bufs, self._n, num_edges, self._s
+        out._nodes_per_hop, out._edges_per_hop = self._nodes_per_hop, self._edges_per_hop
+        out.draws, out._seeds, out._cache = self.draws, self._seeds, None
+        return out
 
     # counts
     @property
@@ -354,6 +361,59 @@ class SampledSubgraph:
         return f"SampledSubgraph(num_nodes={self._n}, num_edges={self._e}, num_seeds={self._s})"
 
 
+def apply_subgraph_type(graph: CsrGraph, subgraph_type: str, sg: SampledSubgraph) -> SampledSubgraph:
+    """`subgraph_type` "bidirectional" / "induced" on a finished batch
+    (crates/aethergraph-core/src/loader/sampler.rs:964-1040): new edge arrays in GPU
+    memory, written by the library's rewrite kernels; nodes, seeds and x are shared
+    with the sampled batch."""
+    import torch
+
+    if subgraph_type == "directional":
+        return sg
+    L = _lib.lib()
+    b, e = sg._b, sg._e
+    dev = b.device
+    track = bool(b.c.edge_ids)
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        plan = None
+        if subgraph_type == "bidirectional":
+            cap = max(2 * e, 1)
+        else:
+            plan, n_out = C.c_void_p(), C.c_uint64()
+            _lib.check(L.ag_subgraph_induce_plan(graph._h, b.c.nodes, sg._n, stream, C.byref(plan), C.byref(n_out)))
+            cap = max(int(n_out.value), 1)
+        try:
+            cap4 = _align4(cap)
+            n64 = 2 * cap4 + (cap4 if track else 0)
+            arena = torch.empty(n64 + 2 * cap4, dtype=torch.int64, device=dev)
+            base64 = arena.data_ptr()
+            base32 = base64 + 8 * n64
+            c = _lib.SubgraphBuffers.from_buffer_copy(b.c)
+            c.cap_edges = cap
+            c.edge_index_local = base64
+            c.edge_ids = base64 + 16 * cap4 if track else None
+            c.edge_src, c.edge_dst = base32, base32 + 4 * cap4
+            c.src_local, c.dst_local = base32 + 8 * cap4, base32 + 12 * cap4
+            nb = _Buffers(c, (*(b.owner if isinstance(b.owner, tuple) else (b.owner,)), arena), dev, b.dim)
+            if subgraph_type == "bidirectional":
+                for name in ("edge_src", "edge_dst", "src_local", "dst_local"):
+                    if e:
+                        nb.view(getattr(c, name), (e,), "<i4").copy_(b.view(getattr(b.c, name), (e,), "<i4"))
+                if track and e:
+                    nb.view(c.edge_ids, (e,), "<i8").copy_(b.view(b.c.edge_ids, (e,), "<i8"))
+                n_out = C.c_uint64()
+                _lib.check(L.ag_subgraph_mirror(dev.index, e, cap, c.edge_src, c.edge_dst, c.src_local, c.dst_local,
+                                                c.edge_ids, c.edge_index_local, C.byref(n_out), stream))
+            else:
+                _lib.check(L.ag_subgraph_induce_fill(plan, cap, c.edge_src, c.edge_dst, c.src_local, c.dst_local,
+                                                     c.edge_ids, c.edge_index_local, stream))
+        finally:
+            if plan is not None and plan.value:
+                L.ag_subgraph_induce_free(plan)
+    return sg._with_edges(nb, int(n_out.value))
+
+
 class _Handle:
     """One ag_sampler: scratch for one group of batches in flight."""
 
@@ -403,7 +463,9 @@ class _PendingGroup:
             n = len(self._bufs)
             counts = (_lib.SampleCounts * n)()
             _lib.check(_lib.lib().ag_sample_group_wait(self._handle.h, counts, None))
-            self._done = [SampledSubgraph(b, c, s) for b, c, s in zip(self._bufs, counts, self._seeds)]
+            kind = self._handle.config.subgraph_type
+            self._done = [apply_subgraph_type(self._handle.graph, kind, SampledSubgraph(b, c, s))
+                          for b, c, s in zip(self._bufs, counts, self._seeds)]
             self._keep = None
         return self._done
 

@@ -488,6 +488,37 @@ int32_t ag_loader_stats_get(const ag_loader *l, ag_loader_stats *stats);
 int32_t ag_loader_shutdown(ag_loader *l);
 void ag_loader_free(ag_loader *l);
 
+/* ---------------------------------------------------- subgraph rewrites --
+ * SamplingConfig.subgraph_type other than "directional"
+ * (crates/aethergraph-core/src/loader/sampler.rs:964-1040 apply_subgraph_type),
+ * applied to the device arrays of a finished batch.  Per-hop counts keep
+ * describing the sampling pass (sampler.rs:1533-1536).  All calls synchronise
+ * `stream` before they return.
+ *
+ * Bidirectional (`mirror`, sampler.rs:1015-1040): the n_edges sampled edges stay;
+ * walking them in order, the reverse of edge i (endpoints and locals swapped, same
+ * edge id) is appended unless its (src_local, dst_local) pair is already among the
+ * sampled edges or the reverses appended before it.  The u32 arrays (and edge_ids,
+ * optional) need room for cap_edges >= 2 * n_edges entries; edge_index_local
+ * (optional, room for [2, cap_edges]) is rewritten as [2, *n_edges_out]. */
+int32_t ag_subgraph_mirror(int32_t device, uint64_t n_edges, uint64_t cap_edges, uint32_t *edge_src,
+                           uint32_t *edge_dst, uint32_t *src_local, uint32_t *dst_local,
+                           uint64_t *edge_ids, int64_t *edge_index_local, uint64_t *n_edges_out,
+                           void *stream);
+/* Induced (`induce`, sampler.rs:972-1013): the edges become every stored edge
+ * u -> w with both ends among the n_nodes sampled nodes (device u32 ids, distinct),
+ * ordered by u's local index, then by position in u's row; edge id = CSR position.
+ * Two steps, because the edge count is only known after counting: plan (returns
+ * the count), then fill into arrays of at least that capacity.  nodes_dev must
+ * stay valid until the plan is freed. */
+typedef struct ag_induce_plan ag_induce_plan;
+int32_t ag_subgraph_induce_plan(const ag_graph *g, const uint32_t *nodes_dev, uint64_t n_nodes,
+                                void *stream, ag_induce_plan **out, uint64_t *n_edges_out);
+int32_t ag_subgraph_induce_fill(ag_induce_plan *plan, uint64_t cap_edges, uint32_t *edge_src,
+                                uint32_t *edge_dst, uint32_t *src_local, uint32_t *dst_local,
+                                uint64_t *edge_ids, int64_t *edge_index_local, void *stream);
+void ag_subgraph_induce_free(ag_induce_plan *plan);
+
 /* -------------------------------------------------- heterogeneous loader --
  * Stands in for HeteroNeighborLoader (_core.pyi:680-720;
  * crates/aethergraph-core/src/loader/prefetch.rs:984-1022 hetero workers,

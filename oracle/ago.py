@@ -383,6 +383,55 @@ class Sampler:
                 "seconds": res.seconds, "threads": res.threads, "checksum": res.checksum}
 
 
+def mirror(sub: dict) -> dict:
+    """Bidirectional rewrite of one sampled subgraph
+    (crates/aethergraph-core/src/loader/sampler.rs:1015-1040 `mirror`): the sampled
+    edges stay as they are, then, walking them in order, the reverse of edge i is
+    appended unless its (src_local, dst_local) pair is already present among the
+    sampled edges or the reverses appended so far; a reverse carries its forward
+    edge's id.  Per-hop counts are those of the sampling pass."""
+    sl, dl = sub["src_local"], sub["dst_local"]
+    pairs = {(int(a), int(b)) for a, b in zip(sl, dl)}
+    keep = []
+    for i, (a, b) in enumerate(zip(sl, dl)):
+        r = (int(b), int(a))
+        if r in pairs:
+            continue
+        pairs.add(r)
+        keep.append(i)
+    k = np.array(keep, dtype=np.int64)
+    out = dict(sub)
+    out["edge_src"] = np.concatenate([sub["edge_src"], sub["edge_dst"][k]])
+    out["edge_dst"] = np.concatenate([sub["edge_dst"], sub["edge_src"][k]])
+    out["src_local"] = np.concatenate([sl, dl[k]])
+    out["dst_local"] = np.concatenate([dl, sl[k]])
+    if sub.get("edge_ids") is not None:
+        out["edge_ids"] = np.concatenate([sub["edge_ids"], sub["edge_ids"][k]])
+    return out
+
+
+def induce(offsets, edges, sub: dict) -> dict:
+    """Induced rewrite (sampler.rs:972-1013 `induce`, no timestamps): the sampled edges
+    are replaced by every stored edge u -> w with both ends among the sampled nodes,
+    in the order of u's local index, then of the position in u's row; the edge id is
+    the CSR position."""
+    nodes = sub["nodes"]
+    local = {int(v): i for i, v in enumerate(nodes)}
+    es, ed, sl, dl, ids = [], [], [], [], []
+    for u_local, u in enumerate(nodes):
+        lo, hi = int(offsets[int(u)]), int(offsets[int(u) + 1])
+        for pos in range(lo, hi):
+            w = int(edges[pos])
+            w_local = local.get(w)
+            if w_local is not None:
+                es.append(int(u)); ed.append(w); sl.append(u_local); dl.append(w_local); ids.append(pos)
+    out = dict(sub)
+    out["edge_src"], out["edge_dst"] = np.array(es, dtype=np.uint32), np.array(ed, dtype=np.uint32)
+    out["src_local"], out["dst_local"] = np.array(sl, dtype=np.uint32), np.array(dl, dtype=np.uint32)
+    out["edge_ids"] = np.array(ids, dtype=np.uint64) if sub.get("edge_ids") is not None else None
+    return out
+
+
 def transpose(offsets, edges, num_src: int, num_dst: int):
     keep = []
     csr = _csr_struct(offsets, edges, None, keep)

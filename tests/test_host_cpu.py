@@ -92,7 +92,8 @@ def test_sampling_config_validation():
     assert ag.SamplingConfig([3], disjoint=True)._unsupported() == "disjoint sampling"
     assert ag.SamplingConfig([3], cumulative=True)._unsupported() == "cumulative sampling"
     assert ag.SamplingConfig([3], temporal_strategy="last")._unsupported() == "temporal sampling"
-    assert "induced" in ag.SamplingConfig([3], subgraph_type="induced")._unsupported()
+    assert ag.SamplingConfig([3], subgraph_type="induced")._unsupported() is None  # rewrites run on the GPU
+    assert ag.SamplingConfig([3], subgraph_type="bidirectional")._unsupported() is None
     c = cfg._to_c(7, 128)
     assert (c.num_hops, c.fanout[0], c.fanout[1], c.seed, c.max_seeds, c.rng_mode) == (2, 25, 10, 7, 128, 0)
 

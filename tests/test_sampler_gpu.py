@@ -156,8 +156,7 @@ def test_config_errors(ag, rmat12):
         ag.SamplingConfig(num_neighbors=[3, -1])
     with pytest.raises(ValueError, match="no edge weights"):
         ag.NeighborSampler(g, ag.SamplingConfig(num_neighbors=[3], weighted=True))
-    for kw in ({"disjoint": True}, {"cumulative": True}, {"subgraph_type": "induced"},
-               {"temporal_strategy": "last"}):
+    for kw in ({"disjoint": True}, {"cumulative": True}, {"temporal_strategy": "last"}):
         with pytest.raises(ValueError, match="not supported"):
             ag.NeighborSampler(g, ag.SamplingConfig(num_neighbors=[3], **kw))
 
