@@ -315,6 +315,8 @@ def run_device(args, w):
     sz_i64, sz_ptr, sz_u64, sz_buf = C.sizeof(C.c_int64), C.sizeof(C.c_void_p), C.sizeof(C.c_uint64), \
         C.sizeof(_lib.SubgraphBuffers)
 
+    recent: list = []  # (n_id pointer, node count) of the last `group` delivered batches
+
     def run_resident(first: int, count: int):
         """Submit batches [first, first+count) with device seeds; returns (edges, nodes)."""
         edges = nodes = 0
@@ -331,6 +333,8 @@ def run_device(args, w):
             for j in range(n_out.value):
                 edges += out_batches[j].counts.num_edges
                 nodes += out_batches[j].counts.num_nodes
+                recent.append((out_batches[j].bufs.n_id, out_batches[j].counts.num_nodes))
+            del recent[:-group]
             delivered += n_out.value
         return edges, nodes
 
@@ -380,6 +384,31 @@ def run_device(args, w):
                                       / (ms * 1e-3) / 1e9) / (peak * world),
                      "sample_ms_per_batch": s_ms / n_timed},
     }
+    # The same kernel on its own: the node ids of the last delivered batches, gathered
+    # by one standalone launch per repetition with nothing else on the GPU (what the
+    # committed ncu capture measures; the in-pipeline figure above shares the SMs and
+    # HBM with the other workers' sampling kernels).
+    if recent and not args.only_value:
+        holder = _Buffers(ring[0].c, ring, dev, w["dim"])  # the ring keeps the memory alive
+        ids = torch.cat([holder.view(ptr, (int(n),), "<i8") for ptr, n in recent])
+        x_alone = torch.empty((ids.shape[0], w["dim"]), dtype=torch.float32, device=dev)
+        for _ in range(3):
+            feats.gather(ids, out=x_alone)
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize(dev)
+        reps = 10
+        a0.record()
+        for _ in range(reps):
+            feats.gather(ids, out=x_alone)
+        a1.record()
+        torch.cuda.synchronize(dev)
+        alone_ms = a0.elapsed_time(a1) / reps
+        alone_gbs = ids.shape[0] * row_bytes / (alone_ms * 1e-3) / 1e9
+        roofline["alone"] = {"achieved": alone_gbs, "frac": alone_gbs / peak, "ms_per_launch": alone_ms,
+                             "rows_per_launch": int(ids.shape[0]), "launches": reps,
+                             "note": "same kernel and ids, one launch at a time on an otherwise idle GPU; "
+                                     "working set per launch exceeds L2"}
+        del ids, x_alone
     L.ag_loader_free(h)
     del ring
 
