@@ -162,6 +162,7 @@ SIGNATURES = {
     "ag_hetero_sampler_free": (None, [_P]),
     "ag_loader_create": (C.c_int32, [_P, _P, C.POINTER(SamplingConfigC), C.c_int32, C.c_uint32, C.c_uint32,
                                      C.c_uint32, C.c_int32, _PP]),
+    "ag_loader_set_seed_sequence": (C.c_int32, [_P, C.c_uint64, C.c_uint64]),
     "ag_loader_bounds": (C.c_int32, [_P, C.c_uint64, _U64P, _U64P]),
     "ag_loader_submit": (C.c_int32, [_P, C.c_int64, _P, C.c_uint64, C.c_int32, C.POINTER(SubgraphBuffers), _P]),
     "ag_loader_next": (C.c_int32, [_P, C.c_int64, C.POINTER(Batch)]),

@@ -570,6 +570,11 @@ extern "C" void ag_features_free(ag_features *f) {
     DeviceGuard guard(f->device);
     if (f->owns_payload) cudaFree(f->payload);
     for (void *p : f->ipc_opened) if (p) cudaIpcCloseMemHandle(p);
+    if (f->sort) {
+        if (f->sort->done) { cudaEventSynchronize(f->sort->done); cudaEventDestroy(f->sort->done); }
+        f->sort->scratch.release();
+        delete f->sort;
+    }
     cudaFree(f->shards);
     cudaFree(f->err);
     delete f;
@@ -749,6 +754,20 @@ extern "C" int32_t ag_gather(const ag_features *f, const void *ids_dev, int32_t 
     GatherArgs a{};
     set_gather_source(a, f);
     a.ids = ids_dev; a.ids64 = ids_are_i64; a.n = n; a.n_dev = n_dev; a.out = out_dev;
+    const bool aligned = ((uintptr_t)a.payload % 16) == 0 && ((uintptr_t)out_dev % 16) == 0;
+    if (f->sort && n >= 2048 && n < (1ull << 23) && sorted_gather_applies(f, a.row_bytes, aligned)) {
+        // Remote rows in address order (gather.cu).  The view owns one sort scratch:
+        // this call's kernels wait for the previous call's, whatever stream that used.
+        cudaStream_t st = (cudaStream_t)stream;
+        std::lock_guard<std::mutex> lk(f->sort->m);
+        if (!f->sort->done) AG_CUDA(cudaEventCreateWithFlags(&f->sort->done, cudaEventDisableTiming));
+        if (f->sort->used) AG_CUDA(cudaStreamWaitEvent(st, f->sort->done, 0));
+        if (n > f->sort->scratch.cap && f->sort->used) AG_CUDA(cudaEventSynchronize(f->sort->done));  // about to be freed
+        AG_CUDA(launch_gather_sorted(a, nullptr, 1, n, a.row_bytes, a.dim, f->dtype, f, f->sort->scratch, st));
+        AG_CUDA(cudaEventRecord(f->sort->done, st));
+        f->sort->used = true;
+        return AG_OK;
+    }
     AG_CUDA(launch_gather(a, f->dtype, (cudaStream_t)stream));
     return AG_OK;
 }

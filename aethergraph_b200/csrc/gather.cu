@@ -18,6 +18,8 @@
 // count) without a host round trip.
 #include <algorithm>
 
+#include <cub/device/device_radix_sort.cuh>
+
 #include "common.cuh"
 #include "internal.h"
 
@@ -113,7 +115,7 @@ __device__ __forceinline__ const uint8_t *shard_row(const ag_shard_table *t, uin
 // owner's memory (local HBM or a peer over NVLink), upcast at the reader.
 template <int DTYPE, int LPR, bool SHARDED>
 __global__ void __launch_bounds__(kThreads)
-k_gather_vec(GatherArgs a, const GatherArgs *__restrict__ group) {
+k_gather_vec(GatherArgs a, const GatherArgs *__restrict__ group, uint64_t first) {
     constexpr int kRowsPerBlock = kThreads / LPR;
     if (group) a = group[blockIdx.y];  // one batch of a group per grid row
     if (!a.payload) return;
@@ -130,7 +132,8 @@ k_gather_vec(GatherArgs a, const GatherArgs *__restrict__ group) {
     const uint64_t stride = kRowsPerBlock;
     const uint64_t pol = l2_evict_first_policy();
 
-    for (uint64_t base = (uint64_t)blockIdx.x * kChunk + sub; base < n; base += (uint64_t)gridDim.x * kChunk) {
+    // `first`: rows before it are somebody else's (the sorted gather's overflow pass).
+    for (uint64_t base = first + (uint64_t)blockIdx.x * kChunk + sub; base < n; base += (uint64_t)gridDim.x * kChunk) {
         for (uint32_t v0 = 0; v0 < vecs; v0 += LPR) {
             const uint32_t v = v0 + lane;
             uint4 val[kInFlight];
@@ -199,20 +202,21 @@ k_gather_elem(GatherArgs a, const GatherArgs *__restrict__ group) {
 }
 
 template <int DTYPE, bool SHARDED>
-cudaError_t launch_vec_s(const GatherArgs &a, const GatherArgs *group, uint32_t row_bytes, dim3 grid, cudaStream_t st) {
+cudaError_t launch_vec_s(const GatherArgs &a, const GatherArgs *group, uint32_t row_bytes, dim3 grid, cudaStream_t st,
+                         uint64_t first) {
     const uint32_t vecs = row_bytes >> 4;
-    if (vecs <= 4) k_gather_vec<DTYPE, 4, SHARDED><<<grid, kThreads, 0, st>>>(a, group);
-    else if (vecs <= 8) k_gather_vec<DTYPE, 8, SHARDED><<<grid, kThreads, 0, st>>>(a, group);
-    else if (vecs <= 16) k_gather_vec<DTYPE, 16, SHARDED><<<grid, kThreads, 0, st>>>(a, group);
-    else k_gather_vec<DTYPE, 32, SHARDED><<<grid, kThreads, 0, st>>>(a, group);
+    if (vecs <= 4) k_gather_vec<DTYPE, 4, SHARDED><<<grid, kThreads, 0, st>>>(a, group, first);
+    else if (vecs <= 8) k_gather_vec<DTYPE, 8, SHARDED><<<grid, kThreads, 0, st>>>(a, group, first);
+    else if (vecs <= 16) k_gather_vec<DTYPE, 16, SHARDED><<<grid, kThreads, 0, st>>>(a, group, first);
+    else k_gather_vec<DTYPE, 32, SHARDED><<<grid, kThreads, 0, st>>>(a, group, first);
     return cudaGetLastError();
 }
 
 template <int DTYPE>
 cudaError_t launch_vec(const GatherArgs &a, const GatherArgs *group, uint32_t row_bytes, dim3 grid, bool sharded,
-                       cudaStream_t st) {
-    return sharded ? launch_vec_s<DTYPE, true>(a, group, row_bytes, grid, st)
-                   : launch_vec_s<DTYPE, false>(a, group, row_bytes, grid, st);
+                       cudaStream_t st, uint64_t first = 0) {
+    return sharded ? launch_vec_s<DTYPE, true>(a, group, row_bytes, grid, st, first)
+                   : launch_vec_s<DTYPE, false>(a, group, row_bytes, grid, st, first);
 }
 
 // f32 -> stored dtype, used to build a store from f32 rows on the device.
@@ -255,6 +259,125 @@ __global__ void k_encode(const float *src, uint16_t *dst, uint64_t count, int dt
         }
         dst[i] = o;
     }
+}
+
+
+// ------------------------------------------------- address-ordered gather --
+// A sharded store's remote rows arrive over NVLink through mappings of the
+// peers' memory.  Random rows spread over tens of gigabytes of such mappings
+// run far below the link's bandwidth (every row needs an address translation
+// that is no longer cached); the same rows requested in address order run at
+// the link's bandwidth.  So a launch first turns its row ids into address-order
+// keys, sorts them (in local memory) together with the output position of each
+// row, and gathers in that order.  The f32 rows are still written at their
+// original positions in local HBM, where order costs nothing.
+//
+// key = row-within-shard * W + owner.  Within one owner the rows ascend, and
+// neighbouring keys alternate between the owners, so at any moment a GPU pulls
+// from all its peers at once (no owner's links are the only ones busy) while
+// each owner is still read in ascending address order.  For round-robin shards
+// the key IS the vertex id; for contiguous ranges it is (id % S) * W + id / S.
+//
+// Sorting has a second use: the batches of one launch chain name many rows more
+// than once (hub vertices turn up in most batches of a chain).  Equal keys are
+// neighbours after the sort, so a row is loaded once — crosses the link once —
+// and written to every batch that asked for it.
+constexpr uint32_t kValRowBits = 23;  // value = batch << 23 | row: rows per batch < 2^23, batches per chain <= 256
+
+__device__ __forceinline__ uint32_t addr_key(const ag_shard_table *t, uint64_t id) {
+    if (t->cyclic) return (uint32_t)id;
+    const uint64_t s = id / t->shard_rows;
+    return (uint32_t)((id - s * t->shard_rows) * t->n_shards + s);
+}
+
+__global__ void __launch_bounds__(256)
+k_make_keys(GatherArgs a, const GatherArgs *__restrict__ group, uint32_t rows_cap, uint32_t sentinel,
+            uint32_t *__restrict__ keys, uint32_t *__restrict__ vals) {
+    if (group) a = group[blockIdx.y];
+    uint64_t n = 0;
+    if (a.payload) n = a.n_dev ? min((uint64_t)*a.n_dev, a.n) : a.n;
+    if (a.ids_off) a.ids = (const uint32_t *)a.ids + *a.ids_off;
+    const uint64_t slot0 = (uint64_t)blockIdx.y * rows_cap;
+    for (uint32_t r = blockIdx.x * blockDim.x + threadIdx.x; r < rows_cap; r += gridDim.x * blockDim.x) {
+        uint32_t key = sentinel;  // slots past the batch's rows sort to the end
+        if (r < n) {
+            const uint64_t id = load_id(a.ids, a.ids64, r);
+            if (id >= a.row_begin && id - a.row_begin < a.rows) key = addr_key(a.shards, id);
+            else atomicOr(a.err, kErrBadId);
+        }
+        keys[slot0 + r] = key;
+        vals[slot0 + r] = (blockIdx.y << kValRowBits) | r;
+    }
+}
+
+template <int DTYPE, int LPR>
+__global__ void __launch_bounds__(kThreads)
+k_gather_sorted(GatherArgs one, const GatherArgs *__restrict__ group, const ag_shard_table *__restrict__ t,
+                const uint32_t *__restrict__ keys, const uint32_t *__restrict__ vals, uint64_t n_items,
+                uint32_t sentinel, uint32_t row_bytes, uint32_t dim) {
+    constexpr int kRowsPerBlock = kThreads / LPR;
+    constexpr uint64_t kChunk = (uint64_t)kRowsPerBlock * kInFlight;
+    const int lane = threadIdx.x % LPR;
+    const int sub = threadIdx.x / LPR;
+    const uint32_t vecs = row_bytes >> 4;
+    const uint32_t out_per_vec = (DTYPE == AG_F32) ? 4u : 8u;
+    const uint32_t W = t->n_shards;
+    for (uint64_t chunk0 = (uint64_t)blockIdx.x * kChunk; chunk0 < n_items; chunk0 += (uint64_t)gridDim.x * kChunk) {
+        if (keys[chunk0] == sentinel) return;  // sorted: nothing but padding from here on
+        const uint64_t base = chunk0 + sub;
+        for (uint32_t v0 = 0; v0 < vecs; v0 += LPR) {
+            const uint32_t v = v0 + lane;
+            uint4 val[kInFlight];
+            uint32_t key[kInFlight];
+            bool head[kInFlight];
+#pragma unroll
+            for (int u = 0; u < kInFlight; ++u) {
+                const uint64_t i = base + (uint64_t)u * kRowsPerBlock;
+                head[u] = false;
+                val[u] = make_uint4(0, 0, 0, 0);
+                key[u] = sentinel;
+                if (i < n_items && v < vecs) {
+                    key[u] = keys[i];
+                    // the first of a run of equal keys fetches the row for the whole run
+                    head[u] = key[u] != sentinel && (i == 0 || keys[i - 1] != key[u]);
+                    if (head[u]) {
+                        const uint32_t owner = key[u] % W;
+                        const uint64_t local = key[u] / W;
+                        val[u] = ld_peer_v4(t->base[owner] + local * row_bytes + ((uint64_t)v << 4));
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kInFlight; ++u) {
+                if (!head[u]) continue;
+                uint64_t j = base + (uint64_t)u * kRowsPerBlock;
+                do {
+                    const uint32_t pv = vals[j];
+                    float *out = group ? group[pv >> kValRowBits].out : one.out;
+                    store_decoded<DTYPE>(out + (uint64_t)(pv & ((1u << kValRowBits) - 1u)) * dim + (uint64_t)v * out_per_vec, val[u]);
+                    ++j;
+                } while (j < n_items && keys[j] == key[u]);
+            }
+        }
+    }
+}
+
+template <int DTYPE>
+cudaError_t launch_sorted(const GatherArgs &one, const GatherArgs *group, const ag_shard_table *t, const uint32_t *keys,
+                          const uint32_t *vals, uint64_t n_items, uint32_t sentinel, uint32_t row_bytes, uint32_t dim,
+                          int blocks, cudaStream_t st) {
+    const uint32_t vecs = row_bytes >> 4;
+    if (vecs <= 4) k_gather_sorted<DTYPE, 4><<<blocks, kThreads, 0, st>>>(one, group, t, keys, vals, n_items, sentinel, row_bytes, dim);
+    else if (vecs <= 8) k_gather_sorted<DTYPE, 8><<<blocks, kThreads, 0, st>>>(one, group, t, keys, vals, n_items, sentinel, row_bytes, dim);
+    else if (vecs <= 16) k_gather_sorted<DTYPE, 16><<<blocks, kThreads, 0, st>>>(one, group, t, keys, vals, n_items, sentinel, row_bytes, dim);
+    else k_gather_sorted<DTYPE, 32><<<blocks, kThreads, 0, st>>>(one, group, t, keys, vals, n_items, sentinel, row_bytes, dim);
+    return cudaGetLastError();
+}
+
+uint32_t bit_width_u64(uint64_t v) {
+    uint32_t b = 0;
+    while (v) { ++b; v >>= 1; }
+    return b;
 }
 
 }  // namespace
@@ -324,6 +447,78 @@ cudaError_t launch_gather_group(const GatherArgs *group_dev, uint32_t n_batches,
         default: k_gather_elem<AG_BF16><<<grid, kThreads, 0, st>>>(none, group_dev); break;
     }
     return cudaGetLastError();
+}
+
+// ------------------------------------------------ sorted gather, host side --
+void SortScratch::release() {
+    cudaFree(keys[0]); cudaFree(keys[1]); cudaFree(vals[0]); cudaFree(vals[1]); cudaFree(temp);
+    keys[0] = keys[1] = vals[0] = vals[1] = nullptr; temp = nullptr;
+    cap = 0; temp_bytes = 0;
+}
+
+cudaError_t SortScratch::ensure(uint64_t items) {
+    if (items <= cap) return cudaSuccess;
+    release();
+    const uint64_t want = items + items / 4 + 1024;  // grow with headroom: the estimate moves from chain to chain
+    size_t tb = 0;
+    cudaError_t e = cub::DeviceRadixSort::SortPairs(nullptr, tb, (const uint32_t *)nullptr, (uint32_t *)nullptr,
+                                                    (const uint32_t *)nullptr, (uint32_t *)nullptr, want, 0, 32, (cudaStream_t)0);
+    if (e != cudaSuccess) return e;
+    for (int i = 0; i < 2 && e == cudaSuccess; ++i) {
+        e = cudaMalloc(&keys[i], want * 4);
+        if (e == cudaSuccess) e = cudaMalloc(&vals[i], want * 4);
+    }
+    if (e == cudaSuccess) e = cudaMalloc(&temp, std::max<size_t>(tb, 16));
+    if (e != cudaSuccess) { release(); return e; }
+    cap = want; temp_bytes = tb;
+    return cudaSuccess;
+}
+
+bool sorted_gather_applies(const ag_features *f, uint32_t row_bytes, bool aligned) {
+    static const bool enabled = [] {
+        const char *v = getenv("AG_GATHER_SORTED");  // "0": keep the unsorted peer-load gather (A/B measurements)
+        return !(v && v[0] == '0');
+    }();
+    if (!enabled || !f || !f->shards || f->n_shards < 2 || !aligned || row_bytes % 16 != 0) return false;
+    // keys are 32 bits and one value above the largest key is the padding mark
+    return f->shard_rows * f->n_shards < 0xFFFFFFFFull;
+}
+
+// Gathers rows [0, min(n_b, rows_cap)) of every batch in address order, then rows
+// [rows_cap, n_b) — only present when a batch outgrew the caller's estimate — with
+// the unsorted kernel.  `one` / `group_dev` as in launch_gather / launch_gather_group.
+cudaError_t launch_gather_sorted(const GatherArgs &one, const GatherArgs *group_dev, uint32_t n_batches, uint64_t rows_cap,
+                                 uint32_t row_bytes, uint32_t dim, int dtype, const ag_features *f, SortScratch &sc,
+                                 cudaStream_t st) {
+    if (n_batches == 0 || rows_cap == 0) return cudaSuccess;
+    rows_cap = std::min<uint64_t>(rows_cap, (1ull << kValRowBits) - 1);
+    const uint64_t n_items = (uint64_t)n_batches * rows_cap;
+    cudaError_t e = sc.ensure(n_items);
+    if (e != cudaSuccess) return e;
+    const uint64_t max_key = f->shard_rows * f->n_shards;  // one past the largest key
+    const uint32_t bits = bit_width_u64(max_key);
+    const uint32_t sentinel = bits >= 32 ? 0xFFFFFFFFu : ((1u << bits) - 1u);
+    const uint32_t kb = (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>((rows_cap + 255) / 256, std::max<uint64_t>(1, (uint64_t)kSMs * 8 / n_batches)));
+    k_make_keys<<<dim3(kb, n_batches), 256, 0, st>>>(one, group_dev, (uint32_t)rows_cap, sentinel, sc.keys[0], sc.vals[0]);
+    if ((e = cudaGetLastError()) != cudaSuccess) return e;
+    size_t tb = sc.temp_bytes;
+    e = cub::DeviceRadixSort::SortPairs(sc.temp, tb, (const uint32_t *)sc.keys[0], sc.keys[1], (const uint32_t *)sc.vals[0],
+                                        sc.vals[1], n_items, 0, (int)bits, st);
+    if (e != cudaSuccess) return e;
+    const int blocks = gather_grid_blocks(n_items, row_bytes);
+    switch (dtype) {
+        case AG_F32: e = launch_sorted<AG_F32>(one, group_dev, f->shards, sc.keys[1], sc.vals[1], n_items, sentinel, row_bytes, dim, blocks, st); break;
+        case AG_F16: e = launch_sorted<AG_F16>(one, group_dev, f->shards, sc.keys[1], sc.vals[1], n_items, sentinel, row_bytes, dim, blocks, st); break;
+        default: e = launch_sorted<AG_BF16>(one, group_dev, f->shards, sc.keys[1], sc.vals[1], n_items, sentinel, row_bytes, dim, blocks, st); break;
+    }
+    if (e != cudaSuccess) return e;
+    // Rows past the estimate (rare): a few blocks per batch, which stride; most exit at once.
+    const dim3 grid(4, n_batches);
+    switch (dtype) {
+        case AG_F32: return launch_vec<AG_F32>(one, group_dev, row_bytes, grid, true, st, rows_cap);
+        case AG_F16: return launch_vec<AG_F16>(one, group_dev, row_bytes, grid, true, st, rows_cap);
+        default: return launch_vec<AG_BF16>(one, group_dev, row_bytes, grid, true, st, rows_cap);
+    }
 }
 
 cudaError_t launch_encode(const float *src, void *dst, uint64_t count, int dtype, cudaStream_t st) {

@@ -4,9 +4,24 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
 #include <vector>
 
 #include "../../include/aethergpu.h"
+
+namespace ag {
+// Device scratch of the address-ordered gather: two key and two value arrays for
+// the radix sort and its temporary storage.  Grows, never shrinks.
+struct SortScratch {
+    uint32_t *keys[2] = {nullptr, nullptr};
+    uint32_t *vals[2] = {nullptr, nullptr};
+    void *temp = nullptr;
+    size_t temp_bytes = 0;
+    uint64_t cap = 0;  // items the arrays hold
+    cudaError_t ensure(uint64_t items);
+    void release();
+};
+}  // namespace ag
 
 struct ag_graph {
     int device = 0;
@@ -32,7 +47,17 @@ struct ag_features {
     // own shard or a peer's mapped into this process.
     struct ag_shard_table *shards = nullptr;  // device copy of the table, or null
     uint32_t n_shards = 0;
+    uint64_t shard_rows = 0;                  // rows per shard (the last may hold fewer)
+    bool shard_cyclic = false;                // rows dealt round-robin instead of contiguous ranges
     void *ipc_opened[8] = {nullptr};          // peer mappings this view opened (closed on free)
+    // ag_gather on a sharded view sorts its ids into address order first; the scratch
+    // belongs to the view, calls take turns (mutex on the host, event on the device).
+    struct SortState {
+        std::mutex m;
+        ag::SortScratch scratch;
+        cudaEvent_t done = nullptr;
+        bool used = false;
+    } *sort = nullptr;
 };
 
 // Device-visible table of a sharded feature store.
@@ -72,6 +97,11 @@ cudaError_t launch_gather(const GatherArgs &a, int dtype, cudaStream_t st);
 cudaError_t launch_gather_group(const GatherArgs *group_dev, uint32_t n_batches, uint32_t row_bytes,
                                 uint32_t dim, uint64_t n_bound, bool aligned, int dtype, bool sharded,
                                 cudaStream_t st);
+// Address-ordered gather over a sharded view (see gather.cu).
+bool sorted_gather_applies(const ag_features *f, uint32_t row_bytes, bool aligned);
+cudaError_t launch_gather_sorted(const GatherArgs &one, const GatherArgs *group_dev, uint32_t n_batches, uint64_t rows_cap,
+                                 uint32_t row_bytes, uint32_t dim, int dtype, const ag_features *f, SortScratch &sc,
+                                 cudaStream_t st);
 cudaError_t launch_encode(const float *src, void *dst, uint64_t count, int dtype, cudaStream_t st);
 int gather_grid_blocks(uint64_t n, uint32_t row_bytes);
 

@@ -74,6 +74,10 @@ struct ag_loader {
     std::map<uint64_t, Done> ready;      // finished batches keyed by seq
     std::deque<uint64_t> arrival;        // completion order, for unseeded delivery
     uint64_t next_seq = 0, next_deliver = 0, in_ready = 0;
+    // Batch number seq draws from ag_batch_seed(cfg.seed, seed_base + seed_stride * seq):
+    // rank r of a W-rank job sets (r, W), so global batch b is sampled from the same
+    // stream whatever W is.  Atomic: workers read them without the queue lock.
+    std::atomic<uint64_t> seed_base{0}, seed_stride{1};
     bool stop = false;
     std::string fault;                   // first worker failure
     std::vector<std::thread> workers;
@@ -212,7 +216,7 @@ void worker_main(ag_loader *l, uint32_t idx) {
             bufs[b] = w.bufs;
             // Seeded loaders restart the stream per batch from its submission number
             // (prefetch.rs:926-930), so any pool size or grouping yields the same results.
-            batch_seeds[b] = ag_batch_seed(l->cfg.seed, w.seq);
+            batch_seeds[b] = ag_batch_seed(l->cfg.seed, l->seed_base.load() + l->seed_stride.load() * w.seq);
             statuses[b] = AG_OK;
         }
         // Unseeded: a worker's own stream continues across its batches, which needs
@@ -392,6 +396,15 @@ extern "C" int32_t ag_loader_create(const ag_graph *g, const ag_features *f, con
     }
     for (uint32_t i = 0; i < sampler_threads; ++i) l->workers.emplace_back(worker_main, l, i);
     *out = l;
+    return AG_OK;
+}
+
+extern "C" int32_t ag_loader_set_seed_sequence(ag_loader *l, uint64_t base, uint64_t stride) {
+    if (!l) return fail(AG_ERR_VALUE, "ag_loader_set_seed_sequence: null loader");
+    if (stride == 0) return fail(AG_ERR_VALUE, "ag_loader_set_seed_sequence: stride must be >= 1");
+    std::unique_lock<std::mutex> lk(l->m);
+    if (l->next_seq != 0) return fail(AG_ERR_VALUE, "the seed sequence is set before the first batch is submitted");
+    l->seed_base = base; l->seed_stride = stride;
     return AG_OK;
 }
 

@@ -720,6 +720,7 @@ struct ag_sampler {
     // in between the short-lived blocks of a running gather (bandwidth-bound).
     cudaStream_t gstream = nullptr;
     cudaEvent_t sampled = nullptr;
+    SortScratch sort;  // sharded feature stores: the chain's row ids in address order (gather.cu)
     // Grid-size estimates from the last group's real counts (the bounds before
     // the first one); kernels stride past an estimate that turns out too small.
     uint64_t est_nodes = 0;
@@ -869,6 +870,7 @@ extern "C" void ag_sampler_free(ag_sampler *s) {
     DeviceGuard guard(s->device);
     if (s->in_flight && s->done) cudaEventSynchronize(s->done);
     free_scratch(s);
+    s->sort.release();
     for (void *p : s->owned) cudaFree(p);
     cudaFree(s->state); cudaFree(s->counts_dev); cudaFree(s->params_dev); cudaFree(s->gather_dev);
     if (s->counts_host) cudaFreeHost(s->counts_host);
@@ -1076,8 +1078,16 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
         AG_CUDA(cudaStreamWaitEvent(s->gstream, s->sampled, 0));
         if (s->profile) AG_CUDA(cudaEventRecord(s->ev[2], s->gstream));
         const uint64_t rows = s->est_nodes ? std::min(b_nodes, s->est_nodes) : b_nodes;
-        AG_CUDA(launch_gather_group(s->gather_dev, n_batches, (uint32_t)(feats->dim * elem_size(feats->dtype)),
-                                    (uint32_t)feats->dim, rows, aligned, feats->dtype, feats->shards != nullptr, s->gstream));
+        const uint32_t row_bytes = (uint32_t)(feats->dim * elem_size(feats->dtype));
+        if (sorted_gather_applies(feats, row_bytes, aligned)) {
+            // Rows of a sharded store are fetched in address order, each distinct row of the
+            // chain once.  (The handle's previous chain has finished: its event was waited for above.)
+            AG_CUDA(launch_gather_sorted(GatherArgs{}, s->gather_dev, n_batches, rows, row_bytes, (uint32_t)feats->dim,
+                                         feats->dtype, feats, s->sort, s->gstream));
+        } else {
+            AG_CUDA(launch_gather_group(s->gather_dev, n_batches, row_bytes, (uint32_t)feats->dim, rows, aligned,
+                                        feats->dtype, feats->shards != nullptr, s->gstream));
+        }
         if (s->profile) AG_CUDA(cudaEventRecord(s->ev[3], s->gstream));
         AG_CUDA(cudaEventRecord(s->done, s->gstream));
         AG_CUDA(cudaStreamWaitEvent(st, s->done, 0));  // the caller's stream stays ordered behind the gather

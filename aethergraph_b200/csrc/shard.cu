@@ -40,6 +40,9 @@ int32_t make_view(const ag_features *local, uint32_t world, bool cyclic, const u
     for (uint32_t r = 0; r < world && !v->payload; ++r) v->payload = const_cast<uint8_t *>(bases[r]);
     v->owns_payload = false;
     v->n_shards = world;
+    v->shard_rows = cyclic ? (n + world - 1) / world : std::max<uint64_t>(shard_rows, 1);
+    v->shard_cyclic = cyclic;
+    v->sort = new ag_features::SortState();
     for (uint32_t r = 0; r < world && opened; ++r) v->ipc_opened[r] = opened[r];
     ag_shard_table t{};
     for (uint32_t r = 0; r < world; ++r) t.base[r] = bases[r];

@@ -79,6 +79,67 @@ __global__ void k_rmat_keys(RmatParams p, uint64_t *keys) {
     }
 }
 
+// Graphs whose edge keys (16 bytes per edge while they are sorted) do not fit the
+// free device memory are built in partitions of the source id range: a first pass
+// counts the edges per bin of source ids, bins are grouped into contiguous ranges
+// that fit, and every range is generated (all edges are drawn again, the ones
+// whose source falls in the range are kept), sorted and written on its own.  The
+// result is the same CSR — rows are sorted by (source, destination) either way.
+constexpr int kHistBits = 12;
+
+__global__ void k_rmat_hist(RmatParams p, uint32_t shift, unsigned long long *hist) {
+    __shared__ uint32_t s_hist[1 << kHistBits];
+    for (int i = threadIdx.x; i < (1 << kHistBits); i += blockDim.x) s_hist[i] = 0;
+    __syncthreads();
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.num_edges;
+         i += (uint64_t)gridDim.x * blockDim.x) {
+        uint32_t s, d;
+        rmat_edge(p, i, s, d);
+        atomicAdd(&s_hist[s >> shift], 1u);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < (1 << kHistBits); i += blockDim.x)
+        if (s_hist[i]) atomicAdd(&hist[i], (unsigned long long)s_hist[i]);
+}
+
+// Keeps the edges whose source lies in [row_lo, row_hi); order does not matter (they are sorted next).
+__global__ void k_rmat_keys_range(RmatParams p, uint64_t row_lo, uint64_t row_hi, uint64_t *keys,
+                                  unsigned long long *count, uint64_t cap) {
+    for (uint64_t i0 = (uint64_t)blockIdx.x * blockDim.x; i0 < p.num_edges; i0 += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t i = i0 + threadIdx.x;
+        uint32_t s = 0, d = 0;
+        bool keep = false;
+        if (i < p.num_edges) {
+            rmat_edge(p, i, s, d);
+            keep = s >= row_lo && s < row_hi;
+        }
+        const uint32_t m = __ballot_sync(0xffffffffu, keep);
+        if (!m) continue;
+        const int lane = threadIdx.x & 31, leader = __ffs(m) - 1;
+        unsigned long long base = 0;
+        if (lane == leader) base = atomicAdd(count, (unsigned long long)__popc(m));
+        base = __shfl_sync(0xffffffffu, base, leader);
+        const uint64_t at = base + __popc(m & ((1u << lane) - 1u));
+        if (keep && at < cap) keys[at] = ((uint64_t)s << 32) | d;
+    }
+}
+
+// One partition's sorted keys -> its slice of dst and the offsets of rows [row_lo, row_hi).
+__global__ void k_keys_to_csr_part(const uint64_t *keys, uint64_t e, uint64_t base, uint64_t row_lo, uint64_t row_hi,
+                                   uint64_t *offsets, uint32_t *dst) {
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < e; i += stride) {
+        const uint64_t k = keys[i];
+        dst[base + i] = (uint32_t)k;
+        const uint64_t s = k >> 32;
+        const uint64_t prev = i ? (keys[i - 1] >> 32) + 1 : row_lo;
+        for (uint64_t v = prev; v <= s; ++v) offsets[v] = base + i;
+        if (i == e - 1) for (uint64_t v = s + 1; v < row_hi; ++v) offsets[v] = base + e;
+    }
+    if (e == 0)
+        for (uint64_t v = row_lo + (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; v < row_hi; v += stride) offsets[v] = base;
+}
+
 // From keys sorted by (src, dst): dst array and CSR offsets.
 __global__ void k_keys_to_csr(const uint64_t *keys, uint64_t e, uint64_t n, uint64_t *offsets, uint32_t *dst) {
     const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
@@ -145,6 +206,9 @@ int grid_for(uint64_t n) {
     return (int)std::max<uint64_t>(1, std::min<uint64_t>(b, (uint64_t)kSMs * 16));
 }
 
+int32_t build_relation_partitioned(const RmatParams &p, float weight_sigma, uint64_t budget_edges,
+                                   uint64_t **offsets_out, uint32_t **dst_out, float **w_out);
+
 int32_t build_relation(uint64_t num_src, uint64_t num_dst, uint64_t num_edges, const float abc[3], uint64_t seed,
                        float weight_sigma, int device, uint64_t **offsets_out, uint32_t **dst_out, float **w_out) {
     if (num_src == 0 || num_dst == 0 || num_src > 0xFFFFFFFFull || num_dst > 0xFFFFFFFFull)
@@ -155,6 +219,23 @@ int32_t build_relation(uint64_t num_src, uint64_t num_dst, uint64_t num_edges, c
     p.a16 = (uint32_t)(abc[0] * 65536.0f);
     p.ab16 = (uint32_t)((abc[0] + abc[1]) * 65536.0f);
     p.abc16 = (uint32_t)((abc[0] + abc[1] + abc[2]) * 65536.0f);
+    {
+        // All keys at once need 16 bytes per edge (two sort buffers) beside the result;
+        // otherwise build the rows a range of sources at a time.
+        size_t free_b = 0, total_b = 0;
+        if (cudaMemGetInfo(&free_b, &total_b) == cudaSuccess) {
+            const uint64_t result = (num_src + 1) * 8 + num_edges * (weight_sigma > 0.f ? 8 : 4);
+            const uint64_t spare = (uint64_t)(0.92 * (double)free_b);
+            const char *force = getenv("AG_SYNTH_PARTITION_EDGES");  // tests: force the partitioned build
+            if (force || num_edges * 16 + num_edges * 4 + (num_src + 1) * 8 + (64ull << 20) > spare) {
+                if (spare < result + (1ull << 30)) return fail(AG_ERR_CUDA, "graph of %llu edges does not fit the free device memory",
+                                                                (unsigned long long)num_edges);
+                uint64_t budget = (spare - result - (256ull << 20)) / 17;  // two key buffers + sort scratch
+                if (force) budget = std::max<uint64_t>(1, strtoull(force, nullptr, 10));
+                return build_relation_partitioned(p, weight_sigma, budget, offsets_out, dst_out, w_out);
+            }
+        }
+    }
     uint64_t *keys_a = nullptr, *keys_b = nullptr, *offsets = nullptr;
     uint32_t *dst = nullptr;
     float *w = nullptr;
@@ -193,6 +274,86 @@ int32_t build_relation(uint64_t num_src, uint64_t num_dst, uint64_t num_edges, c
         cuda_ok(cudaDeviceSynchronize(), "graph generation");
     } while (0);
     cudaFree(keys_a); cudaFree(keys_b); cudaFree(temp);
+    if (st != AG_OK) { cudaFree(offsets); cudaFree(dst); cudaFree(w); return st; }
+    *offsets_out = offsets; *dst_out = dst; *w_out = w;
+    return AG_OK;
+}
+
+int32_t build_relation_partitioned(const RmatParams &p, float weight_sigma, uint64_t budget_edges,
+                                   uint64_t **offsets_out, uint32_t **dst_out, float **w_out) {
+    const uint64_t num_src = p.num_src, num_edges = p.num_edges;
+    const uint32_t hist_bits = std::min<uint32_t>(kHistBits, p.bits_src);
+    const uint32_t shift = p.bits_src - hist_bits;
+    const uint32_t bins = 1u << hist_bits;
+    uint64_t *keys_a = nullptr, *keys_b = nullptr, *offsets = nullptr;
+    unsigned long long *hist_dev = nullptr, *count_dev = nullptr;
+    uint32_t *dst = nullptr;
+    float *w = nullptr;
+    void *temp = nullptr;
+    int32_t st = AG_OK;
+    auto cuda_ok = [&](cudaError_t e, const char *what) {
+        if (e != cudaSuccess && st == AG_OK) st = fail(AG_ERR_CUDA, "%s failed: %s", what, cudaGetErrorString(e));
+        return e == cudaSuccess;
+    };
+    do {
+        if (!cuda_ok(cudaMalloc(&offsets, (num_src + 1) * 8), "cudaMalloc(offsets)")) break;
+        if (!cuda_ok(cudaMalloc(&dst, std::max<uint64_t>(num_edges, 1) * 4), "cudaMalloc(dst)")) break;
+        if (!cuda_ok(cudaMalloc(&hist_dev, (bins + 1) * 8), "cudaMalloc(histogram)")) break;
+        if (!cuda_ok(cudaMemset(hist_dev, 0, (bins + 1) * 8), "cudaMemset")) break;
+        count_dev = hist_dev + bins;
+        k_rmat_hist<<<grid_for(num_edges), 256>>>(p, shift, hist_dev);
+        std::vector<unsigned long long> hist(bins);
+        if (!cuda_ok(cudaMemcpy(hist.data(), hist_dev, bins * 8, cudaMemcpyDeviceToHost), "edge histogram")) break;
+        // contiguous groups of bins with at most budget_edges edges each (a single bin may exceed it)
+        struct Part { uint32_t lo, hi; uint64_t edges; };
+        std::vector<Part> parts;
+        uint64_t biggest = 0;
+        for (uint32_t b = 0; b < bins;) {
+            Part q{b, b, 0};
+            while (q.hi < bins && (q.hi == q.lo || q.edges + hist[q.hi] <= budget_edges)) q.edges += hist[q.hi++];
+            parts.push_back(q);
+            biggest = std::max(biggest, q.edges);
+            b = q.hi;
+        }
+        const uint64_t kb = std::max<uint64_t>(biggest, 1) * 8;
+        if (!cuda_ok(cudaMalloc(&keys_a, kb), "cudaMalloc(keys)")) break;
+        if (!cuda_ok(cudaMalloc(&keys_b, kb), "cudaMalloc(keys)")) break;
+        size_t temp_bytes = 0;
+        const int end_bit = 32 + (int)p.bits_src;
+        {
+            cub::DoubleBuffer<uint64_t> probe(keys_a, keys_b);
+            if (!cuda_ok(cub::DeviceRadixSort::SortKeys(nullptr, temp_bytes, probe, biggest, 0, end_bit), "sort sizing")) break;
+        }
+        if (!cuda_ok(cudaMalloc(&temp, std::max<size_t>(temp_bytes, 16)), "cudaMalloc(sort temp)")) break;
+        uint64_t base = 0;
+        for (const Part &q : parts) {
+            const uint64_t row_lo = std::min<uint64_t>((uint64_t)q.lo << shift, num_src);
+            const uint64_t row_hi = std::min<uint64_t>((uint64_t)q.hi << shift, num_src);
+            if (!cuda_ok(cudaMemset(count_dev, 0, 8), "cudaMemset")) break;
+            if (q.edges) k_rmat_keys_range<<<grid_for(num_edges), 256>>>(p, row_lo, row_hi, keys_a, count_dev, biggest);
+            unsigned long long got = 0;
+            if (!cuda_ok(cudaMemcpy(&got, count_dev, 8, cudaMemcpyDeviceToHost), "k_rmat_keys_range")) break;
+            if (got != q.edges) { st = fail(AG_ERR_CUDA, "partitioned graph build: a range produced %llu edges, its bins hold %llu", got, (unsigned long long)q.edges); break; }
+            cub::DoubleBuffer<uint64_t> buf(keys_a, keys_b);
+            if (q.edges && !cuda_ok(cub::DeviceRadixSort::SortKeys(temp, temp_bytes, buf, (uint64_t)q.edges, 0, end_bit), "radix sort")) break;
+            k_keys_to_csr_part<<<grid_for(std::max<uint64_t>(q.edges, row_hi - row_lo + 1)), 256>>>(buf.Current(), q.edges, base, row_lo,
+                                                                                                   row_hi, offsets, dst);
+            if (!cuda_ok(cudaDeviceSynchronize(), "k_keys_to_csr_part")) break;
+            base += q.edges;
+        }
+        if (st != AG_OK) break;
+        if (base != num_edges) { st = fail(AG_ERR_CUDA, "partitioned graph build lost edges (%llu of %llu)", (unsigned long long)base, (unsigned long long)num_edges); break; }
+        if (!cuda_ok(cudaMemcpy(offsets + num_src, &num_edges, 8, cudaMemcpyHostToDevice), "offsets tail")) break;
+        cudaFree(keys_a); cudaFree(keys_b); cudaFree(temp);
+        keys_a = keys_b = nullptr; temp = nullptr;
+        if (weight_sigma > 0.f) {
+            if (!cuda_ok(cudaMalloc(&w, std::max<uint64_t>(num_edges, 1) * 4), "cudaMalloc(weights)")) break;
+            k_weights<<<grid_for(num_edges), 256>>>(w, num_edges, mix(p.seed ^ 0x77656967687473ull), weight_sigma);
+            if (!cuda_ok(cudaGetLastError(), "k_weights")) break;
+        }
+        cuda_ok(cudaDeviceSynchronize(), "graph generation");
+    } while (0);
+    cudaFree(keys_a); cudaFree(keys_b); cudaFree(temp); cudaFree(hist_dev);
     if (st != AG_OK) { cudaFree(offsets); cudaFree(dst); cudaFree(w); return st; }
     *offsets_out = offsets; *dst_out = dst; *w_out = w;
     return AG_OK;

@@ -2,10 +2,11 @@
 
 The path shards with no data-path collective: batch `b` of the global stream goes
 to rank `b % world`, every rank holds the CSR (and, when it fits, the features),
-and batch `b` is always sampled from `batch_seed(seed, b)`, so the result does not
-depend on the number of ranks — the property the reference tests for its thread
-pool (crates/aethergraph-core/src/loader/sampler.rs:3116-3148).  torch.distributed
-is only used to agree on timings and totals.
+and batch `b` is sampled from `batch_seed(seed, b)` when rank r's loader is created
+with `seed_sequence=(r, world)` (its local batch i is global batch r + world * i), so
+the result does not depend on the number of ranks — the property the reference tests
+for its thread pool (crates/aethergraph-core/src/loader/sampler.rs:3116-3148).
+torch.distributed is only used to agree on timings and totals.
 """
 from __future__ import annotations
 

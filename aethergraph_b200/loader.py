@@ -87,7 +87,12 @@ def _raw_current_stream(device_index: int) -> int:
 class NeighborLoader:
     def __init__(self, graph: CsrGraph, config: SamplingConfig, prefetch_depth: int = 2,
                  sampler_threads: int = 1, *, features: FeatureStore | None = None,
-                 host_features: bool = False, profiling: bool = False, group: int = 8):
+                 host_features: bool = False, profiling: bool = False, group: int = 8,
+                 seed_sequence: tuple[int, int] = (0, 1)):
+        """`seed_sequence=(base, stride)`: the loader's batch number `seq` is sampled
+        from `batch_seed(seed, base + stride * seq)`.  Rank r of a W-rank job that takes
+        global batches r, r + W, ... passes `(r, W)`, so every global batch is drawn from
+        the same stream whatever W is."""
         import torch
 
         _check_config(graph, config)
@@ -104,12 +109,15 @@ class NeighborLoader:
         _lib.check(_lib.lib().ag_loader_create(graph._h, features._h if features is not None else None,
                                                C.byref(cfg), int(self._seeded), prefetch_depth, sampler_threads,
                                                max(1, int(group)), int(profiling), C.byref(self._h)))
+        if tuple(seed_sequence) != (0, 1):
+            _lib.check(_lib.lib().ag_loader_set_seed_sequence(self._h, int(seed_sequence[0]), int(seed_sequence[1])))
         self._dev = torch.device("cuda", graph.device)
         self._dev_index = int(graph.device)
         self._release = _lib.lib().ag_loader_release_batch
         self._dim = features.feature_dim if features is not None else None
         self._lock = threading.Lock()
         self._next_seq = 0
+        self._next_deliver = 0            # seeded loaders deliver in seq order
         self._seeds: dict[int, np.ndarray] = {}
         self._fetched: list = []          # batches already taken from the native queue
         self._fetch_buf = (_lib.Batch * _FETCH)()
@@ -156,13 +164,15 @@ class NeighborLoader:
                 _lib.check(rc)
             self._next_seq += 1
 
-    def submit_epoch(self, batches) -> None:
-        """Queue batches 0 .. len(batches) - 1 in one native call."""
+    def submit_epoch(self, batches, batch_indices=None) -> None:
+        """Queue batches 0 .. len(batches) - 1 (or `batch_indices`) in one native call.
+        The call blocks while the work queue (8 x prefetch_depth batches) is full, so a
+        thread that also consumes the results submits at most that many at a time."""
         seeds = [coerce_seeds(b, self.graph.num_nodes) for b in batches]
         n = len(seeds)
         if n == 0:
             return
-        idx = (C.c_int64 * n)(*range(n))
+        idx = (C.c_int64 * n)(*(range(n) if batch_indices is None else [int(i) for i in batch_indices]))
         ptrs = (C.c_void_p * n)(*[s.ctypes.data if len(s) else None for s in seeds])
         lens = (C.c_uint64 * n)(*[len(s) for s in seeds])
         done = C.c_uint32()
@@ -192,11 +202,16 @@ class NeighborLoader:
                 return None
             if rc == _lib.AG_ERR_TIMEOUT and not blocking:
                 return None
+            if rc in (_lib.AG_ERR_SAMPLING, _lib.AG_ERR_VALUE, _lib.AG_ERR_LOAD) and self._seeded:
+                # a batch that failed by itself was consumed by the library: forget its seeds too
+                self._seeds.pop(self._next_deliver, None)
+                self._next_deliver += 1
             _lib.check(rc)
             for i in range(got.value - 1, -1, -1):  # reversed: pop() hands them out in order
                 b = _lib.Batch.from_buffer_copy(self._fetch_buf[i])
                 self._fetched.append(b)
         b = self._fetched.pop()
+        self._next_deliver = b.seq + 1
         seeds = self._seeds.pop(b.seq)
         bufs = _Buffers(b.bufs, _Lease(self, b), self._dev, self._dim)
         sg = SampledSubgraph(bufs, b.counts, seeds)

@@ -3,11 +3,12 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2] [--impl reference]
 
-One step = one `sample_batches`-sized round of BATCHES_PER_STEP seed batches
-(batch size, fanout, graph and feature shape from the workload), each batch
-sampled, deduplicated, relabelled and its feature rows gathered.  Prints ONE
-JSON line (rank 0).  Inputs are seeded synthetic stand-ins generated in place
-(R-MAT graph, ~N(0,1) features); no dataset is read.
+One step = the workload's `batches_per_step` seed batches (512 for C2; batch size,
+fanout, graph and feature shape from the workload), each batch sampled,
+deduplicated, relabelled and its feature rows gathered.  The timed region of K
+steps is repeated (`--repeats`, default 5) and the median is reported with the
+minimum and maximum.  Prints ONE JSON line (rank 0).  Inputs are seeded synthetic
+stand-ins generated in place (R-MAT graph, ~N(0,1) features); no dataset is read.
 
   value   sampled edges/s with the graph, features and seed batches resident in
           HBM, driven through the C ABI (ag_loader_*), whole job over all GPUs.
@@ -15,6 +16,12 @@ JSON line (rank 0).  Inputs are seeded synthetic stand-ins generated in place
           next_batch) with host seed arrays copied to the device and the batch
           counts read back every batch; the sampled batch itself stays in GPU
           memory, where the training step consumes it.
+  sharded (2 or more GPUs) the same resident leg once more with the feature rows
+          split over the GPUs (1/N each, dealt round-robin) and remote rows
+          fetched over NVLink in address order; a batch is compared bit for bit
+          with the rows of the replicated table.
+  secondary (1 GPU)  C1, C3 and the heterogeneous C4 at 1/10 size, each with its
+          own CPU baseline and full-size parity check.
   --impl reference   the CPU restatement of the reference's sampler + gather
           (oracle/, C + OpenMP) on the host cores, same workload.
 """
@@ -35,7 +42,7 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-BATCHES_PER_STEP = 16
+BATCHES_PER_STEP = 512   # default; a workload may carry its own `per_step`
 METRIC = "sampled edges/s (k-hop sampling + dedup/relabel + feature gather)"
 
 WORKLOADS = {
@@ -52,15 +59,24 @@ WORKLOADS = {
     "c2s": dict(nodes=4_000_000, edges=64_000_000, dim=256, dtype="bf16", batch=1024, fanout=[25, 10],
                 weighted=False, label="C2-small: R-MAT 4M vertices / 64M edges, 256-dim bf16, batch 1024, fanout [25,10]"),
     "tiny": dict(nodes=1 << 16, edges=1 << 20, dim=64, dtype="bf16", batch=256, fanout=[10, 5], weighted=False,
-                 label="tiny: R-MAT 64K vertices / 1M edges, 64-dim bf16, batch 256, fanout [10,5]"),
+                 per_step=32, label="tiny: R-MAT 64K vertices / 1M edges, 64-dim bf16, batch 256, fanout [10,5]"),
+    # 500M-vertex R-MAT, 12B edges (52 GB CSR replicated per GPU), 128-dim bf16 features sharded over the GPUs
+    # (128 GB in all), 4096 seeds per GPU and batch, fanout [15, 10, 5]; 2 or more GPUs
+    "c5": dict(nodes=500_000_000, edges=12_000_000_000, dim=128, dtype="bf16", batch=4096, fanout=[15, 10, 5],
+               weighted=False, per_step=8, group=4, threads=2, depth=4, sharded_only=True,
+               label="C5: R-MAT 500M vertices / 12B edges, 128-dim bf16 sharded over the GPUs, batch 4096, fanout [15,10,5]"),
+    # C5's batch shape and sharded features on a graph that fits next to anything (tests of the sharded leg)
+    "c5s": dict(nodes=20_000_000, edges=480_000_000, dim=128, dtype="bf16", batch=4096, fanout=[15, 10, 5],
+                weighted=False, per_step=8, group=4, threads=2, depth=4, sharded_only=True,
+                label="C5-small: R-MAT 20M vertices / 480M edges, 128-dim bf16 sharded over the GPUs, batch 4096, fanout [15,10,5]"),
 }
 GRAPH_SEED, FEATURE_SEED, SEEDS_SEED, SAMPLER_SEED = 1, 2, 3, 42
 
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per gathered row of
-# k_gather_vec, from the ncu capture summarised in
-# profiles/k_gather_vec_c2small_ncu_full.md: 647.6 MB for a launch over 495,171 rows
-# of 256 bf16 -> f32 (1536 algorithmic bytes per row).
+# k_gather_vec from one ncu capture of the C2-small workload: 647.6 MB for a launch
+# over 495,171 rows of 256 bf16 -> f32 (1536 algorithmic bytes per row).
 NCU_DRAM_BYTES_PER_ROW = {"bf16256": 1308}
+NVLINK_PEER_COPY_GBS = 770.0  # measured peer copy bandwidth per direction per GPU on this pool
 
 
 def sector(x: int) -> int:
@@ -165,6 +181,16 @@ def host_seed_batches(w, first_batch: int, count: int) -> np.ndarray:
                            for i in range(count)]) if count else np.empty(0, dtype=np.uint32)
 
 
+def per_step_of(w) -> int:
+    return int(w.get("per_step", BATCHES_PER_STEP))
+
+
+def common_config(w, world: int, features: str) -> dict:
+    """The `config` keys both arms print (what is measured, not how)."""
+    return {"workload": w["label"], "batches_per_step": per_step_of(w), "rng_mode": "wyrand_exact",
+            "parallelism": f"dp{world}", "features": features, "inputs_larger_than_l2": True}
+
+
 def run_reference(args, w):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -173,15 +199,18 @@ def run_reference(args, w):
 
     ago.build()
     threads = cpu_threads()
-    t_setup = time.time()
-    offsets, dst = ago.synth_rmat_csr(w["nodes"], w["nodes"], w["edges"], GRAPH_SEED, threads=threads)
-    payload = ago.synth_features(w["nodes"], w["dim"], w["dtype"], FEATURE_SEED, threads=threads)
     if w["weighted"]:
         raise SystemExit(json.dumps({"impl": "reference", "unavailable":
                                      "weighted workloads take their weights from the GPU generator"}))
+    if w["nodes"] * w["dim"] * (4 if w["dtype"] == "f32" else 2) + w["edges"] * 4 > 0.8 * host_memory_bytes():
+        raise SystemExit(json.dumps({"impl": "reference", "unavailable":
+                                     "the workload's graph and features do not fit this host's memory"}))
+    t_setup = time.time()
+    offsets, dst = ago.synth_rmat_csr(w["nodes"], w["nodes"], w["edges"], GRAPH_SEED, threads=threads)
+    payload = ago.synth_features(w["nodes"], w["dim"], w["dtype"], FEATURE_SEED, threads=threads)
     t_setup = time.time() - t_setup
     s = ago.Sampler(offsets, dst, w["fanout"], seed=SAMPLER_SEED)
-    per_step = BATCHES_PER_STEP
+    per_step = per_step_of(w)
     total = (args.warmup + args.steps) * per_step
     seeds = host_seed_batches(w, 0, total)
     bs = w["batch"]
@@ -199,10 +228,11 @@ def run_reference(args, w):
         "impl": "reference", "metric": METRIC, "value": value, "unit": "edges/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs * 1e3 / max(args.steps, 1),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u32 ids / " + w["dtype"] + "->f32",
-        "data": "synthetic (seeded R-MAT graph + ~N(0,1) features generated on the host by the generator's CPU twin)",
-        "config": {"workload": w["label"], "batches_per_step": per_step, "rng_mode": "wyrand_exact",
-                   "inputs_larger_than_l2": True, "implementation":
-                   "C restatement of the reference's Rust CPU sampler + gather (no Rust toolchain on this image)"},
+        "data": "synthetic (seeded R-MAT graph + ~N(0,1) features; the reference arm generates them on the host "
+                "with the generator's CPU twin, bit-identical to the device arm's inputs)",
+        "config": common_config(w, args.gpus, "replicated"),
+        "impl_config": {"implementation": "C restatement of the reference's Rust CPU sampler + gather "
+                                          "(no Rust toolchain on this image)", "threads": threads},
         "gather_gbs": gbs, "edges": r["edges"], "nodes": r["nodes"], "checksum": f"{r['checksum']:016x}",
         "setup_s": round(t_setup, 1), "wall_s": round(wall, 3),
         "cpu_baseline": {"value": value, "unit": "edges/s", "cores": threads, "kind": "port", "sample": sample,
@@ -213,9 +243,113 @@ def run_reference(args, w):
     print(json.dumps(line), flush=True)
 
 
+def host_memory_bytes() -> int:
+    try:
+        return os.sysconf("SC_PAGE_SIZE") * os.sysconf("SC_PHYS_PAGES")
+    except (ValueError, OSError):
+        return 1 << 62
+
+
 # --------------------------------------------------------------------------- #
 #  device arm                                                                  #
 # --------------------------------------------------------------------------- #
+class ResidentLeg:
+    """The C-ABI loader fed with device-resident seed batches and recycled output
+    buffers: what `value` (and the sharded record) time."""
+
+    def __init__(self, L, _lib, g, feats, ccfg, dev, w, threads, group, depth, seeds_dev, gidx, rank, world):
+        from aethergraph_b200.sampler import _Buffers
+
+        self.L, self._lib, self.group, self.w = L, _lib, group, w
+        bs = w["batch"]
+        self.h = C.c_void_p()
+        _lib.check(L.ag_loader_create(g._h, feats._h, C.byref(ccfg), 1, depth, threads, group, 1, C.byref(self.h)))
+        # global batch b = rank + world * i draws from batch_seed(seed, b) at any world size
+        _lib.check(L.ag_loader_set_seed_sequence(self.h, rank, world))
+        mn, me = C.c_uint64(), C.c_uint64()
+        _lib.check(L.ag_loader_bounds(self.h, bs, C.byref(mn), C.byref(me)))
+        self.mn, self.me = mn.value, me.value
+        # One thread both submits and consumes, so it must never block in submit:
+        # keep no more batches outstanding than the loader's work queue (8 x depth) holds.
+        self.window = min(8 * depth, depth + threads * group + group)
+        self.ring = [_Buffers.alloc(dev, mn.value, me.value, bs, True, w["dim"]) for _ in range(self.window)]
+        R = self.R = len(self.ring)
+        n_batches = len(gidx)
+        base = seeds_dev.data_ptr()
+        self.idx_all = (C.c_int64 * n_batches)(*gidx)
+        self.ptr_all = (C.c_void_p * n_batches)(*[base + 4 * bs * i for i in range(n_batches)])
+        self.len_all = (C.c_uint64 * n_batches)(*([bs] * n_batches))
+        self.ring_c = (_lib.SubgraphBuffers * (R + group))(*[self.ring[j % R].c for j in range(R + group)])
+        self.out_batches = (_lib.Batch * 64)()
+        self.n_out = C.c_uint32()
+        self.recent: list = []  # (n_id pointer, x pointer, node count) of the last `group` delivered batches
+
+    def run(self, first: int, count: int):
+        """Submit batches [first, first + count) with device seeds; returns (edges, nodes)."""
+        L, _lib, group, R = self.L, self._lib, self.group, self.R
+        sz_i64, sz_ptr, sz_u64 = C.sizeof(C.c_int64), C.sizeof(C.c_void_p), C.sizeof(C.c_uint64)
+        sz_buf = C.sizeof(_lib.SubgraphBuffers)
+        edges = nodes = 0
+        submitted = delivered = 0
+        while delivered < count:
+            while submitted < count and submitted - delivered + min(group, count - submitted) <= R:
+                i = first + submitted
+                n = min(group, count - submitted)
+                _lib.check(L.ag_loader_submit_many(
+                    self.h, n, C.byref(self.idx_all, i * sz_i64), C.byref(self.ptr_all, i * sz_ptr),
+                    C.byref(self.len_all, i * sz_u64), _lib.AG_MEM_DEVICE, C.byref(self.ring_c, (i % R) * sz_buf),
+                    None, None))
+                submitted += n
+            _lib.check(L.ag_loader_next_many(self.h, -1, 64, self.out_batches, C.byref(self.n_out)))
+            for j in range(self.n_out.value):
+                ob = self.out_batches[j]
+                edges += ob.counts.num_edges
+                nodes += ob.counts.num_nodes
+                self.recent.append((ob.bufs.n_id, ob.bufs.x, ob.counts.num_nodes))
+            del self.recent[:-group]
+            delivered += self.n_out.value
+        return edges, nodes
+
+    def stats(self):
+        s = self._lib.LoaderStats()
+        self._lib.check(self.L.ag_loader_stats_get(self.h, C.byref(s)))
+        return s
+
+    def close(self):
+        if self.h:
+            self.L.ag_loader_free(self.h)
+            self.h = None
+        self.ring = None
+
+
+def timed_repeats(run, first, count, repeats, barrier, max_over_ranks, sum_over_ranks):
+    """`repeats` timed regions of `count` batches each, CUDA events around each,
+    barrier + synchronize on both sides, max over ranks.  Returns per-repeat
+    (ms, edges, nodes) with edges / nodes summed over the ranks."""
+    import torch
+
+    out = []
+    for _ in range(repeats):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        got = run(first, count)
+        e1.record()
+        barrier()
+        ms = max_over_ranks(e0.elapsed_time(e1))
+        edges, nodes = got if isinstance(got, tuple) else (got, 0)
+        out.append((ms, sum_over_ranks(edges), sum_over_ranks(nodes)))
+    return out
+
+
+def median_run(runs):
+    """The repeat with the median throughput, and the spread."""
+    vals = sorted((e / (ms * 1e-3), ms, e, n) for (ms, e, n) in runs)
+    mid = vals[len(vals) // 2]
+    return {"value": mid[0], "ms": mid[1], "edges": mid[2], "nodes": mid[3],
+            "min": vals[0][0], "max": vals[-1][0], "n": len(vals)}
+
+
 def run_device(args, w):
     import torch
     import torch.distributed as dist
@@ -236,29 +370,12 @@ def run_device(args, w):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     L = _lib.lib()
-
-    # ---- inputs, resident in HBM (CSR and features replicated per GPU) ------
-    t_setup = time.time()
-    g = synth.rmat_graph(w["nodes"], w["edges"], GRAPH_SEED, weight_sigma=1.0 if w["weighted"] else 0.0)
-    if args.features != "replicated" and world > 1:
-        # every rank holds 1/world of the rows; remote rows cross NVLink inside the gather kernel.
-        # "sharded": rows dealt round-robin (balanced); "sharded-range": contiguous vertex ranges.
-        from aethergraph_b200 import dist as agd
-
-        layout = "range" if args.features == "sharded-range" else "cyclic"
-        local_shard = synth.features_shard(w["nodes"], w["dim"], w["dtype"], FEATURE_SEED, rank, world, layout)
-        feats = agd.open_sharded_features(local_shard)
-    else:
-        feats = synth.features(w["nodes"], w["dim"], w["dtype"], FEATURE_SEED)
-    torch.cuda.synchronize()
-    t_setup = time.time() - t_setup
-    cfg = ag.SamplingConfig(num_neighbors=w["fanout"], seed=SAMPLER_SEED, weighted=w["weighted"])
-    per_step, bs = BATCHES_PER_STEP, w["batch"]
-    n_batches = (args.warmup + args.steps) * per_step
-    # rank r handles global batches r, r + world, ... (weak scaling: every rank does K steps)
-    gidx = [rank + world * i for i in range(n_batches)]
-    seeds_host = [synth.seed_batch(w["nodes"], bs, SEEDS_SEED, b) for b in gidx]
-    seeds_dev = torch.from_numpy(np.concatenate(seeds_host).view(np.int32)).to(dev)
+    sharded_only = bool(w.get("sharded_only"))
+    if sharded_only and world < 2:
+        raise SystemExit(f"workload {args.workload} shards its feature rows over the GPUs: run it with --gpus 2, 4 or 8")
+    main_layout = args.features
+    if sharded_only and main_layout == "replicated":
+        main_layout = "sharded"
 
     def barrier():
         torch.cuda.synchronize()
@@ -280,122 +397,96 @@ def run_device(args, w):
         dist.all_reduce(t, op=dist.ReduceOp.SUM)
         return float(t.item())
 
-    # ---- value: C ABI, inputs resident, recycled output buffers ------------
-    threads = args.threads
-    # Batches per launch chain: large chains amortise the per-kernel latency of the
-    # sampling stages, but every worker should still see several chains in the timed region.
-    if args.group:
-        group = args.group
-    else:
-        per_worker = args.steps * per_step // (3 * threads)
-        group = 32 if per_worker >= 32 else 16 if per_worker >= 16 else 8
-    depth = args.depth if args.depth else max(8, group // 2)
-    h = C.c_void_p()
+    def open_shards(layout_flag: str):
+        """1 / world of the rows on every rank; remote rows cross NVLink inside the gather."""
+        from aethergraph_b200 import dist as agd
+
+        layout = "range" if layout_flag == "sharded-range" else "cyclic"
+        shard = synth.features_shard(w["nodes"], w["dim"], w["dtype"], FEATURE_SEED, rank, world, layout)
+        return agd.open_sharded_features(shard)
+
+    def features_label(layout_flag: str) -> str:
+        if layout_flag == "replicated" or world == 1:
+            return "replicated"
+        how = "contiguous vertex ranges" if layout_flag == "sharded-range" else "rows dealt round-robin by vertex id"
+        return f"sharded over the GPUs ({how}), {world - 1}/{world} of the rows fetched over NVLink"
+
+    # ---- inputs, resident in HBM (CSR replicated per GPU) -------------------
+    t_setup = time.time()
+    g = synth.rmat_graph(w["nodes"], w["edges"], GRAPH_SEED, weight_sigma=1.0 if w["weighted"] else 0.0)
+    feats = open_shards(main_layout) if (main_layout != "replicated" and world > 1) else \
+        synth.features(w["nodes"], w["dim"], w["dtype"], FEATURE_SEED)
+    torch.cuda.synchronize()
+    t_setup = time.time() - t_setup
+    cfg = ag.SamplingConfig(num_neighbors=w["fanout"], seed=SAMPLER_SEED, weighted=w["weighted"])
+    per_step, bs = per_step_of(w), w["batch"]
+    n_batches = (args.warmup + args.steps) * per_step
+    # rank r handles global batches r, r + world, ... (weak scaling: every rank does K steps)
+    gidx = [rank + world * i for i in range(n_batches)]
+    seeds_host = [synth.seed_batch(w["nodes"], bs, SEEDS_SEED, b) for b in gidx]
+    seeds_dev = torch.from_numpy(np.concatenate(seeds_host).view(np.int32)).to(dev)
+
+    threads = args.threads or int(w.get("threads", 3))
+    group = args.group or int(w.get("group", 32))
+    depth = args.depth or int(w.get("depth", max(8, group // 2)))
     ccfg = cfg._to_c(SAMPLER_SEED, bs)
-    _lib.check(L.ag_loader_create(g._h, feats._h, C.byref(ccfg), 1, depth, threads, group, 1, C.byref(h)))
-    mn, me = C.c_uint64(), C.c_uint64()
-    _lib.check(L.ag_loader_bounds(h, bs, C.byref(mn), C.byref(me)))
-    # One thread both submits and consumes here, so it must never block in submit:
-    # keep no more batches outstanding than the loader's work queue (8 x depth) holds.
-    window = min(8 * depth, depth + threads * group + group)
-    ring = [_Buffers.alloc(dev, mn.value, me.value, bs, True, w["dim"]) for _ in range(window)]
-    R = len(ring)
-    batch = _lib.Batch()
-    stats0 = _lib.LoaderStats()
-    stats1 = _lib.LoaderStats()
+    row_bytes = gather_bytes_per_row(w)
+    stored_row = sector(w["dim"] * (4 if w["dtype"] == "f32" else 2))
+    peak, peak_src = peaks()
+    first_timed, n_timed = args.warmup * per_step, args.steps * per_step
+    hops = len(w["fanout"])
 
-    # Argument arrays for ag_loader_submit_many / ag_loader_next_many, built once.
-    base = seeds_dev.data_ptr()
-    idx_all = (C.c_int64 * n_batches)(*gidx)
-    ptr_all = (C.c_void_p * n_batches)(*[base + 4 * bs * i for i in range(n_batches)])
-    len_all = (C.c_uint64 * n_batches)(*([bs] * n_batches))
-    ring_c = (_lib.SubgraphBuffers * (R + group))(*[ring[j % R].c for j in range(R + group)])
-    out_batches = (_lib.Batch * 64)()
-    n_out = C.c_uint32()
-    sz_i64, sz_ptr, sz_u64, sz_buf = C.sizeof(C.c_int64), C.sizeof(C.c_void_p), C.sizeof(C.c_uint64), \
-        C.sizeof(_lib.SubgraphBuffers)
-
-    recent: list = []  # (n_id pointer, node count) of the last `group` delivered batches
-
-    def run_resident(first: int, count: int):
-        """Submit batches [first, first+count) with device seeds; returns (edges, nodes)."""
-        edges = nodes = 0
-        submitted = delivered = 0
-        while delivered < count:
-            while submitted < count and submitted - delivered + min(group, count - submitted) <= R:
-                i = first + submitted
-                n = min(group, count - submitted)
-                _lib.check(L.ag_loader_submit_many(
-                    h, n, C.byref(idx_all, i * sz_i64), C.byref(ptr_all, i * sz_ptr), C.byref(len_all, i * sz_u64),
-                    _lib.AG_MEM_DEVICE, C.byref(ring_c, (i % R) * sz_buf), None, None))
-                submitted += n
-            _lib.check(L.ag_loader_next_many(h, -1, 64, out_batches, C.byref(n_out)))
-            for j in range(n_out.value):
-                edges += out_batches[j].counts.num_edges
-                nodes += out_batches[j].counts.num_nodes
-                recent.append((out_batches[j].bufs.n_id, out_batches[j].counts.num_nodes))
-            del recent[:-group]
-            delivered += n_out.value
-        return edges, nodes
-
-    # NOTE: seeded loaders number batches by submission; to keep every rank's
-    # batch b on ag_batch_seed(seed, b) the loader is fed consecutive positions
-    # and the global batch index only picks the seed ids.
-    run_resident(0, args.warmup * per_step)
+    # ---- value: C ABI, inputs resident, recycled output buffers ------------
+    leg = ResidentLeg(L, _lib, g, feats, ccfg, dev, w, threads, group, depth, seeds_dev, gidx, rank, world)
+    leg.run(0, first_timed)
     clocks = ClockSampler(local)
     clocks.start()
     barrier()
-    _lib.check(L.ag_loader_stats_get(h, C.byref(stats0)))
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    stats0 = leg.stats()
     wall0 = time.time()
-    e0.record()
-    edges, nodes = run_resident(args.warmup * per_step, args.steps * per_step)
-    e1.record()
-    barrier()
+    runs = timed_repeats(leg.run, first_timed, n_timed, args.repeats, barrier, max_over_ranks, sum_over_ranks)
     wall1 = time.time()
-    ms = max_over_ranks(e0.elapsed_time(e1))
-    _lib.check(L.ag_loader_stats_get(h, C.byref(stats1)))
+    stats1 = leg.stats()
     clk = clocks.stop(wall0, wall1)
-    tot_edges, tot_nodes = sum_over_ranks(edges), sum_over_ranks(nodes)
-    value = tot_edges / (ms * 1e-3)
-    row_bytes = gather_bytes_per_row(w)
-    gather_gbs = tot_nodes * row_bytes / (ms * 1e-3) / 1e9
+    med = median_run(runs)
+    value, ms = med["value"], med["ms"]
+    gather_gbs = med["nodes"] * row_bytes / (ms * 1e-3) / 1e9
     g_ms = stats1.gather_ms - stats0.gather_ms
     s_ms = stats1.sample_ms - stats0.sample_ms
-    n_timed = args.steps * per_step
-    peak, peak_src = peaks()
-    achieved = nodes * row_bytes / (g_ms * 1e-3) / 1e9 if g_ms > 0 else None
+    own_nodes = int(stats1.nodes - stats0.nodes)   # this rank, all repeats
+    achieved = own_nodes * row_bytes / (g_ms * 1e-3) / 1e9 if g_ms > 0 else None
     # one gather launch per chain (a chain covers up to `group` batches, the batch is blockIdx.y)
     launches = max(int(stats1.chains - stats0.chains), 1)
     per_row = NCU_DRAM_BYTES_PER_ROW.get(w["dtype"] + str(w["dim"]))
+    pipeline_bytes = med["nodes"] * row_bytes + sampling_bytes(med["edges"], med["nodes"], med["nodes"])
     roofline = {
         "kernel": "k_gather_vec (feature-row gather + upcast)", "bound": "hbm",
         "achieved": achieved, "peak": peak, "unit": "GB/s",
         "frac": (achieved / peak) if achieved else None, "peak_source": peak_src,
         "frac_of_nominal_8tbs": (achieved / 8000.0) if achieved else None,
-        "bytes_per_launch": nodes * row_bytes / launches, "ms_per_launch": g_ms / launches,
-        "launches": launches, "traffic": (per_row * nodes / launches) if per_row else None,
-        "traffic_note": "ncu dram bytes per gathered row on the C2-small capture x rows per launch",
+        "bytes_per_launch": own_nodes * row_bytes / launches, "ms_per_launch": g_ms / launches,
+        "launches": launches, "traffic": (per_row * own_nodes / launches) if per_row else None,
+        "traffic_note": "extrapolated: ncu dram bytes per gathered row on the C2-small capture x rows per launch",
         "note": "per-launch time from CUDA events on the launching stream while the other "
-                "streams' sampling kernels run beside it",
-        "pipeline": {"algorithmic_gbs": (tot_nodes * row_bytes + sampling_bytes(tot_edges, tot_nodes, tot_nodes))
-                     / (ms * 1e-3) / 1e9,
-                     "frac_of_peak": ((tot_nodes * row_bytes + sampling_bytes(tot_edges, tot_nodes, tot_nodes))
-                                      / (ms * 1e-3) / 1e9) / (peak * world),
-                     "sample_ms_per_batch": s_ms / n_timed},
+                "streams' sampling kernels run beside it; `alone` is the same kernel by itself",
+        "step": {"gather_gbs": gather_gbs, "frac_of_peak": gather_gbs / (peak * world),
+                 "note": "gather bytes of a step / step time: the whole pipeline as seen from the gather's roofline"},
+        "pipeline": {"algorithmic_gbs": pipeline_bytes / (ms * 1e-3) / 1e9,
+                     "frac_of_peak": pipeline_bytes / (ms * 1e-3) / 1e9 / (peak * world),
+                     "sample_ms_per_batch": s_ms / max(n_timed * args.repeats, 1)},
     }
     # The same kernel on its own: the node ids of the last delivered batches, gathered
-    # by one standalone launch per repetition with nothing else on the GPU (what the
-    # committed ncu capture measures; the in-pipeline figure above shares the SMs and
-    # HBM with the other workers' sampling kernels).
-    if recent and not args.only_value:
-        holder = _Buffers(ring[0].c, ring, dev, w["dim"])  # the ring keeps the memory alive
-        ids = torch.cat([holder.view(ptr, (int(n),), "<i8") for ptr, n in recent])
+    # by one standalone launch per repetition with nothing else on the GPU (the
+    # in-pipeline figure above shares the SMs and HBM with the other workers'
+    # sampling kernels).
+    if leg.recent and not (args.only_value or args.brief):
+        holder = _Buffers(leg.ring[0].c, leg.ring, dev, w["dim"])  # the ring keeps the memory alive
+        ids = torch.cat([holder.view(ptr, (int(n),), "<i8") for ptr, _, n in leg.recent])
         x_alone = torch.empty((ids.shape[0], w["dim"]), dtype=torch.float32, device=dev)
         for _ in range(3):
             feats.gather(ids, out=x_alone)
         a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize(dev)
+        barrier()
         reps = 10
         a0.record()
         for _ in range(reps):
@@ -409,26 +500,38 @@ def run_device(args, w):
                              "note": "same kernel and ids, one launch at a time on an otherwise idle GPU; "
                                      "working set per launch exceeds L2"}
         del ids, x_alone
-    L.ag_loader_free(h)
-    del ring
+        barrier()
+    sharded_main = None
+    if main_layout != "replicated" and world > 1:
+        sharded_main = sharded_summary(w, world, med, stored_row, leg, feats, None, dev, sum_over_ranks, main_layout, args.steps)
+    leg.close()
+    del leg
 
     # ---- e2e: public Python API, host seeds in, counts back -----------------
-    e2e_value = ms_e2e = host_value = host_ms = None
-    d2h_host = 0
-    if not args.only_value:
-        loader = NeighborLoader(g, cfg, prefetch_depth=depth, sampler_threads=threads, features=feats, group=group)
+    e2e_med = host_med = None
+    d2h_host = host_batches = 0
+    host_sample = ""
+    window = min(8 * depth, depth + threads * group + group)
+    if not (args.only_value or args.brief):
+        loader = NeighborLoader(g, cfg, prefetch_depth=depth, sampler_threads=threads, features=feats, group=group,
+                                seed_sequence=(rank, world))
         pinned = None
+        mn, me = C.c_uint64(), C.c_uint64()
+        _lib.check(L.ag_loader_bounds(loader._h, bs, C.byref(mn), C.byref(me)))
 
         def run_e2e(first: int, count: int, to_host: bool = False):
-            """Host seed arrays in through the public API; `to_host` also copies every
-            batch (ids, local edge index, feature rows) into pinned host memory."""
+            """Host seed arrays in through the public API (submitted a chain at a time);
+            `to_host` also copies every batch (ids, local edge index, feature rows) into
+            pinned host memory."""
             nonlocal d2h_host
-            edges = submitted = delivered = 0
+            edges = nodes = submitted = delivered = 0
             while delivered < count:
-                while submitted < count and submitted - delivered < window:
-                    b = (first + submitted) % n_batches
-                    loader.submit(gidx[b], seeds_host[b])
-                    submitted += 1
+                while submitted < count and submitted - delivered + min(group, count - submitted) <= window:
+                    n = min(group, count - submitted)
+                    b0 = (first + submitted) % n_batches
+                    lo = [(b0 + j) % n_batches for j in range(n)]
+                    loader.submit_epoch([seeds_host[b] for b in lo], [gidx[b] for b in lo])
+                    submitted += n
                 _, sg, x = loader.next_batch()
                 if to_host:
                     nn, ne = sg.num_nodes, sg.num_edges
@@ -438,70 +541,91 @@ def run_device(args, w):
                     torch.cuda.current_stream().synchronize()
                     d2h_host += nn * 8 + ne * 16 + nn * w["dim"] * 4
                 edges += sg.num_edges
+                nodes += sg.num_nodes
                 delivered += 1
-            return edges
+            return edges, nodes
 
         # warm-up long enough for the loader's buffer pool to reach its working size
-        run_e2e(0, max(args.warmup * per_step, 2 * window))
-        barrier()
-        e0.record()
-        edges_e2e = run_e2e(args.warmup * per_step, args.steps * per_step)
-        e1.record()
-        barrier()
-        ms_e2e = max_over_ranks(e0.elapsed_time(e1))
-        e2e_value = sum_over_ranks(edges_e2e) / (ms_e2e * 1e-3)
-        # the same with every batch also copied to pinned host memory (what a host-side consumer sees)
+        run_e2e(0, max(first_timed, 2 * window))
+        e2e_runs = timed_repeats(run_e2e, first_timed, n_timed, max(1, min(args.repeats, 3)), barrier, max_over_ranks,
+                                 sum_over_ranks)
+        e2e_med = median_run(e2e_runs)
+        # the same with every batch also copied to pinned host memory (what a host-side
+        # consumer sees): PCIe-bound, so a bounded sample of the step is enough
+        host_batches = min(n_timed, 2 * per_step, 1024)
         pinned = {"n_id": torch.empty(mn.value, dtype=torch.int64).pin_memory(),
                   "ei": torch.empty((2, me.value), dtype=torch.int64).pin_memory(),
                   "x": torch.empty((mn.value, w["dim"]), dtype=torch.float32).pin_memory()}
-        run_e2e(0, per_step, True)
+        run_e2e(0, min(64, host_batches), True)
         d2h_host = 0
-        barrier()
-        e0.record()
-        edges_host = run_e2e(args.warmup * per_step, args.steps * per_step, True)
-        e1.record()
-        barrier()
-        host_ms = max_over_ranks(e0.elapsed_time(e1))
-        host_value = sum_over_ranks(edges_host) / (host_ms * 1e-3)
+        host_runs = timed_repeats(lambda f, c: run_e2e(f, c, True), first_timed, host_batches, 1, barrier,
+                                  max_over_ranks, sum_over_ranks)
+        host_med = median_run(host_runs)
+        host_sample = f"{host_batches} batches"
         loader.shutdown()
-        del loader
+        del loader, pinned
 
     # ---- CPU baseline beside it (rank 0, one GPU only) ----------------------
     cpu = None
     parity = None
     if rank == 0 and world == 1 and not args.no_cpu and not args.only_value:
-        cpu, parity = cpu_baseline(g, feats, w, cfg)
+        cpu, parity = cpu_baseline(g, feats, w, cfg, seconds=args.cpu_seconds, ref_kernel=not args.brief)
+
+    # ---- sharded features (2 or more GPUs): 1/N of the rows per GPU ----------
+    sharded = sharded_main
+    if world > 1 and main_layout == "replicated" and not args.only_value and not args.no_sharded:
+        view = open_shards("sharded")
+        leg2 = ResidentLeg(L, _lib, g, view, ccfg, dev, w, threads, group, depth, seeds_dev, gidx, rank, world)
+        leg2.run(0, first_timed)
+        runs2 = timed_repeats(leg2.run, first_timed, n_timed, max(1, min(args.repeats, 3)), barrier, max_over_ranks,
+                              sum_over_ranks)
+        sharded = sharded_summary(w, world, median_run(runs2), stored_row, leg2, view, feats, dev, sum_over_ranks, "sharded",
+                                  args.steps)
+        sharded["vs_replicated"] = sharded["value"] / value if value else None
+        leg2.close()
+        barrier()  # no rank frees its shard while a peer may still be reading it
+        del leg2, view
+        barrier()
+
+    secondary = None
+    if rank == 0 and world == 1 and not args.only_value and not args.brief and not args.no_secondary \
+            and args.workload == "c2":
+        del g, feats
+        torch.cuda.empty_cache()
+        g = feats = None
+        secondary = secondary_legs(args)
 
     if rank == 0:
-        hops = len(w["fanout"])
+        chains = -(-n_timed // group)
         line = {
             "metric": METRIC, "value": value, "unit": "edges/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / max(args.steps, 1), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "u32 ids / " + w["dtype"] + "->f32",
             "data": "synthetic (seeded R-MAT graph + ~N(0,1) features generated in HBM)",
-            "config": {"workload": w["label"], "batches_per_step": per_step, "rng_mode": "wyrand_exact",
-                       "sampler_threads": threads, "group": group, "prefetch_depth": depth, "parallelism": f"dp{world}",
-                       "features": ("%s, remote rows over NVLink (%d/%d of the rows)"
-                                    % ("sharded by contiguous vertex range" if args.features == "sharded-range"
-                                       else "sharded round-robin by vertex id", world - 1, world))
-                       if (args.features != "replicated" and world > 1) else "replicated",
-                       "inputs_larger_than_l2": True},
-            "gather_gbs": gather_gbs, "edges_per_step": tot_edges / max(args.steps, 1),
-            "rows_per_step": tot_nodes / max(args.steps, 1), "setup_s": round(t_setup, 1),
+            "config": common_config(w, world, features_label(main_layout)),
+            "impl_config": {"sampler_threads": threads, "group": group, "prefetch_depth": depth,
+                            "implementation": "libaethergpu.so (CUDA, sm_100a) through the C ABI"},
+            "repeats": {"n": med["n"], "min": med["min"], "max": med["max"],
+                        "note": f"value = median of {med['n']} timed regions of {args.steps} steps each"},
+            "gather_gbs": gather_gbs, "edges_per_step": med["edges"] / max(args.steps, 1),
+            "rows_per_step": med["nodes"] / max(args.steps, 1), "setup_s": round(t_setup, 1),
+            "timed_region_s": round(ms * 1e-3, 4),
             "clocks": clk, "roofline": roofline, "cpu_baseline": cpu, "parity_full_scale": parity,
-            "e2e": None if e2e_value is None else {
-                "value": e2e_value, "unit": "edges/s", "h2d_bytes_per_step": world * per_step * bs * 4,
+            "e2e": None if e2e_med is None else {
+                "value": e2e_med["value"], "unit": "edges/s", "h2d_bytes_per_step": world * per_step * bs * 4,
                 "d2h_bytes_per_step": world * per_step * C.sizeof(_lib.SampleCounts),
-                "ms_per_step": ms_e2e / max(args.steps, 1),
-                "note": "public Python API: host seed arrays in, per-batch counts out; the sampled batch and "
-                        "its feature rows stay in GPU memory, where the training step reads them",
-                "host_results": {"value": host_value, "unit": "edges/s", "ms_per_step": host_ms / max(args.steps, 1),
-                                 "d2h_bytes_per_step": d2h_host / max(args.steps, 1),
+                "ms_per_step": e2e_med["ms"] / max(args.steps, 1), "min": e2e_med["min"], "max": e2e_med["max"],
+                "note": "public Python API: host seed arrays in (submit_epoch, a chain at a time), per-batch "
+                        "counts out; the sampled batch and its feature rows stay in GPU memory, where the "
+                        "training step reads them",
+                "host_results": {"value": host_med["value"], "unit": "edges/s", "sample": host_sample,
+                                 "d2h_bytes_per_batch": d2h_host / max(1, host_batches),
                                  "note": "same calls, every batch (int64 ids, local edge index, f32 feature rows) "
                                          "also copied to pinned host memory: PCIe-bound"}},
+            "sharded": sharded, "secondary": secondary,
             # one launch chain per group of batches (the batch is blockIdx.y): seed insert,
-            # hops + 1 assign, hops pick, finalize, gather
-            "gpu_launches": world * -(-n_timed // group) * (2 * hops + 4),
+            # hops + 1 assign, hops pick, gather (sharded: + key, sorted gather, overflow)
+            "gpu_launches": world * chains * (2 * hops + 3 + (3 if sharded_main else 0)),
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -509,6 +633,70 @@ def run_device(args, w):
         del feats
         barrier()
         dist.destroy_process_group()
+
+
+def sharded_summary(w, world, med, stored_row, leg, view, replicated, dev, sum_over_ranks, layout_flag, steps):
+    """The record of a leg over sharded features: throughput, the remote share of the
+    stored rows as GB/s per GPU against the measured peer-copy bandwidth, and a bit
+    for bit check of the last delivered batch's rows (most of them remote) against the
+    replicated table (or, without one, rows regenerated from the counter-based generator)."""
+    import torch
+
+    from aethergraph_b200 import synth
+    from aethergraph_b200.sampler import _Buffers
+
+    ms = med["ms"]
+    remote_share = (world - 1) / world
+    remote_gbs = med["nodes"] * stored_row * remote_share / (ms * 1e-3) / 1e9 / world
+    ok, checked = True, 0
+    if leg.recent:
+        holder = _Buffers(leg.ring[0].c, leg.ring, dev, w["dim"])
+        n_id_ptr, x_ptr, n = leg.recent[-1]
+        n = int(n)
+        ids = holder.view(n_id_ptr, (n,), "<i8")
+        x = holder.view(x_ptr, (n, w["dim"]), "<f4")
+        if replicated is not None:
+            want = replicated.gather(ids)
+            ok = bool(torch.equal(x.view(torch.int32), want.view(torch.int32)))
+            checked = n
+        else:
+            # regenerate some of the rows from (seed, row, column): contiguous runs of the table
+            pick = ids[:: max(1, n // 64)][:64].tolist()
+            for v in pick:
+                one = synth.features(w["nodes"], w["dim"], w["dtype"], FEATURE_SEED, row_range=(v, v + 1))
+                want = one.gather(torch.tensor([v], dtype=torch.int64, device=dev))
+                pos = int((ids == v).nonzero()[0])
+                ok = ok and bool(torch.equal(x[pos].view(torch.int32), want[0].view(torch.int32)))
+                checked += 1
+        del holder
+    ok_all = sum_over_ranks(1.0 if ok else 0.0) == float(world)
+    return {"layout": "contiguous vertex ranges" if layout_flag == "sharded-range" else "round-robin by vertex id",
+            "value": med["value"], "unit": "edges/s", "ms_per_step": ms / max(steps, 1),
+            "min": med["min"], "max": med["max"],
+            "gather_gbs": med["nodes"] * gather_bytes_per_row(w) / (ms * 1e-3) / 1e9,
+            "remote_gbs_per_gpu": remote_gbs, "frac_of_peer_copy_peak": remote_gbs / NVLINK_PEER_COPY_GBS,
+            "peer_copy_peak_gbs": NVLINK_PEER_COPY_GBS,
+            "remote_note": "stored row bytes of the remote share of the gathered rows (as if no row were fetched "
+                           "twice) per second and GPU; rows named by several batches of a chain cross the link once",
+            "parity": bool(ok_all), "parity_rows_checked_per_rank": checked}
+
+
+def secondary_legs(args) -> dict:
+    """C1, C3 and C4 at 1/10 size, each in its own process after the main workload
+    has left the GPU: value, CPU baseline and full-size parity of each."""
+    out = {}
+    for name, steps in (("c1", 4), ("c3", 2), ("c4s", 2)):
+        cmd = [sys.executable, os.path.abspath(__file__), "--workload", name, "--steps", str(steps), "--warmup", "3",
+               "--repeats", "3", "--brief", "--cpu-seconds", "4"]
+        try:
+            r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+            line = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
+            out[name] = {k: line.get(k) for k in ("value", "unit", "ms_per_step", "gather_gbs", "cpu_baseline",
+                                                  "parity_full_scale", "repeats", "steps")}
+            out[name]["workload"] = line["config"]["workload"]
+        except Exception as e:  # a failed secondary leg must not lose the main line
+            out[name] = {"error": f"{type(e).__name__}: {e}"[:300]}
+    return out
 
 
 # --------------------------------------------------------------------------- #
@@ -522,7 +710,7 @@ HETERO = {
 }
 
 
-def hetero_cpu_leg(g, nn, ets, fan, host_rel, seeds, stores):
+def hetero_cpu_leg(g, nn, ets, fan, host_rel, seeds, stores, seconds=6.0):
     """The CPU restatement of the hetero sampler on the same relations (one thread,
     sampling only) and a bit-for-bit check of one batch and its gathered rows."""
     import torch
@@ -543,7 +731,7 @@ def hetero_cpu_leg(g, nn, ets, fan, host_rel, seeds, stores):
     o = ago.HeteroSampler([nn[k] for k in names], rels, fan, seed=SAMPLER_SEED)
     ok, cpu_edges, t_cpu = True, 0, time.time()
     nb_cpu = 0
-    while time.time() - t_cpu < 6.0 and nb_cpu < len(seeds):
+    while time.time() - t_cpu < seconds and nb_cpu < len(seeds):
         o.reseed(ago.batch_seed(SAMPLER_SEED, nb_cpu))
         want = o.sample(0, seeds[nb_cpu])
         cpu_edges += sum(len(x) for x in want["edge_src_local"])
@@ -605,7 +793,7 @@ def run_hetero(args, hw):
     torch.cuda.synchronize()
     t_setup = time.time() - t0
     cfg = ag.HeteroSamplingConfig(dict(zip(ets, fan)), seed=SAMPLER_SEED)
-    bs, per_step = 1024, BATCHES_PER_STEP
+    bs, per_step = 1024, int(hw.get("per_step", 128))
     n_batches = (args.warmup + args.steps) * per_step
     seeds = [synth.seed_batch(nn["user"], bs, SEEDS_SEED, b) for b in range(n_batches)]
     group = args.group if args.group else 16
@@ -627,32 +815,39 @@ def run_hetero(args, hw):
         return edges, rows_b
 
     run(0, args.warmup * per_step)
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    edges, gbytes = run(args.warmup * per_step, args.steps * per_step)
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1)
+    runs = []
+    for _ in range(max(1, args.repeats)):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        edges, gbytes = run(args.warmup * per_step, args.steps * per_step)
+        e1.record()
+        torch.cuda.synchronize()
+        runs.append((e0.elapsed_time(e1), edges, gbytes))
+    med = median_run(runs)
+    ms, edges, gbytes = med["ms"], med["edges"], med["nodes"]
     loader.shutdown()
     cpu, ok = None, None
     if not args.no_cpu and sc > 1:
-        cpu, ok = hetero_cpu_leg(g, nn, ets, fan, host_rel, seeds, stores)
+        cpu, ok = hetero_cpu_leg(g, nn, ets, fan, host_rel, seeds, stores, min(6.0, args.cpu_seconds))
     line = {
         "metric": METRIC, "value": edges / (ms * 1e-3), "unit": "edges/s", "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms / max(args.steps, 1), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "u32 ids / bf16->f32", "data": "synthetic (per-relation R-MAT generated in HBM)",
-        "config": {"workload": hw["label"], "batches_per_step": per_step, "sampler_threads": args.threads, "group": group,
+        "config": {"workload": hw["label"], "batches_per_step": per_step,
                    "fanout": {"/".join(et): f for et, f in zip(ets, fan)}},
+        "impl_config": {"sampler_threads": args.threads, "group": group},
+        "repeats": {"n": med["n"], "min": med["min"], "max": med["max"]},
         "gather_gbs": gbytes / (ms * 1e-3) / 1e9, "edges_per_step": edges / max(args.steps, 1), "setup_s": round(t_setup, 1),
         "cpu_baseline": cpu, "parity_full_scale": ok,
     }
     print(json.dumps(line), flush=True)
 
 
-def cpu_baseline(g, feats, w, cfg):
+def cpu_baseline(g, feats, w, cfg, seconds: float = 10.0, ref_kernel: bool = True):
     """Times the CPU restatement on a bounded sample of the same workload (graph and
-    features copied back from the GPU) and checks two full-size batches bit for bit."""
+    features copied back from the GPU; about `seconds` of CPU work) and checks two
+    full-size batches bit for bit."""
     import aethergraph_b200 as ag
     from aethergraph_b200 import synth
     from oracle import ago
@@ -673,12 +868,12 @@ def cpu_baseline(g, feats, w, cfg):
     while True:
         seeds = np.concatenate(seeds_host[:nb])
         r = s.bench(payload, w["dim"], w["dtype"], seeds, bs, 0, threads)
-        if r["seconds"] >= 8.0 or nb >= cap:
+        if r["seconds"] >= 0.8 * seconds or nb >= cap:
             break
-        nb = min(cap, max(nb + 1, int(nb * min(16.0, 12.0 / max(r["seconds"], 1e-3)))))
+        nb = min(cap, max(nb + 1, int(nb * min(16.0, 1.2 * seconds / max(r["seconds"], 1e-3)))))
         seeds_host += [synth.seed_batch(w["nodes"], bs, SEEDS_SEED, b) for b in range(len(seeds_host), nb)]
     # one thread, one persistent sampler reused across batches (the reference's NeighborSampler reuse)
-    n1 = max(4, min(nb, int(4.0 * nb / max(r["seconds"], 1e-3) / threads)))
+    n1 = max(4, min(nb, int(0.4 * seconds * nb / max(r["seconds"], 1e-3) / threads)))
     r1 = s.bench(payload, w["dim"], w["dtype"], np.concatenate(seeds_host[:n1]), bs, 0, 1)
     cpu = {"value": r["edges"] / r["seconds"], "unit": "edges/s", "cores": threads, "kind": "port",
            "gather_gbs": r["nodes"] * gather_bytes_per_row(w) / r["seconds"] / 1e9,
@@ -698,7 +893,8 @@ def cpu_baseline(g, feats, w, cfg):
             ok = ok and np.array_equal(got[k], want[k])
         xw = ago.gather(payload, n, w["dim"], w["dtype"], want["nodes"])
         ok = ok and np.array_equal(sg.x.cpu().numpy().view(np.uint32), xw.view(np.uint32))
-    cpu["reference_gpu_hop1"] = reference_gpu_hop1(g, w, seeds_host)
+    if ref_kernel:
+        cpu["reference_gpu_hop1"] = reference_gpu_hop1(g, w, seeds_host)
     return cpu, bool(ok)
 
 
@@ -759,21 +955,30 @@ def main():
     ap.add_argument("--workload", default=os.environ.get("AG_BENCH_WORKLOAD", "c2"),
                     choices=sorted(WORKLOADS) + sorted(HETERO))
     ap.add_argument("--threads", type=int, default=int(os.environ.get("AG_BENCH_THREADS", "0")),
-                    help="loader worker threads, each with its own CUDA stream (0: 3, heterogeneous workloads 2)")
+                    help="loader worker threads, each with its own CUDA stream (0: the workload's, normally 3; "
+                         "heterogeneous workloads 2)")
     ap.add_argument("--depth", type=int, default=0, help="prefetch depth (0: max(8, group / 2))")
     ap.add_argument("--group", type=int, default=int(os.environ.get("AG_BENCH_GROUP", "0")),
-                    help="batches a worker runs as one launch chain (0: chosen from --steps)")
+                    help="batches a worker runs as one launch chain (0: the workload's, normally 32)")
     ap.add_argument("--features", default="replicated", choices=["replicated", "sharded", "sharded-range"],
                     help="with more than one GPU: every GPU holds all feature rows, or 1/N of them "
                          "(dealt round-robin, or as contiguous vertex ranges)")
+    ap.add_argument("--repeats", type=int, default=5,
+                    help="timed regions of --steps steps each; the median is reported, with min and max")
+    ap.add_argument("--cpu-seconds", type=float, default=10.0, help="CPU work of the bounded cpu_baseline sample")
+    ap.add_argument("--brief", action="store_true",
+                    help="value, cpu_baseline and parity only (what a secondary workload reports)")
+    ap.add_argument("--no-sharded", action="store_true", help="2 or more GPUs: skip the sharded-features record")
+    ap.add_argument("--no-secondary", action="store_true", help="1 GPU: skip the secondary workloads (C1, C3, C4 at 1/10)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--only-value", action="store_true",
                     help="run the resident (C ABI) leg only: no e2e, no CPU baseline (profiling runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
-    if args.threads <= 0:
-        args.threads = 2 if args.workload in HETERO else 3
+    args.repeats = max(1, args.repeats)
     if args.workload in HETERO:
+        if args.threads <= 0:
+            args.threads = 2
         return run_hetero(args, HETERO[args.workload])
     w = WORKLOADS[args.workload]
     if args.impl == "reference":

@@ -463,6 +463,13 @@ typedef struct {
 int32_t ag_loader_create(const ag_graph *g, const ag_features *f, const ag_sampling_config *cfg,
                          int32_t seeded, uint32_t prefetch_depth, uint32_t sampler_threads,
                          uint32_t group, int32_t profiling, ag_loader **out);
+/* Data-parallel ranks: batch number seq of this loader is sampled from
+ * ag_batch_seed(cfg->seed, base + stride * seq).  Rank r of W ranks that takes
+ * global batches r, r + W, ... sets (r, W) and every global batch draws from
+ * the same stream at any W — the invariance the reference tests for its thread
+ * pool (loader/sampler.rs:3116-3148; prefetch.rs:926-930 is the per-batch
+ * reseed).  Default (0, 1).  Only before the first submit. */
+int32_t ag_loader_set_seed_sequence(ag_loader *l, uint64_t base, uint64_t stride);
 int32_t ag_loader_bounds(const ag_loader *l, uint64_t n_seeds, uint64_t *max_nodes,
                          uint64_t *max_edges);
 int32_t ag_loader_submit(ag_loader *l, int64_t batch_idx, const uint32_t *seeds, uint64_t n_seeds,

@@ -336,13 +336,23 @@ static inline void v64_push(vec64 *v, uint64_t x) {
     if (v->n == v->cap) { v->cap = v->cap ? v->cap * 2 : 1024; v->p = (uint64_t *)realloc(v->p, v->cap * 8); }
     v->p[v->n++] = x;
 }
-static uint32_t *v32_take(vec32 *v) {
+/* Hands the array to the caller and leaves a fresh one of capacity `next_cap`
+ * behind (0: none) — the swap with a planned-capacity vector of
+ * sampler.rs:897-924, so the next batch does not regrow from nothing. */
+static uint32_t *v32_take(vec32 *v, size_t next_cap) {
     uint32_t *p = v->p ? v->p : (uint32_t *)malloc(4);
-    v->p = NULL; v->n = v->cap = 0; return p;
+    v->p = next_cap ? (uint32_t *)malloc(next_cap * 4) : NULL;
+    v->n = 0; v->cap = v->p ? next_cap : 0; return p;
 }
-static uint64_t *v64_take(vec64 *v) {
+static uint64_t *v64_take(vec64 *v, size_t next_cap) {
     uint64_t *p = v->p ? v->p : (uint64_t *)malloc(8);
-    v->p = NULL; v->n = v->cap = 0; return p;
+    v->p = next_cap ? (uint64_t *)malloc(next_cap * 8) : NULL;
+    v->n = 0; v->cap = v->p ? next_cap : 0; return p;
+}
+/* loader/mod.rs:27-29 */
+static inline size_t planned_capacity(size_t produced, size_t floor) {
+    size_t c = produced + produced / 8;
+    return c > floor ? c : floor;
 }
 
 /* Floyd membership for one node's draws (sampler.rs:1342-1379).  The
@@ -542,6 +552,19 @@ int64_t ago_sample(ago_sampler *s, const uint32_t *seeds, size_t n, ago_subgraph
         s->nf_id.n = s->nf_local.n = 0;
         size_t flen = s->fr_id.n;
         for (size_t fi = 0; fi < flen; ++fi) {
+            /* sampler.rs:786-800: the offsets pair of the vertex 4 ahead and the row
+             * start of the vertex 2 ahead (FRONTIER_PREFETCH_DIST = 4, genstamp.rs:23) */
+            if (fi + 4 < flen) {
+                uint64_t ahead = s->fr_id.p[fi + 4];
+                if (ahead < s->g.num_nodes) __builtin_prefetch(&s->g.offsets[ahead], 0, 3);
+            }
+            if (fi + 2 < flen) {
+                uint64_t ahead = s->fr_id.p[fi + 2];
+                if (ahead < s->g.num_nodes) {
+                    uint64_t st = s->g.offsets[ahead];
+                    if (st < s->g.num_edges) __builtin_prefetch(&s->g.edges[st], 0, 3);
+                }
+            }
             uint32_t node = s->fr_id.p[fi], node_local = s->fr_local.p[fi];
             /* csr.rs:318-335 */
             if ((uint64_t)node >= s->g.num_nodes) continue;
@@ -560,13 +583,16 @@ int64_t ago_sample(ago_sampler *s, const uint32_t *seeds, size_t n, ago_subgraph
     }
 
     out->num_nodes = s->nodes.n; out->num_edges = s->edge_src.n; out->num_seeds = n;
-    out->nodes = v32_take(&s->nodes);
-    out->edge_src = v32_take(&s->edge_src);
-    out->edge_dst = v32_take(&s->edge_dst);
-    out->src_local = v32_take(&s->src_local);
-    out->dst_local = v32_take(&s->dst_local);
-    out->seed_locals = v32_take(&s->seed_locals);
-    if (s->track_edge_ids) out->edge_ids = v64_take(&s->edge_ids);
+    /* sampler.rs:897-924: each array is swapped for one sized from what this call
+     * produced (MIN_NODE_CAPACITY 512, MIN_EDGE_CAPACITY 2048, sampler.rs:410-411) */
+    const size_t ncap = planned_capacity(s->nodes.n, 512), ecap = planned_capacity(s->edge_src.n, 2048);
+    out->nodes = v32_take(&s->nodes, ncap);
+    out->edge_src = v32_take(&s->edge_src, ecap);
+    out->edge_dst = v32_take(&s->edge_dst, ecap);
+    out->src_local = v32_take(&s->src_local, ecap);
+    out->dst_local = v32_take(&s->dst_local, ecap);
+    out->seed_locals = v32_take(&s->seed_locals, n ? n : 1);
+    if (s->track_edge_ids) out->edge_ids = v64_take(&s->edge_ids, ecap);
     out->draws = s->draws - draws_before;
     return 0;
 }
@@ -769,14 +795,14 @@ int64_t ago_hetero_sample(ago_hetero_sampler *s, uint32_t seed_type,
     out->edge_src_local = (uint32_t **)calloc(s->et ? s->et : 1, sizeof(uint32_t *));
     out->edge_dst_local = (uint32_t **)calloc(s->et ? s->et : 1, sizeof(uint32_t *));
     out->num_edges = (size_t *)calloc(s->et ? s->et : 1, sizeof(size_t));
-    for (uint32_t t = 0; t < s->nt; ++t) { out->num_nodes[t] = s->nodes[t].n; out->nodes[t] = v32_take(&s->nodes[t]); }
+    for (uint32_t t = 0; t < s->nt; ++t) { out->num_nodes[t] = s->nodes[t].n; out->nodes[t] = v32_take(&s->nodes[t], planned_capacity(s->nodes[t].n, 0)); }
     for (uint32_t e = 0; e < s->et; ++e) {
         out->num_edges[e] = s->esrc[e].n;
-        out->edge_src_local[e] = v32_take(&s->esrc[e]);
-        out->edge_dst_local[e] = v32_take(&s->edst[e]);
+        out->edge_src_local[e] = v32_take(&s->esrc[e], planned_capacity(s->esrc[e].n, 0));
+        out->edge_dst_local[e] = v32_take(&s->edst[e], planned_capacity(s->edst[e].n, 0));
     }
     out->num_seeds = n;
-    out->seed_indices = v32_take(&s->seed_indices);
+    out->seed_indices = v32_take(&s->seed_indices, n ? n : 1);
     out->draws = s->draws - draws_before;
     return 0;
 }

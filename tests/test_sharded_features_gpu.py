@@ -107,6 +107,67 @@ def test_loader_with_sharded_features_matches_the_oracle():
             assert np.array_equal(x.cpu().numpy().view(np.uint32), xw.view(np.uint32))
 
 
+@pytest.mark.parametrize("layout", ["range", "cyclic"])
+def test_chains_over_sharded_features_fetch_each_row_once_and_in_place(layout):
+    """A launch chain over a sharded store gathers its rows in address order, a row
+    named by several batches once.  Batches that share most of their vertices (the
+    same seeds), batches far larger than the chain before them (rows past the
+    estimate take the unsorted pass) and empty batches must all come out exactly
+    as the oracle's rows."""
+    import aethergraph_b200 as ag
+    from aethergraph_b200 import synth
+    from oracle import ago
+
+    n, off, dst, _ = rmat_csr(13, 12, seed=4)
+    g = ag.Graph.from_csr(off, dst)
+    dim, world = 64, 4
+    shards = [synth.features_shard(n, dim, "bf16", 17, r, world, layout) for r in range(world)]
+    view = ag.FeatureStore.view_sharded(shards, 2)
+    payload = ago.synth_features(n, dim, "bf16", 17)
+    s = ago.Sampler(off, dst, [10, 5], seed=11)
+    rng = np.random.default_rng(5)
+    same = rng.integers(0, n, 300).astype(np.uint32)
+    batches = [rng.integers(0, n, 4).astype(np.uint32) for _ in range(8)]          # a small chain first
+    batches += [same.copy() for _ in range(8)]                                      # then big, overlapping ones
+    batches += [np.empty(0, dtype=np.uint32), rng.integers(0, n, 700).astype(np.uint32)]
+    batches += [rng.integers(0, n, 50).astype(np.uint32) for _ in range(6)]
+    with ag.NeighborLoader(g, ag.SamplingConfig(num_neighbors=[10, 5], seed=11), prefetch_depth=8, sampler_threads=1,
+                           features=view, group=8) as ld:
+        for i, b in enumerate(batches):
+            ld.submit(i, b)
+        for i, b in enumerate(batches):
+            idx, sg, x = ld.next_batch()
+            s.reseed(ago.batch_seed(11, i))
+            want = s.sample(b)
+            assert idx == i and np.array_equal(sg.raw_u32()["nodes"], want["nodes"])
+            xw = ago.gather(payload, n, dim, "bf16", want["nodes"])
+            assert np.array_equal(x.cpu().numpy().view(np.uint32).reshape(-1, dim), xw.view(np.uint32).reshape(-1, dim)), i
+
+
+def test_sorted_and_unsorted_sharded_gather_agree_on_duplicates():
+    """ag_gather on a sharded view: ids with many repeats, in both id widths."""
+    import torch
+
+    import aethergraph_b200 as ag
+    from aethergraph_b200 import synth
+    from oracle import ago
+
+    n, dim, world = 9001, 256, 8
+    shards = [synth.features_shard(n, dim, "f16", 3, r, world, "cyclic") for r in range(world)]
+    view = ag.FeatureStore.view_sharded(shards, 0)
+    payload = ago.synth_features(n, dim, "f16", 3)
+    rng = np.random.default_rng(9)
+    ids = np.concatenate([rng.integers(0, 50, 6000), rng.integers(0, n, 6000), [n - 1] * 40, [0] * 40])
+    rng.shuffle(ids)
+    want = ago.gather(payload, n, dim, "f16", ids.astype(np.uint32))
+    for t in (torch.from_numpy(ids).cuda(), torch.from_numpy(ids.astype(np.int32)).cuda()):
+        got = view.gather(t)
+        assert np.array_equal(got.cpu().numpy().view(np.uint32), want.view(np.uint32))
+    with pytest.raises(ValueError, match="out of bounds"):
+        view.gather(torch.from_numpy(np.concatenate([ids, [n]])).cuda())
+        view.check()
+
+
 _WORKER = r"""
 import os, sys
 import numpy as np

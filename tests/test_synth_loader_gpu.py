@@ -39,6 +39,23 @@ def test_rmat_matches_cpu_twin(ag, ago, n, e):
         assert np.all(np.diff(key) >= 0)
 
 
+@pytest.mark.parametrize("n,e,budget", [(1 << 12, 1 << 16, 5000), (5000, 60000, 1), (70_001, 400_000, 150_000)])
+def test_rmat_built_in_source_ranges_is_the_same_graph(ag, ago, n, e, budget, monkeypatch):
+    """Graphs whose sort keys exceed the free device memory are built a range of source
+    ids at a time; forced here with a small budget of edges per range (weights included)."""
+    from aethergraph_b200 import synth
+
+    monkeypatch.setenv("AG_SYNTH_PARTITION_EDGES", str(budget))
+    g = synth.rmat_graph(n, e, seed=11, weight_sigma=1.0)
+    monkeypatch.delenv("AG_SYNTH_PARTITION_EDGES")
+    whole = synth.rmat_graph(n, e, seed=11, weight_sigma=1.0)
+    off, dst, w = g.to_host()
+    off2, dst2, w2 = whole.to_host()
+    assert np.array_equal(off, off2) and np.array_equal(dst, dst2) and np.array_equal(w, w2)
+    off3, dst3 = ago.synth_rmat_csr(n, n, e, 11, threads=4)
+    assert np.array_equal(off, off3) and np.array_equal(dst, dst3)
+
+
 def test_rmat_is_skewed_and_weighted(ag):
     from aethergraph_b200 import synth
 
@@ -158,3 +175,33 @@ def test_loader_backpressure_does_not_deadlock(ag, world):
             loader.submit(i, np.arange(i, i + 32, dtype=np.uint32))
         t.join(60)
         assert done == list(range(total))
+
+
+def test_seed_sequence_makes_batches_independent_of_the_rank_count(ag, ago, world):
+    """Rank r of W ranks takes global batches r, r + W, ... and sets the loader's seed
+    sequence to (r, W): every global batch is then sampled from batch_seed(seed, b),
+    whatever W is (the property the reference tests for its thread pool,
+    crates/aethergraph-core/src/loader/sampler.rs:3116-3148)."""
+    n, g, feats, off, dst, payload = world
+    cfg = ag.SamplingConfig(num_neighbors=[5, 3], seed=77)
+    s = ago.Sampler(off, dst, [5, 3], seed=77)
+    rng = np.random.default_rng(1)
+    batches = [rng.integers(0, n, 64).astype(np.uint32) for _ in range(12)]
+    for W in (1, 2, 3):
+        for r in range(W):
+            mine = list(range(r, len(batches), W))
+            with ag.NeighborLoader(g, cfg, prefetch_depth=4, sampler_threads=2, group=4, seed_sequence=(r, W)) as ld:
+                ld.submit_epoch([batches[b] for b in mine], mine)
+                for b in mine:
+                    idx, sg, _ = ld.next_batch()
+                    s.reseed(ago.batch_seed(77, b))
+                    want = s.sample(batches[b])
+                    assert idx == b
+                    got = sg.raw_u32()
+                    for k in ("nodes", "edge_dst", "src_local", "dst_local"):
+                        assert np.array_equal(got[k], want[k]), (W, r, b, k)
+    with ag.NeighborLoader(g, cfg, prefetch_depth=2, sampler_threads=1) as ld:
+        ld.submit(0, batches[0])
+        from aethergraph_b200 import _lib
+        assert _lib.lib().ag_loader_set_seed_sequence(ld._h, 1, 2) == _lib.AG_ERR_VALUE  # only before the first submit
+        ld.next_batch()
