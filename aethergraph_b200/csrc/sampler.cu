@@ -4,7 +4,7 @@
 // (crates/aethergraph-core/src/loader/sampler.rs:845-961 with the hop loop at
 // :754-842 and the per-node dispatch at :1178-1235), but as a short chain of
 // data-parallel kernels instead of one sequential loop.  A batch with H hops
-// is 2H + 3 launches:
+// is 2H + 2 launches:
 //
 //   insert_seeds   every seed is inserted into a hash table keyed by vertex id
 //                  with atomicMin(position): the smallest position that names a
@@ -25,8 +25,12 @@
 //                  (:1418-1469) — writes the edges of hop s at their scanned
 //                  slots and inserts the destinations into the table as the
 //                  items of stage s + 1.
-//   finalize       every edge and seed reads its endpoint's final local id from
-//                  the table; the int64 views the Python API exposes are written.
+//                  Every item also learns its vertex's final local id here (its own
+//                  if it is the first sighting, else the one the first sighting got,
+//                  for which it may have to wait a moment), so dst_local / seed_locals
+//                  and the int64 views the Python API exposes are written by the same
+//                  kernel; the block that finishes last in the last stage writes the
+//                  batch's counts.
 //
 // The reference draws from one sequential WyRand stream per batch.  WyRand's
 // state is an additive counter, so draw d is a pure function of (seed, d); the
@@ -159,6 +163,7 @@ __device__ __forceinline__ void emit_edge(const SampleParams &p, uint32_t hop, u
     if (p.edge_src) p.edge_src[e] = fe.id;
     p.edge_dst[e] = d;
     if (p.edge_ids) p.edge_ids[e] = pos;
+    if (p.e_id && p.edge_ids) p.e_id[e] = (int64_t)pos;
     p.src_local[e] = fe.local;
     if ((uint64_t)d >= p.num_nodes) {
         // Only reachable on a graph that skipped validation; the reference drops
@@ -407,7 +412,56 @@ __device__ __forceinline__ void pick_weighted(const SampleParams &p, uint32_t ho
 
 // One stage: assign local ids to the first sightings among the stage's items
 // and (has_next) queue the new vertices, with their row bounds, edge slots and
-// draw offsets, as the frontier the pick kernel of hop `stage` expands.
+// draw offsets, as the frontier the pick kernel of hop `stage` expands.  Every
+// item also writes the final local id of its vertex (dst_local / seed_locals and
+// the int64 views): its own if it is the first sighting, the one already in the
+// table if the vertex was registered by an earlier stage, and otherwise the one
+// an earlier item of this stage is about to store — a short, bounded wait that is
+// taken only after the block has passed its next barrier, so a block never waits
+// for a store of its own.
+__device__ __forceinline__ StageInfo load_stage_cg(const StageInfo *s) {
+    // other blocks of this launch wrote it: read it from L2, not from a stale L1 line
+    const uint4 a = __ldcg((const uint4 *)s), b = __ldcg((const uint4 *)s + 1);
+    StageInfo r;
+    r.n_nodes = a.x; r.n_edges = a.y; r.frontier_n = a.z; r.hop_edges = a.w;
+    r.draws = ((uint64_t)b.y << 32) | b.x; r.hop_draws = ((uint64_t)b.w << 32) | b.z;
+    return r;
+}
+
+__device__ __forceinline__ void write_item_local(const SampleParams &p, uint32_t stage, uint32_t n_edges_before,
+                                                 uint32_t item, uint32_t local) {
+    if (stage == 0) {
+        p.seed_locals[item] = local;
+        if (p.seed_index) p.seed_index[item] = (int64_t)local;
+    } else {
+        const uint64_t e = (uint64_t)n_edges_before + item;
+        if (e >= p.cap_edges) return;
+        p.dst_local[e] = local;
+        if (p.edge_index_local) p.edge_index_local[e] = (int64_t)local;  // row 0: sampled neighbor
+    }
+}
+
+// Called by one thread once every block of the batch's last kernel has finished.
+__device__ __noinline__ void publish_counts(const SampleParams &p, BatchState *bs) {
+    __threadfence();
+    const StageInfo fin = load_stage_cg(&bs->stage[p.num_hops + 1]);
+    ag_sample_counts c{};
+    c.num_nodes = (uint32_t)min((uint64_t)fin.n_nodes, p.cap_nodes);
+    c.num_edges = (uint32_t)min((uint64_t)fin.n_edges, p.cap_edges);
+    c.num_seeds = p.n_seeds;
+    c.num_hops = p.num_hops;
+    for (uint32_t st = 0; st <= p.num_hops; ++st) c.nodes_per_hop[st] = __ldcg(&bs->nodes_per_stage[st]);
+    for (uint32_t h = 0; h < p.num_hops; ++h) c.edges_per_hop[h] = load_stage_cg(&bs->stage[h + 1]).hop_edges;
+    c.draws = fin.draws - load_stage_cg(&bs->stage[0]).draws;
+    c.error = atomicOr(&bs->error, 0u);
+    if ((uint64_t)fin.n_nodes > p.cap_nodes || (uint64_t)fin.n_edges > p.cap_edges) c.error |= kErrCapacity;
+    *p.counts = c;
+    bs->stream_pos = fin.draws;  // a bare sampler keeps consuming the same stream
+    bs->error = 0;               // ready for the handle's next batch
+    bs->ticket = 0;
+    bs->done_blocks = 0;
+}
+
 template <bool HAS_NEXT>
 __global__ void __launch_bounds__(kTile, HAS_NEXT ? 2 : 3)
 k_assign(const SampleParams *__restrict__ pa, uint32_t stage, uint32_t k) {
@@ -432,30 +486,54 @@ k_assign(const SampleParams *__restrict__ pa, uint32_t stage, uint32_t k) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t gen = p.table.gen;
 
+    if (!has_next && p.edge_index_local) {
+        // Last stage: every edge of the batch exists, so the row offset of the int64
+        // [2, E] local edge index is known.  Row 1 = the expanded vertex's local id.
+        const uint64_t total = min((uint64_t)edges_before_next, p.cap_edges);
+        for (uint64_t e = (uint64_t)blockIdx.x * kTile + threadIdx.x; e < total; e += (uint64_t)gridDim.x * kTile)
+            p.edge_index_local[total + e] = (int64_t)p.src_local[e];
+    }
+
+    uint32_t wait_slot = 0xFFFFFFFFu, wait_item = 0;  // an item of the previous tile whose vertex is still pending
+
     // The grid is sized for a typical batch, not for the worst case: a block
     // keeps drawing tile tickets until they run out.  Tickets are handed out in
-    // order, so the tiles a look-back waits for are always already running.
+    // order, so the tiles a look-back (or a pending vertex) waits for are always
+    // already running.
     for (;;) {
         __syncthreads();
+        if (wait_slot != 0xFFFFFFFFu) {
+            // The first sighting is an earlier item of this stage: in this block's last tile
+            // (stored before the barrier above) or in a tile with a smaller ticket.
+            uint32_t v = (uint32_t)__ldcg((const unsigned long long *)&p.table.slots[wait_slot]), spins = 0;
+            while (v & kPendingBit) {
+                if (++spins > kSpinLimit) { atomicOr(&bs->error, kErrSpinTimeout); break; }
+                __nanosleep(40);
+                v = (uint32_t)__ldcg((const unsigned long long *)&p.table.slots[wait_slot]);
+            }
+            write_item_local(p, stage, si.n_edges, wait_item, (v & kPendingBit) ? 0xFFFFFFFFu : (v & kPosMask));
+            wait_slot = 0xFFFFFFFFu;
+        }
         if (threadIdx.x == 0) s_tile = atomicAdd(&bs->ticket, 1u);
         __syncthreads();
         const uint32_t tile = s_tile;
         if (tile >= n_tiles) {
             // n_tiles + gridDim.x tickets are drawn in all; the last one resets the counter.
             if (threadIdx.x == 0 && tile == n_tiles + gridDim.x - 1) bs->ticket = 0;
-            return;
+            break;
         }
         const uint32_t item = tile * kTile + threadIdx.x;
 
         // First sighting?  The table holds the pending mark of the smallest
         // position that named the vertex.
-        uint32_t slot = 0xFFFFFFFFu, id = 0;
+        uint32_t slot = 0xFFFFFFFFu, id = 0, cur32 = 0;
         bool first = false;
         if (item < count) {
             slot = (stage == 0) ? p.slot_of_seed[item] : p.slot_of_edge[si.n_edges + item];
             if (slot != 0xFFFFFFFFu) {
                 const uint64_t cur = __ldcg((const unsigned long long *)&p.table.slots[slot]);
-                first = ((uint32_t)cur == enc_pending(gen, stage, item));
+                cur32 = (uint32_t)cur;
+                first = (cur32 == enc_pending(gen, stage, item));
                 id = (uint32_t)(cur >> 32);
             }
         }
@@ -494,7 +572,7 @@ k_assign(const SampleParams *__restrict__ pa, uint32_t stage, uint32_t k) {
                     bs->stage[stage + 1] = nx;
                     bs->nodes_per_stage[stage] = tot.flags;
                     if (p.hub_count) *p.hub_count = 0;  // the hop's hub queue starts empty
-                    if (stage == 0) bs->stage[0] = si;  // what finalize measures the draws against
+                    if (stage == 0) bs->stage[0] = si;  // what the counts measure the draws against
                 }
             }
         }
@@ -508,9 +586,14 @@ k_assign(const SampleParams *__restrict__ pa, uint32_t stage, uint32_t k) {
                 (has_next && (uint64_t)excl.flags >= p.frontier_cap)) {
                 atomicOr(&bs->error, kErrCapacity);
                 if (has_next && (uint64_t)excl.flags < p.frontier_cap) p.frontier[excl.flags] = FrontierEntry{};
+                // the batch has failed; its other items must still not wait for this vertex
+                p.table.slots[slot] = ((uint64_t)id << 32) | enc_final(gen, local & kPosMask);
+                write_item_local(p, stage, si.n_edges, item, 0xFFFFFFFFu);
             } else {
                 p.nodes[local] = id;
+                if (p.n_id) p.n_id[local] = (int64_t)id;
                 p.table.slots[slot] = ((uint64_t)id << 32) | enc_final(gen, local);  // readers accept either form
+                write_item_local(p, stage, si.n_edges, item, local);
                 if (has_next) {
                     FrontierEntry fe;
                     fe.off = off;
@@ -522,8 +605,25 @@ k_assign(const SampleParams *__restrict__ pa, uint32_t stage, uint32_t k) {
                     p.frontier[excl.flags] = fe;
                 }
             }
+        } else if (item < count) {
+            if (slot == 0xFFFFFFFFu) write_item_local(p, stage, si.n_edges, item, 0xFFFFFFFFu);
+            else if (!(cur32 & kPendingBit)) write_item_local(p, stage, si.n_edges, item, cur32 & kPosMask);  // registered by an earlier stage
+            else { wait_slot = slot; wait_item = item; }  // registered by an earlier item of this stage
         }
     }
+
+    if (has_next) return;
+    // Last stage: the block that finishes last publishes the batch's counts (every
+    // error bit any block raised is in by then) and leaves the state ready for the
+    // handle's next batch.
+    __shared__ bool s_last;
+    if (threadIdx.x == 0) {
+        __threadfence();
+        s_last = atomicAdd(&bs->done_blocks, 1u) == gridDim.x - 1;
+    }
+    __syncthreads();
+    if (!s_last || threadIdx.x != 0) return;
+    publish_counts(p, bs);
 }
 
 // Hop `hop`: expand the frontier stage `hop` queued (stage[hop + 1] holds its
@@ -579,54 +679,6 @@ k_pick_hubs(const SampleParams *__restrict__ pa, uint32_t hop, uint32_t k) {
             if ((uint32_t)lane < k) emit_edge(p, hop, nx.n_edges, fe, lane, fe.off + best_pos);
         }
         __syncthreads();
-    }
-}
-
-// --------------------------------------------------------------- finalize --
-__global__ void k_finalize(const SampleParams *__restrict__ pa) {
-    chain_sync();
-    const SampleParams &p = pa[blockIdx.y];
-    BatchState *bs = p.state;
-    const StageInfo fin = bs->stage[p.num_hops + 1];
-    const uint32_t n_nodes = min((uint64_t)fin.n_nodes, p.cap_nodes);
-    const uint32_t n_edges = min((uint64_t)fin.n_edges, p.cap_edges);
-    const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
-    for (uint64_t e = tid; e < n_edges; e += stride) {
-        const uint32_t slot = p.slot_of_edge[e];
-        const uint32_t dl = (slot == 0xFFFFFFFFu) ? 0xFFFFFFFFu
-                          : ((uint32_t)__ldcg((const unsigned long long *)&p.table.slots[slot]) & kPosMask);
-        p.dst_local[e] = dl;
-        if (p.edge_index_local) {
-            p.edge_index_local[e] = (int64_t)dl;                                   // row 0: sampled neighbor
-            p.edge_index_local[(uint64_t)n_edges + e] = (int64_t)p.src_local[e];   // row 1: expanded node
-        }
-        if (p.e_id && p.edge_ids) p.e_id[e] = (int64_t)p.edge_ids[e];
-    }
-    for (uint64_t i = tid; i < p.n_seeds; i += stride) {
-        const uint32_t slot = p.slot_of_seed[i];
-        const uint32_t sl = (slot == 0xFFFFFFFFu) ? 0xFFFFFFFFu
-                          : ((uint32_t)__ldcg((const unsigned long long *)&p.table.slots[slot]) & kPosMask);
-        p.seed_locals[i] = sl;
-        if (p.seed_index) p.seed_index[i] = (int64_t)sl;
-    }
-    if (p.n_id)
-        for (uint64_t i = tid; i < n_nodes; i += stride) p.n_id[i] = (int64_t)p.nodes[i];
-    if (tid == 0) {
-        ag_sample_counts c{};
-        c.num_nodes = n_nodes;
-        c.num_edges = n_edges;
-        c.num_seeds = p.n_seeds;
-        c.num_hops = p.num_hops;
-        for (uint32_t s = 0; s <= p.num_hops; ++s) c.nodes_per_hop[s] = bs->nodes_per_stage[s];
-        for (uint32_t h = 0; h < p.num_hops; ++h) c.edges_per_hop[h] = bs->stage[h + 1].hop_edges;
-        c.draws = fin.draws - bs->stage[0].draws;
-        c.error = bs->error;
-        if ((uint64_t)fin.n_nodes > p.cap_nodes || (uint64_t)fin.n_edges > p.cap_edges) c.error |= kErrCapacity;
-        *p.counts = c;
-        bs->stream_pos = fin.draws;  // a bare sampler keeps consuming the same stream
-        bs->error = 0;               // ready for the handle's next batch
-        bs->ticket = 0;
     }
 }
 
@@ -721,6 +773,20 @@ struct ag_sampler {
     cudaStream_t gstream = nullptr;
     cudaEvent_t sampled = nullptr;
     SortScratch sort;  // sharded feature stores: the chain's row ids in address order (gather.cu)
+    // The arguments of the chain in flight, kept so that it can be launched once more:
+    // the dedup tables are sized from the node counts of earlier chains (small tables stay
+    // in L2), and a batch that outgrows its table is sampled again with the full-size one.
+    struct Launch {
+        uint32_t n_batches = 0;
+        std::vector<const uint32_t *> seeds;
+        std::vector<uint64_t> n_seeds, batch_seeds;
+        bool has_batch_seeds = false;
+        int32_t seeds_mem = AG_MEM_HOST;
+        const ag_features *feats = nullptr;
+        std::vector<ag_subgraph_buffers> bufs;
+        cudaStream_t stream = nullptr;
+        bool reduced_table = false;
+    } last;
     // Grid-size estimates from the last group's real counts (the bounds before
     // the first one); kernels stride past an estimate that turns out too small.
     uint64_t est_nodes = 0;
@@ -915,6 +981,10 @@ extern "C" int32_t ag_sampler_bounds(const ag_sampler *s, uint64_t n_seeds, uint
 // seeds[b] / n_seeds[b] / bufs[b] and, when batch_seeds != NULL, restarts its
 // RNG stream at draw 0 of batch_seeds[b]; with batch_seeds == NULL the handle's
 // own stream continues (only meaningful for a single batch).
+namespace {
+int32_t launch_saved(ag_sampler *s, bool relaunch);
+}  // namespace
+
 extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const uint32_t *const *seeds,
                                         const uint64_t *n_seeds, int32_t seeds_mem, const uint64_t *batch_seeds,
                                         const ag_features *feats, ag_subgraph_buffers *bufs, void *stream) {
@@ -947,8 +1017,40 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
         return fail(AG_ERR_VALUE, "feature store lives on device %d, sampler on %d", feats->device, s->device);
     DeviceGuard guard(s->device);
     if (!guard.ok) return AG_ERR_CUDA;
-    cudaStream_t st = (cudaStream_t)stream;
     if (s->in_flight) { AG_CUDA(cudaEventSynchronize(s->done)); s->in_flight = false; account_stream(s); }
+    ag_sampler::Launch &L = s->last;
+    L.n_batches = n_batches;
+    L.seeds.assign(seeds, seeds + n_batches);
+    L.n_seeds.assign(n_seeds, n_seeds + n_batches);
+    L.has_batch_seeds = batch_seeds != nullptr;
+    if (batch_seeds) L.batch_seeds.assign(batch_seeds, batch_seeds + n_batches);
+    L.seeds_mem = seeds_mem;
+    L.feats = feats;
+    L.bufs.assign(bufs, bufs + n_batches);
+    L.stream = (cudaStream_t)stream;
+    return launch_saved(s, false);
+}
+
+namespace {
+// Queues the chain described by s->last.  relaunch: the same chain once more with
+// full-size dedup tables (host seeds are already in the handle's device copy).
+int32_t launch_saved(ag_sampler *s, bool relaunch) {
+    const ag_sampler::Launch &L = s->last;
+    const uint32_t n_batches = L.n_batches;
+    const uint32_t *const *seeds = L.seeds.data();
+    const uint64_t *n_seeds = L.n_seeds.data();
+    const uint64_t *batch_seeds = L.has_batch_seeds ? L.batch_seeds.data() : nullptr;
+    const int32_t seeds_mem = L.seeds_mem;
+    const ag_features *feats = L.feats;
+    const ag_subgraph_buffers *bufs = L.bufs.data();
+    const ag_graph *g = s->g;
+    uint64_t max_n = 0;
+    bool want_x = false;
+    for (uint32_t b = 0; b < n_batches; ++b) {
+        max_n = std::max(max_n, n_seeds[b]);
+        want_x = want_x || (feats && bufs[b].x);
+    }
+    cudaStream_t st = L.stream;
     AG_TRY(ensure_scratch(s, max_n));
     if (s->profile) AG_CUDA(cudaEventRecord(s->ev[0], st));
     if (s->dirty || s->gen >= kGens) {
@@ -967,12 +1069,16 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
         AG_CUDA(cudaMemsetAsync(s->tiles, 0, (uint64_t)s->group * s->n_tiles * sizeof(TileDesc), st));
         s->epoch = 0;
     }
+    // Tables sized for twice the nodes the last chains really produced (with headroom)
+    // instead of the worst-case bound: a chain's tables then fit in L2.
+    uint64_t used_cap = s->table_cap;
+    if (!relaunch && s->est_nodes) used_cap = std::min(s->table_cap, std::max<uint64_t>(1024, next_pow2(2 * s->est_nodes)));
+    s->last.reduced_table = used_cap < s->table_cap;
     uint32_t log2cap = 0;
-    while ((1ull << log2cap) < s->table_cap) ++log2cap;
-    const uint64_t used_cap = s->table_cap;
+    while ((1ull << log2cap) < used_cap) ++log2cap;
     const uint64_t ecap = std::max<uint64_t>(s->max_edges, 1);
 
-    uint64_t b_nodes = 0, b_edges = 0;
+    uint64_t b_nodes = 0;
     for (uint32_t b = 0; b < n_batches; ++b) {
         const ag_subgraph_buffers &B = bufs[b];
         const uint32_t n = (uint32_t)n_seeds[b];
@@ -985,7 +1091,7 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
         p.epoch_base = s->epoch + 1;
         p.n_seeds = n;
         if (seeds_mem == AG_MEM_HOST) {
-            if (n) memcpy(s->seeds_pinned + (uint64_t)b * s->cap_seeds, seeds[b], (size_t)n * 4);
+            if (n && !relaunch) memcpy(s->seeds_pinned + (uint64_t)b * s->cap_seeds, seeds[b], (size_t)n * 4);
             p.seeds = s->seeds_dev + (uint64_t)b * s->cap_seeds;
         } else {
             p.seeds = seeds[b];
@@ -1011,7 +1117,7 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
         s->params_host[b] = p;
         uint64_t bn, be;
         compute_bounds(s, n, &bn, &be, nullptr);
-        b_nodes = std::max(b_nodes, bn); b_edges = std::max(b_edges, be);
+        b_nodes = std::max(b_nodes, bn);
         if (want_x) {
             GatherArgs ga{};
             if (feats && B.x) {
@@ -1028,7 +1134,7 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
     s->pending_pos = (batch_seeds == nullptr);  // a continuing batch advances the handle's stream
     s->epoch += H + 2;
     s->gen += 1;
-    if (seeds_mem == AG_MEM_HOST)
+    if (seeds_mem == AG_MEM_HOST && !relaunch)
         AG_CUDA(cudaMemcpyAsync(s->seeds_dev, s->seeds_pinned, (uint64_t)n_batches * s->cap_seeds * 4, cudaMemcpyHostToDevice, st));
     AG_CUDA(cudaMemcpyAsync(s->params_dev, s->params_host, n_batches * sizeof(SampleParams), cudaMemcpyHostToDevice, st));
     if (want_x)
@@ -1056,15 +1162,6 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
             launch_pick(s->mode, k, std::min<uint64_t>(expect, g->num_nodes), n_batches, st, pa, stage);
         }
         items = std::min<uint64_t>(items, g->num_nodes) * k;
-    }
-    {
-        uint64_t est_edges = 0;
-        for (uint32_t h = 1; h <= H; ++h) est_edges += s->est_items[h];
-        const uint64_t bound = std::max<uint64_t>(std::max(b_edges, b_nodes), std::max<uint64_t>(nmax, 1));
-        const uint64_t work = est_edges ? std::min(bound, std::max<uint64_t>(est_edges, nmax)) : bound;
-        // one edge per thread where the GPU can hold them: every table lookup in flight at once
-        const uint32_t fx = (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>((work + 255) / 256, std::max<uint64_t>((uint64_t)kSMs * 16 / n_batches, 1)));
-        launch_chained(k_finalize, dim3(fx, n_batches), dim3(256), st, pa);
     }
     AG_CUDA(cudaGetLastError());
     if (s->profile) AG_CUDA(cudaEventRecord(s->ev[1], st));
@@ -1099,6 +1196,7 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
     s->in_flight_n = n_batches;
     return AG_OK;
 }
+}  // namespace
 
 // Waits for the group queued last; counts[b] receives batch b's counts.  Returns
 // the first batch error (the other batches' counts are still valid).
@@ -1107,8 +1205,20 @@ extern "C" int32_t ag_sample_group_wait(ag_sampler *s, ag_sample_counts *counts,
     if (!s->in_flight) return fail(AG_ERR_VALUE, "ag_sample_wait: no batch in flight");
     DeviceGuard guard(s->device);
     if (!guard.ok) return AG_ERR_CUDA;
-    const cudaError_t e = cudaEventSynchronize(s->done);
+    cudaError_t e = cudaEventSynchronize(s->done);
     s->in_flight = false;
+    if (e == cudaSuccess && s->last.reduced_table) {
+        bool full = false;
+        for (uint32_t b = 0; b < s->in_flight_n; ++b) full = full || (s->counts_host[b].error & kErrTableFull);
+        if (full) {
+            // A batch outgrew the table its chain was given: once more, with the full-size tables.
+            s->dirty = true;
+            s->est_nodes = 0;
+            AG_TRY(launch_saved(s, true));
+            e = cudaEventSynchronize(s->done);
+            s->in_flight = false;
+        }
+    }
     if (e != cudaSuccess) {
         s->dirty = true;
         s->pending_pos = false;

@@ -21,7 +21,7 @@ struct __align__(16) FrontierEntry {
 // registration, stage h + 1 the edges of hop h.  A stage's kernel only reads
 // stage[s] and only the last tile writes stage[s + 1], so nothing is read and
 // written concurrently.
-struct StageInfo {
+struct __align__(16) StageInfo {
     uint32_t n_nodes;     // nodes registered before this stage
     uint32_t n_edges;     // edges emitted before this stage
     uint32_t frontier_n;  // vertices this stage discovered (expanded by the next)
@@ -56,6 +56,8 @@ struct BatchState {
     uint32_t error;
     uint32_t ticket;
     uint64_t stream_pos;  // draws consumed by earlier batches of this handle
+    uint32_t done_blocks; // blocks of the last stage's kernel that have finished
+    uint32_t pad;
 };
 
 // ------------------------------------------------------------ dedup table --

@@ -863,7 +863,8 @@ def cpu_baseline(g, feats, w, cfg, seconds: float = 10.0, ref_kernel: bool = Tru
     bs = w["batch"]
     # bounded sample: batches 0, 1, ... of the workload's seed stream, grown until
     # the timed run lasts about ten seconds
-    seeds_host = [synth.seed_batch(w["nodes"], bs, SEEDS_SEED, b) for b in range(4 * threads)]
+    # (weighted picks draw a key per neighbour of every frontier row: start small)
+    seeds_host = [synth.seed_batch(w["nodes"], bs, SEEDS_SEED, b) for b in range(threads if w["weighted"] else 4 * threads)]
     nb, cap = len(seeds_host), 1 << 16
     while True:
         seeds = np.concatenate(seeds_host[:nb])
@@ -873,7 +874,7 @@ def cpu_baseline(g, feats, w, cfg, seconds: float = 10.0, ref_kernel: bool = Tru
         nb = min(cap, max(nb + 1, int(nb * min(16.0, 1.2 * seconds / max(r["seconds"], 1e-3)))))
         seeds_host += [synth.seed_batch(w["nodes"], bs, SEEDS_SEED, b) for b in range(len(seeds_host), nb)]
     # one thread, one persistent sampler reused across batches (the reference's NeighborSampler reuse)
-    n1 = max(4, min(nb, int(0.4 * seconds * nb / max(r["seconds"], 1e-3) / threads)))
+    n1 = max(2, min(nb, int(0.4 * seconds * nb / max(r["seconds"], 1e-3) / threads)))
     r1 = s.bench(payload, w["dim"], w["dtype"], np.concatenate(seeds_host[:n1]), bs, 0, 1)
     cpu = {"value": r["edges"] / r["seconds"], "unit": "edges/s", "cores": threads, "kind": "port",
            "gather_gbs": r["nodes"] * gather_bytes_per_row(w) / r["seconds"] / 1e9,
