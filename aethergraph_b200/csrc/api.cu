@@ -500,8 +500,8 @@ ag_features *new_features(int device, uint64_t n, uint64_t begin, uint64_t rows,
 int32_t alloc_features(ag_features *f, bool alloc_payload) {
     if (alloc_payload)
         AG_CUDA(cudaMalloc(&f->payload, std::max<uint64_t>(f->rows * f->dim * elem_size(f->dtype), 16)));
-    AG_CUDA(cudaMalloc(&f->err, 4));
-    AG_CUDA(cudaMemset(f->err, 0, 4));
+    AG_CUDA(cudaMalloc(&f->err, 32));  // error bits, then the gather counters (internal.h)
+    AG_CUDA(cudaMemset(f->err, 0, 32));
     return AG_OK;
 }
 
@@ -769,6 +769,17 @@ extern "C" int32_t ag_gather(const ag_features *f, const void *ids_dev, int32_t 
         return AG_OK;
     }
     AG_CUDA(launch_gather(a, f->dtype, (cudaStream_t)stream));
+    return AG_OK;
+}
+
+extern "C" int32_t ag_features_gather_stats(const ag_features *f, uint64_t *rows_requested, uint64_t *rows_fetched) {
+    if (!f) return fail(AG_ERR_VALUE, "ag_features_gather_stats: null store");
+    DeviceGuard guard(f->device);
+    if (!guard.ok) return AG_ERR_CUDA;
+    uint64_t h[2] = {0, 0};
+    AG_CUDA(cudaMemcpy(h, (const uint8_t *)f->err + 8, 16, cudaMemcpyDeviceToHost));
+    if (rows_requested) *rows_requested = h[0];
+    if (rows_fetched) *rows_fetched = h[1];
     return AG_OK;
 }
 

@@ -314,8 +314,9 @@ template <int DTYPE, int LPR>
 __global__ void __launch_bounds__(kThreads)
 k_gather_sorted(GatherArgs one, const GatherArgs *__restrict__ group, const ag_shard_table *__restrict__ t,
                 const uint32_t *__restrict__ keys, const uint32_t *__restrict__ vals, uint64_t n_items,
-                uint32_t sentinel, uint32_t row_bytes, uint32_t dim) {
+                uint32_t sentinel, uint32_t row_bytes, uint32_t dim, unsigned long long *__restrict__ counters) {
     constexpr int kRowsPerBlock = kThreads / LPR;
+    uint32_t asked = 0, loaded = 0;  // counted by lane 0 of each row group
     constexpr uint64_t kChunk = (uint64_t)kRowsPerBlock * kInFlight;
     const int lane = threadIdx.x % LPR;
     const int sub = threadIdx.x / LPR;
@@ -340,6 +341,7 @@ k_gather_sorted(GatherArgs one, const GatherArgs *__restrict__ group, const ag_s
                     key[u] = keys[i];
                     // the first of a run of equal keys fetches the row for the whole run
                     head[u] = key[u] != sentinel && (i == 0 || keys[i - 1] != key[u]);
+                    if (lane == 0 && v0 == 0) { asked += key[u] != sentinel; loaded += head[u]; }
                     if (head[u]) {
                         const uint32_t owner = key[u] % W;
                         const uint64_t local = key[u] / W;
@@ -360,17 +362,18 @@ k_gather_sorted(GatherArgs one, const GatherArgs *__restrict__ group, const ag_s
             }
         }
     }
+    if (asked) { atomicAdd(counters, (unsigned long long)asked); atomicAdd(counters + 1, (unsigned long long)loaded); }
 }
 
 template <int DTYPE>
 cudaError_t launch_sorted(const GatherArgs &one, const GatherArgs *group, const ag_shard_table *t, const uint32_t *keys,
                           const uint32_t *vals, uint64_t n_items, uint32_t sentinel, uint32_t row_bytes, uint32_t dim,
-                          int blocks, cudaStream_t st) {
+                          int blocks, unsigned long long *counters, cudaStream_t st) {
     const uint32_t vecs = row_bytes >> 4;
-    if (vecs <= 4) k_gather_sorted<DTYPE, 4><<<blocks, kThreads, 0, st>>>(one, group, t, keys, vals, n_items, sentinel, row_bytes, dim);
-    else if (vecs <= 8) k_gather_sorted<DTYPE, 8><<<blocks, kThreads, 0, st>>>(one, group, t, keys, vals, n_items, sentinel, row_bytes, dim);
-    else if (vecs <= 16) k_gather_sorted<DTYPE, 16><<<blocks, kThreads, 0, st>>>(one, group, t, keys, vals, n_items, sentinel, row_bytes, dim);
-    else k_gather_sorted<DTYPE, 32><<<blocks, kThreads, 0, st>>>(one, group, t, keys, vals, n_items, sentinel, row_bytes, dim);
+    if (vecs <= 4) k_gather_sorted<DTYPE, 4><<<blocks, kThreads, 0, st>>>(one, group, t, keys, vals, n_items, sentinel, row_bytes, dim, counters);
+    else if (vecs <= 8) k_gather_sorted<DTYPE, 8><<<blocks, kThreads, 0, st>>>(one, group, t, keys, vals, n_items, sentinel, row_bytes, dim, counters);
+    else if (vecs <= 16) k_gather_sorted<DTYPE, 16><<<blocks, kThreads, 0, st>>>(one, group, t, keys, vals, n_items, sentinel, row_bytes, dim, counters);
+    else k_gather_sorted<DTYPE, 32><<<blocks, kThreads, 0, st>>>(one, group, t, keys, vals, n_items, sentinel, row_bytes, dim, counters);
     return cudaGetLastError();
 }
 
@@ -484,12 +487,14 @@ bool sorted_gather_applies(const ag_features *f, uint32_t row_bytes, bool aligne
     return f->shard_rows * f->n_shards < 0xFFFFFFFFull;
 }
 
-// Gathers rows [0, min(n_b, rows_cap)) of every batch in address order, then rows
-// [rows_cap, n_b) — only present when a batch outgrew the caller's estimate — with
-// the unsorted kernel.  `one` / `group_dev` as in launch_gather / launch_gather_group.
-cudaError_t launch_gather_sorted(const GatherArgs &one, const GatherArgs *group_dev, uint32_t n_batches, uint64_t rows_cap,
-                                 uint32_t row_bytes, uint32_t dim, int dtype, const ag_features *f, SortScratch &sc,
-                                 cudaStream_t st) {
+// The address-ordered gather in two steps, so that a caller can put them on different
+// streams (small latency-bound kernels first, the bandwidth-bound fetch behind an event).
+// Step 1: keys of rows [0, min(n_b, rows_cap)) of every batch, sorted with their output
+// positions.  Step 2: fetch in that order, then rows [rows_cap, n_b) — only present when a
+// batch outgrew the caller's estimate — with the unsorted kernel.  `one` / `group_dev` as
+// in launch_gather / launch_gather_group.
+cudaError_t launch_sort_keys(const GatherArgs &one, const GatherArgs *group_dev, uint32_t n_batches, uint64_t rows_cap,
+                             const ag_features *f, SortScratch &sc, cudaStream_t st) {
     if (n_batches == 0 || rows_cap == 0) return cudaSuccess;
     rows_cap = std::min<uint64_t>(rows_cap, (1ull << kValRowBits) - 1);
     const uint64_t n_items = (uint64_t)n_batches * rows_cap;
@@ -502,14 +507,25 @@ cudaError_t launch_gather_sorted(const GatherArgs &one, const GatherArgs *group_
     k_make_keys<<<dim3(kb, n_batches), 256, 0, st>>>(one, group_dev, (uint32_t)rows_cap, sentinel, sc.keys[0], sc.vals[0]);
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
     size_t tb = sc.temp_bytes;
-    e = cub::DeviceRadixSort::SortPairs(sc.temp, tb, (const uint32_t *)sc.keys[0], sc.keys[1], (const uint32_t *)sc.vals[0],
-                                        sc.vals[1], n_items, 0, (int)bits, st);
-    if (e != cudaSuccess) return e;
+    return cub::DeviceRadixSort::SortPairs(sc.temp, tb, (const uint32_t *)sc.keys[0], sc.keys[1], (const uint32_t *)sc.vals[0],
+                                           sc.vals[1], n_items, 0, (int)bits, st);
+}
+
+cudaError_t launch_sorted_fetch(const GatherArgs &one, const GatherArgs *group_dev, uint32_t n_batches, uint64_t rows_cap,
+                                uint32_t row_bytes, uint32_t dim, int dtype, const ag_features *f, SortScratch &sc,
+                                cudaStream_t st) {
+    if (n_batches == 0 || rows_cap == 0) return cudaSuccess;
+    rows_cap = std::min<uint64_t>(rows_cap, (1ull << kValRowBits) - 1);
+    const uint64_t n_items = (uint64_t)n_batches * rows_cap;
+    const uint32_t bits = bit_width_u64(f->shard_rows * f->n_shards);
+    const uint32_t sentinel = bits >= 32 ? 0xFFFFFFFFu : ((1u << bits) - 1u);
     const int blocks = gather_grid_blocks(n_items, row_bytes);
+    unsigned long long *counters = (unsigned long long *)((uint8_t *)f->err + 8);
+    cudaError_t e;
     switch (dtype) {
-        case AG_F32: e = launch_sorted<AG_F32>(one, group_dev, f->shards, sc.keys[1], sc.vals[1], n_items, sentinel, row_bytes, dim, blocks, st); break;
-        case AG_F16: e = launch_sorted<AG_F16>(one, group_dev, f->shards, sc.keys[1], sc.vals[1], n_items, sentinel, row_bytes, dim, blocks, st); break;
-        default: e = launch_sorted<AG_BF16>(one, group_dev, f->shards, sc.keys[1], sc.vals[1], n_items, sentinel, row_bytes, dim, blocks, st); break;
+        case AG_F32: e = launch_sorted<AG_F32>(one, group_dev, f->shards, sc.keys[1], sc.vals[1], n_items, sentinel, row_bytes, dim, blocks, counters, st); break;
+        case AG_F16: e = launch_sorted<AG_F16>(one, group_dev, f->shards, sc.keys[1], sc.vals[1], n_items, sentinel, row_bytes, dim, blocks, counters, st); break;
+        default: e = launch_sorted<AG_BF16>(one, group_dev, f->shards, sc.keys[1], sc.vals[1], n_items, sentinel, row_bytes, dim, blocks, counters, st); break;
     }
     if (e != cudaSuccess) return e;
     // Rows past the estimate (rare): a few blocks per batch, which stride; most exit at once.
@@ -519,6 +535,14 @@ cudaError_t launch_gather_sorted(const GatherArgs &one, const GatherArgs *group_
         case AG_F16: return launch_vec<AG_F16>(one, group_dev, row_bytes, grid, true, st, rows_cap);
         default: return launch_vec<AG_BF16>(one, group_dev, row_bytes, grid, true, st, rows_cap);
     }
+}
+
+cudaError_t launch_gather_sorted(const GatherArgs &one, const GatherArgs *group_dev, uint32_t n_batches, uint64_t rows_cap,
+                                 uint32_t row_bytes, uint32_t dim, int dtype, const ag_features *f, SortScratch &sc,
+                                 cudaStream_t st) {
+    const cudaError_t e = launch_sort_keys(one, group_dev, n_batches, rows_cap, f, sc, st);
+    if (e != cudaSuccess) return e;
+    return launch_sorted_fetch(one, group_dev, n_batches, rows_cap, row_bytes, dim, dtype, f, sc, st);
 }
 
 cudaError_t launch_encode(const float *src, void *dst, uint64_t count, int dtype, cudaStream_t st) {

@@ -203,7 +203,8 @@ void worker_main(ag_hetero_loader *l, uint32_t idx) {
             l->cv_work.wait(lk, [&] { return l->stop || !l->queue.empty(); });
             if (l->stop) return;
             const size_t share = std::max<size_t>(1, (l->queue.size() + l->threads - 1) / l->threads);
-            size_t take = std::min<size_t>(G, share);
+            // a full group whenever one is queued: launch floors are paid per chain
+            size_t take = l->queue.size() >= G ? G : std::min<size_t>(G, share);
             // Until a batch has been seen, x is reserved at the worst-case bound: one batch per chain.
             if (l->has_feats && !l->x_seen.load()) take = 1;
             while (ws.size() < take && !l->queue.empty()) {

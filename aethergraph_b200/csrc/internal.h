@@ -40,7 +40,8 @@ struct ag_features {
     uint64_t dim = 0;
     int dtype = AG_F32;
     uint8_t *payload = nullptr;  // device, rows * dim * elem_size
-    uint32_t *err = nullptr;     // device, sticky error bits
+    uint32_t *err = nullptr;     // device, 32 bytes: sticky error bits; at +8 / +16 two u64 counters of the
+                                 // address-ordered gather (rows asked for, rows actually loaded)
     bool owns_payload = true;
     // A sharded view (ag_features_open_sharded / ag_features_view_sharded): rows
     // [r * shard_rows, (r + 1) * shard_rows) live in shard r's memory, this GPU's
@@ -99,6 +100,11 @@ cudaError_t launch_gather_group(const GatherArgs *group_dev, uint32_t n_batches,
                                 cudaStream_t st);
 // Address-ordered gather over a sharded view (see gather.cu).
 bool sorted_gather_applies(const ag_features *f, uint32_t row_bytes, bool aligned);
+cudaError_t launch_sort_keys(const GatherArgs &one, const GatherArgs *group_dev, uint32_t n_batches, uint64_t rows_cap,
+                             const ag_features *f, SortScratch &sc, cudaStream_t st);
+cudaError_t launch_sorted_fetch(const GatherArgs &one, const GatherArgs *group_dev, uint32_t n_batches, uint64_t rows_cap,
+                                uint32_t row_bytes, uint32_t dim, int dtype, const ag_features *f, SortScratch &sc,
+                                cudaStream_t st);
 cudaError_t launch_gather_sorted(const GatherArgs &one, const GatherArgs *group_dev, uint32_t n_batches, uint64_t rows_cap,
                                  uint32_t row_bytes, uint32_t dim, int dtype, const ag_features *f, SortScratch &sc,
                                  cudaStream_t st);

@@ -192,7 +192,8 @@ void worker_main(ag_loader *l, uint32_t idx) {
             // while a shallow one is still spread over the workers.  A group is
             // homogeneous in where its seeds live.
             const size_t share = std::max<size_t>(1, (l->queue.size() + l->threads - 1) / l->threads);
-            const size_t take = std::min<size_t>(G, share);
+            // a full group whenever one is queued: launch floors are paid per chain
+            const size_t take = l->queue.size() >= G ? G : std::min<size_t>(G, share);
             const bool dev_seeds = l->queue.front().seeds_dev != nullptr;
             while (ws.size() < take && !l->queue.empty() && (l->queue.front().seeds_dev != nullptr) == dev_seeds) {
                 ws.push_back(std::move(l->queue.front()));

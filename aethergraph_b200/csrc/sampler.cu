@@ -54,7 +54,9 @@ namespace ag {
 
 namespace {
 
-constexpr int kTile = 512;      // items per tile = threads per block of the assign kernel
+constexpr int kTile = 512;      // threads per block of the assign kernel
+constexpr int kIPT = 4;         // items per thread
+constexpr int kTileItems = kTile * kIPT;  // items per tile of the single-pass scan
 constexpr int kPickThreads = 256;
 constexpr int kLargeK = 1024;   // largest fanout the k > 32 path keeps in shared memory
 
@@ -442,7 +444,7 @@ __device__ __forceinline__ void write_item_local(const SampleParams &p, uint32_t
 }
 
 // Called by one thread once every block of the batch's last kernel has finished.
-__device__ __noinline__ void publish_counts(const SampleParams &p, BatchState *bs) {
+__device__ __forceinline__ void publish_counts(const SampleParams &p, BatchState *bs) {
     __threadfence();
     const StageInfo fin = load_stage_cg(&bs->stage[p.num_hops + 1]);
     ag_sample_counts c{};
@@ -463,9 +465,9 @@ __device__ __noinline__ void publish_counts(const SampleParams &p, BatchState *b
 }
 
 template <bool HAS_NEXT>
-__global__ void __launch_bounds__(kTile, HAS_NEXT ? 2 : 3)
+__global__ void __launch_bounds__(kTile, 2)
 k_assign(const SampleParams *__restrict__ pa, uint32_t stage, uint32_t k) {
-    constexpr bool has_next = HAS_NEXT;  // the last stage queues no frontier and needs fewer registers
+    constexpr bool has_next = HAS_NEXT;  // the last stage queues no frontier
     chain_sync();
     __shared__ uint32_t s_tile;
     __shared__ ScanVal s_warp[kTile / 32];
@@ -481,10 +483,11 @@ k_assign(const SampleParams *__restrict__ pa, uint32_t stage, uint32_t k) {
         si.draws = p.start_draw;
     }
     const uint32_t count = (stage == 0) ? p.n_seeds : si.hop_edges;
-    const uint32_t n_tiles = max(1u, (count + kTile - 1) / kTile);
+    const uint32_t n_tiles = max(1u, (count + kTileItems - 1) / kTileItems);
     const uint32_t edges_before_next = si.n_edges + ((stage == 0) ? 0u : count);  // where hop `stage` starts
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t gen = p.table.gen;
+    const uint32_t *slots_in = (stage == 0) ? p.slot_of_seed : p.slot_of_edge + si.n_edges;
 
     if (!has_next && p.edge_index_local) {
         // Last stage: every edge of the batch exists, so the row offset of the int64
@@ -494,26 +497,13 @@ k_assign(const SampleParams *__restrict__ pa, uint32_t stage, uint32_t k) {
             p.edge_index_local[total + e] = (int64_t)p.src_local[e];
     }
 
-    uint32_t wait_slot = 0xFFFFFFFFu, wait_item = 0;  // an item of the previous tile whose vertex is still pending
-
     // The grid is sized for a typical batch, not for the worst case: a block
     // keeps drawing tile tickets until they run out.  Tickets are handed out in
     // order, so the tiles a look-back (or a pending vertex) waits for are always
-    // already running.
+    // already running.  A thread owns kIPT consecutive items of its tile, so that
+    // many table probes (and row-bound loads) are in flight per thread, and the
+    // barriers, the ticket and the look-back are paid once per kTile * kIPT items.
     for (;;) {
-        __syncthreads();
-        if (wait_slot != 0xFFFFFFFFu) {
-            // The first sighting is an earlier item of this stage: in this block's last tile
-            // (stored before the barrier above) or in a tile with a smaller ticket.
-            uint32_t v = (uint32_t)__ldcg((const unsigned long long *)&p.table.slots[wait_slot]), spins = 0;
-            while (v & kPendingBit) {
-                if (++spins > kSpinLimit) { atomicOr(&bs->error, kErrSpinTimeout); break; }
-                __nanosleep(40);
-                v = (uint32_t)__ldcg((const unsigned long long *)&p.table.slots[wait_slot]);
-            }
-            write_item_local(p, stage, si.n_edges, wait_item, (v & kPendingBit) ? 0xFFFFFFFFu : (v & kPosMask));
-            wait_slot = 0xFFFFFFFFu;
-        }
         if (threadIdx.x == 0) s_tile = atomicAdd(&bs->ticket, 1u);
         __syncthreads();
         const uint32_t tile = s_tile;
@@ -522,31 +512,46 @@ k_assign(const SampleParams *__restrict__ pa, uint32_t stage, uint32_t k) {
             if (threadIdx.x == 0 && tile == n_tiles + gridDim.x - 1) bs->ticket = 0;
             break;
         }
-        const uint32_t item = tile * kTile + threadIdx.x;
+        const uint32_t item0 = tile * kTileItems + threadIdx.x * kIPT;
 
         // First sighting?  The table holds the pending mark of the smallest
         // position that named the vertex.
-        uint32_t slot = 0xFFFFFFFFu, id = 0, cur32 = 0;
-        bool first = false;
-        if (item < count) {
-            slot = (stage == 0) ? p.slot_of_seed[item] : p.slot_of_edge[si.n_edges + item];
-            if (slot != 0xFFFFFFFFu) {
-                const uint64_t cur = __ldcg((const unsigned long long *)&p.table.slots[slot]);
-                cur32 = (uint32_t)cur;
-                first = (cur32 == enc_pending(gen, stage, item));
-                id = (uint32_t)(cur >> 32);
+        uint32_t slot[kIPT], id[kIPT], cur32[kIPT];
+        bool first[kIPT];
+#pragma unroll
+        for (int j = 0; j < kIPT; ++j) slot[j] = (item0 + j < count) ? slots_in[item0 + j] : 0xFFFFFFFFu;
+#pragma unroll
+        for (int j = 0; j < kIPT; ++j) {
+            id[j] = 0; cur32[j] = 0; first[j] = false;
+            if (slot[j] != 0xFFFFFFFFu) {
+                const uint64_t cur = __ldcg((const unsigned long long *)&p.table.slots[slot[j]]);
+                cur32[j] = (uint32_t)cur;
+                first[j] = (cur32[j] == enc_pending(gen, stage, item0 + j));
+                id[j] = (uint32_t)(cur >> 32);
             }
         }
-        ScanVal v{first ? 1u : 0u, 0u, 0ull};
-        uint64_t off = 0, deg = 0;
-        if (first && has_next) {
-            row_bounds(p.offsets, p.num_nodes, p.num_edges, id, off, deg);
-            if (deg > 0xFFFFFFFFull) { atomicOr(&bs->error, kErrCapacity); deg = 0; }
-            row_demand(p.mode, deg, k, v.take, v.draws);
+        ScanVal tv{0u, 0u, 0ull};  // this thread's items together
+        uint64_t off[kIPT];
+        uint32_t deg[kIPT];
+#pragma unroll
+        for (int j = 0; j < kIPT; ++j) {
+            off[j] = 0; deg[j] = 0;
+            if (first[j]) {
+                tv.flags += 1u;
+                if (has_next) {
+                    uint64_t d64;
+                    row_bounds(p.offsets, p.num_nodes, p.num_edges, id[j], off[j], d64);
+                    if (d64 > 0xFFFFFFFFull) { atomicOr(&bs->error, kErrCapacity); d64 = 0; }
+                    deg[j] = (uint32_t)d64;
+                    uint32_t take; uint64_t draws;
+                    row_demand(p.mode, d64, k, take, draws);
+                    tv.take += take; tv.draws += draws;
+                }
+            }
         }
 
-        // Block scan: warp scans, then the warp totals.
-        const ScanVal incl = warp_inclusive_scan(v, lane);
+        // Block scan of the threads' totals: warp scans, then the warp totals.
+        const ScanVal incl = warp_inclusive_scan(tv, lane);
         if (lane == 31) s_warp[warp] = incl;
         __syncthreads();
         if (warp == 0) {
@@ -577,38 +582,66 @@ k_assign(const SampleParams *__restrict__ pa, uint32_t stage, uint32_t k) {
             }
         }
         __syncthreads();
-        if (first) {
-            const ScanVal base = s_prefix + s_warp[warp];
-            const ScanVal excl = ScanVal{base.flags + incl.flags - v.flags, base.take + incl.take - v.take,
-                                         base.draws + incl.draws - v.draws};
-            const uint32_t local = si.n_nodes + excl.flags;
-            if ((uint64_t)local >= p.cap_nodes || (uint64_t)local >= kMaxPos ||
-                (has_next && (uint64_t)excl.flags >= p.frontier_cap)) {
-                atomicOr(&bs->error, kErrCapacity);
-                if (has_next && (uint64_t)excl.flags < p.frontier_cap) p.frontier[excl.flags] = FrontierEntry{};
-                // the batch has failed; its other items must still not wait for this vertex
-                p.table.slots[slot] = ((uint64_t)id << 32) | enc_final(gen, local & kPosMask);
-                write_item_local(p, stage, si.n_edges, item, 0xFFFFFFFFu);
-            } else {
-                p.nodes[local] = id;
-                if (p.n_id) p.n_id[local] = (int64_t)id;
-                p.table.slots[slot] = ((uint64_t)id << 32) | enc_final(gen, local);  // readers accept either form
-                write_item_local(p, stage, si.n_edges, item, local);
-                if (has_next) {
-                    FrontierEntry fe;
-                    fe.off = off;
-                    fe.dbase = si.draws + excl.draws;
-                    fe.id = id;
-                    fe.local = local;
-                    fe.deg = (uint32_t)deg;
-                    fe.ebase = excl.take;
-                    p.frontier[excl.flags] = fe;
+        // exclusive prefix of this thread's first item
+        ScanVal run = s_prefix + s_warp[warp];
+        run.flags += incl.flags - tv.flags; run.take += incl.take - tv.take; run.draws += incl.draws - tv.draws;
+        uint32_t pending = 0;  // bit j: item j's vertex is registered by an earlier item of this stage
+#pragma unroll
+        for (int j = 0; j < kIPT; ++j) {
+            const uint32_t item = item0 + j;
+            if (first[j]) {
+                const uint32_t local = si.n_nodes + run.flags;
+                if ((uint64_t)local >= p.cap_nodes || (uint64_t)local >= kMaxPos ||
+                    (has_next && (uint64_t)run.flags >= p.frontier_cap)) {
+                    atomicOr(&bs->error, kErrCapacity);
+                    if (has_next && (uint64_t)run.flags < p.frontier_cap) p.frontier[run.flags] = FrontierEntry{};
+                    // the batch has failed; its other items must still not wait for this vertex
+                    p.table.slots[slot[j]] = ((uint64_t)id[j] << 32) | enc_final(gen, local & kPosMask);
+                    write_item_local(p, stage, si.n_edges, item, 0xFFFFFFFFu);
+                } else {
+                    p.nodes[local] = id[j];
+                    if (p.n_id) p.n_id[local] = (int64_t)id[j];
+                    p.table.slots[slot[j]] = ((uint64_t)id[j] << 32) | enc_final(gen, local);  // readers accept either form
+                    write_item_local(p, stage, si.n_edges, item, local);
+                    if (has_next) {
+                        FrontierEntry fe;
+                        fe.off = off[j];
+                        fe.dbase = si.draws + run.draws;
+                        fe.id = id[j];
+                        fe.local = local;
+                        fe.deg = deg[j];
+                        fe.ebase = run.take;
+                        p.frontier[run.flags] = fe;
+                    }
                 }
+                run.flags += 1u;
+                if (has_next) {
+                    uint32_t take; uint64_t draws;
+                    row_demand(p.mode, deg[j], k, take, draws);
+                    run.take += take; run.draws += draws;
+                }
+            } else if (item < count) {
+                if (slot[j] == 0xFFFFFFFFu) write_item_local(p, stage, si.n_edges, item, 0xFFFFFFFFu);
+                else if (!(cur32[j] & kPendingBit)) write_item_local(p, stage, si.n_edges, item, cur32[j] & kPosMask);  // an earlier stage's vertex
+                else pending |= 1u << j;
             }
-        } else if (item < count) {
-            if (slot == 0xFFFFFFFFu) write_item_local(p, stage, si.n_edges, item, 0xFFFFFFFFu);
-            else if (!(cur32 & kPendingBit)) write_item_local(p, stage, si.n_edges, item, cur32 & kPosMask);  // registered by an earlier stage
-            else { wait_slot = slot; wait_item = item; }  // registered by an earlier item of this stage
+        }
+        // The first sighting of a pending vertex is an earlier item of this stage: in this
+        // tile (stored before the barrier below) or in a tile with a smaller ticket, whose
+        // block is running and waits for nothing later than itself.
+        __syncthreads();
+        if (pending) {
+#pragma unroll
+            for (int j = 0; j < kIPT; ++j) {
+                if (!(pending & (1u << j))) continue;
+                uint32_t v = (uint32_t)__ldcg((const unsigned long long *)&p.table.slots[slot[j]]), spins = 0;
+                while (v & kPendingBit) {
+                    if (++spins > kSpinLimit) { atomicOr(&bs->error, kErrSpinTimeout); break; }
+                    __nanosleep(40);
+                    v = (uint32_t)__ldcg((const unsigned long long *)&p.table.slots[slot[j]]);
+                }
+                write_item_local(p, stage, si.n_edges, item0 + j, (v & kPendingBit) ? 0xFFFFFFFFu : (v & kPosMask));
+            }
         }
     }
 
@@ -1146,7 +1179,7 @@ int32_t launch_saved(ag_sampler *s, bool relaunch) {
     // over the whole group; the expand kernel draws tile tickets beyond that, so
     // a batch far below its bound does not pay for thousands of empty blocks.
     auto tiles_for = [&](uint64_t items) {
-        const uint64_t blocks = (items + kTile - 1) / kTile;
+        const uint64_t blocks = (items + kTileItems - 1) / kTileItems;
         return (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>(blocks, std::max<uint64_t>(1, (uint64_t)kSMs * 8 / n_batches)));
     };
     if (nmax) k_insert_seeds<<<dim3((nmax + 255) / 256, n_batches), 256, 0, st>>>(pa);
@@ -1170,17 +1203,21 @@ int32_t launch_saved(ag_sampler *s, bool relaunch) {
     if (want_x) {
         bool aligned = ((uintptr_t)feats->payload % 16) == 0;
         for (uint32_t b = 0; b < n_batches; ++b) aligned = aligned && ((uintptr_t)bufs[b].x % 16) == 0;
+        const uint64_t rows = s->est_nodes ? std::min(b_nodes, s->est_nodes) : b_nodes;
+        const uint32_t row_bytes = (uint32_t)(feats->dim * elem_size(feats->dtype));
+        const bool sorted = sorted_gather_applies(feats, row_bytes, aligned);
+        // Rows of a sharded store are fetched in address order, each distinct row of the chain
+        // once.  Making and sorting the keys is small, latency-bound work like the sampling
+        // kernels: it stays on the (high-priority) sampling stream.  (The handle's previous
+        // chain has finished — its event was waited for — so the sort scratch is free.)
+        if (sorted) AG_CUDA(launch_sort_keys(GatherArgs{}, s->gather_dev, n_batches, rows, feats, s->sort, st));
         // sampling chain -> event -> gather on the low-priority stream -> event -> caller's stream
         AG_CUDA(cudaEventRecord(s->sampled, st));
         AG_CUDA(cudaStreamWaitEvent(s->gstream, s->sampled, 0));
         if (s->profile) AG_CUDA(cudaEventRecord(s->ev[2], s->gstream));
-        const uint64_t rows = s->est_nodes ? std::min(b_nodes, s->est_nodes) : b_nodes;
-        const uint32_t row_bytes = (uint32_t)(feats->dim * elem_size(feats->dtype));
-        if (sorted_gather_applies(feats, row_bytes, aligned)) {
-            // Rows of a sharded store are fetched in address order, each distinct row of the
-            // chain once.  (The handle's previous chain has finished: its event was waited for above.)
-            AG_CUDA(launch_gather_sorted(GatherArgs{}, s->gather_dev, n_batches, rows, row_bytes, (uint32_t)feats->dim,
-                                         feats->dtype, feats, s->sort, s->gstream));
+        if (sorted) {
+            AG_CUDA(launch_sorted_fetch(GatherArgs{}, s->gather_dev, n_batches, rows, row_bytes, (uint32_t)feats->dim,
+                                        feats->dtype, feats, s->sort, s->gstream));
         } else {
             AG_CUDA(launch_gather_group(s->gather_dev, n_batches, row_bytes, (uint32_t)feats->dim, rows, aligned,
                                         feats->dtype, feats->shards != nullptr, s->gstream));

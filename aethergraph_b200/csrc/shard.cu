@@ -49,7 +49,7 @@ int32_t make_view(const ag_features *local, uint32_t world, bool cyclic, const u
     t.shard_rows = std::max<uint64_t>(shard_rows, 1);
     t.n_shards = world;
     t.cyclic = cyclic ? 1u : 0u;
-    if (cudaMalloc(&v->err, 4) != cudaSuccess || cudaMemset(v->err, 0, 4) != cudaSuccess ||
+    if (cudaMalloc(&v->err, 32) != cudaSuccess || cudaMemset(v->err, 0, 32) != cudaSuccess ||
         cudaMalloc(&v->shards, sizeof(ag_shard_table)) != cudaSuccess ||
         cudaMemcpy(v->shards, &t, sizeof(t), cudaMemcpyHostToDevice) != cudaSuccess) {
         const int32_t st = fail(AG_ERR_CUDA, "sharded view allocation failed: %s", cudaGetErrorString(cudaGetLastError()));

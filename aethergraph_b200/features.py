@@ -205,6 +205,13 @@ class FeatureStore:
                                         None, out.data_ptr() if n else None, st))
         return out
 
+    def gather_stats(self) -> tuple[int, int]:
+        """Sharded views: `(rows requested, rows loaded)` by the address-ordered gathers
+        so far; the difference is rows that several batches of one launch chain named."""
+        a, b = C.c_uint64(), C.c_uint64()
+        _lib.check(_lib.lib().ag_features_gather_stats(self._h, C.byref(a), C.byref(b)))
+        return a.value, b.value
+
     def check(self) -> None:
         """Raise ValueError if a device gather since the last check saw an out-of-range id."""
         _lib.check(_lib.lib().ag_features_check(self._h))

@@ -669,6 +669,7 @@ def sharded_summary(w, world, med, stored_row, leg, view, replicated, dev, sum_o
                 ok = ok and bool(torch.equal(x[pos].view(torch.int32), want[0].view(torch.int32)))
                 checked += 1
         del holder
+    asked, loaded = view.gather_stats()
     ok_all = sum_over_ranks(1.0 if ok else 0.0) == float(world)
     return {"layout": "contiguous vertex ranges" if layout_flag == "sharded-range" else "round-robin by vertex id",
             "value": med["value"], "unit": "edges/s", "ms_per_step": ms / max(steps, 1),
@@ -678,6 +679,7 @@ def sharded_summary(w, world, med, stored_row, leg, view, replicated, dev, sum_o
             "peer_copy_peak_gbs": NVLINK_PEER_COPY_GBS,
             "remote_note": "stored row bytes of the remote share of the gathered rows (as if no row were fetched "
                            "twice) per second and GPU; rows named by several batches of a chain cross the link once",
+            "rows_loaded_per_row_requested": (loaded / asked) if asked else None,
             "parity": bool(ok_all), "parity_rows_checked_per_rank": checked}
 
 

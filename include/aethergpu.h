@@ -164,6 +164,16 @@ int32_t ag_features_open_sharded(const ag_features *local, uint32_t world, uint3
                                  const void *handles, ag_features **out);
 int32_t ag_features_view_sharded(const ag_features *const *shards, uint32_t world, uint32_t rank,
                                  ag_features **out);
+/* A gather over a sharded view (ag_gather, or the chain of a sampler / loader)
+ * requests its rows in address order: the ids of the launch are turned into
+ * keys (row within shard, owner), sorted in local memory, and fetched in that
+ * order, a row named more than once only once — the counterpart of the
+ * reference's request coalescing in its one-sided remote gather
+ * (crates/aether-stream/src/rdma/sharded.rs:1-33, rdma/gather.rs:1-9).  The
+ * counters say how many rows such gathers were asked for and how many they
+ * loaded (the rest were repeats within a launch), since the view was opened. */
+int32_t ag_features_gather_stats(const ag_features *f, uint64_t *rows_requested,
+                                 uint64_t *rows_fetched);
 /* Copies the stored (encoded) rows held by this handle back to host memory. */
 int32_t ag_features_copy_to_host(const ag_features *f, void *payload);
 
