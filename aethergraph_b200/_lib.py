@@ -113,7 +113,9 @@ SIGNATURES = {
     "ag_graph_copy_to_host": (C.c_int32, [_P, _P, _P, _P]),
     "ag_features_copy_to_host": (C.c_int32, [_P, _P]),
     "ag_features_shard": (C.c_int32, [_P, _U64P, _U64P]),
-    "ag_features_gather_stats": (C.c_int32, [_P, _U64P, _U64P]),
+    "ag_features_gather_stats": (C.c_int32, [_P, _U64P, _U64P, _U64P]),
+    "ag_graph_hot_vertices": (C.c_int32, [_P, C.c_uint64, _PP, _U64P]),
+    "ag_features_cache_rows": (C.c_int32, [_P, _P, C.c_uint64]),
     "ag_graph_free": (None, [_P]),
     "ag_features_save": (C.c_int32, [C.c_char_p, _P, C.c_uint64, C.c_uint64, C.c_int32]),
     "ag_features_load": (C.c_int32, [C.c_char_p, C.c_int32, _PP]),

@@ -575,6 +575,7 @@ extern "C" void ag_features_free(ag_features *f) {
         f->sort->scratch.release();
         delete f->sort;
     }
+    cudaFree(f->hot_rows); cudaFree(f->hot_slot);
     cudaFree(f->shards);
     cudaFree(f->err);
     delete f;
@@ -772,14 +773,16 @@ extern "C" int32_t ag_gather(const ag_features *f, const void *ids_dev, int32_t 
     return AG_OK;
 }
 
-extern "C" int32_t ag_features_gather_stats(const ag_features *f, uint64_t *rows_requested, uint64_t *rows_fetched) {
+extern "C" int32_t ag_features_gather_stats(const ag_features *f, uint64_t *rows_requested, uint64_t *rows_fetched,
+                                            uint64_t *rows_local_copy) {
     if (!f) return fail(AG_ERR_VALUE, "ag_features_gather_stats: null store");
     DeviceGuard guard(f->device);
     if (!guard.ok) return AG_ERR_CUDA;
-    uint64_t h[2] = {0, 0};
-    AG_CUDA(cudaMemcpy(h, (const uint8_t *)f->err + 8, 16, cudaMemcpyDeviceToHost));
+    uint64_t h[3] = {0, 0, 0};
+    AG_CUDA(cudaMemcpy(h, (const uint8_t *)f->err + 8, 24, cudaMemcpyDeviceToHost));
     if (rows_requested) *rows_requested = h[0];
     if (rows_fetched) *rows_fetched = h[1];
+    if (rows_local_copy) *rows_local_copy = h[2];
     return AG_OK;
 }
 

@@ -101,6 +101,10 @@ __device__ __forceinline__ uint4 ld_peer_v4(const void *p) {
 // Where row `id` of a sharded store lives: shard id / shard_rows, which is this
 // GPU's own memory or a peer's (vertex-range shards of equal size).
 __device__ __forceinline__ const uint8_t *shard_row(const ag_shard_table *t, uint64_t id, uint32_t row_bytes) {
+    if (t->hot_slot) {  // a hot row has a copy in this GPU's memory
+        const uint32_t h = __ldg(t->hot_slot + id);
+        if (h != 0xFFFFFFFFu) return t->base[t->n_shards] + (uint64_t)h * row_bytes;
+    }
     if (t->cyclic) {  // rows dealt round-robin: hot vertex ranges spread over all GPUs
         const uint64_t s = id % t->n_shards;
         return t->base[s] + (id / t->n_shards) * row_bytes;
@@ -267,113 +271,197 @@ __global__ void k_encode(const float *src, uint16_t *dst, uint64_t count, int dt
 // peers' memory.  Random rows spread over tens of gigabytes of such mappings
 // run far below the link's bandwidth (every row needs an address translation
 // that is no longer cached); the same rows requested in address order run at
-// the link's bandwidth.  So a launch first turns its row ids into address-order
-// keys, sorts them (in local memory) together with the output position of each
-// row, and gathers in that order.  The f32 rows are still written at their
-// original positions in local HBM, where order costs nothing.
+// the link's bandwidth.  So a launch first turns its row ids into keys, sorts
+// them (in local memory) together with the output position of each row, and
+// gathers in that order.  The f32 rows are still written at their original
+// positions in local HBM, where order costs nothing.
 //
-// key = row-within-shard * W + owner.  Within one owner the rows ascend, and
-// neighbouring keys alternate between the owners, so at any moment a GPU pulls
-// from all its peers at once (no owner's links are the only ones busy) while
-// each owner is still read in ascending address order.  For round-robin shards
-// the key IS the vertex id; for contiguous ranges it is (id % S) * W + id / S.
-//
-// Sorting has a second use: the batches of one launch chain name many rows more
-// than once (hub vertices turn up in most batches of a chain).  Equal keys are
-// neighbours after the sort, so a row is loaded once — crosses the link once —
-// and written to every batch that asked for it.
+// key = remote << B | (row-within-source * S + source), the sources being the W
+// shards and, when the view holds a copy of the hot rows, that copy as source W
+// (S = W or W + 1); `remote` says the source is another GPU's memory.
+//   * Local rows sort before remote ones, and the two parts are fetched by two
+//     launches that can run side by side: the local part streams at HBM speed,
+//     the remote part waits on NVLink round trips, and neither holds the other up.
+//   * Within a part the rows of one source ascend, and neighbouring keys alternate
+//     between the sources, so a GPU pulls from all its peers at once while each
+//     peer is still read in ascending address order.
+// The batches of one launch chain name many rows more than once (hub vertices turn
+// up in most batches of a chain: three rows in ten of a 64-batch chain on the
+// R-MAT benchmark graph are repeats).  Equal keys are neighbours after the sort, so
+// such a row is loaded once and written to every batch that asked for it.  (Sorting
+// only the upper bits of the key would be enough for the address translation and
+// save two of the four radix passes, but it loses the repeats: measured, the extra
+// row loads cost three times what the passes do.)
 constexpr uint32_t kValRowBits = 23;  // value = batch << 23 | row: rows per batch < 2^23, batches per chain <= 256
+constexpr uint32_t kSortedBits = 32;  // key bits the radix sort orders, counted from the top: all of them
+constexpr int kPartLocal = 0, kPartRemote = 1, kPartAll = 2;
 
-__device__ __forceinline__ uint32_t addr_key(const ag_shard_table *t, uint64_t id) {
-    if (t->cyclic) return (uint32_t)id;
-    const uint64_t s = id / t->shard_rows;
-    return (uint32_t)((id - s * t->shard_rows) * t->n_shards + s);
+struct SortedKeys {
+    uint32_t addr_bits;   // B
+    uint32_t sentinel;    // padding mark: above every key
+    int begin_bit, end_bit;
+};
+
+__device__ __forceinline__ uint32_t addr_key(const ag_shard_table *t, uint64_t id, uint32_t addr_bits) {
+    const uint32_t S = t->n_sources;  // the shards, and the local copy of the hot rows as one more source
+    if (t->hot_slot) {
+        const uint32_t h = __ldg(t->hot_slot + id);
+        if (h != 0xFFFFFFFFu) return h * S + t->n_shards;
+    }
+    uint64_t owner, local;
+    if (t->cyclic) { owner = id % t->n_shards; local = id / t->n_shards; }
+    else { owner = id / t->shard_rows; local = id - owner * t->shard_rows; }
+    const uint32_t remote = (owner != t->self) ? 1u : 0u;
+    return (remote << addr_bits) | (uint32_t)(local * S + owner);
 }
 
+// counts[0] / counts[1] receive the number of keys of local / remote rows (local ones sort to the front).
 __global__ void __launch_bounds__(256)
-k_make_keys(GatherArgs a, const GatherArgs *__restrict__ group, uint32_t rows_cap, uint32_t sentinel,
-            uint32_t *__restrict__ keys, uint32_t *__restrict__ vals) {
+k_make_keys(GatherArgs a, const GatherArgs *__restrict__ group, uint32_t rows_cap, uint32_t addr_bits, uint32_t sentinel,
+            uint32_t *__restrict__ keys, uint32_t *__restrict__ vals, uint32_t *__restrict__ counts) {
     if (group) a = group[blockIdx.y];
     uint64_t n = 0;
     if (a.payload) n = a.n_dev ? min((uint64_t)*a.n_dev, a.n) : a.n;
     if (a.ids_off) a.ids = (const uint32_t *)a.ids + *a.ids_off;
     const uint64_t slot0 = (uint64_t)blockIdx.y * rows_cap;
+    uint32_t local_rows = 0, remote_rows = 0;
     for (uint32_t r = blockIdx.x * blockDim.x + threadIdx.x; r < rows_cap; r += gridDim.x * blockDim.x) {
         uint32_t key = sentinel;  // slots past the batch's rows sort to the end
         if (r < n) {
             const uint64_t id = load_id(a.ids, a.ids64, r);
-            if (id >= a.row_begin && id - a.row_begin < a.rows) key = addr_key(a.shards, id);
-            else atomicOr(a.err, kErrBadId);
+            if (id >= a.row_begin && id - a.row_begin < a.rows) {
+                key = addr_key(a.shards, id, addr_bits);
+                if ((key >> addr_bits) == 0) ++local_rows; else ++remote_rows;
+            } else {
+                atomicOr(a.err, kErrBadId);
+            }
         }
         keys[slot0 + r] = key;
         vals[slot0 + r] = (blockIdx.y << kValRowBits) | r;
     }
+    // one atomic per warp and counter
+    for (int o = 16; o > 0; o >>= 1) {
+        local_rows += __shfl_xor_sync(0xffffffffu, local_rows, o);
+        remote_rows += __shfl_xor_sync(0xffffffffu, remote_rows, o);
+    }
+    if ((threadIdx.x & 31) == 0) {
+        if (local_rows) atomicAdd(counts, local_rows);
+        if (remote_rows) atomicAdd(counts + 1, remote_rows);
+    }
+}
+
+// The fetch.  Entry i of the sorted list fetches its row when it starts a run of
+// equal keys or sits at a multiple of kRunCap; it then writes the row to every entry
+// up to the next fetcher.  Repeats are loaded once per kRunCap entries at most, and
+// no lane group is ever left writing a long run on its own.
+constexpr int kRunCap = 4;
+
+// address part of a key -> (source, row within source).  The number of sources is a
+// small run-time value; dividing by it as a constant keeps the divisions off the
+// (slow) special-function pipe, which two of them per row and lane would saturate.
+__device__ __forceinline__ void split_key(uint32_t ak, uint32_t S, uint32_t &src, uint32_t &local) {
+    switch (S) {
+#define AG_SPLIT(N) case N: local = ak / N; src = ak - local * N; break;
+        AG_SPLIT(2) AG_SPLIT(3) AG_SPLIT(4) AG_SPLIT(5) AG_SPLIT(6) AG_SPLIT(7) AG_SPLIT(8) AG_SPLIT(9)
+#undef AG_SPLIT
+        default: local = ak / S; src = ak - local * S; break;
+    }
 }
 
 template <int DTYPE, int LPR>
-__global__ void __launch_bounds__(kThreads)
-k_gather_sorted(GatherArgs one, const GatherArgs *__restrict__ group, const ag_shard_table *__restrict__ t,
-                const uint32_t *__restrict__ keys, const uint32_t *__restrict__ vals, uint64_t n_items,
-                uint32_t sentinel, uint32_t row_bytes, uint32_t dim, unsigned long long *__restrict__ counters) {
+__global__ void __launch_bounds__(kThreads, 4)
+k_gather_sorted(GatherArgs one, const GatherArgs *__restrict__ group, uint32_t n_batches,
+                const ag_shard_table *__restrict__ t, const uint32_t *__restrict__ keys,
+                const uint32_t *__restrict__ vals, uint64_t n_items, uint32_t addr_bits, uint32_t sentinel,
+                uint32_t row_bytes, uint32_t dim, int part, const uint32_t *__restrict__ counts,
+                unsigned long long *__restrict__ counters) {
     constexpr int kRowsPerBlock = kThreads / LPR;
-    uint32_t asked = 0, loaded = 0;  // counted by lane 0 of each row group
-    constexpr uint64_t kChunk = (uint64_t)kRowsPerBlock * kInFlight;
+    constexpr uint32_t kChunk = (uint32_t)kRowsPerBlock * kInFlight;
+    __shared__ float *s_out[256];       // output base of every batch of the chain
+    __shared__ const uint8_t *s_base[9];  // where every source's rows start
+    if (group) { for (uint32_t b = threadIdx.x; b < n_batches; b += kThreads) s_out[b] = group[b].out; }
+    else if (threadIdx.x == 0) s_out[0] = one.out;
+    const uint32_t S = t->n_sources, W = t->n_shards;
+    if (threadIdx.x < 9) s_base[threadIdx.x] = threadIdx.x < S ? t->base[threadIdx.x] : nullptr;
+    __syncthreads();
     const int lane = threadIdx.x % LPR;
     const int sub = threadIdx.x / LPR;
     const uint32_t vecs = row_bytes >> 4;
     const uint32_t out_per_vec = (DTYPE == AG_F32) ? 4u : 8u;
-    const uint32_t W = t->n_shards;
-    for (uint64_t chunk0 = (uint64_t)blockIdx.x * kChunk; chunk0 < n_items; chunk0 += (uint64_t)gridDim.x * kChunk) {
-        if (keys[chunk0] == sentinel) return;  // sorted: nothing but padding from here on
-        const uint64_t base = chunk0 + sub;
+    const uint32_t addr_mask = (1u << addr_bits) - 1u;
+    constexpr uint32_t kRowMask = (1u << kValRowBits) - 1u;
+    // this launch's part of the list: the local rows, the remote rows, or all of them
+    // (32-bit positions: the host keeps a list below 2^31 entries)
+    const uint32_t n_all = (uint32_t)n_items;
+    const uint32_t n_local = min(counts[0], n_all);
+    const uint32_t n_valid = (uint32_t)min((uint64_t)n_local + counts[1], (uint64_t)n_all);
+    const uint32_t begin = (part == kPartRemote) ? n_local : 0u;
+    const uint32_t end = (part == kPartLocal) ? n_local : n_valid;
+    constexpr uint32_t kNoFetch = 0xFFFFFFFFu;  // never an address: the remote bit sits below bit 31
+    uint32_t asked = 0, loaded = 0, local_hits = 0;  // counted by lane 0 of each row group
+    for (uint32_t chunk0 = begin + blockIdx.x * (uint32_t)kChunk; chunk0 < end; chunk0 += gridDim.x * (uint32_t)kChunk) {
+        const uint32_t base = chunk0 + sub;
+        uint32_t ak[kInFlight];   // address part of a fetching entry's key, or kNoFetch
+        uint32_t val[kInFlight];
+#pragma unroll
+        for (int u = 0; u < kInFlight; ++u) {
+            const uint32_t i = base + u * kRowsPerBlock;
+            ak[u] = kNoFetch; val[u] = 0;
+            if (i < end) {
+                const uint32_t key = keys[i];
+                val[u] = vals[i];
+                const uint32_t prev = i > begin ? keys[i - 1] : sentinel;
+                const bool fetch = prev != key || (i % kRunCap) == 0;
+                if (fetch) ak[u] = key & addr_mask;
+                if (lane == 0) { ++asked; loaded += fetch; }
+            }
+        }
         for (uint32_t v0 = 0; v0 < vecs; v0 += LPR) {
             const uint32_t v = v0 + lane;
-            uint4 val[kInFlight];
-            uint32_t key[kInFlight];
-            bool head[kInFlight];
+            uint4 row[kInFlight];
 #pragma unroll
             for (int u = 0; u < kInFlight; ++u) {
-                const uint64_t i = base + (uint64_t)u * kRowsPerBlock;
-                head[u] = false;
-                val[u] = make_uint4(0, 0, 0, 0);
-                key[u] = sentinel;
-                if (i < n_items && v < vecs) {
-                    key[u] = keys[i];
-                    // the first of a run of equal keys fetches the row for the whole run
-                    head[u] = key[u] != sentinel && (i == 0 || keys[i - 1] != key[u]);
-                    if (lane == 0 && v0 == 0) { asked += key[u] != sentinel; loaded += head[u]; }
-                    if (head[u]) {
-                        const uint32_t owner = key[u] % W;
-                        const uint64_t local = key[u] / W;
-                        val[u] = ld_peer_v4(t->base[owner] + local * row_bytes + ((uint64_t)v << 4));
-                    }
+                row[u] = make_uint4(0, 0, 0, 0);
+                if (ak[u] != kNoFetch && v < vecs) {
+                    uint32_t src, local;
+                    split_key(ak[u], S, src, local);
+                    if (lane == 0 && v0 == 0) local_hits += (S > W && src == W);
+                    row[u] = ld_peer_v4(s_base[src] + (uint64_t)local * row_bytes + (v << 4));
                 }
             }
 #pragma unroll
             for (int u = 0; u < kInFlight; ++u) {
-                if (!head[u]) continue;
-                uint64_t j = base + (uint64_t)u * kRowsPerBlock;
-                do {
+                if (ak[u] == kNoFetch || v >= vecs) continue;
+                store_decoded<DTYPE>(s_out[val[u] >> kValRowBits] + (uint64_t)(val[u] & kRowMask) * dim + v * out_per_vec, row[u]);
+                // the rest of the run, up to the next fetcher
+                const uint32_t i = base + u * kRowsPerBlock;
+                for (uint32_t j = i + 1; j < end && (j % kRunCap) != 0 && keys[j] == keys[i]; ++j) {
                     const uint32_t pv = vals[j];
-                    float *out = group ? group[pv >> kValRowBits].out : one.out;
-                    store_decoded<DTYPE>(out + (uint64_t)(pv & ((1u << kValRowBits) - 1u)) * dim + (uint64_t)v * out_per_vec, val[u]);
-                    ++j;
-                } while (j < n_items && keys[j] == key[u]);
+                    store_decoded<DTYPE>(s_out[pv >> kValRowBits] + (uint64_t)(pv & kRowMask) * dim + v * out_per_vec, row[u]);
+                }
             }
         }
     }
-    if (asked) { atomicAdd(counters, (unsigned long long)asked); atomicAdd(counters + 1, (unsigned long long)loaded); }
+    if (lane == 0 && asked) {
+        atomicAdd(counters, (unsigned long long)asked); atomicAdd(counters + 1, (unsigned long long)loaded);
+        if (local_hits) atomicAdd(counters + 2, (unsigned long long)local_hits);
+    }
 }
 
 template <int DTYPE>
-cudaError_t launch_sorted(const GatherArgs &one, const GatherArgs *group, const ag_shard_table *t, const uint32_t *keys,
-                          const uint32_t *vals, uint64_t n_items, uint32_t sentinel, uint32_t row_bytes, uint32_t dim,
-                          int blocks, unsigned long long *counters, cudaStream_t st) {
+cudaError_t launch_sorted(const GatherArgs &one, const GatherArgs *group, uint32_t n_batches, const ag_shard_table *t,
+                          const uint32_t *keys, const uint32_t *vals, uint64_t n_items, const SortedKeys &sk, uint32_t row_bytes,
+                          uint32_t dim, int part, const uint32_t *counts, unsigned long long *counters, cudaStream_t st) {
+    // a few chunks per block: the block's tables of output and source bases are set up once
+    const int blocks = std::max(1, std::min(gather_grid_blocks(n_items, row_bytes), kSMs * 16));
     const uint32_t vecs = row_bytes >> 4;
-    if (vecs <= 4) k_gather_sorted<DTYPE, 4><<<blocks, kThreads, 0, st>>>(one, group, t, keys, vals, n_items, sentinel, row_bytes, dim, counters);
-    else if (vecs <= 8) k_gather_sorted<DTYPE, 8><<<blocks, kThreads, 0, st>>>(one, group, t, keys, vals, n_items, sentinel, row_bytes, dim, counters);
-    else if (vecs <= 16) k_gather_sorted<DTYPE, 16><<<blocks, kThreads, 0, st>>>(one, group, t, keys, vals, n_items, sentinel, row_bytes, dim, counters);
-    else k_gather_sorted<DTYPE, 32><<<blocks, kThreads, 0, st>>>(one, group, t, keys, vals, n_items, sentinel, row_bytes, dim, counters);
+#define AG_LAUNCH_SORTED(L) k_gather_sorted<DTYPE, L><<<blocks, kThreads, 0, st>>>(one, group, n_batches, t, keys, vals, n_items, \
+                                sk.addr_bits, sk.sentinel, row_bytes, dim, part, counts, counters)
+    if (vecs <= 4) AG_LAUNCH_SORTED(4);
+    else if (vecs <= 8) AG_LAUNCH_SORTED(8);
+    else if (vecs <= 16) AG_LAUNCH_SORTED(16);
+    else AG_LAUNCH_SORTED(32);
+#undef AG_LAUNCH_SORTED
     return cudaGetLastError();
 }
 
@@ -454,8 +542,8 @@ cudaError_t launch_gather_group(const GatherArgs *group_dev, uint32_t n_batches,
 
 // ------------------------------------------------ sorted gather, host side --
 void SortScratch::release() {
-    cudaFree(keys[0]); cudaFree(keys[1]); cudaFree(vals[0]); cudaFree(vals[1]); cudaFree(temp);
-    keys[0] = keys[1] = vals[0] = vals[1] = nullptr; temp = nullptr;
+    cudaFree(keys[0]); cudaFree(keys[1]); cudaFree(vals[0]); cudaFree(vals[1]); cudaFree(temp); cudaFree(counts);
+    keys[0] = keys[1] = vals[0] = vals[1] = nullptr; temp = nullptr; counts = nullptr;
     cap = 0; temp_bytes = 0;
 }
 
@@ -472,10 +560,28 @@ cudaError_t SortScratch::ensure(uint64_t items) {
         if (e == cudaSuccess) e = cudaMalloc(&vals[i], want * 4);
     }
     if (e == cudaSuccess) e = cudaMalloc(&temp, std::max<size_t>(tb, 16));
+    if (e == cudaSuccess) e = cudaMalloc(&counts, 16);
     if (e != cudaSuccess) { release(); return e; }
     cap = want; temp_bytes = tb;
     return cudaSuccess;
 }
+
+// One past the largest row-within-source * S + source of the view.
+uint64_t sorted_key_bound(const ag_features *f) {
+    const uint64_t sources = f->n_shards + (f->hot_n ? 1 : 0);
+    return std::max<uint64_t>(f->shard_rows, f->hot_n) * sources;
+}
+
+namespace {
+SortedKeys sorted_keys_of(const ag_features *f) {
+    SortedKeys k{};
+    k.addr_bits = bit_width_u64(sorted_key_bound(f));          // B: every address part is below 2^B
+    k.sentinel = (uint32_t)((1ull << (k.addr_bits + 2)) - 1);   // above remote << B | anything
+    k.end_bit = (int)k.addr_bits + 2;
+    k.begin_bit = std::max(0, k.end_bit - (int)kSortedBits);
+    return k;
+}
+}  // namespace
 
 bool sorted_gather_applies(const ag_features *f, uint32_t row_bytes, bool aligned) {
     static const bool enabled = [] {
@@ -483,16 +589,16 @@ bool sorted_gather_applies(const ag_features *f, uint32_t row_bytes, bool aligne
         return !(v && v[0] == '0');
     }();
     if (!enabled || !f || !f->shards || f->n_shards < 2 || !aligned || row_bytes % 16 != 0) return false;
-    // keys are 32 bits and one value above the largest key is the padding mark
-    return f->shard_rows * f->n_shards < 0xFFFFFFFFull;
+    return bit_width_u64(sorted_key_bound(f)) <= 30;  // 32-bit keys: address part, the remote bit, the padding mark above
 }
 
 // The address-ordered gather in two steps, so that a caller can put them on different
-// streams (small latency-bound kernels first, the bandwidth-bound fetch behind an event).
+// streams (small latency-bound kernels first, the fetch behind an event).
 // Step 1: keys of rows [0, min(n_b, rows_cap)) of every batch, sorted with their output
-// positions.  Step 2: fetch in that order, then rows [rows_cap, n_b) — only present when a
-// batch outgrew the caller's estimate — with the unsorted kernel.  `one` / `group_dev` as
-// in launch_gather / launch_gather_group.
+// positions.  Step 2: fetch in that order — the local part on st_local, the remote part
+// on st_remote (the same stream: one after the other) — then rows [rows_cap, n_b), only
+// present when a batch outgrew the caller's estimate, with the unsorted kernel.
+// `one` / `group_dev` as in launch_gather / launch_gather_group.
 cudaError_t launch_sort_keys(const GatherArgs &one, const GatherArgs *group_dev, uint32_t n_batches, uint64_t rows_cap,
                              const ag_features *f, SortScratch &sc, cudaStream_t st) {
     if (n_batches == 0 || rows_cap == 0) return cudaSuccess;
@@ -500,40 +606,41 @@ cudaError_t launch_sort_keys(const GatherArgs &one, const GatherArgs *group_dev,
     const uint64_t n_items = (uint64_t)n_batches * rows_cap;
     cudaError_t e = sc.ensure(n_items);
     if (e != cudaSuccess) return e;
-    const uint64_t max_key = f->shard_rows * f->n_shards;  // one past the largest key
-    const uint32_t bits = bit_width_u64(max_key);
-    const uint32_t sentinel = bits >= 32 ? 0xFFFFFFFFu : ((1u << bits) - 1u);
+    const SortedKeys sk = sorted_keys_of(f);
+    if ((e = cudaMemsetAsync(sc.counts, 0, 16, st)) != cudaSuccess) return e;
     const uint32_t kb = (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>((rows_cap + 255) / 256, std::max<uint64_t>(1, (uint64_t)kSMs * 8 / n_batches)));
-    k_make_keys<<<dim3(kb, n_batches), 256, 0, st>>>(one, group_dev, (uint32_t)rows_cap, sentinel, sc.keys[0], sc.vals[0]);
+    k_make_keys<<<dim3(kb, n_batches), 256, 0, st>>>(one, group_dev, (uint32_t)rows_cap, sk.addr_bits, sk.sentinel, sc.keys[0],
+                                                    sc.vals[0], sc.counts);
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
     size_t tb = sc.temp_bytes;
     return cub::DeviceRadixSort::SortPairs(sc.temp, tb, (const uint32_t *)sc.keys[0], sc.keys[1], (const uint32_t *)sc.vals[0],
-                                           sc.vals[1], n_items, 0, (int)bits, st);
+                                           sc.vals[1], n_items, sk.begin_bit, sk.end_bit, st);
 }
 
 cudaError_t launch_sorted_fetch(const GatherArgs &one, const GatherArgs *group_dev, uint32_t n_batches, uint64_t rows_cap,
                                 uint32_t row_bytes, uint32_t dim, int dtype, const ag_features *f, SortScratch &sc,
-                                cudaStream_t st) {
+                                cudaStream_t st_local, cudaStream_t st_remote) {
     if (n_batches == 0 || rows_cap == 0) return cudaSuccess;
     rows_cap = std::min<uint64_t>(rows_cap, (1ull << kValRowBits) - 1);
     const uint64_t n_items = (uint64_t)n_batches * rows_cap;
-    const uint32_t bits = bit_width_u64(f->shard_rows * f->n_shards);
-    const uint32_t sentinel = bits >= 32 ? 0xFFFFFFFFu : ((1u << bits) - 1u);
-    const int blocks = gather_grid_blocks(n_items, row_bytes);
+    const SortedKeys sk = sorted_keys_of(f);
     unsigned long long *counters = (unsigned long long *)((uint8_t *)f->err + 8);
-    cudaError_t e;
-    switch (dtype) {
-        case AG_F32: e = launch_sorted<AG_F32>(one, group_dev, f->shards, sc.keys[1], sc.vals[1], n_items, sentinel, row_bytes, dim, blocks, counters, st); break;
-        case AG_F16: e = launch_sorted<AG_F16>(one, group_dev, f->shards, sc.keys[1], sc.vals[1], n_items, sentinel, row_bytes, dim, blocks, counters, st); break;
-        default: e = launch_sorted<AG_BF16>(one, group_dev, f->shards, sc.keys[1], sc.vals[1], n_items, sentinel, row_bytes, dim, blocks, counters, st); break;
-    }
+    auto fetch = [&](int part, cudaStream_t st) {
+        switch (dtype) {
+            case AG_F32: return launch_sorted<AG_F32>(one, group_dev, n_batches, f->shards, sc.keys[1], sc.vals[1], n_items, sk, row_bytes, dim, part, sc.counts, counters, st);
+            case AG_F16: return launch_sorted<AG_F16>(one, group_dev, n_batches, f->shards, sc.keys[1], sc.vals[1], n_items, sk, row_bytes, dim, part, sc.counts, counters, st);
+            default: return launch_sorted<AG_BF16>(one, group_dev, n_batches, f->shards, sc.keys[1], sc.vals[1], n_items, sk, row_bytes, dim, part, sc.counts, counters, st);
+        }
+    };
+    cudaError_t e = fetch(kPartRemote, st_remote);
+    if (e == cudaSuccess) e = fetch(kPartLocal, st_local);
     if (e != cudaSuccess) return e;
     // Rows past the estimate (rare): a few blocks per batch, which stride; most exit at once.
     const dim3 grid(4, n_batches);
     switch (dtype) {
-        case AG_F32: return launch_vec<AG_F32>(one, group_dev, row_bytes, grid, true, st, rows_cap);
-        case AG_F16: return launch_vec<AG_F16>(one, group_dev, row_bytes, grid, true, st, rows_cap);
-        default: return launch_vec<AG_BF16>(one, group_dev, row_bytes, grid, true, st, rows_cap);
+        case AG_F32: return launch_vec<AG_F32>(one, group_dev, row_bytes, grid, true, st_local, rows_cap);
+        case AG_F16: return launch_vec<AG_F16>(one, group_dev, row_bytes, grid, true, st_local, rows_cap);
+        default: return launch_vec<AG_BF16>(one, group_dev, row_bytes, grid, true, st_local, rows_cap);
     }
 }
 
@@ -542,7 +649,7 @@ cudaError_t launch_gather_sorted(const GatherArgs &one, const GatherArgs *group_
                                  cudaStream_t st) {
     const cudaError_t e = launch_sort_keys(one, group_dev, n_batches, rows_cap, f, sc, st);
     if (e != cudaSuccess) return e;
-    return launch_sorted_fetch(one, group_dev, n_batches, rows_cap, row_bytes, dim, dtype, f, sc, st);
+    return launch_sorted_fetch(one, group_dev, n_batches, rows_cap, row_bytes, dim, dtype, f, sc, st, st);
 }
 
 cudaError_t launch_encode(const float *src, void *dst, uint64_t count, int dtype, cudaStream_t st) {

@@ -16,6 +16,7 @@ struct SortScratch {
     uint32_t *keys[2] = {nullptr, nullptr};
     uint32_t *vals[2] = {nullptr, nullptr};
     void *temp = nullptr;
+    uint32_t *counts = nullptr;  // [0]: keys of local rows in the list being sorted
     size_t temp_bytes = 0;
     uint64_t cap = 0;  // items the arrays hold
     cudaError_t ensure(uint64_t items);
@@ -50,6 +51,10 @@ struct ag_features {
     uint32_t n_shards = 0;
     uint64_t shard_rows = 0;                  // rows per shard (the last may hold fewer)
     bool shard_cyclic = false;                // rows dealt round-robin instead of contiguous ranges
+    // Hot rows replicated on this GPU (ag_features_cache_rows): requests for them never cross NVLink.
+    uint8_t *hot_rows = nullptr;              // device, hot_n * row bytes
+    uint32_t *hot_slot = nullptr;             // device, num_nodes entries
+    uint64_t hot_n = 0;
     void *ipc_opened[8] = {nullptr};          // peer mappings this view opened (closed on free)
     // ag_gather on a sharded view sorts its ids into address order first; the scratch
     // belongs to the view, calls take turns (mutex on the host, event on the device).
@@ -63,10 +68,13 @@ struct ag_features {
 
 // Device-visible table of a sharded feature store.
 struct ag_shard_table {
-    const uint8_t *base[8];
-    uint64_t shard_rows;  // range layout: rows per shard
+    const uint8_t *base[9];   // shard r's rows; base[n_shards]: this GPU's copy of the hot rows, if any
+    uint64_t shard_rows;      // range layout: rows per shard
     uint32_t n_shards;
-    uint32_t cyclic;      // 1: row v lives in shard v % n_shards at local row v / n_shards
+    uint32_t cyclic;          // 1: row v lives in shard v % n_shards at local row v / n_shards
+    uint32_t n_sources;       // n_shards, or n_shards + 1 with a hot-row copy
+    uint32_t self;            // the shard that lives in this GPU's own memory
+    const uint32_t *hot_slot; // per vertex: its row in the hot-row copy, or 0xFFFFFFFF (null: no copy)
 };
 
 namespace ag {
@@ -104,7 +112,7 @@ cudaError_t launch_sort_keys(const GatherArgs &one, const GatherArgs *group_dev,
                              const ag_features *f, SortScratch &sc, cudaStream_t st);
 cudaError_t launch_sorted_fetch(const GatherArgs &one, const GatherArgs *group_dev, uint32_t n_batches, uint64_t rows_cap,
                                 uint32_t row_bytes, uint32_t dim, int dtype, const ag_features *f, SortScratch &sc,
-                                cudaStream_t st);
+                                cudaStream_t st_local, cudaStream_t st_remote);
 cudaError_t launch_gather_sorted(const GatherArgs &one, const GatherArgs *group_dev, uint32_t n_batches, uint64_t rows_cap,
                                  uint32_t row_bytes, uint32_t dim, int dtype, const ag_features *f, SortScratch &sc,
                                  cudaStream_t st);

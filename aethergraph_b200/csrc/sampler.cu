@@ -805,6 +805,11 @@ struct ag_sampler {
     // in between the short-lived blocks of a running gather (bandwidth-bound).
     cudaStream_t gstream = nullptr;
     cudaEvent_t sampled = nullptr;
+    // Sharded stores: the remote part of a chain's rows is fetched by a launch of its own on
+    // this stream (between the two priorities), beside the local part on gstream.
+    cudaStream_t rstream = nullptr;
+    cudaEvent_t remote_done = nullptr;
+    uint64_t est_rows_tight = 0;  // rows per batch the last chain produced, with little headroom (sort padding)
     SortScratch sort;  // sharded feature stores: the chain's row ids in address order (gather.cu)
     // The arguments of the chain in flight, kept so that it can be launched once more:
     // the dedup tables are sized from the node counts of earlier chains (small tables stay
@@ -949,7 +954,9 @@ extern "C" int32_t ag_sampler_create_group(const ag_graph *g, const ag_sampling_
         }
         int lo = 0, hi = 0;
         cudaDeviceGetStreamPriorityRange(&lo, &hi);  // lo = least urgent
-        if (cudaStreamCreateWithPriority(&s->gstream, cudaStreamNonBlocking, lo) != cudaSuccess) {
+        if (cudaStreamCreateWithPriority(&s->gstream, cudaStreamNonBlocking, lo) != cudaSuccess ||
+            cudaStreamCreateWithPriority(&s->rstream, cudaStreamNonBlocking, (lo + hi) / 2) != cudaSuccess ||
+            cudaEventCreateWithFlags(&s->remote_done, cudaEventDisableTiming) != cudaSuccess) {
             st = fail(AG_ERR_CUDA, "cudaStreamCreateWithPriority failed: %s", cudaGetErrorString(cudaGetLastError()));
             break;
         }
@@ -978,6 +985,8 @@ extern "C" void ag_sampler_free(ag_sampler *s) {
     if (s->done) cudaEventDestroy(s->done);
     if (s->sampled) cudaEventDestroy(s->sampled);
     if (s->gstream) cudaStreamDestroy(s->gstream);
+    if (s->rstream) cudaStreamDestroy(s->rstream);
+    if (s->remote_done) cudaEventDestroy(s->remote_done);
     for (auto &e : s->ev) if (e) cudaEventDestroy(e);
     delete s;
 }
@@ -1210,14 +1219,18 @@ int32_t launch_saved(ag_sampler *s, bool relaunch) {
         // once.  Making and sorting the keys is small, latency-bound work like the sampling
         // kernels: it stays on the (high-priority) sampling stream.  (The handle's previous
         // chain has finished — its event was waited for — so the sort scratch is free.)
-        if (sorted) AG_CUDA(launch_sort_keys(GatherArgs{}, s->gather_dev, n_batches, rows, feats, s->sort, st));
+        const uint64_t sort_rows = s->est_rows_tight ? std::min(rows, s->est_rows_tight) : rows;  // less padding to sort
+        if (sorted) AG_CUDA(launch_sort_keys(GatherArgs{}, s->gather_dev, n_batches, sort_rows, feats, s->sort, st));
         // sampling chain -> event -> gather on the low-priority stream -> event -> caller's stream
         AG_CUDA(cudaEventRecord(s->sampled, st));
         AG_CUDA(cudaStreamWaitEvent(s->gstream, s->sampled, 0));
         if (s->profile) AG_CUDA(cudaEventRecord(s->ev[2], s->gstream));
         if (sorted) {
-            AG_CUDA(launch_sorted_fetch(GatherArgs{}, s->gather_dev, n_batches, rows, row_bytes, (uint32_t)feats->dim,
-                                        feats->dtype, feats, s->sort, s->gstream));
+            AG_CUDA(cudaStreamWaitEvent(s->rstream, s->sampled, 0));
+            AG_CUDA(launch_sorted_fetch(GatherArgs{}, s->gather_dev, n_batches, sort_rows, row_bytes, (uint32_t)feats->dim,
+                                        feats->dtype, feats, s->sort, s->gstream, s->rstream));
+            AG_CUDA(cudaEventRecord(s->remote_done, s->rstream));
+            AG_CUDA(cudaStreamWaitEvent(s->gstream, s->remote_done, 0));
         } else {
             AG_CUDA(launch_gather_group(s->gather_dev, n_batches, row_bytes, (uint32_t)feats->dim, rows, aligned,
                                         feats->dtype, feats->shards != nullptr, s->gstream));
@@ -1276,6 +1289,7 @@ extern "C" int32_t ag_sample_group_wait(ag_sampler *s, ag_sample_counts *counts,
             mx_items[h + 1] = std::max<uint64_t>(mx_items[h + 1], c.edges_per_hop[h]);
     }
     s->est_nodes = mx_nodes + mx_nodes / 4 + 256;
+    s->est_rows_tight = mx_nodes + mx_nodes / 16 + 64;
     for (uint32_t h = 1; h <= s->cfg.num_hops; ++h) s->est_items[h] = mx_items[h] + mx_items[h] / 4 + 512;
     int32_t first = AG_OK;
     for (uint32_t b = 0; b < s->in_flight_n; ++b) {

@@ -29,8 +29,8 @@ namespace {
 
 bool is_cyclic(const ag_features *f) { return f->row_stride > 1; }
 
-int32_t make_view(const ag_features *local, uint32_t world, bool cyclic, const uint8_t *const *bases, void *const *opened,
-                  ag_features **out) {
+int32_t make_view(const ag_features *local, uint32_t world, uint32_t rank, bool cyclic, const uint8_t *const *bases,
+                  void *const *opened, ag_features **out) {
     const uint64_t n = local->num_nodes;
     const uint64_t shard_rows = (n + world - 1) / world;
     ag_features *v = new ag_features();
@@ -48,6 +48,9 @@ int32_t make_view(const ag_features *local, uint32_t world, bool cyclic, const u
     for (uint32_t r = 0; r < world; ++r) t.base[r] = bases[r];
     t.shard_rows = std::max<uint64_t>(shard_rows, 1);
     t.n_shards = world;
+    t.n_sources = world;
+    t.self = rank;
+    t.hot_slot = nullptr;
     t.cyclic = cyclic ? 1u : 0u;
     if (cudaMalloc(&v->err, 32) != cudaSuccess || cudaMemset(v->err, 0, 32) != cudaSuccess ||
         cudaMalloc(&v->shards, sizeof(ag_shard_table)) != cudaSuccess ||
@@ -121,7 +124,7 @@ extern "C" int32_t ag_features_open_sharded(const ag_features *local, uint32_t w
         }
         opened[r] = p; bases[r] = (const uint8_t *)p;
     }
-    const int32_t st = make_view(local, world, cyclic, bases, opened, out);
+    const int32_t st = make_view(local, world, rank, cyclic, bases, opened, out);
     if (st != AG_OK) for (void *q : opened) if (q) cudaIpcCloseMemHandle(q);
     return st;
 }
@@ -150,5 +153,5 @@ extern "C" int32_t ag_features_view_sharded(const ag_features *const *shards, ui
         if (e == cudaErrorPeerAccessAlreadyEnabled) cudaGetLastError();
         else if (e != cudaSuccess) return fail(AG_ERR_CUDA, "enabling peer access to GPU %d failed: %s", shards[r]->device, cudaGetErrorString(e));
     }
-    return make_view(local, world, is_cyclic(local), bases, nullptr, out);
+    return make_view(local, world, rank, is_cyclic(local), bases, nullptr, out);
 }

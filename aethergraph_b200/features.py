@@ -205,12 +205,28 @@ class FeatureStore:
                                         None, out.data_ptr() if n else None, st))
         return out
 
-    def gather_stats(self) -> tuple[int, int]:
-        """Sharded views: `(rows requested, rows loaded)` by the address-ordered gathers
-        so far; the difference is rows that several batches of one launch chain named."""
-        a, b = C.c_uint64(), C.c_uint64()
-        _lib.check(_lib.lib().ag_features_gather_stats(self._h, C.byref(a), C.byref(b)))
-        return a.value, b.value
+    def gather_stats(self) -> tuple[int, int, int]:
+        """Sharded views: `(rows requested, rows loaded, rows loaded from the local copy of
+        the hot rows)` by the address-ordered gathers so far; requested - loaded is rows that
+        several batches of one launch chain named."""
+        a, b, c = C.c_uint64(), C.c_uint64(), C.c_uint64()
+        _lib.check(_lib.lib().ag_features_gather_stats(self._h, C.byref(a), C.byref(b), C.byref(c)))
+        return a.value, b.value, c.value
+
+    def cache_hot_rows(self, graph, max_bytes: int = 1 << 30) -> int:
+        """Sharded views: keep a copy of the rows of the highest in-degree vertices of
+        `graph` in this GPU's memory, `max_bytes` of them at most, and serve them from
+        there (only the remaining rows cross NVLink).  Returns the number of rows copied."""
+        row = self._dim * (4 if self._dtype == _lib.AG_F32 else 2)
+        want = int(max_bytes) // max(row, 1)
+        ids, n = C.c_void_p(), C.c_uint64()
+        _lib.check(_lib.lib().ag_graph_hot_vertices(graph._h, want, C.byref(ids), C.byref(n)))
+        try:
+            _lib.check(_lib.lib().ag_features_cache_rows(self._h, ids, n.value))
+        finally:
+            if ids.value:
+                _lib.lib().ag_synth_free_device(ids, self._device)
+        return n.value
 
     def check(self) -> None:
         """Raise ValueError if a device gather since the last check saw an out-of-range id."""

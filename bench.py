@@ -272,7 +272,34 @@ class ResidentLeg:
         # One thread both submits and consumes, so it must never block in submit:
         # keep no more batches outstanding than the loader's work queue (8 x depth) holds.
         self.window = min(8 * depth, depth + threads * group + group)
-        self.ring = [_Buffers.alloc(dev, mn.value, me.value, bs, True, w["dim"]) for _ in range(self.window)]
+        # The caller owns the output buffers and sizes them: the worst-case bound of a batch
+        # (every pick a new vertex) is many times what this workload's batches produce, so a
+        # first chain in full-size buffers measures them and the ring gets twice that.  A batch
+        # that outgrew its buffers would come back as an error, not silently cut.
+        cap_n, cap_e = self.mn, self.me
+        probe_n = min(group, len(gidx))
+        if probe_n and not w.get("full_size_buffers"):
+            probe = [_Buffers.alloc(dev, self.mn, self.me, bs, True, w["dim"]) for _ in range(probe_n)]
+            base0 = seeds_dev.data_ptr()
+            idx = (C.c_int64 * probe_n)(*gidx[:probe_n])
+            ptr = (C.c_void_p * probe_n)(*[base0 + 4 * bs * i for i in range(probe_n)])
+            ln = (C.c_uint64 * probe_n)(*([bs] * probe_n))
+            bufs = (_lib.SubgraphBuffers * probe_n)(*[b.c for b in probe])
+            _lib.check(L.ag_loader_submit_many(self.h, probe_n, idx, ptr, ln, _lib.AG_MEM_DEVICE, bufs, None, None))
+            got, seen_n, seen_e = 0, 0, 0
+            out = (_lib.Batch * 64)()
+            n_out = C.c_uint32()
+            while got < probe_n:
+                _lib.check(L.ag_loader_next_many(self.h, -1, 64, out, C.byref(n_out)))
+                for j in range(n_out.value):
+                    seen_n = max(seen_n, out[j].counts.num_nodes)
+                    seen_e = max(seen_e, out[j].counts.num_edges)
+                got += n_out.value
+            cap_n = min(self.mn, 2 * seen_n + 4096)
+            cap_e = min(self.me, 2 * seen_e + 4096)
+            del probe
+        self.cap_n, self.cap_e = cap_n, cap_e
+        self.ring = [_Buffers.alloc(dev, cap_n, cap_e, bs, True, w["dim"]) for _ in range(self.window)]
         R = self.R = len(self.ring)
         n_batches = len(gidx)
         base = seeds_dev.data_ptr()
@@ -402,8 +429,33 @@ def run_device(args, w):
         from aethergraph_b200 import dist as agd
 
         layout = "range" if layout_flag == "sharded-range" else "cyclic"
+        if world == 1:
+            # one GPU: eight shards that all live here — the sharded code path (keys, sort,
+            # address-ordered fetch) without a link, for profiling the kernels under ncu
+            parts = [synth.features_shard(w["nodes"], w["dim"], w["dtype"], FEATURE_SEED, r, 8, layout) for r in range(8)]
+            return ag.FeatureStore.view_sharded(parts, 0)
         shard = synth.features_shard(w["nodes"], w["dim"], w["dtype"], FEATURE_SEED, rank, world, layout)
         return agd.open_sharded_features(shard)
+
+    def sharded_leg(view, layout_flag: str, replicated, cache_gb: float, repeats: int):
+        """One resident leg over the sharded view, with `cache_gb` GiB of hot rows copied to
+        every GPU first (0: none).  Returns the record."""
+        cached_rows = view.cache_hot_rows(g, int(cache_gb * (1 << 30))) if cache_gb > 0 else view.cache_hot_rows(g, 0)
+        barrier()
+        lg = ResidentLeg(L, _lib, g, view, ccfg, dev, w, threads_sh, group_sh, depth_sh, seeds_dev, gidx, rank, world)
+        lg.run(0, first_timed)
+        barrier()
+        st0 = view.gather_stats()
+        runs_s = timed_repeats(lg.run, first_timed, n_timed, repeats, barrier, max_over_ranks, sum_over_ranks)
+        st1 = view.gather_stats()
+        rec = sharded_summary(w, world, median_run(runs_s), stored_row, lg, view, replicated, dev, sum_over_ranks,
+                              layout_flag, args.steps, [a - b for a, b in zip(st1, st0)], sum(r[0] for r in runs_s))
+        rec["hot_rows_copied_per_gpu"] = int(cached_rows)
+        rec["hot_rows_gib_per_gpu"] = cached_rows * stored_row / float(1 << 30)
+        rec["impl_config"] = {"sampler_threads": threads_sh, "group": group_sh, "prefetch_depth": depth_sh}
+        lg.close()
+        barrier()
+        return rec
 
     def features_label(layout_flag: str) -> str:
         if layout_flag == "replicated" or world == 1:
@@ -414,8 +466,10 @@ def run_device(args, w):
     # ---- inputs, resident in HBM (CSR replicated per GPU) -------------------
     t_setup = time.time()
     g = synth.rmat_graph(w["nodes"], w["edges"], GRAPH_SEED, weight_sigma=1.0 if w["weighted"] else 0.0)
-    feats = open_shards(main_layout) if (main_layout != "replicated" and world > 1) else \
+    feats = open_shards(main_layout) if main_layout != "replicated" else \
         synth.features(w["nodes"], w["dim"], w["dtype"], FEATURE_SEED)
+    if main_layout != "replicated" and args.hot_cache_gb > 0:
+        feats.cache_hot_rows(g, int(args.hot_cache_gb * (1 << 30)))
     torch.cuda.synchronize()
     t_setup = time.time() - t_setup
     cfg = ag.SamplingConfig(num_neighbors=w["fanout"], seed=SAMPLER_SEED, weighted=w["weighted"])
@@ -429,6 +483,10 @@ def run_device(args, w):
     threads = args.threads or int(w.get("threads", 3))
     group = args.group or int(w.get("group", 32))
     depth = args.depth or int(w.get("depth", max(8, group // 2)))
+    # sharded legs: remote rows have a longer way, so more chains are kept in flight
+    threads_sh = args.threads or int(w.get("threads_sharded", w.get("threads", 4)))
+    group_sh = args.group or int(w.get("group_sharded", w.get("group", 64)))
+    depth_sh = args.depth or int(w.get("depth", max(8, group_sh // 2)))
     ccfg = cfg._to_c(SAMPLER_SEED, bs)
     row_bytes = gather_bytes_per_row(w)
     stored_row = sector(w["dim"] * (4 if w["dtype"] == "f32" else 2))
@@ -501,11 +559,18 @@ def run_device(args, w):
                                      "working set per launch exceeds L2"}
         del ids, x_alone
         barrier()
-    sharded_main = None
-    if main_layout != "replicated" and world > 1:
-        sharded_main = sharded_summary(w, world, med, stored_row, leg, feats, None, dev, sum_over_ranks, main_layout, args.steps)
     leg.close()
     del leg
+    sharded_main = None
+    if main_layout != "replicated" and world > 1:
+        sharded_main = sharded_leg(feats, main_layout, None, args.hot_cache_gb, max(1, min(args.repeats, 3)))
+        nc = sharded_leg(feats, main_layout, None, 0.0, 1)   # the same without the hot-row copy
+        sharded_main["without_hot_rows"] = {k: nc[k] for k in ("value", "ms_per_step", "remote_gbs_per_gpu",
+                                                               "frac_of_peer_copy_peak", "rows_loaded_per_row_requested",
+                                                               "parity")}
+        if args.hot_cache_gb > 0:
+            feats.cache_hot_rows(g, int(args.hot_cache_gb * (1 << 30)))
+        barrier()
 
     # ---- e2e: public Python API, host seeds in, counts back -----------------
     e2e_med = host_med = None
@@ -575,16 +640,13 @@ def run_device(args, w):
     sharded = sharded_main
     if world > 1 and main_layout == "replicated" and not args.only_value and not args.no_sharded:
         view = open_shards("sharded")
-        leg2 = ResidentLeg(L, _lib, g, view, ccfg, dev, w, threads, group, depth, seeds_dev, gidx, rank, world)
-        leg2.run(0, first_timed)
-        runs2 = timed_repeats(leg2.run, first_timed, n_timed, max(1, min(args.repeats, 3)), barrier, max_over_ranks,
-                              sum_over_ranks)
-        sharded = sharded_summary(w, world, median_run(runs2), stored_row, leg2, view, feats, dev, sum_over_ranks, "sharded",
-                                  args.steps)
+        sharded = sharded_leg(view, "sharded", feats, args.hot_cache_gb, max(1, min(args.repeats, 3)))
         sharded["vs_replicated"] = sharded["value"] / value if value else None
-        leg2.close()
+        nc = sharded_leg(view, "sharded", feats, 0.0, 1)   # the same without the hot-row copy: every remote row crosses NVLink
+        sharded["without_hot_rows"] = {k: nc[k] for k in ("value", "ms_per_step", "remote_gbs_per_gpu", "frac_of_peer_copy_peak",
+                                                          "rows_loaded_per_row_requested", "parity")}
         barrier()  # no rank frees its shard while a peer may still be reading it
-        del leg2, view
+        del view
         barrier()
 
     secondary = None
@@ -635,7 +697,8 @@ def run_device(args, w):
         dist.destroy_process_group()
 
 
-def sharded_summary(w, world, med, stored_row, leg, view, replicated, dev, sum_over_ranks, layout_flag, steps):
+def sharded_summary(w, world, med, stored_row, leg, view, replicated, dev, sum_over_ranks, layout_flag, steps,
+                    stats_delta, total_ms):
     """The record of a leg over sharded features: throughput, the remote share of the
     stored rows as GB/s per GPU against the measured peer-copy bandwidth, and a bit
     for bit check of the last delivered batch's rows (most of them remote) against the
@@ -647,7 +710,10 @@ def sharded_summary(w, world, med, stored_row, leg, view, replicated, dev, sum_o
 
     ms = med["ms"]
     remote_share = (world - 1) / world
-    remote_gbs = med["nodes"] * stored_row * remote_share / (ms * 1e-3) / 1e9 / world
+    asked, loaded, from_copy = stats_delta   # this rank, all timed repeats
+    # rows that really crossed NVLink: loaded once per chain, not served by the local copy of the
+    # hot rows, and (round-robin or range shards alike) owned by a peer with probability (W - 1) / W
+    remote_gbs = (loaded - from_copy) * remote_share * stored_row / (total_ms * 1e-3) / 1e9 if total_ms else 0.0
     ok, checked = True, 0
     if leg.recent:
         holder = _Buffers(leg.ring[0].c, leg.ring, dev, w["dim"])
@@ -669,7 +735,6 @@ def sharded_summary(w, world, med, stored_row, leg, view, replicated, dev, sum_o
                 ok = ok and bool(torch.equal(x[pos].view(torch.int32), want[0].view(torch.int32)))
                 checked += 1
         del holder
-    asked, loaded = view.gather_stats()
     ok_all = sum_over_ranks(1.0 if ok else 0.0) == float(world)
     return {"layout": "contiguous vertex ranges" if layout_flag == "sharded-range" else "round-robin by vertex id",
             "value": med["value"], "unit": "edges/s", "ms_per_step": ms / max(steps, 1),
@@ -677,9 +742,10 @@ def sharded_summary(w, world, med, stored_row, leg, view, replicated, dev, sum_o
             "gather_gbs": med["nodes"] * gather_bytes_per_row(w) / (ms * 1e-3) / 1e9,
             "remote_gbs_per_gpu": remote_gbs, "frac_of_peer_copy_peak": remote_gbs / NVLINK_PEER_COPY_GBS,
             "peer_copy_peak_gbs": NVLINK_PEER_COPY_GBS,
-            "remote_note": "stored row bytes of the remote share of the gathered rows (as if no row were fetched "
-                           "twice) per second and GPU; rows named by several batches of a chain cross the link once",
+            "remote_note": "stored bytes of the rows rank 0 fetched from its peers per second: rows loaded (once per "
+                           "launch chain) less the ones served by the local copy of the hot rows, times (W - 1) / W",
             "rows_loaded_per_row_requested": (loaded / asked) if asked else None,
+            "rows_from_hot_copy_per_row_loaded": (from_copy / loaded) if loaded else None,
             "parity": bool(ok_all), "parity_rows_checked_per_rank": checked}
 
 
@@ -972,6 +1038,8 @@ def main():
     ap.add_argument("--brief", action="store_true",
                     help="value, cpu_baseline and parity only (what a secondary workload reports)")
     ap.add_argument("--no-sharded", action="store_true", help="2 or more GPUs: skip the sharded-features record")
+    ap.add_argument("--hot-cache-gb", type=float, default=1.0,
+                    help="sharded features: GiB of the hottest rows (highest in-degree) copied to every GPU (0: none)")
     ap.add_argument("--no-secondary", action="store_true", help="1 GPU: skip the secondary workloads (C1, C3, C4 at 1/10)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--only-value", action="store_true",

@@ -170,10 +170,27 @@ int32_t ag_features_view_sharded(const ag_features *const *shards, uint32_t worl
  * order, a row named more than once only once — the counterpart of the
  * reference's request coalescing in its one-sided remote gather
  * (crates/aether-stream/src/rdma/sharded.rs:1-33, rdma/gather.rs:1-9).  The
- * counters say how many rows such gathers were asked for and how many they
- * loaded (the rest were repeats within a launch), since the view was opened. */
+ * counters say how many rows such gathers were asked for, how many they loaded
+ * (the rest were repeats within a launch) and how many of the loaded ones came
+ * from the local copy of the hot rows, since the view was opened (or since
+ * ag_features_cache_rows). */
 int32_t ag_features_gather_stats(const ag_features *f, uint64_t *rows_requested,
-                                 uint64_t *rows_fetched);
+                                 uint64_t *rows_fetched, uint64_t *rows_local_copy);
+/* Hot rows.  On a skewed graph a small share of the vertices receives most of the
+ * row requests (a vertex is gathered in proportion to its in-degree).
+ * ag_graph_hot_vertices returns the `max_rows` vertices of highest in-degree,
+ * hottest first, as a device array (free it with ag_synth_free_device);
+ * ag_features_cache_rows copies the stored rows of such a list into this GPU's
+ * memory and lets the sharded view serve them locally, so only the cold rows
+ * cross NVLink.  Same bits either way; nothing to keep coherent, the rows never
+ * change.  Counterpart: the GPU-resident hot tier of the reference's feature
+ * cache, which pins the hottest nodes when frequencies are known
+ * (crates/aethergraph-core/src/features/cache/mod.rs:1-20), in front of its
+ * remote gather (crates/aether-stream/src/rdma/sharded.rs:1-33).  No gather over
+ * the view may run while ag_features_cache_rows does. */
+int32_t ag_graph_hot_vertices(const ag_graph *g, uint64_t max_rows, uint32_t **ids_dev,
+                              uint64_t *n_out);
+int32_t ag_features_cache_rows(ag_features *view, const uint32_t *ids_dev, uint64_t n);
 /* Copies the stored (encoded) rows held by this handle back to host memory. */
 int32_t ag_features_copy_to_host(const ag_features *f, void *payload);
 

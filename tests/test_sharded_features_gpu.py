@@ -254,3 +254,52 @@ def test_c5_shaped_batch_over_eight_shards():
     xw = ago.gather(payload, n, 128, "bf16", want["nodes"])
     assert np.array_equal(sg.x.cpu().numpy().view(np.uint32), xw.view(np.uint32))
     assert len(want["nodes"]) > 20_000
+
+
+@pytest.mark.parametrize("layout,dtype,dim", [("cyclic", "bf16", 64), ("range", "f16", 24), ("cyclic", "f32", 5)])
+def test_hot_rows_copy_serves_the_same_bits(layout, dtype, dim):
+    """A sharded view with a local copy of the highest in-degree rows returns the same
+    rows as without one, through the address-ordered gather (large id lists), the
+    plain one (short lists, odd row sizes) and the loader; the counters tell the copy's
+    share; the hot list is the in-degree order of the graph."""
+    import torch
+
+    import aethergraph_b200 as ag
+    from aethergraph_b200 import synth
+    from oracle import ago
+
+    n, off, dst, _ = rmat_csr(13, 12, seed=6)
+    g = ag.Graph.from_csr(off, dst)
+    world = 4
+    shards = [synth.features_shard(n, dim, dtype, 23, r, world, layout) for r in range(world)]
+    view = ag.FeatureStore.view_sharded(shards, 1)
+    payload = ago.synth_features(n, dim, dtype, 23)
+    row = dim * (4 if dtype == "f32" else 2)
+    copied = view.cache_hot_rows(g, 300 * row)
+    indeg = np.bincount(dst, minlength=n)
+    assert copied == min(300, int((indeg > 0).sum()))
+    rng = np.random.default_rng(3)
+    hot = np.argsort(-indeg, kind="stable")[:copied]
+    ids = np.concatenate([rng.integers(0, n, 5000), hot, hot[:50], [0, n - 1]])
+    rng.shuffle(ids)
+    want = ago.gather(payload, n, dim, dtype, ids.astype(np.uint32))
+    got = view.gather(torch.from_numpy(ids).cuda())
+    assert np.array_equal(got.cpu().numpy().view(np.uint32), want.view(np.uint32))
+    short = view.gather(torch.from_numpy(ids[:100]).cuda())
+    assert np.array_equal(short.cpu().numpy().view(np.uint32), want[:100].view(np.uint32))
+    asked, loaded, from_copy = view.gather_stats()
+    if row % 16 == 0:
+        assert asked == len(ids) and loaded <= asked and from_copy >= copied * 0.9  # every hot row was asked for
+        # rows the degree order puts in the copy are served from it
+        assert from_copy <= loaded
+    s = ago.Sampler(off, dst, [8, 4], seed=2)
+    seeds = rng.integers(0, n, 256).astype(np.uint32)
+    sg = ag.NeighborSampler(g, ag.SamplingConfig(num_neighbors=[8, 4], seed=2), features=view).sample(seeds)
+    w = s.sample(seeds)
+    assert np.array_equal(sg.raw_u32()["nodes"], w["nodes"])
+    assert np.array_equal(sg.x.cpu().numpy().view(np.uint32), ago.gather(payload, n, dim, dtype, w["nodes"]).view(np.uint32))
+    # dropping the copy gives the plain view back
+    assert view.cache_hot_rows(g, 0) == 0
+    got = view.gather(torch.from_numpy(ids).cuda())
+    assert np.array_equal(got.cpu().numpy().view(np.uint32), want.view(np.uint32))
+    assert view.gather_stats()[2] == 0
