@@ -87,6 +87,13 @@ class HeteroCounts(C.Structure):
                 ("total_edges", C.c_uint32), ("draws", C.c_uint64)]
 
 
+class HeteroNames(C.Structure):
+    _fields_ = [("num_node_types", C.c_uint32), ("num_edge_types", C.c_uint32),
+                ("node_type", (C.c_char * 64) * AG_MAX_NODE_TYPES),
+                ("src", (C.c_char * 64) * AG_MAX_EDGE_TYPES), ("rel", (C.c_char * 64) * AG_MAX_EDGE_TYPES),
+                ("dst", (C.c_char * 64) * AG_MAX_EDGE_TYPES)]
+
+
 class HeteroBatch(C.Structure):
     _fields_ = [("batch_idx", C.c_int64), ("seq", C.c_uint64), ("bufs", HeteroBuffers), ("counts", HeteroCounts)]
 
@@ -165,6 +172,8 @@ SIGNATURES = {
     "ag_hetero_sampler_free": (None, [_P]),
     "ag_loader_create": (C.c_int32, [_P, _P, C.POINTER(SamplingConfigC), C.c_int32, C.c_uint32, C.c_uint32,
                                      C.c_uint32, C.c_int32, _PP]),
+    "ag_hetero_load": (C.c_int32, [C.c_char_p, C.c_int32, _PP, C.POINTER(HeteroNames)]),
+    "ag_hetero_save": (C.c_int32, [_P, C.POINTER(HeteroNames), C.c_char_p]),
     "ag_loader_set_seed_sequence": (C.c_int32, [_P, C.c_uint64, C.c_uint64]),
     "ag_loader_bounds": (C.c_int32, [_P, C.c_uint64, _U64P, _U64P]),
     "ag_loader_submit": (C.c_int32, [_P, C.c_int64, _P, C.c_uint64, C.c_int32, C.POINTER(SubgraphBuffers), _P]),

@@ -8,6 +8,8 @@
 #include <unistd.h>
 
 #include <algorithm>
+#include <atomic>
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -25,6 +27,18 @@ void set_error(const char *fmt, ...) {
     va_end(ap);
 }
 
+int sm_count() {
+    static std::atomic<int> cache[64];  // 0: not read yet
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    int n = cache[dev].load(std::memory_order_relaxed);
+    if (n == 0) {
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cache[dev].store(n, std::memory_order_relaxed);
+    }
+    return n;
+}
+
 int32_t fail(int32_t status, const char *fmt, ...) {
     va_list ap;
     va_start(ap, fmt);
@@ -39,8 +53,8 @@ namespace {
 // (reference: internal/mmap.rs:642-652).
 uint32_t crc32_update(uint32_t crc, const void *data, size_t len) {
     static uint32_t table[8][256];
-    static bool ready = false;
-    if (!ready) {
+    static std::once_flag built;  // graphs may be loaded and saved from several threads at once
+    std::call_once(built, [] {
         for (uint32_t i = 0; i < 256; ++i) {
             uint32_t c = i;
             for (int k = 0; k < 8; ++k) c = (c & 1u) ? 0xEDB88320u ^ (c >> 1) : c >> 1;
@@ -48,8 +62,7 @@ uint32_t crc32_update(uint32_t crc, const void *data, size_t len) {
         }
         for (uint32_t i = 0; i < 256; ++i)
             for (int t = 1; t < 8; ++t) table[t][i] = table[0][table[t - 1][i] & 0xFF] ^ (table[t - 1][i] >> 8);
-        ready = true;
-    }
+    });
     const uint8_t *p = (const uint8_t *)data;
     crc = ~crc;
     while (len >= 8) {  // slicing-by-8
@@ -182,17 +195,18 @@ int write_all(int fd, const void *buf, uint64_t bytes) {
 // Writes go to a sibling temporary that is fsynced and renamed over the target
 // (reference: internal/mmap.rs:38-87, features/store.rs:923-986).
 struct AtomicFile {
-    std::string path, tmp;
+    std::string path, tmp, parent;
     int fd = -1;
     bool open_tmp(const char *target) {
         path = target;
-        static int seq = 0;
+        static std::atomic<int> seq{0};
         std::string dir = ".", name = path;
         const size_t slash = path.find_last_of('/');
         if (slash != std::string::npos) { dir = path.substr(0, slash); name = path.substr(slash + 1); if (dir.empty()) dir = "/"; }
         char suffix[64];
         snprintf(suffix, sizeof suffix, ".tmp.%d.%d", (int)getpid(), seq++);
         tmp = dir + "/." + name + suffix;
+        parent = dir;
         fd = open(tmp.c_str(), O_WRONLY | O_CREAT | O_EXCL, 0644);
         return fd >= 0;
     }
@@ -200,8 +214,11 @@ struct AtomicFile {
         bool ok = fsync(fd) == 0;
         close(fd); fd = -1;
         if (ok) ok = rename(tmp.c_str(), path.c_str()) == 0;
-        if (!ok) unlink(tmp.c_str());
-        return ok;
+        if (!ok) { unlink(tmp.c_str()); return false; }
+        // the rename itself becomes durable with the directory (internal/mmap.rs:33-87)
+        const int dfd = open(parent.c_str(), O_RDONLY | O_DIRECTORY);
+        if (dfd >= 0) { fsync(dfd); close(dfd); }
+        return true;
     }
     void abort() { if (fd >= 0) { close(fd); fd = -1; unlink(tmp.c_str()); } }
 };
@@ -210,6 +227,253 @@ constexpr uint32_t kGraphMagic = 0x41455448u;  // "AETH" (internal/mmap.rs:20)
 constexpr uint64_t kMaxEdges = 100000000000ull;  // internal/mmap.rs:31
 constexpr uint64_t kFullValidationBytes = 512ull << 20;  // internal/mmap.rs:27
 
+
+// ------------------------------------------------ AETHHETG v1 (hetero graphs) --
+// The reference's multi-relational file (internal/mmap_hetero.rs:1-45): 64-byte
+// header ("AETHHETG", version, type counts), node type table (64-byte name + u64
+// count), edge type table (three 64-byte names, u64 source count, u64 edge count,
+// u32 has_weights, u32 pad), then per edge type its CSR over the source type:
+// u64 offsets, u32 destinations and optional f32 weights, the u32 sections padded
+// to 8 bytes.  Like the reference's loader (mmap_hetero.rs:161-330) every size is
+// checked against the file length with overflow-checked arithmetic before anything
+// is read, names must be NUL-terminated, and each relation is proven in full
+// (offsets start at 0, never decrease, end at the edge count; every destination
+// below its destination type's count) — here on the device, after the sections
+// were streamed into HBM.
+constexpr uint64_t kHetHeader = 64, kHetNodeEntry = 72, kHetEdgeEntry = 216, kHetFormatTypes = 256;
+constexpr uint64_t kHetMaxNodes = 0xFFFFFFFFull;
+
+uint64_t pad8(uint64_t len) { return (0 - len) & 7; }
+
+bool checked_add(uint64_t a, uint64_t b, uint64_t *out) { *out = a + b; return *out >= a; }
+bool checked_mul(uint64_t a, uint64_t b, uint64_t *out) {
+    if (a != 0 && b > 0xFFFFFFFFFFFFFFFFull / a) return false;
+    *out = a * b;
+    return true;
+}
+
+// A 64-byte name field: NUL-terminated, zero-padded (mmap_hetero.rs:73-81).
+bool read_name(const uint8_t *field, char *out) {
+    const void *nul = memchr(field, 0, 64);
+    if (!nul) return false;
+    memset(out, 0, 64);
+    memcpy(out, field, (const uint8_t *)nul - field);
+    return true;
+}
+
+__global__ void k_in_adjacency_keys(const uint64_t *in_offsets, const uint32_t *in_sources, uint64_t num_dst, uint64_t e,
+                                    uint64_t *keys) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < e; i += (uint64_t)gridDim.x * blockDim.x) {
+        // destination of stored position i = the row of the transposed adjacency that holds it
+        uint64_t lo = 0, hi = num_dst;  // invariant: in_offsets[lo] <= i < in_offsets[hi]
+        while (hi - lo > 1) {
+            const uint64_t mid = (lo + hi) / 2;
+            if (in_offsets[mid] <= i) lo = mid; else hi = mid;
+        }
+        keys[i] = ((uint64_t)in_sources[i] << 32) | lo;
+    }
+}
+
+}  // namespace
+}  // namespace ag
+
+using namespace ag;
+
+extern "C" int32_t ag_hetero_load(const char *path, int32_t device, ag_hetero_graph **out, ag_hetero_names *names) {
+    if (!path || !out || !names) return fail(AG_ERR_VALUE, "ag_hetero_load: null argument");
+    const int fd = open(path, O_RDONLY);
+    if (fd < 0) return fail(AG_ERR_LOAD, "failed to open hetero graph file %s: %s", path, strerror(errno));
+    struct stat sb;
+    if (fstat(fd, &sb) != 0) { close(fd); return fail(AG_ERR_LOAD, "failed to stat %s", path); }
+    const uint64_t file_len = (uint64_t)sb.st_size;
+    int32_t st = AG_OK;
+    std::vector<uint8_t> tables;
+    uint8_t header[kHetHeader];
+    uint32_t num_nt = 0, num_et = 0;
+    uint64_t num_nodes[AG_MAX_NODE_TYPES] = {0}, num_edges[AG_MAX_EDGE_TYPES] = {0};
+    uint32_t src_type[AG_MAX_EDGE_TYPES] = {0}, dst_type[AG_MAX_EDGE_TYPES] = {0};
+    uint64_t off_at[AG_MAX_EDGE_TYPES] = {0}, dst_at[AG_MAX_EDGE_TYPES] = {0};
+    uint64_t *off_dev[AG_MAX_EDGE_TYPES] = {nullptr};
+    uint32_t *dst_dev[AG_MAX_EDGE_TYPES] = {nullptr};
+    uint32_t *flag = nullptr;
+    memset(names, 0, sizeof *names);
+    do {
+        if (file_len < kHetHeader) { st = fail(AG_ERR_LOAD, "file too small for header: %llu bytes", (unsigned long long)file_len); break; }
+        if (!read_exact(fd, header, kHetHeader, 0)) { st = fail(AG_ERR_LOAD, "failed to read the header"); break; }
+        if (memcmp(header, "AETHHETG", 8) != 0) { st = fail(AG_ERR_LOAD, "invalid magic (expected AETHHETG)"); break; }
+        uint32_t version;
+        memcpy(&version, header + 8, 4); memcpy(&num_nt, header + 12, 4); memcpy(&num_et, header + 16, 4);
+        if (version != 1) { st = fail(AG_ERR_LOAD, "hetero graph file format version %u is not supported by this build (max 1)", version); break; }
+        if (num_nt > kHetFormatTypes || num_et > kHetFormatTypes) {
+            st = fail(AG_ERR_LOAD, "type counts (%u node, %u edge) exceed the format limit of 256 - file is corrupt", num_nt, num_et);
+            break;
+        }
+        if (num_nt == 0 || num_nt > AG_MAX_NODE_TYPES || num_et > AG_MAX_EDGE_TYPES) {
+            st = fail(AG_ERR_LOAD, "the file holds %u node types and %u edge types; this build samples graphs of 1 to %d node types and "
+                      "at most %d edge types", num_nt, num_et, AG_MAX_NODE_TYPES, AG_MAX_EDGE_TYPES);
+            break;
+        }
+        const uint64_t tables_len = kHetHeader + num_nt * kHetNodeEntry + num_et * kHetEdgeEntry;
+        if (tables_len > file_len) {
+            st = fail(AG_ERR_LOAD, "file truncated: type tables need %llu bytes, file has %llu", (unsigned long long)tables_len, (unsigned long long)file_len);
+            break;
+        }
+        tables.resize(tables_len - kHetHeader);
+        if (!tables.empty() && !read_exact(fd, tables.data(), tables.size(), kHetHeader)) { st = fail(AG_ERR_LOAD, "failed to read the type tables"); break; }
+        const uint8_t *p = tables.data();
+        for (uint32_t t = 0; t < num_nt && st == AG_OK; ++t, p += kHetNodeEntry) {
+            if (!read_name(p, names->node_type[t])) { st = fail(AG_ERR_LOAD, "type name field has no NUL terminator - file is corrupt"); break; }
+            memcpy(&num_nodes[t], p + 64, 8);
+            if (num_nodes[t] > kHetMaxNodes)
+                st = fail(AG_ERR_LOAD, "node type '%s' count %llu exceeds maximum %llu - file is corrupt", names->node_type[t],
+                          (unsigned long long)num_nodes[t], (unsigned long long)kHetMaxNodes);
+        }
+        if (st != AG_OK) break;
+        uint64_t at = tables_len;
+        for (uint32_t e = 0; e < num_et && st == AG_OK; ++e, p += kHetEdgeEntry) {
+            if (!read_name(p, names->src[e]) || !read_name(p + 64, names->rel[e]) || !read_name(p + 128, names->dst[e])) {
+                st = fail(AG_ERR_LOAD, "type name field has no NUL terminator - file is corrupt");
+                break;
+            }
+            uint64_t ns;
+            uint32_t has_w;
+            memcpy(&ns, p + 192, 8); memcpy(&num_edges[e], p + 200, 8); memcpy(&has_w, p + 208, 4);
+            const char *rel = names->rel[e];
+            if (ns > kHetMaxNodes) { st = fail(AG_ERR_LOAD, "edge type '%s' num_src_nodes %llu exceeds maximum %llu - file is corrupt", rel, (unsigned long long)ns, (unsigned long long)kHetMaxNodes); break; }
+            if (num_edges[e] > kMaxEdges) { st = fail(AG_ERR_LOAD, "edge type '%s' num_edges %llu exceeds maximum %llu - file is corrupt", rel, (unsigned long long)num_edges[e], (unsigned long long)kMaxEdges); break; }
+            int s_id = -1, d_id = -1;
+            for (uint32_t t = 0; t < num_nt; ++t) {
+                if (s_id < 0 && strcmp(names->node_type[t], names->src[e]) == 0) s_id = (int)t;
+                if (d_id < 0 && strcmp(names->node_type[t], names->dst[e]) == 0) d_id = (int)t;
+            }
+            if (d_id < 0) { st = fail(AG_ERR_LOAD, "edge type '%s' names unknown destination type '%s' - file is corrupt", rel, names->dst[e]); break; }
+            if (s_id < 0) { st = fail(AG_ERR_LOAD, "edge type '%s' names unknown source type '%s' - file is corrupt", rel, names->src[e]); break; }
+            if (ns != num_nodes[s_id]) {
+                st = fail(AG_ERR_LOAD, "edge type '%s' has %llu source rows but node type '%s' holds %llu nodes", rel, (unsigned long long)ns,
+                          names->src[e], (unsigned long long)num_nodes[s_id]);
+                break;
+            }
+            src_type[e] = (uint32_t)s_id; dst_type[e] = (uint32_t)d_id;
+            uint64_t off_bytes, edge_bytes, end;
+            if (!checked_mul(ns + 1, 8, &off_bytes) || !checked_mul(num_edges[e], 4, &edge_bytes)) { st = fail(AG_ERR_LOAD, "section size overflows for edge type '%s'", rel); break; }
+            auto take = [&](uint64_t len, const char *what) {
+                if (!checked_add(at, len, &end)) { st = fail(AG_ERR_LOAD, "section size overflows for edge type '%s'", rel); return false; }
+                if (end > file_len) {
+                    st = fail(AG_ERR_LOAD, "file truncated: %s section of edge type '%s' needs bytes %llu..%llu, file has %llu", what, rel,
+                              (unsigned long long)at, (unsigned long long)end, (unsigned long long)file_len);
+                    return false;
+                }
+                at = end;
+                return true;
+            };
+            off_at[e] = at;
+            if (!take(off_bytes, "offsets")) break;
+            dst_at[e] = at;
+            if (!take(edge_bytes, "edges")) break;
+            at += pad8(edge_bytes);
+            if (has_w) {  // weights are validated for size and skipped: hetero sampling is uniform (hetero_sampler.rs:36-39)
+                if (!take(edge_bytes, "weights")) break;
+                at += pad8(edge_bytes);
+            }
+            if (at > file_len) { st = fail(AG_ERR_LOAD, "file truncated: section padding of edge type '%s' extends past EOF", rel); break; }
+        }
+        if (st != AG_OK) break;
+        DeviceGuard guard(device);
+        if (!guard.ok) { st = AG_ERR_CUDA; break; }
+        if (cudaMalloc(&flag, 4) != cudaSuccess) { st = fail(AG_ERR_CUDA, "out of device memory"); break; }
+        for (uint32_t e = 0; e < num_et && st == AG_OK; ++e) {
+            const uint64_t ns = num_nodes[src_type[e]], E = num_edges[e];
+            if (cudaMalloc(&off_dev[e], (ns + 1) * 8) != cudaSuccess || cudaMalloc(&dst_dev[e], std::max<uint64_t>(E, 1) * 4) != cudaSuccess) {
+                st = fail(AG_ERR_CUDA, "out of device memory for edge type '%s'", names->rel[e]);
+                break;
+            }
+            if ((st = stream_to_device(fd, off_at[e], (ns + 1) * 8, off_dev[e], nullptr)) != AG_OK) break;
+            if (E && (st = stream_to_device(fd, dst_at[e], E * 4, dst_dev[e], nullptr)) != AG_OK) break;
+            cudaMemset(flag, 0, 4);
+            uint32_t hflag = 0;
+            cudaError_t ce = launch_validate_csr(off_dev[e], dst_dev[e], ns, E, num_nodes[dst_type[e]], flag, 0);
+            if (ce == cudaSuccess) ce = cudaMemcpy(&hflag, flag, 4, cudaMemcpyDeviceToHost);
+            if (ce != cudaSuccess) { st = fail(AG_ERR_CUDA, "validation of edge type '%s' failed to run: %s", names->rel[e], cudaGetErrorString(ce)); break; }
+            if (hflag & 1u) st = fail(AG_ERR_LOAD, "edge type '%s': offsets[0] != 0", names->rel[e]);
+            else if (hflag & 2u) st = fail(AG_ERR_LOAD, "edge type '%s': offsets[num_src_nodes] != num_edges", names->rel[e]);
+            else if (hflag & 4u) st = fail(AG_ERR_LOAD, "edge type '%s': offsets are not non-decreasing", names->rel[e]);
+            else if (hflag & 8u) st = fail(AG_ERR_LOAD, "edge type '%s': a destination is >= the count of node type '%s'", names->rel[e], names->dst[e]);
+        }
+        if (st != AG_OK) break;
+        names->num_node_types = num_nt; names->num_edge_types = num_et;
+        st = ag_hetero_create(num_nt, num_nodes, num_et, src_type, dst_type, (const uint64_t *const *)off_dev, nullptr,
+                              (const uint32_t *const *)dst_dev, num_edges, AG_MEM_DEVICE, device, out);
+        if (st == AG_ERR_VALUE) st = AG_ERR_LOAD;  // same message, the reference's class for a bad file
+    } while (0);
+    close(fd);
+    {
+        DeviceGuard guard(device);
+        for (uint32_t e = 0; e < AG_MAX_EDGE_TYPES; ++e) { cudaFree(off_dev[e]); cudaFree(dst_dev[e]); }
+        cudaFree(flag);
+    }
+    return st;
+}
+
+// Writes the graph as AETHHETG v1, atomically (temporary file, fsync, rename:
+// mmap_hetero.rs:83-96).  The forward CSR of every edge type is rebuilt from the
+// transposed adjacency the handle holds, rows sorted by destination; the
+// reference keeps the caller's order within a row, which no sampler observes
+// (hetero sampling walks the transposed adjacency, whose order is the same).
+extern "C" int32_t ag_hetero_save(const ag_hetero_graph *h, const ag_hetero_names *names, const char *path) {
+    if (!h || !names || !path) return fail(AG_ERR_VALUE, "ag_hetero_save: null argument");
+    DeviceGuard guard(h->device);
+    if (!guard.ok) return AG_ERR_CUDA;
+    for (uint32_t t = 0; t < h->nt; ++t)
+        if (strnlen(names->node_type[t], 64) >= 64) return fail(AG_ERR_VALUE, "type name too long");
+    AtomicFile f;
+    if (!f.open_tmp(path)) return fail(AG_ERR_LOAD, "failed to create %s: %s", path, strerror(errno));
+    std::vector<uint8_t> head(kHetHeader + h->nt * kHetNodeEntry + h->et * kHetEdgeEntry, 0);
+    memcpy(head.data(), "AETHHETG", 8);
+    const uint32_t version = 1;
+    memcpy(head.data() + 8, &version, 4); memcpy(head.data() + 12, &h->nt, 4); memcpy(head.data() + 16, &h->et, 4);
+    uint8_t *p = head.data() + kHetHeader;
+    for (uint32_t t = 0; t < h->nt; ++t, p += kHetNodeEntry) {
+        memcpy(p, names->node_type[t], strnlen(names->node_type[t], 63));
+        memcpy(p + 64, &h->num_nodes[t], 8);
+    }
+    for (uint32_t e = 0; e < h->et; ++e, p += kHetEdgeEntry) {
+        memcpy(p, names->node_type[h->src_type[e]], strnlen(names->node_type[h->src_type[e]], 63));
+        memcpy(p + 64, names->rel[e], strnlen(names->rel[e], 63));
+        memcpy(p + 128, names->node_type[h->dst_type[e]], strnlen(names->node_type[h->dst_type[e]], 63));
+        memcpy(p + 192, &h->num_nodes[h->src_type[e]], 8);
+        memcpy(p + 200, &h->num_edges[e], 8);
+    }
+    int32_t st = AG_OK;
+    if (write_all(f.fd, head.data(), head.size()) != 0) st = fail(AG_ERR_LOAD, "failed to write %s: %s", path, strerror(errno));
+    std::vector<uint8_t> bounce(64u << 20);
+    for (uint32_t e = 0; e < h->et && st == AG_OK; ++e) {
+        const uint64_t E = h->num_edges[e], ns = h->num_nodes[h->src_type[e]], nd = h->num_nodes[h->dst_type[e]];
+        uint64_t *keys = nullptr, *off = nullptr;
+        uint32_t *dst = nullptr;
+        if (cudaMalloc(&keys, std::max<uint64_t>(E, 1) * 8) != cudaSuccess) { st = fail(AG_ERR_CUDA, "out of device memory"); break; }
+        if (E) k_in_adjacency_keys<<<grid_for(E), 256>>>(h->in_offsets[e], h->in_sources[e], nd, E, keys);
+        st = keys_to_sorted_csr(keys, E, ns, &off, &dst);  // consumes keys
+        auto dump = [&](const void *dev, uint64_t bytes) {
+            for (uint64_t done = 0; done < bytes && st == AG_OK; done += bounce.size()) {
+                const uint64_t m = std::min<uint64_t>(bounce.size(), bytes - done);
+                if (cudaMemcpy(bounce.data(), (const uint8_t *)dev + done, m, cudaMemcpyDeviceToHost) != cudaSuccess)
+                    st = fail(AG_ERR_CUDA, "copy to host failed: %s", cudaGetErrorString(cudaGetLastError()));
+                else if (write_all(f.fd, bounce.data(), m) != 0) st = fail(AG_ERR_LOAD, "failed to write %s: %s", path, strerror(errno));
+            }
+        };
+        if (st == AG_OK) dump(off, (ns + 1) * 8);
+        if (st == AG_OK) dump(dst, E * 4);
+        const uint8_t zeros[8] = {0};
+        if (st == AG_OK && pad8(E * 4) && write_all(f.fd, zeros, pad8(E * 4)) != 0) st = fail(AG_ERR_LOAD, "failed to write %s: %s", path, strerror(errno));
+        cudaFree(off); cudaFree(dst);
+    }
+    if (st != AG_OK) { f.abort(); return st; }
+    if (!f.commit()) return fail(AG_ERR_LOAD, "failed to replace %s: %s", path, strerror(errno));
+    return AG_OK;
+}
+
+namespace ag {
+namespace {
 }  // namespace
 }  // namespace ag
 

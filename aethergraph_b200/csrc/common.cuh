@@ -43,7 +43,11 @@ struct DeviceGuard {
     ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
 };
 
-constexpr int kSMs = 148;  // B200: 2 dies x 74 SMs
+// Multiprocessors of the CURRENT device (B200: 148 = 2 dies x 74), read once per
+// device; grids are sized in multiples of it.  Every entry point selects its
+// handle's device before it sizes a grid.
+int sm_count();
+#define kSMs (::ag::sm_count())
 
 // Device-side error bits (ag_sample_counts.error).
 enum : uint32_t {

@@ -18,6 +18,7 @@
 #include <string.h>
 
 #include <algorithm>
+#include <string>
 #include <vector>
 
 #include "common.cuh"
@@ -517,15 +518,6 @@ uint64_t next_pow2(uint64_t v) { uint64_t p = 1; while (p < v) p <<= 1; return p
 
 using namespace ag;
 
-struct ag_hetero_graph {
-    int device = 0;
-    uint32_t nt = 0, et = 0;
-    uint64_t num_nodes[kMaxNT] = {0};
-    uint32_t src_type[kMaxET] = {0}, dst_type[kMaxET] = {0};
-    uint64_t num_edges[kMaxET] = {0};
-    uint64_t *in_offsets[kMaxET] = {nullptr};
-    uint32_t *in_sources[kMaxET] = {nullptr};
-};
 
 struct ag_hetero_sampler {
     const ag_hetero_graph *g = nullptr;
@@ -840,10 +832,37 @@ extern "C" int32_t ag_hetero_sampler_bounds(const ag_hetero_sampler *s, uint64_t
 // only) the handle's stream continues.  feats: NULL, or one feature store per
 // node type (entries may be NULL); node type t's rows are gathered into
 // bufs[b].x[t] in the order of its `nodes` segment.
+namespace {
+int32_t hetero_group_into(ag_hetero_sampler *s, uint32_t n_batches, uint32_t seed_type, const uint32_t *const *seeds,
+                          const uint64_t *n_seeds, const uint64_t *batch_seeds, const ag_features *const *feats,
+                          ag_hetero_buffers *bufs, void *stream);
+}  // namespace
+
+// A failure after the first kernel of the chain was queued leaves work running on the
+// stream: wait for it and mark the handle's device state unknown, so the next call
+// clears it instead of reusing staging buffers and table generations under it.
 extern "C" int32_t ag_hetero_sample_group_into(ag_hetero_sampler *s, uint32_t n_batches, uint32_t seed_type,
                                                const uint32_t *const *seeds, const uint64_t *n_seeds,
                                                const uint64_t *batch_seeds, const ag_features *const *feats,
                                                ag_hetero_buffers *bufs, void *stream) {
+    const int32_t st = hetero_group_into(s, n_batches, seed_type, seeds, n_seeds, batch_seeds, feats, bufs, stream);
+    if (st != AG_OK && s && !s->in_flight) {
+        const std::string msg = ag_last_error();
+        DeviceGuard guard(s->device);
+        cudaStreamSynchronize((cudaStream_t)stream);
+        cudaDeviceSynchronize();
+        cudaGetLastError();
+        s->dirty = true;
+        s->pending_pos = false;
+        set_error("%s", msg.c_str());
+    }
+    return st;
+}
+
+namespace {
+int32_t hetero_group_into(ag_hetero_sampler *s, uint32_t n_batches, uint32_t seed_type, const uint32_t *const *seeds,
+                          const uint64_t *n_seeds, const uint64_t *batch_seeds, const ag_features *const *feats,
+                          ag_hetero_buffers *bufs, void *stream) {
     if (!s || !bufs || !seeds || !n_seeds) return fail(AG_ERR_VALUE, "ag_hetero_sample_group_into: null argument");
     if (n_batches == 0 || n_batches > s->group)
         return fail(AG_ERR_VALUE, "group of %u batches does not fit a sampler created for %u", n_batches, s->group);
@@ -984,6 +1003,7 @@ extern "C" int32_t ag_hetero_sample_group_into(ag_hetero_sampler *s, uint32_t n_
     s->in_flight = true;
     return AG_OK;
 }
+}  // namespace
 
 extern "C" int32_t ag_hetero_sample_group_wait(ag_hetero_sampler *s, ag_hetero_counts *counts, int32_t *statuses) {
     if (!s) return fail(AG_ERR_VALUE, "ag_hetero_sample_group_wait: null sampler");

@@ -66,6 +66,18 @@ struct ag_features {
     } *sort = nullptr;
 };
 
+// Heterogeneous graph: per edge type only the transposed adjacency lives on the
+// device (for each destination, its sources ascending).
+struct ag_hetero_graph {
+    int device = 0;
+    uint32_t nt = 0, et = 0;
+    uint64_t num_nodes[AG_MAX_NODE_TYPES] = {0};
+    uint32_t src_type[AG_MAX_EDGE_TYPES] = {0}, dst_type[AG_MAX_EDGE_TYPES] = {0};
+    uint64_t num_edges[AG_MAX_EDGE_TYPES] = {0};
+    uint64_t *in_offsets[AG_MAX_EDGE_TYPES] = {nullptr};
+    uint32_t *in_sources[AG_MAX_EDGE_TYPES] = {nullptr};
+};
+
 // Device-visible table of a sharded feature store.
 struct ag_shard_table {
     const uint8_t *base[9];   // shard r's rows; base[n_shards]: this GPU's copy of the hot rows, if any

@@ -44,6 +44,7 @@
 #include <string.h>
 
 #include <algorithm>
+#include <string>
 #include <vector>
 
 #include "common.cuh"
@@ -443,6 +444,81 @@ __device__ __forceinline__ void write_item_local(const SampleParams &p, uint32_t
     }
 }
 
+// Weighted picks with a fanout above 32 (up to kLargeK): one block per frontier vertex.
+// The block streams the row, every thread evaluating the exact key of one position per
+// round (sampler.rs:1440-1452), and collects the positions that beat the current k-th
+// best in a shared buffer; when the buffer fills up it is sorted (bitonic, ascending
+// (key, position)) and cut back to the best k, which tightens the threshold.  The k
+// smallest (key, position) pairs are a property of the row alone, so neither the order
+// in which threads append nor the moments of the cuts change the result; the winners
+// are emitted in ascending order like the fanout <= 32 path.
+constexpr int kWLThreads = 256;
+constexpr int kWLBuf = 2048;  // >= kLargeK + kWLThreads
+
+__device__ __forceinline__ void wl_sort(double *key, uint32_t *pos) {  // whole block, kWLBuf entries
+    for (uint32_t size = 2; size <= (uint32_t)kWLBuf; size <<= 1) {
+        for (uint32_t stride = size >> 1; stride > 0; stride >>= 1) {
+            __syncthreads();
+            for (uint32_t t = threadIdx.x; t < (uint32_t)kWLBuf / 2; t += kWLThreads) {
+                const uint32_t lo = 2 * t - (t & (stride - 1));  // index with bit `stride` clear
+                const uint32_t hi = lo + stride;
+                const bool up = (lo & size) == 0;
+                const double ka = key[lo], kb = key[hi];
+                const uint32_t pa = pos[lo], pb = pos[hi];
+                if (key_less(kb, pb, ka, pa) == up) { key[lo] = kb; pos[lo] = pb; key[hi] = ka; pos[hi] = pa; }
+            }
+        }
+    }
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(kWLThreads)
+k_pick_weighted_large(const SampleParams *__restrict__ pa, uint32_t hop, uint32_t k) {
+    __shared__ double s_key[kWLBuf];
+    __shared__ uint32_t s_pos[kWLBuf];
+    __shared__ uint32_t s_fill;
+    chain_sync();
+    const SampleParams &p = pa[blockIdx.y];
+    const StageInfo nx = p.state->stage[hop + 1];
+    const double inf = __longlong_as_double(0x7FF0000000000000ll);
+    for (uint32_t j = blockIdx.x; j < nx.frontier_n; j += gridDim.x) {
+        const FrontierEntry fe = p.frontier[j];
+        const uint32_t deg = fe.deg;
+        if (deg == 0 || k == 0) continue;
+        if (k >= deg) {  // take-all, row order, no draws
+            for (uint32_t t = threadIdx.x; t < deg; t += kWLThreads) emit_edge(p, hop, nx.n_edges, fe, t, fe.off + t);
+            continue;
+        }
+        __syncthreads();
+        for (uint32_t t = threadIdx.x; t < (uint32_t)kWLBuf; t += kWLThreads) { s_key[t] = inf; s_pos[t] = 0xFFFFFFFFu; }
+        if (threadIdx.x == 0) s_fill = 0;
+        __syncthreads();
+        double thr_key = inf;            // the k-th best so far (block-uniform)
+        uint32_t thr_pos = 0xFFFFFFFFu;
+        for (uint32_t c = 0; c < deg; c += kWLThreads) {
+            const uint32_t pos = c + threadIdx.x;
+            if (pos < deg) {
+                const double key = weighted_key(p, hop, fe, pos);
+                if (key_less(key, pos, thr_key, thr_pos)) {
+                    const uint32_t at = atomicAdd(&s_fill, 1u);  // < kWLBuf: at most k + one round are ever held
+                    s_key[at] = key; s_pos[at] = pos;
+                }
+            }
+            __syncthreads();
+            if (s_fill + kWLThreads > (uint32_t)kWLBuf || c + kWLThreads >= deg) {
+                wl_sort(s_key, s_pos);
+                const uint32_t keep = min(s_fill, k);
+                for (uint32_t t = keep + threadIdx.x; t < (uint32_t)kWLBuf; t += kWLThreads) { s_key[t] = inf; s_pos[t] = 0xFFFFFFFFu; }
+                if (keep == k) { thr_key = s_key[k - 1]; thr_pos = s_pos[k - 1]; }
+                __syncthreads();
+                if (threadIdx.x == 0) s_fill = keep;
+                __syncthreads();
+            }
+        }
+        for (uint32_t t = threadIdx.x; t < k; t += kWLThreads) emit_edge(p, hop, nx.n_edges, fe, t, fe.off + s_pos[t]);
+    }
+}
+
 // Called by one thread once every block of the batch's last kernel has finished.
 __device__ __forceinline__ void publish_counts(const SampleParams &p, BatchState *bs) {
     __threadfence();
@@ -740,7 +816,9 @@ void launch_pick(int mode, uint32_t k, uint64_t frontier_est, uint32_t n_batches
         const uint64_t b = (vertices + per_block - 1) / per_block;
         return (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>(b, std::max<uint64_t>(1, (uint64_t)kSMs * 16 / n_batches)));
     };
-    if (mode == kModeWeighted) {
+    if (mode == kModeWeighted && k > 32) {
+        launch_chained(k_pick_weighted_large, dim3(blocks_for(frontier_est, 1), n_batches), dim3(kWLThreads), st, pa, hop, k);
+    } else if (mode == kModeWeighted) {
         launch_chained(k_pick<32, kPickWeighted>, dim3(blocks_for(frontier_est, kPickThreads / 32), n_batches), dim3(kPickThreads), st, pa, hop, k);
         // rows longer than kHubDegree were only queued: one block per queued row
         launch_chained(k_pick_hubs, dim3(std::max<uint32_t>(1, (uint32_t)(kSMs * 2 / n_batches)), n_batches), dim3(kHubThreads), st, pa, hop, k);
@@ -923,8 +1001,6 @@ extern "C" int32_t ag_sampler_create_group(const ag_graph *g, const ag_sampling_
     if (cfg->rng_mode != AG_RNG_WYRAND_EXACT && cfg->rng_mode != AG_RNG_PHILOX)
         return fail(AG_ERR_VALUE, "unknown rng_mode %d", cfg->rng_mode);
     for (uint32_t h = 0; h < cfg->num_hops; ++h) {
-        if (cfg->weighted && cfg->fanout[h] > 32)
-            return fail(AG_ERR_VALUE, "weighted sampling supports a fanout of at most 32 per hop (hop %u asks %u)", h, cfg->fanout[h]);
         if (cfg->fanout[h] > (uint32_t)kLargeK)
             return fail(AG_ERR_VALUE, "fanout of at most %d per hop is supported (hop %u asks %u)", kLargeK, h, cfg->fanout[h]);
     }
@@ -1074,9 +1150,30 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
 }
 
 namespace {
+int32_t launch_saved_impl(ag_sampler *s, bool relaunch);
+
 // Queues the chain described by s->last.  relaunch: the same chain once more with
 // full-size dedup tables (host seeds are already in the handle's device copy).
+// A failure part way through leaves kernels of the chain queued: wait for them and
+// mark the handle's device state unknown, so that the next call clears it instead of
+// reusing staging buffers, table generation and batch state under running kernels.
 int32_t launch_saved(ag_sampler *s, bool relaunch) {
+    const int32_t st = launch_saved_impl(s, relaunch);
+    if (st != AG_OK) {
+        const std::string msg = ag_last_error();
+        cudaStreamSynchronize(s->last.stream);
+        if (s->gstream) cudaStreamSynchronize(s->gstream);
+        if (s->rstream) cudaStreamSynchronize(s->rstream);
+        cudaGetLastError();
+        s->dirty = true;
+        s->pending_pos = false;
+        s->in_flight = false;
+        set_error("%s", msg.c_str());
+    }
+    return st;
+}
+
+int32_t launch_saved_impl(ag_sampler *s, bool relaunch) {
     const ag_sampler::Launch &L = s->last;
     const uint32_t n_batches = L.n_batches;
     const uint32_t *const *seeds = L.seeds.data();

@@ -65,6 +65,20 @@ class CsrGraph:
                                             C.byref(out)))
         return CsrGraph(out.value)
 
+    def load_features(self, path):
+        """Load an AETHFEAT file into this graph's GPU and attach it: the store is
+        returned and kept as `graph.features`, where `aethergraph_b200.pytorch.NeighborLoader`
+        finds it when neither `features` nor `feature_path` is passed.  (The reference's
+        README spells the workflow `graph = Graph.load(p); graph.load_features(f)`; its
+        current loaders take the same file as `feature_path`, which works here too.)"""
+        from .features import FeatureStore
+
+        store = FeatureStore.load(os.fspath(path), device=self.device)
+        if store.num_nodes < self.num_nodes:
+            raise ValueError(f"feature file has {store.num_nodes} rows but the graph has {self.num_nodes} nodes")
+        self.features = store
+        return store
+
     @staticmethod
     def from_edges(num_nodes: int, src, dst, weights=None, *, device: int | None = None) -> "CsrGraph":
         """Build from an edge list; edges keep their input order within a row."""

@@ -100,6 +100,48 @@ class HeteroCsrGraph:
         return HeteroCsrGraph(out.value, nt, names, [int(v) for v in ne], device)
 
     @staticmethod
+    def load(path, device: int | None = None) -> "HeteroCsrGraph":
+        """Load an AETHHETG v1 file (crates/aethergraph-core/src/internal/mmap_hetero.rs:1-45)
+        into GPU memory.  Every relation is validated in full; a malformed file raises
+        GraphLoadError."""
+        import os
+
+        import torch
+
+        if device is None:
+            device = torch.cuda.current_device() if torch.cuda.is_available() else 0
+        out, names = C.c_void_p(), _lib.HeteroNames()
+        _lib.check(_lib.lib().ag_hetero_load(os.fspath(path).encode(), device, C.byref(out), C.byref(names)))
+        nt_n, et_n = names.num_node_types, names.num_edge_types
+        counts = (C.c_uint64 * _lib.AG_MAX_NODE_TYPES)()
+        edges = (C.c_uint64 * _lib.AG_MAX_EDGE_TYPES)()
+        _lib.check(_lib.lib().ag_hetero_info(out, None, None, counts, edges, None))
+        nt = [(names.node_type[t].value.decode(), int(counts[t])) for t in range(nt_n)]
+        ets = [(names.src[e].value.decode(), names.rel[e].value.decode(), names.dst[e].value.decode()) for e in range(et_n)]
+        return HeteroCsrGraph(out.value, nt, ets, [int(edges[e]) for e in range(et_n)], device)
+
+    def save(self, path) -> None:
+        """Write the graph as an AETHHETG v1 file, atomically.  Rows of the stored forward
+        CSR are sorted by destination id (the sampler never observes the order within a
+        forward row: it walks the transposed adjacency)."""
+        import os
+
+        names = _lib.HeteroNames()
+        names.num_node_types, names.num_edge_types = len(self._node_types), len(self._edge_types)
+        for t, (name, _) in enumerate(self._node_types):
+            b = name.encode()
+            if len(b) >= 64:
+                raise ValueError(f"type name too long: {name}")
+            names.node_type[t].value = b
+        for e, (s, rel, d) in enumerate(self._edge_types):
+            for field, text in ((names.src, s), (names.rel, rel), (names.dst, d)):
+                b = text.encode()
+                if len(b) >= 64:
+                    raise ValueError(f"type name too long: {text}")
+                field[e].value = b
+        _lib.check(_lib.lib().ag_hetero_save(self._h, C.byref(names), os.fspath(path).encode()))
+
+    @staticmethod
     def from_device_edges(node_types: dict[str, int], edge_types: list[tuple], device: int | None = None) -> "HeteroCsrGraph":
         """Like `from_edge_arrays` with the COO arrays already in GPU memory: every
         `src_ids` / `dst_ids` is a contiguous int32 CUDA tensor holding u32 ids."""

@@ -213,6 +213,8 @@ class NeighborLoader:
                                         subgraph_type=subgraph_type, track_edge_ids=track_edge_ids,
                                         temporal_strategy=temporal_strategy, disjoint=disjoint, rng_mode=rng_mode)
         n = data.num_nodes
+        if features is None and feature_path is None:
+            features = getattr(data, "features", None)  # attached by Graph.load_features
         if features is None and feature_path is not None:
             features = FeatureStore.load(os.fspath(feature_path), device=data.device)
         if features is not None and not isinstance(features, FeatureStore):

@@ -390,6 +390,24 @@ int32_t ag_hetero_in_adjacency(const ag_hetero_graph *h, uint32_t edge_type, uin
                                uint32_t *sources);
 void ag_hetero_free(ag_hetero_graph *h);
 
+/* AETHHETG v1 files (crates/aethergraph-core/src/internal/mmap_hetero.rs:1-45;
+ * HeteroCsrGraph.save / .load, _core.pyi:609-660).  The type names travel in
+ * ag_hetero_names (64-byte fields as in the file).  Loading checks every size
+ * against the file length before reading, streams each relation's CSR into GPU
+ * memory and proves it in full (offsets start at 0, never decrease, end at the
+ * edge count; destinations below the destination type's count) as
+ * mmap_hetero.rs:161-330 does; a bad file is AG_ERR_LOAD.  Edge weights, if the
+ * file has them, are skipped: heterogeneous sampling is uniform
+ * (hetero_sampler.rs:36-39).  Saving writes to a temporary file that is fsynced
+ * and renamed over `path`. */
+typedef struct {
+    uint32_t num_node_types, num_edge_types;
+    char node_type[AG_MAX_NODE_TYPES][64];
+    char src[AG_MAX_EDGE_TYPES][64], rel[AG_MAX_EDGE_TYPES][64], dst[AG_MAX_EDGE_TYPES][64];
+} ag_hetero_names;
+int32_t ag_hetero_load(const char *path, int32_t device, ag_hetero_graph **out, ag_hetero_names *names);
+int32_t ag_hetero_save(const ag_hetero_graph *h, const ag_hetero_names *names, const char *path);
+
 /* Device output buffers of one heterogeneous batch.  Node type t's nodes are
  * nodes[node_start(t) .. +counts.nodes[t]) with node_start(t) = sum of the
  * counts of the types before it; edge type e's edges likewise in

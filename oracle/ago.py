@@ -32,7 +32,9 @@ def build(force: bool = False) -> str:
 
 
 REF_WARP_SAMPLER = os.path.join(_HERE, "_ref", "libref_warp_sampler.so")
-_REF_ROOT = "/root/reference"
+# A checkout of the reference: $AETHERGRAPH_REFERENCE, else a directory named
+# `reference` beside this repository.
+_REF_ROOT = os.environ.get("AETHERGRAPH_REFERENCE") or os.path.normpath(os.path.join(_HERE, "..", "..", "reference"))
 
 
 def build_ref() -> str | None:
@@ -500,3 +502,69 @@ class HeteroSampler:
         finally:
             lib().ago_hetero_subgraph_free(C.byref(sg))
         return out
+
+
+# ---------------------------------------------------------------------------
+# AETHHETG v1 (crates/aethergraph-core/src/internal/mmap_hetero.rs:1-45), in numpy:
+# the oracle-side writer and reader the GPU loader / saver are checked against.
+# ---------------------------------------------------------------------------
+def _name64(text: str) -> bytes:
+    b = text.encode()
+    assert len(b) < 64, f"type name too long: {text}"
+    return b + b"\0" * (64 - len(b))
+
+
+def write_hetero_file(path, node_types, relations) -> None:
+    """node_types: [(name, count)]; relations: [(src, rel, dst, offsets u64[num_src + 1], edges u32[E], weights f32[E] | None)]
+    (mmap_hetero.rs:98-157: header, node type table, edge type table, then per relation
+    offsets, edges and optional weights, the u32 sections zero-padded to 8 bytes)."""
+    out = bytearray(64)
+    out[:8] = b"AETHHETG"
+    out[8:12] = np.uint32(1).tobytes()
+    out[12:16] = np.uint32(len(node_types)).tobytes()
+    out[16:20] = np.uint32(len(relations)).tobytes()
+    for name, count in node_types:
+        out += _name64(name) + np.uint64(count).tobytes()
+    for (s, rel, d, offsets, edges, weights) in relations:
+        out += _name64(s) + _name64(rel) + _name64(d)
+        out += np.uint64(len(offsets) - 1).tobytes() + np.uint64(len(edges)).tobytes()
+        out += np.uint32(1 if weights is not None else 0).tobytes() + np.uint32(0).tobytes()
+    for (_, _, _, offsets, edges, weights) in relations:
+        out += np.ascontiguousarray(offsets, dtype=np.uint64).tobytes()
+        eb = np.ascontiguousarray(edges, dtype=np.uint32).tobytes()
+        out += eb + b"\0" * (-len(eb) % 8)
+        if weights is not None:
+            wb = np.ascontiguousarray(weights, dtype=np.float32).tobytes()
+            out += wb + b"\0" * (-len(wb) % 8)
+    with open(path, "wb") as f:
+        f.write(bytes(out))
+
+
+def read_hetero_file(path):
+    """Inverse of write_hetero_file (no validation beyond the layout): returns
+    (node_types, relations)."""
+    raw = open(path, "rb").read()
+    assert raw[:8] == b"AETHHETG" and int(np.frombuffer(raw[8:12], np.uint32)[0]) == 1
+    nt_n, et_n = (int(v) for v in np.frombuffer(raw[12:20], np.uint32))
+    at = 64
+    name = lambda b: b[:b.index(b"\0")].decode()
+    node_types = []
+    for _ in range(nt_n):
+        node_types.append((name(raw[at:at + 64]), int(np.frombuffer(raw[at + 64:at + 72], np.uint64)[0])))
+        at += 72
+    heads = []
+    for _ in range(et_n):
+        ns, ne = (int(v) for v in np.frombuffer(raw[at + 192:at + 208], np.uint64))
+        heads.append((name(raw[at:at + 64]), name(raw[at + 64:at + 128]), name(raw[at + 128:at + 192]), ns, ne,
+                      int(np.frombuffer(raw[at + 208:at + 212], np.uint32)[0]) != 0))
+        at += 216
+    relations = []
+    for (s, rel, d, ns, ne, has_w) in heads:
+        offsets = np.frombuffer(raw[at:at + 8 * (ns + 1)], np.uint64).copy(); at += 8 * (ns + 1)
+        edges = np.frombuffer(raw[at:at + 4 * ne], np.uint32).copy(); at += 4 * ne + (-4 * ne % 8)
+        weights = None
+        if has_w:
+            weights = np.frombuffer(raw[at:at + 4 * ne], np.float32).copy(); at += 4 * ne + (-4 * ne % 8)
+        relations.append((s, rel, d, offsets, edges, weights))
+    assert at == len(raw), "trailing bytes"
+    return node_types, relations

@@ -71,7 +71,8 @@ def main():
     off = np.array([0, 2, 4, 5, 6, 6], dtype=np.uint64)
     edges = np.array([1, 2, 2, 3, 3, 4], dtype=np.uint32)
     blob = aeth_v1_bytes(off, edges)
-    ref = "/root/reference/test_data/simple_graph.bin"
+    ref_root = os.environ.get("AETHERGRAPH_REFERENCE") or os.path.normpath(os.path.join(ROOT, "..", "reference"))
+    ref = os.path.join(ref_root, "test_data", "simple_graph.bin")
     if os.path.exists(ref):
         assert open(ref, "rb").read() == blob, "format restatement differs from the reference's fixture"
         print("simple_graph: identical to the reference's test_data/simple_graph.bin")

@@ -171,6 +171,32 @@ def test_loader_with_feature_file(ag, ago, tmp_path):
         ag.NeighborLoader.with_features(g, cfg, tmp_path / "short.bin")
 
 
+def test_graph_load_features_attaches_the_store(ag, ago, tmp_path):
+    """`graph = Graph.load(p); graph.load_features(f)` then the epoch loader, the
+    workflow the reference's README shows: batches carry x == features[n_id]."""
+    from helpers import rmat_csr
+
+    from aethergraph_b200.pytorch import NeighborLoader
+
+    n, off, dst, _ = rmat_csr(10, 8, seed=4)
+    feats = np.random.default_rng(2).standard_normal((n, 32)).astype(np.float32)
+    ag.save_features(tmp_path / "feat.bin", feats, dtype="f16")
+    ag.Graph.from_csr(off, dst).save(tmp_path / "g.bin")
+    graph = ag.Graph.load(tmp_path / "g.bin")
+    store = graph.load_features(tmp_path / "feat.bin")
+    assert store is graph.features and store.feature_dim == 32
+    payload = ago.encode(feats, "f16")
+    seen = 0
+    for batch in NeighborLoader(graph, num_neighbors=[4, 3], batch_size=64, shuffle=False, seed=1):
+        want = ago.gather(payload, n, 32, "f16", batch.n_id.cpu().numpy().astype(np.uint32))
+        assert np.array_equal(batch.x.cpu().numpy().view(np.uint32), want.view(np.uint32))
+        seen += 1
+    assert seen == n // 64
+    ag.save_features(tmp_path / "short.bin", feats[:10])
+    with pytest.raises(ValueError, match="rows but the graph has"):
+        graph.load_features(tmp_path / "short.bin")
+
+
 def test_gpu_reproduces_the_golden_samples(ag):
     g = np.load(os.path.join(GOLDEN, "golden_samples.npz"))
     off, dst, w, feats = g["offsets"], g["dst"], g["weights"], g["features"]

@@ -353,3 +353,30 @@ def test_cpu_generators_are_deterministic_and_shaped():
     assert abs(x.mean()) < 0.02 and abs(x.std() - 1.0) < 0.02
     assert np.array_equal(ago.synth_features(2000, 64, "bf16", 9, (500, 700)),
                           ago.synth_features(2000, 64, "bf16", 9).reshape(2000, 64)[500:700].reshape(-1))
+
+
+def test_hetero_file_layout_follows_the_reference(tmp_path):
+    """AETHHETG v1 field offsets and sizes as documented at
+    crates/aethergraph-core/src/internal/mmap_hetero.rs:1-45 (64-byte header, 72-byte
+    node entries, 216-byte edge entries, u32 sections padded to 8 bytes)."""
+    from oracle import ago
+
+    nt = [("user", 3), ("post", 2)]
+    rels = [("user", "votes", "post", np.array([0, 2, 2, 3], np.uint64), np.array([0, 1, 1], np.uint32), None),
+            ("post", "by", "user", np.array([0, 1, 2], np.uint64), np.array([2, 0], np.uint32), np.array([1.0, 2.0], np.float32))]
+    p = tmp_path / "h.hetg"
+    ago.write_hetero_file(p, nt, rels)
+    raw = p.read_bytes()
+    assert raw[:8] == b"AETHHETG" and raw[20:64] == bytes(44)
+    assert np.frombuffer(raw[8:20], np.uint32).tolist() == [1, 2, 2]
+    assert raw[64:68] == b"user" and raw[68:128] == bytes(60) and np.frombuffer(raw[128:136], np.uint64)[0] == 3
+    e0 = 64 + 2 * 72
+    assert raw[e0:e0 + 4] == b"user" and raw[e0 + 64:e0 + 69] == b"votes" and raw[e0 + 128:e0 + 132] == b"post"
+    assert np.frombuffer(raw[e0 + 192:e0 + 208], np.uint64).tolist() == [3, 3]
+    assert np.frombuffer(raw[e0 + 208:e0 + 216], np.uint32).tolist() == [0, 0]
+    body = e0 + 2 * 216
+    # relation 0: 4 offsets (32 B), 3 edges (12 B + 4 B pad); relation 1: 3 offsets, 2 edges (8 B), 2 weights (8 B)
+    assert len(raw) == body + 32 + 16 + 24 + 8 + 8
+    assert np.frombuffer(raw[body + 32:body + 44], np.uint32).tolist() == [0, 1, 1] and raw[body + 44:body + 48] == bytes(4)
+    nt2, rels2 = ago.read_hetero_file(p)
+    assert nt2 == nt and rels2[1][5].tolist() == [1.0, 2.0] and rels2[0][4].tolist() == [0, 1, 1]

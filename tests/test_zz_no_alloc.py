@@ -10,8 +10,11 @@ The test calls it through the C ABI twice in a row (the second call meets the
 first call's leftovers in the shared scratch) and compares nodes, per-seed local
 indices and the distinct count with what the regular, allocating entry point
 (ag_sample_into on a sampler handle, fanout 0) returns for the same seeds.
-Bit-exact: these are ids and indices.  This file sorts last on purpose, so a run
-that stops at the first failure has already run every other test.
+The CPU oracle's seed registration (a sampler with fanout 0) is checked beside
+it, so the comparison is anchored to the reference's algorithm and not only to
+this library's other path.  Bit-exact: these are ids and indices.  This file
+sorts last on purpose, so a run that stops at the first failure has already run
+every other test.
 """
 import ctypes as C
 
@@ -60,8 +63,13 @@ def test_register_seeds_static_matches_sampler_twice():
     rng = np.random.default_rng(5)
     first = rng.integers(0, 3000, size=8192).astype(np.uint32)      # the maximum size, many duplicates
     second = rng.integers(0, num_nodes, size=1000).astype(np.uint32)  # smaller: must not see stale entries
+    from oracle import ago
+
+    off = np.zeros(num_nodes + 1, dtype=np.uint64)
     for seeds in (first, second):
         want_nodes, want_locals = _reference(ag, graph, seeds)
+        cpu = ago.Sampler(off, np.zeros(0, dtype=np.uint32), [0], seed=1).sample(seeds)
+        assert np.array_equal(want_nodes, cpu["nodes"]) and np.array_equal(want_locals, cpu["seed_locals"])
         nodes, locals_, count, err = _static(_lib, device, seeds, num_nodes)
         assert err == 0
         assert count == len(want_nodes)
