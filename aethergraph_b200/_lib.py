@@ -15,8 +15,8 @@ LIB_PATH = os.path.join(_HERE, "libaethergpu.so")
 AG_OK, AG_ERR_VALUE, AG_ERR_LOAD, AG_ERR_SAMPLING, AG_ERR_TIMEOUT, AG_ERR_WORKER, AG_ERR_CUDA, \
     AG_ERR_SHUTDOWN = range(8)
 AG_MEM_HOST, AG_MEM_DEVICE = 0, 1
-AG_F32, AG_F16, AG_BF16 = 0, 1, 2
-DTYPE_TAG = {"f32": AG_F32, "f16": AG_F16, "bf16": AG_BF16}
+AG_F32, AG_F16, AG_BF16, AG_I8 = 0, 1, 2, 3
+DTYPE_TAG = {"f32": AG_F32, "f16": AG_F16, "bf16": AG_BF16, "i8": AG_I8}
 DTYPE_NAME = {v: k for k, v in DTYPE_TAG.items()}
 VALIDATION = {"auto": 0, "header_only": 1, "offsets_only": 2, "full": 3}
 AG_RNG_WYRAND_EXACT, AG_RNG_PHILOX = 0, 1
@@ -47,7 +47,7 @@ class SubgraphBuffers(C.Structure):
                 ("edge_ids", C.c_void_p), ("src_local", C.c_void_p), ("dst_local", C.c_void_p),
                 ("seed_locals", C.c_void_p), ("n_id", C.c_void_p),
                 ("edge_index_local", C.c_void_p), ("e_id", C.c_void_p),
-                ("seed_index", C.c_void_p), ("x", C.c_void_p)]
+                ("seed_index", C.c_void_p), ("x", C.c_void_p), ("cap_x", C.c_uint64)]
 
 
 class SampleCounts(C.Structure):
@@ -120,6 +120,7 @@ SIGNATURES = {
     "ag_graph_copy_to_host": (C.c_int32, [_P, _P, _P, _P]),
     "ag_features_copy_to_host": (C.c_int32, [_P, _P]),
     "ag_features_shard": (C.c_int32, [_P, _U64P, _U64P]),
+    "ag_features_scales_to_host": (C.c_int32, [_P, _P]),
     "ag_features_gather_stats": (C.c_int32, [_P, _U64P, _U64P, _U64P]),
     "ag_graph_hot_vertices": (C.c_int32, [_P, C.c_uint64, _PP, _U64P]),
     "ag_features_cache_rows": (C.c_int32, [_P, _P, C.c_uint64]),

@@ -764,6 +764,8 @@ ag_features *new_features(int device, uint64_t n, uint64_t begin, uint64_t rows,
 int32_t alloc_features(ag_features *f, bool alloc_payload) {
     if (alloc_payload)
         AG_CUDA(cudaMalloc(&f->payload, std::max<uint64_t>(f->rows * f->dim * elem_size(f->dtype), 16)));
+    if (alloc_payload && f->dtype == AG_I8)
+        AG_CUDA(cudaMalloc(&f->scales, std::max<uint64_t>(f->rows * ((f->dim + kQuantBlock - 1) / kQuantBlock) * 4, 16)));
     AG_CUDA(cudaMalloc(&f->err, 32));  // error bits, then the gather counters (internal.h)
     AG_CUDA(cudaMemset(f->err, 0, 32));
     return AG_OK;
@@ -832,7 +834,7 @@ extern "C" int32_t ag_features_save(const char *path, const float *features, uin
 extern "C" void ag_features_free(ag_features *f) {
     if (!f) return;
     DeviceGuard guard(f->device);
-    if (f->owns_payload) cudaFree(f->payload);
+    if (f->owns_payload) { cudaFree(f->payload); cudaFree(f->scales); }
     for (void *p : f->ipc_opened) if (p) cudaIpcCloseMemHandle(p);
     if (f->sort) {
         if (f->sort->done) { cudaEventSynchronize(f->sort->done); cudaEventDestroy(f->sort->done); }
@@ -942,13 +944,15 @@ extern "C" int32_t ag_features_from_memory(const void *payload, uint64_t num_nod
 extern "C" int32_t ag_features_from_f32(const float *features, uint64_t num_nodes, uint64_t dim, int32_t dtype,
                                         int32_t mem_kind, int32_t device, ag_features **out) {
     if ((!features && num_nodes * dim) || !out) return fail(AG_ERR_VALUE, "ag_features_from_f32: null argument");
-    if (dtype < 0 || dtype > 2) return fail(AG_ERR_VALUE, "unknown feature dtype tag: %d", dtype);
+    if (dtype < 0 || dtype > AG_I8) return fail(AG_ERR_VALUE, "unknown feature dtype tag: %d", dtype);
+    if (dtype == AG_I8 && dim == 0) return fail(AG_ERR_VALUE, "feature_dim must be non-zero");  // FeatureCodecError::ZeroDim
     DeviceGuard guard(device);
     if (!guard.ok) return AG_ERR_CUDA;
     ag_features *f = new_features(device, num_nodes, 0, num_nodes, dim, dtype);
     int32_t st = alloc_features(f, true);
     const uint64_t count = num_nodes * dim;
     float *staged = nullptr;
+    uint32_t *bad = nullptr;
     do {
         if (st != AG_OK || count == 0) break;
         const float *src = features;
@@ -960,11 +964,21 @@ extern "C" int32_t ag_features_from_f32(const float *features, uint64_t num_node
             }
             src = staged;
         }
-        cudaError_t e = launch_encode(src, f->payload, count, dtype, 0);
+        cudaError_t e;
+        if (dtype == AG_I8) {
+            uint32_t hbad = 0;
+            e = cudaMalloc(&bad, 4);
+            if (e == cudaSuccess) e = cudaMemset(bad, 0, 4);
+            if (e == cudaSuccess) e = launch_encode_i8(src, num_nodes, dim, (int8_t *)f->payload, f->scales, bad, 0);
+            if (e == cudaSuccess) e = cudaMemcpy(&hbad, bad, 4, cudaMemcpyDeviceToHost);
+            if (e == cudaSuccess && hbad) { st = fail(AG_ERR_VALUE, "feature values must be finite"); break; }  // FeatureCodecError::NotFinite
+        } else {
+            e = launch_encode(src, f->payload, count, dtype, 0);
+        }
         if (e == cudaSuccess) e = cudaDeviceSynchronize();
         if (e != cudaSuccess) st = fail(AG_ERR_CUDA, "feature encode failed: %s", cudaGetErrorString(e));
     } while (0);
-    cudaFree(staged);
+    cudaFree(staged); cudaFree(bad);
     if (st != AG_OK) { ag_features_free(f); return st; }
     *out = f;
     return AG_OK;
@@ -973,7 +987,7 @@ extern "C" int32_t ag_features_from_f32(const float *features, uint64_t num_node
 extern "C" int32_t ag_features_adopt_device(void *payload_dev, uint64_t num_nodes, uint64_t dim, int32_t dtype,
                                             int32_t device, ag_features **out) {
     if (!payload_dev || !out) return fail(AG_ERR_VALUE, "ag_features_adopt_device: null argument");
-    if (dtype < 0 || dtype > 2) return fail(AG_ERR_VALUE, "unknown feature dtype tag: %d", dtype);
+    if (dtype < 0 || dtype > AG_I8) return fail(AG_ERR_VALUE, "unknown feature dtype tag: %d", dtype);
     DeviceGuard guard(device);
     if (!guard.ok) return AG_ERR_CUDA;
     ag_features *f = new_features(device, num_nodes, 0, num_nodes, dim, dtype);
@@ -1034,6 +1048,15 @@ extern "C" int32_t ag_gather(const ag_features *f, const void *ids_dev, int32_t 
         return AG_OK;
     }
     AG_CUDA(launch_gather(a, f->dtype, (cudaStream_t)stream));
+    return AG_OK;
+}
+
+extern "C" int32_t ag_features_scales_to_host(const ag_features *f, float *scales) {
+    if (!f || !scales) return fail(AG_ERR_VALUE, "ag_features_scales_to_host: null argument");
+    if (f->dtype != AG_I8 || !f->scales) return fail(AG_ERR_VALUE, "only the int8 payload carries scales");
+    DeviceGuard guard(f->device);
+    if (!guard.ok) return AG_ERR_CUDA;
+    AG_CUDA(cudaMemcpy(scales, f->scales, f->rows * ((f->dim + kQuantBlock - 1) / kQuantBlock) * 4, cudaMemcpyDeviceToHost));
     return AG_OK;
 }
 

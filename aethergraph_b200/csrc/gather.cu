@@ -170,6 +170,101 @@ k_gather_vec(GatherArgs a, const GatherArgs *__restrict__ group, uint64_t first)
     }
 }
 
+// Block-scaled int8 rows: LPR lanes per row, every lane owns 16 codes (one 16-byte
+// vector, inside one 32-element scale block) of kInFlight rows at a time and writes
+// 16 floats per row.  decode = (float)code * scale: one IEEE multiply, the same value
+// the reference's BlockScaledI8::decode computes (feature_codec.rs:121-133; its own
+// device kernel: crates/aether-stream/src/gpu/kernels/quant/feature_dequant.cu:21-75).
+template <int LPR>
+__global__ void __launch_bounds__(kThreads)
+k_gather_i8(GatherArgs a, const GatherArgs *__restrict__ group, uint64_t first) {
+    constexpr int kRowsPerBlock = kThreads / LPR;
+    if (group) a = group[blockIdx.y];
+    if (!a.payload) return;
+    const uint64_t n = a.n_dev ? min((uint64_t)*a.n_dev, a.n) : a.n;
+    if (a.ids_off) a.ids = (const uint32_t *)a.ids + *a.ids_off;
+    const int lane = threadIdx.x % LPR;
+    const int sub = threadIdx.x / LPR;
+    const uint32_t vecs = a.row_bytes >> 4;                       // 16 codes per vector
+    const uint32_t blocks_per_row = (a.dim + kQuantBlock - 1) / kQuantBlock;
+    constexpr uint64_t kChunk = (uint64_t)kRowsPerBlock * kInFlight;
+    const uint64_t pol = l2_evict_first_policy();
+    for (uint64_t base = first + (uint64_t)blockIdx.x * kChunk + sub; base < n; base += (uint64_t)gridDim.x * kChunk) {
+        for (uint32_t v0 = 0; v0 < vecs; v0 += LPR) {
+            const uint32_t v = v0 + lane;
+            uint4 val[kInFlight];
+            float scale[kInFlight];
+            bool ok[kInFlight];
+#pragma unroll
+            for (int u = 0; u < kInFlight; ++u) {
+                const uint64_t r = base + (uint64_t)u * kRowsPerBlock;
+                ok[u] = false; scale[u] = 0.f;
+                val[u] = make_uint4(0, 0, 0, 0);
+                if (r < n && v < vecs) {
+                    const uint64_t id = load_id(a.ids, a.ids64, r);
+                    const uint64_t local = id - a.row_begin;
+                    ok[u] = true;
+                    if (id >= a.row_begin && local < a.rows) {
+                        val[u] = ld_stream_v4_l2ef(a.payload + local * a.row_bytes + ((uint64_t)v << 4), pol);
+                        scale[u] = __ldg(a.scales + local * blocks_per_row + (v >> 1));  // 32-element blocks: two vectors each
+                    } else if (lane == 0) {
+                        atomicOr(a.err, kErrBadId);
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kInFlight; ++u) {
+                if (!ok[u]) continue;
+                const uint64_t r = base + (uint64_t)u * kRowsPerBlock;
+                float *dst = a.out + r * a.dim + (uint64_t)v * 16;
+                const uint32_t w[4] = {val[u].x, val[u].y, val[u].z, val[u].w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    uint4 o;
+                    o.x = __float_as_uint((float)(int)(signed char)(w[q] & 0xFFu) * scale[u]);
+                    o.y = __float_as_uint((float)(int)(signed char)((w[q] >> 8) & 0xFFu) * scale[u]);
+                    o.z = __float_as_uint((float)(int)(signed char)((w[q] >> 16) & 0xFFu) * scale[u]);
+                    o.w = __float_as_uint((float)(int)(signed char)(w[q] >> 24) * scale[u]);
+                    st_stream_v4(dst + q * 4, o);
+                }
+            }
+        }
+    }
+}
+
+cudaError_t launch_i8(const GatherArgs &a, const GatherArgs *group, uint32_t row_bytes, dim3 grid, cudaStream_t st, uint64_t first = 0) {
+    const uint32_t vecs = row_bytes >> 4;
+    if (vecs <= 4) k_gather_i8<4><<<grid, kThreads, 0, st>>>(a, group, first);
+    else if (vecs <= 8) k_gather_i8<8><<<grid, kThreads, 0, st>>>(a, group, first);
+    else if (vecs <= 16) k_gather_i8<16><<<grid, kThreads, 0, st>>>(a, group, first);
+    else k_gather_i8<32><<<grid, kThreads, 0, st>>>(a, group, first);
+    return cudaGetLastError();
+}
+
+// f32 -> block-scaled int8 (feature_codec.rs:73-112): a warp per 32-element block.
+__global__ void k_encode_i8(const float *__restrict__ src, uint64_t rows, uint64_t dim, int8_t *__restrict__ codes,
+                            float *__restrict__ scales, uint32_t *bad) {
+    const uint64_t blocks_per_row = (dim + kQuantBlock - 1) / kQuantBlock;
+    const uint64_t total = rows * blocks_per_row;
+    const int lane = threadIdx.x & 31;
+    for (uint64_t b = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; b < total; b += ((uint64_t)gridDim.x * blockDim.x) >> 5) {
+        const uint64_t row = b / blocks_per_row, blk = b - row * blocks_per_row;
+        const uint64_t e = blk * kQuantBlock + lane;
+        const bool in = e < dim;
+        const float v = in ? src[row * dim + e] : 0.f;
+        if (in && !isfinite(v)) atomicOr(bad, 1u);
+        float peak = fabsf(v);
+        for (int o = 16; o > 0; o >>= 1) peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, o));
+        const float scale = peak == 0.f ? 0.f : __fdiv_rn(peak, 127.0f);
+        if (lane == 0) scales[b] = scale;
+        if (in) {
+            int q = 0;
+            if (scale != 0.f) q = (int)fminf(fmaxf(roundf(__fdiv_rn(v, scale)), -127.0f), 127.0f);  // round half away from zero
+            codes[row * dim + e] = (int8_t)q;
+        }
+    }
+}
+
 // Element path for rows that are not a whole number of 16-byte vectors.
 template <int DTYPE>
 __global__ void __launch_bounds__(kThreads)
@@ -196,6 +291,8 @@ k_gather_elem(GatherArgs a, const GatherArgs *__restrict__ group) {
                 const uint8_t *row = a.payload + local * a.row_bytes;
                 if (DTYPE == AG_F32) f = __uint_as_float(ld_stream_u32(row + 4ull * j));
                 else if (DTYPE == AG_BF16) f = bf16lo(ld_stream_u16(row + 2ull * j));
+                else if (DTYPE == AG_I8) f = (float)(int)(signed char)row[j] *
+                                             a.scales[local * ((a.dim + kQuantBlock - 1) / kQuantBlock) + j / kQuantBlock];
                 else f = f16_to_f32_bits(ld_stream_u16(row + 2ull * j));
             }
         } else if (j == 0) {
@@ -490,6 +587,7 @@ cudaError_t launch_gather(const GatherArgs &a, int dtype, cudaStream_t st) {
     if (vec_ok) {
         const dim3 grid(gather_grid_blocks(a.n, a.row_bytes), 1);
         switch (dtype) {
+            case AG_I8: return launch_i8(a, nullptr, a.row_bytes, grid, st);
             case AG_F32: return launch_vec<AG_F32>(a, nullptr, a.row_bytes, grid, a.shards != nullptr, st);
             case AG_F16: return launch_vec<AG_F16>(a, nullptr, a.row_bytes, grid, a.shards != nullptr, st);
             default: return launch_vec<AG_BF16>(a, nullptr, a.row_bytes, grid, a.shards != nullptr, st);
@@ -499,6 +597,7 @@ cudaError_t launch_gather(const GatherArgs &a, int dtype, cudaStream_t st) {
     uint64_t blocks = (total + kThreads - 1) / kThreads;
     if (blocks > (uint64_t)kSMs * 8) blocks = (uint64_t)kSMs * 8;
     switch (dtype) {
+        case AG_I8: k_gather_elem<AG_I8><<<(int)blocks, kThreads, 0, st>>>(a, nullptr); break;
         case AG_F32: k_gather_elem<AG_F32><<<(int)blocks, kThreads, 0, st>>>(a, nullptr); break;
         case AG_F16: k_gather_elem<AG_F16><<<(int)blocks, kThreads, 0, st>>>(a, nullptr); break;
         default: k_gather_elem<AG_BF16><<<(int)blocks, kThreads, 0, st>>>(a, nullptr); break;
@@ -523,6 +622,7 @@ cudaError_t launch_gather_group(const GatherArgs *group_dev, uint32_t n_batches,
         per = std::min(per, cap);
         const dim3 grid(per, n_batches);
         switch (dtype) {
+            case AG_I8: return launch_i8(none, group_dev, row_bytes, grid, st);
             case AG_F32: return launch_vec<AG_F32>(none, group_dev, row_bytes, grid, sharded, st);
             case AG_F16: return launch_vec<AG_F16>(none, group_dev, row_bytes, grid, sharded, st);
             default: return launch_vec<AG_BF16>(none, group_dev, row_bytes, grid, sharded, st);
@@ -533,6 +633,7 @@ cudaError_t launch_gather_group(const GatherArgs *group_dev, uint32_t n_batches,
     blocks = std::max<uint64_t>(1, std::min<uint64_t>(blocks, (uint64_t)kSMs * 8 / n_batches + 1));
     const dim3 grid((uint32_t)blocks, n_batches);
     switch (dtype) {
+        case AG_I8: k_gather_elem<AG_I8><<<grid, kThreads, 0, st>>>(none, group_dev); break;
         case AG_F32: k_gather_elem<AG_F32><<<grid, kThreads, 0, st>>>(none, group_dev); break;
         case AG_F16: k_gather_elem<AG_F16><<<grid, kThreads, 0, st>>>(none, group_dev); break;
         default: k_gather_elem<AG_BF16><<<grid, kThreads, 0, st>>>(none, group_dev); break;
@@ -650,6 +751,15 @@ cudaError_t launch_gather_sorted(const GatherArgs &one, const GatherArgs *group_
     const cudaError_t e = launch_sort_keys(one, group_dev, n_batches, rows_cap, f, sc, st);
     if (e != cudaSuccess) return e;
     return launch_sorted_fetch(one, group_dev, n_batches, rows_cap, row_bytes, dim, dtype, f, sc, st, st);
+}
+
+cudaError_t launch_encode_i8(const float *src, uint64_t rows, uint64_t dim, int8_t *codes, float *scales, uint32_t *bad_dev,
+                             cudaStream_t st) {
+    const uint64_t blocks = rows * ((dim + kQuantBlock - 1) / kQuantBlock);
+    if (blocks == 0) return cudaSuccess;
+    const uint64_t grid = std::max<uint64_t>(1, std::min<uint64_t>((blocks * 32 + 255) / 256, (uint64_t)kSMs * 16));
+    k_encode_i8<<<(int)grid, 256, 0, st>>>(src, rows, dim, codes, scales, bad_dev);
+    return cudaGetLastError();
 }
 
 cudaError_t launch_encode(const float *src, void *dst, uint64_t count, int dtype, cudaStream_t st) {

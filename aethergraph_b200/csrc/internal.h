@@ -41,6 +41,7 @@ struct ag_features {
     uint64_t dim = 0;
     int dtype = AG_F32;
     uint8_t *payload = nullptr;  // device, rows * dim * elem_size
+    float *scales = nullptr;     // device, AG_I8 only: rows * ceil(dim / 32) per-block scales
     uint32_t *err = nullptr;     // device, 32 bytes: sticky error bits; at +8 / +16 two u64 counters of the
                                  // address-ordered gather (rows asked for, rows actually loaded)
     bool owns_payload = true;
@@ -91,7 +92,8 @@ struct ag_shard_table {
 
 namespace ag {
 
-inline uint32_t elem_size(int dtype) { return dtype == AG_F32 ? 4u : 2u; }
+inline uint32_t elem_size(int dtype) { return dtype == AG_F32 ? 4u : dtype == AG_I8 ? 1u : 2u; }
+constexpr uint32_t kQuantBlock = 32;  // elements per scale of the int8 payload (feature_codec.rs: BlockScaledI8::BLOCK)
 
 struct GatherArgs {
     const uint8_t *payload;
@@ -105,13 +107,14 @@ struct GatherArgs {
     uint32_t *err;
     const ag_shard_table *shards;  // non-null: rows are looked up through the shard table
     const uint32_t *ids_off;       // non-null (u32 ids only): the ids start at ids + *ids_off (device value)
+    const float *scales;           // AG_I8 stores: per-block scales
 };
 
 // The source half of a gather's arguments, from a feature store handle.
 inline void set_gather_source(GatherArgs &a, const ag_features *f) {
     a.payload = f->payload; a.row_begin = f->row_begin; a.rows = f->rows;
     a.row_bytes = (uint32_t)(f->dim * elem_size(f->dtype)); a.dim = (uint32_t)f->dim;
-    a.err = f->err; a.shards = f->shards;
+    a.err = f->err; a.shards = f->shards; a.scales = f->scales;
 }
 
 cudaError_t launch_gather(const GatherArgs &a, int dtype, cudaStream_t st);
@@ -129,6 +132,9 @@ cudaError_t launch_gather_sorted(const GatherArgs &one, const GatherArgs *group_
                                  uint32_t row_bytes, uint32_t dim, int dtype, const ag_features *f, SortScratch &sc,
                                  cudaStream_t st);
 cudaError_t launch_encode(const float *src, void *dst, uint64_t count, int dtype, cudaStream_t st);
+// f32 rows -> block-scaled int8 codes + scales; *bad_dev is set when a value is not finite.
+cudaError_t launch_encode_i8(const float *src, uint64_t rows, uint64_t dim, int8_t *codes, float *scales, uint32_t *bad_dev,
+                             cudaStream_t st);
 int gather_grid_blocks(uint64_t n, uint32_t row_bytes);
 
 // Device-side validation of a CSR: offsets monotone, offsets[n] == e, dst < n.

@@ -32,7 +32,8 @@ using namespace ag;
 namespace {
 
 struct PoolSet {
-    void *base = nullptr;              // one cudaMalloc
+    void *base = nullptr;              // one cudaMalloc: every array but x
+    void *x_base = nullptr;            // x on its own, so that a batch that outgrew it can get a larger one
     ag_subgraph_buffers bufs{};
     cudaEvent_t last_use = nullptr;    // consumer's last use of the memory, if any
 };
@@ -85,6 +86,10 @@ struct ag_loader {
     std::vector<cudaStream_t> streams;
     ag_loader_stats stats{};
 
+    // x of a pooled batch is reserved from the node counts batches really produce (the
+    // worst-case bound, every pick a new vertex, is several times larger): 1.5 x the
+    // largest batch seen, in steps of 4096 rows, full size until a batch has been seen.
+    std::atomic<uint64_t> x_rows_seen{0};
     std::mutex pool_m;
     std::vector<PoolSet> pool_free;
     std::unordered_map<void *, PoolSet> pool_live;  // keyed by bufs.nodes
@@ -98,12 +103,15 @@ int32_t pool_take(ag_loader *l, uint64_t n_seeds, ag_subgraph_buffers *out, cuda
     uint64_t mn = 0, me = 0;
     AG_TRY(ag_sampler_bounds(l->samplers[0], n_seeds, &mn, &me));
     const uint64_t cn = std::max<uint64_t>(mn, 1), ce = std::max<uint64_t>(me, 1), cs = std::max<uint64_t>(n_seeds, 1);
+    const uint64_t seen = l->x_rows_seen.load();
+    const uint64_t cx = seen ? std::min<uint64_t>(cn, ((seen + seen / 2 + 4095) / 4096) * 4096) : cn;
     *last_use = nullptr;
     {
         std::lock_guard<std::mutex> lk(l->pool_m);
         for (size_t i = 0; i < l->pool_free.size(); ++i) {
             PoolSet &p = l->pool_free[i];
-            if (p.bufs.cap_nodes == cn && p.bufs.cap_edges == ce && p.bufs.cap_seeds == cs) {
+            if (p.bufs.cap_nodes == cn && p.bufs.cap_edges == ce && p.bufs.cap_seeds == cs &&
+                (!l->f || (p.bufs.cap_x >= cx && p.bufs.cap_x <= 2 * cx))) {
                 PoolSet s = p;
                 l->pool_free[i] = l->pool_free.back();
                 l->pool_free.pop_back();
@@ -121,14 +129,17 @@ int32_t pool_take(ag_loader *l, uint64_t n_seeds, ag_subgraph_buffers *out, cuda
     auto carve = [&](uint64_t bytes) { const uint64_t o = off; off += align256(bytes); return o; };
     const uint64_t o_nodes = carve(cn * 4), o_esrc = carve(ce * 4), o_edst = carve(ce * 4), o_sl = carve(ce * 4),
                    o_dl = carve(ce * 4), o_seedl = carve(cs * 4), o_eid = eids ? carve(ce * 8) : 0,
-                   o_nid = carve(cn * 8), o_eil = carve(ce * 16), o_sidx = carve(cs * 8),
-                   o_x = dim ? carve(cn * dim * 4) : 0;
+                   o_nid = carve(cn * 8), o_eil = carve(ce * 16), o_sidx = carve(cs * 8);
     uint8_t *base = nullptr;
-    if (cudaMalloc(&base, std::max<uint64_t>(off, 256)) != cudaSuccess)
+    float *xb = nullptr;
+    if (cudaMalloc(&base, std::max<uint64_t>(off, 256)) != cudaSuccess ||
+        (dim && cudaMalloc(&xb, std::max<uint64_t>(cx * dim * 4, 256)) != cudaSuccess)) {
+        cudaFree(base);
         return fail(AG_ERR_CUDA, "loader: out of device memory for a %llu-byte batch buffer: %s",
-                    (unsigned long long)off, cudaGetErrorString(cudaGetLastError()));
+                    (unsigned long long)(off + cx * dim * 4), cudaGetErrorString(cudaGetLastError()));
+    }
     PoolSet s;
-    s.base = base;
+    s.base = base; s.x_base = xb;
     ag_subgraph_buffers &b = s.bufs;
     b.cap_nodes = cn; b.cap_edges = ce; b.cap_seeds = cs;
     b.nodes = (uint32_t *)(base + o_nodes); b.edge_src = (uint32_t *)(base + o_esrc);
@@ -138,7 +149,7 @@ int32_t pool_take(ag_loader *l, uint64_t n_seeds, ag_subgraph_buffers *out, cuda
     b.n_id = (int64_t *)(base + o_nid); b.edge_index_local = (int64_t *)(base + o_eil);
     b.e_id = nullptr;  // int64(edge id) shares its bits with the u64 edge_ids
     b.seed_index = (int64_t *)(base + o_sidx);
-    b.x = dim ? (float *)(base + o_x) : nullptr;
+    b.x = xb; b.cap_x = dim ? cx : 0;
     *out = b;
     std::lock_guard<std::mutex> lk(l->pool_m);
     l->pool_live.emplace(b.nodes, s);
@@ -158,7 +169,7 @@ void pool_give(ag_loader *l, const ag_subgraph_buffers &bufs, bool record, cudaS
             cudaEventRecord(s.last_use, stream) != cudaSuccess) {
             // Cannot order the reuse: do not reuse.
             if (s.last_use) cudaEventDestroy(s.last_use);
-            cudaFree(s.base);
+            cudaFree(s.base); cudaFree(s.x_base);
             return;
         }
     }
@@ -241,6 +252,42 @@ void worker_main(ag_loader *l, uint32_t idx) {
             }
         } else {
             err = ag_last_error();
+        }
+        if (launched && l->f) {
+            for (uint32_t b = 0; b < nb; ++b) {
+                if (statuses[b] != AG_OK) continue;
+                const uint64_t nn = counts[b].num_nodes;
+                uint64_t prev = l->x_rows_seen.load();
+                while (nn > prev && !l->x_rows_seen.compare_exchange_weak(prev, nn)) {}
+                Work &w = ws[b];
+                const uint64_t have = w.bufs.cap_x ? w.bufs.cap_x : w.bufs.cap_nodes;
+                if (!w.bufs.x || nn <= have) continue;
+                // The batch has more nodes than rows were reserved for: its first `have` rows are
+                // in place; gather all of them again into a buffer that fits.  Pooled sets get a
+                // new x; a caller's own buffer cannot grow, so that batch is reported as too small.
+                if (!w.owned) {
+                    statuses[b] = fail(AG_ERR_VALUE, "x holds %llu rows, the batch has %llu nodes", (unsigned long long)have, (unsigned long long)nn);
+                    err = ag_last_error();
+                    if (rc == AG_OK) rc = statuses[b];
+                    continue;
+                }
+                float *bigger = nullptr;
+                const uint64_t rows = ((nn + nn / 4 + 4095) / 4096) * 4096;
+                int32_t g = AG_OK;
+                if (cudaMalloc(&bigger, rows * l->f->dim * 4) != cudaSuccess) g = fail(AG_ERR_CUDA, "loader: out of device memory for %llu feature rows", (unsigned long long)rows);
+                if (g == AG_OK) g = ag_gather(l->f, w.bufs.nodes, 0, nn, nullptr, bigger, st);
+                if (g == AG_OK && cudaStreamSynchronize(st) != cudaSuccess) g = fail(AG_ERR_CUDA, "loader: gathering an outgrown batch again failed");
+                if (g != AG_OK) { cudaFree(bigger); statuses[b] = g; err = ag_last_error(); if (rc == AG_OK) rc = g; continue; }
+                std::lock_guard<std::mutex> pk(l->pool_m);
+                auto it = l->pool_live.find(w.bufs.nodes);
+                if (it != l->pool_live.end()) {
+                    cudaFree(it->second.x_base);
+                    it->second.x_base = bigger; it->second.bufs.x = bigger; it->second.bufs.cap_x = rows;
+                    w.bufs.x = bigger; w.bufs.cap_x = rows;
+                } else {
+                    cudaFree(bigger);
+                }
+            }
         }
         const uint64_t ns = (uint64_t)std::chrono::duration_cast<std::chrono::nanoseconds>(Clock::now() - t0).count();
         std::unique_lock<std::mutex> lk(l->m);
@@ -554,7 +601,7 @@ extern "C" void ag_loader_free(ag_loader *l) {
     for (ag_sampler *s : l->samplers) ag_sampler_free(s);
     for (cudaStream_t s : l->streams) cudaStreamDestroy(s);
     // Batches still held by a consumer keep their memory valid until now.
-    for (PoolSet &p : l->pool_free) { if (p.last_use) cudaEventDestroy(p.last_use); cudaFree(p.base); }
-    for (auto &kv : l->pool_live) cudaFree(kv.second.base);
+    for (PoolSet &p : l->pool_free) { if (p.last_use) cudaEventDestroy(p.last_use); cudaFree(p.base); cudaFree(p.x_base); }
+    for (auto &kv : l->pool_live) { cudaFree(kv.second.base); cudaFree(kv.second.x_base); }
     delete l;
 }

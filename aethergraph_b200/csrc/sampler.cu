@@ -61,7 +61,7 @@ constexpr int kTileItems = kTile * kIPT;  // items per tile of the single-pass s
 constexpr int kPickThreads = 256;
 constexpr int kLargeK = 1024;   // largest fanout the k > 32 path keeps in shared memory
 
-enum : int { kModeUniform = 0, kModeReplace = 1, kModeWeighted = 2 };
+enum : int { kModeUniform = 0, kModeReplace = 1, kModeWeighted = 2, kModeWeightedReplace = 3 };
 enum : int { kPickSmall = 0, kPickLarge = 1, kPickWeighted = 2 };
 
 // Parameter block of one batch; a group's blocks sit in one device array that
@@ -116,7 +116,7 @@ __device__ __forceinline__ void row_demand(int mode, uint64_t deg, uint32_t k, u
                                            uint64_t &draws) {
     take = 0; draws = 0;
     if (deg == 0 || k == 0) return;
-    if (mode == kModeReplace) { take = k; draws = k; return; }
+    if (mode == kModeReplace || mode == kModeWeightedReplace) { take = k; draws = k; return; }
     if ((uint64_t)k >= deg) { take = (uint32_t)deg; return; }
     take = k;
     draws = (mode == kModeWeighted) ? deg : (uint64_t)k;
@@ -441,6 +441,47 @@ __device__ __forceinline__ void write_item_local(const SampleParams &p, uint32_t
         if (e >= p.cap_edges) return;
         p.dst_local[e] = local;
         if (p.edge_index_local) p.edge_index_local[e] = (int64_t)local;  // row 0: sampled neighbor
+    }
+}
+
+// Weighted picks with replacement (sampler.rs:1383-1412): the reference sums the row's
+// weights in f64 in row order, draws u = next_u64 * (total / u64::MAX) k times and takes,
+// for each draw, the first position whose running sum exceeds u.  The running sums must
+// be the reference's own, rounding included, so every lane of the warp that owns the row
+// adds the weights in the same row order (redundantly: the loads are warp-wide
+// broadcasts) — once for the total, once more to place its own draw.  Lane t owns draw t
+// of the current round of 32.
+__global__ void __launch_bounds__(kPickThreads)
+k_pick_weighted_replace(const SampleParams *__restrict__ pa, uint32_t hop, uint32_t k) {
+    chain_sync();
+    const SampleParams &p = pa[blockIdx.y];
+    const StageInfo nx = p.state->stage[hop + 1];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (uint32_t j = blockIdx.x * (kPickThreads / 32) + warp; j < nx.frontier_n; j += gridDim.x * (kPickThreads / 32)) {
+        const FrontierEntry fe = p.frontier[j];
+        const uint32_t deg = fe.deg;
+        if (deg == 0 || k == 0) continue;
+        const float *w = p.weights + fe.off;
+        double total = 0.0;
+        for (uint32_t i = 0; i < deg; ++i) total += (double)__ldg(w + i);
+        const double scale = total / 18446744073709551615.0;  // u64::MAX as f64
+        for (uint32_t t0 = 0; t0 < k; t0 += 32) {
+            const uint32_t t = t0 + lane;
+            const bool mine = t < k;
+            const uint64_t bits = (p.rng_mode == AG_RNG_PHILOX)
+                ? (((uint64_t)philox_u32(p.seed, hop, fe.id, 2 * t) << 32) | philox_u32(p.seed, hop, fe.id, 2 * t + 1))
+                : wyrand_at(p.seed, fe.dbase + t);
+            const double u = __ull2double_rn(bits) * scale;
+            uint32_t idx = deg - 1;  // partition_point(c <= u) clamped to the last position
+            bool placed = !mine;
+            double c = 0.0;
+            for (uint32_t i = 0; i < deg; ++i) {
+                c += (double)__ldg(w + i);
+                if (!placed && !(c <= u)) { idx = i; placed = true; }
+                if (__all_sync(0xffffffffu, placed)) break;
+            }
+            if (mine) emit_edge(p, hop, nx.n_edges, fe, t, fe.off + idx);
+        }
     }
 }
 
@@ -816,7 +857,9 @@ void launch_pick(int mode, uint32_t k, uint64_t frontier_est, uint32_t n_batches
         const uint64_t b = (vertices + per_block - 1) / per_block;
         return (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>(b, std::max<uint64_t>(1, (uint64_t)kSMs * 16 / n_batches)));
     };
-    if (mode == kModeWeighted && k > 32) {
+    if (mode == kModeWeightedReplace) {
+        launch_chained(k_pick_weighted_replace, dim3(blocks_for(frontier_est, kPickThreads / 32), n_batches), dim3(kPickThreads), st, pa, hop, k);
+    } else if (mode == kModeWeighted && k > 32) {
         launch_chained(k_pick_weighted_large, dim3(blocks_for(frontier_est, 1), n_batches), dim3(kWLThreads), st, pa, hop, k);
     } else if (mode == kModeWeighted) {
         launch_chained(k_pick<32, kPickWeighted>, dim3(blocks_for(frontier_est, kPickThreads / 32), n_batches), dim3(kPickThreads), st, pa, hop, k);
@@ -996,8 +1039,6 @@ extern "C" int32_t ag_sampler_create_group(const ag_graph *g, const ag_sampling_
     // SamplerConfigError::WeightsMissing (sampler.rs:331-337)
     if (cfg->weighted && !g->weights)
         return fail(AG_ERR_VALUE, "weighted sampling requested, but the graph has no edge weights");
-    if (cfg->weighted && cfg->replace)
-        return fail(AG_ERR_VALUE, "weighted sampling with replacement is not supported on the GPU path");
     if (cfg->rng_mode != AG_RNG_WYRAND_EXACT && cfg->rng_mode != AG_RNG_PHILOX)
         return fail(AG_ERR_VALUE, "unknown rng_mode %d", cfg->rng_mode);
     for (uint32_t h = 0; h < cfg->num_hops; ++h) {
@@ -1011,7 +1052,7 @@ extern "C" int32_t ag_sampler_create_group(const ag_graph *g, const ag_sampling_
     s->cfg = *cfg;
     s->device = g->device;
     s->group = group;
-    s->mode = cfg->weighted ? kModeWeighted : (cfg->replace ? kModeReplace : kModeUniform);
+    s->mode = cfg->weighted ? (cfg->replace ? kModeWeightedReplace : kModeWeighted) : (cfg->replace ? kModeReplace : kModeUniform);
     s->seed = cfg->seed;
     int32_t st = AG_OK;
     do {
@@ -1262,7 +1303,7 @@ int32_t launch_saved_impl(ag_sampler *s, bool relaunch) {
             if (feats && B.x) {
                 set_gather_source(ga, feats);
                 ga.ids = B.nodes; ga.ids64 = 0;
-                ga.n = std::min<uint64_t>(bn, B.cap_nodes);
+                ga.n = std::min<uint64_t>(bn, B.cap_x ? std::min(B.cap_x, B.cap_nodes) : B.cap_nodes);
                 // rows to gather = nodes registered by the last stage (read on the device)
                 ga.n_dev = &s->state[b].stage[H + 1].n_nodes;
                 ga.out = B.x;

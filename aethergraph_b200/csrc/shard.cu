@@ -67,6 +67,7 @@ int32_t make_view(const ag_features *local, uint32_t world, uint32_t rank, bool 
 int32_t check_local(const ag_features *local, uint32_t world, uint32_t rank, const char *who) {
     if (world == 0 || world > 8 || rank >= world) return fail(AG_ERR_VALUE, "%s: bad rank %u of %u (at most 8 shards)", who, rank, world);
     if (local->shards) return fail(AG_ERR_VALUE, "%s: the local store is already a sharded view", who);
+    if (local->dtype == AG_I8) return fail(AG_ERR_VALUE, "%s: the int8 payload cannot be sharded", who);
     const uint64_t n = local->num_nodes;
     if (is_cyclic(local)) {
         const uint64_t rows = n > rank ? (n - rank + world - 1) / world : 0;

@@ -457,9 +457,37 @@ namespace {
 int32_t synth_feature_rows(uint64_t num_nodes, uint64_t dim, int32_t dtype, uint64_t seed, int32_t device,
                            uint64_t row_begin, uint64_t row_stride, uint64_t rows, ag_features **out) {
     if (!out) return fail(AG_ERR_VALUE, "ag_synth_features: null argument");
-    if (dtype < 0 || dtype > 2) return fail(AG_ERR_VALUE, "unknown feature dtype tag: %d", dtype);
+    if (dtype < 0 || dtype > AG_I8) return fail(AG_ERR_VALUE, "unknown feature dtype tag: %d", dtype);
     DeviceGuard guard(device);
     if (!guard.ok) return AG_ERR_CUDA;
+    if (dtype == AG_I8) {
+        // the same values as the f32 table, quantised block by block: generated and encoded a slab of rows at a time
+        if (row_stride != 1 || dim == 0) return fail(AG_ERR_VALUE, "the int8 payload is generated for contiguous rows of a non-zero dim");
+        const uint64_t bpr = (dim + kQuantBlock - 1) / kQuantBlock;
+        int8_t *codes = nullptr;
+        float *scales = nullptr, *slab = nullptr;
+        uint32_t *bad = nullptr;
+        const uint64_t slab_rows = std::max<uint64_t>(1, std::min<uint64_t>(rows, (256ull << 20) / (dim * 4)));
+        cudaError_t e = cudaMalloc(&codes, std::max<uint64_t>(rows * dim, 16));
+        if (e == cudaSuccess) e = cudaMalloc(&scales, std::max<uint64_t>(rows * bpr * 4, 16));
+        if (e == cudaSuccess) e = cudaMalloc(&slab, slab_rows * dim * 4);
+        if (e == cudaSuccess) e = cudaMalloc(&bad, 4);
+        if (e == cudaSuccess) e = cudaMemset(bad, 0, 4);
+        for (uint64_t r0 = 0; r0 < rows && e == cudaSuccess; r0 += slab_rows) {
+            const uint64_t m = std::min(slab_rows, rows - r0);
+            k_features<<<grid_for(m * dim), 256>>>((uint8_t *)slab, row_begin + r0, 1, m, dim, AG_F32, seed);
+            e = launch_encode_i8(slab, m, dim, codes + r0 * dim, scales + r0 * bpr, bad, 0);
+        }
+        if (e == cudaSuccess) e = cudaDeviceSynchronize();
+        cudaFree(slab); cudaFree(bad);
+        ag_features *f = nullptr;
+        int32_t st = e == cudaSuccess ? ag_features_adopt_device(codes, rows, dim, AG_I8, device, &f)
+                                      : fail(AG_ERR_CUDA, "int8 feature generation failed: %s", cudaGetErrorString(e));
+        if (st != AG_OK) { cudaFree(codes); cudaFree(scales); return st; }
+        f->num_nodes = num_nodes; f->row_begin = row_begin; f->rows = rows; f->owns_payload = true; f->scales = scales;
+        *out = f;
+        return AG_OK;
+    }
     uint8_t *payload = nullptr;
     AG_CUDA(cudaMalloc(&payload, std::max<uint64_t>(rows * dim * elem_size(dtype), 16)));
     k_features<<<grid_for(rows * dim), 256>>>(payload, row_begin, row_stride, rows, dim, dtype, seed);

@@ -19,7 +19,7 @@ __all__ = ["FeatureStore", "save_features"]
 
 def save_features(path, features, dtype: str = "f32") -> None:
     """Write an AETHFEAT file: 512-byte header, then rows in `dtype`."""
-    if dtype not in _lib.DTYPE_TAG:
+    if dtype not in ("f32", "f16", "bf16"):
         raise ValueError(f"Invalid dtype '{dtype}'. Must be 'f32', 'f16', or 'bf16'")
     f = np.asarray(features)
     if f.ndim != 2:
@@ -76,11 +76,15 @@ class FeatureStore:
 
     @staticmethod
     def from_array(features, dtype: str = "f32", *, device: int | None = None) -> "FeatureStore":
-        """Encode f32 rows (numpy, or a CUDA float32 tensor) into `dtype` on the device."""
+        """Encode f32 rows (numpy, or a CUDA float32 tensor) into `dtype` on the device.
+        `"i8"` is the reference's block-scaled int8 codec (one byte per element and one f32
+        scale per 32 elements of a row, crates/aethergraph-core/src/internal/feature_codec.rs):
+        lossy, a quarter of f32's bytes; gathers decode to exactly what the reference's
+        `BlockScaledI8::decode` gives."""
         import torch
 
         if dtype not in _lib.DTYPE_TAG:
-            raise ValueError(f"Invalid dtype '{dtype}'. Must be 'f32', 'f16', or 'bf16'")
+            raise ValueError(f"Invalid dtype '{dtype}'. Must be 'f32', 'f16', 'bf16', or 'i8'")
         out = C.c_void_p()
         dev = FeatureStore._dev(device)
         if isinstance(features, torch.Tensor):
@@ -185,9 +189,17 @@ class FeatureStore:
     def payload_to_host(self) -> np.ndarray:
         """The stored (encoded) rows held by this handle as a flat host array
         (float32 for f32 stores, uint16 bit patterns for f16 / bf16)."""
-        out = np.empty(self._rows * self._dim, dtype=np.float32 if self._dtype == _lib.AG_F32 else np.uint16)
+        kind = {_lib.AG_F32: np.float32, _lib.AG_I8: np.int8}.get(self._dtype, np.uint16)
+        out = np.empty(self._rows * self._dim, dtype=kind)
         if out.size:
             _lib.check(_lib.lib().ag_features_copy_to_host(self._h, out.ctypes.data))
+        return out
+
+    def scales_to_host(self) -> np.ndarray:
+        """`"i8"` stores: the per-block scales, f32 [rows, ceil(dim / 32)]."""
+        out = np.empty((self._rows, (self._dim + 31) // 32), dtype=np.float32)
+        if out.size:
+            _lib.check(_lib.lib().ag_features_scales_to_host(self._h, out.ctypes.data))
         return out
 
     def gather(self, ids, out=None, stream=None):

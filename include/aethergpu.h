@@ -110,7 +110,14 @@ void ag_graph_free(ag_graph *g);
  * header crates/aethergraph-core/src/features/header.rs:165-244).
  * The payload (num_nodes x dim elements of f32 / f16 / bf16) lives in HBM.
  */
-enum { AG_F32 = 0, AG_F16 = 1, AG_BF16 = 2 };
+enum { AG_F32 = 0, AG_F16 = 1, AG_BF16 = 2,
+       /* Block-scaled int8 (crates/aethergraph-core/src/internal/feature_codec.rs:1-60): one
+        * signed byte per element, row-major, plus one f32 scale per 32 elements of a row;
+        * scale = max|x| / 127 over the block, code = round(x / scale) clamped to +-127,
+        * decode = code * scale (one IEEE multiply: the gather's rows are bit-identical to
+        * the reference's BlockScaledI8::decode).  In-memory only (the reference defines no
+        * file layout for it): ag_features_from_f32, ag_synth_features.  Not shardable. */
+       AG_I8 = 3 };
 
 int32_t ag_features_save(const char *path, const float *features, uint64_t num_nodes,
                          uint64_t dim, int32_t dtype);
@@ -191,6 +198,8 @@ int32_t ag_features_gather_stats(const ag_features *f, uint64_t *rows_requested,
 int32_t ag_graph_hot_vertices(const ag_graph *g, uint64_t max_rows, uint32_t **ids_dev,
                               uint64_t *n_out);
 int32_t ag_features_cache_rows(ag_features *view, const uint32_t *ids_dev, uint64_t n);
+/* AG_I8 stores: the per-block scales (rows x ceil(dim / 32) f32) to host memory. */
+int32_t ag_features_scales_to_host(const ag_features *f, float *scales);
 /* Copies the stored (encoded) rows held by this handle back to host memory. */
 int32_t ag_features_copy_to_host(const ag_features *f, void *payload);
 
@@ -253,7 +262,11 @@ typedef struct {
     int64_t *edge_index_local; /* [2 * num_edges] packed at the final count (optional) */
     int64_t *e_id;          /* [cap_edges] int64(edge_ids)              (optional) */
     int64_t *seed_index;    /* [cap_seeds] int64(seed_locals)           (optional) */
-    float *x;               /* [cap_nodes, dim] gathered rows           (optional) */
+    float *x;               /* [cap_x or cap_nodes, dim] gathered rows  (optional) */
+    uint64_t cap_x;         /* rows x holds; 0 = cap_nodes.  A batch with more nodes gets its first
+                             * cap_x rows only (compare ag_sample_counts.num_nodes): the worst-case
+                             * node bound is many times a typical batch, so a caller may reserve x
+                             * from observed counts and gather the rare overflow again (ag_gather). */
 } ag_subgraph_buffers;
 
 typedef struct {

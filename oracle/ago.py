@@ -159,6 +159,10 @@ def lib():
         L.ago_encode_rows.argtypes = [C.c_void_p, C.c_size_t, C.c_int, C.c_void_p]
         L.ago_decode_rows.restype = None
         L.ago_decode_rows.argtypes = [C.c_void_p, C.c_size_t, C.c_int, C.c_void_p]
+        L.ago_encode_i8.restype = C.c_int
+        L.ago_encode_i8.argtypes = [C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p]
+        L.ago_gather_i8.restype = C.c_int64
+        L.ago_gather_i8.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_void_p, C.c_size_t, C.c_void_p]
         L.ago_gather.restype = C.c_int64
         L.ago_gather.argtypes = [C.c_void_p, C.c_uint64, C.c_uint64, C.c_int, C.c_void_p,
                                  C.c_size_t, C.c_void_p]
@@ -295,6 +299,31 @@ def gather(payload: np.ndarray, num_nodes: int, dim: int, dtype: str, ids) -> np
     out = np.empty((len(ids), dim), dtype=np.float32)
     rc = lib().ago_gather(payload.ctypes.data, num_nodes, dim, DTYPE_TAG[dtype],
                           ids.ctypes.data, len(ids), out.ctypes.data)
+    if rc != 0:
+        raise ValueError(f"node {int(ids[-1 - rc])} out of bounds")
+    return out
+
+
+def encode_i8(features) -> tuple[np.ndarray, np.ndarray]:
+    """Block-scaled int8 (internal/feature_codec.rs:73-112): (codes int8 [n, dim], scales f32 [n, ceil(dim / 32)])."""
+    f = np.ascontiguousarray(features, dtype=np.float32)
+    n, dim = f.shape
+    if dim == 0:
+        raise ValueError("feature_dim must be non-zero")
+    codes = np.zeros((n, dim), dtype=np.int8)
+    scales = np.zeros((n, (dim + 31) // 32), dtype=np.float32)
+    if lib().ago_encode_i8(f.ctypes.data, n, dim, codes.ctypes.data, scales.ctypes.data) != 0:
+        raise ValueError("feature values must be finite")
+    return codes, scales
+
+
+def gather_i8(codes: np.ndarray, scales: np.ndarray, ids) -> np.ndarray:
+    """Decoded rows `ids` of a block-scaled int8 table (feature_codec.rs:121-133)."""
+    ids = np.ascontiguousarray(ids, dtype=np.uint32)
+    n, dim = codes.shape
+    out = np.empty((len(ids), dim), dtype=np.float32)
+    rc = lib().ago_gather_i8(np.ascontiguousarray(codes).ctypes.data, np.ascontiguousarray(scales).ctypes.data, n, dim,
+                             ids.ctypes.data, len(ids), out.ctypes.data)
     if rc != 0:
         raise ValueError(f"node {int(ids[-1 - rc])} out of bounds")
     return out

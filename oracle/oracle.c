@@ -212,6 +212,56 @@ int64_t ago_gather(const void *payload, uint64_t num_nodes, uint64_t dim,
 }
 
 /* ======================================================================
+ * Block-scaled int8 feature codec (internal/feature_codec.rs:73-133)
+ * ==================================================================== */
+/* encode_rows: per 32-element block of a row, scale = max|x| / 127 (0 for an
+ * all-zero block, whose codes stay 0), code = round(x / scale) clamped to
+ * [-127, 127] (f32::round: half away from zero).  Returns -1 for a value that is
+ * not finite (FeatureCodecError::NotFinite), -2 for dim == 0. */
+int ago_encode_i8(const float *values, size_t rows, size_t dim, int8_t *codes, float *scales) {
+    if (dim == 0) return -2;
+    size_t per_row = (dim + 31) / 32;
+    memset(codes, 0, rows * dim);
+    for (size_t row = 0; row < rows; ++row) {
+        const float *src = values + row * dim;
+        for (size_t b = 0; b < per_row; ++b) {
+            size_t lo = b * 32, hi = lo + 32 < dim ? lo + 32 : dim;
+            float peak = 0.0f;
+            for (size_t i = lo; i < hi; ++i) {
+                if (!isfinite(src[i])) return -1;
+                float a = fabsf(src[i]);
+                if (a > peak) peak = a;
+            }
+            float scale = peak == 0.0f ? 0.0f : peak / 127.0f;
+            scales[row * per_row + b] = scale;
+            if (scale == 0.0f) continue;
+            for (size_t i = lo; i < hi; ++i) {
+                float q = roundf(src[i] / scale);
+                if (q < -127.0f) q = -127.0f;
+                if (q > 127.0f) q = 127.0f;
+                codes[row * dim + i] = (int8_t)q;
+            }
+        }
+    }
+    return 0;
+}
+
+/* decode_into (feature_codec.rs:121-133) of the rows `ids`, in ids order:
+ * out[i][e] = (float)codes[ids[i]][e] * scales[ids[i]][e / 32]. */
+int64_t ago_gather_i8(const int8_t *codes, const float *scales, uint64_t num_nodes, uint64_t dim,
+                      const uint32_t *ids, size_t n, float *out) {
+    for (size_t i = 0; i < n; ++i)
+        if ((uint64_t)ids[i] >= num_nodes) return -1 - (int64_t)i;
+    size_t per_row = (dim + 31) / 32;
+    for (size_t i = 0; i < n; ++i) {
+        const int8_t *c = codes + (size_t)ids[i] * dim;
+        const float *sc = scales + (size_t)ids[i] * per_row;
+        for (size_t e = 0; e < dim; ++e) out[i * dim + e] = (float)c[e] * sc[e / 32];
+    }
+    return 0;
+}
+
+/* ======================================================================
  * CRC32 (IEEE 802.3, reflected, poly 0xEDB88320) — mmap.rs:642-652
  * ==================================================================== */
 uint32_t ago_crc32(uint32_t crc, const void *data, size_t len) {
@@ -491,13 +541,38 @@ static void sample_weighted(ago_sampler *s, uint32_t node, uint32_t node_local,
     }
 }
 
+/* sampler.rs:1383-1412: cumulative weights summed in f64 in row order, then k
+ * draws u = next_u64 * (total / u64::MAX), each picking the first position whose
+ * cumulative weight exceeds u (partition_point(c <= u), clamped to the last). */
+static void sample_weighted_replace(ago_sampler *s, uint32_t node, uint32_t node_local,
+                                    const uint32_t *nb, const float *w, uint64_t n,
+                                    uint64_t edge_offset, uint64_t k) {
+    if (n == 0) return;
+    if (s->wkeys_cap < n) { s->wkeys_cap = n * 2; s->wkeys = (wkey_t *)realloc(s->wkeys, s->wkeys_cap * sizeof(wkey_t)); }
+    double total = 0.0;
+    for (uint64_t i = 0; i < n; ++i) { total += (double)w[i]; s->wkeys[i].key = total; }
+    double scale = total / 18446744073709551615.0; /* u64::MAX as f64 */
+    for (uint64_t t = 0; t < k; ++t) {
+        uint64_t bits = ago_wyrand_next_u64(&s->rng);
+        s->draws++;
+        double u = (double)bits * scale;
+        uint64_t lo = 0, hi = n; /* partition_point: first i with !(c_i <= u) */
+        while (lo < hi) {
+            uint64_t mid = lo + (hi - lo) / 2;
+            if (s->wkeys[mid].key <= u) lo = mid + 1; else hi = mid;
+        }
+        uint64_t idx = lo < n - 1 ? lo : n - 1;
+        emit_edge(s, node, node_local, nb[idx], edge_offset + idx);
+    }
+}
+
 /* sampler.rs:1178-1235 (no hub cap: max_degree is None on this path) */
 static void sample_normal(ago_sampler *s, uint32_t node, uint32_t node_local,
                           const uint32_t *nb, const float *w, uint64_t n,
                           uint64_t edge_offset, uint64_t k) {
     if (w) {
-        /* weighted with replacement (sampler.rs:1383-1412) is outside this path */
-        sample_weighted(s, node, node_local, nb, w, n, edge_offset, k);
+        if (s->replace) sample_weighted_replace(s, node, node_local, nb, w, n, edge_offset, k);
+        else sample_weighted(s, node, node_local, nb, w, n, edge_offset, k);
         return;
     }
     if (s->replace) { /* sampler.rs:1289-1308 */

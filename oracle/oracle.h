@@ -85,6 +85,10 @@ void ago_decode_rows(const void *src, size_t count, int dtype, float *dst);
 /* crates/aethergraph-core/src/features/store.rs:777-838 (get_batch_into).
  * payload: num_nodes rows of dim elements of `dtype`; ids are checked against
  * num_nodes first.  Returns 0, or -1 - (position of the first bad id). */
+/* internal/feature_codec.rs:73-133 (block-scaled int8) */
+int ago_encode_i8(const float *values, size_t rows, size_t dim, int8_t *codes, float *scales);
+int64_t ago_gather_i8(const int8_t *codes, const float *scales, uint64_t num_nodes, uint64_t dim,
+                      const uint32_t *ids, size_t n, float *out);
 int64_t ago_gather(const void *payload, uint64_t num_nodes, uint64_t dim,
                    int dtype, const uint32_t *ids, size_t n, float *out);
 

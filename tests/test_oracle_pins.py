@@ -380,3 +380,38 @@ def test_hetero_file_layout_follows_the_reference(tmp_path):
     assert np.frombuffer(raw[body + 32:body + 44], np.uint32).tolist() == [0, 1, 1] and raw[body + 44:body + 48] == bytes(4)
     nt2, rels2 = ago.read_hetero_file(p)
     assert nt2 == nt and rels2[1][5].tolist() == [1.0, 2.0] and rels2[0][4].tolist() == [0, 1, 1]
+
+
+def test_block_scaled_int8_codec_follows_the_reference_tests():
+    """crates/aethergraph-core/src/internal/feature_codec.rs tests (:182-262): values come
+    back within half a quantisation step of their block; the scale is per block, not per
+    row; an all-zero block round-trips exactly with scale 0; a partial trailing block is
+    encoded; NaN / infinite values and dim 0 are refused; 1.125 bytes per feature."""
+    from oracle import ago
+
+    ramp = lambda rows, dim: (np.arange(rows * dim, dtype=np.float32) * np.float32(0.25) - np.float32(3.0)).reshape(rows, dim)
+    src = ramp(4, 96)
+    codes, scales = ago.encode_i8(src)
+    out = ago.gather_i8(codes, scales, np.arange(4))
+    for b in range(3):
+        blk = slice(32 * b, 32 * b + 32)
+        step = np.abs(src[:, blk]).max(axis=1, keepdims=True) / 127.0
+        assert np.all(np.abs(src[:, blk] - out[:, blk]) <= step * 0.5 + 1e-6)
+    row = np.zeros((1, 64), dtype=np.float32)
+    row[0, 0], row[0, 32], row[0, 33] = 1000.0, 0.5, -0.25
+    codes, scales = ago.encode_i8(row)
+    out = ago.gather_i8(codes, scales, [0])
+    assert scales.shape == (1, 2) and abs(out[0, 32] - 0.5) < 0.01 and abs(out[0, 33] + 0.25) < 0.01
+    codes, scales = ago.encode_i8(np.zeros((2, 32), dtype=np.float32))
+    assert np.all(scales == 0) and np.all(ago.gather_i8(codes, scales, [0, 1]) == 0)
+    codes, scales = ago.encode_i8(ramp(2, 40))
+    assert scales.shape == (2, 2) and codes.shape == (2, 40)
+    for bad in ([[1.0, np.nan]], [[np.inf, 1.0]]):
+        with pytest.raises(ValueError, match="finite"):
+            ago.encode_i8(np.array(bad, dtype=np.float32))
+    with pytest.raises(ValueError, match="non-zero"):
+        ago.encode_i8(np.zeros((3, 0), dtype=np.float32))
+    codes, scales = ago.encode_i8(ramp(8, 128))
+    assert abs((codes.size + scales.size * 4) / (codes.size * 4) - 1.125 / 4.0) < 1e-9
+    # codes are symmetric, clamped to +-127, the peak of a block is +-127
+    assert codes.min() >= -127 and np.all(np.abs(codes.reshape(8, 4, 32)).max(axis=2) == 127)

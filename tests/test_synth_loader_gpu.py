@@ -205,3 +205,29 @@ def test_seed_sequence_makes_batches_independent_of_the_rank_count(ag, ago, worl
         from aethergraph_b200 import _lib
         assert _lib.lib().ag_loader_set_seed_sequence(ld._h, 1, 2) == _lib.AG_ERR_VALUE  # only before the first submit
         ld.next_batch()
+
+
+def test_pooled_x_is_reserved_from_observed_counts_and_outgrown_batches_are_gathered_again(ag, ago, world):
+    """The loader's own batch buffers reserve feature rows for 1.5 x the largest batch seen
+    so far, not for the worst-case bound; a batch that outgrows the reservation gets every
+    row all the same (exact second gather), and later buffers are sized for it."""
+    n, g, feats, off, dst, payload = world
+    cfg = ag.SamplingConfig(num_neighbors=[10, 5], seed=21)
+    s = ago.Sampler(off, dst, [10, 5], seed=21)
+    rng = np.random.default_rng(3)
+    small = [rng.integers(0, n, 300)[:2].astype(np.uint32) for _ in range(6)]
+    big = [rng.integers(0, n, 300).astype(np.uint32) for _ in range(6)]
+    with ag.NeighborLoader(g, cfg, prefetch_depth=4, sampler_threads=1, features=feats, group=2) as ld:
+        seq = 0
+        for phase in (small, big, small):
+            ld.submit_epoch(phase, list(range(seq, seq + len(phase))))
+            for b in phase:
+                idx, sg, x = ld.next_batch()
+                s.reseed(ago.batch_seed(21, seq))
+                want = s.sample(b)
+                assert idx == seq and np.array_equal(sg.raw_u32()["nodes"], want["nodes"])
+                xw = ago.gather(payload, n, 32, "f16", want["nodes"])
+                assert x.shape[0] == len(want["nodes"])
+                assert np.array_equal(x.cpu().numpy().view(np.uint32), xw.view(np.uint32)), seq
+                seq += 1
+                del sg, x   # hand the pooled buffers back

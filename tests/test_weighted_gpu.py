@@ -131,3 +131,43 @@ def test_large_weighted_fanout_matches_the_oracle(fanout):
     want = ago.Sampler(off, dst, fanout, weights=w, weighted=True, seed=9).sample(seeds)
     assert_same_subgraph(got, want)
     assert want["num_sampled_edges"][0] > 0
+
+
+@pytest.mark.parametrize("fanout", [[4], [10, 5], [40, 3]])
+def test_weighted_with_replacement_matches_the_oracle(fanout):
+    """sampler.rs:1383-1412: k draws over the row's cumulative weights (f64 sums in row
+    order), repeats allowed.  Every array bit for bit, loader included."""
+    import aethergraph_b200 as ag
+    from helpers import assert_same_subgraph, rmat_csr
+    from oracle import ago
+
+    n, off, dst, w = rmat_csr(11, 20, seed=8, weighted=True)
+    g = ag.Graph.from_csr(off, dst, w)
+    seeds = np.random.default_rng(2).integers(0, n, 200).astype(np.uint32)
+    cfg = ag.SamplingConfig(num_neighbors=fanout, weighted=True, replace=True, seed=13)
+    s = ag.NeighborSampler(g, cfg)
+    o = ago.Sampler(off, dst, fanout, weights=w, weighted=True, replace=True, seed=13)
+    for _ in range(2):   # the handle's stream continues across calls
+        assert_same_subgraph(s.sample(seeds).raw_u32(), o.sample(seeds))
+    with ag.NeighborLoader(g, cfg, prefetch_depth=2, sampler_threads=2, group=4) as ld:
+        ld.submit_epoch([seeds[:50], seeds[50:120], seeds[120:]])
+        for i, part in enumerate((seeds[:50], seeds[50:120], seeds[120:])):
+            _, sg, _ = ld.next_batch()
+            o.reseed(ago.batch_seed(13, i))
+            assert_same_subgraph(sg.raw_u32(), o.sample(part))
+
+
+def test_heavy_edge_with_replacement_as_the_reference_tests_it():
+    """sampler.rs:2574-2618 verbatim: weights [100, 1, 1, 1], fanout [1], replace = true,
+    seeds 123 + trial; the heavy edge must win more than 500 of 1000 trials."""
+    import aethergraph_b200 as ag
+
+    off = np.array([0, 4, 4, 4, 4, 4], dtype=np.uint64)
+    g = ag.Graph.from_csr(off, np.array([1, 2, 3, 4], dtype=np.uint32), np.array([100.0, 1.0, 1.0, 1.0], dtype=np.float32))
+    heavy = 0
+    for trial in range(1000):
+        s = ag.NeighborSampler(g, ag.SamplingConfig(num_neighbors=[1], weighted=True, replace=True, seed=123 + trial))
+        sg = s.sample(np.array([0], dtype=np.uint32)).raw_u32()
+        assert len(sg["edge_dst"]) == 1
+        heavy += int(sg["edge_dst"][0] == 1)
+    assert heavy > 500, f"the heavy edge won {heavy} of 1000 trials"
