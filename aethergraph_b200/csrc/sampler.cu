@@ -56,8 +56,9 @@ namespace ag {
 namespace {
 
 constexpr int kTile = 512;      // threads per block of the assign kernel
-constexpr int kIPT = 4;         // items per thread
-constexpr int kTileItems = kTile * kIPT;  // items per tile of the single-pass scan
+// Items per thread of the assign kernel.  The last stage holds no row bounds per item,
+// so it can afford twice as many table probes in flight per thread.
+template <bool HAS_NEXT> struct AssignShape { static constexpr int kIPT = HAS_NEXT ? 4 : 8; static constexpr int kTileItems = kTile * kIPT; };
 constexpr int kPickThreads = 256;
 constexpr int kLargeK = 1024;   // largest fanout the k > 32 path keeps in shared memory
 
@@ -156,13 +157,13 @@ __device__ __forceinline__ uint32_t draw_u32(const SampleParams &p, uint32_t hop
     return (uint32_t)wyrand_at(p.seed, dbase + slot);  // next_u32: genstamp.rs:199-201
 }
 
-// Edge t of vertex fe at hop `hop` (= item fe.ebase + t of stage hop + 1).
-__device__ __forceinline__ void emit_edge(const SampleParams &p, uint32_t hop, uint32_t edges_before,
-                                          const FrontierEntry &fe, uint32_t t, uint64_t pos) {
+// Edge t of vertex fe at hop `hop` (= item fe.ebase + t of stage hop + 1), its
+// destination d already loaded from CSR position pos.
+__device__ __forceinline__ void emit_edge_loaded(const SampleParams &p, uint32_t hop, uint32_t edges_before,
+                                                 const FrontierEntry &fe, uint32_t t, uint64_t pos, uint32_t d) {
     const uint32_t e_rel = fe.ebase + t;
     const uint64_t e = (uint64_t)edges_before + e_rel;
     if (e >= p.cap_edges || e_rel >= kMaxPos) { atomicOr(&p.state->error, kErrCapacity); return; }
-    const uint32_t d = ld_stream_u32(p.dst + pos);
     if (p.edge_src) p.edge_src[e] = fe.id;
     p.edge_dst[e] = d;
     if (p.edge_ids) p.edge_ids[e] = pos;
@@ -178,51 +179,72 @@ __device__ __forceinline__ void emit_edge(const SampleParams &p, uint32_t hop, u
     p.slot_of_edge[e] = table_insert_min(p.table, d, enc_pending(p.table.gen, hop + 1, e_rel), &p.state->error);
 }
 
+__device__ __forceinline__ void emit_edge(const SampleParams &p, uint32_t hop, uint32_t edges_before,
+                                          const FrontierEntry &fe, uint32_t t, uint64_t pos) {
+    const uint32_t e_rel = fe.ebase + t;
+    if ((uint64_t)edges_before + e_rel >= p.cap_edges || e_rel >= kMaxPos) { atomicOr(&p.state->error, kErrCapacity); return; }
+    emit_edge_loaded(p, hop, edges_before, fe, t, pos, ld_stream_u32(p.dst + pos));
+}
+
 __device__ __forceinline__ bool key_less(double ka, uint32_t pa, double kb, uint32_t pb) {
     return ka < kb || (ka == kb && pa < pb);
 }
 
-// Fanout <= G <= 32: G lanes per vertex, lane t owns edge slot t.
+// Fanout <= G <= 32: G lanes per vertex, lane t owns edge slot t.  A lane group works
+// on two vertices per round, so the two destination loads (random sectors of the CSR)
+// and the table probes behind them are in flight together.
 template <int G>
 __device__ __forceinline__ void pick_small(const SampleParams &p, uint32_t hop, uint32_t k, uint32_t edges_before,
                                            const FrontierEntry *fes, uint32_t n) {
+    constexpr int U = 2;
     const uint32_t t = threadIdx.x % G;
     const uint32_t gshift = (threadIdx.x & 31) & ~(G - 1);
     const uint32_t gmask = (G == 32) ? 0xffffffffu : ((1u << G) - 1u);
+    constexpr uint32_t kPerBlock = kPickThreads / G;
     // Grid-stride over the frontier; the loop bound is block-uniform.
-    for (uint32_t base = blockIdx.x * (kPickThreads / G); base < n; base += gridDim.x * (kPickThreads / G)) {
-        const uint32_t j = base + threadIdx.x / G;
-        const bool active = j < n;
-        FrontierEntry fe{};
-        if (active) fe = fes[j];
-        const uint32_t deg = fe.deg;
-        const bool sampled = active && p.mode != kModeReplace && deg > k;  // Floyd row
-        uint32_t pick = t;                                                  // take-all: row order
-        uint32_t ip = 0;
-        if (active && p.mode == kModeReplace && deg > 0 && t < k) {
-            // sampler.rs:1298-1300: k independent draws over the whole row
-            pick = (uint32_t)(((uint64_t)draw_u32(p, hop, fe.id, fe.dbase, t) * deg) >> 32);
-        } else if (sampled && t < k) {
-            // sampler.rs:1345-1346: i runs over deg-k .. deg-1, j = rand_below(i + 1)
-            ip = deg - k + t;
-            pick = (uint32_t)(((uint64_t)draw_u32(p, hop, fe.id, fe.dbase, t) * ((uint64_t)ip + 1)) >> 32);
-        }
-        // Floyd's "already taken?" is sequential in t (sampler.rs:1347-1352):
-        // resolve slot s against the finished slots below it, one ballot per s.
-        if (__any_sync(0xffffffffu, sampled)) {
-            for (uint32_t s = 1; s < k; ++s) {
-                const uint32_t js = __shfl_sync(0xffffffffu, pick, s, G);
-                const bool hit = sampled && t < s && pick == js;
-                const uint32_t m = (__ballot_sync(0xffffffffu, hit) >> gshift) & gmask;
-                if (sampled && t == s && m) pick = ip;
+    for (uint32_t base = blockIdx.x * kPerBlock * U; base < n; base += gridDim.x * kPerBlock * U) {
+        FrontierEntry fe[U];
+        uint32_t pick[U];
+        bool emit[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const uint32_t j = base + u * kPerBlock + threadIdx.x / G;
+            const bool active = j < n;
+            fe[u] = FrontierEntry{};
+            if (active) fe[u] = fes[j];
+            const uint32_t deg = fe[u].deg;
+            const bool sampled = active && p.mode != kModeReplace && deg > k;  // Floyd row
+            pick[u] = t;                                                         // take-all: row order
+            uint32_t ip = 0;
+            if (active && p.mode == kModeReplace && deg > 0 && t < k) {
+                // sampler.rs:1298-1300: k independent draws over the whole row
+                pick[u] = (uint32_t)(((uint64_t)draw_u32(p, hop, fe[u].id, fe[u].dbase, t) * deg) >> 32);
+            } else if (sampled && t < k) {
+                // sampler.rs:1345-1346: i runs over deg-k .. deg-1, j = rand_below(i + 1)
+                ip = deg - k + t;
+                pick[u] = (uint32_t)(((uint64_t)draw_u32(p, hop, fe[u].id, fe[u].dbase, t) * ((uint64_t)ip + 1)) >> 32);
             }
-        }
-        if (active) {
-            uint32_t take;
+            // Floyd's "already taken?" is sequential in t (sampler.rs:1347-1352):
+            // resolve slot s against the finished slots below it, one ballot per s.
+            if (__any_sync(0xffffffffu, sampled)) {
+                for (uint32_t s = 1; s < k; ++s) {
+                    const uint32_t js = __shfl_sync(0xffffffffu, pick[u], s, G);
+                    const bool hit = sampled && t < s && pick[u] == js;
+                    const uint32_t m = (__ballot_sync(0xffffffffu, hit) >> gshift) & gmask;
+                    if (sampled && t == s && m) pick[u] = ip;
+                }
+            }
+            uint32_t take = 0;
             uint64_t draws;
-            row_demand(p.mode, deg, k, take, draws);
-            if (t < take) emit_edge(p, hop, edges_before, fe, t, fe.off + pick);
+            if (active) row_demand(p.mode, deg, k, take, draws);
+            emit[u] = t < take;
         }
+        uint32_t d[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) d[u] = emit[u] ? ld_stream_u32(p.dst + fe[u].off + pick[u]) : 0u;
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            if (emit[u]) emit_edge_loaded(p, hop, edges_before, fe[u], t, fe[u].off + pick[u], d[u]);
     }
 }
 
@@ -585,6 +607,7 @@ template <bool HAS_NEXT>
 __global__ void __launch_bounds__(kTile, 2)
 k_assign(const SampleParams *__restrict__ pa, uint32_t stage, uint32_t k) {
     constexpr bool has_next = HAS_NEXT;  // the last stage queues no frontier
+    constexpr int kIPT = AssignShape<HAS_NEXT>::kIPT, kTileItems = AssignShape<HAS_NEXT>::kTileItems;
     chain_sync();
     __shared__ uint32_t s_tile;
     __shared__ ScanVal s_warp[kTile / 32];
@@ -617,8 +640,8 @@ k_assign(const SampleParams *__restrict__ pa, uint32_t stage, uint32_t k) {
     // The grid is sized for a typical batch, not for the worst case: a block
     // keeps drawing tile tickets until they run out.  Tickets are handed out in
     // order, so the tiles a look-back (or a pending vertex) waits for are always
-    // already running.  A thread owns kIPT consecutive items of its tile, so that
-    // many table probes (and row-bound loads) are in flight per thread, and the
+    // already running.  A thread owns kIPT (4, last stage 8) consecutive items of its tile,
+    // so that many table probes (and row-bound loads) are in flight per thread, and the
     // barriers, the ticket and the look-back are paid once per kTile * kIPT items.
     for (;;) {
         if (threadIdx.x == 0) s_tile = atomicAdd(&bs->ticket, 1u);
@@ -869,7 +892,7 @@ void launch_pick(int mode, uint32_t k, uint64_t frontier_est, uint32_t n_batches
         launch_chained(k_pick<32, kPickLarge>, dim3(blocks_for(frontier_est, 4), n_batches), dim3(128), st, pa, hop, k);
     } else {
         const uint32_t G = k <= 4 ? 4 : k <= 8 ? 8 : k <= 16 ? 16 : 32;
-        const dim3 grid(blocks_for(frontier_est, kPickThreads / G), n_batches);
+        const dim3 grid(blocks_for(frontier_est, 2 * kPickThreads / G), n_batches);  // two vertices per lane group and round
         switch (G) {
             case 4: launch_chained(k_pick<4, kPickSmall>, grid, dim3(kPickThreads), st, pa, hop, k); break;
             case 8: launch_chained(k_pick<8, kPickSmall>, grid, dim3(kPickThreads), st, pa, hop, k); break;
@@ -1325,8 +1348,9 @@ int32_t launch_saved_impl(ag_sampler *s, bool relaunch) {
     // Grids cover the worst case only up to about two waves of resident blocks
     // over the whole group; the expand kernel draws tile tickets beyond that, so
     // a batch far below its bound does not pay for thousands of empty blocks.
-    auto tiles_for = [&](uint64_t items) {
-        const uint64_t blocks = (items + kTileItems - 1) / kTileItems;
+    auto tiles_for = [&](uint64_t items, bool last) {
+        const uint64_t per = last ? AssignShape<false>::kTileItems : AssignShape<true>::kTileItems;
+        const uint64_t blocks = (items + per - 1) / per;
         return (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>(blocks, std::max<uint64_t>(1, (uint64_t)kSMs * 8 / n_batches)));
     };
     if (nmax) k_insert_seeds<<<dim3((nmax + 255) / 256, n_batches), 256, 0, st>>>(pa);
@@ -1335,8 +1359,8 @@ int32_t launch_saved_impl(ag_sampler *s, bool relaunch) {
         const bool has_next = stage < H;
         const uint32_t k = has_next ? s->cfg.fanout[stage] : 0;
         const uint64_t expect = (stage && s->est_items[stage]) ? std::min(items, s->est_items[stage]) : items;
-        if (has_next) launch_chained(k_assign<true>, dim3(tiles_for(expect), n_batches), dim3(kTile), st, pa, stage, k);
-        else launch_chained(k_assign<false>, dim3(tiles_for(expect), n_batches), dim3(kTile), st, pa, stage, k);
+        if (has_next) launch_chained(k_assign<true>, dim3(tiles_for(expect, false), n_batches), dim3(kTile), st, pa, stage, k);
+        else launch_chained(k_assign<false>, dim3(tiles_for(expect, true), n_batches), dim3(kTile), st, pa, stage, k);
         if (has_next && k) {
             // the new vertices of this stage are at most its items
             launch_pick(s->mode, k, std::min<uint64_t>(expect, g->num_nodes), n_batches, st, pa, stage);
