@@ -23,7 +23,7 @@ AG_RNG_WYRAND_EXACT, AG_RNG_PHILOX = 0, 1
 RNG_MODE = {"wyrand_exact": AG_RNG_WYRAND_EXACT, "philox": AG_RNG_PHILOX,
             "philox_fast": AG_RNG_PHILOX}
 AG_MAX_HOPS = 8
-AG_IPC_HANDLE_BYTES = 64
+AG_IPC_HANDLE_BYTES = 128
 SHARD_LAYOUT = {"range": 0, "cyclic": 1}
 
 
@@ -122,6 +122,7 @@ SIGNATURES = {
     "ag_features_shard": (C.c_int32, [_P, _U64P, _U64P]),
     "ag_features_scales_to_host": (C.c_int32, [_P, _P]),
     "ag_features_gather_stats": (C.c_int32, [_P, _U64P, _U64P, _U64P]),
+    "ag_features_set_gather_order": (C.c_int32, [_P, C.c_int32]),
     "ag_graph_hot_vertices": (C.c_int32, [_P, C.c_uint64, _PP, _U64P]),
     "ag_features_cache_rows": (C.c_int32, [_P, _P, C.c_uint64]),
     "ag_graph_free": (None, [_P]),

@@ -762,8 +762,11 @@ ag_features *new_features(int device, uint64_t n, uint64_t begin, uint64_t rows,
 }
 
 int32_t alloc_features(ag_features *f, bool alloc_payload) {
-    if (alloc_payload)
-        AG_CUDA(cudaMalloc(&f->payload, std::max<uint64_t>(f->rows * f->dim * elem_size(f->dtype), 16)));
+    if (alloc_payload) {
+        // a block peers can map with large pages, should the store become a shard of a view
+        AG_TRY(alloc_feature_payload(f->device, std::max<uint64_t>(f->rows * f->dim * elem_size(f->dtype), 16), &f->payload,
+                                     &f->block));
+    }
     if (alloc_payload && f->dtype == AG_I8)
         AG_CUDA(cudaMalloc(&f->scales, std::max<uint64_t>(f->rows * ((f->dim + kQuantBlock - 1) / kQuantBlock) * 4, 16)));
     AG_CUDA(cudaMalloc(&f->err, 32));  // error bits, then the gather counters (internal.h)
@@ -834,8 +837,12 @@ extern "C" int32_t ag_features_save(const char *path, const float *features, uin
 extern "C" void ag_features_free(ag_features *f) {
     if (!f) return;
     DeviceGuard guard(f->device);
-    if (f->owns_payload) { cudaFree(f->payload); cudaFree(f->scales); }
+    if (f->owns_payload) {
+        if (f->block) peer_block_free(f->block); else cudaFree(f->payload);
+        cudaFree(f->scales);
+    }
     for (void *p : f->ipc_opened) if (p) cudaIpcCloseMemHandle(p);
+    for (PeerBlock *b : f->peer_opened) if (b) peer_block_free(b);
     if (f->sort) {
         if (f->sort->done) { cudaEventSynchronize(f->sort->done); cudaEventDestroy(f->sort->done); }
         f->sort->scratch.release();

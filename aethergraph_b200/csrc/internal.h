@@ -32,6 +32,20 @@ struct ag_graph {
     float *weights = nullptr;     // device, num_edges or null
 };
 
+namespace ag {
+// Device memory that peers map with 2 MB pages (peer_block.cu).
+struct PeerBlock;
+int32_t peer_block_alloc(int device, size_t bytes, PeerBlock **out);
+int32_t alloc_feature_payload(int device, size_t bytes, uint8_t **ptr, PeerBlock **block);  // a block, or cudaMalloc when asked
+void peer_block_free(PeerBlock *b);
+void *peer_block_ptr(const PeerBlock *b);
+int32_t peer_block_grant(PeerBlock *b, int reader_device);            // same process, another GPU
+int32_t peer_block_export(PeerBlock *b, void *handle_out);            // AG_IPC_HANDLE_BYTES
+int32_t peer_block_import(const void *handle, int device, PeerBlock **out);
+int peer_handle_kind(const void *handle);                             // 0 empty, 1 legacy CUDA IPC, 2 shareable block
+void peer_handle_mark_legacy(void *handle);
+}  // namespace ag
+
 struct ag_features {
     int device = 0;
     uint64_t num_nodes = 0;   // rows of the whole store
@@ -56,7 +70,11 @@ struct ag_features {
     uint8_t *hot_rows = nullptr;              // device, hot_n * row bytes
     uint32_t *hot_slot = nullptr;             // device, num_nodes entries
     uint64_t hot_n = 0;
-    void *ipc_opened[8] = {nullptr};          // peer mappings this view opened (closed on free)
+    void *ipc_opened[8] = {nullptr};          // legacy CUDA IPC mappings this view opened (closed on free)
+    struct ag::PeerBlock *peer_opened[8] = {nullptr};  // peers' shareable blocks this view mapped (unmapped on free)
+    struct ag::PeerBlock *block = nullptr;    // the payload's own shareable block (null: a plain device allocation)
+    bool legacy_peer = false;                 // some peer is mapped through a legacy CUDA IPC handle (small pages)
+    int gather_order = 0;                     // AG_GATHER_AUTO / _ORDERED / _DIRECT (ag_features_set_gather_order)
     // ag_gather on a sharded view sorts its ids into address order first; the scratch
     // belongs to the view, calls take turns (mutex on the host, event on the device).
     struct SortState {

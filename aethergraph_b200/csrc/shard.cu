@@ -5,8 +5,11 @@
 // (python/aethergraph/ray/datasource.py:6-10 keeps the topology replicated and
 // the features partitioned; crates/aether-stream's RDMA gather is its transport).
 // On one NVSwitch node the transport is a plain load: every GPU maps its peers'
-// shards (CUDA IPC across processes, peer access inside one process) and the
-// gather kernel reads row v straight out of the owner's HBM.  The stored
+// shards and the gather kernel reads row v straight out of the owner's HBM.  A
+// payload the library allocated is a shareable block (peer_block.cu) that peers map
+// with 2 MB pages, across processes or inside one; a payload adopted from the caller
+// falls back to a legacy CUDA IPC handle, whose mapping is an order of magnitude
+// slower to read at random once tens of GB are mapped.  The stored
 // (bf16 / f16) row crosses NVLink; the upcast happens at the reader.  There is no
 // staging buffer, no collective, and nothing here uses TMA.
 //
@@ -30,7 +33,7 @@ namespace {
 bool is_cyclic(const ag_features *f) { return f->row_stride > 1; }
 
 int32_t make_view(const ag_features *local, uint32_t world, uint32_t rank, bool cyclic, const uint8_t *const *bases,
-                  void *const *opened, ag_features **out) {
+                  void *const *opened, PeerBlock *const *blocks, ag_features **out) {
     const uint64_t n = local->num_nodes;
     const uint64_t shard_rows = (n + world - 1) / world;
     ag_features *v = new ag_features();
@@ -43,7 +46,8 @@ int32_t make_view(const ag_features *local, uint32_t world, uint32_t rank, bool 
     v->shard_rows = cyclic ? (n + world - 1) / world : std::max<uint64_t>(shard_rows, 1);
     v->shard_cyclic = cyclic;
     v->sort = new ag_features::SortState();
-    for (uint32_t r = 0; r < world && opened; ++r) v->ipc_opened[r] = opened[r];
+    for (uint32_t r = 0; r < world && opened; ++r) { v->ipc_opened[r] = opened[r]; v->legacy_peer |= opened[r] != nullptr; }
+    for (uint32_t r = 0; r < world && blocks; ++r) v->peer_opened[r] = blocks[r];
     ag_shard_table t{};
     for (uint32_t r = 0; r < world; ++r) t.base[r] = bases[r];
     t.shard_rows = std::max<uint64_t>(shard_rows, 1);
@@ -90,14 +94,16 @@ int32_t check_local(const ag_features *local, uint32_t world, uint32_t rank, con
 
 extern "C" int32_t ag_features_ipc_export(const ag_features *f, void *handle_out) {
     if (!f || !handle_out) return fail(AG_ERR_VALUE, "ag_features_ipc_export: null argument");
-    static_assert(sizeof(cudaIpcMemHandle_t) == AG_IPC_HANDLE_BYTES, "IPC handle size");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64 && AG_IPC_HANDLE_BYTES >= 128, "IPC handle size");
     DeviceGuard guard(f->device);
     if (!guard.ok) return AG_ERR_CUDA;
     memset(handle_out, 0, AG_IPC_HANDLE_BYTES);
     if (!f->payload || f->rows == 0) return AG_OK;  // an empty shard has nothing to map
+    if (f->block) return peer_block_export(f->block, handle_out);
     cudaIpcMemHandle_t h;
     AG_CUDA(cudaIpcGetMemHandle(&h, f->payload));
     memcpy(handle_out, &h, sizeof(h));
+    peer_handle_mark_legacy(handle_out);
     return AG_OK;
 }
 
@@ -109,24 +115,38 @@ extern "C" int32_t ag_features_open_sharded(const ag_features *local, uint32_t w
     if (!guard.ok) return AG_ERR_CUDA;
     const uint8_t *bases[8] = {nullptr};
     void *opened[8] = {nullptr};
+    PeerBlock *blocks[8] = {nullptr};
+    auto close_all = [&] {
+        for (void *q : opened) if (q) cudaIpcCloseMemHandle(q);
+        for (PeerBlock *b : blocks) if (b) peer_block_free(b);
+    };
     const bool cyclic = is_cyclic(local) || (world > 1 && local->row_stride == world);
     const uint64_t n = local->num_nodes, shard_rows = (n + world - 1) / world;
     for (uint32_t r = 0; r < world; ++r) {
         if (r == rank) { bases[r] = local->payload; continue; }
         const bool empty = cyclic ? (uint64_t)r >= n : (uint64_t)r * shard_rows >= n;
         if (empty) continue;
+        const uint8_t *handle = (const uint8_t *)handles + (size_t)r * AG_IPC_HANDLE_BYTES;
+        const int kind = peer_handle_kind(handle);
+        if (kind == 2) {
+            const int32_t st = peer_block_import(handle, local->device, &blocks[r]);
+            if (st != AG_OK) { close_all(); return st; }
+            bases[r] = (const uint8_t *)peer_block_ptr(blocks[r]);
+            continue;
+        }
+        if (kind != 1) { close_all(); return fail(AG_ERR_VALUE, "ag_features_open_sharded: rank %u's handle is empty or malformed", r); }
         cudaIpcMemHandle_t h;
-        memcpy(&h, (const uint8_t *)handles + (size_t)r * AG_IPC_HANDLE_BYTES, sizeof(h));
+        memcpy(&h, handle, sizeof(h));
         void *p = nullptr;
         const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
         if (e != cudaSuccess) {
-            for (void *q : opened) if (q) cudaIpcCloseMemHandle(q);
+            close_all();
             return fail(AG_ERR_CUDA, "cannot map the feature shard of rank %u: %s", r, cudaGetErrorString(e));
         }
         opened[r] = p; bases[r] = (const uint8_t *)p;
     }
-    const int32_t st = make_view(local, world, rank, cyclic, bases, opened, out);
-    if (st != AG_OK) for (void *q : opened) if (q) cudaIpcCloseMemHandle(q);
+    const int32_t st = make_view(local, world, rank, cyclic, bases, opened, blocks, out);
+    if (st != AG_OK) close_all();
     return st;
 }
 
@@ -147,6 +167,7 @@ extern "C" int32_t ag_features_view_sharded(const ag_features *const *shards, ui
     for (uint32_t r = 0; r < world; ++r) {
         bases[r] = shards[r]->payload;
         if (shards[r]->device == local->device || shards[r]->rows == 0) continue;
+        if (shards[r]->block) { AG_TRY(peer_block_grant(shards[r]->block, local->device)); continue; }
         int can = 0;
         AG_CUDA(cudaDeviceCanAccessPeer(&can, local->device, shards[r]->device));
         if (!can) return fail(AG_ERR_CUDA, "GPU %d cannot access GPU %d's memory", local->device, shards[r]->device);
@@ -154,5 +175,12 @@ extern "C" int32_t ag_features_view_sharded(const ag_features *const *shards, ui
         if (e == cudaErrorPeerAccessAlreadyEnabled) cudaGetLastError();
         else if (e != cudaSuccess) return fail(AG_ERR_CUDA, "enabling peer access to GPU %d failed: %s", shards[r]->device, cudaGetErrorString(e));
     }
-    return make_view(local, world, rank, is_cyclic(local), bases, nullptr, out);
+    return make_view(local, world, rank, is_cyclic(local), bases, nullptr, nullptr, out);
+}
+
+extern "C" int32_t ag_features_set_gather_order(ag_features *view, int32_t order) {
+    if (!view) return fail(AG_ERR_VALUE, "ag_features_set_gather_order: null store");
+    if (order < AG_GATHER_AUTO || order > AG_GATHER_DIRECT) return fail(AG_ERR_VALUE, "unknown gather order: %d", order);
+    view->gather_order = order;
+    return AG_OK;
 }

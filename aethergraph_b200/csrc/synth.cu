@@ -488,14 +488,17 @@ int32_t synth_feature_rows(uint64_t num_nodes, uint64_t dim, int32_t dtype, uint
         *out = f;
         return AG_OK;
     }
+    PeerBlock *block = nullptr;  // peers can map it with large pages when the store becomes a shard
     uint8_t *payload = nullptr;
-    AG_CUDA(cudaMalloc(&payload, std::max<uint64_t>(rows * dim * elem_size(dtype), 16)));
+    AG_TRY(alloc_feature_payload(device, std::max<uint64_t>(rows * dim * elem_size(dtype), 16), &payload, &block));
     k_features<<<grid_for(rows * dim), 256>>>(payload, row_begin, row_stride, rows, dim, dtype, seed);
     const cudaError_t e = cudaDeviceSynchronize();
-    if (e != cudaSuccess) { cudaFree(payload); return fail(AG_ERR_CUDA, "k_features: %s", cudaGetErrorString(e)); }
+    auto drop = [&] { if (block) peer_block_free(block); else cudaFree(payload); };
+    if (e != cudaSuccess) { drop(); return fail(AG_ERR_CUDA, "k_features: %s", cudaGetErrorString(e)); }
     ag_features *f = nullptr;
     const int32_t st = ag_features_adopt_device(payload, rows, dim, dtype, device, &f);
-    if (st != AG_OK) { cudaFree(payload); return st; }
+    if (st != AG_OK) { drop(); return st; }
+    f->block = block;
     f->num_nodes = num_nodes; f->row_begin = row_begin; f->rows = rows; f->row_stride = row_stride; f->owns_payload = true;
     *out = f;
     return AG_OK;

@@ -225,6 +225,16 @@ class FeatureStore:
         _lib.check(_lib.lib().ag_features_gather_stats(self._h, C.byref(a), C.byref(b), C.byref(c)))
         return a.value, b.value, c.value
 
+    def set_gather_order(self, order: str = "auto") -> None:
+        """Sharded views: "direct" loads every row from its owner where the request stands,
+        "ordered" sorts the requests of a launch chain into address order first and loads
+        repeats once, "auto" (the default) picks direct unless a peer is mapped through a
+        legacy CUDA IPC handle.  Same bits either way."""
+        modes = {"auto": 0, "ordered": 1, "direct": 2}
+        if order not in modes:
+            raise ValueError(f"gather order must be one of {sorted(modes)}, got {order!r}")
+        _lib.check(_lib.lib().ag_features_set_gather_order(self._h, modes[order]))
+
     def cache_hot_rows(self, graph, max_bytes: int = 1 << 30) -> int:
         """Sharded views: keep a copy of the rows of the highest in-degree vertices of
         `graph` in this GPU's memory, `max_bytes` of them at most, and serve them from

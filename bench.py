@@ -437,10 +437,11 @@ def run_device(args, w):
         shard = synth.features_shard(w["nodes"], w["dim"], w["dtype"], FEATURE_SEED, rank, world, layout)
         return agd.open_sharded_features(shard)
 
-    def sharded_leg(view, layout_flag: str, replicated, cache_gb: float, repeats: int):
+    def sharded_leg(view, layout_flag: str, replicated, cache_gb: float, repeats: int, order: str = "auto"):
         """One resident leg over the sharded view, with `cache_gb` GiB of hot rows copied to
-        every GPU first (0: none).  Returns the record."""
+        every GPU first (0: none) and the given gather order.  Returns the record."""
         cached_rows = view.cache_hot_rows(g, int(cache_gb * (1 << 30))) if cache_gb > 0 else view.cache_hot_rows(g, 0)
+        view.set_gather_order(order)
         barrier()
         lg = ResidentLeg(L, _lib, g, view, ccfg, dev, w, threads_sh, group_sh, depth_sh, seeds_dev, gidx, rank, world)
         lg.run(0, first_timed)
@@ -450,11 +451,29 @@ def run_device(args, w):
         st1 = view.gather_stats()
         rec = sharded_summary(w, world, median_run(runs_s), stored_row, lg, view, replicated, dev, sum_over_ranks,
                               layout_flag, args.steps, [a - b for a, b in zip(st1, st0)], sum(r[0] for r in runs_s))
+        rec["gather_order"] = order if order != "auto" else "direct (auto: every peer is mapped with large pages)"
         rec["hot_rows_copied_per_gpu"] = int(cached_rows)
         rec["hot_rows_gib_per_gpu"] = cached_rows * stored_row / float(1 << 30)
         rec["impl_config"] = {"sampler_threads": threads_sh, "group": group_sh, "prefetch_depth": depth_sh}
         lg.close()
+        view.set_gather_order(args.gather_order)
         barrier()
+        return rec
+
+    def sharded_record(view, layout_flag: str, replicated):
+        """The sharded leg as configured, and beside it the same leg without the hot-row copy
+        and with the address-ordered gather (one timed region each)."""
+        keys = ("value", "ms_per_step", "remote_gbs_per_gpu", "frac_of_peer_copy_peak", "rows_loaded_per_row_requested",
+                "rows_from_hot_copy_per_row_loaded", "parity")
+        rec = sharded_leg(view, layout_flag, replicated, args.hot_cache_gb, max(1, min(args.repeats, 3)), args.gather_order)
+        if args.hot_cache_gb > 0:
+            nc = sharded_leg(view, layout_flag, replicated, 0.0, 1, args.gather_order)
+            rec["without_hot_rows"] = {k: nc[k] for k in keys}
+        other = "ordered" if args.gather_order != "ordered" else "direct"
+        oc = sharded_leg(view, layout_flag, replicated, args.hot_cache_gb, 1, other)
+        rec["address_ordered" if other == "ordered" else "direct"] = {k: oc[k] for k in keys}
+        if args.hot_cache_gb > 0:
+            view.cache_hot_rows(g, int(args.hot_cache_gb * (1 << 30)))
         return rec
 
     def features_label(layout_flag: str) -> str:
@@ -468,8 +487,10 @@ def run_device(args, w):
     g = synth.rmat_graph(w["nodes"], w["edges"], GRAPH_SEED, weight_sigma=1.0 if w["weighted"] else 0.0)
     feats = open_shards(main_layout) if main_layout != "replicated" else \
         synth.features(w["nodes"], w["dim"], w["dtype"], FEATURE_SEED)
-    if main_layout != "replicated" and args.hot_cache_gb > 0:
-        feats.cache_hot_rows(g, int(args.hot_cache_gb * (1 << 30)))
+    if main_layout != "replicated":
+        feats.set_gather_order(args.gather_order)
+        if args.hot_cache_gb > 0:
+            feats.cache_hot_rows(g, int(args.hot_cache_gb * (1 << 30)))
     torch.cuda.synchronize()
     t_setup = time.time() - t_setup
     cfg = ag.SamplingConfig(num_neighbors=w["fanout"], seed=SAMPLER_SEED, weighted=w["weighted"])
@@ -563,13 +584,7 @@ def run_device(args, w):
     del leg
     sharded_main = None
     if main_layout != "replicated" and world > 1:
-        sharded_main = sharded_leg(feats, main_layout, None, args.hot_cache_gb, max(1, min(args.repeats, 3)))
-        nc = sharded_leg(feats, main_layout, None, 0.0, 1)   # the same without the hot-row copy
-        sharded_main["without_hot_rows"] = {k: nc[k] for k in ("value", "ms_per_step", "remote_gbs_per_gpu",
-                                                               "frac_of_peer_copy_peak", "rows_loaded_per_row_requested",
-                                                               "parity")}
-        if args.hot_cache_gb > 0:
-            feats.cache_hot_rows(g, int(args.hot_cache_gb * (1 << 30)))
+        sharded_main = sharded_record(feats, main_layout, None)
         barrier()
 
     # ---- e2e: public Python API, host seeds in, counts back -----------------
@@ -640,14 +655,39 @@ def run_device(args, w):
     sharded = sharded_main
     if world > 1 and main_layout == "replicated" and not args.only_value and not args.no_sharded:
         view = open_shards("sharded")
-        sharded = sharded_leg(view, "sharded", feats, args.hot_cache_gb, max(1, min(args.repeats, 3)))
+        sharded = sharded_record(view, "sharded", feats)
         sharded["vs_replicated"] = sharded["value"] / value if value else None
-        nc = sharded_leg(view, "sharded", feats, 0.0, 1)   # the same without the hot-row copy: every remote row crosses NVLink
-        sharded["without_hot_rows"] = {k: nc[k] for k in ("value", "ms_per_step", "remote_gbs_per_gpu", "frac_of_peer_copy_peak",
-                                                          "rows_loaded_per_row_requested", "parity")}
         barrier()  # no rank frees its shard while a peer may still be reading it
         del view
         barrier()
+
+    # ---- the same leg over the block-scaled int8 payload (1 GPU) -------------------
+    int8_leg = None
+    if world == 1 and not args.only_value and not args.brief and not args.no_secondary and w["dim"] % 16 == 0 \
+            and main_layout == "replicated":
+        f8 = synth.features(w["nodes"], w["dim"], "i8", FEATURE_SEED)
+        leg8 = ResidentLeg(L, _lib, g, f8, ccfg, dev, w, threads, group, depth, seeds_dev, gidx, rank, world)
+        leg8.run(0, first_timed)
+        med8 = median_run(timed_repeats(leg8.run, first_timed, n_timed, max(1, min(args.repeats, 3)), barrier,
+                                        max_over_ranks, sum_over_ranks))
+        rb8 = sector(w["dim"] + 4 * ((w["dim"] + 31) // 32)) + w["dim"] * 4
+        # rows of the last batch against the codec's own decode of the same stored bytes
+        ok8 = None
+        if leg8.recent:
+            holder = _Buffers(leg8.ring[0].c, leg8.ring, dev, w["dim"])
+            n_id_ptr, x_ptr, nn = leg8.recent[-1]
+            ids8 = holder.view(n_id_ptr, (int(nn),), "<i8")[:4096]
+            x8 = holder.view(x_ptr, (int(nn), w["dim"]), "<f4")[:4096]
+            ok8 = bool(torch.equal(x8.view(torch.int32), f8.gather(ids8).view(torch.int32)))
+            del holder
+        int8_leg = {"value": med8["value"], "unit": "edges/s", "ms_per_step": med8["ms"] / max(args.steps, 1),
+                    "gather_gbs": med8["nodes"] * rb8 / (med8["ms"] * 1e-3) / 1e9, "bytes_per_row": rb8,
+                    "rows_match_standalone_gather": ok8,
+                    "note": "features stored as block-scaled int8 (one byte per element + one f32 scale per 32 "
+                            "elements of a row, the reference's BlockScaledI8): lossy, the gathered rows are what its "
+                            "decode gives; 288 B read + 1024 B written per row instead of 512 + 1024"}
+        leg8.close()
+        del leg8, f8
 
     secondary = None
     if rank == 0 and world == 1 and not args.only_value and not args.brief and not args.no_secondary \
@@ -684,7 +724,7 @@ def run_device(args, w):
                                  "d2h_bytes_per_batch": d2h_host / max(1, host_batches),
                                  "note": "same calls, every batch (int64 ids, local edge index, f32 feature rows) "
                                          "also copied to pinned host memory: PCIe-bound"}},
-            "sharded": sharded, "secondary": secondary,
+            "sharded": sharded, "int8_payload": int8_leg, "secondary": secondary,
             # one launch chain per group of batches (the batch is blockIdx.y): seed insert,
             # hops + 1 assign, hops pick, gather (sharded: + key, sorted gather, overflow)
             "gpu_launches": world * chains * (2 * hops + 3 + (3 if sharded_main else 0)),
@@ -742,8 +782,9 @@ def sharded_summary(w, world, med, stored_row, leg, view, replicated, dev, sum_o
             "gather_gbs": med["nodes"] * gather_bytes_per_row(w) / (ms * 1e-3) / 1e9,
             "remote_gbs_per_gpu": remote_gbs, "frac_of_peer_copy_peak": remote_gbs / NVLINK_PEER_COPY_GBS,
             "peer_copy_peak_gbs": NVLINK_PEER_COPY_GBS,
-            "remote_note": "stored bytes of the rows rank 0 fetched from its peers per second: rows loaded (once per "
-                           "launch chain) less the ones served by the local copy of the hot rows, times (W - 1) / W",
+            "remote_note": "stored bytes of the rows rank 0 fetched from its peers per second: rows loaded (every "
+                           "requested row in direct order, once per launch chain in address order) less the ones "
+                           "served by the local copy of the hot rows, times (W - 1) / W",
             "rows_loaded_per_row_requested": (loaded / asked) if asked else None,
             "rows_from_hot_copy_per_row_loaded": (from_copy / loaded) if loaded else None,
             "parity": bool(ok_all), "parity_rows_checked_per_rank": checked}
@@ -1040,6 +1081,9 @@ def main():
     ap.add_argument("--no-sharded", action="store_true", help="2 or more GPUs: skip the sharded-features record")
     ap.add_argument("--hot-cache-gb", type=float, default=1.0,
                     help="sharded features: GiB of the hottest rows (highest in-degree) copied to every GPU (0: none)")
+    ap.add_argument("--gather-order", default="auto", choices=["auto", "ordered", "direct"],
+                    help="sharded features: how remote rows are requested (auto: direct loads when every peer is "
+                         "mapped with large pages)")
     ap.add_argument("--no-secondary", action="store_true", help="1 GPU: skip the secondary workloads (C1, C3, C4 at 1/10)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--only-value", action="store_true",

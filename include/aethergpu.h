@@ -165,7 +165,16 @@ int32_t ag_features_device_ptr(const ag_features *f, const void **payload_dev);
 enum { AG_SHARD_RANGE = 0, AG_SHARD_CYCLIC = 1 };
 int32_t ag_features_load_shard(const char *path, int32_t device, uint32_t rank, uint32_t world,
                                int32_t layout, ag_features **out);
-#define AG_IPC_HANDLE_BYTES 64
+/* ag_features_ipc_export writes the AG_IPC_HANDLE_BYTES another process needs to map
+ * this shard; the ranks exchange them (all-gather over any transport) and hand
+ * the table to ag_features_open_sharded.  A payload the library allocated (every
+ * loader, ag_features_from_f32, the synthetic generators) is exported as a file
+ * descriptor of a driver memory handle, served to the peers over an abstract unix
+ * socket until the store is freed, and mapped there with 2 MB pages; a payload
+ * adopted from the caller (ag_features_adopt_device) is exported as a legacy CUDA
+ * IPC handle, whose mapping reads an order of magnitude slower at random once tens
+ * of GB are mapped. */
+#define AG_IPC_HANDLE_BYTES 128
 int32_t ag_features_ipc_export(const ag_features *f, void *handle_out);
 int32_t ag_features_open_sharded(const ag_features *local, uint32_t world, uint32_t rank,
                                  const void *handles, ag_features **out);
@@ -183,6 +192,14 @@ int32_t ag_features_view_sharded(const ag_features *const *shards, uint32_t worl
  * ag_features_cache_rows). */
 int32_t ag_features_gather_stats(const ag_features *f, uint64_t *rows_requested,
                                  uint64_t *rows_fetched, uint64_t *rows_local_copy);
+/* How a sharded view fetches.  AG_GATHER_DIRECT: every row is loaded from its owner
+ * where the request stands, no sort, repeats loaded again (the counters then count
+ * every requested row as loaded).  AG_GATHER_ORDERED: the address-ordered gather
+ * above.  AG_GATHER_AUTO (the default): direct when every peer is mapped with large
+ * pages (all payloads the library allocated), ordered when a peer came through a
+ * legacy CUDA IPC handle.  Same bits either way. */
+enum { AG_GATHER_AUTO = 0, AG_GATHER_ORDERED = 1, AG_GATHER_DIRECT = 2 };
+int32_t ag_features_set_gather_order(ag_features *view, int32_t order);
 /* Hot rows.  On a skewed graph a small share of the vertices receives most of the
  * row requests (a vertex is gathered in proportion to its in-degree).
  * ag_graph_hot_vertices returns the `max_rows` vertices of highest in-degree,

@@ -107,10 +107,12 @@ def test_loader_with_sharded_features_matches_the_oracle():
             assert np.array_equal(x.cpu().numpy().view(np.uint32), xw.view(np.uint32))
 
 
+@pytest.mark.parametrize("order", ["ordered", "direct"])
 @pytest.mark.parametrize("layout", ["range", "cyclic"])
-def test_chains_over_sharded_features_fetch_each_row_once_and_in_place(layout):
+def test_chains_over_sharded_features_fetch_each_row_once_and_in_place(layout, order):
     """A launch chain over a sharded store gathers its rows in address order, a row
-    named by several batches once.  Batches that share most of their vertices (the
+    named by several batches once ("ordered"), or every row from its owner where the
+    request stands ("direct").  Batches that share most of their vertices (the
     same seeds), batches far larger than the chain before them (rows past the
     estimate take the unsorted pass) and empty batches must all come out exactly
     as the oracle's rows."""
@@ -123,6 +125,7 @@ def test_chains_over_sharded_features_fetch_each_row_once_and_in_place(layout):
     dim, world = 64, 4
     shards = [synth.features_shard(n, dim, "bf16", 17, r, world, layout) for r in range(world)]
     view = ag.FeatureStore.view_sharded(shards, 2)
+    view.set_gather_order(order)
     payload = ago.synth_features(n, dim, "bf16", 17)
     s = ago.Sampler(off, dst, [10, 5], seed=11)
     rng = np.random.default_rng(5)
@@ -160,9 +163,18 @@ def test_sorted_and_unsorted_sharded_gather_agree_on_duplicates():
     ids = np.concatenate([rng.integers(0, 50, 6000), rng.integers(0, n, 6000), [n - 1] * 40, [0] * 40])
     rng.shuffle(ids)
     want = ago.gather(payload, n, dim, "f16", ids.astype(np.uint32))
-    for t in (torch.from_numpy(ids).cuda(), torch.from_numpy(ids.astype(np.int32)).cuda()):
-        got = view.gather(t)
-        assert np.array_equal(got.cpu().numpy().view(np.uint32), want.view(np.uint32))
+    for order in ("ordered", "direct", "auto"):
+        view.set_gather_order(order)
+        before = view.gather_stats()
+        for t in (torch.from_numpy(ids).cuda(), torch.from_numpy(ids.astype(np.int32)).cuda()):
+            got = view.gather(t)
+            assert np.array_equal(got.cpu().numpy().view(np.uint32), want.view(np.uint32))
+        asked, loaded, _ = (a - b for a, b in zip(view.gather_stats(), before))
+        assert asked == 2 * len(ids)
+        # only the ordered gather merges repeats (a run of equal rows is loaded once per four requests)
+        assert (loaded < asked) if order == "ordered" else (loaded == asked)
+    with pytest.raises(ValueError, match="gather order"):
+        view.set_gather_order("sideways")
     with pytest.raises(ValueError, match="out of bounds"):
         view.gather(torch.from_numpy(np.concatenate([ids, [n]])).cuda())
         view.check()
@@ -186,9 +198,12 @@ local = synth.features_shard(n, dim, dtype, 21, rank, world, "cyclic")   # rows 
 view = agd.open_sharded_features(local)
 payload = ago.synth_features(n, dim, dtype, 21)
 ids = np.random.default_rng(100 + rank).integers(0, n, 50_000)
-got = view.gather(torch.from_numpy(ids).cuda())
 want = ago.gather(payload, n, dim, dtype, ids.astype(np.uint32))
-ok = np.array_equal(got.cpu().numpy().view(np.uint32), want.view(np.uint32))
+ok = True
+for order in ("auto", "ordered", "direct"):
+    view.set_gather_order(order)
+    got = view.gather(torch.from_numpy(ids).cuda())
+    ok = ok and np.array_equal(got.cpu().numpy().view(np.uint32), want.view(np.uint32))
 remote = float(np.mean(ids[:2000] % world != rank))
 # the loader path over the sharded view
 from helpers import rmat_csr
@@ -216,7 +231,11 @@ sys.exit(0 if ok else 1)
 """
 
 
-def test_ipc_shards_across_processes_and_gpus(tmp_path):
+@pytest.mark.parametrize("alloc", ["block", "cudamalloc"])
+def test_ipc_shards_across_processes_and_gpus(tmp_path, alloc):
+    """Shards mapped across processes: as shareable blocks (file descriptor over a unix
+    socket, large pages) and, for payloads that are plain device allocations, through
+    legacy CUDA IPC handles."""
     import torch
 
     world = min(torch.cuda.device_count(), 4)
@@ -224,7 +243,7 @@ def test_ipc_shards_across_processes_and_gpus(tmp_path):
         pytest.skip("needs at least two GPUs")
     script = tmp_path / "worker.py"
     script.write_text(_WORKER)
-    env = dict(os.environ, AG_ROOT=ROOT, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, AG_ROOT=ROOT, NCCL_NVLS_ENABLE="0", AG_FEATURE_ALLOC=alloc)
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
                         "--master-addr", "127.0.0.1", "--master-port", "29533", str(script)],
                        env=env, capture_output=True, text=True, timeout=600)
@@ -256,8 +275,9 @@ def test_c5_shaped_batch_over_eight_shards():
     assert len(want["nodes"]) > 20_000
 
 
+@pytest.mark.parametrize("order", ["ordered", "direct"])
 @pytest.mark.parametrize("layout,dtype,dim", [("cyclic", "bf16", 64), ("range", "f16", 24), ("cyclic", "f32", 5)])
-def test_hot_rows_copy_serves_the_same_bits(layout, dtype, dim):
+def test_hot_rows_copy_serves_the_same_bits(layout, dtype, dim, order):
     """A sharded view with a local copy of the highest in-degree rows returns the same
     rows as without one, through the address-ordered gather (large id lists), the
     plain one (short lists, odd row sizes) and the loader; the counters tell the copy's
@@ -273,6 +293,7 @@ def test_hot_rows_copy_serves_the_same_bits(layout, dtype, dim):
     world = 4
     shards = [synth.features_shard(n, dim, dtype, 23, r, world, layout) for r in range(world)]
     view = ag.FeatureStore.view_sharded(shards, 1)
+    view.set_gather_order(order)
     payload = ago.synth_features(n, dim, dtype, 23)
     row = dim * (4 if dtype == "f32" else 2)
     copied = view.cache_hot_rows(g, 300 * row)
@@ -289,7 +310,8 @@ def test_hot_rows_copy_serves_the_same_bits(layout, dtype, dim):
     assert np.array_equal(short.cpu().numpy().view(np.uint32), want[:100].view(np.uint32))
     asked, loaded, from_copy = view.gather_stats()
     if row % 16 == 0:
-        assert asked == len(ids) and loaded <= asked and from_copy >= copied * 0.9  # every hot row was asked for
+        # the short list takes the direct kernel in either mode
+        assert asked == len(ids) + 100 and loaded <= asked and from_copy >= copied * 0.9  # every hot row was asked for
         # rows the degree order puts in the copy are served from it
         assert from_copy <= loaded
     s = ago.Sampler(off, dst, [8, 4], seed=2)
