@@ -119,10 +119,8 @@ __device__ __forceinline__ const uint8_t *shard_row(const ag_shard_table *t, uin
 }
 
 // Vector path: row_bytes % 16 == 0 and the payload base is 16-byte aligned.
-// LPR lanes share a row; vecs = row_bytes / 16.  SHARDED: the store is split by
-// vertex range over several GPUs and every row is fetched straight from its
-// owner's memory (local HBM or a peer over NVLink), upcast at the reader.
-template <int DTYPE, int LPR, bool SHARDED>
+// LPR lanes share a row; vecs = row_bytes / 16.
+template <int DTYPE, int LPR>
 __global__ void __launch_bounds__(kThreads)
 k_gather_vec(GatherArgs a, const GatherArgs *__restrict__ group, uint64_t first) {
     constexpr int kRowsPerBlock = kThreads / LPR;
@@ -141,7 +139,6 @@ k_gather_vec(GatherArgs a, const GatherArgs *__restrict__ group, uint64_t first)
     const uint64_t stride = kRowsPerBlock;
     const uint64_t pol = l2_evict_first_policy();
 
-    uint32_t asked = 0, hot_hits = 0;  // SHARDED: counted by lane 0 of each row group
     // `first`: rows before it are somebody else's (the sorted gather's overflow pass).
     for (uint64_t base = first + (uint64_t)blockIdx.x * kChunk + sub; base < n; base += (uint64_t)gridDim.x * kChunk) {
         for (uint32_t v0 = 0; v0 < vecs; v0 += LPR) {
@@ -158,13 +155,7 @@ k_gather_vec(GatherArgs a, const GatherArgs *__restrict__ group, uint64_t first)
                     const uint64_t local = id - a.row_begin;
                     ok[u] = true;
                     if (id >= a.row_begin && local < a.rows) {
-                        if (SHARDED) {
-                            bool hot;
-                            val[u] = ld_peer_v4(shard_row(a.shards, id, a.row_bytes, hot) + ((uint64_t)v << 4));
-                            if (lane == 0 && v0 == 0) { ++asked; hot_hits += hot ? 1u : 0u; }
-                        } else {
-                            val[u] = ld_stream_v4_l2ef(a.payload + local * a.row_bytes + ((uint64_t)v << 4), pol);
-                        }
+                        val[u] = ld_stream_v4_l2ef(a.payload + local * a.row_bytes + ((uint64_t)v << 4), pol);
                     } else if (lane == 0) {
                         atomicOr(a.err, kErrBadId);
                     }
@@ -179,17 +170,103 @@ k_gather_vec(GatherArgs a, const GatherArgs *__restrict__ group, uint64_t first)
             }
         }
     }
-    if (SHARDED) {
-        // the view's counters: rows asked for = rows loaded here (nothing is merged), rows served by the hot copy
-        for (int o = 16; o > 0; o >>= 1) {
-            asked += __shfl_xor_sync(0xffffffffu, asked, o);
-            hot_hits += __shfl_xor_sync(0xffffffffu, hot_hits, o);
+}
+
+// Direct gather over a sharded store: every row is fetched straight from where it
+// lives — the local copy of the hot rows, this GPU's shard, or a peer's shard over
+// NVLink — and upcast at the reader.
+//
+// A peer's row takes several times longer to arrive than a local one, and finding
+// it takes two dependent loads first (the id, then the hot-row slot).  So the work of
+// a block is split: one thread per row resolves the row's address into shared memory,
+// for the NEXT set of rows, while all lanes have the loads of the current set in
+// flight — kPeerWaves rows per lane group, twice the local kernel's — and a block
+// walks through kPeerSets sets instead of retiring after one.
+constexpr int kPeerWaves = 8;
+constexpr int kPeerSets = 4;
+
+template <int DTYPE, int LPR>
+__global__ void __launch_bounds__(kThreads, 3)
+k_gather_peer(GatherArgs a, const GatherArgs *__restrict__ group, uint64_t first) {
+    constexpr int kRowsPerWave = kThreads / LPR;
+    constexpr int kRows = kRowsPerWave * kPeerWaves;  // rows of one set
+    __shared__ const uint8_t *s_row[2][kRows];        // where every row of a set starts; null: nothing to fetch
+    if (group) a = group[blockIdx.y];  // one batch of a group per grid row
+    if (!a.payload) return;
+    const uint64_t n = a.n_dev ? min((uint64_t)*a.n_dev, a.n) : a.n;
+    if (a.ids_off) a.ids = (const uint32_t *)a.ids + *a.ids_off;
+    const int lane = threadIdx.x % LPR;
+    const int sub = threadIdx.x / LPR;
+    const uint32_t vecs = a.row_bytes >> 4;
+    const uint32_t out_per_vec = (DTYPE == AG_F32) ? 4u : 8u;
+    uint32_t asked = 0, hot_hits = 0;
+
+    // set i covers rows [first + i * kRows, + kRows); a block takes kPeerSets consecutive
+    // sets, then the ones a whole grid further on
+    auto next_set = [&](uint64_t i) {
+        return ((i + 1) % kPeerSets != 0) ? i + 1 : i + 1 + (uint64_t)(gridDim.x - 1) * kPeerSets;
+    };
+    auto resolve = [&](int buf, uint64_t set) {
+        const uint64_t base = first + set * kRows;
+        for (int j = threadIdx.x; j < kRows; j += kThreads) {
+            const uint64_t r = base + j;
+            const uint8_t *p = nullptr;
+            if (r < n) {
+                const uint64_t id = load_id(a.ids, a.ids64, r);
+                if (id >= a.row_begin && id - a.row_begin < a.rows) {
+                    bool hot;
+                    p = shard_row(a.shards, id, a.row_bytes, hot);
+                    ++asked;
+                    hot_hits += hot ? 1u : 0u;
+                } else {
+                    atomicOr(a.err, kErrBadId);
+                }
+            }
+            s_row[buf][j] = p;
         }
-        if ((threadIdx.x & 31) == 0 && asked) {
-            unsigned long long *counters = (unsigned long long *)(a.err + 2);
-            atomicAdd(counters, (unsigned long long)asked); atomicAdd(counters + 1, (unsigned long long)asked);
-            if (hot_hits) atomicAdd(counters + 2, (unsigned long long)hot_hits);
+    };
+
+    uint64_t set = (uint64_t)blockIdx.x * kPeerSets;
+    int buf = 0;
+    if (first + set * kRows < n) resolve(0, set);
+    __syncthreads();
+    while (first + set * kRows < n) {
+        const uint64_t base = first + set * kRows;
+        const uint64_t following = next_set(set);
+        for (uint32_t v0 = 0; v0 < vecs; v0 += LPR) {
+            const uint32_t v = v0 + lane;
+            uint4 val[kPeerWaves];
+            uint32_t ok = 0;  // bit u: row u of this lane group is fetched
+            const uint32_t voff = v << 4;
+#pragma unroll
+            for (int u = 0; u < kPeerWaves; ++u) {
+                const uint8_t *p = s_row[buf][u * kRowsPerWave + sub];
+                val[u] = make_uint4(0, 0, 0, 0);
+                if (p != nullptr && v < vecs) { ok |= 1u << u; val[u] = ld_peer_v4(p + voff); }
+            }
+            // the addresses of the following set, while this set's rows are on their way
+            if (v0 == 0 && first + following * kRows < n) resolve(buf ^ 1, following);
+            float *dst = a.out + (base + sub) * a.dim + (uint64_t)v * out_per_vec;
+            const uint64_t wave_stride = (uint64_t)kRowsPerWave * a.dim;
+#pragma unroll
+            for (int u = 0; u < kPeerWaves; ++u) {
+                if (ok & (1u << u)) store_decoded<DTYPE>(dst, val[u]);
+                dst += wave_stride;
+            }
         }
+        __syncthreads();  // the following set's addresses are in place, this set's are free to overwrite
+        set = following;
+        buf ^= 1;
+    }
+    // the view's counters: rows asked for = rows loaded (nothing is merged), rows served by the hot copy
+    for (int o = 16; o > 0; o >>= 1) {
+        asked += __shfl_xor_sync(0xffffffffu, asked, o);
+        hot_hits += __shfl_xor_sync(0xffffffffu, hot_hits, o);
+    }
+    if ((threadIdx.x & 31) == 0 && asked) {
+        unsigned long long *counters = (unsigned long long *)(a.err + 2);
+        atomicAdd(counters, (unsigned long long)asked); atomicAdd(counters + 1, (unsigned long long)asked);
+        if (hot_hits) atomicAdd(counters + 2, (unsigned long long)hot_hits);
     }
 }
 
@@ -325,22 +402,25 @@ k_gather_elem(GatherArgs a, const GatherArgs *__restrict__ group) {
     }
 }
 
-template <int DTYPE, bool SHARDED>
-cudaError_t launch_vec_s(const GatherArgs &a, const GatherArgs *group, uint32_t row_bytes, dim3 grid, cudaStream_t st,
-                         uint64_t first) {
-    const uint32_t vecs = row_bytes >> 4;
-    if (vecs <= 4) k_gather_vec<DTYPE, 4, SHARDED><<<grid, kThreads, 0, st>>>(a, group, first);
-    else if (vecs <= 8) k_gather_vec<DTYPE, 8, SHARDED><<<grid, kThreads, 0, st>>>(a, group, first);
-    else if (vecs <= 16) k_gather_vec<DTYPE, 16, SHARDED><<<grid, kThreads, 0, st>>>(a, group, first);
-    else k_gather_vec<DTYPE, 32, SHARDED><<<grid, kThreads, 0, st>>>(a, group, first);
-    return cudaGetLastError();
-}
-
 template <int DTYPE>
 cudaError_t launch_vec(const GatherArgs &a, const GatherArgs *group, uint32_t row_bytes, dim3 grid, bool sharded,
                        cudaStream_t st, uint64_t first = 0) {
-    return sharded ? launch_vec_s<DTYPE, true>(a, group, row_bytes, grid, st, first)
-                   : launch_vec_s<DTYPE, false>(a, group, row_bytes, grid, st, first);
+    const uint32_t vecs = row_bytes >> 4;
+    if (sharded) {
+        // `grid.x` counts blocks of kInFlight waves; a block of the peer kernel takes kPeerSets sets of kPeerWaves
+        constexpr unsigned kFold = (unsigned)(kPeerWaves / kInFlight * kPeerSets);
+        grid.x = std::max(1u, (grid.x + kFold - 1) / kFold);
+        if (vecs <= 4) k_gather_peer<DTYPE, 4><<<grid, kThreads, 0, st>>>(a, group, first);
+        else if (vecs <= 8) k_gather_peer<DTYPE, 8><<<grid, kThreads, 0, st>>>(a, group, first);
+        else if (vecs <= 16) k_gather_peer<DTYPE, 16><<<grid, kThreads, 0, st>>>(a, group, first);
+        else k_gather_peer<DTYPE, 32><<<grid, kThreads, 0, st>>>(a, group, first);
+        return cudaGetLastError();
+    }
+    if (vecs <= 4) k_gather_vec<DTYPE, 4><<<grid, kThreads, 0, st>>>(a, group, first);
+    else if (vecs <= 8) k_gather_vec<DTYPE, 8><<<grid, kThreads, 0, st>>>(a, group, first);
+    else if (vecs <= 16) k_gather_vec<DTYPE, 16><<<grid, kThreads, 0, st>>>(a, group, first);
+    else k_gather_vec<DTYPE, 32><<<grid, kThreads, 0, st>>>(a, group, first);
+    return cudaGetLastError();
 }
 
 // f32 -> stored dtype, used to build a store from f32 rows on the device.

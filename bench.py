@@ -63,11 +63,11 @@ WORKLOADS = {
     # 500M-vertex R-MAT, 12B edges (52 GB CSR replicated per GPU), 128-dim bf16 features sharded over the GPUs
     # (128 GB in all), 4096 seeds per GPU and batch, fanout [15, 10, 5]; 2 or more GPUs
     "c5": dict(nodes=500_000_000, edges=12_000_000_000, dim=128, dtype="bf16", batch=4096, fanout=[15, 10, 5],
-               weighted=False, per_step=8, group=4, threads=2, depth=4, sharded_only=True,
+               weighted=False, per_step=32, group=4, threads=2, depth=4, sharded_only=True,
                label="C5: R-MAT 500M vertices / 12B edges, 128-dim bf16 sharded over the GPUs, batch 4096, fanout [15,10,5]"),
     # C5's batch shape and sharded features on a graph that fits next to anything (tests of the sharded leg)
     "c5s": dict(nodes=20_000_000, edges=480_000_000, dim=128, dtype="bf16", batch=4096, fanout=[15, 10, 5],
-                weighted=False, per_step=8, group=4, threads=2, depth=4, sharded_only=True,
+                weighted=False, per_step=32, group=4, threads=2, depth=4, sharded_only=True,
                 label="C5-small: R-MAT 20M vertices / 480M edges, 128-dim bf16 sharded over the GPUs, batch 4096, fanout [15,10,5]"),
 }
 GRAPH_SEED, FEATURE_SEED, SEEDS_SEED, SAMPLER_SEED = 1, 2, 3, 42
@@ -347,6 +347,10 @@ class ResidentLeg:
             self.L.ag_loader_free(self.h)
             self.h = None
         self.ring = None
+        self.recent = []
+        import torch
+
+        torch.cuda.empty_cache()  # the ring came from torch's allocator; the library's own allocations need the room
 
 
 def timed_repeats(run, first, count, repeats, barrier, max_over_ranks, sum_over_ranks):
