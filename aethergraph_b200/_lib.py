@@ -55,7 +55,8 @@ class SampleCounts(C.Structure):
                 ("num_hops", C.c_uint32), ("nodes_per_hop", C.c_uint32 * (AG_MAX_HOPS + 1)),
                 ("edges_per_hop", C.c_uint32 * AG_MAX_HOPS), ("draws", C.c_uint64),
                 ("error", C.c_uint32), ("reserved", C.c_uint32),
-                ("sample_ms", C.c_float), ("gather_ms", C.c_float)]
+                ("sample_ms", C.c_float), ("gather_ms", C.c_float),
+                ("gather_begin_ms", C.c_double), ("gather_end_ms", C.c_double)]
 
 
 class Batch(C.Structure):

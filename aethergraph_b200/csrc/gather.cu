@@ -270,62 +270,80 @@ k_gather_peer(GatherArgs a, const GatherArgs *__restrict__ group, uint64_t first
     }
 }
 
-// Block-scaled int8 rows: LPR lanes per row, every lane owns 16 codes (one 16-byte
-// vector, inside one 32-element scale block) of kInFlight rows at a time and writes
-// 16 floats per row.  decode = (float)code * scale: one IEEE multiply, the same value
-// the reference's BlockScaledI8::decode computes (feature_codec.rs:121-133; its own
-// device kernel: crates/aether-stream/src/gpu/kernels/quant/feature_dequant.cu:21-75).
+// Block-scaled int8 rows: LPR lanes per row.  A row is a run of 4-byte words (4 codes
+// each); lane l of the row's group takes words l, l + LPR, l + 2 LPR, l + 3 LPR, so
+// that every load of the group reads LPR consecutive words and every 16-byte store of
+// the four decoded floats lands beside its neighbours' (a lane that decoded a whole
+// 16-byte vector would write 64 bytes on its own, a quarter of every sector per store
+// instruction).  decode = (float)code * scale: one IEEE multiply, the same value the
+// reference's BlockScaledI8::decode computes (feature_codec.rs:121-133; its own device
+// kernel: crates/aether-stream/src/gpu/kernels/quant/feature_dequant.cu:21-75).
 template <int LPR>
 __global__ void __launch_bounds__(kThreads)
 k_gather_i8(GatherArgs a, const GatherArgs *__restrict__ group, uint64_t first) {
     constexpr int kRowsPerBlock = kThreads / LPR;
+    constexpr int kWordsPerLane = 4;
+    constexpr int kRowsInFlight = 2;  // x 4 words per lane: eight loads in flight
     if (group) a = group[blockIdx.y];
     if (!a.payload) return;
     const uint64_t n = a.n_dev ? min((uint64_t)*a.n_dev, a.n) : a.n;
     if (a.ids_off) a.ids = (const uint32_t *)a.ids + *a.ids_off;
     const int lane = threadIdx.x % LPR;
     const int sub = threadIdx.x / LPR;
-    const uint32_t vecs = a.row_bytes >> 4;                       // 16 codes per vector
+    const uint32_t words = a.row_bytes >> 2;                      // 4 codes per word; row_bytes % 16 == 0
     const uint32_t blocks_per_row = (a.dim + kQuantBlock - 1) / kQuantBlock;
-    constexpr uint64_t kChunk = (uint64_t)kRowsPerBlock * kInFlight;
-    const uint64_t pol = l2_evict_first_policy();
+    constexpr uint64_t kChunk = (uint64_t)kRowsPerBlock * kInFlight;  // the grid is sized for this many rows per block
     for (uint64_t base = first + (uint64_t)blockIdx.x * kChunk + sub; base < n; base += (uint64_t)gridDim.x * kChunk) {
-        for (uint32_t v0 = 0; v0 < vecs; v0 += LPR) {
-            const uint32_t v = v0 + lane;
-            uint4 val[kInFlight];
-            float scale[kInFlight];
-            bool ok[kInFlight];
+        for (int u0 = 0; u0 < kInFlight; u0 += kRowsInFlight) {
+            for (uint32_t w0 = 0; w0 < words; w0 += LPR * kWordsPerLane) {
+                uint32_t val[kRowsInFlight][kWordsPerLane];
+                float scale[kRowsInFlight][kWordsPerLane];
+                bool ok[kRowsInFlight];
 #pragma unroll
-            for (int u = 0; u < kInFlight; ++u) {
-                const uint64_t r = base + (uint64_t)u * kRowsPerBlock;
-                ok[u] = false; scale[u] = 0.f;
-                val[u] = make_uint4(0, 0, 0, 0);
-                if (r < n && v < vecs) {
-                    const uint64_t id = load_id(a.ids, a.ids64, r);
-                    const uint64_t local = id - a.row_begin;
-                    ok[u] = true;
-                    if (id >= a.row_begin && local < a.rows) {
-                        val[u] = ld_stream_v4_l2ef(a.payload + local * a.row_bytes + ((uint64_t)v << 4), pol);
-                        scale[u] = __ldg(a.scales + local * blocks_per_row + (v >> 1));  // 32-element blocks: two vectors each
-                    } else if (lane == 0) {
-                        atomicOr(a.err, kErrBadId);
+                for (int u = 0; u < kRowsInFlight; ++u) {
+                    const uint64_t r = base + (uint64_t)(u0 + u) * kRowsPerBlock;
+                    ok[u] = false;
+                    if (r < n) {
+                        const uint64_t id = load_id(a.ids, a.ids64, r);
+                        const uint64_t local = id - a.row_begin;
+                        if (id >= a.row_begin && local < a.rows) {
+                            ok[u] = true;
+                            const uint32_t *row = (const uint32_t *)(a.payload + local * a.row_bytes);
+                            const float *sc = a.scales + local * blocks_per_row;
+#pragma unroll
+                            for (int q = 0; q < kWordsPerLane; ++q) {
+                                const uint32_t w = w0 + q * LPR + lane;
+                                val[u][q] = 0; scale[u][q] = 0.f;
+                                if (w < words) {
+                                    val[u][q] = __ldg(row + w);
+                                    scale[u][q] = __ldg(sc + (w >> 3));  // eight words per 32-element block
+                                }
+                            }
+                        } else if (lane == 0 && w0 == 0) {
+                            atomicOr(a.err, kErrBadId);
+                        }
                     }
                 }
-            }
 #pragma unroll
-            for (int u = 0; u < kInFlight; ++u) {
-                if (!ok[u]) continue;
-                const uint64_t r = base + (uint64_t)u * kRowsPerBlock;
-                float *dst = a.out + r * a.dim + (uint64_t)v * 16;
-                const uint32_t w[4] = {val[u].x, val[u].y, val[u].z, val[u].w};
+                for (int u = 0; u < kRowsInFlight; ++u) {
+                    const uint64_t r = base + (uint64_t)(u0 + u) * kRowsPerBlock;
+                    if (r >= n) continue;
+                    float *dst = a.out + r * a.dim;
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    uint4 o;
-                    o.x = __float_as_uint((float)(int)(signed char)(w[q] & 0xFFu) * scale[u]);
-                    o.y = __float_as_uint((float)(int)(signed char)((w[q] >> 8) & 0xFFu) * scale[u]);
-                    o.z = __float_as_uint((float)(int)(signed char)((w[q] >> 16) & 0xFFu) * scale[u]);
-                    o.w = __float_as_uint((float)(int)(signed char)(w[q] >> 24) * scale[u]);
-                    st_stream_v4(dst + q * 4, o);
+                    for (int q = 0; q < kWordsPerLane; ++q) {
+                        const uint32_t w = w0 + q * LPR + lane;
+                        if (w >= words) continue;
+                        uint4 o = make_uint4(0, 0, 0, 0);  // a row outside the store decodes to zeros
+                        if (ok[u]) {
+                            const uint32_t c = val[u][q];
+                            const float sf = scale[u][q];
+                            o.x = __float_as_uint((float)(int)(signed char)(c & 0xFFu) * sf);
+                            o.y = __float_as_uint((float)(int)(signed char)((c >> 8) & 0xFFu) * sf);
+                            o.z = __float_as_uint((float)(int)(signed char)((c >> 16) & 0xFFu) * sf);
+                            o.w = __float_as_uint((float)(int)(signed char)(c >> 24) * sf);
+                        }
+                        st_stream_v4(dst + (uint64_t)w * 4, o);
+                    }
                 }
             }
         }

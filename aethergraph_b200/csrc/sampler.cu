@@ -1214,6 +1214,21 @@ extern "C" int32_t ag_sample_group_into(ag_sampler *s, uint32_t n_batches, const
 }
 
 namespace {
+// Time zero of the profiled intervals on a GPU: an event recorded once, on the stream of
+// the first profiled launch there.  Called with a null stream it only returns the event.
+cudaEvent_t profile_origin(int device, cudaStream_t st) {
+    static std::mutex m;
+    static cudaEvent_t origin[64] = {nullptr};
+    std::lock_guard<std::mutex> lk(m);
+    if (device < 0 || device >= 64) return nullptr;
+    if (!origin[device] && st) {
+        cudaEvent_t e = nullptr;
+        if (cudaEventCreate(&e) == cudaSuccess && cudaEventRecord(e, st) == cudaSuccess) origin[device] = e;
+        else if (e) cudaEventDestroy(e);
+    }
+    return origin[device];
+}
+
 int32_t launch_saved_impl(ag_sampler *s, bool relaunch);
 
 // Queues the chain described by s->last.  relaunch: the same chain once more with
@@ -1255,7 +1270,10 @@ int32_t launch_saved_impl(ag_sampler *s, bool relaunch) {
     }
     cudaStream_t st = L.stream;
     AG_TRY(ensure_scratch(s, max_n));
-    if (s->profile) AG_CUDA(cudaEventRecord(s->ev[0], st));
+    if (s->profile) {
+        profile_origin(s->device, st);
+        AG_CUDA(cudaEventRecord(s->ev[0], st));
+    }
     if (s->dirty || s->gen >= kGens) {
         // Every slot free again.  A launch marks its entries with its generation,
         // so this real clear is only needed once the generations have cycled (or
@@ -1437,10 +1455,13 @@ extern "C" int32_t ag_sample_group_wait(ag_sampler *s, ag_sample_counts *counts,
         return fail(AG_ERR_CUDA, "sampling kernels failed: %s", cudaGetErrorString(e));
     }
     account_stream(s);
-    float sample_ms = 0.f, gather_ms = 0.f;
+    float sample_ms = 0.f, gather_ms = 0.f, gather_begin = 0.f;
     if (s->profile) {
         cudaEventElapsedTime(&sample_ms, s->ev[0], s->ev[1]);
-        if (s->gathered) cudaEventElapsedTime(&gather_ms, s->ev[2], s->ev[3]);
+        if (s->gathered) {
+            cudaEventElapsedTime(&gather_ms, s->ev[2], s->ev[3]);
+            if (cudaEvent_t origin = profile_origin(s->device, nullptr)) cudaEventElapsedTime(&gather_begin, origin, s->ev[2]);
+        }
     }
     // Next group's grids follow what this one really produced (with headroom).
     uint64_t mx_nodes = 0, mx_items[AG_MAX_HOPS + 2] = {0};
@@ -1458,6 +1479,8 @@ extern "C" int32_t ag_sample_group_wait(ag_sampler *s, ag_sample_counts *counts,
         ag_sample_counts c = s->counts_host[b];
         c.sample_ms = sample_ms / s->in_flight_n;
         c.gather_ms = gather_ms / s->in_flight_n;
+        c.gather_begin_ms = gather_begin;
+        c.gather_end_ms = (double)gather_begin + gather_ms;
         if (counts) counts[b] = c;
         int32_t st = AG_OK;
         if (c.error & kErrBadSeed) st = fail(AG_ERR_SAMPLING, "a seed node is out of range for %llu nodes", (unsigned long long)s->g->num_nodes);

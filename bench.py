@@ -310,6 +310,7 @@ class ResidentLeg:
         self.out_batches = (_lib.Batch * 64)()
         self.n_out = C.c_uint32()
         self.recent: list = []  # (n_id pointer, x pointer, node count) of the last `group` delivered batches
+        self.intervals: set = set()  # (begin, end) of every chain's gather on the device clock, in ms
 
     def run(self, first: int, count: int):
         """Submit batches [first, first + count) with device seeds; returns (edges, nodes)."""
@@ -333,6 +334,8 @@ class ResidentLeg:
                 edges += ob.counts.num_edges
                 nodes += ob.counts.num_nodes
                 self.recent.append((ob.bufs.n_id, ob.bufs.x, ob.counts.num_nodes))
+                if ob.counts.gather_end_ms > ob.counts.gather_begin_ms:
+                    self.intervals.add((ob.counts.gather_begin_ms, ob.counts.gather_end_ms))
             del self.recent[:-group]
             delivered += self.n_out.value
         return edges, nodes
@@ -351,6 +354,21 @@ class ResidentLeg:
         import torch
 
         torch.cuda.empty_cache()  # the ring came from torch's allocator; the library's own allocations need the room
+
+
+def union_ms(intervals) -> float:
+    """Total length of the union of (begin, end) intervals."""
+    total, cur_b, cur_e = 0.0, None, None
+    for b, e in sorted(intervals):
+        if cur_e is None or b > cur_e:
+            if cur_e is not None:
+                total += cur_e - cur_b
+            cur_b, cur_e = b, e
+        else:
+            cur_e = max(cur_e, e)
+    if cur_e is not None:
+        total += cur_e - cur_b
+    return total
 
 
 def timed_repeats(run, first, count, repeats, barrier, max_over_ranks, sum_over_ranks):
@@ -379,6 +397,69 @@ def median_run(runs):
     mid = vals[len(vals) // 2]
     return {"value": mid[0], "ms": mid[1], "edges": mid[2], "nodes": mid[3],
             "min": vals[0][0], "max": vals[-1][0], "n": len(vals)}
+
+
+def run_peer_probe(args, w):
+    """The gather kernel alone over a sharded store, rows fetched from the peers only:
+    GB/s of stored bytes arriving per GPU, all ranks gathering at once, for several
+    request sizes and both request orders.  `AG_FEATURE_ALLOC=cudamalloc` in the
+    environment makes the shards plain device allocations mapped through legacy CUDA IPC
+    handles, the default shareable blocks mapped with 2 MB pages."""
+    import torch
+    import torch.distributed as dist
+
+    from aethergraph_b200 import dist as agd
+    from aethergraph_b200 import synth
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world < 2:
+        raise SystemExit("--peer-probe needs 2 or more GPUs (one process per GPU)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    n, dim, dtype = w["nodes"], w["dim"], w["dtype"]
+    stored_row = dim * (4 if dtype == "f32" else 2)
+    shard = synth.features_shard(n, dim, dtype, FEATURE_SEED, rank, world, "cyclic")
+    view = agd.open_sharded_features(shard)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1000 + rank)
+    rows_out = []
+    for order in ("direct", "ordered"):
+        view.set_gather_order(order)
+        for rows in (100_000, 400_000, 1_600_000, 3_200_000):
+            base = torch.randint(0, n // world - 1, (rows,), device=dev, generator=gen, dtype=torch.int64)
+            off = torch.randint(1, world, (rows,), device=dev, generator=gen)
+            ids = base * world + (rank + off) % world      # rows of the peers only, uniform over them
+            out = torch.empty((rows, dim), dtype=torch.float32, device=dev)
+            for _ in range(2):
+                view.gather(ids, out=out)
+            torch.cuda.synchronize()
+            dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = 5
+            e0.record()
+            for _ in range(reps):
+                view.gather(ids, out=out)
+            e1.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) / reps], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+            rows_out.append({"order": order, "rows": rows, "ms": ms, "peer_gbs_per_gpu": rows * stored_row / ms / 1e6})
+            del ids, out, base, off
+    torch.cuda.synchronize()
+    dist.barrier()
+    if rank == 0:
+        print(json.dumps({"probe": "rows gathered from the peers' shards only, all ranks at once (max over ranks)",
+                          "n_gpus": world, "peer_memory_gb": n * stored_row * (world - 1) / world / 1e9,
+                          "row_bytes": stored_row, "mapping": os.environ.get("AG_FEATURE_ALLOC", "shareable blocks, 2 MB pages"),
+                          "results": rows_out}), flush=True)
+    del view
+    dist.barrier()
+    del shard
+    dist.destroy_process_group()
 
 
 def run_device(args, w):
@@ -526,6 +607,7 @@ def run_device(args, w):
     clocks.start()
     barrier()
     stats0 = leg.stats()
+    leg.intervals = set()
     wall0 = time.time()
     runs = timed_repeats(leg.run, first_timed, n_timed, args.repeats, barrier, max_over_ranks, sum_over_ranks)
     wall1 = time.time()
@@ -537,21 +619,33 @@ def run_device(args, w):
     g_ms = stats1.gather_ms - stats0.gather_ms
     s_ms = stats1.sample_ms - stats0.sample_ms
     own_nodes = int(stats1.nodes - stats0.nodes)   # this rank, all repeats
-    achieved = own_nodes * row_bytes / (g_ms * 1e-3) / 1e9 if g_ms > 0 else None
+    # Every sampler thread's chain has its own gather stream, so gather launches of
+    # different chains overlap one another: the time the kernel was running is the union
+    # of the launches' device intervals, not the sum of their durations.
+    busy_ms = union_ms(leg.intervals)
+    raw = own_nodes * row_bytes / (g_ms * 1e-3) / 1e9 if g_ms > 0 else None
+    achieved = own_nodes * row_bytes / (busy_ms * 1e-3) / 1e9 if busy_ms > 0 else raw
     # one gather launch per chain (a chain covers up to `group` batches, the batch is blockIdx.y)
     launches = max(int(stats1.chains - stats0.chains), 1)
     per_row = NCU_DRAM_BYTES_PER_ROW.get(w["dtype"] + str(w["dim"]))
     pipeline_bytes = med["nodes"] * row_bytes + sampling_bytes(med["edges"], med["nodes"], med["nodes"])
+    total_ms = sum(r[0] for r in runs)
     roofline = {
-        "kernel": "k_gather_vec (feature-row gather + upcast)", "bound": "hbm",
+        "kernel": "k_gather_vec (feature-row gather + upcast)" if main_layout == "replicated" else
+                  "k_gather_peer (feature-row gather over the shards + upcast)", "bound": "hbm",
         "achieved": achieved, "peak": peak, "unit": "GB/s",
         "frac": (achieved / peak) if achieved else None, "peak_source": peak_src,
         "frac_of_nominal_8tbs": (achieved / 8000.0) if achieved else None,
-        "bytes_per_launch": own_nodes * row_bytes / launches, "ms_per_launch": g_ms / launches,
+        "bytes_per_launch": own_nodes * row_bytes / launches,
+        "ms_per_launch": (busy_ms if busy_ms > 0 else g_ms) / launches,
         "launches": launches, "traffic": (per_row * own_nodes / launches) if per_row else None,
         "traffic_note": "extrapolated: ncu dram bytes per gathered row on the C2-small capture x rows per launch",
-        "note": "per-launch time from CUDA events on the launching stream while the other "
-                "streams' sampling kernels run beside it; `alone` is the same kernel by itself",
+        "note": "CUDA events around every gather launch on its launching stream, over the timed regions, while "
+                "the sampling kernels of the other chains run beside it.  Launches of different chains overlap "
+                "one another, so the duration is the union of their device intervals / launches; "
+                "`events_per_launch` is the plain mean of the launch durations, `alone` the same kernel by itself",
+        "gather_running_share_of_timed_region": (busy_ms / total_ms) if total_ms else None,
+        "events_per_launch": {"achieved": raw, "frac": (raw / peak) if raw else None, "ms_per_launch": g_ms / launches},
         "step": {"gather_gbs": gather_gbs, "frac_of_peak": gather_gbs / (peak * world),
                  "note": "gather bytes of a step / step time: the whole pipeline as seen from the gather's roofline"},
         "pipeline": {"algorithmic_gbs": pipeline_bytes / (ms * 1e-3) / 1e9,
@@ -1090,6 +1184,8 @@ def main():
                          "mapped with large pages)")
     ap.add_argument("--no-secondary", action="store_true", help="1 GPU: skip the secondary workloads (C1, C3, C4 at 1/10)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--peer-probe", action="store_true",
+                    help="2 or more GPUs: time the gather kernel alone on rows of the peers' shards")
     ap.add_argument("--only-value", action="store_true",
                     help="run the resident (C ABI) leg only: no e2e, no CPU baseline (profiling runs)")
     args = ap.parse_args()
@@ -1102,6 +1198,8 @@ def main():
     w = WORKLOADS[args.workload]
     if args.impl == "reference":
         run_reference(args, w)
+    elif args.peer_probe:
+        run_peer_probe(args, w)
     else:
         run_device(args, w)
 

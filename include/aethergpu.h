@@ -296,6 +296,11 @@ typedef struct {
     /* Device time of the sampling kernels and of the gather kernel for this
      * batch, in milliseconds; filled only after ag_sampler_set_profiling(s, 1). */
     float sample_ms, gather_ms;
+    /* When the gather of this batch's launch chain began and ended on the device, in
+     * milliseconds since the library's first profiled launch on that GPU (all batches
+     * of a chain carry the same pair).  Chains of different handles overlap; the union
+     * of these intervals is the time some gather kernel was running. */
+    double gather_begin_ms, gather_end_ms;
 } ag_sample_counts;
 
 int32_t ag_sampler_create(const ag_graph *g, const ag_sampling_config *cfg, ag_sampler **out);
