@@ -13,6 +13,8 @@
 #include <string>
 #include <vector>
 
+#include <cub/device/device_scan.cuh>
+
 #include "common.cuh"
 #include "internal.h"
 
@@ -555,6 +557,308 @@ extern "C" int32_t ag_graph_from_edges(uint64_t num_nodes, const uint32_t *src, 
                              AG_MEM_HOST, device, out);
 }
 
+// ------------------------------------------------ AETH version 2 (compressed) --
+// The same 32-byte header with version = 2; the checksum covers the payload
+// (reference: internal/compressed_graph.rs:1-19,39-88,99-175).  Payload:
+//   offsets as Elias-Fano  (internal/succinct.rs:22-92 coding, :198-214 wire format):
+//     len u64 | universe u64 | low_bits u32 | low word count u64 | low words |
+//     high word count u64 | high words;  element i has a set bit at (v_i >> low_bits) + i
+//   edges as StreamVByte wrapping deltas over the WHOLE array (succinct.rs:392-420, :486-500):
+//     len u64 | first u32 | control byte count u64 | control | data byte count u64 | data
+//   weights, when present, raw f32.
+// The reference decodes on the host; here the sections are streamed to the GPU as they
+// lie in the file and decoded there: a scan of the high words' popcounts gives every
+// word the index of its first element, a scan of the control bytes' lengths gives every
+// group of four deltas its place in the data stream, and a wrapping inclusive sum turns
+// the deltas into ids.
+namespace ag {
+namespace {
+
+constexpr uint32_t kCompressedVersion = 2;  // internal/compressed_graph.rs:35
+
+__global__ void k_popcount_words(const uint64_t *__restrict__ w, uint64_t n, uint64_t *__restrict__ counts) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i <= n; i += (uint64_t)gridDim.x * blockDim.x)
+        counts[i] = i < n ? (uint64_t)__popcll(w[i]) : 0ull;  // entry n: receives the total
+}
+
+// flag bits: 1 more set bits than elements, 2 an element above the universe
+__global__ void k_ef_decode(const uint64_t *__restrict__ high, uint64_t n_words, const uint64_t *__restrict__ first_index,
+                            const uint64_t *__restrict__ low, uint32_t low_bits, uint64_t len, uint64_t max_high,
+                            uint64_t *__restrict__ out, uint32_t *flag) {
+    const uint64_t low_mask = low_bits == 0 ? 0ull : ((1ull << low_bits) - 1ull);
+    for (uint64_t wi = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; wi < n_words; wi += (uint64_t)gridDim.x * blockDim.x) {
+        uint64_t w = high[wi];
+        uint64_t i = first_index[wi];
+        while (w) {
+            const uint64_t pos = wi * 64 + (uint64_t)(__ffsll((long long)w) - 1);
+            w &= w - 1;
+            if (i >= len) { atomicOr(flag, 1u); break; }
+            const uint64_t high_part = pos - i;
+            if (high_part > max_high) { atomicOr(flag, 2u); break; }
+            uint64_t low_part = 0;
+            if (low_bits) {  // succinct.rs:318-333
+                const uint64_t bit = i * low_bits, word = bit >> 6, off = bit & 63;
+                low_part = low[word] >> off;
+                if (off + low_bits > 64) low_part |= low[word + 1] << (64 - off);
+                low_part &= low_mask;
+            }
+            out[i] = (high_part << low_bits) | low_part;
+            ++i;
+        }
+    }
+}
+
+// Data bytes taken by the (up to four) deltas of every control byte.
+__global__ void k_svb_group_bytes(const uint8_t *__restrict__ control, uint64_t n_control, uint64_t n_deltas,
+                                  uint64_t *__restrict__ bytes) {
+    for (uint64_t c = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; c <= n_control; c += (uint64_t)gridDim.x * blockDim.x) {
+        uint32_t total = 0;
+        if (c < n_control) {
+            const uint32_t tags = control[c];
+            for (uint32_t j = 0; j < 4 && c * 4 + j < n_deltas; ++j) total += ((tags >> (2 * j)) & 3u) + 1u;
+        }
+        bytes[c] = total;  // entry n_control: receives the total
+    }
+}
+
+// out[0] = first, out[i + 1] = delta i (succinct.rs:466-484 before its running sum).
+__global__ void k_svb_deltas(const uint8_t *__restrict__ control, const uint8_t *__restrict__ data,
+                             const uint64_t *__restrict__ group_at, uint64_t n_control, uint64_t n_deltas, uint32_t first,
+                             uint32_t *__restrict__ out) {
+    if (blockIdx.x == 0 && threadIdx.x == 0) out[0] = first;
+    for (uint64_t c = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; c < n_control; c += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t tags = control[c];
+        uint64_t at = group_at[c];
+        for (uint32_t j = 0; j < 4 && c * 4 + j < n_deltas; ++j) {
+            const uint32_t nbytes = ((tags >> (2 * j)) & 3u) + 1u;
+            uint32_t v = 0;
+            for (uint32_t b = 0; b < nbytes; ++b) v |= (uint32_t)data[at + b] << (8 * b);
+            out[c * 4 + j + 1] = v;
+            at += nbytes;
+        }
+    }
+}
+
+template <typename T>
+int32_t device_scan(T *d, uint64_t n, bool inclusive) {
+    if (n == 0) return AG_OK;
+    void *temp = nullptr;
+    size_t temp_bytes = 0;
+    cudaError_t e = inclusive ? cub::DeviceScan::InclusiveSum(nullptr, temp_bytes, d, d, (size_t)n)
+                              : cub::DeviceScan::ExclusiveSum(nullptr, temp_bytes, d, d, (size_t)n);
+    if (e == cudaSuccess) e = cudaMalloc(&temp, std::max<size_t>(temp_bytes, 16));
+    if (e == cudaSuccess)
+        e = inclusive ? cub::DeviceScan::InclusiveSum(temp, temp_bytes, d, d, (size_t)n)
+                      : cub::DeviceScan::ExclusiveSum(temp, temp_bytes, d, d, (size_t)n);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    cudaFree(temp);
+    if (e != cudaSuccess) return fail(AG_ERR_CUDA, "device scan failed: %s", cudaGetErrorString(e));
+    return AG_OK;
+}
+
+// A cursor over the payload: every byte read goes through the checksum, in file order.
+struct PayloadReader {
+    int fd;
+    uint64_t pos, end;
+    uint32_t crc = 0;
+    bool take(void *buf, uint64_t n) {
+        if (n > end - pos || !read_exact(fd, buf, n, pos)) return false;
+        crc = crc32_update(crc, buf, n);
+        pos += n;
+        return true;
+    }
+    bool u64(uint64_t *v) { return take(v, 8); }
+    bool u32(uint32_t *v) { return take(v, 4); }
+    // a section of `bytes` bytes straight into device memory
+    int32_t to_device(void *dev, uint64_t bytes) {
+        if (bytes > end - pos) return fail(AG_ERR_LOAD, "truncated: need %llu bytes at %llu", (unsigned long long)bytes, (unsigned long long)(pos - 32));
+        AG_TRY(stream_to_device(fd, pos, bytes, dev, &crc));
+        pos += bytes;
+        return AG_OK;
+    }
+};
+
+struct DevBuf {  // frees what a failed load leaves behind
+    void *p = nullptr;
+    ~DevBuf() { cudaFree(p); }
+    cudaError_t alloc(uint64_t bytes) { return cudaMalloc(&p, std::max<uint64_t>(bytes, 16)); }
+    template <typename T> T *as() { return (T *)p; }
+    void *release() { void *q = p; p = nullptr; return q; }
+};
+
+int32_t load_graph_compressed(int fd, uint64_t file_size, uint64_t n, uint64_t e, bool has_w, uint32_t checksum,
+                              int device, ag_graph **out) {
+    PayloadReader r{fd, 32, file_size};
+    auto truncated = [&](const char *what) {
+        return fail(AG_ERR_LOAD, "%s: truncated: the payload ends at byte %llu", what, (unsigned long long)(file_size - 32));
+    };
+    // ---- offsets section
+    uint64_t ef_len, universe, low_words, high_words;
+    uint32_t low_bits;
+    if (!r.u64(&ef_len) || !r.u64(&universe) || !r.u32(&low_bits) || !r.u64(&low_words)) return truncated("offsets section");
+    if (low_bits >= 64) return fail(AG_ERR_LOAD, "offsets section: EF low_bits %u out of range", low_bits);
+    if (low_words > (file_size - r.pos) / 8) return truncated("offsets section: EF low words");
+    DevBuf low, high, first_index, offsets, control, data, group_at, dst, weights, flag;
+    if (low.alloc((low_words + 1) * 8) != cudaSuccess) return fail(AG_ERR_CUDA, "out of device memory for the offsets section");
+    AG_CUDA(cudaMemset(low.p, 0, (low_words + 1) * 8));  // one word past the end: the two-word read of the last element
+    AG_TRY(r.to_device(low.p, low_words * 8));
+    if (!r.u64(&high_words)) return truncated("offsets section");
+    if (high_words > (file_size - r.pos) / 8) return truncated("offsets section: EF high words");
+    if (ef_len != n + 1) return fail(AG_ERR_LOAD, "offsets section has %llu entries for %llu nodes", (unsigned long long)ef_len, (unsigned long long)n);
+    // succinct.rs:236-246: the low array must cover len * low_bits bits
+    const unsigned __int128 low_bits_total = (unsigned __int128)ef_len * low_bits;
+    if ((unsigned __int128)low_words * 64 < low_bits_total)
+        return fail(AG_ERR_LOAD, "offsets section: EF low array truncated: %llu words", (unsigned long long)low_words);
+    if (high.alloc(high_words * 8) != cudaSuccess || first_index.alloc((high_words + 1) * 8) != cudaSuccess ||
+        offsets.alloc(ef_len * 8) != cudaSuccess || flag.alloc(4) != cudaSuccess)
+        return fail(AG_ERR_CUDA, "out of device memory for the offsets section");
+    AG_TRY(r.to_device(high.p, high_words * 8));
+    AG_CUDA(cudaMemset(flag.p, 0, 4));
+    k_popcount_words<<<grid_for(high_words + 1), 256>>>(high.as<uint64_t>(), high_words, first_index.as<uint64_t>());
+    AG_TRY(device_scan(first_index.as<uint64_t>(), high_words + 1, false));
+    uint64_t ones = 0;
+    AG_CUDA(cudaMemcpy(&ones, first_index.as<uint64_t>() + high_words, 8, cudaMemcpyDeviceToHost));
+    if (ones != ef_len)
+        return fail(AG_ERR_LOAD, "offsets section: EF high array has %llu set bits for %llu elements", (unsigned long long)ones, (unsigned long long)ef_len);
+    if (high_words)
+        k_ef_decode<<<grid_for(high_words), 256>>>(high.as<uint64_t>(), high_words, first_index.as<uint64_t>(), low.as<uint64_t>(),
+                                                   low_bits, ef_len, universe >> low_bits, offsets.as<uint64_t>(), flag.as<uint32_t>());
+    uint32_t bad = 0;
+    uint64_t last = 0;
+    AG_CUDA(cudaMemcpy(&bad, flag.p, 4, cudaMemcpyDeviceToHost));
+    if (bad) return fail(AG_ERR_LOAD, "offsets section: an EF element exceeds universe %llu", (unsigned long long)universe);
+    AG_CUDA(cudaMemcpy(&last, offsets.as<uint64_t>() + ef_len - 1, 8, cudaMemcpyDeviceToHost));
+    if (last != universe)
+        return fail(AG_ERR_LOAD, "offsets section: EF last element %llu disagrees with universe %llu", (unsigned long long)last, (unsigned long long)universe);
+    cudaFree(low.release()); cudaFree(high.release()); cudaFree(first_index.release());
+
+    // ---- edges section
+    uint64_t svb_len, n_control, n_data;
+    uint32_t first;
+    if (!r.u64(&svb_len) || !r.u32(&first) || !r.u64(&n_control)) return truncated("edges section");
+    if (svb_len != e) return fail(AG_ERR_LOAD, "edges section has %llu entries, header says %llu", (unsigned long long)svb_len, (unsigned long long)e);
+    const uint64_t n_deltas = svb_len ? svb_len - 1 : 0;
+    if (n_control != (n_deltas + 3) / 4)
+        return fail(AG_ERR_LOAD, "edges section: SVB control stream is %llu bytes for %llu deltas", (unsigned long long)n_control, (unsigned long long)n_deltas);
+    if (n_control > file_size - r.pos) return truncated("edges section: SVB control stream");
+    if (control.alloc(n_control) != cudaSuccess || group_at.alloc((n_control + 1) * 8) != cudaSuccess)
+        return fail(AG_ERR_CUDA, "out of device memory for the edges section");
+    AG_TRY(r.to_device(control.p, n_control));
+    if (!r.u64(&n_data)) return truncated("edges section");
+    if (n_data > file_size - r.pos) return truncated("edges section: SVB data stream");
+    k_svb_group_bytes<<<grid_for(n_control + 1), 256>>>(control.as<uint8_t>(), n_control, n_deltas, group_at.as<uint64_t>());
+    AG_TRY(device_scan(group_at.as<uint64_t>(), n_control + 1, false));
+    uint64_t need = 0;
+    AG_CUDA(cudaMemcpy(&need, group_at.as<uint64_t>() + n_control, 8, cudaMemcpyDeviceToHost));
+    if (need != n_data)
+        return fail(AG_ERR_LOAD, "edges section: SVB data stream is %llu bytes, control tags call for %llu", (unsigned long long)n_data, (unsigned long long)need);
+    if (data.alloc(n_data) != cudaSuccess || dst.alloc(e * 4) != cudaSuccess)
+        return fail(AG_ERR_CUDA, "out of device memory for the edges section");
+    AG_TRY(r.to_device(data.p, n_data));
+    if (e) {
+        k_svb_deltas<<<grid_for(std::max<uint64_t>(n_control, 1)), 256>>>(control.as<uint8_t>(), data.as<uint8_t>(), group_at.as<uint64_t>(),
+                                                                         n_control, n_deltas, first, dst.as<uint32_t>());
+        AG_TRY(device_scan(dst.as<uint32_t>(), e, true));  // wrapping running sum (succinct.rs:472-483)
+    }
+    cudaFree(control.release()); cudaFree(data.release()); cudaFree(group_at.release());
+
+    // ---- weights
+    if (has_w) {
+        if (file_size - r.pos != e * 4)
+            return fail(AG_ERR_LOAD, "weights section is %llu bytes for %llu edges", (unsigned long long)(file_size - r.pos), (unsigned long long)e);
+        if (weights.alloc(e * 4) != cudaSuccess) return fail(AG_ERR_CUDA, "out of device memory for the weights");
+        AG_TRY(r.to_device(weights.p, e * 4));
+    } else if (r.pos != file_size) {
+        return fail(AG_ERR_LOAD, "trailing bytes after edges section");
+    }
+    // every load with a checksum verifies it (compressed_graph.rs:107-117)
+    if (checksum != 0 && r.crc != checksum)
+        return fail(AG_ERR_LOAD, "compressed graph checksum mismatch: expected %#x, got %#x", checksum, r.crc);
+    AG_CUDA(cudaDeviceSynchronize());
+    ag_graph *g = new ag_graph();
+    g->device = device; g->num_nodes = n; g->num_edges = e;
+    g->offsets = (uint64_t *)offsets.release(); g->dst = (uint32_t *)dst.release();
+    g->weights = has_w ? (float *)weights.release() : nullptr;
+    const int32_t st = validate_on_device(g, true);  // always Full (compressed_graph.rs:84-89,165-172)
+    if (st != AG_OK) { ag_graph_free(g); return st; }
+    *out = g;
+    return AG_OK;
+}
+
+}  // namespace
+}  // namespace ag
+
+// Host-side encoder (the write path is not hot): Graph.save(path, compressed=True).
+extern "C" int32_t ag_graph_save_compressed(const ag_graph *g, const char *path) {
+    if (!g || !path) return fail(AG_ERR_VALUE, "ag_graph_save_compressed: null argument");
+    DeviceGuard guard(g->device);
+    if (!guard.ok) return AG_ERR_CUDA;
+    const uint64_t n = g->num_nodes, e = g->num_edges;
+    std::vector<uint64_t> offsets(n + 1);
+    std::vector<uint32_t> edges(e);
+    std::vector<float> w(g->weights ? e : 0);
+    AG_CUDA(cudaMemcpy(offsets.data(), g->offsets, offsets.size() * 8, cudaMemcpyDeviceToHost));
+    if (e) AG_CUDA(cudaMemcpy(edges.data(), g->dst, e * 4, cudaMemcpyDeviceToHost));
+    if (g->weights && e) AG_CUDA(cudaMemcpy(w.data(), g->weights, e * 4, cudaMemcpyDeviceToHost));
+    std::vector<uint8_t> payload;
+    auto put = [&](const void *p, size_t bytes) { payload.insert(payload.end(), (const uint8_t *)p, (const uint8_t *)p + bytes); };
+    {   // Elias-Fano of the offsets (succinct.rs:52-92)
+        const uint64_t len = offsets.size(), universe = offsets.back();
+        uint32_t low_bits = 0;
+        if (universe >= len) { uint64_t q = universe / len; while (q >>= 1) ++low_bits; }
+        const uint64_t high_len = len + (universe >> low_bits) + 1;
+        std::vector<uint64_t> high((high_len + 63) / 64, 0), low;
+        const uint64_t low_mask = low_bits ? ((1ull << low_bits) - 1ull) : 0ull;
+        uint64_t bit_len = 0;
+        for (uint64_t i = 0; i < len; ++i) {
+            const uint64_t v = offsets[i];
+            if (low_bits) {
+                const uint64_t value = v & low_mask, word = bit_len / 64, off = bit_len % 64;
+                if (word >= low.size()) low.push_back(0);
+                low[word] |= value << off;
+                if (off + low_bits > 64) low.push_back(value >> (64 - off));
+                bit_len += low_bits;
+            }
+            const uint64_t hp = (v >> low_bits) + i;
+            high[hp / 64] |= 1ull << (hp % 64);
+        }
+        const uint64_t lw = low.size(), hw = high.size();
+        put(&len, 8); put(&universe, 8); put(&low_bits, 4); put(&lw, 8); put(low.data(), lw * 8); put(&hw, 8); put(high.data(), hw * 8);
+    }
+    {   // StreamVByte of the wrapping deltas of the whole edge array (succinct.rs:397-420)
+        const uint64_t len = e;
+        const uint32_t first = e ? edges[0] : 0;
+        const uint64_t n_deltas = e ? e - 1 : 0;
+        std::vector<uint8_t> control((n_deltas + 3) / 4, 0), data;
+        data.reserve(n_deltas);
+        uint32_t prev = first;
+        for (uint64_t i = 0; i < n_deltas; ++i) {
+            const uint32_t v = edges[i + 1], delta = v - prev;
+            const uint32_t nbytes = delta < (1u << 8) ? 1 : delta < (1u << 16) ? 2 : delta < (1u << 24) ? 3 : 4;
+            for (uint32_t b = 0; b < nbytes; ++b) data.push_back((uint8_t)(delta >> (8 * b)));
+            control[i / 4] |= (uint8_t)((nbytes - 1) << ((i % 4) * 2));
+            prev = v;
+        }
+        const uint64_t nc = control.size(), nd = data.size();
+        put(&len, 8); put(&first, 4); put(&nc, 8); put(control.data(), nc); put(&nd, 8); put(data.data(), nd);
+    }
+    if (g->weights) put(w.data(), w.size() * 4);
+    const uint32_t crc = crc32_update(0, payload.data(), payload.size());
+    uint8_t h[32] = {0};
+    const uint32_t version = kCompressedVersion, has_w = g->weights ? 1 : 0;
+    memcpy(h, &kGraphMagic, 4); memcpy(h + 4, &version, 4); memcpy(h + 8, &n, 8);
+    memcpy(h + 16, &e, 8); memcpy(h + 24, &has_w, 4); memcpy(h + 28, &crc, 4);
+    AtomicFile f;
+    if (!f.open_tmp(path)) return fail(AG_ERR_LOAD, "failed to create %s: %s", path, strerror(errno));
+    if (write_all(f.fd, h, 32) || write_all(f.fd, payload.data(), payload.size())) {
+        f.abort();
+        return fail(AG_ERR_LOAD, "failed to write %s: %s", path, strerror(errno));
+    }
+    if (!f.commit()) return fail(AG_ERR_LOAD, "failed to move output into %s: %s", path, strerror(errno));
+    return AG_OK;
+}
+
+
 // AETH v1 (reference: internal/mmap.rs:114-121 header, :502-600 layout,
 // :601-632 checksum policy, :633-643 default validation level).
 extern "C" int32_t ag_graph_load(const char *path, int32_t validation, int32_t device, ag_graph **out) {
@@ -575,9 +879,16 @@ extern "C" int32_t ag_graph_load(const char *path, int32_t validation, int32_t d
     memcpy(&has_w, h + 24, 4); memcpy(&checksum, h + 28, 4);
     auto bail = [&](int32_t st) { close(fd); return st; };
     if (magic != kGraphMagic) return bail(fail(AG_ERR_LOAD, "invalid magic number"));
-    if (version != 1) return bail(fail(AG_ERR_LOAD, "unsupported version: expected 1, got %u", version));
+    if (version != 1 && version != 2) return bail(fail(AG_ERR_LOAD, "unsupported version: expected 1, got %u", version));
     if (n > 0xFFFFFFFFull) return bail(fail(AG_ERR_LOAD, "num_nodes %llu exceeds maximum %llu", (unsigned long long)n, 0xFFFFFFFFull));
     if (e > kMaxEdges) return bail(fail(AG_ERR_LOAD, "num_edges %llu exceeds maximum %llu", (unsigned long long)e, (unsigned long long)kMaxEdges));
+    if (version == 2) {  // succinct-coded CSR: decoded on the device, always fully validated
+        DeviceGuard guard2(device);
+        if (!guard2.ok) return bail(AG_ERR_CUDA);
+        const int32_t st2 = load_graph_compressed(fd, file_size, n, e, has_w != 0, checksum, device, out);
+        close(fd);
+        return st2;
+    }
     const uint64_t off_bytes = (n + 1) * 8, edge_bytes = e * 4, w_bytes = has_w ? e * 4 : 0;
     const uint64_t need = 32 + off_bytes + edge_bytes + w_bytes;
     if (file_size < need)
@@ -643,6 +954,7 @@ extern "C" int32_t ag_graph_save(const ag_graph *g, const char *path) {
     if (!f.commit()) return fail(AG_ERR_LOAD, "failed to move output into %s: %s", path, strerror(errno));
     return AG_OK;
 }
+
 
 extern "C" int32_t ag_graph_info(const ag_graph *g, uint64_t *num_nodes, uint64_t *num_edges,
                                  int32_t *has_weights, int32_t *device) {

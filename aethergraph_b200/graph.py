@@ -47,7 +47,8 @@ class CsrGraph:
     # -- constructors ------------------------------------------------------
     @staticmethod
     def load(path, *, storage: str = "auto", validation: str = "auto", device: int | None = None) -> "CsrGraph":
-        """Load an AETH v1 file into GPU memory.
+        """Load an AETH file (flat version 1, or the compressed version 2, which is decoded
+        on the GPU and always fully validated) into GPU memory.
 
         `storage` is accepted for signature compatibility; the CSR always
         lives in HBM.  `validation` picks whether the body checksum is
@@ -129,9 +130,11 @@ class CsrGraph:
         return CsrGraph(out.value)
 
     def save(self, path, *, compressed: bool = False) -> None:
-        if compressed:
-            raise ValueError("the compressed (version 2) graph format is not supported on this path")
-        _lib.check(_lib.lib().ag_graph_save(self._h, os.fspath(path).encode()))
+        """Write the graph: the flat AETH v1 file, or with `compressed=True` the succinct-coded
+        version 2 (Elias-Fano offsets, StreamVByte edge deltas; python/aethergraph/_core.pyi:95-99).
+        `Graph.load` reads either."""
+        fn = _lib.lib().ag_graph_save_compressed if compressed else _lib.lib().ag_graph_save
+        _lib.check(fn(self._h, os.fspath(path).encode()))
 
     # -- properties --------------------------------------------------------
     @property

@@ -90,6 +90,13 @@ int32_t ag_graph_from_edges(uint64_t num_nodes, const uint32_t *src, const uint3
                             const float *weights, uint64_t num_edges, int32_t device,
                             ag_graph **out);
 int32_t ag_graph_save(const ag_graph *g, const char *path);
+/* The version-2 file: the same 32-byte header with version = 2, the offsets as
+ * Elias-Fano and the edge array as StreamVByte wrapping deltas, weights raw, checksum
+ * over the payload (crates/aethergraph-core/src/internal/compressed_graph.rs:39-88;
+ * codecs and wire formats internal/succinct.rs:52-92,198-214,397-420,486-500).
+ * ag_graph_load recognises the version, decodes both sections on the GPU and always
+ * verifies the checksum and the whole CSR (compressed_graph.rs:99-175). */
+int32_t ag_graph_save_compressed(const ag_graph *g, const char *path);
 int32_t ag_graph_info(const ag_graph *g, uint64_t *num_nodes, uint64_t *num_edges,
                       int32_t *has_weights, int32_t *device);
 int32_t ag_graph_device_ptrs(const ag_graph *g, const uint64_t **offsets_dev,

@@ -597,3 +597,128 @@ def read_hetero_file(path):
         relations.append((s, rel, d, offsets, edges, weights))
     assert at == len(raw), "trailing bytes"
     return node_types, relations
+
+
+# ------------------------------------------------ AETH version 2 (compressed) --
+# Succinct-coded CSR at rest (crates/aethergraph-core/src/internal/compressed_graph.rs:1-19,
+# 39-88, 99-175) through the two codecs of internal/succinct.rs, restated in numpy.
+def ef_encode(values):
+    """Elias-Fano of a non-decreasing u64 sequence (succinct.rs:52-92):
+    -> (len, universe, low_bits, low words, high words)."""
+    v = np.ascontiguousarray(values, dtype=np.uint64)
+    n = int(v.size)
+    assert n < 2 or bool(np.all(v[:-1] <= v[1:])), "EliasFano requires a sorted sequence"
+    universe = int(v[-1]) if n else 0
+    low_bits = 0 if n == 0 or universe < n else (universe // n).bit_length() - 1
+    high = np.zeros((n + (universe >> low_bits) + 1 + 63) // 64, dtype=np.uint64)
+    idx = np.arange(n, dtype=np.uint64)
+    pos = (v >> np.uint64(low_bits)) + idx
+    np.bitwise_or.at(high, (pos // np.uint64(64)).astype(np.int64), np.uint64(1) << (pos % np.uint64(64)))
+    low = np.zeros((n * low_bits + 63) // 64, dtype=np.uint64)
+    if low_bits:
+        part = v & np.uint64((1 << low_bits) - 1)
+        bit = idx * np.uint64(low_bits)
+        word, off = (bit // np.uint64(64)).astype(np.int64), bit % np.uint64(64)
+        np.bitwise_or.at(low, word, part << off)                      # the bits that fit the word
+        spill = (off + np.uint64(low_bits)) > np.uint64(64)           # the rest starts the next word
+        np.bitwise_or.at(low, word[spill] + 1, part[spill] >> (np.uint64(64) - off[spill]))
+    return n, universe, low_bits, low, high
+
+
+def ef_decode(n: int, universe: int, low_bits: int, low: np.ndarray, high: np.ndarray) -> np.ndarray:
+    """The sequence back (succinct.rs:162-192): element i sits at the (i+1)-th set bit."""
+    bits = np.unpackbits(np.ascontiguousarray(high, dtype="<u8").view(np.uint8), bitorder="little")
+    pos = np.flatnonzero(bits).astype(np.uint64)
+    assert pos.size == n, f"EF high array has {pos.size} set bits for {n} elements"
+    idx = np.arange(n, dtype=np.uint64)
+    out = (pos - idx) << np.uint64(low_bits)
+    if low_bits and n:
+        lw = np.concatenate([np.ascontiguousarray(low, dtype=np.uint64), np.zeros(1, dtype=np.uint64)])
+        bit = idx * np.uint64(low_bits)
+        word, off = (bit // np.uint64(64)).astype(np.int64), bit % np.uint64(64)
+        part = lw[word] >> off
+        spill = (off + np.uint64(low_bits)) > np.uint64(64)
+        part[spill] |= lw[word[spill] + 1] << (np.uint64(64) - off[spill])
+        out |= part & np.uint64((1 << low_bits) - 1)
+    return out
+
+
+def svb_encode(values):
+    """StreamVByte of the wrapping deltas of a u32 sequence (succinct.rs:397-420, 586-600):
+    -> (len, first, control bytes, data bytes)."""
+    v = np.ascontiguousarray(values, dtype=np.uint32)
+    n = int(v.size)
+    if n == 0:
+        return 0, 0, np.zeros(0, np.uint8), np.zeros(0, np.uint8)
+    d = (v[1:] - v[:-1]).astype(np.uint32)  # wraps modulo 2^32
+    nbytes = 1 + (d >= (1 << 8)).astype(np.int64) + (d >= (1 << 16)) + (d >= (1 << 24))
+    control = np.zeros((d.size + 3) // 4, dtype=np.uint8)
+    i = np.arange(d.size)
+    np.bitwise_or.at(control, i // 4, ((nbytes - 1) << ((i % 4) * 2)).astype(np.uint8))
+    le = d.astype("<u4").view(np.uint8).reshape(-1, 4)
+    data = le[np.arange(4)[None, :] < nbytes[:, None]]
+    return n, int(v[0]), control, np.ascontiguousarray(data)
+
+
+def svb_decode(n: int, first: int, control: np.ndarray, data: np.ndarray) -> np.ndarray:
+    """Running wrapping sum of the deltas (succinct.rs:468-484)."""
+    if n == 0:
+        return np.zeros(0, np.uint32)
+    nd = n - 1
+    i = np.arange(nd)
+    nbytes = ((control[i // 4].astype(np.int64) >> ((i % 4) * 2)) & 3) + 1
+    start = np.concatenate([[0], np.cumsum(nbytes)[:-1]]) if nd else np.zeros(0, np.int64)
+    assert int(nbytes.sum()) == data.size, f"SVB data stream is {data.size} bytes, control tags call for {int(nbytes.sum())}"
+    padded = np.concatenate([data, np.zeros(4, np.uint8)])
+    d = np.zeros(nd, dtype=np.uint64)
+    for b in range(4):
+        d |= np.where(b < nbytes, padded[start + b].astype(np.uint64) << np.uint64(8 * b), np.uint64(0))
+    acc = (np.uint64(first) + np.concatenate([[np.uint64(0)], np.cumsum(d, dtype=np.uint64)])) & np.uint64(0xFFFFFFFF)
+    return acc.astype(np.uint32)
+
+
+def compressed_graph_bytes(offsets, dst, weights=None, checksum: bool = True) -> bytes:
+    """The whole version-2 file (compressed_graph.rs:39-88; wire formats succinct.rs:198-214, 486-500)."""
+    import struct
+
+    off = np.ascontiguousarray(offsets, dtype=np.uint64)
+    n, universe, low_bits, low, high = ef_encode(off)
+    m, first, control, data = svb_encode(dst)
+    payload = struct.pack("<QQIQ", n, universe, low_bits, low.size) + low.astype("<u8").tobytes()
+    payload += struct.pack("<Q", high.size) + high.astype("<u8").tobytes()
+    payload += struct.pack("<QIQ", m, first, control.size) + control.tobytes() + struct.pack("<Q", data.size) + data.tobytes()
+    if weights is not None:
+        payload += np.ascontiguousarray(weights, dtype="<f4").tobytes()
+    head = struct.pack("<IIQQII", 0x41455448, 2, off.size - 1, m, 1 if weights is not None else 0,
+                       crc32(payload) if checksum else 0)
+    return head + payload
+
+
+def read_compressed_graph(raw: bytes):
+    """-> (num_nodes, offsets u64, dst u32, weights f32 | None), with the loader's checks
+    (compressed_graph.rs:99-175)."""
+    import struct
+
+    magic, version, n, e, has_w, crc = struct.unpack_from("<IIQQII", raw, 0)
+    assert magic == 0x41455448 and version == 2
+    payload = raw[32:]
+    if crc:
+        assert crc32(payload) == crc, "compressed graph checksum mismatch"
+    ef_len, universe, low_bits, lw = struct.unpack_from("<QQIQ", payload, 0)
+    at = 28
+    low = np.frombuffer(payload, "<u8", lw, at); at += lw * 8
+    (hw,) = struct.unpack_from("<Q", payload, at); at += 8
+    high = np.frombuffer(payload, "<u8", hw, at); at += hw * 8
+    assert ef_len == n + 1
+    m, first, nc = struct.unpack_from("<QIQ", payload, at); at += 20
+    control = np.frombuffer(payload, np.uint8, nc, at); at += nc
+    (nd,) = struct.unpack_from("<Q", payload, at); at += 8
+    data = np.frombuffer(payload, np.uint8, nd, at); at += nd
+    assert m == e
+    w = None
+    if has_w:
+        w = np.frombuffer(payload, "<f4", e, at).copy(); at += e * 4
+    assert at == len(payload), "trailing bytes after edges section"
+    off = ef_decode(ef_len, universe, low_bits, low, high)
+    assert off.size == 0 or int(off[-1]) == universe
+    return n, off, svb_decode(m, first, control, data), w

@@ -215,3 +215,111 @@ def test_gpu_reproduces_the_golden_samples(ag):
             store = ag.FeatureStore.from_array(feats, dtype)
             x = store.get_batch(sg.nodes[:64])
             assert np.array_equal(x.view(np.uint32), g[f"{name}.x.{dtype}"].view(np.uint32))
+
+
+# ---- AETH version 2 (Elias-Fano offsets + StreamVByte edges), decoded on the GPU ----
+def _csr_cases():
+    from helpers import rmat_csr
+
+    rng = np.random.default_rng(5)
+    n, off, dst, _ = rmat_csr(12, 12, seed=8)
+    sorted_rows = np.concatenate([np.sort(dst[off[v]:off[v + 1]]) for v in range(n)]).astype(np.uint32)
+    yield "rmat sorted rows", n, off, sorted_rows, None
+    yield "rmat unsorted rows, weighted", n, off, dst, rng.random(dst.size).astype(np.float32)  # backward steps: 4-byte deltas
+    yield "no edges", 7, np.zeros(8, np.uint64), np.zeros(0, np.uint32), None
+    yield "one edge", 2, np.array([0, 1, 1], np.uint64), np.array([1], np.uint32), np.array([0.5], np.float32)
+    deg = rng.integers(0, 3, 3000)
+    off2 = np.concatenate([[0], np.cumsum(deg)]).astype(np.uint64)
+    yield "sparse degrees", 3000, off2, rng.integers(0, 3000, int(off2[-1])).astype(np.uint32), None
+    # five deltas (not a multiple of four) of every byte length
+    seq = np.array([0, 1, 300, 70_000, 17_000_000, 5], np.uint32)
+    yield "delta lengths", 17_000_001, np.concatenate([[0], np.full(17_000_001, 6)]).astype(np.uint64), seq, None
+
+
+def test_compressed_graph_files_decode_on_the_gpu_and_save_bit_for_bit(ag, ago, tmp_path):
+    """Files written by the numpy restatement of the reference's codecs load into the same
+    CSR, and what `save(compressed=True)` writes is the same file byte for byte
+    (compressed_graph.rs:39-175; round trips of its tests :205-235)."""
+    for name, n, off, dst, w in _csr_cases():
+        raw = ago.compressed_graph_bytes(off, dst, w)
+        p = tmp_path / "g2.bin"
+        p.write_bytes(raw)
+        g = ag.Graph.load(p)
+        assert (g.num_nodes, g.num_edges, g.has_weights) == (n, dst.size, w is not None), name
+        o2, d2, w2 = g.to_host()
+        assert np.array_equal(o2, off) and np.array_equal(d2, dst), name
+        if w is not None:
+            assert np.array_equal(w2, w), name
+        out = tmp_path / "saved2.bin"
+        g.save(out, compressed=True)
+        assert out.read_bytes() == raw, name
+        flat = tmp_path / "flat.bin"
+        g.save(flat)                                     # and back to version 1
+        assert np.array_equal(ag.Graph.load(flat).to_host()[1], dst), name
+
+
+def test_compressed_graph_samples_like_the_flat_one(ag, ago, tmp_path):
+    # compressed_graph.rs:281-297
+    from helpers import rmat_csr
+
+    n, off, dst, _ = rmat_csr(11, 10, seed=3)
+    p = tmp_path / "g2.bin"
+    p.write_bytes(ago.compressed_graph_bytes(off, dst))
+    g = ag.Graph.load(p)
+    seeds = np.arange(64, dtype=np.uint32)
+    got = ag.NeighborSampler(g, ag.SamplingConfig(num_neighbors=[5, 3], seed=7)).sample(seeds)
+    want = ago.Sampler(off, dst, [5, 3], seed=7).sample(seeds)
+    assert_same_subgraph(got.raw_u32(), want)
+
+
+def test_loader_rejects_malformed_compressed_files(ag, ago, tmp_path):
+    """One malformed file per check of the reader (compressed_graph.rs:105-160;
+    succinct.rs:225-262 and its tests :735-795, :506-535)."""
+    from helpers import rmat_csr
+
+    n, off, dst, _ = rmat_csr(8, 8, seed=1)
+    dst = np.concatenate([np.sort(dst[off[v]:off[v + 1]]) for v in range(n)]).astype(np.uint32)
+    good = bytearray(ago.compressed_graph_bytes(off, dst, checksum=False))
+
+    def load(data, match):
+        p = tmp_path / "bad2.bin"
+        p.write_bytes(bytes(data))
+        with pytest.raises(ag.GraphLoadError, match=match):
+            ag.Graph.load(p)
+
+    ag.Graph.load(_write(tmp_path, "ok2.bin", good))                      # zero checksum: not verified
+    with_crc = bytearray(ago.compressed_graph_bytes(off, dst))
+    with_crc[-1] ^= 0x01
+    load(with_crc, "checksum mismatch")
+    load(good[:-1], "truncated|control tags")                             # data stream one byte short
+    load(good + b"\0", "trailing bytes")
+    ef_len, universe, low_bits, lw = struct.unpack_from("<QQIQ", good, 32)
+    hw_at = 32 + 28 + lw * 8
+    (hw,) = struct.unpack_from("<Q", good, hw_at)
+    bad = bytearray(good); struct.pack_into("<Q", bad, 32, ef_len + 1)
+    load(bad, "offsets section has")
+    bad = bytearray(good); struct.pack_into("<I", bad, 32 + 16, 64)
+    load(bad, "low_bits")
+    bad = bytearray(good); bad[hw_at + 8 + hw * 8 - 8: hw_at + 8 + hw * 8] = b"\0" * 8    # a cleared high word
+    load(bad, "set bits")
+    bad = bytearray(good); struct.pack_into("<Q", bad, 32 + 8, universe + (1 << 40))      # universe the last element misses
+    load(bad, "universe")
+    svb_at = hw_at + 8 + hw * 8
+    bad = bytearray(good); struct.pack_into("<Q", bad, svb_at, dst.size + 1)
+    load(bad, "edges section has")
+    (nc,) = struct.unpack_from("<Q", good, svb_at + 12)
+    bad = bytearray(good); bad[svb_at + 20] |= 0x03                                        # first delta claims 4 bytes
+    load(bad, "control tags call for")
+    # offsets that decrease through the low bits (succinct.rs:772-781), as a whole file: 1 node, offsets [3, 1]
+    payload = struct.pack("<QQIQ", 2, 3, 2, 1) + struct.pack("<Q", 3 | (1 << 2)) + struct.pack("<QQ", 1, 0b11)
+    payload += struct.pack("<QIQ", 3, 0, 1) + bytes([0]) + struct.pack("<Q", 2) + bytes([0, 0])
+    load(struct.pack("<IIQQII", 0x41455448, 2, 1, 3, 0, 0) + payload, "invalid CSR|universe")
+    # a destination outside the graph is caught by the full validation every compressed load runs
+    bad_dst = dst.copy(); bad_dst[3] = n + 5
+    load(ago.compressed_graph_bytes(off, bad_dst), "destination")
+
+
+def _write(tmp_path, name, data):
+    p = tmp_path / name
+    p.write_bytes(bytes(data))
+    return p

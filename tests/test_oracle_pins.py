@@ -415,3 +415,75 @@ def test_block_scaled_int8_codec_follows_the_reference_tests():
     assert abs((codes.size + scales.size * 4) / (codes.size * 4) - 1.125 / 4.0) < 1e-9
     # codes are symmetric, clamped to +-127, the peak of a block is +-127
     assert codes.min() >= -127 and np.all(np.abs(codes.reshape(8, 4, 32)).max(axis=2) == 127)
+
+
+# ---- AETH version 2: the succinct codecs (crates/aethergraph-core/src/internal/succinct.rs) ----
+def test_elias_fano_cases_of_the_reference_round_trip():
+    # succinct.rs:607-640 (round trips, large universe), :704-722 (serialisation cases)
+    from oracle import ago
+
+    cases = [[], [0], [5], [0, 0, 0, 0], [1, 2, 3, 4, 5], [0, 10, 20, 30, 1000], [i * 7 for i in range(1000)],
+             [0, 1, 1, 2, 3, 5, 8, 13, 21, 34, 55], [0, 1_000, 1_000_000, 4_000_000_000], [0, 0, 7, 7, 1_000_000],
+             [i * 13 for i in range(2048)]]
+    for c in cases:
+        n, universe, low_bits, low, high = ago.ef_encode(np.array(c, dtype=np.uint64))
+        assert n == len(c) and universe == (c[-1] if c else 0)
+        assert int(sum(bin(int(w)).count("1") for w in high)) == len(c)           # one set bit per element
+        assert low.size == (len(c) * low_bits + 63) // 64
+        assert ago.ef_decode(n, universe, low_bits, low, high).tolist() == c
+    # 4096 ids in a 65536 universe stay well under 16 bits per element (succinct.rs:642-650)
+    n, _, _, low, high = ago.ef_encode(np.arange(4096, dtype=np.uint64) * 16)
+    assert (low.size + high.size) * 64 / n < 16.0
+
+
+def test_elias_fano_bit_layout_matches_the_reference_hand_built_records():
+    # succinct.rs:772-781: two elements in high bucket 0 with low parts 3 then 1 -> low = 3 | 1 << 2, high = 0b11
+    from oracle import ago
+
+    assert ago.ef_decode(2, 3, 2, np.array([3 | (1 << 2)], np.uint64), np.array([0b11], np.uint64)).tolist() == [3, 1]
+    # the encoder's own record for [1, 5, 9, 200] (succinct.rs:739-741) decodes to itself and follows
+    # low_bits = floor(log2(universe / len)) (succinct.rs:60-66)
+    n, universe, low_bits, low, high = ago.ef_encode(np.array([1, 5, 9, 200], np.uint64))
+    assert (n, universe, low_bits) == (4, 200, 5)
+    assert int(low[0]) == 1 | (5 << 5) | (9 << 10) | ((200 & 31) << 15)
+    assert [i for i in range(64) if int(high[0]) >> i & 1] == [0, 1, 2, (200 >> 5) + 3]
+    # succinct.rs:785-789: one element with bit 2 set, low_bits 0 -> value 2 (the reader rejects it for universe 5)
+    assert ago.ef_decode(1, 5, 0, np.zeros(0, np.uint64), np.array([1 << 2], np.uint64)).tolist() == [2]
+
+
+def test_streamvbyte_cases_of_the_reference_round_trip():
+    # succinct.rs:659-673, :688-702 (non-monotone, wrapping), :797-806 (length boundaries)
+    from oracle import ago
+
+    cases = [[], [42], [0, 1, 2, 3, 4], [0, 255, 256, 65535, 65536, 16_777_215, 16_777_216], [i * 3 for i in range(1000)],
+             [100] * 4, [0, 2**32 - 1], [5, 3], [10, 0, 2**32 - 1, 1, 2, 1], [2**32 - 1, 0, 2**32 - 1],
+             [(i * 2_654_435_761) % 4_294_967_291 for i in range(500)]]
+    for c in cases:
+        n, first, control, data = ago.svb_encode(np.array(c, dtype=np.uint32))
+        assert n == len(c) and control.size == (max(len(c) - 1, 0) + 3) // 4
+        assert ago.svb_decode(n, first, control, data).tolist() == c
+    # deltas 0, 255 | 256, 65535 | 65536, 16777215 | 16777216, 2^32-1 take 1, 1, 2, 2, 3, 3, 4, 4 bytes
+    seq = np.cumsum([0, 0, 255, 256, 65_535, 65_536, 16_777_215, 16_777_216, 2**32 - 1], dtype=np.uint64).astype(np.uint32)
+    _, _, control, data = ago.svb_encode(seq)
+    assert control.tolist() == [0b01_01_00_00, 0b11_11_10_10] and data.size == 20
+    # consecutive ids: about one byte per value (succinct.rs:675-686)
+    _, _, control, data = ago.svb_encode(np.arange(10_000, dtype=np.uint32))
+    assert control.size + data.size < 20_000
+
+
+def test_compressed_graph_file_layout_and_round_trip():
+    # compressed_graph.rs:39-88 (writer), :99-175 (reader), tests :205-235
+    import struct
+
+    from oracle import ago
+
+    n, off, dst, _ = rmat_csr(10, 8, seed=2)
+    order = np.concatenate([np.sort(dst[off[v]:off[v + 1]]) for v in range(n)]).astype(np.uint32)  # sorted rows compress
+    w = np.random.default_rng(1).random(order.size).astype(np.float32)
+    raw = ago.compressed_graph_bytes(off, order, w)
+    magic, version, nn, ee, has_w, crc = struct.unpack_from("<IIQQII", raw, 0)
+    assert (magic, version, nn, ee, has_w) == (0x41455448, 2, n, order.size, 1) and crc == ago.crc32(raw[32:])
+    back = ago.read_compressed_graph(raw)
+    assert back[0] == n and np.array_equal(back[1], off) and np.array_equal(back[2], order) and np.array_equal(back[3], w)
+    flat = (n + 1) * 8 + order.size * 4
+    assert len(ago.compressed_graph_bytes(off, order)) < flat          # "compresses below flat"
