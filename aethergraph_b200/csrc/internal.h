@@ -154,6 +154,7 @@ cudaError_t launch_encode(const float *src, void *dst, uint64_t count, int dtype
 cudaError_t launch_encode_i8(const float *src, uint64_t rows, uint64_t dim, int8_t *codes, float *scales, uint32_t *bad_dev,
                              cudaStream_t st);
 int gather_grid_blocks(uint64_t n, uint32_t row_bytes);
+int32_t sampler_set_yielding_wait(ag_sampler *s, bool on);  // poll + yield instead of spinning in ag_sample_group_wait
 
 // Device-side validation of a CSR: offsets monotone, offsets[n] == e, dst < n.
 // Writes a non-zero code to *flag_dev on failure.

@@ -30,6 +30,14 @@
 using namespace ag;
 
 namespace {
+// AG_LOADER_SPIN_WAIT=1 keeps the runtime's spinning waits (A/B measurements).
+bool yielding_waits() {
+    static const bool on = [] { const char *v = getenv("AG_LOADER_SPIN_WAIT"); return !(v && v[0] == '1'); }();
+    return on;
+}
+}  // namespace
+
+namespace {
 
 struct PoolSet {
     void *base = nullptr;              // one cudaMalloc: every array but x
@@ -427,6 +435,7 @@ extern "C" int32_t ag_loader_create(const ag_graph *g, const ag_features *f, con
         if (st != AG_OK) break;
         l->samplers.push_back(s);
         if (profiling) st = ag_sampler_set_profiling(s, 1);
+        if (st == AG_OK && yielding_waits()) st = sampler_set_yielding_wait(s, true);
         cudaStream_t stream = nullptr;
         // Sampling chains run at the highest priority; each handle's gather runs on
         // its own lowest-priority stream, so chains of other workers cut in.
