@@ -489,6 +489,13 @@ def run_device(args, w):
     if sharded_only and main_layout == "replicated":
         main_layout = "sharded"
 
+    def memlog(where: str):
+        """AG_BENCH_MEMLOG=1: free device memory at the stages of the run, on stderr."""
+        if os.environ.get("AG_BENCH_MEMLOG") == "1":
+            free, total = torch.cuda.mem_get_info(dev)
+            print(f"[rank {rank}] {where}: {free / 1e9:.1f} GB free of {total / 1e9:.1f}, torch holds "
+                  f"{torch.cuda.memory_reserved(dev) / 1e9:.1f} GB", file=sys.stderr, flush=True)
+
     def barrier():
         torch.cuda.synchronize()
         if world > 1:
@@ -577,6 +584,7 @@ def run_device(args, w):
         if args.hot_cache_gb > 0:
             feats.cache_hot_rows(g, int(args.hot_cache_gb * (1 << 30)))
     torch.cuda.synchronize()
+    memlog("after set-up")
     t_setup = time.time() - t_setup
     cfg = ag.SamplingConfig(num_neighbors=w["fanout"], seed=SAMPLER_SEED, weighted=w["weighted"])
     per_step, bs = per_step_of(w), w["batch"]
@@ -676,14 +684,16 @@ def run_device(args, w):
                              "rows_per_launch": int(ids.shape[0]), "launches": reps,
                              "note": "same kernel and ids, one launch at a time on an otherwise idle GPU; "
                                      "working set per launch exceeds L2"}
-        del ids, x_alone
+        del ids, x_alone, holder
         barrier()
     leg.close()
     del leg
+    memlog("after the resident leg")
     sharded_main = None
     if main_layout != "replicated" and world > 1:
         sharded_main = sharded_record(feats, main_layout, None)
         barrier()
+        memlog("after the sharded legs")
 
     # ---- e2e: public Python API, host seeds in, counts back -----------------
     e2e_med = host_med = None
