@@ -17,6 +17,7 @@
 // over the rows, so the row count may live on the device (the sampler's node
 // count) without a host round trip.
 #include <algorithm>
+#include <mutex>
 
 #include <cub/device/device_radix_sort.cuh>
 
@@ -441,6 +442,146 @@ cudaError_t launch_vec(const GatherArgs &a, const GatherArgs *group, uint32_t ro
     return cudaGetLastError();
 }
 
+// Staged gather: the rows of a set travel global -> shared memory as bulk asynchronous
+// copies (cp.async.bulk, one per row, issued by one warp, completion counted in bytes
+// on an mbarrier), and the block's warps convert and store a set that has landed while
+// the copies of the next sets are in flight.  The bytes in flight are held by shared
+// memory instead of registers: a block is 128 threads and ~5 K registers for up to
+// 48 KiB in flight, so the latency-bound sampling kernels of the other chains find
+// room on the SM beside it — the register version needs 12 K registers per 16 KiB.
+// Source and destination of every copy are 16-byte aligned and the size is a multiple
+// of 16 (row_bytes % 16 == 0, aligned payload; the shared rows are packed at row_bytes).
+constexpr int kBulkThreads = 128;
+constexpr int kBulkRows = 32;     // rows per set: one copy per lane of the issuing warp
+constexpr int kBulkStages = 4;    // sets in shared memory (three in flight while one is converted)
+constexpr long long kBulkWaitCycles = 2000000000ll;  // about a second of SM clock: then the kernel gives up on a set
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// Polls the barrier's phase; false when it has not completed within kBulkWaitCycles.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    const long long t0 = clock64();
+    for (uint32_t i = 0;; ++i) {
+        uint32_t done;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+        if ((i & 63u) == 63u) {
+            if (clock64() - t0 > kBulkWaitCycles) return false;
+            __nanosleep(32);
+        }
+    }
+}
+
+template <int DTYPE>
+__global__ void __launch_bounds__(kBulkThreads)
+k_gather_bulk(GatherArgs a, const GatherArgs *__restrict__ group, uint64_t first) {
+    extern __shared__ __align__(128) uint8_t s_rows[];           // kBulkStages sets of kBulkRows rows
+    __shared__ __align__(8) unsigned long long s_bar[kBulkStages];
+    __shared__ uint32_t s_ok[kBulkStages];                        // bit r: row r of the set was copied
+    if (group) a = group[blockIdx.y];
+    if (!a.payload) return;
+    const uint64_t n = a.n_dev ? min((uint64_t)*a.n_dev, a.n) : a.n;
+    if (a.ids_off) a.ids = (const uint32_t *)a.ids + *a.ids_off;
+    const uint32_t row_bytes = a.row_bytes;
+    const uint32_t set_bytes = (uint32_t)kBulkRows * row_bytes;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int st = 0; st < kBulkStages; ++st)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(smem_u32(&s_bar[st])));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const uint64_t pol = l2_evict_first_policy();
+    const uint64_t sets = n > first ? (n - first + kBulkRows - 1) / kBulkRows : 0;
+    // this block's sets: blockIdx.x, blockIdx.x + gridDim.x, ...
+    const uint64_t mine = sets > blockIdx.x ? (sets - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+
+    // warp 0 issues the copies of this block's k-th set into stage k % kBulkStages
+    auto issue = [&](uint64_t k) {
+        const int st = (int)(k % kBulkStages);
+        const uint64_t r = first + (blockIdx.x + k * gridDim.x) * kBulkRows + lane;
+        bool ok = false;
+        const uint8_t *src = nullptr;
+        if (r < n) {
+            const uint64_t id = load_id(a.ids, a.ids64, r);
+            const uint64_t local = id - a.row_begin;
+            if (id >= a.row_begin && local < a.rows) { ok = true; src = a.payload + local * row_bytes; }
+            else atomicOr(a.err, kErrBadId);
+        }
+        const uint32_t okmask = __ballot_sync(0xffffffffu, ok);
+        const uint32_t bar = smem_u32(&s_bar[st]);
+        if (lane == 0) {  // the one arrival of the phase, with the bytes the copies below will deliver
+            s_ok[st] = okmask;
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;"
+                         :: "r"(bar), "r"((uint32_t)__popc(okmask) * row_bytes) : "memory");
+        }
+        __syncwarp();
+        if (ok) {
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+                         :: "r"(smem_u32(s_rows + (size_t)st * set_bytes + (size_t)lane * row_bytes)), "l"(src), "r"(row_bytes),
+                            "r"(bar), "l"(pol) : "memory");
+        }
+    };
+
+    if (warp == 0)
+        for (uint64_t k = 0; k < mine && k < (uint64_t)(kBulkStages - 1); ++k) issue(k);
+    const uint32_t vecs = row_bytes >> 4;
+    const uint32_t out_per_vec = (DTYPE == AG_F32) ? 4u : 8u;
+    constexpr int kWarps = kBulkThreads / 32;
+    bool failed = false;
+    for (uint64_t k = 0; k < mine; ++k) {
+        const int st = (int)(k % kBulkStages);
+        // the stage of set k + kBulkStages - 1 held set k - 1: every warp finished reading it before the barrier below
+        if (warp == 0 && k + kBulkStages - 1 < mine) issue(k + kBulkStages - 1);
+        // A set that never arrives is reported and skipped; every thread still reaches the
+        // block barrier of every set, and the polls are bounded, so the kernel always ends.
+        if (!failed && !mbar_wait(smem_u32(&s_bar[st]), (uint32_t)((k / kBulkStages) & 1))) {
+            failed = true;
+            atomicOr(a.err, kErrSpinTimeout);
+        }
+        if (!failed) {
+            const uint32_t okmask = s_ok[st];
+            const uint64_t r0 = first + (blockIdx.x + k * gridDim.x) * kBulkRows;
+            const uint8_t *set = s_rows + (size_t)st * set_bytes;
+            for (int rr = warp; rr < kBulkRows; rr += kWarps) {
+                const uint64_t r = r0 + rr;
+                if (r >= n) break;
+                float *dst = a.out + r * a.dim;
+                const bool ok = (okmask >> rr) & 1u;
+                for (uint32_t v = lane; v < vecs; v += 32) {
+                    uint4 val = make_uint4(0, 0, 0, 0);  // a row outside the store decodes to zeros
+                    if (ok) val = *(const uint4 *)(set + (size_t)rr * row_bytes + ((size_t)v << 4));
+                    store_decoded<DTYPE>(dst + (uint64_t)v * out_per_vec, val);
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
+template <int DTYPE>
+cudaError_t launch_bulk(const GatherArgs &a, const GatherArgs *group, uint32_t row_bytes, uint64_t rows_per_batch,
+                        uint32_t n_batches, cudaStream_t st, uint64_t first = 0) {
+    const size_t smem = (size_t)kBulkStages * kBulkRows * row_bytes;
+    // per device, so set on every launch (cheap next to the launch itself)
+    const cudaError_t ae = cudaFuncSetAttribute(k_gather_bulk<DTYPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (ae != cudaSuccess) return ae;
+    // a block walks many sets, so that its pipeline fills once per few hundred rows
+    static const uint64_t per_block = [] { const char *v = getenv("AG_BULK_SETS"); return v ? (uint64_t)std::max(1, atoi(v)) : 16ull; }();
+    const uint64_t sets = std::max<uint64_t>(1, (rows_per_batch + kBulkRows - 1) / kBulkRows);
+    const uint64_t cap = std::max<uint64_t>(1, ((uint64_t)kSMs * 32 + n_batches - 1) / n_batches);
+    const dim3 grid((unsigned)std::max<uint64_t>(1, std::min<uint64_t>((sets + per_block - 1) / per_block, cap)), n_batches);
+    k_gather_bulk<DTYPE><<<grid, kBulkThreads, smem, st>>>(a, group, first);
+    return cudaGetLastError();
+}
+
+// AG_GATHER_BULK=1: the replicated gather goes through shared memory (A/B measurements).
+bool bulk_gather_enabled(uint32_t row_bytes) {
+    static const bool on = [] { const char *v = getenv("AG_GATHER_BULK"); return v && v[0] == '1'; }();
+    return on && row_bytes >= 64 && (size_t)kBulkStages * kBulkRows * row_bytes <= 200 * 1024;
+}
+
 // f32 -> stored dtype, used to build a store from f32 rows on the device.
 // bf16: round to nearest even on the dropped 16 bits, NaN -> (bits >> 16) | 0x40
 // (reference: features/store.rs:1094-1104).  f16: IEEE RNE (__float2half_rn),
@@ -761,6 +902,13 @@ cudaError_t launch_gather_group(const GatherArgs *group_dev, uint32_t n_batches,
         const int cap = std::max(1, (kSMs * 64 + (int)n_batches - 1) / (int)n_batches);
         per = std::min(per, cap);
         const dim3 grid(per, n_batches);
+        if (!sharded && dtype != AG_I8 && bulk_gather_enabled(row_bytes)) {
+            switch (dtype) {
+                case AG_F32: return launch_bulk<AG_F32>(none, group_dev, row_bytes, n_bound, n_batches, st);
+                case AG_F16: return launch_bulk<AG_F16>(none, group_dev, row_bytes, n_bound, n_batches, st);
+                default: return launch_bulk<AG_BF16>(none, group_dev, row_bytes, n_bound, n_batches, st);
+            }
+        }
         switch (dtype) {
             case AG_I8: return launch_i8(none, group_dev, row_bytes, grid, st);
             case AG_F32: return launch_vec<AG_F32>(none, group_dev, row_bytes, grid, sharded, st);

@@ -1,4 +1,6 @@
 """GPU parity: the gather / upcast kernel against the CPU oracle, bit for bit."""
+import os
+
 import numpy as np
 import pytest
 
@@ -99,3 +101,50 @@ def test_sampler_gathers_x_for_nodes(ag, ago):
         payload = ago.encode(feats, dtype)
         want = ago.gather(payload, n, 128, dtype, sg.nodes)
         assert np.array_equal(_bits(sg.x.cpu().numpy()), _bits(want)), dtype
+
+
+_BULK_WORKER = r"""
+import os, sys
+import numpy as np
+sys.path.insert(0, os.environ["AG_ROOT"]); sys.path.insert(0, os.path.join(os.environ["AG_ROOT"], "tests"))
+import aethergraph_b200 as ag
+from aethergraph_b200 import synth
+from oracle import ago
+from helpers import rmat_csr
+n, off, dst, _ = rmat_csr(13, 10, seed=5)
+g = ag.Graph.from_csr(off, dst)
+ok = True
+for dtype, dim in (("bf16", 256), ("f16", 64), ("f32", 24), ("bf16", 8)):
+    feats = synth.features(n, dim, dtype, 7)
+    payload = ago.synth_features(n, dim, dtype, 7)
+    rng = np.random.default_rng(1)
+    batches = [rng.integers(0, n, s).astype(np.uint32) for s in (300, 1, 0, 700, 31, 33, 64)] * 3
+    s = ago.Sampler(off, dst, [10, 5], seed=3)
+    with ag.NeighborLoader(g, ag.SamplingConfig(num_neighbors=[10, 5], seed=3), prefetch_depth=8, sampler_threads=2,
+                           features=feats, group=8) as ld:
+        for i, b in enumerate(batches):
+            ld.submit(i, b)
+        for i, b in enumerate(batches):
+            _, sg, x = ld.next_batch()
+            s.reseed(ago.batch_seed(3, i))
+            w = s.sample(b)
+            ok = ok and np.array_equal(sg.raw_u32()["nodes"], w["nodes"])
+            ok = ok and np.array_equal(x.cpu().numpy().view(np.uint32), ago.gather(payload, n, dim, dtype, w["nodes"]).view(np.uint32))
+    feats.check()
+print("BULK ok=%s" % ok)
+sys.exit(0 if ok else 1)
+"""
+
+
+def test_staged_bulk_copy_gather_gives_the_same_rows(tmp_path):
+    """AG_GATHER_BULK=1 sends the chains' gathers through shared memory (cp.async.bulk + mbarrier):
+    same rows, bit for bit, at row sizes from 16 bytes to 512, ragged and empty batches."""
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = tmp_path / "bulk_worker.py"
+    script.write_text(_BULK_WORKER)
+    r = subprocess.run([sys.executable, str(script)], env=dict(os.environ, AG_ROOT=root, AG_GATHER_BULK="1"),
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "BULK ok=True" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
