@@ -55,22 +55,36 @@ class PrefetchStats:
 
 class _Lease:
     """Holds one pooled batch; gives it back to the loader when nothing refers to it
-    any more.  The release records the consumer's current stream, so kernels
-    already queued on it finish before the memory is written again."""
+    any more, or when `release()` is called.  The release records a stream — the one
+    given to `record_stream` / `release`, else torch's current stream at that moment —
+    so kernels already queued on it finish before the memory is written again."""
 
-    __slots__ = ("loader", "batch")
+    __slots__ = ("loader", "batch", "stream", "released")
 
     def __init__(self, loader: "NeighborLoader", batch: _lib.Batch):
-        self.loader, self.batch = loader, batch
+        self.loader, self.batch, self.stream, self.released = loader, batch, None, False
 
-    def __del__(self):
+    def release(self, stream=None) -> None:
+        if self.released:
+            return
         ld = self.loader
         if ld is None or not ld._h:
             return
+        st = stream if stream is not None else self.stream
+        raw = _raw_stream(st) if st is not None else _raw_current_stream(ld._dev_index)
+        self.released = True
+        ld._release(ld._h, C.byref(self.batch), raw)
+
+    def __del__(self):
         try:
-            ld._release(ld._h, C.byref(self.batch), _raw_current_stream(ld._dev_index))
+            self.release()
         except Exception:
             pass
+
+
+def _raw_stream(stream) -> int:
+    """cudaStream_t of a torch.cuda.Stream, or the integer itself."""
+    return int(getattr(stream, "cuda_stream", stream))
 
 
 def _raw_current_stream(device_index: int) -> int:

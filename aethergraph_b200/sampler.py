@@ -233,6 +233,24 @@ class SampledSubgraph:
         out.draws, out._seeds, out._cache = self.draws, self._seeds, None
         return out
 
+    # pooled batches (a loader's): which stream still reads them, and giving them back early
+    def record_stream(self, stream) -> None:
+        """A batch delivered by a loader lives in pooled memory that the loader writes again
+        once the batch is dropped; by default it waits for the work queued on torch's
+        CURRENT stream at that moment.  A consumer that reads the tensors on another stream
+        names it here (a `torch.cuda.Stream` or a raw `cudaStream_t`)."""
+        owner = self._b.owner
+        if hasattr(owner, "stream"):
+            owner.stream = stream
+
+    def release(self, stream=None) -> None:
+        """Give a loader's batch back now.  The loader reuses the memory after the work
+        already queued on `stream` (default: the recorded stream, else the current one);
+        the tensors of this batch must not be used by work queued later."""
+        owner = self._b.owner
+        if hasattr(owner, "release"):
+            owner.release(stream)
+
     # counts
     @property
     def num_nodes(self) -> int:

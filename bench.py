@@ -50,7 +50,10 @@ WORKLOADS = {
     "c2": dict(nodes=100_000_000, edges=2_000_000_000, dim=256, dtype="bf16", batch=1024, fanout=[25, 10],
                weighted=False, label="C2: R-MAT 100M vertices / 2B edges, 256-dim bf16, batch 1024, fanout [25,10]"),
     # 1M-vertex R-MAT, 16M edges, 128-dim f32, batch 128, fanout [15, 10]
+    # small batches are bound by launch latency and host work per chain: long chains, two workers
+    # (measured: 3 x 32 -> 0.78, 3 x 128 -> 1.46, 2 x 128 -> 2.16, 4 x 128 -> 0.93 G edges/s)
     "c1": dict(nodes=1 << 20, edges=16 << 20, dim=128, dtype="f32", batch=128, fanout=[15, 10], weighted=False,
+               group=128, threads=2, depth=64,
                label="C1: R-MAT 1M vertices / 16M edges, 128-dim f32, batch 128, fanout [15,10]"),
     # 10M-vertex weighted R-MAT, 200M edges, 128-dim f16, batch 512, fanout [15, 10, 5]
     "c3": dict(nodes=10_000_000, edges=200_000_000, dim=128, dtype="f16", batch=512, fanout=[15, 10, 5],

@@ -231,3 +231,42 @@ def test_pooled_x_is_reserved_from_observed_counts_and_outgrown_batches_are_gath
                 assert np.array_equal(x.cpu().numpy().view(np.uint32), xw.view(np.uint32)), seq
                 seq += 1
                 del sg, x   # hand the pooled buffers back
+
+
+def test_batches_given_back_early_or_read_on_a_side_stream(ag, ago, world):
+    """`release(stream)` hands a pooled batch back before the object dies (a second release and
+    the later destructor do nothing), `record_stream` names the stream that still reads it:
+    the loader keeps delivering exact batches out of the few buffers it has."""
+    import torch
+
+    n, g, feats, off, dst, payload = world
+    cfg = ag.SamplingConfig(num_neighbors=[8, 4], seed=9)
+    s = ago.Sampler(off, dst, [8, 4], seed=9)
+    rng = np.random.default_rng(11)
+    batches = [rng.integers(0, n, 200).astype(np.uint32) for _ in range(40)]
+    side = torch.cuda.Stream()
+    kept = []
+    with ag.NeighborLoader(g, cfg, prefetch_depth=2, sampler_threads=1, features=feats, group=2) as ld:
+        ld.submit_epoch(batches[:8], list(range(8)))
+        for i, b in enumerate(batches):
+            idx, sg, x = ld.next_batch()
+            if i + 8 < len(batches):
+                ld.submit(i + 8, batches[i + 8])
+            s.reseed(ago.batch_seed(9, i))
+            want = s.sample(b)
+            assert idx == i and np.array_equal(sg.raw_u32()["nodes"], want["nodes"])
+            if i % 3 == 0:
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    total = x.sum()                       # read on the side stream ...
+                sg.record_stream(side)                    # ... which the loader must wait for
+                xw = ago.gather(payload, n, 32, "f16", want["nodes"])
+                side.synchronize()
+                assert np.isclose(float(total), float(xw.astype(np.float64).sum()), rtol=1e-3)
+            elif i % 3 == 1:
+                assert np.array_equal(x.cpu().numpy().view(np.uint32),
+                                      ago.gather(payload, n, 32, "f16", want["nodes"]).view(np.uint32))
+                sg.release(torch.cuda.current_stream())
+                sg.release()                              # harmless
+                kept.append(sg)                           # the destructor must not give it back twice
+            del x
