@@ -313,7 +313,11 @@ void worker_main(ag_loader *l, uint32_t idx) {
             // Results channel holds `depth` batches: wait for room (prefetch.rs:1135-1143),
             // except for the batch the consumer is waiting on — holding it back could
             // stall an ordered loader whose later batches filled the channel first.
-            l->cv_room.wait(lk, [&] { return l->stop || l->in_ready < l->depth || w.seq == l->next_deliver; });
+            auto room = [&] { return l->stop || l->in_ready < l->depth || w.seq == l->next_deliver; };
+            if (!room()) {
+                l->cv_done.notify_all();  // the consumer drains what is ready while this worker waits for room
+                l->cv_room.wait(lk, room);
+            }
             if (l->stop) {
                 lk.unlock();
                 for (uint32_t r = b; r < nb; ++r) drop_work(l, ws[r]);
@@ -325,8 +329,9 @@ void worker_main(ag_loader *l, uint32_t idx) {
             l->ready.emplace(w.seq, std::move(d));
             l->arrival.push_back(w.seq);
             l->in_ready++;
-            l->cv_done.notify_all();
         }
+        // one wake-up per chain, not per batch: the consumer takes the batches in bulk
+        l->cv_done.notify_all();
     }
 }
 
