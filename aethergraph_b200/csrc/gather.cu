@@ -899,7 +899,9 @@ cudaError_t launch_gather_group(const GatherArgs *group_dev, uint32_t n_batches,
         // n_bound is the caller's estimate of the rows per batch (the true count is
         // read on the device); a batch with more rows strides over extra chunks.
         int per = gather_grid_blocks(n_bound, row_bytes);
-        const int cap = std::max(1, (kSMs * 64 + (int)n_batches - 1) / (int)n_batches);
+        // AG_GATHER_BLOCKS_PER_SM: grid cap of a chain's gather in blocks per SM (A/B measurements)
+        static const int per_sm = [] { const char *v = getenv("AG_GATHER_BLOCKS_PER_SM"); return v ? std::max(1, atoi(v)) : 64; }();
+        const int cap = std::max(1, (kSMs * per_sm + (int)n_batches - 1) / (int)n_batches);
         per = std::min(per, cap);
         const dim3 grid(per, n_batches);
         if (!sharded && dtype != AG_I8 && bulk_gather_enabled(row_bytes)) {

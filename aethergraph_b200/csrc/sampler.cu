@@ -1097,7 +1097,9 @@ extern "C" int32_t ag_sampler_create_group(const ag_graph *g, const ag_sampling_
         }
         int lo = 0, hi = 0;
         cudaDeviceGetStreamPriorityRange(&lo, &hi);  // lo = least urgent
-        if (cudaStreamCreateWithPriority(&s->gstream, cudaStreamNonBlocking, lo) != cudaSuccess ||
+        // AG_GATHER_PRIORITY=high: the gather streams as urgent as the sampling streams (A/B measurements)
+        static const bool gather_high = [] { const char *v = getenv("AG_GATHER_PRIORITY"); return v && v[0] == 'h'; }();
+        if (cudaStreamCreateWithPriority(&s->gstream, cudaStreamNonBlocking, gather_high ? hi : lo) != cudaSuccess ||
             cudaStreamCreateWithPriority(&s->rstream, cudaStreamNonBlocking, (lo + hi) / 2) != cudaSuccess ||
             cudaEventCreateWithFlags(&s->remote_done, cudaEventDisableTiming) != cudaSuccess) {
             st = fail(AG_ERR_CUDA, "cudaStreamCreateWithPriority failed: %s", cudaGetErrorString(cudaGetLastError()));
