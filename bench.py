@@ -597,8 +597,10 @@ def run_device(args, w):
     seeds_host = [synth.seed_batch(w["nodes"], bs, SEEDS_SEED, b) for b in gidx]
     seeds_dev = torch.from_numpy(np.concatenate(seeds_host).view(np.int32)).to(dev)
 
-    threads = args.threads or int(w.get("threads", 3))
-    group = args.group or int(w.get("group", 32))
+    # two workers x chains of 64: the same resident value as three x 32 and a better e2e, because
+    # one more host thread per rank is left to the consumer (measured at one and at eight GPUs)
+    threads = args.threads or int(w.get("threads", 2))
+    group = args.group or int(w.get("group", 64))
     depth = args.depth or int(w.get("depth", max(8, group // 2)))
     # sharded legs: remote rows have a longer way, so more chains are kept in flight
     threads_sh = args.threads or int(w.get("threads_sharded", w.get("threads", 4)))
