@@ -7,7 +7,7 @@ the reference's Python sampler / feature-store / loader surface.
 """
 from ._lib import GraphLoadError, SamplingError
 from .features import FeatureStore, save_features
-from .graph import CsrGraph, Graph
+from .graph import CsrGraph, Graph, partition_aligned_batches
 from .loader import NeighborLoader, PrefetchStats
 from .hetero import (HeteroCsrGraph, HeteroNeighborLoader, HeteroNeighborSampler, HeteroSampledSubgraph,
                      HeteroSamplingConfig)
@@ -19,5 +19,6 @@ __all__ = [
     "CsrGraph", "FeatureStore", "Graph", "GraphLoadError", "HeteroCsrGraph", "HeteroNeighborLoader",
     "HeteroNeighborSampler", "HeteroSampledSubgraph", "HeteroSamplingConfig", "NeighborLoader", "NeighborSampler",
     "ParallelBatchSampler", "PrefetchStats",
-    "SampledSubgraph", "Sampler", "SamplingConfig", "SamplingError", "__version__", "save_features",
+    "SampledSubgraph", "Sampler", "SamplingConfig", "SamplingError", "__version__", "partition_aligned_batches",
+    "save_features",
 ]

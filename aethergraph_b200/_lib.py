@@ -115,6 +115,8 @@ SIGNATURES = {
     "ag_graph_from_edges": (C.c_int32, [C.c_uint64, _P, _P, _P, C.c_uint64, C.c_int32, _PP]),
     "ag_graph_save": (C.c_int32, [_P, C.c_char_p]),
     "ag_graph_save_compressed": (C.c_int32, [_P, C.c_char_p]),
+    "ag_graph_rabbit_order": (C.c_int32, [_P, C.c_void_p, C.c_void_p]),
+    "ag_graph_permute": (C.c_int32, [_P, C.c_void_p, C.c_uint64, _PP]),
     "ag_graph_info": (C.c_int32, [_P, _U64P, _U64P, _I32P, _I32P]),
     "ag_graph_device_ptrs": (C.c_int32, [_P, _PP, _PP, _PP]),
     "ag_graph_degrees": (C.c_int32, [_P, _P, C.c_uint64, _P]),

@@ -17,7 +17,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libaethergpu.so")
 SOURCES = ["api.cu", "gather.cu", "sampler.cu", "synth.cu", "loader.cu", "noalloc.cu", "hetero.cu", "hop.cu", "shard.cu",
-           "hetero_loader.cu", "rewrite.cu", "hot.cu", "peer_block.cu"]
+           "hetero_loader.cu", "rewrite.cu", "hot.cu", "peer_block.cu", "reorder.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-Wall,-Wno-unused-function", "--expt-relaxed-constexpr",

@@ -14,7 +14,7 @@ import numpy as np
 from . import _lib
 from ._ids import to_uint32_ids
 
-__all__ = ["CsrGraph", "Graph"]
+__all__ = ["CsrGraph", "Graph", "partition_aligned_batches"]
 
 
 def _current_device() -> int:
@@ -129,6 +129,35 @@ class CsrGraph:
                                                 C.byref(out)))
         return CsrGraph(out.value)
 
+    # -- locality reordering (python/aethergraph/_core.pyi:121-130) ----------
+    def reorder_rabbit_with_partitions(self) -> tuple[np.ndarray, np.ndarray]:
+        """`(perm, partitions)` of Rabbit Order community detection in one pass: `perm[new_id] =
+        old_id` keeps every community of the dendrogram contiguous, `partitions[v]` is the dense
+        id of v's top-level community.  Deterministic; the merge itself is sequential and runs on
+        the host (crates/aethergraph-core/src/graph/reorder.rs:142-262)."""
+        perm = np.empty(self._n, dtype=np.uint32)
+        parts = np.empty(self._n, dtype=np.uint32)
+        _lib.check(_lib.lib().ag_graph_rabbit_order(self._h, perm.ctypes.data if self._n else None,
+                                                    parts.ctypes.data if self._n else None))
+        return perm, parts
+
+    def reorder_rabbit(self) -> np.ndarray:
+        return self.reorder_rabbit_with_partitions()[0]
+
+    def rabbit_partitions(self) -> np.ndarray:
+        return self.reorder_rabbit_with_partitions()[1]
+
+    def permute(self, perm) -> "CsrGraph":
+        """The graph relabelled by `perm[new_id] = old_id`, built on the GPU; rows keep their
+        edge order and weights (reorder.rs:297-383)."""
+        p = np.ascontiguousarray(perm)
+        if p.ndim != 1 or p.dtype.kind not in "iu" or (p.size and (p.min() < 0 or p.max() > 0xFFFFFFFF)):
+            raise ValueError("perm must be a 1-D array of node ids")
+        p = p.astype(np.uint32, copy=False)
+        out = C.c_void_p()
+        _lib.check(_lib.lib().ag_graph_permute(self._h, p.ctypes.data if p.size else None, p.size, C.byref(out)))
+        return CsrGraph(out.value)
+
     def save(self, path, *, compressed: bool = False) -> None:
         """Write the graph: the flat AETH v1 file, or with `compressed=True` the succinct-coded
         version 2 (Elias-Fano offsets, StreamVByte edge deltas; python/aethergraph/_core.pyi:95-99).
@@ -234,3 +263,34 @@ class CsrGraph:
 
 
 Graph = CsrGraph
+
+
+def partition_aligned_batches(partitions, seeds, batch_size: int, shuffle_partitions: bool = False,
+                              seed: int = 0) -> list[np.ndarray]:
+    """Seed batches that follow the Rabbit partitions: seeds of one community land in the
+    same batch, so their sampled neighbourhoods (and feature rows, on a reordered graph)
+    overlap.  Seeds are grouped by partition, keeping their order inside one; the partitions
+    are visited in id order, or shuffled by the reference's LCG Fisher-Yates; batches of
+    `batch_size` are cut from that sequence (crates/aethergraph-core/src/graph/reorder.rs:385-463)."""
+    if batch_size < 1:
+        raise ValueError("batch_size must be >= 1")
+    parts = np.ascontiguousarray(partitions, dtype=np.uint32)
+    s = np.ascontiguousarray(seeds).astype(np.int64, copy=False)
+    if s.size and (s.min() < 0 or s.max() >= parts.size):
+        bad = int(s[(s < 0) | (s >= parts.size)][0])
+        raise ValueError(f"seed {bad} is out of range for partitions of length {parts.size}")
+    keyed = np.sort((parts[s].astype(np.uint64) << np.uint64(32)) | np.arange(s.size, dtype=np.uint64))
+    run_id = keyed >> np.uint64(32)
+    starts = np.flatnonzero(np.concatenate([[True], run_id[1:] != run_id[:-1]])) if s.size else np.zeros(0, np.int64)
+    ends = np.concatenate([starts[1:], [s.size]]) if s.size else np.zeros(0, np.int64)
+    runs = list(zip(starts.tolist(), ends.tolist()))
+    if shuffle_partitions:
+        mask, mul = (1 << 64) - 1, 0x517CC1B727220A95
+        rng = (seed * mul + 1) & mask
+        for i in range(len(runs) - 1, 0, -1):
+            rng = (rng * mul + 1) & mask
+            j = (rng >> 33) % (i + 1)
+            runs[i], runs[j] = runs[j], runs[i]
+    order = np.concatenate([keyed[a:b] for a, b in runs]) if runs else np.zeros(0, np.uint64)
+    picked = s[(order & np.uint64(0xFFFFFFFF)).astype(np.int64)].astype(np.uint32)
+    return [picked[i:i + batch_size] for i in range(0, picked.size, batch_size)]

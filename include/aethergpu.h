@@ -97,6 +97,21 @@ int32_t ag_graph_save(const ag_graph *g, const char *path);
  * ag_graph_load recognises the version, decodes both sections on the GPU and always
  * verifies the checksum and the whole CSR (compressed_graph.rs:99-175). */
 int32_t ag_graph_save_compressed(const ag_graph *g, const char *path);
+/* Locality reordering (crates/aethergraph-core/src/graph/reorder.rs:142-383;
+ * Graph.reorder_rabbit / rabbit_partitions / permute, python/aethergraph/_core.pyi:121-130).
+ * ag_graph_rabbit_order: Rabbit Order community detection — vertices in ascending
+ * (undirected degree, id) order, each merged into the neighbouring community of largest
+ * positive modularity gain (exact integers, ties to the smaller id) — sequential and
+ * deterministic as in the reference, run on the host over a copy of the CSR.
+ * perm_out[new_id] = old_id (pre-order walk of the dendrogram) and partitions_out[v] =
+ * dense id of v's top-level community, numbered by first vertex; either may be NULL;
+ * both are host arrays of num_nodes entries.
+ * ag_graph_permute: the relabelled graph, built on the GPU; row new_id holds the edges
+ * of row perm[new_id] in their order, endpoints relabelled, weights carried along.
+ * AG_ERR_VALUE for a permutation of the wrong length, with an out-of-range or a
+ * duplicate entry. */
+int32_t ag_graph_rabbit_order(const ag_graph *g, uint32_t *perm_out, uint32_t *partitions_out);
+int32_t ag_graph_permute(const ag_graph *g, const uint32_t *perm, uint64_t perm_len, ag_graph **out);
 int32_t ag_graph_info(const ag_graph *g, uint64_t *num_nodes, uint64_t *num_edges,
                       int32_t *has_weights, int32_t *device);
 int32_t ag_graph_device_ptrs(const ag_graph *g, const uint64_t **offsets_dev,

@@ -722,3 +722,97 @@ def read_compressed_graph(raw: bytes):
     off = ef_decode(ef_len, universe, low_bits, low, high)
     assert off.size == 0 or int(off[-1]) == universe
     return n, off, svb_decode(m, first, control, data), w
+
+
+# ------------------------------------------------------- locality reordering --
+# Rabbit Order (crates/aethergraph-core/src/graph/reorder.rs:142-262) and the walks of
+# its dendrogram (:46-105), restated in plain Python for small graphs; permute (:297-383)
+# in numpy.  Python integers are exact, like the reference's i128 gains.
+def rabbit_order(offsets, dst):
+    """-> (perm, partitions): perm[new_id] = old_id, partitions[v] = dense community id."""
+    off = [int(x) for x in np.asarray(offsets)]
+    d = [int(x) for x in np.asarray(dst)]
+    n = len(off) - 1
+    parent, first_child, next_sibling = list(range(n)), [None] * n, [None] * n
+
+    def root(v):
+        r = v
+        while parent[r] != r:
+            r = parent[r]
+        while parent[v] != r:
+            parent[v], v = r, parent[v]
+        return r
+
+    if n > 1 and d:
+        ins = [[] for _ in range(n)]                       # sources ascending per destination
+        for u in range(n):
+            for e in range(off[u], off[u + 1]):
+                ins[d[e]].append(u)
+        degree = [sum(1 for e in range(off[v], off[v + 1]) if d[e] != v) + sum(1 for s in ins[v] if s != v)
+                  for v in range(n)]
+        two_m = sum(degree)
+        if two_m:
+            carried, visited = [None] * n, [False] * n
+            for u in sorted(range(n), key=lambda v: (degree[v], v)):
+                weight_to = {}
+
+                def add(c, w):
+                    c = root(c)
+                    if c != u:
+                        weight_to[c] = weight_to.get(c, 0) + w
+
+                for e in range(off[u], off[u + 1]):
+                    add(d[e], 1)
+                for s in ins[u]:
+                    add(s, 1)
+                child = first_child[u]
+                while child is not None:
+                    if carried[child] is not None:
+                        for c, w in carried[child]:
+                            add(c, w)
+                        carried[child] = None
+                    child = next_sibling[child]
+                best = None
+                for c, w in weight_to.items():
+                    gain = two_m * w - degree[u] * degree[c]
+                    if (gain > 0) if best is None else (gain > best[0] or (gain == best[0] and c < best[1])):
+                        best = (gain, c)
+                if best is not None:
+                    c = best[1]
+                    parent[u] = c
+                    degree[c] += degree[u]
+                    next_sibling[u], first_child[c] = first_child[c], u
+                    if not visited[c]:
+                        carried[u] = list(weight_to.items())
+                visited[u] = True
+    perm = []
+    for r in range(n):
+        if parent[r] != r:
+            continue
+        perm.append(r)
+        stack = [first_child[r]]
+        while stack:
+            c = stack[-1]
+            if c is None:
+                stack.pop()
+                continue
+            stack[-1] = next_sibling[c]
+            perm.append(c)
+            stack.append(first_child[c])
+    ids, parts = {}, []
+    for v in range(n):
+        parts.append(ids.setdefault(root(v), len(ids)))
+    return np.array(perm, dtype=np.uint32), np.array(parts, dtype=np.uint32)
+
+
+def permute_csr(offsets, dst, weights, perm):
+    """Row new_id = row perm[new_id] of the old graph in its order, endpoints relabelled."""
+    off = np.asarray(offsets, dtype=np.uint64)
+    d = np.asarray(dst, dtype=np.uint32)
+    p = np.asarray(perm, dtype=np.int64)
+    inv = np.empty(p.size, dtype=np.uint32)
+    inv[p] = np.arange(p.size, dtype=np.uint32)
+    lens = (off[p + 1] - off[p]).astype(np.int64)
+    new_off = np.concatenate([[0], np.cumsum(lens)]).astype(np.uint64)
+    src = np.concatenate([np.arange(int(off[o]), int(off[o + 1])) for o in p]).astype(np.int64) if d.size else np.zeros(0, np.int64)
+    return new_off, inv[d[src]], (None if weights is None else np.asarray(weights, dtype=np.float32)[src])
