@@ -109,7 +109,7 @@ class NeighborLoader:
         the same stream whatever W is."""
         import torch
 
-        _check_config(graph, config)
+        _check_config(graph, config, pipelined=True)
         if prefetch_depth < 1:
             raise ValueError("prefetch_depth must be >= 1")
         if sampler_threads < 1:

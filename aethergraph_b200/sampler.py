@@ -76,8 +76,6 @@ class SamplingConfig:
         """Modes of the reference this GPU path does not implement."""
         if self.temporal_strategy is not None:
             return "temporal sampling"
-        if self.disjoint:
-            return "disjoint sampling"
         if self.cumulative:
             return "cumulative sampling"
         if self.max_degree is not None and self.weighted:
@@ -212,10 +210,11 @@ class SampledSubgraph:
     is the CSR position of the stored edge row1 -> row0.  The `*_t` accessors
     return the same data as CUDA tensors without a copy."""
 
-    __slots__ = ("_b", "_n", "_e", "_s", "_nodes_per_hop", "_edges_per_hop", "draws", "_seeds", "_cache")
+    __slots__ = ("_b", "_n", "_e", "_s", "_nodes_per_hop", "_edges_per_hop", "draws", "_seeds", "_cache", "_batch")
 
     def __init__(self, bufs: _Buffers, counts: _lib.SampleCounts, seeds: np.ndarray):
         self._b = bufs
+        self._batch = None
         self._n, self._e, self._s = counts.num_nodes, counts.num_edges, counts.num_seeds
         h = counts.num_hops
         self._nodes_per_hop = counts.nodes_per_hop[:h + 1]
@@ -231,6 +230,7 @@ class SampledSubgraph:
         out._b, out._n, out._e, out._s = bufs, self._n, num_edges, self._s
         out._nodes_per_hop, out._edges_per_hop = self._nodes_per_hop, self._edges_per_hop
         out.draws, out._seeds, out._cache = self.draws, self._seeds, None
+        out._batch = self._batch
         return out
 
     # pooled batches (a loader's): which stream still reads them, and giving them back early
@@ -356,7 +356,9 @@ class SampledSubgraph:
 
     @property
     def batch(self):
-        return None
+        """Disjoint sampling: for every node the index of the seed whose block it belongs to
+        (int64); None otherwise."""
+        return self._batch
 
     @property
     def num_sampled_nodes_per_hop(self) -> list[int]:
@@ -370,7 +372,7 @@ class SampledSubgraph:
         return {
             "nodes": self.nodes, "seeds": self.seeds, "edge_index": self.edge_index,
             "edge_index_local": self.edge_index_local, "edge_ids": self.edge_ids,
-            "seed_indices": self.seed_indices, "batch": None,
+            "seed_indices": self.seed_indices, "batch": self.batch,
             "num_sampled_nodes_per_hop": self.num_sampled_nodes_per_hop,
             "num_sampled_edges_per_hop": self.num_sampled_edges_per_hop,
         }
@@ -513,10 +515,15 @@ def _submit_group(handle: _Handle, seeds: list[np.ndarray], batch_seeds: list[in
     return _PendingGroup(handle, bufs, seeds, (cbufs, ptrs, lens, bseeds))
 
 
-def _check_config(graph: CsrGraph, config: SamplingConfig) -> None:
+def _check_config(graph: CsrGraph, config: SamplingConfig, *, pipelined: bool = False) -> None:
+    """`pipelined`: the caller runs groups of batches per launch chain (loaders, the parallel
+    batch sampler).  Disjoint sampling is sequential seed by seed in the exact mode, so only
+    the plain `NeighborSampler` offers it."""
     if not isinstance(config, SamplingConfig):
         raise TypeError("config must be a SamplingConfig")
     bad = config._unsupported()
+    if bad is None and pipelined and config.disjoint:
+        bad = "disjoint sampling in a loader (use NeighborSampler.sample; it runs one seed after the other)"
     if bad:
         raise ValueError(f"{bad} is not supported by the GPU minibatch path")
     if config.weighted and not graph.has_weights:
@@ -539,7 +546,64 @@ class NeighborSampler:
         if input_times is not None:
             raise SamplingError("temporal sampling: SamplingConfig::temporal_strategy is None")
         s = coerce_seeds(seeds, self.graph.num_nodes)
+        if self.config.disjoint:
+            return self._sample_disjoint(s)
         return _submit_group(self._handle, [s], None, self.features).results()[0]
+
+    def _sample_disjoint(self, seeds: np.ndarray) -> SampledSubgraph:
+        """Every seed sampled on its own, nothing shared between the blocks, the blocks
+        concatenated with their local indices shifted and a `batch` vector naming each node's
+        seed (crates/aethergraph-core/src/loader/sampler.rs:600-690).  The reference's RNG
+        stream runs on from one seed's tree into the next, and how many draws a tree takes
+        depends on what it sampled, so in the exact mode the seeds are inherently sequential:
+        one launch chain per seed.  Exact, and slow; `subgraph_type` applies inside each block."""
+        import torch
+
+        h = self._handle
+        blocks = [_submit_group(h, [seeds[i:i + 1]], None, self.features).results()[0] for i in range(len(seeds))]
+        n_tot, e_tot, S = sum(b._n for b in blocks), sum(b._e for b in blocks), len(seeds)
+        dim = self.features.feature_dim if self.features is not None else None
+        track = self.config.track_edge_ids
+        out = _Buffers.alloc(h.device, max(n_tot, 1), max(e_tot, 1), max(S, 1), track, dim)
+        c = out.c
+        hops = len(self.config.num_neighbors)
+        counts = _lib.SampleCounts()
+        counts.num_nodes, counts.num_edges, counts.num_seeds, counts.num_hops = n_tot, e_tot, S, hops
+        counts.nodes_per_hop[0] = S        # every block contributes its one seed node up front
+        n_at = e_at = 0
+        batch = np.empty(n_tot, dtype=np.int64)
+        for i, b in enumerate(blocks):
+            bb, n, e = b._b, b._n, b._e
+            if n:
+                out.view(c.nodes + 4 * n_at, (n,), "<i4").copy_(bb.view(bb.c.nodes, (n,), "<i4"))
+                out.view(c.n_id + 8 * n_at, (n,), "<i8").copy_(bb.view(bb.c.n_id, (n,), "<i8"))
+                if dim is not None:
+                    out.view(c.x + 4 * dim * n_at, (n, dim), "<f4").copy_(bb.view(bb.c.x, (n, dim), "<f4"))
+            if e:
+                for name in ("edge_src", "edge_dst"):
+                    out.view(getattr(c, name) + 4 * e_at, (e,), "<i4").copy_(bb.view(getattr(bb.c, name), (e,), "<i4"))
+                for name in ("src_local", "dst_local"):
+                    out.view(getattr(c, name) + 4 * e_at, (e,), "<i4").copy_(bb.view(getattr(bb.c, name), (e,), "<i4") + n_at)
+                if track:
+                    out.view(c.edge_ids + 8 * e_at, (e,), "<i8").copy_(bb.view(bb.c.edge_ids, (e,), "<i8"))
+            out.view(c.seed_locals + 4 * i, (1,), "<i4").copy_(bb.view(bb.c.seed_locals, (1,), "<i4") + n_at)
+            out.view(c.seed_index + 8 * i, (1,), "<i8").copy_(bb.view(bb.c.seed_index, (1,), "<i8") + n_at)
+            for k in range(hops):
+                counts.nodes_per_hop[k + 1] += b._nodes_per_hop[k + 1]
+                counts.edges_per_hop[k] += b._edges_per_hop[k]
+            counts.draws += b.draws
+            batch[n_at:n_at + n] = i
+            n_at += n
+            e_at += e
+        # the packed [2, E] int64 edge index of the whole batch: neighbour row, then expanded-node row
+        if e_tot:
+            ei = out.view(c.edge_index_local, (2, e_tot), "<i8")
+            ei[0].copy_(_u32_to_i64(out.view(c.dst_local, (e_tot,), "<i4")))
+            ei[1].copy_(_u32_to_i64(out.view(c.src_local, (e_tot,), "<i4")))
+        torch.cuda.current_stream(h.device).synchronize()
+        sg = SampledSubgraph(out, counts, seeds)
+        sg._batch = batch
+        return sg
 
     def __repr__(self) -> str:
         return f"NeighborSampler(num_neighbors={self.config.num_neighbors}, replace={self.config.replace})"
@@ -561,7 +625,7 @@ class ParallelBatchSampler:
                  streams: int = 2, group: int = 16):
         import torch
 
-        _check_config(graph, config)
+        _check_config(graph, config, pipelined=True)
         self.graph, self.config, self.features = graph, config, features
         self._base = config.seed if config.seed is not None else secrets.randbits(64)
         self._next = 0

@@ -816,3 +816,40 @@ def permute_csr(offsets, dst, weights, perm):
     new_off = np.concatenate([[0], np.cumsum(lens)]).astype(np.uint64)
     src = np.concatenate([np.arange(int(off[o]), int(off[o + 1])) for o in p]).astype(np.int64) if d.size else np.zeros(0, np.int64)
     return new_off, inv[d[src]], (None if weights is None else np.asarray(weights, dtype=np.float32)[src])
+
+
+def sample_disjoint(sampler: "Sampler", seeds, offsets=None, edges=None, subgraph_type: str = "directional") -> dict:
+    """Disjoint sampling (crates/aethergraph-core/src/loader/sampler.rs:600-690): one pass per
+    seed on the sampler's running stream, `subgraph_type` applied inside each block, the
+    blocks concatenated with their local indices shifted by the nodes before them."""
+    seeds = np.asarray(seeds, dtype=np.uint32)
+    keys = ("nodes", "edge_src", "edge_dst", "src_local", "dst_local")
+    parts = {k: [] for k in keys}
+    seed_locals, batch = [], []
+    nodes_per_hop = edges_per_hop = None
+    at = 0
+    for i, s in enumerate(seeds):
+        sub = sampler.sample(seeds[i:i + 1])
+        hop_nodes = np.asarray(sub["num_sampled_nodes"], dtype=np.uint64)
+        hop_edges = np.asarray(sub["num_sampled_edges"], dtype=np.uint64)
+        if subgraph_type == "bidirectional":
+            sub = mirror(sub)
+        elif subgraph_type == "induced":
+            sub = induce(offsets, edges, sub)
+        for k in ("nodes", "edge_src", "edge_dst"):
+            parts[k].append(np.asarray(sub[k], dtype=np.uint32))
+        parts["src_local"].append(np.asarray(sub["src_local"], dtype=np.uint32) + np.uint32(at))
+        parts["dst_local"].append(np.asarray(sub["dst_local"], dtype=np.uint32) + np.uint32(at))
+        seed_locals.append(int(sub["seed_locals"][0]) + at)
+        batch.extend([i] * len(sub["nodes"]))
+        if nodes_per_hop is None:
+            nodes_per_hop, edges_per_hop = np.zeros_like(hop_nodes), np.zeros_like(hop_edges)
+        nodes_per_hop[1:] += hop_nodes[1:]
+        edges_per_hop += hop_edges
+        at += len(sub["nodes"])
+    out = {k: (np.concatenate(v) if v else np.zeros(0, np.uint32)) for k, v in parts.items()}
+    if nodes_per_hop is not None:
+        nodes_per_hop[0] = len(seeds)           # every block contributes its one seed node up front
+    out.update(seed_locals=np.array(seed_locals, dtype=np.uint32), batch=np.array(batch, dtype=np.int64),
+               num_sampled_nodes=nodes_per_hop, num_sampled_edges=edges_per_hop)
+    return out

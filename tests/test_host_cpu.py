@@ -89,7 +89,7 @@ def test_sampling_config_validation():
     assert (cfg.replace, cfg.seed, cfg.weighted, cfg.track_edge_ids, cfg.subgraph_type) == (False, None, False, True,
                                                                                           "directional")
     assert cfg._unsupported() is None
-    assert ag.SamplingConfig([3], disjoint=True)._unsupported() == "disjoint sampling"
+    assert ag.SamplingConfig([3], disjoint=True)._unsupported() is None     # the plain sampler runs it seed by seed
     assert ag.SamplingConfig([3], cumulative=True)._unsupported() == "cumulative sampling"
     assert ag.SamplingConfig([3], temporal_strategy="last")._unsupported() == "temporal sampling"
     assert ag.SamplingConfig([3], subgraph_type="induced")._unsupported() is None  # rewrites run on the GPU

@@ -156,9 +156,44 @@ def test_config_errors(ag, rmat12):
         ag.SamplingConfig(num_neighbors=[3, -1])
     with pytest.raises(ValueError, match="no edge weights"):
         ag.NeighborSampler(g, ag.SamplingConfig(num_neighbors=[3], weighted=True))
-    for kw in ({"disjoint": True}, {"cumulative": True}, {"temporal_strategy": "last"}):
+    for kw in ({"cumulative": True}, {"temporal_strategy": "last"}):
         with pytest.raises(ValueError, match="not supported"):
             ag.NeighborSampler(g, ag.SamplingConfig(num_neighbors=[3], **kw))
+    # disjoint runs seed by seed in the plain sampler only
+    for make in (lambda c: ag.NeighborLoader(g, c), lambda c: ag.ParallelBatchSampler(g, c)):
+        with pytest.raises(ValueError, match="disjoint sampling in a loader"):
+            make(ag.SamplingConfig(num_neighbors=[3], disjoint=True, seed=1))
+
+
+@pytest.mark.parametrize("kw", [{}, {"replace": True}, {"weighted": True}, {"subgraph_type": "bidirectional"}])
+def test_disjoint_sampling_matches_the_oracle(ag, kw):
+    """Every seed its own block, the RNG stream running on from block to block, local indices
+    shifted per block, `batch` naming each node's seed (sampler.rs:600-690); repeated and
+    isolated seeds included."""
+    from oracle import ago
+
+    n, off, dst, w = rmat_csr(10, 8, seed=6, weighted=True)
+    g = ag.Graph.from_csr(off, dst, w)
+    feats = ag.FeatureStore.from_array(np.random.default_rng(0).standard_normal((n, 16)).astype(np.float32), "f32")
+    cfg = ag.SamplingConfig(num_neighbors=[4, 3], seed=12, disjoint=True, **kw)
+    okw = {k: v for k, v in kw.items() if k != "subgraph_type"}
+    oracle = ago.Sampler(off, dst, [4, 3], seed=12, weights=w if kw.get("weighted") else None, **okw)
+    deg = np.diff(off.astype(np.int64))
+    isolated = int(np.flatnonzero(deg == 0)[0]) if (deg == 0).any() else 0
+    seeds = np.array([5, 9, 5, isolated, 700, 1, 2, 3], dtype=np.uint32)
+    sampler = ag.NeighborSampler(g, cfg, features=feats)
+    for _ in range(2):                                     # the stream also runs on from call to call
+        sg = sampler.sample(seeds)
+        want = ago.sample_disjoint(oracle, seeds, off, dst, kw.get("subgraph_type", "directional"))
+        got = sg.raw_u32()
+        for k in ("nodes", "edge_src", "edge_dst", "src_local", "dst_local", "seed_locals", "num_sampled_nodes",
+                  "num_sampled_edges"):
+            assert np.array_equal(got[k], want[k]), k
+        assert np.array_equal(sg.batch, want["batch"])
+        assert np.array_equal(sg.edge_index_local, np.stack([want["dst_local"], want["src_local"]]).astype(np.int64))
+        assert np.array_equal(sg.seed_indices, want["seed_locals"].astype(np.int64))
+        assert np.array_equal(sg.x.cpu().numpy(), feats.get_batch(want["nodes"].astype(np.int64)))
+        assert got["nodes"][got["seed_locals"]].tolist() == seeds.tolist()
 
 
 def test_philox_mode_invariants_and_uniformity(ag, rmat12):
