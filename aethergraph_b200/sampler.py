@@ -76,8 +76,6 @@ class SamplingConfig:
         """Modes of the reference this GPU path does not implement."""
         if self.temporal_strategy is not None:
             return "temporal sampling"
-        if self.cumulative:
-            return "cumulative sampling"
         if self.max_degree is not None and self.weighted:
             return "max_degree with weighted sampling"
         if len(self.num_neighbors) > _lib.AG_MAX_HOPS:
@@ -524,6 +522,10 @@ def _check_config(graph: CsrGraph, config: SamplingConfig, *, pipelined: bool = 
     bad = config._unsupported()
     if bad is None and pipelined and config.disjoint:
         bad = "disjoint sampling in a loader (use NeighborSampler.sample; it runs one seed after the other)"
+    if bad is None and pipelined and config.cumulative:
+        bad = "cumulative sampling in a loader (use NeighborSampler.sample; it runs one launch chain per hop)"
+    if bad is None and config.cumulative and config.disjoint:
+        bad = "cumulative together with disjoint sampling"
     if bad:
         raise ValueError(f"{bad} is not supported by the GPU minibatch path")
     if config.weighted and not graph.has_weights:
@@ -541,6 +543,8 @@ class NeighborSampler:
         self.graph, self.config, self.features = graph, config, features
         seed = config.seed if config.seed is not None else secrets.randbits(64)
         self._handle = _Handle(graph, config, seed)
+        self._handle_seed = seed
+        self._cum_draws = 0   # cumulative mode carries the stream position itself
 
     def sample(self, seeds, input_times=None) -> SampledSubgraph:
         if input_times is not None:
@@ -548,7 +552,95 @@ class NeighborSampler:
         s = coerce_seeds(seeds, self.graph.num_nodes)
         if self.config.disjoint:
             return self._sample_disjoint(s)
+        if self.config.cumulative:
+            return self._sample_cumulative(s)
         return _submit_group(self._handle, [s], None, self.features).results()[0]
+
+    _WYRAND_STEP = 0xA0761D6478BD642F  # the generator's additive constant (internal/genstamp.rs:181-202)
+
+    def _sample_cumulative(self, seeds: np.ndarray) -> SampledSubgraph:
+        """Cumulative sampling (crates/aethergraph-core/src/loader/sampler.rs:834-837,
+        1250-1258, 1277-1285): every hop expands ALL nodes seen so far, and an edge that an
+        earlier hop emitted is refused (repeats within one hop pass).  Composed hop by hop from
+        the one-hop sampler: the frontier of hop h is the node list so far, which is exactly
+        the distinct-seed prefix of a one-hop batch seeded with it, so local ids agree from hop
+        to hop; the refused edges are filtered by edge id on the device.  The RNG stream is
+        carried by reseeding: draw d of a WyRand stream seeded s is draw 0 of one seeded
+        s + d * step."""
+        import torch
+
+        cfg, dev = self.config, self._handle.device
+        base = self._handle_seed
+        frontier, seed_locals = seeds, None
+        kept: list[dict] = []
+        nodes_t = None
+        emitted = torch.empty(0, dtype=torch.int64, device=dev)
+        nodes_per_hop, edges_per_hop = [], []
+        for hop, k in enumerate(cfg.num_neighbors):
+            h = self._hop_handle(k)
+            if cfg.rng_mode == "wyrand_exact":
+                h.reseed(base + self._cum_draws * self._WYRAND_STEP)
+            else:  # counter-based draws are keyed on (seed, vertex, slot): a key of its own per hop and call
+                h.reseed(int(_lib.lib().ag_batch_seed(base, self._cum_draws * 64 + hop)))
+            one = _submit_group(h, [np.ascontiguousarray(frontier, dtype=np.uint32)], None, None).results()[0]
+            self._cum_draws += int(one.draws) if cfg.rng_mode == "wyrand_exact" else 1
+            b, n, e = one._b, one._n, one._e
+            if hop == 0:
+                nodes_per_hop.append(int(one._nodes_per_hop[0]))
+                seed_locals = b.view(b.c.seed_locals, (len(seeds),), "<i4").clone()
+            nodes_per_hop.append(int(one._nodes_per_hop[1]))
+            nodes_t = b.view(b.c.nodes, (n,), "<i4").clone()
+            if e:
+                eid = b.view(b.c.edge_ids, (e,), "<i8")
+                keep = ~torch.isin(eid, emitted) if emitted.numel() else torch.ones(e, dtype=torch.bool, device=dev)
+                part = {name: b.view(getattr(b.c, name), (e,), "<i4")[keep].clone()
+                        for name in ("edge_src", "edge_dst", "src_local", "dst_local")}
+                part["edge_ids"] = eid[keep].clone()
+            else:
+                part = {name: torch.empty(0, dtype=torch.int32, device=dev)
+                        for name in ("edge_src", "edge_dst", "src_local", "dst_local")}
+                part["edge_ids"] = torch.empty(0, dtype=torch.int64, device=dev)
+            kept.append(part)
+            edges_per_hop.append(int(part["edge_ids"].numel()))
+            emitted = torch.unique(torch.cat([emitted, part["edge_ids"]]))
+            frontier = nodes_t.cpu().numpy().view(np.uint32)
+        n_tot, e_tot, S = int(nodes_t.numel()), sum(edges_per_hop), len(seeds)
+        dim = self.features.feature_dim if self.features is not None else None
+        out = _Buffers.alloc(dev, max(n_tot, 1), max(e_tot, 1), max(S, 1), cfg.track_edge_ids, dim)
+        c = out.c
+        out.view(c.nodes, (n_tot,), "<i4").copy_(nodes_t)
+        out.view(c.n_id, (n_tot,), "<i8").copy_(_u32_to_i64(nodes_t))
+        if S:
+            out.view(c.seed_locals, (S,), "<i4").copy_(seed_locals)
+            out.view(c.seed_index, (S,), "<i8").copy_(_u32_to_i64(seed_locals))
+        if e_tot:
+            for name in ("edge_src", "edge_dst", "src_local", "dst_local"):
+                out.view(getattr(c, name), (e_tot,), "<i4").copy_(torch.cat([p[name] for p in kept]))
+            if cfg.track_edge_ids:
+                out.view(c.edge_ids, (e_tot,), "<i8").copy_(torch.cat([p["edge_ids"] for p in kept]))
+            ei = out.view(c.edge_index_local, (2, e_tot), "<i8")
+            ei[0].copy_(_u32_to_i64(out.view(c.dst_local, (e_tot,), "<i4")))
+            ei[1].copy_(_u32_to_i64(out.view(c.src_local, (e_tot,), "<i4")))
+        if dim is not None and n_tot:
+            self.features.gather(out.view(c.n_id, (n_tot,), "<i8"), out=out.view(c.x, (n_tot, dim), "<f4"))
+        torch.cuda.current_stream(dev).synchronize()
+        counts = _lib.SampleCounts()
+        counts.num_nodes, counts.num_edges, counts.num_seeds, counts.num_hops = n_tot, e_tot, S, len(cfg.num_neighbors)
+        for i, v in enumerate(nodes_per_hop):
+            counts.nodes_per_hop[i] = v
+        for i, v in enumerate(edges_per_hop):
+            counts.edges_per_hop[i] = v
+        sg = SampledSubgraph(out, counts, seeds)
+        return apply_subgraph_type(self.graph, cfg.subgraph_type, sg)
+
+    def _hop_handle(self, fanout: int) -> "_Handle":
+        """A one-hop sampler with this fanout and the batch's flags, edge ids on."""
+        handles = self.__dict__.setdefault("_hop_handles", {})
+        if fanout not in handles:
+            one = SamplingConfig(num_neighbors=[fanout], replace=self.config.replace, weighted=self.config.weighted,
+                                 track_edge_ids=True, seed=0, rng_mode=self.config.rng_mode)
+            handles[fanout] = _Handle(self.graph, one, 0)
+        return handles[fanout]
 
     def _sample_disjoint(self, seeds: np.ndarray) -> SampledSubgraph:
         """Every seed sampled on its own, nothing shared between the blocks, the blocks

@@ -853,3 +853,42 @@ def sample_disjoint(sampler: "Sampler", seeds, offsets=None, edges=None, subgrap
     out.update(seed_locals=np.array(seed_locals, dtype=np.uint32), batch=np.array(batch, dtype=np.int64),
                num_sampled_nodes=nodes_per_hop, num_sampled_edges=edges_per_hop)
     return out
+
+
+WYRAND_STEP = 0xA0761D6478BD642F  # the generator's additive constant (internal/genstamp.rs:181-202)
+
+
+def sample_cumulative(offsets, edges, fanout, seeds, *, seed: int, weights=None, replace=False, weighted=False,
+                      start_draw: int = 0) -> dict:
+    """Cumulative sampling (crates/aethergraph-core/src/loader/sampler.rs:776-840 run_hops with
+    `cumulative`, :1250-1258 fresh_edge, :1277-1285 emit_edge): hop h expands every node seen so
+    far, in local-id order, and refuses an edge an earlier hop emitted.  Restated hop by hop on
+    the one-hop restatement: a sampler seeded `seed + d * WYRAND_STEP` starts at draw d of the
+    batch's stream.  Returns the arrays and `draws`, the stream position after the batch."""
+    seeds = np.asarray(seeds, dtype=np.uint32)
+    frontier, d = seeds, start_draw
+    emitted: set = set()
+    parts = {k: [] for k in ("edge_src", "edge_dst", "src_local", "dst_local", "edge_ids")}
+    nodes = seed_locals = None
+    nodes_per_hop, edges_per_hop = [], []
+    for hop, k in enumerate(fanout):
+        s = Sampler(offsets, edges, [k], weights=weights, replace=replace, weighted=weighted, track_edge_ids=True,
+                    seed=(seed + d * WYRAND_STEP) & (2**64 - 1))
+        one = s.sample(frontier)
+        d += one["draws"]
+        if hop == 0:
+            nodes_per_hop.append(int(one["num_sampled_nodes"][0]))
+            seed_locals = one["seed_locals"].copy()
+        nodes_per_hop.append(int(one["num_sampled_nodes"][1]))
+        eids = one["edge_ids"]
+        keep = np.array([int(e) not in emitted for e in eids], dtype=bool)
+        for name in parts:
+            parts[name].append(one[name][keep])
+        emitted.update(int(e) for e in eids[keep])
+        edges_per_hop.append(int(keep.sum()))
+        nodes = one["nodes"].copy()
+        frontier = nodes
+    out = {k: np.concatenate(v) for k, v in parts.items()}
+    out.update(nodes=nodes, seed_locals=seed_locals, num_sampled_nodes=np.array(nodes_per_hop, dtype=np.uint64),
+               num_sampled_edges=np.array(edges_per_hop, dtype=np.uint64), draws=d)
+    return out

@@ -90,7 +90,7 @@ def test_sampling_config_validation():
                                                                                           "directional")
     assert cfg._unsupported() is None
     assert ag.SamplingConfig([3], disjoint=True)._unsupported() is None     # the plain sampler runs it seed by seed
-    assert ag.SamplingConfig([3], cumulative=True)._unsupported() == "cumulative sampling"
+    assert ag.SamplingConfig([3], cumulative=True)._unsupported() is None   # the plain sampler runs it hop by hop
     assert ag.SamplingConfig([3], temporal_strategy="last")._unsupported() == "temporal sampling"
     assert ag.SamplingConfig([3], subgraph_type="induced")._unsupported() is None  # rewrites run on the GPU
     assert ag.SamplingConfig([3], subgraph_type="bidirectional")._unsupported() is None

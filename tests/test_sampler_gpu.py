@@ -156,13 +156,50 @@ def test_config_errors(ag, rmat12):
         ag.SamplingConfig(num_neighbors=[3, -1])
     with pytest.raises(ValueError, match="no edge weights"):
         ag.NeighborSampler(g, ag.SamplingConfig(num_neighbors=[3], weighted=True))
-    for kw in ({"cumulative": True}, {"temporal_strategy": "last"}):
+    for kw in ({"temporal_strategy": "last"}, {"cumulative": True, "disjoint": True}):
         with pytest.raises(ValueError, match="not supported"):
             ag.NeighborSampler(g, ag.SamplingConfig(num_neighbors=[3], **kw))
-    # disjoint runs seed by seed in the plain sampler only
+    # disjoint (seed by seed) and cumulative (hop by hop) run in the plain sampler only
     for make in (lambda c: ag.NeighborLoader(g, c), lambda c: ag.ParallelBatchSampler(g, c)):
         with pytest.raises(ValueError, match="disjoint sampling in a loader"):
             make(ag.SamplingConfig(num_neighbors=[3], disjoint=True, seed=1))
+        with pytest.raises(ValueError, match="cumulative sampling in a loader"):
+            make(ag.SamplingConfig(num_neighbors=[3], cumulative=True, seed=1))
+
+
+@pytest.mark.parametrize("kw", [{}, {"replace": True}, {"weighted": True}])
+def test_cumulative_sampling_matches_the_oracle(ag, kw):
+    """Every hop expands all nodes seen so far and an edge of an earlier hop is refused
+    (sampler.rs:834-837, 1250-1258, 1277-1285; test cumulative_mode_emits_each_edge_once
+    :3362-3390); the stream runs on from call to call."""
+    from oracle import ago
+
+    n, off, dst, w = rmat_csr(10, 8, seed=6, weighted=True)
+    g = ag.Graph.from_csr(off, dst, w)
+    feats = ag.FeatureStore.from_array(np.random.default_rng(0).standard_normal((n, 16)).astype(np.float32), "f32")
+    fan = [5, 3, 2]
+    sampler = ag.NeighborSampler(g, ag.SamplingConfig(num_neighbors=fan, seed=6, cumulative=True, **kw), features=feats)
+    okw = dict(kw, weights=w) if kw.get("weighted") else kw
+    draw = 0
+    for seeds in (np.array([0, 1, 2, 1], dtype=np.uint32), np.arange(40, 90, dtype=np.uint32), np.zeros(0, np.uint32)):
+        sg = sampler.sample(seeds)
+        want = ago.sample_cumulative(off, dst, fan, seeds, seed=6, start_draw=draw, **okw)
+        draw = want["draws"]
+        got = sg.raw_u32()
+        for k in ("nodes", "edge_src", "edge_dst", "src_local", "dst_local", "seed_locals", "edge_ids",
+                  "num_sampled_nodes", "num_sampled_edges"):
+            assert np.array_equal(got[k], want[k]), (k, len(seeds))
+        e, at, seen = got["edge_ids"], 0, set()
+        for c in got["num_sampled_edges"]:
+            hop = set(e[at:at + int(c)].tolist())
+            assert not (seen & hop), "a later hop re-emitted an edge"
+            seen |= hop
+            at += int(c)
+        if not kw.get("replace"):
+            assert len(set(e.tolist())) == len(e), "cumulative mode repeated an edge"
+        if len(seeds):
+            assert np.array_equal(sg.x.cpu().numpy(), feats.get_batch(want["nodes"].astype(np.int64)))
+            assert np.array_equal(sg.edge_index_local, np.stack([want["dst_local"], want["src_local"]]).astype(np.int64))
 
 
 @pytest.mark.parametrize("kw", [{}, {"replace": True}, {"weighted": True}, {"subgraph_type": "bidirectional"}])
