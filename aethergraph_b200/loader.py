@@ -109,7 +109,8 @@ class NeighborLoader:
         the same stream whatever W is."""
         import torch
 
-        _check_config(graph, config, pipelined=True)
+        composed = config.disjoint or config.cumulative
+        _check_config(graph, config, pipelined=not composed)
         if prefetch_depth < 1:
             raise ValueError("prefetch_depth must be >= 1")
         if sampler_threads < 1:
@@ -118,6 +119,22 @@ class NeighborLoader:
         self._depth, self._host_features = prefetch_depth, host_features
         self._seeded = config.seed is not None
         seed = config.seed if self._seeded else secrets.randbits(64)
+        self._composed = None
+        if composed:
+            # Disjoint and cumulative batches are compositions of the plain sampler's launch
+            # chains (one per seed / per hop): they are sampled when they are asked for, in
+            # submission order, batch `seq` from batch_seed(seed, base + stride * seq) like
+            # every other batch.  Same interface, no prefetch.
+            from .sampler import NeighborSampler
+
+            self._composed = NeighborSampler(graph, config, features=features)
+            self._composed_seed, self._seed_seq = seed, tuple(int(v) for v in seed_sequence)
+            self._h = None
+            self._dim = features.feature_dim if features is not None else None
+            self._pending: list = []
+            self._next_seq = self._served = 0
+            self._closed = False
+            return
         cfg = config._to_c(seed)
         self._h = C.c_void_p()
         _lib.check(_lib.lib().ag_loader_create(graph._h, features._h if features is not None else None,
@@ -166,6 +183,12 @@ class NeighborLoader:
     def submit(self, batch_idx: int, seeds) -> None:
         """Queue a batch.  `batch_idx` is echoed back by `next_batch()`; any value is accepted."""
         s = coerce_seeds(seeds, self.graph.num_nodes)
+        if self._composed is not None:
+            if self._closed:
+                raise RuntimeError("loader is shut down")
+            self._pending.append((int(batch_idx), self._next_seq, s))
+            self._next_seq += 1
+            return
         with self._lock:
             # The C call blocks while the work queue is full; the lock keeps the
             # Python-side sequence counter in step with the library's.
@@ -186,6 +209,10 @@ class NeighborLoader:
         n = len(seeds)
         if n == 0:
             return
+        if self._composed is not None:
+            for i, s in enumerate(seeds):
+                self.submit(i if batch_indices is None else int(batch_indices[i]), s)
+            return
         idx = (C.c_int64 * n)(*(range(n) if batch_indices is None else [int(i) for i in batch_indices]))
         ptrs = (C.c_void_p * n)(*[s.ctypes.data if len(s) else None for s in seeds])
         lens = (C.c_uint64 * n)(*[len(s) for s in seeds])
@@ -203,6 +230,17 @@ class NeighborLoader:
 
     # -- consumer side -----------------------------------------------------
     def _take(self, blocking: bool):
+        if self._composed is not None:
+            if self._closed or not self._pending:
+                if self._closed or not blocking:
+                    return None
+                raise TimeoutError("no batch was submitted")
+            idx, seq, seeds = self._pending.pop(0)
+            base, stride = self._seed_seq
+            if self._seeded:
+                self._composed.reseed(_lib.lib().ag_batch_seed(self._composed_seed, base + stride * seq))
+            self._served += 1
+            return idx, self._composed.sample(seeds)
         if not self._fetched:
             if self._closed:
                 return None
@@ -258,10 +296,17 @@ class NeighborLoader:
 
     def stats(self) -> PrefetchStats:
         s = _lib.LoaderStats()
+        if self._composed is not None:
+            s.total = s.misses = self._served       # nothing is sampled ahead of time
+            s.submitted = self._next_seq
+            return PrefetchStats(s)
         _lib.check(_lib.lib().ag_loader_stats_get(self._h, C.byref(s)))
         return PrefetchStats(s)
 
     def shutdown(self) -> None:
+        if self._composed is not None:
+            self._closed = True
+            return
         if self._h:
             _lib.lib().ag_loader_shutdown(self._h)
         self._closed = True

@@ -521,9 +521,9 @@ def _check_config(graph: CsrGraph, config: SamplingConfig, *, pipelined: bool = 
         raise TypeError("config must be a SamplingConfig")
     bad = config._unsupported()
     if bad is None and pipelined and config.disjoint:
-        bad = "disjoint sampling in a loader (use NeighborSampler.sample; it runs one seed after the other)"
+        bad = "disjoint sampling in a parallel batch sampler (use NeighborSampler or NeighborLoader; it runs one seed after the other)"
     if bad is None and pipelined and config.cumulative:
-        bad = "cumulative sampling in a loader (use NeighborSampler.sample; it runs one launch chain per hop)"
+        bad = "cumulative sampling in a parallel batch sampler (use NeighborSampler or NeighborLoader; it runs one launch chain per hop)"
     if bad is None and config.cumulative and config.disjoint:
         bad = "cumulative together with disjoint sampling"
     if bad:
@@ -545,6 +545,12 @@ class NeighborSampler:
         self._handle = _Handle(graph, config, seed)
         self._handle_seed = seed
         self._cum_draws = 0   # cumulative mode carries the stream position itself
+
+    def reseed(self, seed: int) -> None:
+        """Restart the RNG stream at draw 0 of `seed` (NeighborSampler::reseed, sampler.rs:509-511)."""
+        seed = int(seed) & (2**64 - 1)
+        self._handle.reseed(seed)
+        self._handle_seed, self._cum_draws = seed, 0
 
     def sample(self, seeds, input_times=None) -> SampledSubgraph:
         if input_times is not None:

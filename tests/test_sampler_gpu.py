@@ -159,12 +159,42 @@ def test_config_errors(ag, rmat12):
     for kw in ({"temporal_strategy": "last"}, {"cumulative": True, "disjoint": True}):
         with pytest.raises(ValueError, match="not supported"):
             ag.NeighborSampler(g, ag.SamplingConfig(num_neighbors=[3], **kw))
-    # disjoint (seed by seed) and cumulative (hop by hop) run in the plain sampler only
-    for make in (lambda c: ag.NeighborLoader(g, c), lambda c: ag.ParallelBatchSampler(g, c)):
-        with pytest.raises(ValueError, match="disjoint sampling in a loader"):
-            make(ag.SamplingConfig(num_neighbors=[3], disjoint=True, seed=1))
-        with pytest.raises(ValueError, match="cumulative sampling in a loader"):
-            make(ag.SamplingConfig(num_neighbors=[3], cumulative=True, seed=1))
+    # disjoint (seed by seed) and cumulative (hop by hop) are compositions of launch chains: the plain
+    # sampler and the loader run them, the parallel batch sampler (groups of batches per chain) does not
+    with pytest.raises(ValueError, match="disjoint sampling in a parallel batch sampler"):
+        ag.ParallelBatchSampler(g, ag.SamplingConfig(num_neighbors=[3], disjoint=True, seed=1))
+    with pytest.raises(ValueError, match="cumulative sampling in a parallel batch sampler"):
+        ag.ParallelBatchSampler(g, ag.SamplingConfig(num_neighbors=[3], cumulative=True, seed=1))
+
+
+def test_loader_runs_disjoint_and_cumulative_batches_in_order(ag):
+    """Behind the loader interface both modes are sampled on demand, batch `seq` from
+    batch_seed(seed, seq) like every other batch (prefetch.rs:926-930)."""
+    from oracle import ago
+
+    n, off, dst, _ = rmat_csr(10, 8, seed=6)
+    g = ag.Graph.from_csr(off, dst)
+    feats = ag.FeatureStore.from_array(np.random.default_rng(0).standard_normal((n, 8)).astype(np.float32), "f32")
+    rng = np.random.default_rng(2)
+    batches = [rng.integers(0, n, 12).astype(np.uint32) for _ in range(4)]
+    with ag.NeighborLoader(g, ag.SamplingConfig(num_neighbors=[4, 2], seed=3, cumulative=True), features=feats) as ld:
+        ld.submit_epoch(batches, [10, 11, 12, 13])
+        for i, b in enumerate(batches):
+            idx, sg, x = ld.next_batch()
+            want = ago.sample_cumulative(off, dst, [4, 2], b, seed=ago.batch_seed(3, i))
+            assert idx == 10 + i and np.array_equal(sg.raw_u32()["nodes"], want["nodes"])
+            assert np.array_equal(sg.raw_u32()["edge_ids"], want["edge_ids"])
+            assert np.array_equal(x.cpu().numpy(), feats.get_batch(want["nodes"].astype(np.int64)))
+        assert ld.stats().total == 4 and ld.try_next() is None
+    with ag.NeighborLoader(g, ag.SamplingConfig(num_neighbors=[4, 2], seed=3, disjoint=True)) as ld:
+        for i, b in enumerate(batches):
+            ld.submit(i, b)
+        for i, b in enumerate(batches):
+            idx, sg, x = ld.next_batch()
+            oracle = ago.Sampler(off, dst, [4, 2], seed=ago.batch_seed(3, i))
+            want = ago.sample_disjoint(oracle, b)
+            assert idx == i and x is None and np.array_equal(sg.raw_u32()["nodes"], want["nodes"])
+            assert np.array_equal(sg.batch, want["batch"])
 
 
 @pytest.mark.parametrize("kw", [{}, {"replace": True}, {"weighted": True}])
