@@ -55,7 +55,8 @@ def open_sharded_features(local):
     """Every rank passes the FeatureStore holding ITS vertex range
     (`shard_range(rank, num_nodes, world)`); returns a store over all rows whose
     remote rows are read from the owning rank's GPU memory over NVLink.  The only
-    communication is the one-off exchange of 64-byte IPC handles."""
+    communication is the one-off exchange of the 128-byte shard handles (a shard the library
+    allocated is then fetched as a file descriptor from its owner and mapped with 2 MB pages)."""
     import torch.distributed as dist
 
     from .features import FeatureStore

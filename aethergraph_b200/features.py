@@ -126,7 +126,7 @@ class FeatureStore:
         return FeatureStore(out.value)
 
     def ipc_handle(self) -> bytes:
-        """64-byte CUDA IPC handle of this shard's rows, for the other ranks of the node."""
+        """The handle (AG_IPC_HANDLE_BYTES) the other ranks of the node need to map this shard's rows."""
         buf = C.create_string_buffer(_lib.AG_IPC_HANDLE_BYTES)
         _lib.check(_lib.lib().ag_features_ipc_export(self._h, buf))
         return buf.raw
