@@ -182,8 +182,20 @@ int32_t alloc_feature_payload(int device, size_t bytes, uint8_t **ptr, PeerBlock
         AG_CUDA(cudaMalloc(ptr, bytes));
         return AG_OK;
     }
-    AG_TRY(peer_block_alloc(device, bytes, block));
-    *ptr = (uint8_t *)peer_block_ptr(*block);
+    if (peer_block_alloc(device, bytes, block) == AG_OK) {
+        *ptr = (uint8_t *)peer_block_ptr(*block);
+        return AG_OK;
+    }
+    // A driver or a container that does not offer shareable allocations (no virtual memory
+    // management, no file-descriptor handles): a plain allocation still works in every
+    // respect except that peers have to map it through a legacy IPC handle.  Said once.
+    static std::once_flag warned;
+    std::call_once(warned, [] {
+        fprintf(stderr, "aethergpu: shareable device allocations are unavailable (%s); feature rows fall back to "
+                        "cudaMalloc, and shards mapped by other processes to legacy CUDA IPC handles\n", ag_last_error());
+    });
+    *block = nullptr;
+    AG_CUDA(cudaMalloc(ptr, bytes));
     return AG_OK;
 }
 
