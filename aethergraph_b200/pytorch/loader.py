@@ -294,6 +294,8 @@ class NeighborLoader:
                     n_id=sg.nodes_t, batch_size=int(seed_index.shape[0]), input_id=input_id, seed_index=seed_index,
                     num_nodes=sg.num_nodes, num_sampled_nodes=sg.num_sampled_nodes_per_hop,
                     num_sampled_edges=sg.num_sampled_edges_per_hop)
+                if sg.batch is not None:  # disjoint batches: which seed's block a node belongs to (loader.py:985-991)
+                    data.batch = torch.from_numpy(sg.batch).to(dev, non_blocking=True)
                 if self._out_device is not None and torch.device(self._out_device).type != "cuda":
                     data = data.to(self._out_device)
                 if self.transform is not None:

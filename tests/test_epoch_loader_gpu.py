@@ -185,3 +185,30 @@ def test_hetero_epoch_loader_matches_the_oracle():
         HeteroNeighborLoader(g, fan)
     with pytest.raises(ValueError, match="same number of hops"):
         HeteroNeighborLoader(g, {ets[0]: [1], ets[1]: [1, 2]}, input_nodes=("user", None))
+
+
+def test_disjoint_epoch_batches_carry_the_batch_vector():
+    """`disjoint=True`: every seed its own block, `data.batch` names each node's seed
+    (python/aethergraph/pytorch/loader.py:985-991); sampled from batch_seed(epoch seed, b)."""
+    import aethergraph_b200 as ag
+    from aethergraph_b200.pytorch import NeighborLoader
+    from aethergraph_b200.pytorch.loader import epoch_sampling_seed
+    from oracle import ago
+
+    n, off, dst, g, feats = _graph_and_features(ag, scale=9, dim=8)
+    ids = np.arange(0, 40)
+    loader = NeighborLoader(g, [3, 2], batch_size=16, shuffle=False, seed=5, features=feats, input_nodes=ids,
+                            disjoint=True)
+    es = epoch_sampling_seed(np.random.SeedSequence(5))
+    seen = 0
+    for b, data in enumerate(loader):
+        seeds = ids[b * 16:(b + 1) * 16]
+        want = ago.sample_disjoint(ago.Sampler(off, dst, [3, 2], seed=ago.batch_seed(es, b)), seeds)
+        n_id = data.n_id.cpu().numpy()
+        assert np.array_equal(n_id, want["nodes"].astype(np.int64))
+        assert np.array_equal(data.batch.cpu().numpy(), want["batch"])
+        assert np.array_equal(data.seed_index.cpu().numpy(), want["seed_locals"].astype(np.int64))
+        assert np.array_equal(data.x.cpu().numpy().view(np.uint32), feats[n_id].view(np.uint32))
+        assert np.array_equal(n_id[data.seed_index.cpu().numpy()], seeds)
+        seen += 1
+    assert seen == 3
