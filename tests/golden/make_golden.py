@@ -7,6 +7,10 @@
   description (crates/aethergraph-core/src/internal/mmap.rs:114-121; golden layout
   crates/aethergraph-core/tests/golden_format.rs:22-87) with checksum 0, and compared
   byte for byte with the reference's test_data/simple_graph.bin when that tree is present.
+* simple_graph_aeth_v2.bin — the same graph in the compressed version-2 format (Elias-Fano
+  offsets, StreamVByte edge deltas, payload checksum), written by the numpy restatement of
+  the reference's codecs (crates/aethergraph-core/src/internal/compressed_graph.rs:39-88,
+  internal/succinct.rs:52-92,198-214,397-420,486-500).
 * golden_samples.npz — sampled subgraphs and gathered rows the CPU oracle produces for
   fixed seeds on a small seeded R-MAT graph.  The reference holds no known-answer sample
   vectors, so these pin this repository's oracle and CUDA path against drift.
@@ -77,6 +81,7 @@ def main():
         assert open(ref, "rb").read() == blob, "format restatement differs from the reference's fixture"
         print("simple_graph: identical to the reference's test_data/simple_graph.bin")
     open(os.path.join(HERE, "simple_graph_aeth_v1.bin"), "wb").write(blob)
+    open(os.path.join(HERE, "simple_graph_aeth_v2.bin"), "wb").write(ago.compressed_graph_bytes(off, edges))
     np.savez_compressed(os.path.join(HERE, "golden_samples.npz"), **golden_cases())
     print("wrote", os.listdir(HERE))
 

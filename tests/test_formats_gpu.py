@@ -323,3 +323,18 @@ def _write(tmp_path, name, data):
     p = tmp_path / name
     p.write_bytes(bytes(data))
     return p
+
+
+def test_load_the_compressed_golden_of_the_reference_fixture(ag, tmp_path):
+    """tests/golden/simple_graph_aeth_v2.bin decodes to the fixture graph and is written back
+    byte for byte (crates/aethergraph-core/tests/golden_format.rs:22-87 for the graph itself)."""
+    gold = os.path.join(GOLDEN, "simple_graph_aeth_v2.bin")
+    g = ag.Graph.load(gold)
+    assert (g.num_nodes, g.num_edges, g.has_weights) == (5, 6, False)
+    assert [g.neighbors(v).tolist() for v in range(5)] == [[1, 2], [2, 3], [3], [4], []]
+    out = tmp_path / "again.bin"
+    g.save(out, compressed=True)
+    assert out.read_bytes() == open(gold, "rb").read()
+    flat = tmp_path / "flat.bin"
+    g.save(flat)
+    assert flat.read_bytes()[32:] == open(os.path.join(GOLDEN, "simple_graph_aeth_v1.bin"), "rb").read()[32:]

@@ -1,6 +1,7 @@
 """CPU tests: the oracle against every known answer and invariant the reference's
 own tests hold for the minibatch path (file:line cites are the reference's).
 No GPU needed."""
+import os
 import zlib
 
 import numpy as np
@@ -487,3 +488,27 @@ def test_compressed_graph_file_layout_and_round_trip():
     assert back[0] == n and np.array_equal(back[1], off) and np.array_equal(back[2], order) and np.array_equal(back[3], w)
     flat = (n + 1) * 8 + order.size * 4
     assert len(ago.compressed_graph_bytes(off, order)) < flat          # "compresses below flat"
+
+
+def test_compressed_golden_file_of_the_reference_fixture_graph():
+    """tests/golden/simple_graph_aeth_v2.bin: header fields, section layout byte by byte, and the
+    decoded CSR of the reference's fixture graph (test_data/simple_graph.txt)."""
+    import struct
+
+    from oracle import ago
+
+    raw = open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "simple_graph_aeth_v2.bin"), "rb").read()
+    magic, version, n, e, has_w, crc = struct.unpack_from("<IIQQII", raw, 0)
+    assert (magic, version, n, e, has_w) == (0x41455448, 2, 5, 6, 0) and crc == zlib.crc32(raw[32:])
+    # offsets [0,2,4,5,6,6]: len 6, universe 6, low_bits floor(log2(6/6)) = 0, no low words, one high word
+    # with a set bit at value + index: 0, 3, 6, 8, 10, 11
+    assert struct.unpack_from("<QQIQ", raw, 32) == (6, 6, 0, 0)
+    assert struct.unpack_from("<QQ", raw, 32 + 28) == (1, sum(1 << b for b in (0, 3, 6, 8, 10, 11)))
+    # edges [1,2,2,3,3,4]: first 1, deltas 1,0,1,0,1 of one byte each -> two control bytes of zeros
+    at = 32 + 28 + 16
+    assert struct.unpack_from("<QIQ", raw, at) == (6, 1, 2)
+    assert raw[at + 20:at + 22] == bytes(2) and struct.unpack_from("<Q", raw, at + 22) == (5,)
+    assert raw[at + 30:] == bytes([1, 0, 1, 0, 1])
+    back = ago.read_compressed_graph(raw)
+    assert back[0] == 5 and back[1].tolist() == [0, 2, 4, 5, 6, 6] and back[2].tolist() == [1, 2, 2, 3, 3, 4]
+    assert ago.compressed_graph_bytes(back[1], back[2]) == raw
